@@ -1,0 +1,439 @@
+// Neighbour list + radial / angular descriptors (op ComputeDescriptorsLight).
+//
+// Follows the arithmetic of STAF/src/descriptor_builder/celle_gpu.cu.cc:11-260 and
+// STAF/src/descriptor_builder/reforce.cu.cc:17-236 of the reference, with a different
+// execution plan: no host synchronisation (the inverse box and the cell grid are computed on
+// the device), all frames in one launch, one warp per central atom that discovers, sorts and
+// describes its own neighbour row in shared memory, and a CSR cell list whose slot order is
+// made deterministic (ascending atom index) so that ties in dist2 resolve reproducibly.
+//
+// This translation unit is compiled with -fmad=false: positions, squared distances and the
+// cutoff tests must round in expression order, because neighbour sets and neighbour ORDER
+// are compared bit-exactly.
+#include "common.cuh"
+
+namespace stafb {
+
+template <class T>
+__global__ void k_frame_setup(const T* __restrict__ box, int nf, int N, T cutoff, int cell_cap,
+                              FrameGeom<T>* __restrict__ fg, int* __restrict__ status) {
+  int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nf) return;
+  FrameGeom<T> g;
+  const T* B = box + 6 * b;
+  for (int q = 0; q < 6; q++) g.box[q] = B[q];
+  if (!(B[0] != T(0) && B[3] != T(0) && B[5] != T(0))) {
+    set_status(status, STAFB_ERR_BAD_BOX);
+    for (int q = 0; q < 6; q++) g.inv[q] = T(0);
+    g.nx = g.ny = g.nz = 3;
+    g.ncell = 27;
+    g.sx = g.sy = g.sz = T(1) / T(3);
+    fg[b] = g;
+    return;
+  }
+  // inverse of the upper-triangular box: descriptor_builder/reforce.cc:283-299
+  g.inv[0] = T(1.) / B[0];
+  g.inv[1] = -B[1] / (B[0] * B[3]);
+  g.inv[2] = (B[1] * B[4]) / (B[0] * B[3] * B[5]) - B[2] / (B[0] * B[5]);
+  g.inv[3] = T(1.) / B[3];
+  g.inv[4] = -B[4] / (B[3] * B[5]);
+  g.inv[5] = T(1.) / B[5];
+  // cell counts: celle_gpu.cu.cc:208-228
+  T volume = B[0] * B[3] * B[5];
+  int cx = (int)(volume / (r_sqrt(B[3] * B[3] * B[5] * B[5] + B[5] * B[5] * B[1] * B[1] +
+                                  B[3] * B[3] * B[2] * B[2] + B[4] * B[4] * B[1] * B[1]) *
+                           cutoff));
+  int cy = (int)(volume / (B[0] * r_sqrt(B[5] * B[5] + B[4] * B[4]) * cutoff));
+  int cz = (int)(volume / (B[0] * B[3] * cutoff));
+  while ((cx * cy * cz > 27) && (cx * cy * cz > N)) {
+    if (cx > cy) {
+      if (cx > cz) cx--; else cz--;
+    } else {
+      if (cy > cz) cy--; else cz--;
+    }
+  }
+  if (cx < 3) cx = 3;
+  if (cy < 3) cy = 3;
+  if (cz < 3) cz = 3;
+  if ((long long)cx * cy * cz > cell_cap) {
+    set_status(status, STAFB_ERR_CAPACITY);
+    cx = cy = cz = 3;
+  }
+  g.nx = cx; g.ny = cy; g.nz = cz;
+  g.ncell = cx * cy * cz;
+  g.sx = T(1.) / (T)cx;
+  g.sy = T(1.) / (T)cy;
+  g.sz = T(1.) / (T)cz;
+  fg[b] = g;
+}
+
+// Fractional coordinates (celle_gpu.cu.cc:11-28) and cell of every atom (celle_gpu.cu.cc:176-201).
+template <class T>
+__global__ void k_bin(const T* __restrict__ pos, int nf, int N, const FrameGeom<T>* __restrict__ fg,
+                      T* __restrict__ frac, int* __restrict__ cell_of, int* __restrict__ cell_count, int cell_cap) {
+  int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= nf * N) return;
+  int b = t / N;
+  const FrameGeom<T>& g = fg[b];
+  T px = pos[(size_t)t * 3 + 0], py = pos[(size_t)t * 3 + 1], pz = pos[(size_t)t * 3 + 2];
+  T fx = (g.inv[0] * px + g.inv[1] * py + g.inv[2] * pz);
+  T fy = (g.inv[3] * py + g.inv[4] * pz);
+  T fz = (g.inv[5] * pz);
+  frac[(size_t)t * 3 + 0] = fx;
+  frac[(size_t)t * 3 + 1] = fy;
+  frac[(size_t)t * 3 + 2] = fz;
+  int cx = (int)r_floor(fx / g.sx);
+  cx = cx % g.nx;
+  if (cx < 0) cx += g.nx;
+  int cy = (int)r_floor(fy / g.sy);
+  cy = cy % g.ny;
+  if (cy < 0) cy += g.ny;
+  int cz = (int)r_floor(fz / g.sz);
+  cz = cz % g.nz;
+  if (cz < 0) cz += g.nz;
+  int c = cx + cy * g.nx + cz * (g.nx * g.ny);
+  cell_of[t] = c;
+  atomicAdd(cell_count + (size_t)b * cell_cap + c, 1);
+}
+
+// Exclusive scan of the per-cell counts of one frame (one block per frame).
+template <class T>
+__global__ void k_scan(const FrameGeom<T>* __restrict__ fg, const int* __restrict__ cell_count,
+                       int* __restrict__ cell_start, int* __restrict__ cell_cursor, int cell_cap, int mpc,
+                       int* __restrict__ status) {
+  __shared__ int part[32];
+  __shared__ int carry;
+  const int b = blockIdx.x, ncell = fg[b].ncell;
+  const int* cnt = cell_count + (size_t)b * cell_cap;
+  int* st = cell_start + (size_t)b * (cell_cap + 1);
+  int* cur = cell_cursor + (size_t)b * cell_cap;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int base = 0; base < ncell; base += blockDim.x) {
+    int c = base + threadIdx.x;
+    int v = (c < ncell) ? cnt[c] : 0;
+    if (v > mpc) set_status(status, STAFB_ERR_CELL_OVERFLOW);
+    int x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) part[w] = x;
+    __syncthreads();
+    int off = carry;
+    for (int q = 0; q < w; q++) off += part[q];
+    if (c < ncell) {
+      st[c] = off + x - v;
+      cur[c] = 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int tot = 0;
+      for (int q = 0; q < nw; q++) tot += part[q];
+      carry += tot;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) st[ncell] = carry;
+}
+
+__global__ void k_fill(int nf, int N, const int* __restrict__ cell_of, const int* __restrict__ cell_start,
+                       int* __restrict__ cell_cursor, int* __restrict__ cells_raw, int cell_cap) {
+  int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= nf * N) return;
+  int b = t / N, i = t - b * N;
+  int c = cell_of[t];
+  int slot = atomicAdd(cell_cursor + (size_t)b * cell_cap + c, 1);
+  cells_raw[(size_t)b * N + cell_start[(size_t)b * (cell_cap + 1) + c] + slot] = i;
+}
+
+// Orders every cell's members by atom index (one warp per cell): the reference's slot order
+// is the atomicAdd arrival order (celle_gpu.cu.cc:197-200), restated as ascending index.
+template <class T>
+__global__ void k_sort_cells(const FrameGeom<T>* __restrict__ fg, int nf, int N, const int* __restrict__ cell_start,
+                             const int* __restrict__ cells_raw, int* __restrict__ cells_sorted, int cell_cap) {
+  int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  int b = gw / cell_cap, c = gw - b * cell_cap;
+  if (b >= nf || c >= fg[b].ncell) return;
+  const int* st = cell_start + (size_t)b * (cell_cap + 1);
+  int s0 = st[c], s1 = st[c + 1];
+  const int* src = cells_raw + (size_t)b * N;
+  int* dst = cells_sorted + (size_t)b * N;
+  for (int e = s0 + lane; e < s1; e += 32) {
+    int me = src[e], r = 0;
+    for (int f = s0; f < s1; f++) r += (src[f] < me);
+    dst[s0 + r] = me;
+  }
+}
+
+template <class T>
+__device__ __forceinline__ void mic_vec(const FrameGeom<T>& g, T ax, T ay, T az, T bx, T by, T bz, T& dx, T& dy,
+                                        T& dz) {
+  // a - b in fractional space, nearest image, back to Cartesian (celle_gpu.cu.cc:96-109)
+  T ox = ax - bx, oy = ay - by, oz = az - bz;
+  ox -= r_rint(ox);
+  oy -= r_rint(oy);
+  oz -= r_rint(oz);
+  dx = g.box[0] * ox + g.box[1] * oy + g.box[2] * oz;
+  dy = g.box[3] * oy + g.box[4] * oz;
+  dz = g.box[5] * oz;
+}
+
+// One warp per central atom: candidate discovery over the 27 neighbour cells in the
+// reference's visiting order (x outer, y, z inner, offsets -1,0,1: celle_gpu.cu.cc:61-82),
+// stable sort by dist2 (celle_gpu.cu.cc:128-152), then the radial descriptor row
+// (reforce.cu.cc:17-110).
+template <class T, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
+    k_nl_radial(int nf, int N, int nr, CoreCoef<T> cc, const FrameGeom<T>* __restrict__ fg,
+                const T* __restrict__ frac, const int* __restrict__ cell_of, const int* __restrict__ cell_start,
+                const int* __restrict__ cells_sorted, int cell_cap, T* __restrict__ raddescr,
+                T* __restrict__ des3bsupp, int* __restrict__ intmap2b, T* __restrict__ der2b,
+                T* __restrict__ der3bsupp, int* __restrict__ numtriplet, T* __restrict__ geom, int na,
+                int* __restrict__ status) {
+  extern __shared__ unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gi = blockIdx.x * WARPS + warp;
+  if (gi >= nf * N) return;
+  const int b = gi / N, i = gi - b * N;
+  // per-warp rows: d2a[nr] d2b[nr] (T) then ja[nr] jb[nr] (int)
+  T* d2a = reinterpret_cast<T*>(smem_raw) + (size_t)warp * 2 * nr;
+  T* d2b = d2a + nr;
+  int* ja = reinterpret_cast<int*>(reinterpret_cast<T*>(smem_raw) + (size_t)WARPS * 2 * nr) + (size_t)warp * 2 * nr;
+  int* jb = ja + nr;
+
+  const FrameGeom<T> g = fg[b];
+  const T* fr = frac + (size_t)b * N * 3;
+  const T pix = fr[3 * i], piy = fr[3 * i + 1], piz = fr[3 * i + 2];
+  const int ci = cell_of[gi];
+  const int cz = ci / (g.nx * g.ny), rem = ci - cz * (g.nx * g.ny), cy = rem / g.nx, cx = rem - cy * g.nx;
+  const int* cst = cell_start + (size_t)b * (cell_cap + 1);
+  const int* cl = cells_sorted + (size_t)b * N;
+  const T cut2 = cc.Rc * cc.Rc;
+  const unsigned lt = (1u << lane) - 1u;
+  int count = 0;
+  for (int di = -1; di < 2; di++) {
+    int bi = cx + di;
+    if (bi < 0) bi = g.nx - 1; else if (bi == g.nx) bi = 0;
+    for (int dj = -1; dj < 2; dj++) {
+      int bj = cy + dj;
+      if (bj < 0) bj = g.ny - 1; else if (bj == g.ny) bj = 0;
+      for (int dk = -1; dk < 2; dk++) {
+        int bk = cz + dk;
+        if (bk < 0) bk = g.nz - 1; else if (bk == g.nz) bk = 0;
+        const int c = bi + bj * g.nx + bk * g.nx * g.ny;
+        const int s0 = cst[c], s1 = cst[c + 1];
+        for (int e0 = s0; e0 < s1; e0 += 32) {
+          const int e = e0 + lane;
+          bool pred = false;
+          int j = -1;
+          T dist2 = T(0);
+          if (e < s1) {
+            j = cl[e];
+            T dx, dy, dz;
+            mic_vec(g, fr[3 * j], fr[3 * j + 1], fr[3 * j + 2], pix, piy, piz, dx, dy, dz);
+            dist2 = dx * dx + dy * dy + dz * dz;
+            pred = (dist2 < cut2) && (j != i);
+          }
+          const unsigned bal = __ballot_sync(0xffffffffu, pred);
+          const int slot = count + __popc(bal & lt);
+          if (pred && slot < nr) {
+            d2a[slot] = dist2;
+            ja[slot] = j;
+          }
+          count += __popc(bal);
+        }
+      }
+    }
+  }
+  if (count > nr && lane == 0) set_status(status, STAFB_ERR_RADIAL_OVERFLOW);
+  const int n = count < nr ? count : nr;
+  __syncwarp();
+  // stable rank sort: position = #{f : d2[f] < d2[e] or (equal and f < e)}
+  for (int e = lane; e < n; e += 32) {
+    const T key = d2a[e];
+    int r = 0;
+    for (int f = 0; f < n; f++) {
+      const T kf = d2a[f];
+      r += (kf < key) || (kf == key && f < e);
+    }
+    d2b[r] = key;
+    jb[r] = ja[e];
+  }
+  __syncwarp();
+  const T PI = PIc<T>();
+  const size_t base = (size_t)gi;
+  int nang = 0;
+  for (int k = lane; k < nr; k += 32) {
+    T rd = T(0), d3 = T(0), g2x = T(0), g2y = T(0), g2z = T(0), g3x = T(0), g3y = T(0), g3z = T(0);
+    T vx = T(0), vy = T(0), vz = T(0), dn = T(0);
+    int j = 0;
+    if (k < n) {
+      j = jb[k];
+      mic_vec(g, pix, piy, piz, fr[3 * j], fr[3 * j + 1], fr[3 * j + 2], vx, vy, vz);
+      dn = r_sqrt(vx * vx + vy * vy + vz * vz);
+      if (dn < cc.Ra) {
+        nang++;
+        d3 = T(0.5) * (r_cos(PI * dn / cc.Ra) + T(1));
+        const T pre = T(-0.5) * r_sin(PI * dn / cc.Ra) * PI / cc.Ra;
+        g3x = pre * vx / dn;
+        g3y = pre * vy / dn;
+        g3z = pre * vz / dn;
+      }
+      if (dn < cc.Rs) {
+        rd = cc.A / r_pow(dn, cc.pa) + cc.B / r_pow(dn, cc.pb) + cc.C;
+        const T pre = (-cc.pa * cc.A / r_pow(dn, cc.pa + T(1.)) - cc.pb * cc.B / r_pow(dn, cc.pb + T(1.)));
+        g2x = pre * vx / dn;
+        g2y = pre * vy / dn;
+        g2z = pre * vz / dn;
+      } else {
+        rd = T(0.5) * (r_cos(PI * dn / cc.Rc) + T(1));
+        const T pre = T(-0.5) * r_sin(PI * dn / cc.Rc) * PI / cc.Rc;
+        g2x = pre * vx / dn;
+        g2y = pre * vy / dn;
+        g2z = pre * vz / dn;
+      }
+    }
+    raddescr[base * nr + k] = rd;
+    des3bsupp[base * nr + k] = d3;
+    der2b[(base * 3 + 0) * nr + k] = g2x;
+    der2b[(base * 3 + 1) * nr + k] = g2y;
+    der2b[(base * 3 + 2) * nr + k] = g2z;
+    der3bsupp[(base * 3 + 0) * nr + k] = g3x;
+    der3bsupp[(base * 3 + 1) * nr + k] = g3y;
+    der3bsupp[(base * 3 + 2) * nr + k] = g3z;
+    intmap2b[base * (nr + 1) + 1 + k] = (k < n) ? j : 0;
+    if (geom) {
+      typename Vec4<T>::type q;
+      q.x = vx; q.y = vy; q.z = vz; q.w = dn;
+      reinterpret_cast<typename Vec4<T>::type*>(geom)[base * nr + k] = q;
+    }
+  }
+  nang = warp_sum(nang);
+  if (lane == 0) {
+    intmap2b[base * (nr + 1)] = n;
+    numtriplet[base] = nang;
+    if ((long long)nang * (nang - 1) / 2 > na) set_status(status, STAFB_ERR_ANGULAR_OVERFLOW);
+  }
+}
+
+// Angular descriptor rows (reforce.cu.cc:112-236): one block per central atom; the sorted
+// neighbour geometry is staged in shared memory and the block writes the three angular
+// tensors with consecutive threads on consecutive triplet slots.
+template <class T, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+    k_angular(int nf, int N, int nr, int na, T Ra, const T* __restrict__ geom, const int* __restrict__ intmap2b,
+              const int* __restrict__ numtriplet, T* __restrict__ angdescr, int* __restrict__ intmap3b,
+              T* __restrict__ der3b) {
+  extern __shared__ unsigned char smem_raw[];
+  typedef typename Vec4<T>::type T4;
+  typedef typename Vec2<T>::type T2;
+  T4* v = reinterpret_cast<T4*>(smem_raw);             // [nr] vector + norm
+  T* fc = reinterpret_cast<T*>(v + nr);                // [nr] cutoff
+  T* dcp = fc + nr;                                    // [nr] dc prefactor
+  int* ids = reinterpret_cast<int*>(dcp + nr);         // [nr]
+  const size_t base = blockIdx.x;
+  int m = numtriplet[base];
+  if (m > nr) m = nr;
+  const T PI = PIc<T>();
+  for (int k = threadIdx.x; k < m; k += THREADS) {
+    T4 q = reinterpret_cast<const T4*>(geom)[base * nr + k];
+    v[k] = q;
+    fc[k] = T(0.5) * (T(1.) + r_cos(PI * q.w / Ra));
+    dcp[k] = -T(0.5) * r_sin(PI * q.w / Ra) * PI / Ra / q.w;
+    ids[k] = intmap2b[base * (nr + 1) + 1 + k];
+  }
+  __syncthreads();
+  long long Tl = (long long)m * (m - 1) / 2;
+  const int Tn = Tl < na ? (int)Tl : na;
+  int2* im3 = reinterpret_cast<int2*>(intmap3b) + base * na;
+  T* ad = angdescr + base * na;
+  T2* d3x = reinterpret_cast<T2*>(der3b) + (base * 3 + 0) * na;
+  T2* d3y = reinterpret_cast<T2*>(der3b) + (base * 3 + 1) * na;
+  T2* d3z = reinterpret_cast<T2*>(der3b) + (base * 3 + 2) * na;
+  for (int nn = threadIdx.x; nn < na; nn += THREADS) {
+    T t = T(0);
+    int2 id = make_int2(0, 0);
+    T2 ox, oy, oz;
+    ox.x = ox.y = oy.x = oy.y = oz.x = oz.y = T(0);
+    if (nn < Tn) {
+      int j, k;
+      unrank_pair(nn, m, j, k);
+      const T4 a = v[j], c = v[k];
+      const T cj = fc[j], ck = fc[k];
+      const T dot = a.x * c.x + a.y * c.y + a.z * c.z;
+      const T angle = dot / (a.w * c.w);
+      const T half = T(0.5) * (angle + T(1));
+      t = half * cj * ck;
+      const T dj3 = a.w * a.w * a.w * c.w, dk3 = c.w * c.w * c.w * a.w;
+      const T nj2 = a.w * a.w, nk2 = c.w * c.w;
+      const T pj = dcp[j], pk = dcp[k];
+      ox.x = (T(0.5) * (nj2 * c.x - a.x * dot) / dj3) * cj * ck + half * (pj * a.x) * ck;
+      ox.y = (T(0.5) * (nk2 * a.x - c.x * dot) / dk3) * cj * ck + half * cj * (pk * c.x);
+      oy.x = (T(0.5) * (nj2 * c.y - a.y * dot) / dj3) * cj * ck + half * (pj * a.y) * ck;
+      oy.y = (T(0.5) * (nk2 * a.y - c.y * dot) / dk3) * cj * ck + half * cj * (pk * c.y);
+      oz.x = (T(0.5) * (nj2 * c.z - a.z * dot) / dj3) * cj * ck + half * (pj * a.z) * ck;
+      oz.y = (T(0.5) * (nk2 * a.z - c.z * dot) / dk3) * cj * ck + half * cj * (pk * c.z);
+      id = make_int2(ids[j], ids[k]);
+    }
+    ad[nn] = t;
+    im3[nn] = id;
+    d3x[nn] = ox;
+    d3y[nn] = oy;
+    d3z[nn] = oz;
+  }
+}
+
+template <class T>
+int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box, int nf, int N, T* raddescr,
+                       T* angdescr, T* des3bsupp, int* intmap2b, int* intmap3b, T* der2b, T* der3b, T* der3bsupp,
+                       int* numtriplet) {
+  if (nf <= 0 || N <= 0) return STAFB_ERR_INVALID;
+  if (nf > c->max_batch || N > c->n_max) return STAFB_ERR_CAPACITY;
+  const int nr = c->nr, na = c->na, cap = c->cell_cap;
+  FrameGeom<T>* fg = reinterpret_cast<FrameGeom<T>*>(c->fgeom);
+  T* frac = reinterpret_cast<T*>(c->frac);
+  T* geom = reinterpret_cast<T*>(c->geom);
+  int mpc = N / 3;  // descriptor_builder/reforce.cc:306-309
+  if (mpc < 1) mpc = 1;
+  if (mpc > 256) mpc = 256;
+  CoreCoef<T> cc;
+  cc.Rc = (T)c->Rc; cc.Rs = (T)c->Rs; cc.Ra = (T)c->Ra;
+  cc.A = (T)c->coef[0]; cc.B = (T)c->coef[1]; cc.C = (T)c->coef[2]; cc.pa = (T)c->coef[3]; cc.pb = (T)c->coef[4];
+  STAFB_CUDA_OK(cudaMemsetAsync(c->cell_count, 0, sizeof(int) * (size_t)nf * cap, s));
+  k_frame_setup<T><<<(nf + 31) / 32, 32, 0, s>>>(box, nf, N, cc.Rc, cap, fg, c->status_d);
+  const int tot = nf * N;
+  k_bin<T><<<(tot + 255) / 256, 256, 0, s>>>(pos, nf, N, fg, frac, c->cell_of, c->cell_count, cap);
+  k_scan<T><<<nf, 256, 0, s>>>(fg, c->cell_count, c->cell_start, c->cell_cursor, cap, mpc, c->status_d);
+  k_fill<<<(tot + 255) / 256, 256, 0, s>>>(nf, N, c->cell_of, c->cell_start, c->cell_cursor, c->cells_raw, cap);
+  {
+    long long warps = (long long)nf * cap;
+    k_sort_cells<T><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(fg, nf, N, c->cell_start, c->cells_raw,
+                                                                       c->cells_sorted, cap);
+  }
+  {
+    constexpr int W = 4;
+    size_t sm = (size_t)W * 2 * nr * (sizeof(T) + sizeof(int));
+    k_nl_radial<T, W><<<(tot + W - 1) / W, W * 32, sm, s>>>(nf, N, nr, cc, fg, frac, c->cell_of, c->cell_start,
+                                                          c->cells_sorted, cap, raddescr, des3bsupp, intmap2b, der2b,
+                                                          der3bsupp, numtriplet, geom, na, c->status_d);
+  }
+  c->launches += 6;
+  if (angdescr && intmap3b && der3b) {
+    constexpr int TH = 128;
+    size_t sm = (size_t)nr * (sizeof(typename Vec4<T>::type) + 2 * sizeof(T) + sizeof(int));
+    k_angular<T, TH><<<tot, TH, sm, s>>>(nf, N, nr, na, cc.Ra, geom, intmap2b, numtriplet, angdescr, intmap3b, der3b);
+    c->launches += 1;
+  }
+  STAFB_CUDA_OK(cudaGetLastError());
+  return STAFB_OK;
+}
+
+template int launch_descriptors<float>(stafb_ctx*, cudaStream_t, const float*, const float*, int, int, float*, float*,
+                                       float*, int*, int*, float*, float*, float*, int*);
+template int launch_descriptors<double>(stafb_ctx*, cudaStream_t, const double*, const double*, int, int, double*,
+                                        double*, double*, int*, int*, double*, double*, double*, int*);
+
+}  // namespace stafb

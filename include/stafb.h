@@ -1,0 +1,191 @@
+/* stafb.h - C ABI of the B200 (sm_100a) implementation of the STAF descriptor / fingerprint /
+ * force / gradient hot path.
+ *
+ * Every entry point takes plain pointers and sizes.  Pointers named *_d are DEVICE pointers
+ * unless the function name ends in _host.  `real` tensors are float or double according to
+ * the dtype the context was created with (the reference builds two op trees, ops_float and
+ * ops_double, from one source: STAF/include/staf_real.h:21-37).  All index tensors are int32.
+ * `stream` is a cudaStream_t passed as void* (NULL = default stream).  Calls are asynchronous
+ * on that stream unless stated otherwise.  No entry point ever terminates the process: where
+ * the reference calls exit() the library returns / records a status code.
+ *
+ * Paths in the comments are relative to the reference project root.
+ */
+#ifndef STAFB_H
+#define STAFB_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define STAFB_OK 0
+#define STAFB_ERR_RADIAL_OVERFLOW 1  /* an atom has more than radial_buffer neighbours
+                                        (reference: printf + exit(0), descriptor_builder/reforce.cc:324-340) */
+#define STAFB_ERR_ANGULAR_OVERFLOW 2 /* m(m-1)/2 > angular_buffer (reference: silently dropped by the kernels,
+                                        sys.exit in staf_train.py:709-714) */
+#define STAFB_ERR_CELL_OVERFLOW 3    /* a cell holds more than MAX_PARTICLE_CELLS atoms (reference: silently
+                                        dropped, descriptor_builder/celle_gpu.cu.cc:197-200) */
+#define STAFB_ERR_BAD_BOX 4          /* zero box length (reference: libstaf/src/staf_api.cpp returns -7) */
+#define STAFB_ERR_INVALID 5          /* bad argument */
+#define STAFB_ERR_CUDA 6             /* a CUDA runtime call failed; see stafb_last_cuda_error() */
+#define STAFB_ERR_CAPACITY 7         /* nf or N larger than what the context was created for */
+#define STAFB_ERR_NONFINITE 8        /* non-finite energy */
+
+#define STAFB_F32 0
+#define STAFB_F64 1
+#define STAFB_MAX_TYPES 4
+#define STAFB_MAX_DENSE 6
+
+typedef struct stafb_ctx stafb_ctx;
+typedef struct stafb_model stafb_model;
+
+/* ---- context ------------------------------------------------------------------------------
+ * Replaces op ConstructDescriptorsLight (descriptor_builder/reforce.cc:182-238): stores the
+ * cutoffs and buffer sizes, computes the repulsive-core coefficients (fill_repulsion,
+ * reforce.cc:101-125; the cutoff_curve.dat side effect is dropped) and allocates the per-device
+ * scratch (cells, neighbour rows) for max_batch frames of n_max atoms on the CURRENT device.
+ * State lives in the handle, not in process globals. */
+int stafb_create(stafb_ctx** out, int dtype, double radial_cutoff, double rs, double ra, int radial_buffer,
+                 int angular_buffer, int n_max, int max_batch);
+void stafb_destroy(stafb_ctx* ctx);
+/* Synchronises `stream` and returns the first status recorded by device code since the last
+ * call (STAFB_OK if none), then clears it. */
+int stafb_status(stafb_ctx* ctx, void* stream);
+const char* stafb_strerror(int status);
+const char* stafb_last_cuda_error(void);
+/* coefficients A, B, C and the powers (1, -30) of the repulsive core, as doubles */
+void stafb_core_coefficients(const stafb_ctx* ctx, double out5[5]);
+
+/* ---- the reference's operators, one function each ------------------------------------------
+ * Shapes: nf frames, N atoms, Nl atoms of the central species, nr = radial_buffer,
+ * na = angular_buffer, nt species, C = nt(nt+1)/2, Fr / Fa radial / angular fingerprints. */
+
+/* ComputeDescriptorsLight (descriptor_builder/reforce.cc:241-252,262-444).
+ * positions[nf,3N] Cartesian, boxer[nf,6] = Lx,xy,xz,Ly,yz,Lz ->
+ * raddescr[nf,N,nr] angdescr[nf,N,na] des3bsupp[nf,N,nr] intmap2b[nf,N,nr+1] intmap3b[nf,N,2na]
+ * der2b[nf,N,3,nr] der3b[nf,N,3,2na] der3bsupp[nf,N,3,nr] numtriplet[nf,N].
+ * angdescr, intmap3b and der3b may all be NULL (the three angular tensors are then not produced).
+ * Padded slots, which the reference leaves uninitialised in the float tensors, are zero. */
+int stafb_compute_descriptors_light(stafb_ctx* ctx, void* stream, const void* positions_d, const void* boxer_d,
+                                    int nf, int N, void* raddescr_d, void* angdescr_d, void* des3bsupp_d,
+                                    int* intmap2b_d, int* intmap3b_d, void* der2b_d, void* der3b_d,
+                                    void* der3bsupp_d, int* numtriplet_d);
+
+/* ComputeSortProj (fingerprint/rad/reforce.cc:13-19) -> two_body_afs[nf,Nl,Fr] */
+int stafb_compute_sort_proj(stafb_ctx* ctx, void* stream, const void* radial_descriptor_d,
+                            const int* interaction_map_rad_d, const void* alpha2b_d, const void* type_emb2b_sq_d,
+                            const int* type_map_d, int nf, int Nl, int nt, int Fr, void* two_body_afs_d);
+
+/* ComputeSortProj3body (fingerprint/ang/reforce.cc:15-24) -> three_body_afs[nf,Nl,Fa].
+ * radial_descriptor is des3bsupp (source_routine/physics_layer_mod.py:40). */
+int stafb_compute_sort_proj3body(stafb_ctx* ctx, void* stream, const void* angular_descriptor_d,
+                                 const void* radial_descriptor_d, const int* interaction_map_angular_d,
+                                 const int* interaction_map_rad_d, const void* alpha3b_d,
+                                 const void* type_emb3b_sq_d, const int* type_map_d, const int* num_triplet_d, int nf,
+                                 int Nl, int nt, int Fa, void* three_body_afs_d);
+
+/* InitForceRadial / InitForceTripl / InitGradForceRadial / InitGradForceTripl
+ * (force/rad/reforce.cc:13-36 and siblings) chose a CUDA block size from the buffer size; the
+ * library needs no such state.  Kept so that callers can keep calling them: returns 0. */
+int stafb_init_force_radial(int buffdim);
+int stafb_init_force_tripl(int buffdim);
+int stafb_init_grad_force_radial(int buffdim);
+int stafb_init_grad_force_tripl(int buffdim);
+
+/* ComputeForceRadial (force/rad/reforce.cc:39-49) -> force[nf,3N] (zero-filled, then this
+ * species' contribution).  tipos[nt] and actual_type[1] are device tensors as in the op. */
+int stafb_compute_force_radial(stafb_ctx* ctx, void* stream, const void* netderiv_d,
+                               const void* descriptor_derivative_rad_d, const int* interaction_map_rad_d,
+                               const void* radial_descriptor_d, const void* alpha2b_d, const void* type_emb2b_sq_d,
+                               const int* type_map_d, const int* tipos_d, const int* actual_type_d, int nf, int Nl,
+                               int N, int nt, int Fr, void* force_d);
+
+/* ComputeForceTripl (force/ang/reforce.cc:44-58) -> force[nf,3N] */
+int stafb_compute_force_tripl(stafb_ctx* ctx, void* stream, const void* netderiv_d, const void* radial_descriptor_d,
+                              const void* angular_descriptor_d, const void* descriptor_derivative_rad_d,
+                              const void* descriptor_derivative_ang_d, const int* interaction_map_rad_d,
+                              const int* interaction_map_ang_d, const void* alpha3b_d, const void* type_emb3b_sq_d,
+                              const int* type_map_d, const int* tipos_d, const int* actual_type_d,
+                              const int* num_triplets_d, int nf, int Nl, int N, int nt, int Fa, void* force_d);
+
+/* ComputeTwoBodyParGrad (grad_finger/rad/reforce.cc:14-22) -> nextgrad_alpha2b[nt,Fr], nextgrad_emb2b[nt,Fr] */
+int stafb_compute_two_body_par_grad(stafb_ctx* ctx, void* stream, const void* prev_grad_d,
+                                    const void* radial_descriptor_d, const int* interaction_map_rad_d,
+                                    const void* alpha2b_d, const void* type_emb2b_sq_d, const int* type_map_d, int nf,
+                                    int Nl, int nt, int Fr, void* nextgrad_alpha2b_d, void* nextgrad_emb2b_d);
+
+/* ComputeSortProj3bodyGrad (grad_finger/ang/reforce.cc:12-23) -> alphagrad3body[C,3Fa] and
+ * nextgrad_emb3b[C,Fa], which the reference never accumulates into: written as zeros. */
+int stafb_compute_sort_proj3body_grad(stafb_ctx* ctx, void* stream, const void* previous_gradient_d,
+                                      const void* angular_descriptors_d, const void* radial_descriptors_d,
+                                      const int* intmap3b_d, const int* intmap2b_d, const void* alpha3b_d,
+                                      const void* type_emb3b_sq_d, const int* type_map_d, const int* num_triplets_d,
+                                      int nf, int Nl, int nt, int Fa, void* alphagrad3body_d, void* nextgrad_emb3b_d);
+
+/* ComputeForceRadialGrad (grad_force/rad/reforce.cc:42-55) -> gradnet[nf,Nl,Fr], grad_alpha2b[nt,Fr], grad_emb2b[nt,Fr] */
+int stafb_compute_force_radial_grad(stafb_ctx* ctx, void* stream, const void* prevgrad_d, const void* netderiv_d,
+                                    const void* descriptor_derivative_rad_d, const int* interaction_map_rad_d,
+                                    const void* radial_descriptor_d, const void* alpha2b_d,
+                                    const void* type_emb2b_sq_d, const int* type_map_d, const int* tipos_d,
+                                    const int* actual_type_d, int nf, int Nl, int N, int nt, int Fr, void* gradnet_d,
+                                    void* grad_alpha2b_d, void* grad_emb2b_d);
+
+/* ComputeForceTriplGrad (grad_force/ang/reforce.cc:39-56) -> gradnet[nf,Nl,Fa], gradalpha[C,3Fa],
+ * gradck[C,Fa] (never written by the reference: zeros). */
+int stafb_compute_force_tripl_grad(stafb_ctx* ctx, void* stream, const void* prevgrad_d, const void* netderiv_d,
+                                   const void* radial_descriptor_d, const void* angular_descriptor_d,
+                                   const void* descriptor_derivative_rad_d, const void* descriptor_derivative_ang_d,
+                                   const int* interaction_map_rad_d, const int* interaction_map_ang_d,
+                                   const void* alpha3b_d, const void* type_emb3b_sq_d, const int* type_map_d,
+                                   const int* tipos_d, const int* actual_type_d, const int* num_triplets_d, int nf,
+                                   int Nl, int N, int nt, int Fa, void* gradnet_d, void* gradalpha_d, void* gradck_d);
+
+/* ---- fused path ----------------------------------------------------------------------------
+ * One model = nt per-species blocks of trained parameters in ONE flat buffer `theta`
+ *     alpha2b[nt,Fr_t] | alpha3b[C,3Fa_t] | mu[Fr_t+Fa_t] | W0[in,out] b0 | W1 b1 | ...   (t = 0..nt-1)
+ * and the squared type embeddings (never trained: staf_models/staf_model.py:225-253) in `emb`
+ *     e2[nt,Fr_t] | e3[C,Fa_t]                                                                (t = 0..nt-1).
+ * shape_desc = int32[20]: nt, tipos[4], Fr[4], Fa[4], n_dense, width[6] (width[n_dense-1] == 1; hidden
+ * layers are tanh, the output layer is linear).  Atoms are species-sorted (staf_train.py:217-224). */
+int stafb_model_create(stafb_ctx* ctx, const int* shape_desc, stafb_model** out);
+void stafb_model_destroy(stafb_model* m);
+int stafb_model_n_params(const stafb_model* m);
+int stafb_model_n_emb(const stafb_model* m);
+/* offsets of species t: a2, a3, mu, w (into theta), emb (into emb), block size */
+void stafb_model_offsets(const stafb_model* m, int t, int out6[6]);
+
+/* Energy and forces of nf frames (staf_models/staf_model.py:174-211; inference convention
+ * staf_models/staf_model_inference_full.py:118-119 when per_atom_energy == 0):
+ * energy[nf] = 0.5*mean_i e_i (per_atom_energy) or 0.5*sum_i e_i; force[nf,3N]. */
+int stafb_energy_force(stafb_ctx* ctx, stafb_model* m, void* stream, const void* positions_d, const void* boxer_d,
+                       int nf, const void* theta_d, const void* emb_d, int per_atom_energy, void* energy_d,
+                       void* force_d);
+
+/* One energy+force training evaluation (full_train_e_f, staf_models/staf_model.py:168-258, without
+ * the optimizer update): loss = pe*L(E,e_label) + pb*sum(alpha*[alpha>alpha_bound]) + pf*L(F,f_label),
+ * L = Keras Huber(delta=1, mean) if loss_kind == 0 else MSE.  Writes losses[4] (double: loss, loss_e,
+ * loss_bound, loss_f) and grad[n_params] = dloss/dtheta.  energy_d / force_d may be NULL. */
+int stafb_train_step(stafb_ctx* ctx, stafb_model* m, void* stream, const void* positions_d, const void* boxer_d,
+                     int nf, const void* theta_d, const void* emb_d, const void* e_label_d, const void* f_label_d,
+                     double pe, double pf, double pb, double alpha_bound, int loss_kind, double* losses_d,
+                     void* grad_d, void* energy_d, void* force_d);
+
+/* Adam update of theta in place (Keras Adam, epsilon default 1e-7: optimizer_learning_rate_utility.py:64-68):
+ * g = grad*grad_scale; m,v moments; step counts from 1. */
+int stafb_adam_step(stafb_ctx* ctx, void* stream, void* theta_d, const void* grad_d, void* m_d, void* v_d, int n,
+                    double lr, double beta1, double beta2, double eps, int step, double grad_scale);
+
+/* Same as stafb_train_step but positions, boxer and labels are HOST buffers and losses is a
+ * host double[4]: copies in, runs, copies the losses back and synchronises the stream. */
+int stafb_train_step_host(stafb_ctx* ctx, stafb_model* m, void* stream, const void* positions_h, const void* boxer_h,
+                          int nf, const void* theta_d, const void* emb_d, const void* e_label_h,
+                          const void* f_label_h, double pe, double pf, double pb, double alpha_bound, int loss_kind,
+                          double* losses_h, void* grad_d);
+
+/* number of kernels the last fused call launched (for accounting) */
+int stafb_last_launch_count(const stafb_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* STAFB_H */
