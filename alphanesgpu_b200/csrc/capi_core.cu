@@ -93,6 +93,7 @@ extern "C" int stafb_create(stafb_ctx** out, int dtype, double Rc, double Rs, do
   STAFB_CUDA_OK(cudaMalloc((void**)&c->cells_raw, sizeof(int) * B * Nn));
   STAFB_CUDA_OK(cudaMalloc((void**)&c->cells_sorted, sizeof(int) * B * Nn));
   STAFB_CUDA_OK(cudaMalloc(&c->geom, es * B * Nn * nr * 4));
+  STAFB_CUDA_OK(cudaMalloc(&c->gsc, es * B * Nn * nr * 2));
   STAFB_CUDA_OK(cudaMalloc((void**)&c->status_d, sizeof(int)));
   STAFB_CUDA_OK(cudaMemset(c->status_d, 0, sizeof(int)));
   STAFB_CUDA_OK(cudaMallocHost((void**)&c->status_h, sizeof(int)));
@@ -107,7 +108,7 @@ extern "C" void stafb_destroy(stafb_ctx* c) {
   cudaSetDevice(c->device);
   cudaFree(c->fgeom); cudaFree(c->frac); cudaFree(c->cell_of); cudaFree(c->cell_count);
   cudaFree(c->cell_start); cudaFree(c->cell_cursor); cudaFree(c->cells_raw); cudaFree(c->cells_sorted);
-  cudaFree(c->geom); cudaFree(c->status_d);
+  cudaFree(c->geom); cudaFree(c->gsc); cudaFree(c->status_d);
   cudaFreeHost(c->status_h);
   cudaSetDevice(cur);
   free(c);

@@ -108,6 +108,7 @@ struct stafb_ctx {
   int* cells_raw;     // [max_batch, n_max]
   int* cells_sorted;  // [max_batch, n_max]
   void* geom;         // T[max_batch, n_max, nr, 4]: MIC vector r_i - r_j and its norm, sorted order
+  void* gsc;          // T[max_batch, n_max, nr, 2]: d(raddescr)/dr and d(des3bsupp)/dr
   int* status_d;
   int* status_h;  // pinned
   int launches;

@@ -191,8 +191,8 @@ __global__ void __launch_bounds__(WARPS * 32)
                 const T* __restrict__ frac, const int* __restrict__ cell_of, const int* __restrict__ cell_start,
                 const int* __restrict__ cells_sorted, int cell_cap, T* __restrict__ raddescr,
                 T* __restrict__ des3bsupp, int* __restrict__ intmap2b, T* __restrict__ der2b,
-                T* __restrict__ der3bsupp, int* __restrict__ numtriplet, T* __restrict__ geom, int na,
-                int* __restrict__ status) {
+                T* __restrict__ der3bsupp, int* __restrict__ numtriplet, T* __restrict__ geom, T* __restrict__ gsc,
+                int na, int* __restrict__ status) {
   extern __shared__ unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gi = blockIdx.x * WARPS + warp;
@@ -268,7 +268,7 @@ __global__ void __launch_bounds__(WARPS * 32)
   int nang = 0;
   for (int k = lane; k < nr; k += 32) {
     T rd = T(0), d3 = T(0), g2x = T(0), g2y = T(0), g2z = T(0), g3x = T(0), g3y = T(0), g3z = T(0);
-    T vx = T(0), vy = T(0), vz = T(0), dn = T(0);
+    T vx = T(0), vy = T(0), vz = T(0), dn = T(0), s2 = T(0), s3 = T(0);
     int j = 0;
     if (k < n) {
       j = jb[k];
@@ -278,6 +278,7 @@ __global__ void __launch_bounds__(WARPS * 32)
         nang++;
         d3 = T(0.5) * (r_cos(PI * dn / cc.Ra) + T(1));
         const T pre = T(-0.5) * r_sin(PI * dn / cc.Ra) * PI / cc.Ra;
+        s3 = pre;
         g3x = pre * vx / dn;
         g3y = pre * vy / dn;
         g3z = pre * vz / dn;
@@ -285,12 +286,14 @@ __global__ void __launch_bounds__(WARPS * 32)
       if (dn < cc.Rs) {
         rd = cc.A / r_pow(dn, cc.pa) + cc.B / r_pow(dn, cc.pb) + cc.C;
         const T pre = (-cc.pa * cc.A / r_pow(dn, cc.pa + T(1.)) - cc.pb * cc.B / r_pow(dn, cc.pb + T(1.)));
+        s2 = pre;
         g2x = pre * vx / dn;
         g2y = pre * vy / dn;
         g2z = pre * vz / dn;
       } else {
         rd = T(0.5) * (r_cos(PI * dn / cc.Rc) + T(1));
         const T pre = T(-0.5) * r_sin(PI * dn / cc.Rc) * PI / cc.Rc;
+        s2 = pre;
         g2x = pre * vx / dn;
         g2y = pre * vy / dn;
         g2z = pre * vz / dn;
@@ -298,17 +301,27 @@ __global__ void __launch_bounds__(WARPS * 32)
     }
     raddescr[base * nr + k] = rd;
     des3bsupp[base * nr + k] = d3;
-    der2b[(base * 3 + 0) * nr + k] = g2x;
-    der2b[(base * 3 + 1) * nr + k] = g2y;
-    der2b[(base * 3 + 2) * nr + k] = g2z;
-    der3bsupp[(base * 3 + 0) * nr + k] = g3x;
-    der3bsupp[(base * 3 + 1) * nr + k] = g3y;
-    der3bsupp[(base * 3 + 2) * nr + k] = g3z;
+    if (der2b) {
+      der2b[(base * 3 + 0) * nr + k] = g2x;
+      der2b[(base * 3 + 1) * nr + k] = g2y;
+      der2b[(base * 3 + 2) * nr + k] = g2z;
+    }
+    if (der3bsupp) {
+      der3bsupp[(base * 3 + 0) * nr + k] = g3x;
+      der3bsupp[(base * 3 + 1) * nr + k] = g3y;
+      der3bsupp[(base * 3 + 2) * nr + k] = g3z;
+    }
     intmap2b[base * (nr + 1) + 1 + k] = (k < n) ? j : 0;
     if (geom) {
       typename Vec4<T>::type q;
       q.x = vx; q.y = vy; q.z = vz; q.w = dn;
       reinterpret_cast<typename Vec4<T>::type*>(geom)[base * nr + k] = q;
+    }
+    if (gsc) {
+      // scalar radial derivatives: der2b = s2 * v/|v|, der3bsupp = s3 * v/|v|
+      typename Vec2<T>::type q;
+      q.x = s2; q.y = s3;
+      reinterpret_cast<typename Vec2<T>::type*>(gsc)[base * nr + k] = q;
     }
   }
   nang = warp_sum(nang);
@@ -396,6 +409,7 @@ int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box,
   FrameGeom<T>* fg = reinterpret_cast<FrameGeom<T>*>(c->fgeom);
   T* frac = reinterpret_cast<T*>(c->frac);
   T* geom = reinterpret_cast<T*>(c->geom);
+  T* gsc = reinterpret_cast<T*>(c->gsc);
   int mpc = N / 3;  // descriptor_builder/reforce.cc:306-309
   if (mpc < 1) mpc = 1;
   if (mpc > 256) mpc = 256;
@@ -418,7 +432,7 @@ int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box,
     size_t sm = (size_t)W * 2 * nr * (sizeof(T) + sizeof(int));
     k_nl_radial<T, W><<<(tot + W - 1) / W, W * 32, sm, s>>>(nf, N, nr, cc, fg, frac, c->cell_of, c->cell_start,
                                                           c->cells_sorted, cap, raddescr, des3bsupp, intmap2b, der2b,
-                                                          der3bsupp, numtriplet, geom, na, c->status_d);
+                                                          der3bsupp, numtriplet, geom, gsc, na, c->status_d);
   }
   c->launches += 6;
   if (angdescr && intmap3b && der3b) {

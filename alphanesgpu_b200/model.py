@@ -1,0 +1,119 @@
+"""Host-side driver of the fused path: the model the reference builds in
+STAF/staf_models/staf_model.py (per-species fingerprints -> log-normalisation -> MLP ->
+energy; forces through d(sum e)/dAF; Huber/MSE loss; Adam), with every device step done by
+the C ABI (include/stafb.h).  torch supplies device buffers, streams and, for data-parallel
+training, the NCCL all-reduce of the flat gradient.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import check
+from .ops import Context
+from .params import ModelShape
+
+
+def _p(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+class StafModel:
+    """One potential: geometry config + parameter layout + device buffers."""
+
+    def __init__(self, shape: ModelShape, cfg, theta, emb, max_batch, dtype=torch.float32, device=None,
+                 pe=1.0, pf=1.0, pb=1.0, alpha_bound=5.0, loss="huber"):
+        self.shape = shape
+        self.cfg = dict(cfg)
+        self.dtype = dtype
+        self.ctx = Context(cfg["Rc"], cfg["nr"], cfg["na"], shape.N, cfg["Rs"], cfg["Ra"], max_batch, dtype, device)
+        self.device = self.ctx.device
+        self.max_batch = int(max_batch)
+        h = C.c_void_p()
+        sd = shape.desc()
+        with torch.cuda.device(self.device):
+            check(_lib.lib().stafb_model_create(self.ctx.h, sd.ctypes.data_as(C.c_void_p), C.byref(h)),
+                  "stafb_model_create")
+        self.h = h
+        assert _lib.lib().stafb_model_n_params(h) == shape.n_params
+        assert _lib.lib().stafb_model_n_emb(h) == shape.n_emb
+        self.theta = torch.as_tensor(np.asarray(theta), dtype=dtype).to(self.device).contiguous()
+        self.emb = torch.as_tensor(np.asarray(emb), dtype=dtype).to(self.device).contiguous()
+        self.grad = torch.zeros_like(self.theta)
+        self.adam_m = torch.zeros_like(self.theta)
+        self.adam_v = torch.zeros_like(self.theta)
+        self.losses = torch.zeros(4, dtype=torch.float64, device=self.device)
+        self.losses_h = np.zeros(4, np.float64)
+        self.step = 0
+        self.pe, self.pf, self.pb, self.alpha_bound = float(pe), float(pf), float(pb), float(alpha_bound)
+        self.loss_kind = 0 if loss == "huber" else 1
+
+    def close(self):
+        if getattr(self, "h", None):
+            _lib.lib().stafb_model_destroy(self.h)
+            self.h = None
+        self.ctx.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _dev(self, a):
+        if torch.is_tensor(a):
+            return a.to(device=self.device, dtype=self.dtype).contiguous()
+        return torch.as_tensor(np.asarray(a), dtype=self.dtype).to(self.device).contiguous()
+
+    def energy_force(self, pos, box, per_atom_energy=False, check_status=True):
+        """Energies [nf] and forces [nf,3N] (inference convention 0.5*sum e_i unless per_atom_energy)."""
+        pos, box = self._dev(pos), self._dev(box)
+        nf = box.shape[0]
+        energy = torch.empty(nf, dtype=self.dtype, device=self.device)
+        force = torch.empty(nf, 3 * self.shape.N, dtype=self.dtype, device=self.device)
+        check(_lib.lib().stafb_energy_force(self.ctx.h, self.h, self.ctx.stream(), _p(pos), _p(box), nf,
+                                            _p(self.theta), _p(self.emb), int(per_atom_energy), _p(energy),
+                                            _p(force)), "stafb_energy_force")
+        if check_status:
+            self.ctx.raise_on_status("stafb_energy_force")
+        return energy, force
+
+    def loss_and_grad(self, pos, box, e_label, f_label, want_outputs=False):
+        """One training evaluation on device tensors: fills self.losses (loss, loss_e, loss_bound, loss_f)
+        and self.grad; asynchronous on the current stream."""
+        nf = box.shape[0]
+        energy = force = None
+        if want_outputs:
+            energy = torch.empty(nf, dtype=self.dtype, device=self.device)
+            force = torch.empty(nf, 3 * self.shape.N, dtype=self.dtype, device=self.device)
+        check(_lib.lib().stafb_train_step(self.ctx.h, self.h, self.ctx.stream(), _p(pos), _p(box), nf, _p(self.theta),
+                                          _p(self.emb), _p(e_label), _p(f_label), self.pe, self.pf, self.pb,
+                                          self.alpha_bound, self.loss_kind, _p(self.losses), _p(self.grad),
+                                          _p(energy), _p(force)), "stafb_train_step")
+        return energy, force
+
+    def loss_and_grad_host(self, pos, box, e_label, f_label):
+        """Same with HOST numpy inputs: host->device copies, the step and the device->host read of the
+        losses all happen inside the call (it returns after the stream has drained)."""
+        dt = np.float32 if self.dtype == torch.float32 else np.float64
+        pos, box = np.ascontiguousarray(pos, dt), np.ascontiguousarray(box, dt)
+        e_label, f_label = np.ascontiguousarray(e_label, dt), np.ascontiguousarray(f_label, dt)
+        nf = box.shape[0]
+        vp = lambda a: a.ctypes.data_as(C.c_void_p)
+        check(_lib.lib().stafb_train_step_host(self.ctx.h, self.h, self.ctx.stream(), vp(pos), vp(box), nf,
+                                               _p(self.theta), _p(self.emb), vp(e_label), vp(f_label), self.pe,
+                                               self.pf, self.pb, self.alpha_bound, self.loss_kind,
+                                               vp(self.losses_h), _p(self.grad)), "stafb_train_step_host")
+        return self.losses_h
+
+    def adam_update(self, lr, beta1=0.9, beta2=0.999, eps=1e-7, grad_scale=1.0):
+        """Keras Adam (epsilon default 1e-7: STAF/optimizer_learning_rate_utility.py:64-68)."""
+        self.step += 1
+        check(_lib.lib().stafb_adam_step(self.ctx.h, self.ctx.stream(), _p(self.theta), _p(self.grad),
+                                         _p(self.adam_m), _p(self.adam_v), self.theta.numel(), float(lr),
+                                         float(beta1), float(beta2), float(eps), self.step, float(grad_scale)),
+              "stafb_adam_step")
+
+    def launches(self):
+        return _lib.lib().stafb_last_launch_count(self.ctx.h)

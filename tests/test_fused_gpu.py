@@ -1,0 +1,121 @@
+"""GPU parity of the fused energy/force/training path (C ABI: stafb_energy_force, stafb_train_step,
+stafb_adam_step) against the CPU oracle's full step on the same seeded inputs."""
+import numpy as np
+import pytest
+
+from alphanesgpu_b200 import synth
+from conftest import CFG, rel_err
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+TOL = {np.float32: 1e-5, np.float64: 1e-11}
+
+
+def _tdt(dtype):
+    return torch.float32 if dtype == np.float32 else torch.float64
+
+
+def _case(name, seeds, frame0):
+    if name == "frame0":
+        return frame0["pos"], frame0["box"], frame0["shape"], frame0["theta"], frame0["emb"]
+    pos, box, tipos = synth.water_frames(name, seeds)
+    shape = synth.baseline_shape(tipos)
+    theta, emb = synth.init_params(shape)
+    return pos, box, shape, theta, emb
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("name,seeds", [("water96", [1000, 1001]), ("water768", [1100, 1101, 1102, 1103]),
+                                        ("frame0", None)])
+def test_energy_force(oracle, frame0, name, seeds, dtype):
+    from alphanesgpu_b200.model import StafModel
+    pos, box, shape, theta, emb = _case(name, seeds, frame0)
+    nf = pos.shape[0]
+    ref = oracle.energy_force_grad(CFG, shape.desc(), pos, box, shape.type_map, theta, emb, dtype,
+                                   per_atom_energy=False)
+    assert ref["status"] == 0
+    m = StafModel(shape, CFG, theta, emb, nf, dtype=_tdt(dtype))
+    e, f = m.energy_force(pos.astype(dtype), box.astype(dtype))
+    assert rel_err(e.cpu().numpy(), ref["energy"]) <= TOL[dtype]
+    assert rel_err(f.cpu().numpy(), ref["force"]) <= TOL[dtype]
+    if name == "frame0" and dtype == np.float32:
+        # the reference's recorded values for this frame and model
+        # (test/test-lammps-STAF-inference-STAF-comp/results/frames.csv:2)
+        assert abs(float(e[0]) - (-102.25880432)) < 1.2e-4
+        assert abs(float(torch.sqrt((f.double() ** 2).mean())) - 0.6993059698907058) < 5e-6
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("name,seeds,loss", [("water96", [1000, 1001], "huber"), ("water96", [1000, 1001], "mse"),
+                                             ("water768", [1100, 1101, 1102, 1103], "huber")])
+def test_train_step_losses_and_gradient(oracle, frame0, name, seeds, loss, dtype):
+    from alphanesgpu_b200.model import StafModel
+    pos, box, shape, theta, emb = _case(name, seeds, frame0)
+    theta = theta.copy()
+    theta[shape.offsets(0)["a2"] + 1] = 5.5  # exercise the bound term
+    theta[shape.offsets(1)["a3"] + 4] = 6.0
+    nf = pos.shape[0]
+    el, fl = synth.labels(nf, shape.N)
+    kw = dict(pe=0.7, pf=1.3, pb=0.9, alpha_bound=5.0)
+    ref = oracle.energy_force_grad(CFG, shape.desc(), pos, box, shape.type_map, theta, emb, dtype, with_grad=True,
+                                   e_label=el, f_label=fl, loss_kind=0 if loss == "huber" else 1, **kw)
+    m = StafModel(shape, CFG, theta, emb, nf, dtype=_tdt(dtype), loss=loss, **kw)
+    d = lambda a: torch.as_tensor(a.astype(dtype)).cuda()
+    e, f = m.loss_and_grad(d(pos), d(box), d(el), d(fl), want_outputs=True)
+    m.ctx.raise_on_status("train_step")
+    tol = TOL[dtype]
+    assert rel_err(e.cpu().numpy(), ref["energy"]) <= tol
+    assert rel_err(f.cpu().numpy(), ref["force"]) <= tol
+    losses = m.losses.cpu().numpy()
+    assert np.allclose(losses, ref["losses"], rtol=tol * 10, atol=0)
+    g, gr = m.grad.cpu().numpy().astype(np.float64), ref["grad"].astype(np.float64)
+    # per parameter family, as the reference's own gradient regression does
+    # (test/test-regression/regression-grad-param/run_grad_param_regression.py:80-253)
+    for t in range(shape.nt):
+        o = shape.offsets(t)
+        for lo, hi in ((o["a2"], o["a3"]), (o["a3"], o["mu"]), (o["mu"], o["w"]), (o["w"], o["a2"] + o["size"])):
+            assert rel_err(g[lo:hi], gr[lo:hi]) <= tol, (t, lo, hi)
+    # host-buffer entry point gives the same numbers
+    lh = m.loss_and_grad_host(pos, box, el, fl).copy()
+    assert np.allclose(lh, losses, rtol=1e-6 if dtype == np.float32 else 1e-12)
+    assert rel_err(m.grad.cpu().numpy(), g) <= (2e-6 if dtype == np.float32 else 1e-12)
+    m.close()
+
+
+def test_adam_matches_reference_formula():
+    from alphanesgpu_b200.model import StafModel
+    pos, box, tipos = synth.water_frames("water96", [1000])
+    shape = synth.baseline_shape(tipos)
+    theta, emb = synth.init_params(shape)
+    m = StafModel(shape, CFG, theta, emb, 1, dtype=torch.float64)
+    rng = np.random.default_rng(3)
+    th, mm, vv = theta.copy(), np.zeros_like(theta), np.zeros_like(theta)
+    for step in range(1, 4):
+        g = rng.normal(size=theta.shape)
+        m.grad.copy_(torch.as_tensor(g).cuda())
+        m.adam_update(1e-3)
+        mm = 0.9 * mm + 0.1 * g
+        vv = 0.999 * vv + 0.001 * g * g
+        lr_t = 1e-3 * np.sqrt(1 - 0.999 ** step) / (1 - 0.9 ** step)
+        th = th - lr_t * mm / (np.sqrt(vv) + 1e-7)
+        assert np.allclose(m.theta.cpu().numpy(), th, rtol=1e-13, atol=1e-15)
+    m.close()
+
+
+def test_training_reduces_the_loss():
+    from alphanesgpu_b200.model import StafModel
+    pos, box, tipos = synth.water_frames("water96", [1000, 1001])
+    shape = synth.baseline_shape(tipos)
+    theta, emb = synth.init_params(shape)
+    el, fl = synth.labels(2, shape.N)
+    m = StafModel(shape, CFG, theta, emb, 2, dtype=torch.float32)
+    first = last = None
+    for it in range(30):
+        l = m.loss_and_grad_host(pos, box, el * 0.01, fl * 0.05)[0]
+        first = l if first is None else first
+        last = l
+        m.adam_update(2e-3)
+    assert np.isfinite(last) and last < first
+    m.close()
