@@ -110,6 +110,8 @@ extern "C" void stafb_destroy(stafb_ctx* c) {
   cudaFree(c->cell_start); cudaFree(c->cell_cursor); cudaFree(c->cells_raw); cudaFree(c->cells_sorted);
   cudaFree(c->geom); cudaFree(c->gsc); cudaFree(c->status_d);
   cudaFreeHost(c->status_h);
+  for (int q = 0; q < 16; q++)
+    if (c->ev[q]) cudaEventDestroy(c->ev[q]);
   cudaSetDevice(cur);
   free(c);
 }
@@ -125,6 +127,28 @@ extern "C" int stafb_status(stafb_ctx* c, void* stream) {
 
 extern "C" void stafb_core_coefficients(const stafb_ctx* c, double out5[5]) {
   for (int i = 0; i < 5; i++) out5[i] = c->coef[i];
+}
+
+extern "C" int stafb_set_phase_timing(stafb_ctx* c, int on) {
+  if (!c) return STAFB_ERR_INVALID;
+  if (on && !c->ev[0]) {
+    for (int q = 0; q < 16; q++) STAFB_CUDA_OK(cudaEventCreate(&c->ev[q]));
+  }
+  c->timing = on ? 1 : 0;
+  c->n_phase = 0;
+  return STAFB_OK;
+}
+
+extern "C" int stafb_get_phase_times(stafb_ctx* c, float* ms, int cap) {
+  if (!c || !ms || !c->timing || c->n_phase < 2) return 0;
+  if (cudaEventSynchronize(c->ev[c->n_phase - 1]) != cudaSuccess) return 0;
+  int n = c->n_phase - 1;
+  if (n > cap) n = cap;
+  for (int q = 0; q < n; q++) {
+    ms[q] = 0.f;
+    cudaEventElapsedTime(&ms[q], c->ev[q], c->ev[q + 1]);
+  }
+  return n;
 }
 
 extern "C" int stafb_last_launch_count(const stafb_ctx* c) { return c ? c->launches : 0; }

@@ -112,6 +112,10 @@ struct stafb_ctx {
   int* status_d;
   int* status_h;  // pinned
   int launches;
+  // optional per-phase timing of the fused path (CUDA events on the launching stream)
+  int timing;
+  int n_phase;
+  cudaEvent_t ev[16];
 };
 
 #define STAFB_CUDA_OK(call)                                        \

@@ -781,6 +781,24 @@ __global__ void k_adam(int n, T* __restrict__ theta, const T* __restrict__ grad,
   theta[q] -= lr_t * mm / (r_sqrt(vv) + eps);
 }
 
+// Adam with the step count kept on the device, so that a captured CUDA graph can be replayed
+template <class T>
+__global__ void k_adam_dev(int n, T* __restrict__ theta, const T* __restrict__ grad, T* __restrict__ m,
+                           T* __restrict__ v, double lr, double b1, double b2, T eps, T gscale,
+                           const int* __restrict__ step_d) {
+  const int q = blockIdx.x * blockDim.x + threadIdx.x;
+  if (q >= n) return;
+  const int step = *step_d + 1;
+  const T lr_t = (T)(lr * sqrt(1.0 - pow(b2, (double)step)) / (1.0 - pow(b1, (double)step)));
+  const T g = grad[q] * gscale;
+  const T mm = (T)b1 * m[q] + (T(1) - (T)b1) * g;
+  const T vv = (T)b2 * v[q] + (T(1) - (T)b2) * g * g;
+  m[q] = mm;
+  v[q] = vv;
+  theta[q] -= lr_t * mm / (r_sqrt(vv) + eps);
+}
+__global__ void k_inc(int* p) { *p += 1; }
+
 }  // namespace stafb
 
 using namespace stafb;
@@ -927,10 +945,16 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
   const ModelDev& d = m->md;
   const int N = d.N;
   c->launches = 0;
+  c->n_phase = 0;
+  auto mark = [&]() {
+    if (c->timing && c->n_phase < 16) cudaEventRecord(c->ev[c->n_phase++], s);
+  };
+  mark();
   T* rad = (T*)m->rad; T* d3s = (T*)m->d3s;
   int rc = launch_descriptors<T>(c, s, pos, box, nf, N, rad, nullptr, d3s, m->im2, nullptr, nullptr, nullptr,
                                  nullptr, m->ntr);
   if (rc != STAFB_OK) return rc;
+  mark();  // descriptors
   SweepIn<T> in;
   in.geom = (const T*)c->geom; in.gsc = (const T*)c->gsc; in.rad = rad; in.d3s = d3s; in.im2 = m->im2; in.ntr = m->ntr;
   in.nf = nf; in.nr = c->nr;
@@ -939,6 +963,7 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
   T* energy = energy_out ? energy_out : (T*)m->energy;
   rc = launch_sweep<T, MODE_AF>(m, s, nf, in, theta, emb, nullptr, nullptr, af, nullptr);
   if (rc != STAFB_OK) return rc;
+  mark();  // af_fwd
   const int mblocks = species_blocks(d, nf, ML_WARPS);
   {
     const size_t sm = sizeof(T) * (size_t)(d.Fmax + d.Hsum + 2 * d.maxw) * ML_WARPS;
@@ -952,9 +977,11 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
     k_mlp_fwd<T><<<mblocks, ML_WARPS * 32, sm, s>>>(d, nf, theta, af, acts, e_atom, nd);
     c->launches++;
   }
+  mark();  // mlp_fwd
   STAFB_CUDA_OK(cudaMemsetAsync(force, 0, sizeof(T) * (size_t)nf * 3 * N, s));
   rc = launch_sweep<T, MODE_FORCE>(m, s, nf, in, theta, emb, nd, nullptr, force, nullptr);
   if (rc != STAFB_OK) return rc;
+  mark();  // force
   if (train) {
     STAFB_CUDA_OK(cudaMemsetAsync(losses_d, 0, sizeof(double) * 4, s));
     STAFB_CUDA_OK(cudaMemsetAsync(grad, 0, sizeof(T) * (size_t)m->n_params, s));
@@ -969,10 +996,12 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
     k_force_loss<T><<<fb, 256, 0, s>>>(nF, force, f_label, (T)pf, loss_kind, (T*)m->fbar, losses_d);
     k_bound<T><<<1, 256, 0, s>>>(d, theta, (T)bound, (T)pb, grad, losses_d);
     c->launches += 2;
+    mark();  // loss
     T* gradnet = (T*)m->gradnet;
     T* gaf = (T*)m->gaf;
     rc = launch_sweep<T, MODE_FGRAD>(m, s, nf, in, theta, emb, nd, (const T*)m->fbar, gradnet, grad);
     if (rc != STAFB_OK) return rc;
+    mark();  // force_grad
     {
       const size_t sm = sizeof(T) * (size_t)(3 * d.Fmax + 5 * d.Hsum + 2 * d.maxw) * ML_WARPS;
       if (sm > m->smem_limit) return STAFB_ERR_CAPACITY;
@@ -985,10 +1014,12 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
       k_mlp_bwd<T><<<mblocks, ML_WARPS * 32, sm, s>>>(d, nf, theta, af, acts, (const T*)m->ebar, gradnet, gaf, grad);
       c->launches++;
     }
+    mark();  // mlp_bwd
     rc = launch_sweep<T, MODE_AFGRAD>(m, s, nf, in, theta, emb, gaf, nullptr, nullptr, grad);
     if (rc != STAFB_OK) return rc;
     k_finalize<<<1, 1, 0, s>>>(pe, pf, pb, losses_d);
     c->launches++;
+    mark();  // af_grad
   }
   STAFB_CUDA_OK(cudaGetLastError());
   return STAFB_OK;
@@ -1072,6 +1103,21 @@ extern "C" int stafb_adam_step(stafb_ctx* c, void* stream, void* theta, const vo
   else
     k_adam<double><<<(n + 255) / 256, 256, 0, s>>>(n, (double*)theta, (const double*)grad, (double*)mm, (double*)vv,
                                                    lr_t, b1, b2, eps, gscale);
+  STAFB_CUDA_OK(cudaGetLastError());
+  return STAFB_OK;
+}
+
+extern "C" int stafb_adam_step_dev(stafb_ctx* c, void* stream, void* theta, const void* grad, void* mm, void* vv,
+                                   int n, double lr, double b1, double b2, double eps, int* step_d, double gscale) {
+  if (!c || !theta || !grad || !mm || !vv || n <= 0 || !step_d) return STAFB_ERR_INVALID;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (c->dtype == STAFB_F32)
+    k_adam_dev<float><<<(n + 255) / 256, 256, 0, s>>>(n, (float*)theta, (const float*)grad, (float*)mm, (float*)vv, lr,
+                                                      b1, b2, (float)eps, (float)gscale, step_d);
+  else
+    k_adam_dev<double><<<(n + 255) / 256, 256, 0, s>>>(n, (double*)theta, (const double*)grad, (double*)mm,
+                                                       (double*)vv, lr, b1, b2, eps, gscale, step_d);
+  k_inc<<<1, 1, 0, s>>>(step_d);
   STAFB_CUDA_OK(cudaGetLastError());
   return STAFB_OK;
 }

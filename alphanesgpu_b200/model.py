@@ -115,5 +115,24 @@ class StafModel:
                                          float(beta1), float(beta2), float(eps), self.step, float(grad_scale)),
               "stafb_adam_step")
 
+    PHASES = ["descriptors", "af_fwd", "mlp_fwd", "force", "loss", "force_grad", "mlp_bwd", "af_grad"]
+
+    def adam_update_dev(self, lr, beta1=0.9, beta2=0.999, eps=1e-7, grad_scale=1.0):
+        """Adam with the step counter on the device (safe to capture in a CUDA graph and replay)."""
+        if not hasattr(self, "step_d"):
+            self.step_d = torch.zeros(1, dtype=torch.int32, device=self.device)
+        check(_lib.lib().stafb_adam_step_dev(self.ctx.h, self.ctx.stream(), _p(self.theta), _p(self.grad),
+                                             _p(self.adam_m), _p(self.adam_v), self.theta.numel(), float(lr),
+                                             float(beta1), float(beta2), float(eps), _p(self.step_d),
+                                             float(grad_scale)), "stafb_adam_step_dev")
+
+    def set_phase_timing(self, on):
+        check(_lib.lib().stafb_set_phase_timing(self.ctx.h, int(on)), "stafb_set_phase_timing")
+
+    def phase_times_ms(self):
+        buf = np.zeros(16, np.float32)
+        n = _lib.lib().stafb_get_phase_times(self.ctx.h, buf.ctypes.data_as(C.c_void_p), 16)
+        return dict(zip(self.PHASES[:n], buf[:n].tolist()))
+
     def launches(self):
         return _lib.lib().stafb_last_launch_count(self.ctx.h)

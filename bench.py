@@ -1,0 +1,386 @@
+#!/usr/bin/env python
+"""Benchmark of the STAF hot path on B200: 768-atom water energy+force training step, fp32.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
+
+One "step" = one training evaluation of a batch of B frames (neighbour list, descriptors,
+fingerprints, MLP, forces, loss, backward to alpha/mu/MLP weights) followed by the Adam update;
+with N > 1 (launched by torch.distributed.run, one rank per GPU) every rank works on its own frames
+and the flat gradient is summed with ONE NCCL all-reduce per step before Adam (learning rate not
+scaled by N).  Prints one JSON line (rank 0).
+
+`value`   frames/s with the inputs resident in HBM, the step replayed from a CUDA graph, L2 flushed
+          between steps, CUDA-event time summed over exactly K steps, max over ranks.
+`e2e`     frames/s through the host-buffer entry point of the C ABI (stafb_train_step_host + Adam):
+          host->device copies of positions/box/labels and the device->host read of the losses are
+          inside the timed region (wall clock, synchronised both sides).
+`roofline` the dominant kernel of the step, timed live with CUDA events on the launching stream.
+`cpu_baseline` the CPU oracle (a port of the reference's kernel math; the reference's own ops are
+          GPU-only) on a bounded sample, all host threads.
+`--impl reference` times that same CPU port as the reference arm.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(Rc=4.5, Rs=2.25, Ra=4.5, nr=60, na=1770)
+METRIC = "768-atom water E+F train frames/s"
+PUBLISHED_V100_FRAMES_PER_S = 10.9  # reference README.md:42-45 (V100, fp32, batch 4)
+
+
+def make_batches(rank, n_batches, B, dtype):
+    from alphanesgpu_b200 import synth
+    seeds = [1100 + 64 * rank + i for i in range(n_batches * B)]
+    pos, box, tipos = synth.water_frames("water768", seeds)
+    shape = synth.baseline_shape(tipos)
+    N = shape.N
+    el, fl = synth.labels(n_batches * B, N, seed=3000 + rank)
+    rs = lambda a, *s: np.ascontiguousarray(a.reshape(n_batches, B, *s).astype(dtype))
+    return shape, rs(pos, 3 * N), rs(box, 6), rs(el), rs(fl, 3 * N)
+
+
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.index, self.rows, self._stop, self._t = index, [], threading.Event(), None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                rs = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(
+                    nv, "nvmlDeviceGetCurrentClocksEventReasons") else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.rows.append((sm, rs))
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def start(self):
+        if self.nv:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+
+    def stop(self):
+        if self._t:
+            self._stop.set()
+            self._t.join()
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.nv or not self.rows:
+            return out
+        nv = self.nv
+        out["sm_mhz"] = float(np.median([r[0] for r in self.rows]))
+        try:
+            out["sm_max_mhz"] = float(nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM))
+        except Exception:
+            pass
+        names = {0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+                 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+        seen = 0
+        for _, rs in self.rows:
+            seen |= rs
+        out["reasons"] = [n for bit, n in names.items() if seen & bit]
+        out["samples"] = len(self.rows)
+        return out
+
+
+def cpu_port_frames_per_s(B, n_steps, threads=None):
+    """Times the CPU oracle's full training evaluation (no optimizer) on n_steps batches of B frames."""
+    from oracle import oracle
+    if threads:
+        oracle.set_threads(threads)
+    shape, pos, box, el, fl = make_batches(0, n_steps, B, np.float32)
+    from alphanesgpu_b200 import synth
+    theta, emb = synth.init_params(shape, dtype=np.float32)
+    sd = shape.desc()
+    oracle.energy_force_grad(CFG, sd, pos[0], box[0], shape.type_map, theta, emb, np.float32, with_grad=True,
+                             e_label=el[0], f_label=fl[0])  # warm-up
+    t0 = time.perf_counter()
+    for i in range(n_steps):
+        r = oracle.energy_force_grad(CFG, sd, pos[i], box[i], shape.type_map, theta, emb, np.float32, with_grad=True,
+                                     e_label=el[i], f_label=fl[i])
+        assert r["status"] == 0
+    dt = time.perf_counter() - t0
+    return B * n_steps / dt, dt, oracle.max_threads()
+
+
+def run_reference(args):
+    """Reference arm: the reference's hot path on the host cores.  Its own ops are GPU-only TensorFlow
+    kernels (TensorFlow is not installable here), so the timed code is the CPU port in oracle/."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    B = args.batch
+    # bounded sample: each "step" is one batch; cap the total so the run ends within minutes
+    steps = max(1, min(args.steps, 12))
+    warm = max(1, min(args.warmup, 1))
+    for _ in range(warm):
+        cpu_port_frames_per_s(B, 1)
+    fps, dt, cores = cpu_port_frames_per_s(B, steps)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": fps, "unit": "frames/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": warm, "ms_per_step": 1e3 * dt / steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "water768 E+F training evaluation, batch %d, fp32 (BASELINE configs[1])" % B,
+                   "note": "CPU port of the reference kernels (oracle/), OpenMP over atoms; no optimizer step"},
+        "cpu_baseline": {"value": fps, "unit": "frames/s", "cores": cores, "kind": "port",
+                         "sample": "%d batches of %d frames" % (steps, B)},
+        "e2e": {"value": fps, "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from alphanesgpu_b200 import ops, synth
+    from alphanesgpu_b200.model import StafModel
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, K, W = args.batch, args.steps, max(args.warmup, 3)
+    dtype = np.float32
+    NB = 8  # distinct batches cycled through
+    shape, pos, box, el, fl = make_batches(rank, NB, B, dtype)
+    N = shape.N
+    theta, emb = synth.init_params(shape, dtype=dtype)
+    model = StafModel(shape, CFG, theta, emb, B, dtype=torch.float32, device=dev)
+    lr = 1e-3
+    d_pos, d_box, d_el, d_fl = (torch.as_tensor(a).to(dev) for a in (pos, box, el, fl))
+
+    def step_eager(i):
+        model.loss_and_grad(d_pos[i], d_box[i], d_el[i], d_fl[i])
+        if world > 1:
+            dist.all_reduce(model.grad)
+        model.adam_update_dev(lr, grad_scale=1.0 / world)
+
+    for w in range(W):
+        step_eager(w % NB)
+    model.ctx.raise_on_status("bench warm-up")
+    launches_per_step = model.launches() + 2  # + Adam and its step counter
+    torch.cuda.synchronize()
+
+    # ---- CUDA graphs: one per distinct batch (pointers differ); NCCL stays outside the graphs
+    graphs = []
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(NB):
+            g1 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g1, stream=side):
+                model.loss_and_grad(d_pos[i], d_box[i], d_el[i], d_fl[i])
+                if world == 1:
+                    model.adam_update_dev(lr)
+            g2 = None
+            if world > 1:
+                g2 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g2, stream=side):
+                    model.adam_update_dev(lr, grad_scale=1.0 / world)
+            graphs.append((g1, g2))
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+
+    def step_graph(i):
+        g1, g2 = graphs[i % NB]
+        g1.replay()
+        if world > 1:
+            dist.all_reduce(model.grad)
+            g2.replay()
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for w in range(W):
+        step_graph(w)
+        flush.zero_()
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- timed region: exactly K steps, L2 flushed between steps, device time per step summed
+    sampler = ClockSampler(local)
+    ev0 = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+    ev1 = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+    barrier()
+    sampler.start()
+    for k in range(K):
+        flush.zero_()
+        ev0[k].record()
+        step_graph(k)
+        ev1[k].record()
+    barrier()
+    per_step = np.array([a.elapsed_time(b) for a, b in zip(ev0, ev1)])
+    total_ms = float(per_step.sum())
+    # ---- same, back to back without flushing (working set stays in L2)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    a.record()
+    for k in range(K):
+        step_graph(k)
+    b.record()
+    barrier()
+    warm_ms = a.elapsed_time(b)
+    clocks = sampler.stop()
+    model.ctx.raise_on_status("bench timed region")
+    t = torch.tensor([total_ms, warm_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, warm_ms = float(t[0]), float(t[1])
+    value = world * B * K / (total_ms * 1e-3)
+    value_warm = world * B * K / (warm_ms * 1e-3)
+
+    # ---- end to end through host buffers (H2D of inputs + D2H of losses inside the call)
+    Ke = max(10, min(K, 500))
+    for k in range(3):
+        model.loss_and_grad_host(pos[k % NB], box[k % NB], el[k % NB], fl[k % NB])
+    barrier()
+    t0 = time.perf_counter()
+    for k in range(Ke):
+        i = k % NB
+        model.loss_and_grad_host(pos[i], box[i], el[i], fl[i])
+        if world > 1:
+            dist.all_reduce(model.grad)
+        model.adam_update_dev(lr, grad_scale=1.0 / world)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = world * B * Ke / float(t[0])
+    isz = np.dtype(dtype).itemsize
+    h2d = isz * (B * 3 * N * 2 + B * 6 + B)
+    d2h = 8 * 4 + 4
+
+    # ---- per-phase device times (eager launches, CUDA events between phases, L2 flushed)
+    model.set_phase_timing(True)
+    acc = {}
+    Kp = 30
+    for k in range(Kp):
+        flush.zero_()
+        model.loss_and_grad(d_pos[k % NB], d_box[k % NB], d_el[k % NB], d_fl[k % NB])
+        for name, ms in model.phase_times_ms().items():
+            acc[name] = acc.get(name, 0.0) + ms / Kp
+    model.set_phase_timing(False)
+    dom = max((n for n in acc if n not in ("descriptors", "loss")), key=lambda n: acc[n])
+    # algorithmic bytes of one launch of the dominant sweep kernel: the compact neighbour rows it
+    # reads (vector+norm 16 B, two scalar derivatives 8 B, descriptor 4 B, cutoff 4 B, index 4 B per
+    # neighbour), its per-atom channel row in and out, and the gathered force cotangents
+    ctx = ops.construct_descriptors_light(CFG["Rc"], CFG["nr"], CFG["na"], N, None, CFG["Rs"], CFG["Ra"], B,
+                                          dtype=torch.float32, device=dev)
+    outs = ops.compute_descriptors_light(d_pos[0], d_box[0], with_angular=False, ctx=ctx)
+    n_i = outs[3][..., 0].to(torch.float64)
+    m_i = outs[8].to(torch.float64)
+    trip = float((m_i * (m_i - 1) / 2).sum())
+    F = shape.Fr[0] + shape.Fa[0]
+    row_bytes = float((n_i * (16 + 8 + 4 + 4 + 4) + 8).sum())
+    chan = B * N * F * isz
+    alg = {"af_fwd": row_bytes + chan, "force": row_bytes + chan + float(((n_i + 1) * 3 * isz).sum()),
+           "force_grad": row_bytes + 2 * chan + float(((n_i + 1) * 3 * isz).sum()),
+           "af_grad": row_bytes + chan, "mlp_fwd": 3 * chan, "mlp_bwd": 4 * chan}[dom]
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = alg / (acc[dom] * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "k_sweep<%s>" % dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
+                "ms_per_launch": acc[dom], "algorithmic_bytes_per_launch": alg,
+                "note": "geometry is rebuilt on chip, so this kernel is bound by the FP32/SFU pipes, not by HBM; "
+                        "triplet-channel evaluations per launch = %.3g" % (trip * shape.Fa[0] / shape.C)}
+    # the HBM-bound kernel of the operator boundary: the angular descriptor fill (write-once tensors)
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    ops.compute_descriptors_light(d_pos[0], d_box[0], with_angular=True, ctx=ctx)
+    t_no, t_with = 0.0, 0.0
+    for k in range(10):
+        flush.zero_()
+        e0.record()
+        ops_out = ops.compute_descriptors_light(d_pos[k % NB], d_box[k % NB], with_angular=False, ctx=ctx)
+        e1.record()
+        ops_out = ops.compute_descriptors_light(d_pos[k % NB], d_box[k % NB], with_angular=True, ctx=ctx)
+        e2.record()
+        torch.cuda.synchronize()
+        t_no += e0.elapsed_time(e1) / 10
+        t_with += e1.elapsed_time(e2) / 10
+    ang_bytes = B * N * CFG["na"] * (isz + 8 + 6 * isz)
+    ang_ms = max(t_with - t_no, 1e-6)
+    roofline_ops = {"bound": "hbm", "kernel": "k_angular (ComputeDescriptorsLight angular tensors)",
+                    "achieved": ang_bytes / (ang_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                    "frac": ang_bytes / (ang_ms * 1e-3) / 1e9 / peak, "traffic": None, "ms_per_launch": ang_ms,
+                    "algorithmic_bytes_per_launch": ang_bytes}
+    del ops_out
+
+    line = None
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            fps, dt, cores = cpu_port_frames_per_s(B, 6)
+            cpu = {"value": fps, "unit": "frames/s", "cores": cores, "kind": "port",
+                   "sample": "6 batches of %d frames (%.1f s)" % (B, dt)}
+        line = {
+            "metric": METRIC, "value": value, "unit": "frames/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": value / PUBLISHED_V100_FRAMES_PER_S, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "water768 E+F training step (eval + Adam), batch %d per GPU, fp32 "
+                                   "(BASELINE configs[1])" % B,
+                       "frames": "seeded synthetic water, 256 O + 512 H, L=19.6 A, %d distinct batches" % NB,
+                       "model": "2 species, Fr=10, Fa=15, MLP 25-64-32-1 tanh", "parallelism": "dp%d" % world,
+                       "l2": "flushed between steps (256 MiB write); per-step CUDA events summed",
+                       "launch": "CUDA graph replay per step",
+                       "vs_baseline_note": "published number is the reference on a V100 (README.md:42-45)"},
+            "value_l2_warm": value_warm, "ms_per_step_min": float(per_step.min()),
+            "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": Ke},
+            "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step,
+            "clocks": clocks, "roofline": roofline, "roofline_operator_boundary": roofline_ops,
+            "phase_ms": acc, "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    model.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--batch", type=int, default=4)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

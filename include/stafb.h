@@ -175,12 +175,24 @@ int stafb_train_step(stafb_ctx* ctx, stafb_model* m, void* stream, const void* p
 int stafb_adam_step(stafb_ctx* ctx, void* stream, void* theta_d, const void* grad_d, void* m_d, void* v_d, int n,
                     double lr, double beta1, double beta2, double eps, int step, double grad_scale);
 
+/* Adam with the step counter in device memory (*step_d counts completed updates and is incremented by
+ * the call): the same launch sequence can be captured in a CUDA graph and replayed. */
+int stafb_adam_step_dev(stafb_ctx* ctx, void* stream, void* theta_d, const void* grad_d, void* m_d, void* v_d, int n,
+                        double lr, double beta1, double beta2, double eps, int* step_d, double grad_scale);
+
 /* Same as stafb_train_step but positions, boxer and labels are HOST buffers and losses is a
  * host double[4]: copies in, runs, copies the losses back and synchronises the stream. */
 int stafb_train_step_host(stafb_ctx* ctx, stafb_model* m, void* stream, const void* positions_h, const void* boxer_h,
                           int nf, const void* theta_d, const void* emb_d, const void* e_label_h,
                           const void* f_label_h, double pe, double pf, double pb, double alpha_bound, int loss_kind,
                           double* losses_h, void* grad_d);
+
+/* Per-phase device timing of the fused calls, with CUDA events on the launching stream.  Phases, in
+ * order: descriptors, af_fwd, mlp_fwd, force, loss, force_grad, mlp_bwd, af_grad (the last four only for
+ * stafb_train_step).  stafb_get_phase_times waits for the last event, writes up to cap durations in
+ * milliseconds and returns how many.  Not for use while the stream is being captured. */
+int stafb_set_phase_timing(stafb_ctx* ctx, int on);
+int stafb_get_phase_times(stafb_ctx* ctx, float* ms, int cap);
 
 /* number of kernels the last fused call launched (for accounting) */
 int stafb_last_launch_count(const stafb_ctx* ctx);
