@@ -11,7 +11,10 @@
 // (row = type_j + type_k, STAF/src/fingerprint/ang/reforce.cu.cc:56), so the channel loop is
 // uniform across the warp and channels whose squared embedding is zero are skipped for the
 // whole class.  exp(a1*sj + a2*sk) is formed as a product of per-neighbour factors
-// exp(a1*sj), exp(a2*sk) tabulated once per (class, channel chunk).
+// exp(a1*sj), exp(a2*sk) tabulated once per (class, channel chunk); in fp32 all exponentials
+// are base-2 with parameters pre-scaled by log2(e) (one multiply + one MUFU per evaluation).
+// The force sweep walks ORDERED pairs so that every lane accumulates the force on "its"
+// neighbour in registers - no shared-memory atomics in the inner loop.
 //
 // Math: STAF/src/fingerprint, force, grad_finger, grad_force (rad and ang) reforce.cu.cc and
 // STAF/staf_models/staf_model.py:168-258 of the reference (see include/stafb.h).
@@ -22,9 +25,20 @@
 
 namespace stafb {
 
-constexpr int MAXCH = 8;    // channels processed per pair sweep
-constexpr int SW_WARPS = 4; // warps (= atoms) per block in the sweep kernels
-constexpr int ML_WARPS = 8; // atoms per block in the MLP kernels
+constexpr int MAXCH = 8;     // channels processed per pair sweep
+constexpr int SW_WARPS = 4;  // warps (= atoms) per block in the sweep kernels
+constexpr int ML_THREADS = 256;
+
+// exponential with a pre-scaled argument: fp32 uses 2^x (MUFU.EX2), fp64 the full-precision exp
+template <class T> struct Ex;
+template <> struct Ex<float> {
+  static __host__ __device__ __forceinline__ float scale() { return 1.4426950408889634f; }
+  static __device__ __forceinline__ float f(float x) { return exp2f(x); }
+};
+template <> struct Ex<double> {
+  static __host__ __device__ __forceinline__ double scale() { return 1.0; }
+  static __device__ __forceinline__ double f(double x) { return exp(x); }
+};
 
 struct ModelDev {
   int nt, C, N, ncls;
@@ -64,8 +78,9 @@ struct SweepIn {
 
 enum { MODE_AF = 0, MODE_FORCE = 1, MODE_FGRAD = 2, MODE_AFGRAD = 3 };
 
-// species-major enumeration: block -> (species, first atom); W atoms per block
-__device__ __forceinline__ bool locate_atom(const ModelDev& md, int nf, int W, int warp, int& t, int& b, int& i) {
+// species-major enumeration: block -> (species t, index q0 of its first atom among the nf*tipos[t]
+// atoms of that species); W atoms per block, blocks never mix species
+__device__ __forceinline__ void locate_block(const ModelDev& md, int nf, int W, int& t, int& q0) {
   int blk = blockIdx.x;
   t = 0;
   while (t < md.nt - 1) {
@@ -74,7 +89,13 @@ __device__ __forceinline__ bool locate_atom(const ModelDev& md, int nf, int W, i
     blk -= nb;
     t++;
   }
-  const int q = blk * W + warp;
+  q0 = blk * W;
+}
+
+__device__ __forceinline__ bool locate_atom(const ModelDev& md, int nf, int W, int slot, int& t, int& b, int& i) {
+  int q0;
+  locate_block(md, nf, W, t, q0);
+  const int q = q0 + slot;
   if (q >= nf * md.tipos[t]) return false;
   b = q / md.tipos[t];
   i = md.shift[t] + (q - b * md.tipos[t]);
@@ -89,7 +110,7 @@ static inline int species_blocks(const ModelDev& md, int nf, int W) {
 
 // per-warp shared memory layout of the sweep kernels (offsets in bytes)
 struct SweepLayout {
-  int u, d, fc, gd, gfc, tab, chp, xtra, acc, ids, tj, lst, actl, total;
+  int p0, p1, tab, chpa, chpb, xtra, acc, ids, tj, lst, actl, total;
 };
 
 template <class T>
@@ -97,13 +118,11 @@ static inline SweepLayout sweep_layout(int nr, int nt, int xt, int nacc, int fam
   SweepLayout L;
   int o = 0;
   auto take = [&](int bytes) { int r = o; o += (bytes + 15) & ~15; return r; };
-  L.u = take(nr * 4 * sizeof(T));
-  L.d = take(nr * sizeof(T));
-  L.fc = take(nr * sizeof(T));
-  L.gd = take(nr * sizeof(T));
-  L.gfc = take(nr * sizeof(T));
+  L.p0 = take(nr * 4 * sizeof(T));
+  L.p1 = take(nr * 4 * sizeof(T));
   L.tab = take(MAXCH * nr * 2 * sizeof(T));
-  L.chp = take(MAXCH * 8 * sizeof(T));
+  L.chpa = take(MAXCH * 4 * sizeof(T));
+  L.chpb = take(MAXCH * 2 * sizeof(T));
   L.xtra = take(nr * xt * sizeof(T));
   L.acc = take(nacc * sizeof(T));
   L.ids = take(nr * sizeof(int));
@@ -113,6 +132,26 @@ static inline SweepLayout sweep_layout(int nr, int nt, int xt, int nacc, int fam
   L.total = o;
   return L;
 }
+
+// steps through the pairs of a class, 32 at a time, without divisions
+struct PairStep {
+  int ja, kb;
+  __device__ __forceinline__ void init_rect(int p, int nb) { ja = p / nb; kb = p - ja * nb; }
+  __device__ __forceinline__ void step_rect(int nb, int q32, int r32) {
+    ja += q32;
+    kb += r32;
+    if (kb >= nb) { kb -= nb; ja++; }
+  }
+  __device__ __forceinline__ void init_tri(int p, int n) { unrank_pair(p, n, ja, kb); }
+  __device__ __forceinline__ void step_tri(int n) {  // advance 32 positions in the row-major upper triangle
+    kb += 32;
+    while (kb >= n && ja < n - 1) {
+      const int o = kb - n;
+      ja++;
+      kb = ja + 1 + o;
+    }
+  }
+};
 
 template <class T, int MODE>
 __global__ void __launch_bounds__(SW_WARPS * 32)
@@ -128,13 +167,11 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
   int t, b, i;
   if (!locate_atom(md, in.nf, SW_WARPS, warp, t, b, i)) return;
   unsigned char* base = smem_raw + (size_t)warp * L.total;
-  T4* u = reinterpret_cast<T4*>(base + L.u);
-  T* d = reinterpret_cast<T*>(base + L.d);
-  T* fc = reinterpret_cast<T*>(base + L.fc);
-  T* gd = reinterpret_cast<T*>(base + L.gd);
-  T* gfc = reinterpret_cast<T*>(base + L.gfc);
+  T4* P0 = reinterpret_cast<T4*>(base + L.p0);   // unit vector (i - k)/r and cutoff fc
+  T4* P1 = reinterpret_cast<T4*>(base + L.p1);   // 1/r, dfc/dr, radial descriptor d, dd/dr
   T2* tab = reinterpret_cast<T2*>(base + L.tab);
-  T* chp = reinterpret_cast<T*>(base + L.chp);
+  T4* chpa = reinterpret_cast<T4*>(base + L.chpa);  // alpha1, alpha2, beta, beta*scale
+  T2* chpb = reinterpret_cast<T2*>(base + L.chpb);  // mode-dependent coefficient, netderiv
   T* xtra = reinterpret_cast<T*>(base + L.xtra);
   T* acc = reinterpret_cast<T*>(base + L.acc);
   int* ids = reinterpret_cast<int*>(base + L.ids);
@@ -150,6 +187,7 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
   const T* e2 = emb + md.off_emb[t];
   const T* e3 = e2 + nt * Fr;
   const T* chrow = chan_in ? chan_in + gi * Fmax : nullptr;
+  const T SC = Ex<T>::scale();
   // accumulator regions inside acc[]
   const int ACC_GN = 0;                      // [Famax]     AF: fingerprints; FGRAD: gradnet (angular part)
   const int ACC_A2 = md.Famax;               // [nt*Frmax]  dL/dalpha2b
@@ -161,16 +199,14 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
   int m = in.ntr[gi];
   if (m > n) m = n;
   for (int k = lane; k < n; k += 32) {
-    T4 g = reinterpret_cast<const T4*>(in.geom)[gi * nr + k];
+    const T4 g = reinterpret_cast<const T4*>(in.geom)[gi * nr + k];
+    const T2 s = reinterpret_cast<const T2*>(in.gsc)[gi * nr + k];
     const T inv = T(1) / g.w;
-    T4 q;
-    q.x = g.x * inv; q.y = g.y * inv; q.z = g.z * inv; q.w = g.w;
-    u[k] = q;
-    d[k] = in.rad[gi * nr + k];
-    fc[k] = in.d3s[gi * nr + k];
-    T2 s = reinterpret_cast<const T2*>(in.gsc)[gi * nr + k];
-    gd[k] = s.x;
-    gfc[k] = s.y;
+    T4 q0, q1;
+    q0.x = g.x * inv; q0.y = g.y * inv; q0.z = g.z * inv; q0.w = in.d3s[gi * nr + k];
+    q1.x = inv; q1.y = s.y; q1.z = in.rad[gi * nr + k]; q1.w = s.x;
+    P0[k] = q0;
+    P1[k] = q1;
     const int id = in.im2[gi * (nr + 1) + 1 + k];
     ids[k] = id;
     tj[k] = (unsigned char)md.type_of(id);
@@ -206,7 +242,7 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
       const int id = ids[k];
       const T dx = fb[id * 3] - fx, dy = fb[id * 3 + 1] - fy, dz = fb[id * 3 + 2] - fz;
       xtra[k * 4 + 0] = dx; xtra[k * 4 + 1] = dy; xtra[k * 4 + 2] = dz;
-      xtra[k * 4 + 3] = dx * u[k].x + dy * u[k].y + dz * u[k].z;
+      xtra[k * 4 + 3] = dx * P0[k].x + dy * P0[k].y + dz * P0[k].z;
     }
   }
   __syncwarp();
@@ -217,7 +253,8 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
       T s = T(0);
       for (int k = lane; k < n; k += 32) {
         const T ch = e2[Fr * tj[k] + c];
-        if (ch != T(0)) s += d[k] * (r_exp(a2[Fr * tj[k] + c] * d[k]) * ch);
+        const T dk = P1[k].z;
+        if (ch != T(0)) s += dk * (Ex<T>::f(a2[Fr * tj[k] + c] * SC * dk) * ch);
       }
       s = warp_sum(s);
       if (lane == 0) out[gi * Fmax + c] = s;
@@ -225,16 +262,16 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
   } else if (MODE == MODE_FORCE) {
     for (int k = lane; k < n; k += 32) {
       const int tk = tj[k];
-      const T dk = d[k];
+      const T dk = P1[k].z;
       T w = T(0);
       for (int c = 0; c < Fr; c++) {
         const T ch = e2[Fr * tk + c];
         if (ch == T(0)) continue;
         const T al = a2[Fr * tk + c];
-        w += chrow[c] * (T(0.5) * ch * r_exp(al * dk) * (T(1) + al * dk));
+        w += chrow[c] * (T(0.5) * ch * Ex<T>::f(al * SC * dk) * (T(1) + al * dk));
       }
-      const T g = w * gd[k];
-      const T gx = g * u[k].x, gy = g * u[k].y, gz = g * u[k].z;
+      const T g = w * P1[k].w;
+      const T gx = g * P0[k].x, gy = g * P0[k].y, gz = g * P0[k].z;
       xtra[k * 3 + 0] = gx; xtra[k * 3 + 1] = gy; xtra[k * 3 + 2] = gz;
       fix -= gx; fiy -= gy; fiz -= gz;
     }
@@ -249,11 +286,11 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
         const int tk = tj[k];
         const T ch = e2[Fr * tk + c];
         if (ch == T(0)) continue;
-        const T al = a2[Fr * tk + c], dk = d[k];
-        const T ex = r_exp(al * dk);
+        const T al = a2[Fr * tk + c], dk = P1[k].z;
+        const T ex = Ex<T>::f(al * SC * dk);
         T va;
         if (MODE == MODE_FGRAD) {
-          const T q = T(0.5) * gd[k] * xtra[k * 4 + 3];
+          const T q = T(0.5) * P1[k].w * xtra[k * 4 + 3];
           gn += q * ch * ex * (T(1) + al * dk);
           va = q * cin * ch * ex * dk * (T(2) + al * dk);
         } else {
@@ -288,7 +325,8 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
         if (q == ta) na_ = cnt[q];
         if (q == tb) nb_ = cnt[q];
       }
-      const int np = (ta == tb) ? na_ * (na_ - 1) / 2 : na_ * nb_;
+      const bool same = (ta == tb);
+      const int np = same ? na_ * (na_ - 1) / 2 : na_ * nb_;
       if (np <= 0 || s >= md.ncls) continue;
       const unsigned char* la = lst + ta * nr;
       const unsigned char* lb = lst + tb * nr;
@@ -308,130 +346,183 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
           const int c = actl[c0 + lane];
           const T* al = a3 + (s * Fa + c) * 3;
           const T ee = e3[s * Fa + c];
-          chp[lane * 8 + 0] = al[0];
-          chp[lane * 8 + 1] = al[1];
-          chp[lane * 8 + 2] = al[2];
-          if (MODE == MODE_AF) chp[lane * 8 + 3] = T(0.5) * ee;
-          if (MODE == MODE_FORCE) chp[lane * 8 + 3] = T(0.5) * chrow[Fr + c] * ee;
-          if (MODE == MODE_FGRAD) { chp[lane * 8 + 3] = T(0.5) * ee; chp[lane * 8 + 4] = chrow[Fr + c]; }
-          if (MODE == MODE_AFGRAD) chp[lane * 8 + 3] = T(0.5) * chrow[Fr + c] * ee;
+          T4 pa;
+          pa.x = al[0]; pa.y = al[1]; pa.z = al[2]; pa.w = al[2] * SC;
+          chpa[lane] = pa;
+          T2 pb;
+          pb.x = T(0); pb.y = T(0);
+          if (MODE == MODE_AF) pb.x = T(0.5) * ee;
+          if (MODE == MODE_FORCE) pb.x = T(0.25) * chrow[Fr + c] * ee;
+          if (MODE == MODE_FGRAD) { pb.x = T(0.5) * ee; pb.y = chrow[Fr + c]; }
+          if (MODE == MODE_AFGRAD) pb.x = T(0.5) * chrow[Fr + c] * ee;
+          chpb[lane] = pb;
         }
         __syncwarp();
         // tables exp(a1*fc_k), exp(a2*fc_k) for the neighbours of the two species
-        const int nu = (ta == tb) ? na_ : na_ + nb_;
+        const int nu = same ? na_ : na_ + nb_;
         for (int q = lane; q < nch * nu; q += 32) {
           const int l = q / nu, r = q - l * nu;
           const int k = (r < na_) ? la[r] : lb[r - na_];
+          const T fck = P0[k].w;
           T2 v;
-          v.x = r_exp(chp[l * 8 + 0] * fc[k]);
-          v.y = r_exp(chp[l * 8 + 1] * fc[k]);
+          v.x = Ex<T>::f(chpa[l].x * SC * fck);
+          v.y = Ex<T>::f(chpa[l].y * SC * fck);
           tab[l * nr + k] = v;
         }
         __syncwarp();
-        T r0[MAXCH], r1[MAXCH], r2[MAXCH], r3[MAXCH];
+
+        if (MODE == MODE_FORCE) {
+          // ordered pairs (owner j, partner k): each lane takes a contiguous run of the row-major
+          // list, keeps the owner's data and its force accumulator in registers and flushes when the
+          // row changes.  Two passes when the two species differ (owners of ta, then owners of tb).
+          const int npass = same ? 1 : 2;
+          for (int pass = 0; pass < npass; pass++) {
+            const unsigned char* lo = pass == 0 ? la : lb;
+            const unsigned char* lp = pass == 0 ? lb : la;
+            const int no = pass == 0 ? na_ : nb_;
+            const int npt = same ? na_ - 1 : (pass == 0 ? nb_ : na_);
+            const int E = no * npt;
+            const int cchunk = (E + 31) / 32;
+            int e0 = lane * cchunk, e1 = e0 + cchunk;
+            if (e1 > E) e1 = E;
+            if (e0 < e1) {
+              int ja = e0 / npt, kb = e0 - ja * npt;
+              int j = lo[ja];
+              T4 uj = P0[j];
+              T rinvj = P1[j].x, gfcj = P1[j].y;
+              T2 Aj[MAXCH];
 #pragma unroll
-        for (int l = 0; l < MAXCH; l++) r0[l] = r1[l] = r2[l] = r3[l] = T(0);
-        for (int p = lane; p < np; p += 32) {
-          int ja, kb;
-          if (ta == tb) unrank_pair(p, na_, ja, kb);
-          else { ja = p / nb_; kb = p - ja * nb_; }
-          const int j = la[ja], k = lb[kb];
-          const T4 uj = u[j], uk = u[k];
-          const T fcj = fc[j], fck = fc[k];
-          const T cs = uj.x * uk.x + uj.y * uk.y + uj.z * uk.z;
-          const T half = T(0.5) * (cs + T(1));
-          const T tt = half * fcj * fck;
-          T Q = T(0), Pj = T(0), Pk = T(0);
-          if (MODE == MODE_FGRAD) {
-            const T hf = T(0.5) * fcj * fck;
-            const T ajk = hf / uj.w, akj = hf / uk.w;
-            const T bjk = -cs * ajk + half * gfc[j] * fck;
-            const T bkj = -cs * akj + half * gfc[k] * fcj;
-            const T* dFj = xtra + j * 4;
-            const T* dFk = xtra + k * 4;
-            const T djuk = dFj[0] * uk.x + dFj[1] * uk.y + dFj[2] * uk.z;
-            const T dkuj = dFk[0] * uj.x + dFk[1] * uj.y + dFk[2] * uj.z;
-            Q = ajk * djuk + bjk * dFj[3] + akj * dkuj + bkj * dFk[3];
-            Pj = gfc[j] * dFj[3];
-            Pk = gfc[k] * dFk[3];
+              for (int l = 0; l < MAXCH; l++)
+                if (l < nch) Aj[l] = tab[l * nr + j];
+              T ax = T(0), ay = T(0), az = T(0), as = T(0);
+              for (int e = e0; e < e1; e++) {
+                const int kk = (same && kb >= ja) ? kb + 1 : kb;
+                const int k = lp[kk];
+                const T4 uk = P0[k];
+                const T cs = uj.x * uk.x + uj.y * uk.y + uj.z * uk.z;
+                const T half = T(0.5) * (cs + T(1));
+                const T tt = half * uj.w * uk.w;
+                T D = T(0), BJ = T(0);
+#pragma unroll
+                for (int l = 0; l < MAXCH; l++) {
+                  if (l < nch) {
+                    const T2 B = tab[l * nr + k];
+                    const T4 pa = chpa[l];
+                    const T S1 = Aj[l].y * B.x, S2 = Aj[l].x * B.y;
+                    const T ev = chpb[l].x * Ex<T>::f(pa.w * tt);
+                    D += ev * (T(1) + pa.z * tt) * (S1 + S2);
+                    BJ += ev * tt * (pa.x * S2 + pa.y * S1);
+                  }
+                }
+                // f_ij = cjk*u_k + cjj*u_j
+                const T cjk = D * T(0.5) * uj.w * uk.w * rinvj;
+                ax += cjk * uk.x; ay += cjk * uk.y; az += cjk * uk.z;
+                as += -cs * cjk + gfcj * (D * half * uk.w + BJ);
+                kb++;
+                if (kb == npt || e + 1 == e1) {
+                  const T fx = ax + as * uj.x, fy = ay + as * uj.y, fz = az + as * uj.z;
+                  atomicAdd(&xtra[j * 3 + 0], fx);
+                  atomicAdd(&xtra[j * 3 + 1], fy);
+                  atomicAdd(&xtra[j * 3 + 2], fz);
+                  fix -= fx; fiy -= fy; fiz -= fz;
+                  ax = ay = az = as = T(0);
+                  if (kb == npt && e + 1 < e1) {
+                    kb = 0;
+                    ja++;
+                    j = lo[ja];
+                    uj = P0[j];
+                    rinvj = P1[j].x;
+                    gfcj = P1[j].y;
+#pragma unroll
+                    for (int l = 0; l < MAXCH; l++)
+                      if (l < nch) Aj[l] = tab[l * nr + j];
+                  }
+                }
+              }
+            }
+            __syncwarp();
           }
-          T D = T(0), BJ = T(0), BK = T(0);
-          const T sj = fcj, sk = fck;
+        } else {
+          T r0[MAXCH], r1[MAXCH], r2[MAXCH], r3[MAXCH];
 #pragma unroll
-          for (int l = 0; l < MAXCH; l++) {
-            if (l < nch) {
-              const T2 A = tab[l * nr + j], B = tab[l * nr + k];
-              const T al1 = chp[l * 8 + 0], al2 = chp[l * 8 + 1], be = chp[l * 8 + 2], cf = chp[l * 8 + 3];
-              const T S1 = A.y * B.x;  // exp(a2*sj + a1*sk)
-              const T S2 = A.x * B.y;  // exp(a1*sj + a2*sk)
-              const T eb = r_exp(be * tt);
-              if (MODE == MODE_AF) {
-                r0[l] += cf * tt * (S1 + S2) * eb;
-              } else if (MODE == MODE_FORCE) {
-                D += cf * (eb * (T(1) + be * tt) * (S1 + S2) * T(0.5));
-                BJ += cf * ((al1 * S2 + al2 * S1) * eb * T(0.5) * tt);
-                BK += cf * ((al1 * S1 + al2 * S2) * eb * T(0.5) * tt);
-              } else if (MODE == MODE_AFGRAD) {
-                const T cm = cf * eb * tt;
-                r1[l] += cm * (S2 * sj + S1 * sk);
-                r2[l] += cm * (S2 * sk + S1 * sj);
-                r3[l] += cm * (S1 + S2) * tt;
-              } else {  // FGRAD
-                const T NG = chp[l * 8 + 4];
-                const T ss = S1 + S2, opb = T(1) + be * tt;
-                const T delta = eb * opb * ss * T(0.5);
-                const T et = eb * T(0.5) * tt;
-                const T Bj = (al1 * S2 + al2 * S1) * et, Bk = (al1 * S1 + al2 * S2) * et;
-                r0[l] += cf * (delta * Q + Bj * Pj + Bk * Pk);
-                const T hn = cf * NG;
-                const T ba1 = eb * opb * (S1 * sk + S2 * sj) * T(0.5);
-                const T ba2 = eb * opb * (S1 * sj + S2 * sk) * T(0.5);
-                const T bb = eb * tt * (T(2) + be * tt) * ss * T(0.5);
-                const T a1j = (S2 + al1 * S2 * sj + al2 * S1 * sk) * et;
-                const T a2j = (S1 + al2 * S1 * sj + al1 * S2 * sk) * et;
-                const T a1k = (S1 + al1 * S1 * sk + al2 * S2 * sj) * et;
-                const T a2k = (S2 + al2 * S2 * sk + al1 * S1 * sj) * et;
-                r1[l] += hn * (ba1 * Q + a1j * Pj + a1k * Pk);
-                r2[l] += hn * (ba2 * Q + a2j * Pj + a2k * Pk);
-                r3[l] += hn * (bb * Q + Bj * tt * Pj + Bk * tt * Pk);
+          for (int l = 0; l < MAXCH; l++) r0[l] = r1[l] = r2[l] = r3[l] = T(0);
+          PairStep ps;
+          ps.ja = ps.kb = 0;
+          const int q32 = same ? 0 : 32 / nb_, r32 = same ? 0 : 32 - q32 * nb_;
+          if (lane < np) {
+            if (same) ps.init_tri(lane, na_); else ps.init_rect(lane, nb_);
+          }
+          for (int p = lane; p < np; p += 32) {
+            const int j = la[ps.ja], k = lb[ps.kb];
+            if (same) ps.step_tri(na_); else ps.step_rect(nb_, q32, r32);
+            const T4 uj = P0[j], uk = P0[k];
+            const T fcj = uj.w, fck = uk.w;
+            const T cs = uj.x * uk.x + uj.y * uk.y + uj.z * uk.z;
+            const T half = T(0.5) * (cs + T(1));
+            const T tt = half * fcj * fck;
+            T Q = T(0), Pj = T(0), Pk = T(0);
+            if (MODE == MODE_FGRAD) {
+              const T4 pj = P1[j], pk = P1[k];
+              const T hf = T(0.5) * fcj * fck;
+              const T ajk = hf * pj.x, akj = hf * pk.x;
+              const T bjk = -cs * ajk + half * pj.y * fck;
+              const T bkj = -cs * akj + half * pk.y * fcj;
+              const T4 dFj = *reinterpret_cast<const T4*>(xtra + j * 4);
+              const T4 dFk = *reinterpret_cast<const T4*>(xtra + k * 4);
+              const T djuk = dFj.x * uk.x + dFj.y * uk.y + dFj.z * uk.z;
+              const T dkuj = dFk.x * uj.x + dFk.y * uj.y + dFk.z * uj.z;
+              Q = ajk * djuk + bjk * dFj.w + akj * dkuj + bkj * dFk.w;
+              Pj = pj.y * dFj.w;
+              Pk = pk.y * dFk.w;
+            }
+#pragma unroll
+            for (int l = 0; l < MAXCH; l++) {
+              if (l < nch) {
+                const T2 A = tab[l * nr + j], B = tab[l * nr + k];
+                const T4 pa = chpa[l];
+                const T S1 = A.y * B.x;  // exp(a2*sj + a1*sk)
+                const T S2 = A.x * B.y;  // exp(a1*sj + a2*sk)
+                const T eb = Ex<T>::f(pa.w * tt);
+                if (MODE == MODE_AF) {
+                  r0[l] += tt * (S1 + S2) * eb;  // the channel coefficient is applied after the reduction
+                } else if (MODE == MODE_AFGRAD) {
+                  const T cm = eb * tt;
+                  r1[l] += cm * (S2 * fcj + S1 * fck);
+                  r2[l] += cm * (S2 * fck + S1 * fcj);
+                  r3[l] += cm * (S1 + S2) * tt;
+                } else {  // FGRAD
+                  const T al1 = pa.x, al2 = pa.y, be = pa.z;
+                  const T ss = S1 + S2, opb = T(1) + be * tt;
+                  const T et = eb * T(0.5) * tt;
+                  const T eo = eb * opb * T(0.5);
+                  const T Bj = (al1 * S2 + al2 * S1) * et, Bk = (al1 * S1 + al2 * S2) * et;
+                  r0[l] += eo * ss * Q + Bj * Pj + Bk * Pk;
+                  const T a1j = (S2 + al1 * S2 * fcj + al2 * S1 * fck) * et;
+                  const T a2j = (S1 + al2 * S1 * fcj + al1 * S2 * fck) * et;
+                  const T a1k = (S1 + al1 * S1 * fck + al2 * S2 * fcj) * et;
+                  const T a2k = (S2 + al2 * S2 * fck + al1 * S1 * fcj) * et;
+                  r1[l] += eo * (S1 * fck + S2 * fcj) * Q + a1j * Pj + a1k * Pk;
+                  r2[l] += eo * (S1 * fcj + S2 * fck) * Q + a2j * Pj + a2k * Pk;
+                  r3[l] += eb * tt * (T(2) + be * tt) * ss * T(0.5) * Q + tt * (Bj * Pj + Bk * Pk);
+                }
               }
             }
           }
-          if (MODE == MODE_FORCE) {
-            const T hf = T(0.5) * fcj * fck;
-            const T ajk = hf / uj.w, akj = hf / uk.w;
-            const T bjk = -cs * ajk + half * gfc[j] * fck;
-            const T bkj = -cs * akj + half * gfc[k] * fcj;
-            // f_ij = D*(ajk*uk + bjk*uj) + BJ*gfc_j*uj ; f_ik likewise
-            const T cjk = D * ajk, cjj = D * bjk + BJ * gfc[j];
-            const T ckj = D * akj, ckk = D * bkj + BK * gfc[k];
-            const T fjx = cjk * uk.x + cjj * uj.x, fjy = cjk * uk.y + cjj * uj.y, fjz = cjk * uk.z + cjj * uj.z;
-            const T fkx = ckj * uj.x + ckk * uk.x, fky = ckj * uj.y + ckk * uk.y, fkz = ckj * uj.z + ckk * uk.z;
-            atomicAdd(&xtra[j * 3 + 0], fjx);
-            atomicAdd(&xtra[j * 3 + 1], fjy);
-            atomicAdd(&xtra[j * 3 + 2], fjz);
-            atomicAdd(&xtra[k * 3 + 0], fkx);
-            atomicAdd(&xtra[k * 3 + 1], fky);
-            atomicAdd(&xtra[k * 3 + 2], fkz);
-            fix -= fjx + fkx;
-            fiy -= fjy + fky;
-            fiz -= fjz + fkz;
-          }
-        }
-        if (MODE != MODE_FORCE) {
 #pragma unroll
           for (int l = 0; l < MAXCH; l++) {
             if (l < nch) {
               const int c = actl[c0 + l];
+              const T cf = chpb[l].x;
               if (MODE == MODE_AF || MODE == MODE_FGRAD) {
                 const T v = warp_sum(r0[l]);
-                if (lane == 0) acc[ACC_GN + c] += v;
+                if (lane == 0) acc[ACC_GN + c] += cf * v;
               }
               if (MODE == MODE_AFGRAD || MODE == MODE_FGRAD) {
+                const T hn = MODE == MODE_FGRAD ? cf * chpb[l].y : cf;
                 const T v1 = warp_sum(r1[l]), v2 = warp_sum(r2[l]), v3 = warp_sum(r3[l]);
                 if (lane == 0) {
                   T* g = acc + ACC_A3 + (s * md.Famax + c) * 3;
-                  g[0] += v1; g[1] += v2; g[2] += v3;
+                  g[0] += hn * v1; g[1] += hn * v2; g[2] += hn * v3;
                 }
               }
             }
@@ -477,225 +568,290 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
 
 // ---------------------------------------------------------------------------- MLP head
 // x = log(AF+1e-3) - mu ; Dense(tanh)... Dense(1)  (staf_models/staf_model.py:188-191,
-// libstaf/src/mlp/staf_mlp_ort.cc:196-242).  One warp per atom; weights stream through L1/L2.
-template <class T>
-__device__ __forceinline__ void mlp_forward(const ModelDev& md, int t, int lane, const T* __restrict__ w,
-                                            const T* x, T* h /*[Hsum]*/) {
-  const int Lq = md.n_dense;
-  const T* hin = x;
+// libstaf/src/mlp/staf_mlp_ort.cc:196-242).  A block of 256 threads owns TA = 8*APT atoms of one
+// species; activations live in shared memory feature-major ([feature][atom]) so that a thread holds
+// APT atoms in registers while it streams one weight column, coalesced, from global memory.
+
+// Y[j][a] = act( b[j] + sum_i X[i][a] W[i,j] ), a in the thread's APT atoms, j over lanes
+template <class T, int APT, bool TANH, bool BIAS>
+__device__ __forceinline__ void dense_fwd(int in, int out, const T* __restrict__ Wl, const T* __restrict__ Bl,
+                                          const T* X, T* Y) {
+  constexpr int TA = 8 * APT;
+  const int jl = threadIdx.x & 31, ag = threadIdx.x >> 5;
+  for (int j0 = 0; j0 < out; j0 += 32) {
+    const int j = j0 + jl;
+    if (j < out) {
+      T a[APT];
+      const T bj = BIAS ? Bl[j] : T(0);
+#pragma unroll
+      for (int q = 0; q < APT; q++) a[q] = bj;
+      for (int i = 0; i < in; i++) {
+        const T w = Wl[i * out + j];
+        const T* xp = X + i * TA + ag * APT;
+#pragma unroll
+        for (int q = 0; q < APT; q++) a[q] += xp[q] * w;
+      }
+#pragma unroll
+      for (int q = 0; q < APT; q++) Y[j * TA + ag * APT + q] = TANH ? r_tanh(a[q]) : a[q];
+    }
+  }
+}
+
+// Xo[i][a] = sum_j D[j][a] W[i,j]  (and the same for a second cotangent D2 -> Xo2 when given).
+// W is staged through shared memory in column chunks; the transposed access is then conflict-free.
+template <class T, int APT>
+__device__ __forceinline__ void dense_bwd(int in, int out, const T* __restrict__ Wl, const T* D, T* Xo, const T* D2,
+                                          T* Xo2, T* wt /*[in][33]*/) {
+  constexpr int TA = 8 * APT;
+  const int il = threadIdx.x & 31, ag = threadIdx.x >> 5;
+  __syncthreads();
+  for (int i0 = 0; i0 < in; i0 += 32) {
+    const int i = i0 + il;
+    if (i < in) {
+#pragma unroll
+      for (int q = 0; q < APT; q++) {
+        Xo[i * TA + ag * APT + q] = T(0);
+        if (D2) Xo2[i * TA + ag * APT + q] = T(0);
+      }
+    }
+  }
+  for (int j0 = 0; j0 < out; j0 += 32) {
+    const int jc = (out - j0) < 32 ? (out - j0) : 32;
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < in * jc; idx += ML_THREADS) {
+      const int i = idx / jc, jj = idx - i * jc;
+      wt[i * 33 + jj] = Wl[i * out + j0 + jj];
+    }
+    __syncthreads();
+    for (int i0 = 0; i0 < in; i0 += 32) {
+      const int i = i0 + il;
+      if (i < in) {
+        T a[APT], a2[APT];
+#pragma unroll
+        for (int q = 0; q < APT; q++) a[q] = a2[q] = T(0);
+        for (int jj = 0; jj < jc; jj++) {
+          const T w = wt[i * 33 + jj];
+          const T* dp = D + (j0 + jj) * TA + ag * APT;
+#pragma unroll
+          for (int q = 0; q < APT; q++) a[q] += dp[q] * w;
+          if (D2) {
+            const T* dp2 = D2 + (j0 + jj) * TA + ag * APT;
+#pragma unroll
+            for (int q = 0; q < APT; q++) a2[q] += dp2[q] * w;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < APT; q++) {
+          Xo[i * TA + ag * APT + q] += a[q];
+          if (D2) Xo2[i * TA + ag * APT + q] += a2[q];
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
+
+template <class T, int APT>
+__global__ void __launch_bounds__(ML_THREADS)
+    k_mlp_fwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ af, T* __restrict__ acts,
+              T* __restrict__ e_atom, T* __restrict__ netderiv) {
+  constexpr int TA = 8 * APT;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  int t, q0;
+  locate_block(md, nf, TA, t, q0);
+  const int nat = nf * md.tipos[t];
+  const int F = md.Fr[t] + md.Fa[t], Lq = md.n_dense, Fm = md.Fmax, Hs = md.Hsum, mw = md.maxw;
+  T* X = reinterpret_cast<T*>(smem_raw);  // [Fm][TA]
+  T* H = X + Fm * TA;                     // [Hs][TA]
+  T* C0 = H + Hs * TA;                    // [mw][TA]
+  T* C1 = C0 + mw * TA;                   // [mw][TA]
+  T* wt = C1 + mw * TA;                   // [mw][33]
+  const T* mu = theta + md.off_mu[t];
+  const T* w = theta + md.off_w[t];
+  auto gidx = [&](int a) -> long long {
+    const int q = q0 + a;
+    if (q >= nat) return -1;
+    const int b = q / md.tipos[t];
+    return (long long)b * md.N + md.shift[t] + (q - b * md.tipos[t]);
+  };
+  for (int idx = threadIdx.x; idx < F * TA; idx += ML_THREADS) {
+    const int a = idx % TA, i = idx / TA;
+    const long long gi = gidx(a);
+    X[i * TA + a] = gi >= 0 ? r_log(af[gi * Fm + i] + T(1e-3)) - mu[i] : T(0);
+  }
+  __syncthreads();
+  const T* hin = X;
   for (int l = 0; l < Lq; l++) {
     const int in = md.in_of(t, l), out = md.width[l];
     const T* Wl = w + md.w_off(t, l);
-    const T* Bl = Wl + in * out;
-    T* hout = h + md.h_off(l);
-    for (int j = lane; j < out; j += 32) {
-      T s = Bl[j];
-      for (int q = 0; q < in; q++) s += hin[q] * Wl[q * out + j];
-      if (l < Lq - 1) s = r_tanh(s);
-      hout[j] = s;
-    }
-    __syncwarp();
+    T* hout = H + md.h_off(l) * TA;
+    if (l < Lq - 1) dense_fwd<T, APT, true, true>(in, out, Wl, Wl + in * out, hin, hout);
+    else dense_fwd<T, APT, false, true>(in, out, Wl, Wl + in * out, hin, hout);
+    __syncthreads();
     hin = hout;
   }
-}
-
-// y[i] = sum_j v[j] * W[i,j]  for i < in (row-major [in,out]); coalesced over j, reduced per row
-template <class T>
-__device__ __forceinline__ void matvec_t(int lane, const T* __restrict__ Wl, int in, int out, const T* v, T* y) {
-  for (int q = 0; q < in; q++) {
-    T s = T(0);
-    for (int j = lane; j < out; j += 32) s += v[j] * Wl[q * out + j];
-    s = warp_sum(s);
-    if (lane == 0) y[q] = s;
+  // activations, block-local feature-major copy for the backward kernel
+  T* ab = acts + (size_t)blockIdx.x * Hs * TA;
+  for (int idx = threadIdx.x; idx < Hs * TA; idx += ML_THREADS) ab[idx] = H[idx];
+  if (threadIdx.x < TA) {
+    const long long gi = gidx(threadIdx.x);
+    if (gi >= 0) e_atom[gi] = H[md.h_off(Lq - 1) * TA + threadIdx.x];
   }
-  __syncwarp();
-}
-
-template <class T>
-__global__ void __launch_bounds__(ML_WARPS * 32)
-    k_mlp_fwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ af, T* __restrict__ acts,
-              T* __restrict__ e_atom, T* __restrict__ netderiv) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int t, b, i;
-  if (!locate_atom(md, nf, ML_WARPS, warp, t, b, i)) return;
-  const int per = md.Fmax + md.Hsum + 2 * md.maxw;
-  T* x = reinterpret_cast<T*>(smem_raw) + (size_t)warp * per;
-  T* h = x + md.Fmax;
-  T* p0 = h + md.Hsum;
-  T* p1 = p0 + md.maxw;
-  const int F = md.Fr[t] + md.Fa[t], Lq = md.n_dense;
-  const size_t gi = (size_t)b * md.N + i;
-  const T* mu = theta + md.off_mu[t];
-  const T* w = theta + md.off_w[t];
-  for (int q = lane; q < F; q += 32) x[q] = r_log(af[gi * md.Fmax + q] + T(1e-3)) - mu[q];
-  __syncwarp();
-  mlp_forward(md, t, lane, w, x, h);
-  for (int q = lane; q < md.Hsum; q += 32) acts[gi * md.Hsum + q] = h[q];
-  if (lane == 0) e_atom[gi] = h[md.h_off(Lq - 1)];
-  // de/dx by the reverse sweep
-  T* pn = p0;  // cotangent on the output of layer l
-  T* pc = p1;
-  if (lane == 0) pn[0] = T(1);
-  __syncwarp();
+  // de/dx by the reverse sweep: cn = cotangent on the output of layer l
+  T* cn = C0;
+  T* cp = C1;
+  if (threadIdx.x < TA) cn[threadIdx.x] = T(1);
+  __syncthreads();
   for (int l = Lq - 1; l >= 0; l--) {
     const int in = md.in_of(t, l), out = md.width[l];
     if (l < Lq - 1) {
-      const T* hl = h + md.h_off(l);
-      for (int j = lane; j < out; j += 32) pn[j] *= (T(1) - hl[j] * hl[j]);
-      __syncwarp();
+      const T* hl = H + md.h_off(l) * TA;
+      for (int idx = threadIdx.x; idx < out * TA; idx += ML_THREADS) cn[idx] *= (T(1) - hl[idx] * hl[idx]);
     }
-    matvec_t(lane, w + md.w_off(t, l), in, out, pn, pc);
-    T* tmp = pn; pn = pc; pc = tmp;
+    dense_bwd<T, APT>(in, out, w + md.w_off(t, l), cn, cp, nullptr, nullptr, wt);
+    T* tmp = cn; cn = cp; cp = tmp;
   }
-  for (int q = lane; q < md.Fmax; q += 32)
-    netderiv[gi * md.Fmax + q] = (q < F) ? pn[q] / (af[gi * md.Fmax + q] + T(1e-3)) : T(0);
+  for (int idx = threadIdx.x; idx < Fm * TA; idx += ML_THREADS) {
+    const int a = idx % TA, i = idx / TA;
+    const long long gi = gidx(a);
+    if (gi >= 0) netderiv[gi * Fm + i] = (i < F) ? cn[i * TA + a] / (af[gi * Fm + i] + T(1e-3)) : T(0);
+  }
 }
 
 // Backward of  S = sum_a ebar[a]*e[a] + sum_{a,c} u[a,c]*netderiv[a,c]  with respect to the
 // weights, mu and AF: the first term is plain back-propagation, the second is the derivative
 // of a directional derivative (tangent v = u/(AF+eps) pushed forward, then reversed) - what
 // TensorFlow's autodiff does through grad_ene for the force loss (staf_model.py:191,225-228).
-template <class T>
-__global__ void __launch_bounds__(ML_WARPS * 32)
+template <class T, int APT>
+__global__ void __launch_bounds__(ML_THREADS)
     k_mlp_bwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ af,
               const T* __restrict__ acts, const T* __restrict__ ebar /*[nf]*/, const T* __restrict__ u /*[nf,N,Fmax]*/,
               T* __restrict__ gaf, T* __restrict__ grad) {
+  constexpr int TA = 8 * APT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int t, b, i;
-  const bool active = locate_atom(md, nf, ML_WARPS, warp, t, b, i);
-  // locate_atom leaves t valid for the whole block (blocks are species-homogeneous)
-  const int Fm = md.Fmax, Hs = md.Hsum, mw = md.maxw;
-  const int per = 3 * Fm + 5 * Hs + 2 * mw;
-  T* x = reinterpret_cast<T*>(smem_raw) + (size_t)warp * per;
-  T* v = x + Fm;      // tangent on x
-  T* q0 = v + Fm;     // dS/dx
-  T* h = q0 + Fm;     // activations (outputs of every Dense)
-  T* hd = h + Hs;     // tangents of the activations
-  T* ad = hd + Hs;    // tangents of the pre-activations
-  T* dq = ad + Hs;    // cotangent on the pre-activation (first-order channel)
-  T* dp = dq + Hs;    // cotangent on the pre-activation tangent
-  T* c0 = dp + Hs;    // scratch [maxw]
-  T* c1 = c0 + mw;
-  const int F = md.Fr[t] + md.Fa[t], Lq = md.n_dense;
+  int t, q0;
+  locate_block(md, nf, TA, t, q0);
+  const int nat = nf * md.tipos[t];
+  const int F = md.Fr[t] + md.Fa[t], Lq = md.n_dense, Fm = md.Fmax, Hs = md.Hsum, mw = md.maxw;
+  T* X = reinterpret_cast<T*>(smem_raw);  // [Fm][TA] x
+  T* V = X + Fm * TA;                     // [Fm][TA] tangent on x
+  T* H = V + Fm * TA;                     // [Hs][TA] activations
+  T* HD = H + Hs * TA;                    // tangents of the activations
+  T* AD = HD + Hs * TA;                   // tangents of the pre-activations
+  T* DQ = AD + Hs * TA;                   // cotangent on the pre-activation (first-order channel)
+  T* DP = DQ + Hs * TA;                   // cotangent on the pre-activation tangent
+  T* CQ = DP + Hs * TA;                   // [mw][TA]
+  T* CP = CQ + mw * TA;                   // [mw][TA]
+  T* wt = CP + mw * TA;                   // [mw][33]
+  const T* mu = theta + md.off_mu[t];
   const T* w = theta + md.off_w[t];
-  const size_t gi = active ? (size_t)b * md.N + i : 0;
-  if (active) {
-    const T* mu = theta + md.off_mu[t];
-    for (int q = lane; q < F; q += 32) {
-      const T den = af[gi * Fm + q] + T(1e-3);
-      x[q] = r_log(den) - mu[q];
-      v[q] = u[gi * Fm + q] / den;
+  auto gidx = [&](int a) -> long long {
+    const int q = q0 + a;
+    if (q >= nat) return -1;
+    const int b = q / md.tipos[t];
+    return (long long)b * md.N + md.shift[t] + (q - b * md.tipos[t]);
+  };
+  for (int idx = threadIdx.x; idx < F * TA; idx += ML_THREADS) {
+    const int a = idx % TA, i = idx / TA;
+    const long long gi = gidx(a);
+    T xv = T(0), vv = T(0);
+    if (gi >= 0) {
+      const T den = af[gi * Fm + i] + T(1e-3);
+      xv = r_log(den) - mu[i];
+      vv = u[gi * Fm + i] / den;
     }
-    for (int q = lane; q < Hs; q += 32) h[q] = acts[gi * Hs + q];
-    __syncwarp();
-    // forward tangent
-    const T* hdin = v;
-    for (int l = 0; l < Lq; l++) {
-      const int in = md.in_of(t, l), out = md.width[l];
-      const T* Wl = w + md.w_off(t, l);
-      T* ho = h + md.h_off(l);
-      T* hdo = hd + md.h_off(l);
-      T* ado = ad + md.h_off(l);
-      for (int j = lane; j < out; j += 32) {
-        T s = T(0);
-        for (int q = 0; q < in; q++) s += hdin[q] * Wl[q * out + j];
-        ado[j] = s;
-        hdo[j] = (l < Lq - 1) ? s * (T(1) - ho[j] * ho[j]) : s;
-      }
-      __syncwarp();
-      hdin = hdo;
-    }
-    // reverse over (h, hd): cq = cotangent on h[l+1], cp = cotangent on hd[l+1]
-    T* cq = c0;
-    T* cp = c1;
-    if (lane == 0) { cq[0] = ebar[b]; cp[0] = T(1); }
-    __syncwarp();
-    for (int l = Lq - 1; l >= 0; l--) {
-      const int in = md.in_of(t, l), out = md.width[l];
-      const T* Wl = w + md.w_off(t, l);
-      const T* ho = h + md.h_off(l);
-      const T* ado = ad + md.h_off(l);
-      T* dql = dq + md.h_off(l);
-      T* dpl = dp + md.h_off(l);
-      for (int j = lane; j < out; j += 32) {
-        T qa, pa;
-        if (l < Lq - 1) {
-          const T hh = ho[j], d1 = T(1) - hh * hh;
-          pa = cp[j] * d1;
-          qa = cq[j] * d1 + cp[j] * (T(-2) * hh * d1 * ado[j]);
-        } else {
-          pa = cp[j];
-          qa = cq[j];
-        }
-        dql[j] = qa;
-        dpl[j] = pa;
-      }
-      __syncwarp();
-      // propagate to the layer input: cq_in = W dq, cp_in = W dp  (reuse cq/cp as outputs)
-      for (int q = 0; q < in; q++) {
-        T s1 = T(0), s2 = T(0);
-        for (int j = lane; j < out; j += 32) {
-          const T wv = Wl[q * out + j];
-          s1 += dql[j] * wv;
-          s2 += dpl[j] * wv;
-        }
-        s1 = warp_sum(s1);
-        s2 = warp_sum(s2);
-        if (lane == 0) {
-          if (l == 0) { q0[q] = s1; c1[q] = s2; }  // dS/dx, dS/dv
-          else { cq[q] = s1; cp[q] = s2; }
-        }
-      }
-      __syncwarp();
-    }
-    // dS/dAF: through x = log(AF+eps) - mu and through v = u/(AF+eps)
-    for (int q = lane; q < Fm; q += 32) {
-      T g = T(0);
-      if (q < F) {
-        const T den = af[gi * Fm + q] + T(1e-3);
-        g = q0[q] / den + c1[q] * (-u[gi * Fm + q] / (den * den));
-      }
-      gaf[gi * Fm + q] = g;
-    }
-  } else {
-    for (int q = lane; q < Fm; q += 32) { x[q] = T(0); v[q] = T(0); q0[q] = T(0); }
-    for (int q = lane; q < Hs; q += 32) { h[q] = hd[q] = dq[q] = dp[q] = T(0); }
+    X[idx] = xv;
+    V[idx] = vv;
+  }
+  const T* ab = acts + (size_t)blockIdx.x * Hs * TA;
+  for (int idx = threadIdx.x; idx < Hs * TA; idx += ML_THREADS) {
+    const int a = idx % TA;
+    H[idx] = (q0 + a < nat) ? ab[idx] : T(0);
   }
   __syncthreads();
-  // cooperative weight gradient over the atoms of this block (same species), one coalesced
-  // atomic per weight per block
-  T* gw = grad + md.off_w[t];
-  const T* S = reinterpret_cast<const T*>(smem_raw);
+  // forward tangent: AD = HDin W ; HD = AD * act'
+  const T* hdin = V;
   for (int l = 0; l < Lq; l++) {
     const int in = md.in_of(t, l), out = md.width[l];
-    const int woff = md.w_off(t, l), ho = md.h_off(l);
-    const int hin_off = (l == 0) ? 0 : 3 * Fm + md.h_off(l - 1);            // x or h[l-1]
-    const int hdin_off = (l == 0) ? Fm : 3 * Fm + Hs + md.h_off(l - 1);     // v or hd[l-1]
-    const int dq_off = 3 * Fm + 3 * Hs + ho, dp_off = 3 * Fm + 4 * Hs + ho;
-    for (int idx = threadIdx.x; idx < in * out + out; idx += ML_WARPS * 32) {
+    T* ado = AD + md.h_off(l) * TA;
+    T* hdo = HD + md.h_off(l) * TA;
+    dense_fwd<T, APT, false, false>(in, out, w + md.w_off(t, l), nullptr, hdin, ado);
+    __syncthreads();
+    const T* ho = H + md.h_off(l) * TA;
+    for (int idx = threadIdx.x; idx < out * TA; idx += ML_THREADS)
+      hdo[idx] = (l < Lq - 1) ? ado[idx] * (T(1) - ho[idx] * ho[idx]) : ado[idx];
+    __syncthreads();
+    hdin = hdo;
+  }
+  // reverse over (h, hd)
+  if (threadIdx.x < TA) {
+    const long long gi = gidx(threadIdx.x);
+    CQ[threadIdx.x] = gi >= 0 ? ebar[gi / md.N] : T(0);
+    CP[threadIdx.x] = gi >= 0 ? T(1) : T(0);
+  }
+  __syncthreads();
+  T* gw = grad + md.off_w[t];
+  for (int l = Lq - 1; l >= 0; l--) {
+    const int in = md.in_of(t, l), out = md.width[l];
+    const T* Wl = w + md.w_off(t, l);
+    const T* ho = H + md.h_off(l) * TA;
+    const T* ado = AD + md.h_off(l) * TA;
+    T* dql = DQ + md.h_off(l) * TA;
+    T* dpl = DP + md.h_off(l) * TA;
+    for (int idx = threadIdx.x; idx < out * TA; idx += ML_THREADS) {
+      T qa, pa;
+      if (l < Lq - 1) {
+        const T hh = ho[idx], d1 = T(1) - hh * hh;
+        pa = CP[idx] * d1;
+        qa = CQ[idx] * d1 + CP[idx] * (T(-2) * hh * d1 * ado[idx]);
+      } else {
+        pa = CP[idx];
+        qa = CQ[idx];
+      }
+      dql[idx] = qa;
+      dpl[idx] = pa;
+    }
+    __syncthreads();
+    // weight and bias gradients of this layer, summed over the block's atoms
+    const T* hin = (l == 0) ? X : H + md.h_off(l - 1) * TA;
+    const T* hdi = (l == 0) ? V : HD + md.h_off(l - 1) * TA;
+    const int woff = md.w_off(t, l);
+    for (int idx = threadIdx.x; idx < in * out + out; idx += ML_THREADS) {
       T g = T(0);
       if (idx < in * out) {
         const int q = idx / out, j = idx - q * out;
-#pragma unroll
-        for (int a = 0; a < ML_WARPS; a++) {
-          const T* A = S + (size_t)a * per;
-          g += A[hin_off + q] * A[dq_off + j] + A[hdin_off + q] * A[dp_off + j];
-        }
+        const T* hp = hin + q * TA;
+        const T* hdp = hdi + q * TA;
+        const T* qp = dql + j * TA;
+        const T* pp = dpl + j * TA;
+#pragma unroll 8
+        for (int a = 0; a < TA; a++) g += hp[a] * qp[a] + hdp[a] * pp[a];
       } else {
-        const int j = idx - in * out;
-#pragma unroll
-        for (int a = 0; a < ML_WARPS; a++) g += S[(size_t)a * per + dq_off + j];
+        const T* qp = dql + (idx - in * out) * TA;
+#pragma unroll 8
+        for (int a = 0; a < TA; a++) g += qp[a];
       }
       atomicAdd(gw + woff + idx, g);
     }
+    // cotangents on the layer input
+    dense_bwd<T, APT>(in, out, Wl, dql, CQ, dpl, CP, wt);
   }
-  for (int q = threadIdx.x; q < F; q += ML_WARPS * 32) {
+  // CQ = dS/dx, CP = dS/dv
+  for (int idx = threadIdx.x; idx < Fm * TA; idx += ML_THREADS) {
+    const int a = idx % TA, i = idx / TA;
+    const long long gi = gidx(a);
+    if (gi < 0) continue;
     T g = T(0);
-#pragma unroll
-    for (int a = 0; a < ML_WARPS; a++) g -= S[(size_t)a * per + 2 * Fm + q];
-    atomicAdd(grad + md.off_mu[t] + q, g);
+    if (i < F) {
+      const T den = af[gi * Fm + i] + T(1e-3);
+      g = CQ[idx] / den + CP[idx] * (-u[gi * Fm + i] / (den * den));
+    }
+    gaf[gi * Fm + i] = g;
+  }
+  for (int i = threadIdx.x; i < F; i += ML_THREADS) {
+    T g = T(0);
+    for (int a = 0; a < TA; a++) g -= CQ[i * TA + a];
+    atomicAdd(grad + md.off_mu[t] + i, g);
   }
 }
 
@@ -705,67 +861,78 @@ __device__ __forceinline__ T huber(T e) { T a = r_abs(e); return a <= T(1) ? T(0
 template <class T>
 __device__ __forceinline__ T huber_d(T e) { return e > T(1) ? T(1) : (e < T(-1) ? T(-1) : e); }
 
-// one block per frame: E_b = 0.5 * mean_i e_i (or 0.5 * sum), energy loss and its cotangent
+// zero-fills up to three buffers (sizes in bytes, multiples of 4) in one launch
+__global__ void k_zero3(void* a, size_t na, void* b, size_t nb, void* c, size_t nc) {
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  for (size_t q = tid; q < na / 4; q += st) reinterpret_cast<int*>(a)[q] = 0;
+  for (size_t q = tid; q < nb / 4; q += st) reinterpret_cast<int*>(b)[q] = 0;
+  for (size_t q = tid; q < nc / 4; q += st) reinterpret_cast<int*>(c)[q] = 0;
+}
+
+// One launch for everything between the force sweep and the backward sweeps.  Blocks [0,nf):
+// frame energy E_b = 0.5*mean_i e_i (or 0.5*sum), energy loss and the cotangent on the atomic
+// energies.  Blocks [nf, nf+fb): force loss and dL/dF.  Last block: bound loss
+// sum(alpha*[alpha>bound]) over alpha2b and alpha3b (Keras ReLU(threshold):
+// staf_models/staf_model.py:60-62,215-219) and its gradient.  The block that finishes last adds up
+// the total.  losses = {loss, loss_e, loss_bound, loss_f, done-counter}.
 template <class T>
-__global__ void k_energy(int N, int nf, int per_atom, const T* __restrict__ e_atom, T* __restrict__ energy,
-                         const T* __restrict__ e_label, T pe, int loss_kind, T* __restrict__ ebar,
-                         double* __restrict__ losses, int* __restrict__ status) {
+__global__ void __launch_bounds__(256)
+    k_loss(ModelDev md, int nf, int fb, int per_atom, int train, const T* __restrict__ e_atom, T* __restrict__ energy,
+           const T* __restrict__ e_label, const T* __restrict__ force, const T* __restrict__ f_label,
+           const T* __restrict__ theta, T pe, T pf, T pb, T bound, int loss_kind, T* __restrict__ ebar,
+           T* __restrict__ fbar, T* __restrict__ grad, double* __restrict__ losses, int* __restrict__ status) {
   __shared__ double red[9];
-  const int b = blockIdx.x;
-  double s = 0.0;
-  for (int q = threadIdx.x; q < N; q += blockDim.x) s += (double)e_atom[(size_t)b * N + q];
-  s = block_sum<double, 8>(s, red);
-  if (threadIdx.x == 0) {
-    const double Eb = per_atom ? 0.5 * s / N : 0.5 * s;
-    if (!isfinite(Eb)) set_status(status, STAFB_ERR_NONFINITE);
-    if (energy) energy[b] = (T)Eb;
-    if (e_label) {
-      const T e = (T)Eb - e_label[b];
-      const T le = loss_kind == 0 ? huber(e) : e * e;
-      const T de = loss_kind == 0 ? huber_d(e) : T(2) * e;
-      atomicAdd(losses + 1, (double)le / nf);
-      // cotangent on every atomic energy of the frame
-      ebar[b] = pe * de / T(nf) * T(0.5) / (per_atom ? T(N) : T(1));
+  const int N = md.N;
+  const int blk = blockIdx.x;
+  if (blk < nf) {
+    double s = 0.0;
+    for (int q = threadIdx.x; q < N; q += blockDim.x) s += (double)e_atom[(size_t)blk * N + q];
+    s = block_sum<double, 8>(s, red);
+    if (threadIdx.x == 0) {
+      const double Eb = per_atom ? 0.5 * s / N : 0.5 * s;
+      if (!isfinite(Eb)) set_status(status, STAFB_ERR_NONFINITE);
+      if (energy) energy[blk] = (T)Eb;
+      if (train) {
+        const T e = (T)Eb - e_label[blk];
+        const T le = loss_kind == 0 ? huber(e) : e * e;
+        const T de = loss_kind == 0 ? huber_d(e) : T(2) * e;
+        atomicAdd(losses + 1, (double)le / nf);
+        ebar[blk] = pe * de / T(nf) * T(0.5) / (per_atom ? T(N) : T(1));
+      }
+    }
+  } else if (blk < nf + fb) {
+    const size_t n = (size_t)nf * 3 * N;
+    double s = 0.0;
+    const T scale = pf / T((double)n);
+    for (size_t q = (size_t)(blk - nf) * blockDim.x + threadIdx.x; q < n; q += (size_t)fb * blockDim.x) {
+      const T e = force[q] - f_label[q];
+      s += (double)(loss_kind == 0 ? huber(e) : e * e);
+      fbar[q] = scale * (loss_kind == 0 ? huber_d(e) : T(2) * e);
+    }
+    s = block_sum<double, 8>(s, red);
+    if (threadIdx.x == 0) atomicAdd(losses + 3, s / (double)n);
+  } else {
+    double s = 0.0;
+    for (int t = 0; t < md.nt; t++) {
+      const int n2 = md.nt * md.Fr[t], n3 = md.C * 3 * md.Fa[t];
+      for (int q = threadIdx.x; q < n2 + n3; q += blockDim.x) {
+        const int idx = q < n2 ? md.off_a2[t] + q : md.off_a3[t] + (q - n2);
+        const T x = theta[idx];
+        if (x > bound) { s += (double)x; atomicAdd(grad + idx, pb); }
+      }
+    }
+    s = block_sum<double, 8>(s, red);
+    if (threadIdx.x == 0) atomicAdd(losses + 2, s);
+  }
+  if (train && threadIdx.x == 0) {
+    __threadfence();
+    const unsigned done = atomicAdd(reinterpret_cast<unsigned*>(losses + 4), 1u);
+    if (done == gridDim.x - 1) {
+      __threadfence();
+      const double le = atomicAdd(losses + 1, 0.0), lb = atomicAdd(losses + 2, 0.0), lf = atomicAdd(losses + 3, 0.0);
+      losses[0] = (double)pe * le + (double)pb * lb + (double)pf * lf;
     }
   }
-}
-
-template <class T>
-__global__ void k_force_loss(size_t n, const T* __restrict__ force, const T* __restrict__ f_label, T pf,
-                             int loss_kind, T* __restrict__ fbar, double* __restrict__ losses) {
-  __shared__ double red[9];
-  double s = 0.0;
-  const T scale = pf / T((double)n);
-  for (size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x; q < n; q += (size_t)gridDim.x * blockDim.x) {
-    const T e = force[q] - f_label[q];
-    s += (double)(loss_kind == 0 ? huber(e) : e * e);
-    fbar[q] = scale * (loss_kind == 0 ? huber_d(e) : T(2) * e);
-  }
-  s = block_sum<double, 8>(s, red);
-  if (threadIdx.x == 0) atomicAdd(losses + 3, s / (double)n);
-}
-
-// bound loss sum(alpha * [alpha > bound]) over alpha2b and alpha3b of every species
-// (Keras ReLU(threshold): staf_models/staf_model.py:60-62,215-219) and its gradient
-template <class T>
-__global__ void k_bound(ModelDev md, const T* __restrict__ theta, T bound, T pb, T* __restrict__ grad,
-                        double* __restrict__ losses) {
-  __shared__ double red[9];
-  double s = 0.0;
-  for (int t = 0; t < md.nt; t++) {
-    const int n2 = md.nt * md.Fr[t], n3 = md.C * 3 * md.Fa[t];
-    for (int q = threadIdx.x; q < n2 + n3; q += blockDim.x) {
-      const int idx = q < n2 ? md.off_a2[t] + q : md.off_a3[t] + (q - n2);
-      const T x = theta[idx];
-      if (x > bound) { s += (double)x; atomicAdd(grad + idx, pb); }
-    }
-  }
-  s = block_sum<double, 8>(s, red);
-  if (threadIdx.x == 0) losses[2] = s;
-}
-
-__global__ void k_finalize(double pe, double pf, double pb, double* __restrict__ losses) {
-  losses[0] = pe * losses[1] + pb * losses[2] + pf * losses[3];
 }
 
 template <class T>
@@ -781,23 +948,33 @@ __global__ void k_adam(int n, T* __restrict__ theta, const T* __restrict__ grad,
   theta[q] -= lr_t * mm / (r_sqrt(vv) + eps);
 }
 
-// Adam with the step count kept on the device, so that a captured CUDA graph can be replayed
+// Adam with the step count kept on the device, so that a captured CUDA graph can be replayed.
+// Every thread reads the counter; the block that finishes last increments it.
 template <class T>
 __global__ void k_adam_dev(int n, T* __restrict__ theta, const T* __restrict__ grad, T* __restrict__ m,
                            T* __restrict__ v, double lr, double b1, double b2, T eps, T gscale,
-                           const int* __restrict__ step_d) {
+                           int* __restrict__ step_d /*[2]: step, blocks done*/) {
   const int q = blockIdx.x * blockDim.x + threadIdx.x;
-  if (q >= n) return;
-  const int step = *step_d + 1;
-  const T lr_t = (T)(lr * sqrt(1.0 - pow(b2, (double)step)) / (1.0 - pow(b1, (double)step)));
-  const T g = grad[q] * gscale;
-  const T mm = (T)b1 * m[q] + (T(1) - (T)b1) * g;
-  const T vv = (T)b2 * v[q] + (T(1) - (T)b2) * g * g;
-  m[q] = mm;
-  v[q] = vv;
-  theta[q] -= lr_t * mm / (r_sqrt(vv) + eps);
+  const int step = *reinterpret_cast<volatile int*>(step_d) + 1;
+  if (q < n) {
+    const T lr_t = (T)(lr * sqrt(1.0 - pow(b2, (double)step)) / (1.0 - pow(b1, (double)step)));
+    const T g = grad[q] * gscale;
+    const T mm = (T)b1 * m[q] + (T(1) - (T)b1) * g;
+    const T vv = (T)b2 * v[q] + (T(1) - (T)b2) * g * g;
+    m[q] = mm;
+    v[q] = vv;
+    theta[q] -= lr_t * mm / (r_sqrt(vv) + eps);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(step_d + 1, 1) == (int)gridDim.x - 1) {
+      step_d[1] = 0;
+      __threadfence();
+      atomicAdd(step_d, 1);
+    }
+  }
 }
-__global__ void k_inc(int* p) { *p += 1; }
 
 }  // namespace stafb
 
@@ -809,16 +986,25 @@ struct stafb_model {
   int n_params, n_emb;
   int blk_size[STAFB_MAX_TYPES];
   size_t es;
+  int apt;  // atoms per thread group of the MLP kernels (TA = 8*apt atoms per block)
+  size_t mlp_fwd_smem, mlp_bwd_smem;
   // scratch for max_batch frames
   void *rad, *d3s, *af, *nd, *acts, *e_atom, *force, *fbar, *ebar, *gradnet, *gaf, *energy;
   int *im2, *ntr;
-  double* losses_d;
+  double* losses_d;  // 5 doubles: the four losses + the done-counter of k_loss
   // staging for the *_host entry points
   void *pos_d, *box_d, *el_d, *fl_d;
-  void* pin;  // pinned staging: pos | box | e_label | f_label
+  void* pin;  // pinned staging: pos | f_label | box | e_label
   double* losses_h;
   size_t smem_limit;
 };
+
+static size_t mlp_smem_fwd(const ModelDev& d, size_t es, int apt) {
+  return es * ((size_t)(d.Fmax + d.Hsum + 2 * d.maxw) * 8 * apt + (size_t)d.maxw * 33);
+}
+static size_t mlp_smem_bwd(const ModelDev& d, size_t es, int apt) {
+  return es * ((size_t)(2 * d.Fmax + 5 * d.Hsum + 2 * d.maxw) * 8 * apt + (size_t)d.maxw * 33);
+}
 
 extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out) {
   if (!c || !sd || !out) return STAFB_ERR_INVALID;
@@ -866,7 +1052,19 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   m->n_emb = eoff;
   m->ctx = c;
   m->es = c->dtype == STAFB_F32 ? 4 : 8;
+  int dev = 0, lim = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&lim, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  m->smem_limit = (size_t)lim;
+  m->apt = 0;
+  for (int apt = 4; apt >= 1; apt >>= 1) {
+    if (mlp_smem_bwd(d, m->es, apt) <= m->smem_limit) { m->apt = apt; break; }
+  }
+  if (!m->apt) { free(m); return STAFB_ERR_CAPACITY; }
+  m->mlp_fwd_smem = mlp_smem_fwd(d, m->es, m->apt);
+  m->mlp_bwd_smem = mlp_smem_bwd(d, m->es, m->apt);
   const size_t es = m->es, A = (size_t)c->max_batch * d.N, nr = c->nr;
+  const size_t mlp_blocks = (size_t)species_blocks(d, c->max_batch, 8 * m->apt);
   STAFB_CUDA_OK(cudaMalloc(&m->rad, es * A * nr));
   STAFB_CUDA_OK(cudaMalloc(&m->d3s, es * A * nr));
   STAFB_CUDA_OK(cudaMalloc((void**)&m->im2, sizeof(int) * A * (nr + 1)));
@@ -875,23 +1073,19 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   STAFB_CUDA_OK(cudaMalloc(&m->nd, es * A * d.Fmax));
   STAFB_CUDA_OK(cudaMalloc(&m->gradnet, es * A * d.Fmax));
   STAFB_CUDA_OK(cudaMalloc(&m->gaf, es * A * d.Fmax));
-  STAFB_CUDA_OK(cudaMalloc(&m->acts, es * A * d.Hsum));
+  STAFB_CUDA_OK(cudaMalloc(&m->acts, es * mlp_blocks * 8 * m->apt * d.Hsum));
   STAFB_CUDA_OK(cudaMalloc(&m->e_atom, es * A));
   STAFB_CUDA_OK(cudaMalloc(&m->force, es * A * 3));
   STAFB_CUDA_OK(cudaMalloc(&m->fbar, es * A * 3));
   STAFB_CUDA_OK(cudaMalloc(&m->ebar, es * c->max_batch));
   STAFB_CUDA_OK(cudaMalloc(&m->energy, es * c->max_batch));
-  STAFB_CUDA_OK(cudaMalloc((void**)&m->losses_d, sizeof(double) * 4));
+  STAFB_CUDA_OK(cudaMalloc((void**)&m->losses_d, sizeof(double) * 5));
   STAFB_CUDA_OK(cudaMalloc(&m->pos_d, es * A * 3));
   STAFB_CUDA_OK(cudaMalloc(&m->box_d, es * c->max_batch * 6));
   STAFB_CUDA_OK(cudaMalloc(&m->el_d, es * c->max_batch));
   STAFB_CUDA_OK(cudaMalloc(&m->fl_d, es * A * 3));
   STAFB_CUDA_OK(cudaMallocHost(&m->pin, es * (A * 6 + (size_t)c->max_batch * 7)));
   STAFB_CUDA_OK(cudaMallocHost((void**)&m->losses_h, sizeof(double) * 4));
-  int dev = 0, lim = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&lim, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-  m->smem_limit = (size_t)lim;
   *out = m;
   return STAFB_OK;
 }
@@ -934,14 +1128,44 @@ static int launch_sweep(stafb_model* m, cudaStream_t s, int nf, const SweepIn<T>
   return STAFB_OK;
 }
 
+template <class T, int APT>
+static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, T* acts, T* e_atom,
+                          T* nd) {
+  static bool attr = false;
+  if (m->mlp_fwd_smem > 48 * 1024 && !attr) {
+    STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_fwd<T, APT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)m->smem_limit));
+    attr = true;
+  }
+  k_mlp_fwd<T, APT><<<species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_fwd_smem, s>>>(m->md, nf, theta, af, acts,
+                                                                                           e_atom, nd);
+  m->ctx->launches++;
+  return STAFB_OK;
+}
+
+template <class T, int APT>
+static int launch_mlp_bwd(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, const T* acts,
+                          const T* ebar, const T* u, T* gaf, T* grad) {
+  static bool attr = false;
+  if (m->mlp_bwd_smem > 48 * 1024 && !attr) {
+    STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_bwd<T, APT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)m->smem_limit));
+    attr = true;
+  }
+  k_mlp_bwd<T, APT><<<species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_bwd_smem, s>>>(m->md, nf, theta, af, acts,
+                                                                                           ebar, u, gaf, grad);
+  m->ctx->launches++;
+  return STAFB_OK;
+}
+
 template <class T>
 static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos, const T* box, int nf,
                      const T* theta, const T* emb, int per_atom, bool train, const T* e_label, const T* f_label,
-                     double pe, double pf, double pb, double bound, int loss_kind, double* losses_d, T* grad,
+                     double pe, double pf, double pb, double bound, int loss_kind, double* losses_out, T* grad,
                      T* energy_out, T* force_out) {
   if (!c || !m || !pos || !box || !theta || !emb || nf <= 0) return STAFB_ERR_INVALID;
   if (nf > c->max_batch) return STAFB_ERR_CAPACITY;
-  if (train && (!e_label || !f_label || !grad || !losses_d)) return STAFB_ERR_INVALID;
+  if (train && (!e_label || !f_label || !grad || !losses_out)) return STAFB_ERR_INVALID;
   const ModelDev& d = m->md;
   const int N = d.N;
   c->launches = 0;
@@ -954,71 +1178,55 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
   int rc = launch_descriptors<T>(c, s, pos, box, nf, N, rad, nullptr, d3s, m->im2, nullptr, nullptr, nullptr,
                                  nullptr, m->ntr);
   if (rc != STAFB_OK) return rc;
+  T* af = (T*)m->af; T* nd = (T*)m->nd; T* acts = (T*)m->acts; T* e_atom = (T*)m->e_atom;
+  T* force = force_out ? force_out : (T*)m->force;
+  T* energy = energy_out ? energy_out : (T*)m->energy;
+  k_zero3<<<64, 256, 0, s>>>(force, sizeof(T) * (size_t)nf * 3 * N, train ? (void*)grad : nullptr,
+                             train ? sizeof(T) * (size_t)m->n_params : 0, m->losses_d, sizeof(double) * 5);
+  c->launches++;
   mark();  // descriptors
   SweepIn<T> in;
   in.geom = (const T*)c->geom; in.gsc = (const T*)c->gsc; in.rad = rad; in.d3s = d3s; in.im2 = m->im2; in.ntr = m->ntr;
   in.nf = nf; in.nr = c->nr;
-  T* af = (T*)m->af; T* nd = (T*)m->nd; T* acts = (T*)m->acts; T* e_atom = (T*)m->e_atom;
-  T* force = force_out ? force_out : (T*)m->force;
-  T* energy = energy_out ? energy_out : (T*)m->energy;
   rc = launch_sweep<T, MODE_AF>(m, s, nf, in, theta, emb, nullptr, nullptr, af, nullptr);
   if (rc != STAFB_OK) return rc;
   mark();  // af_fwd
-  const int mblocks = species_blocks(d, nf, ML_WARPS);
-  {
-    const size_t sm = sizeof(T) * (size_t)(d.Fmax + d.Hsum + 2 * d.maxw) * ML_WARPS;
-    if (sm > m->smem_limit) return STAFB_ERR_CAPACITY;
-    static bool attr[2] = {false, false};
-    if (sm > 48 * 1024 && !attr[sizeof(T) == 8]) {
-      STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_fwd<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)m->smem_limit));
-      attr[sizeof(T) == 8] = true;
-    }
-    k_mlp_fwd<T><<<mblocks, ML_WARPS * 32, sm, s>>>(d, nf, theta, af, acts, e_atom, nd);
-    c->launches++;
-  }
+  rc = m->apt == 4 ? launch_mlp_fwd<T, 4>(m, s, nf, theta, af, acts, e_atom, nd)
+       : m->apt == 2 ? launch_mlp_fwd<T, 2>(m, s, nf, theta, af, acts, e_atom, nd)
+                     : launch_mlp_fwd<T, 1>(m, s, nf, theta, af, acts, e_atom, nd);
+  if (rc != STAFB_OK) return rc;
   mark();  // mlp_fwd
-  STAFB_CUDA_OK(cudaMemsetAsync(force, 0, sizeof(T) * (size_t)nf * 3 * N, s));
   rc = launch_sweep<T, MODE_FORCE>(m, s, nf, in, theta, emb, nd, nullptr, force, nullptr);
   if (rc != STAFB_OK) return rc;
   mark();  // force
-  if (train) {
-    STAFB_CUDA_OK(cudaMemsetAsync(losses_d, 0, sizeof(double) * 4, s));
-    STAFB_CUDA_OK(cudaMemsetAsync(grad, 0, sizeof(T) * (size_t)m->n_params, s));
+  {
+    int fb = 0;
+    if (train) {
+      fb = (int)(((size_t)nf * 3 * N + 255) / 256);
+      if (fb > 296) fb = 296;
+    }
+    const int grid = nf + fb + (train ? 1 : 0);
+    k_loss<T><<<grid, 256, 0, s>>>(d, nf, fb, per_atom, train ? 1 : 0, e_atom, energy, e_label, force, f_label, theta,
+                                   (T)pe, (T)pf, (T)pb, (T)bound, loss_kind, (T*)m->ebar, (T*)m->fbar, grad,
+                                   m->losses_d, c->status_d);
+    c->launches++;
   }
-  k_energy<T><<<nf, 256, 0, s>>>(N, nf, per_atom, e_atom, energy, train ? e_label : nullptr, (T)pe, loss_kind,
-                                 (T*)m->ebar, losses_d, c->status_d);
-  c->launches++;
+  mark();  // loss
   if (train) {
-    const size_t nF = (size_t)nf * 3 * N;
-    int fb = (int)((nF + 255) / 256);
-    if (fb > 1184) fb = 1184;
-    k_force_loss<T><<<fb, 256, 0, s>>>(nF, force, f_label, (T)pf, loss_kind, (T*)m->fbar, losses_d);
-    k_bound<T><<<1, 256, 0, s>>>(d, theta, (T)bound, (T)pb, grad, losses_d);
-    c->launches += 2;
-    mark();  // loss
     T* gradnet = (T*)m->gradnet;
     T* gaf = (T*)m->gaf;
     rc = launch_sweep<T, MODE_FGRAD>(m, s, nf, in, theta, emb, nd, (const T*)m->fbar, gradnet, grad);
     if (rc != STAFB_OK) return rc;
     mark();  // force_grad
-    {
-      const size_t sm = sizeof(T) * (size_t)(3 * d.Fmax + 5 * d.Hsum + 2 * d.maxw) * ML_WARPS;
-      if (sm > m->smem_limit) return STAFB_ERR_CAPACITY;
-      static bool attr[2] = {false, false};
-      if (sm > 48 * 1024 && !attr[sizeof(T) == 8]) {
-        STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_bwd<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)m->smem_limit));
-        attr[sizeof(T) == 8] = true;
-      }
-      k_mlp_bwd<T><<<mblocks, ML_WARPS * 32, sm, s>>>(d, nf, theta, af, acts, (const T*)m->ebar, gradnet, gaf, grad);
-      c->launches++;
-    }
+    rc = m->apt == 4 ? launch_mlp_bwd<T, 4>(m, s, nf, theta, af, acts, (const T*)m->ebar, gradnet, gaf, grad)
+         : m->apt == 2 ? launch_mlp_bwd<T, 2>(m, s, nf, theta, af, acts, (const T*)m->ebar, gradnet, gaf, grad)
+                       : launch_mlp_bwd<T, 1>(m, s, nf, theta, af, acts, (const T*)m->ebar, gradnet, gaf, grad);
+    if (rc != STAFB_OK) return rc;
     mark();  // mlp_bwd
     rc = launch_sweep<T, MODE_AFGRAD>(m, s, nf, in, theta, emb, gaf, nullptr, nullptr, grad);
     if (rc != STAFB_OK) return rc;
-    k_finalize<<<1, 1, 0, s>>>(pe, pf, pb, losses_d);
-    c->launches++;
+    if (losses_out != m->losses_d)
+      STAFB_CUDA_OK(cudaMemcpyAsync(losses_out, m->losses_d, sizeof(double) * 4, cudaMemcpyDeviceToDevice, s));
     mark();  // af_grad
   }
   STAFB_CUDA_OK(cudaGetLastError());
@@ -1117,7 +1325,6 @@ extern "C" int stafb_adam_step_dev(stafb_ctx* c, void* stream, void* theta, cons
   else
     k_adam_dev<double><<<(n + 255) / 256, 256, 0, s>>>(n, (double*)theta, (const double*)grad, (double*)mm,
                                                        (double*)vv, lr, b1, b2, eps, gscale, step_d);
-  k_inc<<<1, 1, 0, s>>>(step_d);
   STAFB_CUDA_OK(cudaGetLastError());
   return STAFB_OK;
 }

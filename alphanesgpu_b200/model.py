@@ -120,7 +120,7 @@ class StafModel:
     def adam_update_dev(self, lr, beta1=0.9, beta2=0.999, eps=1e-7, grad_scale=1.0):
         """Adam with the step counter on the device (safe to capture in a CUDA graph and replay)."""
         if not hasattr(self, "step_d"):
-            self.step_d = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.step_d = torch.zeros(2, dtype=torch.int32, device=self.device)  # step, block counter
         check(_lib.lib().stafb_adam_step_dev(self.ctx.h, self.ctx.stream(), _p(self.theta), _p(self.grad),
                                              _p(self.adam_m), _p(self.adam_v), self.theta.numel(), float(lr),
                                              float(beta1), float(beta2), float(eps), _p(self.step_d),
