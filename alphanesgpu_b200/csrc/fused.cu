@@ -26,7 +26,9 @@
 namespace stafb {
 
 constexpr int MAXCH = 8;     // channels processed per pair sweep
-constexpr int SW_WARPS = 4;  // warps (= atoms) per block in the sweep kernels
+// warps per central atom (= per block) in the sweep kernels: the ordered force loop is long enough to
+// profit from two warps; the unordered sweeps run fastest with one
+template <int MODE> struct SweepWpa { static constexpr int value = (MODE == 1) ? 2 : 1; };
 constexpr int ML_THREADS = 256;
 
 // exponential with a pre-scaled argument: fp32 uses 2^x (MUFU.EX2), fp64 the full-precision exp
@@ -110,11 +112,11 @@ static inline int species_blocks(const ModelDev& md, int nf, int W) {
 
 // per-warp shared memory layout of the sweep kernels (offsets in bytes)
 struct SweepLayout {
-  int p0, p1, tab, chpa, chpb, xtra, acc, ids, tj, lst, actl, total;
+  int p0, p1, tab, chpa, chpb, xtra, acc, red, ids, cnts, tj, lst, actl, total;
 };
 
 template <class T>
-static inline SweepLayout sweep_layout(int nr, int nt, int xt, int nacc, int famax) {
+static inline SweepLayout sweep_layout(int nr, int nt, int xt, int nacc, int famax, int wpa) {
   SweepLayout L;
   int o = 0;
   auto take = [&](int bytes) { int r = o; o += (bytes + 15) & ~15; return r; };
@@ -125,7 +127,9 @@ static inline SweepLayout sweep_layout(int nr, int nt, int xt, int nacc, int fam
   L.chpb = take(MAXCH * 2 * sizeof(T));
   L.xtra = take(nr * xt * sizeof(T));
   L.acc = take(nacc * sizeof(T));
+  L.red = take(wpa * 4 * MAXCH * sizeof(T));
   L.ids = take(nr * sizeof(int));
+  L.cnts = take(STAFB_MAX_TYPES * sizeof(int));
   L.tj = take(nr);
   L.lst = take(nt * nr);
   L.actl = take(famax);
@@ -143,8 +147,8 @@ struct PairStep {
     if (kb >= nb) { kb -= nb; ja++; }
   }
   __device__ __forceinline__ void init_tri(int p, int n) { unrank_pair(p, n, ja, kb); }
-  __device__ __forceinline__ void step_tri(int n) {  // advance 32 positions in the row-major upper triangle
-    kb += 32;
+  __device__ __forceinline__ void step_tri(int n, int st) {  // advance st positions in the row-major upper triangle
+    kb += st;
     while (kb >= n && ja < n - 1) {
       const int o = kb - n;
       ja++;
@@ -153,8 +157,14 @@ struct PairStep {
   }
 };
 
-template <class T, int MODE>
-__global__ void __launch_bounds__(SW_WARPS * 32)
+template <int WPA>
+__device__ __forceinline__ void gsync() {
+  if (WPA == 1) __syncwarp(); else __syncthreads();
+}
+
+// One block of WPA warps per central atom.
+template <class T, int MODE, int WPA>
+__global__ void __launch_bounds__(WPA * 32)
     k_sweep(ModelDev md, SweepIn<T> in, SweepLayout L, const T* __restrict__ theta, const T* __restrict__ emb,
             const T* __restrict__ chan_in,  // FORCE/FGRAD: netderiv[nf,N,Fmax]; AFGRAD: dL/dAF[nf,N,Fmax]
             const T* __restrict__ fbar,     // FGRAD: dL/dF[nf,3N]
@@ -163,10 +173,11 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
   extern __shared__ __align__(16) unsigned char smem_raw[];
   typedef typename Vec4<T>::type T4;
   typedef typename Vec2<T>::type T2;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int NT = WPA * 32;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int t, b, i;
-  if (!locate_atom(md, in.nf, SW_WARPS, warp, t, b, i)) return;
-  unsigned char* base = smem_raw + (size_t)warp * L.total;
+  if (!locate_atom(md, in.nf, 1, 0, t, b, i)) return;
+  unsigned char* base = smem_raw;
   T4* P0 = reinterpret_cast<T4*>(base + L.p0);   // unit vector (i - k)/r and cutoff fc
   T4* P1 = reinterpret_cast<T4*>(base + L.p1);   // 1/r, dfc/dr, radial descriptor d, dd/dr
   T2* tab = reinterpret_cast<T2*>(base + L.tab);
@@ -174,7 +185,9 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
   T2* chpb = reinterpret_cast<T2*>(base + L.chpb);  // mode-dependent coefficient, netderiv
   T* xtra = reinterpret_cast<T*>(base + L.xtra);
   T* acc = reinterpret_cast<T*>(base + L.acc);
+  T* red = reinterpret_cast<T*>(base + L.red);      // [WPA][4*MAXCH] per-warp partial sums
   int* ids = reinterpret_cast<int*>(base + L.ids);
+  int* cnts = reinterpret_cast<int*>(base + L.cnts);
   unsigned char* tj = base + L.tj;
   unsigned char* lst = base + L.lst;
   unsigned char* actl = base + L.actl;
@@ -198,7 +211,7 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
   if (n > nr) n = nr;
   int m = in.ntr[gi];
   if (m > n) m = n;
-  for (int k = lane; k < n; k += 32) {
+  for (int k = tid; k < n; k += NT) {
     const T4 g = reinterpret_cast<const T4*>(in.geom)[gi * nr + k];
     const T2 s = reinterpret_cast<const T2*>(in.gsc)[gi * nr + k];
     const T inv = T(1) / g.w;
@@ -212,44 +225,49 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
     tj[k] = (unsigned char)md.type_of(id);
   }
   if (MODE != MODE_FORCE)
-    for (int q = lane; q < NACC; q += 32) acc[q] = T(0);
-  __syncwarp();
-  // per-species lists of the angular neighbours (first m sorted entries)
-  int cnt[STAFB_MAX_TYPES];
+    for (int q = tid; q < NACC; q += NT) acc[q] = T(0);
+  if (MODE == MODE_FORCE)
+    for (int q = tid; q < 3 * nr; q += NT) xtra[q] = T(0);
+  gsync<WPA>();
+  // per-species lists of the angular neighbours (first m sorted entries), built by warp 0
   const unsigned lt = (1u << lane) - 1u;
+  if (warp == 0) {
 #pragma unroll
-  for (int t2 = 0; t2 < STAFB_MAX_TYPES; t2++) {
-    cnt[t2] = 0;
-    if (t2 < nt) {
-      for (int k0 = 0; k0 < m; k0 += 32) {
-        const int k = k0 + lane;
-        const bool p = (k < m) && (tj[k] == t2);
-        const unsigned bal = __ballot_sync(0xffffffffu, p);
-        if (p) lst[t2 * nr + cnt[t2] + __popc(bal & lt)] = (unsigned char)k;
-        cnt[t2] += __popc(bal);
+    for (int t2 = 0; t2 < STAFB_MAX_TYPES; t2++) {
+      if (t2 < nt) {
+        int c2 = 0;
+        for (int k0 = 0; k0 < m; k0 += 32) {
+          const int k = k0 + lane;
+          const bool p = (k < m) && (tj[k] == t2);
+          const unsigned bal = __ballot_sync(0xffffffffu, p);
+          if (p) lst[t2 * nr + c2 + __popc(bal & lt)] = (unsigned char)k;
+          c2 += __popc(bal);
+        }
+        if (lane == 0) cnts[t2] = c2;
       }
     }
   }
   T fix = T(0), fiy = T(0), fiz = T(0);  // FORCE: force on the central atom
-  if (MODE == MODE_FORCE) {
-    for (int q = lane; q < 3 * nr; q += 32) xtra[q] = T(0);
-  }
   if (MODE == MODE_FGRAD) {
     // dF_k = Fbar_k - Fbar_i and its projection on the unit vector
     const T* fb = fbar + (size_t)b * N * 3;
     const T fx = fb[i * 3], fy = fb[i * 3 + 1], fz = fb[i * 3 + 2];
-    for (int k = lane; k < n; k += 32) {
+    for (int k = tid; k < n; k += NT) {
       const int id = ids[k];
       const T dx = fb[id * 3] - fx, dy = fb[id * 3 + 1] - fy, dz = fb[id * 3 + 2] - fz;
       xtra[k * 4 + 0] = dx; xtra[k * 4 + 1] = dy; xtra[k * 4 + 2] = dz;
       xtra[k * 4 + 3] = dx * P0[k].x + dy * P0[k].y + dz * P0[k].z;
     }
   }
-  __syncwarp();
+  gsync<WPA>();
+  int cnt[STAFB_MAX_TYPES];
+#pragma unroll
+  for (int t2 = 0; t2 < STAFB_MAX_TYPES; t2++) cnt[t2] = (t2 < nt) ? cnts[t2] : 0;
 
   // ------------------------------------------------------------------ radial part
+  // channels are dealt round-robin to the warps, so no cross-warp reduction is needed
   if (MODE == MODE_AF) {
-    for (int c = 0; c < Fr; c++) {
+    for (int c = warp; c < Fr; c += WPA) {
       T s = T(0);
       for (int k = lane; k < n; k += 32) {
         const T ch = e2[Fr * tj[k] + c];
@@ -260,7 +278,7 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
       if (lane == 0) out[gi * Fmax + c] = s;
     }
   } else if (MODE == MODE_FORCE) {
-    for (int k = lane; k < n; k += 32) {
+    for (int k = tid; k < n; k += NT) {
       const int tk = tj[k];
       const T dk = P1[k].z;
       T w = T(0);
@@ -272,11 +290,13 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
       }
       const T g = w * P1[k].w;
       const T gx = g * P0[k].x, gy = g * P0[k].y, gz = g * P0[k].z;
-      xtra[k * 3 + 0] = gx; xtra[k * 3 + 1] = gy; xtra[k * 3 + 2] = gz;
+      atomicAdd(&xtra[k * 3 + 0], gx);
+      atomicAdd(&xtra[k * 3 + 1], gy);
+      atomicAdd(&xtra[k * 3 + 2], gz);
       fix -= gx; fiy -= gy; fiz -= gz;
     }
   } else {  // FGRAD / AFGRAD: gradients with respect to alpha2b (and gradnet for FGRAD)
-    for (int c = 0; c < Fr; c++) {
+    for (int c = warp; c < Fr; c += WPA) {
       const T cin = chrow[c];  // FGRAD: netderiv ; AFGRAD: dL/dAF
       T gn = T(0);
       T ga[STAFB_MAX_TYPES];
@@ -313,7 +333,6 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
       }
     }
   }
-  __syncwarp();
 
   // ------------------------------------------------------------------ angular part
   for (int ta = 0; ta < nt; ta++) {
@@ -330,49 +349,51 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
       if (np <= 0 || s >= md.ncls) continue;
       const unsigned char* la = lst + ta * nr;
       const unsigned char* lb = lst + tb * nr;
-      // active channels of this class
+      // active channels of this class (every warp counts, warp 0 writes the list)
       int nact = 0;
       for (int c0 = 0; c0 < Fa; c0 += 32) {
         const int c = c0 + lane;
         const bool p = (c < Fa) && (e3[s * Fa + c] != T(0));
         const unsigned bal = __ballot_sync(0xffffffffu, p);
-        if (p) actl[nact + __popc(bal & lt)] = (unsigned char)c;
+        if (p && warp == 0) actl[nact + __popc(bal & lt)] = (unsigned char)c;
         nact += __popc(bal);
       }
-      __syncwarp();
       for (int c0 = 0; c0 < nact; c0 += MAXCH) {
         const int nch = (nact - c0) < MAXCH ? (nact - c0) : MAXCH;
-        if (lane < nch) {
-          const int c = actl[c0 + lane];
+        gsync<WPA>();  // actl visible; previous chunk's readers of chp/tab/red are done
+        if (tid < nch) {
+          const int c = actl[c0 + tid];
           const T* al = a3 + (s * Fa + c) * 3;
           const T ee = e3[s * Fa + c];
           T4 pa;
           pa.x = al[0]; pa.y = al[1]; pa.z = al[2]; pa.w = al[2] * SC;
-          chpa[lane] = pa;
+          chpa[tid] = pa;
           T2 pb;
           pb.x = T(0); pb.y = T(0);
           if (MODE == MODE_AF) pb.x = T(0.5) * ee;
           if (MODE == MODE_FORCE) pb.x = T(0.25) * chrow[Fr + c] * ee;
           if (MODE == MODE_FGRAD) { pb.x = T(0.5) * ee; pb.y = chrow[Fr + c]; }
           if (MODE == MODE_AFGRAD) pb.x = T(0.5) * chrow[Fr + c] * ee;
-          chpb[lane] = pb;
+          chpb[tid] = pb;
         }
-        __syncwarp();
+        gsync<WPA>();
         // tables exp(a1*fc_k), exp(a2*fc_k) for the neighbours of the two species
         const int nu = same ? na_ : na_ + nb_;
-        for (int q = lane; q < nch * nu; q += 32) {
-          const int l = q / nu, r = q - l * nu;
-          const int k = (r < na_) ? la[r] : lb[r - na_];
-          const T fck = P0[k].w;
-          T2 v;
-          v.x = Ex<T>::f(chpa[l].x * SC * fck);
-          v.y = Ex<T>::f(chpa[l].y * SC * fck);
-          tab[l * nr + k] = v;
+        for (int l = 0; l < nch; l++) {
+          const T a1s = chpa[l].x * SC, a2s = chpa[l].y * SC;
+          for (int r = tid; r < nu; r += NT) {
+            const int k = (r < na_) ? la[r] : lb[r - na_];
+            const T fck = P0[k].w;
+            T2 v;
+            v.x = Ex<T>::f(a1s * fck);
+            v.y = Ex<T>::f(a2s * fck);
+            tab[l * nr + k] = v;
+          }
         }
-        __syncwarp();
+        gsync<WPA>();
 
         if (MODE == MODE_FORCE) {
-          // ordered pairs (owner j, partner k): each lane takes a contiguous run of the row-major
+          // ordered pairs (owner j, partner k): each thread takes a contiguous run of the row-major
           // list, keeps the owner's data and its force accumulator in registers and flushes when the
           // row changes.  Two passes when the two species differ (owners of ta, then owners of tb).
           const int npass = same ? 1 : 2;
@@ -382,8 +403,8 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
             const int no = pass == 0 ? na_ : nb_;
             const int npt = same ? na_ - 1 : (pass == 0 ? nb_ : na_);
             const int E = no * npt;
-            const int cchunk = (E + 31) / 32;
-            int e0 = lane * cchunk, e1 = e0 + cchunk;
+            const int cchunk = (E + NT - 1) / NT;
+            int e0 = tid * cchunk, e1 = e0 + cchunk;
             if (e1 > E) e1 = E;
             if (e0 < e1) {
               int ja = e0 / npt, kb = e0 - ja * npt;
@@ -440,7 +461,6 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
                 }
               }
             }
-            __syncwarp();
           }
         } else {
           T r0[MAXCH], r1[MAXCH], r2[MAXCH], r3[MAXCH];
@@ -448,13 +468,13 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
           for (int l = 0; l < MAXCH; l++) r0[l] = r1[l] = r2[l] = r3[l] = T(0);
           PairStep ps;
           ps.ja = ps.kb = 0;
-          const int q32 = same ? 0 : 32 / nb_, r32 = same ? 0 : 32 - q32 * nb_;
-          if (lane < np) {
-            if (same) ps.init_tri(lane, na_); else ps.init_rect(lane, nb_);
+          const int qst = same ? 0 : NT / nb_, rst = same ? 0 : NT - qst * nb_;
+          if (tid < np) {
+            if (same) ps.init_tri(tid, na_); else ps.init_rect(tid, nb_);
           }
-          for (int p = lane; p < np; p += 32) {
+          for (int p = tid; p < np; p += NT) {
             const int j = la[ps.ja], k = lb[ps.kb];
-            if (same) ps.step_tri(na_); else ps.step_rect(nb_, q32, r32);
+            if (same) ps.step_tri(na_, NT); else ps.step_rect(nb_, qst, rst);
             const T4 uj = P0[j], uk = P0[k];
             const T fcj = uj.w, fck = uk.w;
             const T cs = uj.x * uk.x + uj.y * uk.y + uj.z * uk.z;
@@ -508,39 +528,56 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
               }
             }
           }
+          // per-warp sums -> red[warp][4*l + v]; then one thread per value combines the warps
 #pragma unroll
           for (int l = 0; l < MAXCH; l++) {
             if (l < nch) {
-              const int c = actl[c0 + l];
-              const T cf = chpb[l].x;
               if (MODE == MODE_AF || MODE == MODE_FGRAD) {
                 const T v = warp_sum(r0[l]);
-                if (lane == 0) acc[ACC_GN + c] += cf * v;
+                if (lane == 0) red[warp * 4 * MAXCH + 4 * l + 0] = v;
               }
               if (MODE == MODE_AFGRAD || MODE == MODE_FGRAD) {
-                const T hn = MODE == MODE_FGRAD ? cf * chpb[l].y : cf;
                 const T v1 = warp_sum(r1[l]), v2 = warp_sum(r2[l]), v3 = warp_sum(r3[l]);
                 if (lane == 0) {
-                  T* g = acc + ACC_A3 + (s * md.Famax + c) * 3;
-                  g[0] += hn * v1; g[1] += hn * v2; g[2] += hn * v3;
+                  red[warp * 4 * MAXCH + 4 * l + 1] = v1;
+                  red[warp * 4 * MAXCH + 4 * l + 2] = v2;
+                  red[warp * 4 * MAXCH + 4 * l + 3] = v3;
                 }
               }
             }
           }
+          gsync<WPA>();
+          if (tid < 4 * nch) {
+            const int l = tid >> 2, v = tid & 3;
+            const bool use = (v == 0) ? (MODE == MODE_AF || MODE == MODE_FGRAD)
+                                      : (MODE == MODE_AFGRAD || MODE == MODE_FGRAD);
+            if (use) {
+              T sum = T(0);
+#pragma unroll
+              for (int w = 0; w < WPA; w++) sum += red[w * 4 * MAXCH + tid];
+              const int c = actl[c0 + l];
+              const T cf = chpb[l].x;
+              if (v == 0) acc[ACC_GN + c] += cf * sum;
+              else {
+                const T hn = MODE == MODE_FGRAD ? cf * chpb[l].y : cf;
+                acc[ACC_A3 + (s * md.Famax + c) * 3 + (v - 1)] += hn * sum;
+              }
+            }
+          }
         }
-        __syncwarp();
       }
+      gsync<WPA>();  // before the next class rewrites actl
     }
   }
-  __syncwarp();
+  gsync<WPA>();
 
   // ------------------------------------------------------------------ write-back
   if (MODE == MODE_AF) {
-    for (int c = lane; c < Fa; c += 32) out[gi * Fmax + Fr + c] = acc[ACC_GN + c];
-    for (int c = Fr + Fa + lane; c < Fmax; c += 32) out[gi * Fmax + c] = T(0);
+    for (int c = tid; c < Fa; c += NT) out[gi * Fmax + Fr + c] = acc[ACC_GN + c];
+    for (int c = Fr + Fa + tid; c < Fmax; c += NT) out[gi * Fmax + c] = T(0);
   } else if (MODE == MODE_FORCE) {
     T* fb = out + (size_t)b * N * 3;
-    for (int q = lane; q < 3 * n; q += 32) atomicAdd(fb + (size_t)ids[q / 3] * 3 + (q % 3), xtra[q]);
+    for (int q = tid; q < 3 * n; q += NT) atomicAdd(fb + (size_t)ids[q / 3] * 3 + (q % 3), xtra[q]);
     fix = warp_sum(fix); fiy = warp_sum(fiy); fiz = warp_sum(fiz);
     if (lane == 0) {
       atomicAdd(fb + (size_t)i * 3 + 0, fix);
@@ -549,16 +586,16 @@ __global__ void __launch_bounds__(SW_WARPS * 32)
     }
   } else {
     if (MODE == MODE_FGRAD) {
-      for (int c = lane; c < Fa; c += 32) out[gi * Fmax + Fr + c] = acc[ACC_GN + c];
-      for (int c = Fr + Fa + lane; c < Fmax; c += 32) out[gi * Fmax + c] = T(0);
+      for (int c = tid; c < Fa; c += NT) out[gi * Fmax + Fr + c] = acc[ACC_GN + c];
+      for (int c = Fr + Fa + tid; c < Fmax; c += NT) out[gi * Fmax + c] = T(0);
     }
     T* g2 = grad + md.off_a2[t];
-    for (int q = lane; q < nt * Fr; q += 32) {
+    for (int q = tid; q < nt * Fr; q += NT) {
       const T v = acc[ACC_A2 + (q / Fr) * md.Frmax + (q % Fr)];
       if (v != T(0)) atomicAdd(g2 + q, v);
     }
     T* g3 = grad + md.off_a3[t];
-    for (int q = lane; q < md.C * 3 * Fa; q += 32) {
+    for (int q = tid; q < md.C * 3 * Fa; q += NT) {
       const int sc = q / 3, comp = q - sc * 3, s = sc / Fa, c = sc - s * Fa;
       const T v = acc[ACC_A3 + (s * md.Famax + c) * 3 + comp];
       if (v != T(0)) atomicAdd(g3 + q, v);
@@ -824,12 +861,18 @@ __global__ void __launch_bounds__(ML_THREADS)
         const T* hdp = hdi + q * TA;
         const T* qp = dql + j * TA;
         const T* pp = dpl + j * TA;
+        // consecutive lanes hold consecutive j (stride TA words): start each lane at a different atom
+        const int rot = threadIdx.x & (TA - 1);
 #pragma unroll 8
-        for (int a = 0; a < TA; a++) g += hp[a] * qp[a] + hdp[a] * pp[a];
+        for (int a0 = 0; a0 < TA; a0++) {
+          const int a = (a0 + rot) & (TA - 1);
+          g += hp[a] * qp[a] + hdp[a] * pp[a];
+        }
       } else {
         const T* qp = dql + (idx - in * out) * TA;
+        const int rot = threadIdx.x & (TA - 1);
 #pragma unroll 8
-        for (int a = 0; a < TA; a++) g += qp[a];
+        for (int a0 = 0; a0 < TA; a0++) g += qp[(a0 + rot) & (TA - 1)];
       }
       atomicAdd(gw + woff + idx, g);
     }
@@ -1057,8 +1100,13 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   cudaDeviceGetAttribute(&lim, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   m->smem_limit = (size_t)lim;
   m->apt = 0;
+  int nsm = 148;
+  cudaDeviceGetAttribute(&nsm, cudaDevAttrMultiProcessorCount, dev);
   for (int apt = 4; apt >= 1; apt >>= 1) {
-    if (mlp_smem_bwd(d, m->es, apt) <= m->smem_limit) { m->apt = apt; break; }
+    if (mlp_smem_bwd(d, m->es, apt) > m->smem_limit) continue;
+    if (!m->apt) m->apt = apt;  // largest tile that fits
+    m->apt = apt;               // keep shrinking until the grid gives every SM at least two blocks
+    if (species_blocks(d, c->max_batch, 8 * apt) >= 2 * nsm) break;
   }
   if (!m->apt) { free(m); return STAFB_ERR_CAPACITY; }
   m->mlp_fwd_smem = mlp_smem_fwd(d, m->es, m->apt);
@@ -1113,17 +1161,18 @@ static int launch_sweep(stafb_model* m, cudaStream_t s, int nf, const SweepIn<T>
   const ModelDev& d = m->md;
   const int xt = MODE == MODE_FORCE ? 3 : (MODE == MODE_FGRAD ? 4 : 0);
   const int nacc = d.Famax + d.nt * d.Frmax + d.C * 3 * d.Famax;
-  SweepLayout L = sweep_layout<T>(in.nr, d.nt, xt, nacc, d.Famax > 0 ? d.Famax : 1);
-  const size_t sm = (size_t)L.total * SW_WARPS;
+  constexpr int SW_WPA = SweepWpa<MODE>::value;
+  SweepLayout L = sweep_layout<T>(in.nr, d.nt, xt, nacc, d.Famax > 0 ? d.Famax : 1, SW_WPA);
+  const size_t sm = (size_t)L.total;
   if (sm > m->smem_limit) return STAFB_ERR_CAPACITY;
   static bool attr[2][4] = {{false}};
   if (sm > 48 * 1024 && !attr[sizeof(T) == 8][MODE]) {
-    STAFB_CUDA_OK(cudaFuncSetAttribute(k_sweep<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    STAFB_CUDA_OK(cudaFuncSetAttribute(k_sweep<T, MODE, SW_WPA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)m->smem_limit));
     attr[sizeof(T) == 8][MODE] = true;
   }
-  const int blocks = species_blocks(d, nf, SW_WARPS);
-  k_sweep<T, MODE><<<blocks, SW_WARPS * 32, sm, s>>>(d, in, L, theta, emb, chan_in, fbar, out, grad);
+  const int blocks = nf * d.N;
+  k_sweep<T, MODE, SW_WPA><<<blocks, SW_WPA * 32, sm, s>>>(d, in, L, theta, emb, chan_in, fbar, out, grad);
   m->ctx->launches++;
   return STAFB_OK;
 }

@@ -284,8 +284,12 @@ __global__ void __launch_bounds__(WARPS * 32)
         g3z = pre * vz / dn;
       }
       if (dn < cc.Rs) {
-        rd = cc.A / r_pow(dn, cc.pa) + cc.B / r_pow(dn, cc.pb) + cc.C;
-        const T pre = (-cc.pa * cc.A / r_pow(dn, cc.pa + T(1.)) - cc.pb * cc.B / r_pow(dn, cc.pb + T(1.)));
+        // A/r^1 + B/r^-30 + C with the powers by repeated multiplication (the reference calls pow;
+        // the exponents are the constants 1 and -30 of descriptor_builder/reforce.cc:102-103)
+        const T r2 = dn * dn, r4 = r2 * r2, r8 = r4 * r4, r16 = r8 * r8;
+        const T r28 = r16 * r8 * r4, r29 = r28 * dn, r30 = r28 * r2;
+        rd = cc.A / dn + cc.B * r30 + cc.C;
+        const T pre = (-cc.pa * cc.A / r2 - cc.pb * cc.B * r29);
         s2 = pre;
         g2x = pre * vx / dn;
         g2y = pre * vy / dn;
