@@ -589,6 +589,7 @@ __global__ void __launch_bounds__(WPA * 32)
       for (int c = tid; c < Fa; c += NT) out[gi * Fmax + Fr + c] = acc[ACC_GN + c];
       for (int c = Fr + Fa + tid; c < Fmax; c += NT) out[gi * Fmax + c] = T(0);
     }
+    if (grad == nullptr) return;
     T* g2 = grad + md.off_a2[t];
     for (int q = tid; q < nt * Fr; q += NT) {
       const T v = acc[ACC_A2 + (q / Fr) * md.Frmax + (q % Fr)];
@@ -1108,6 +1109,7 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
     m->apt = apt;               // keep shrinking until the grid gives every SM at least two blocks
     if (species_blocks(d, c->max_batch, 8 * apt) >= 2 * nsm) break;
   }
+  if (getenv("STAFB_MLP_APT")) m->apt = atoi(getenv("STAFB_MLP_APT"));
   if (!m->apt) { free(m); return STAFB_ERR_CAPACITY; }
   m->mlp_fwd_smem = mlp_smem_fwd(d, m->es, m->apt);
   m->mlp_bwd_smem = mlp_smem_bwd(d, m->es, m->apt);
@@ -1172,7 +1174,8 @@ static int launch_sweep(stafb_model* m, cudaStream_t s, int nf, const SweepIn<T>
     attr[sizeof(T) == 8][MODE] = true;
   }
   const int blocks = nf * d.N;
-  k_sweep<T, MODE, SW_WPA><<<blocks, SW_WPA * 32, sm, s>>>(d, in, L, theta, emb, chan_in, fbar, out, grad);
+  static const bool noatom = getenv("STAFB_EXP_NOATOM") != nullptr;
+  k_sweep<T, MODE, SW_WPA><<<blocks, SW_WPA * 32, sm, s>>>(d, in, L, theta, emb, chan_in, fbar, out, noatom ? nullptr : grad);
   m->ctx->launches++;
   return STAFB_OK;
 }
