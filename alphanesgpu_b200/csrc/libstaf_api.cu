@@ -1,0 +1,303 @@
+// libstaf C API (include/staf.h) on top of the fused energy/force path.
+// Mirrors the contract of the reference's libstaf/src/staf_api.cpp:39-412: type-sorted slot remap
+// (staf_api.cpp:249-294), Cartesian in / Cartesian forces out in the caller's atom order, energy
+// 0.5*sum(e_i), negative integer error codes, never exit().
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <string>
+#include <vector>
+#include "../../include/staf.h"
+#include "common.cuh"
+
+extern "C" {
+int stafb_model_create(stafb_ctx* ctx, const int* shape_desc, stafb_model** out);
+void stafb_model_destroy(stafb_model* m);
+int stafb_energy_force(stafb_ctx* ctx, stafb_model* m, void* stream, const void* positions_d, const void* boxer_d,
+                       int nf, const void* theta_d, const void* emb_d, int per_atom_energy, void* energy_d,
+                       void* force_d);
+}
+
+struct StafModel {
+  std::string dir;
+  StafOptions opt;
+  double Rc, Rs, Ra;
+  int nr, na, nt;
+  std::vector<int> Fr, Fa, widths;
+  std::vector<double> theta, emb;  // flat, in the layout of include/stafb.h
+  // device side, (re)built when the atom count or the species counts change
+  stafb_ctx* ctx;
+  stafb_model* model;
+  int cap_n;
+  std::vector<int> tipos;
+  void *theta_d, *emb_d, *pos_d, *box_d, *e_d, *f_d;
+  std::vector<int> to_slot, from_slot;
+};
+
+static bool read_matrix(const std::string& path, std::vector<double>& out) {
+  FILE* f = fopen(path.c_str(), "r");
+  if (!f) { fprintf(stderr, "libstaf: missing %s\n", path.c_str()); return false; }
+  out.clear();
+  double v;
+  while (fscanf(f, "%lf", &v) == 1) out.push_back(v);
+  fclose(f);
+  return !out.empty();
+}
+
+// STAFMLP1: magic, int32 precision, n_af, n_layers; mu[n_af]; per layer int32 act,in,out; W[in*out]; b[out]
+// (libstaf/src/mlp/staf_mlp_ort.cc:99-165)
+static bool read_mlp_bin(const std::string& path, int& n_af, std::vector<int>& widths, std::vector<double>& w) {
+  FILE* f = fopen(path.c_str(), "rb");
+  if (!f) { fprintf(stderr, "libstaf: cannot open %s\n", path.c_str()); return false; }
+  char magic[8];
+  int hdr[3];
+  bool ok = fread(magic, 1, 8, f) == 8 && memcmp(magic, "STAFMLP1", 8) == 0 && fread(hdr, 4, 3, f) == 3;
+  if (!ok) { fclose(f); fprintf(stderr, "libstaf: bad header in %s\n", path.c_str()); return false; }
+  const bool dbl = hdr[0] == 1;
+  n_af = hdr[1];
+  const int nl = hdr[2];
+  auto rd = [&](size_t n, std::vector<double>* dst) -> bool {
+    if (dbl) {
+      std::vector<double> t(n);
+      if (fread(t.data(), 8, n, f) != n) return false;
+      if (dst) dst->insert(dst->end(), t.begin(), t.end());
+    } else {
+      std::vector<float> t(n);
+      if (fread(t.data(), 4, n, f) != n) return false;
+      if (dst) dst->insert(dst->end(), t.begin(), t.end());
+    }
+    return true;
+  };
+  if (!rd(n_af, nullptr)) { fclose(f); return false; }  // mu is taken from type{k}_alpha_mu.dat
+  widths.clear();
+  w.clear();
+  for (int l = 0; l < nl; l++) {
+    int meta[3];
+    if (fread(meta, 4, 3, f) != 3) { fclose(f); return false; }
+    const int act = meta[0];
+    if ((l < nl - 1 && act != 1) || (l == nl - 1 && act != 0)) {
+      fprintf(stderr, "libstaf: %s: only tanh hidden layers and a linear output are supported\n", path.c_str());
+      fclose(f);
+      return false;
+    }
+    widths.push_back(meta[2]);
+    if (!rd((size_t)meta[1] * meta[2], &w) || !rd(meta[2], &w)) { fclose(f); return false; }
+  }
+  fclose(f);
+  return true;
+}
+
+extern "C" void staf_options_default(StafOptions* opt) {
+  if (!opt) return;
+  memset(opt, 0, sizeof(*opt));
+  opt->mlp_backend = STAF_MLP_ORT;
+  opt->device_id = 0;
+  opt->precision = 0;
+}
+
+extern "C" int staf_cuda_set_device(int device_id) {
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0) return -1;
+  if (device_id < 0) device_id = 0;
+  device_id %= ndev;
+  if (cudaSetDevice(device_id) != cudaSuccess) return -1;
+  return device_id;
+}
+
+static void release_device(StafModel* m) {
+  if (m->model) stafb_model_destroy(m->model);
+  if (m->ctx) stafb_destroy(m->ctx);
+  m->model = nullptr;
+  m->ctx = nullptr;
+  void** p[] = {&m->theta_d, &m->emb_d, &m->pos_d, &m->box_d, &m->e_d, &m->f_d};
+  for (void** q : p) { if (*q) cudaFree(*q); *q = nullptr; }
+  m->cap_n = 0;
+}
+
+extern "C" StafModel* staf_load(const char* model_dir, const StafOptions* opt) {
+  if (!model_dir) return NULL;
+  StafModel* m = new StafModel();
+  m->dir = model_dir;
+  staf_options_default(&m->opt);
+  if (opt) m->opt = *opt;
+  m->ctx = nullptr; m->model = nullptr; m->cap_n = 0;
+  m->theta_d = m->emb_d = m->pos_d = m->box_d = m->e_d = m->f_d = nullptr;
+  const int dev = staf_cuda_set_device(m->opt.device_id);
+  if (dev < 0) { delete m; return NULL; }
+  m->opt.device_id = dev;
+  // staf_jmd.cfg (keys of libstaf/vendor/jmd/nn_nn_mlp.cu:371-383), defaults of staf_api.cpp:137-147
+  m->nr = 60; m->na = 1770; m->Rc = 4.5; m->Ra = 4.5; m->Rs = 2.25; m->nt = 2;
+  {
+    FILE* f = fopen((m->dir + "/staf_jmd.cfg").c_str(), "r");
+    if (!f) f = fopen((m->dir + "/.staf_jmd_auto.cfg").c_str(), "r");
+    if (f) {
+      char line[512];
+      while (fgets(line, sizeof(line), f)) {
+        char key[256];
+        double v;
+        if (sscanf(line, " %255[^= ] = %lf", key, &v) == 2) {
+          if (!strcmp(key, "Buffer_radial_descriptors")) m->nr = (int)v;
+          else if (!strcmp(key, "Buffer_angular_descriptors")) m->na = (int)v;
+          else if (!strcmp(key, "Cutoff")) m->Rc = v;
+          else if (!strcmp(key, "Cutoff_Angular")) m->Ra = v;
+          else if (!strcmp(key, "Hardcore_Cutoff")) m->Rs = v;
+          else if (!strcmp(key, "number_of_types")) m->nt = (int)v;
+        }
+      }
+      fclose(f);
+    }
+  }
+  const int nt = m->nt, C = nt * (nt + 1) / 2;
+  if (nt < 1 || nt > STAFB_MAX_TYPES) { delete m; return NULL; }
+  std::vector<std::vector<double>> a2(nt), a3(nt), e2(nt), e3(nt), mu(nt), w(nt);
+  m->Fr.resize(nt); m->Fa.resize(nt);
+  for (int k = 0; k < nt; k++) {
+    char p[64];
+    auto path = [&](const char* suffix) { snprintf(p, sizeof(p), "/type%d_%s", k, suffix); return m->dir + p; };
+    int n_af = 0;
+    std::vector<int> widths;
+    snprintf(p, sizeof(p), "/mlp_type%d.bin", k);
+    if (!read_matrix(path("alpha_2body.dat"), a2[k]) || !read_matrix(path("alpha_3body.dat"), a3[k]) ||
+        !read_matrix(path("type_emb_2b_sq.dat"), e2[k]) || !read_matrix(path("type_emb_3b_sq.dat"), e3[k]) ||
+        !read_matrix(path("alpha_mu.dat"), mu[k]) || !read_mlp_bin(m->dir + p, n_af, widths, w[k])) {
+      delete m;
+      return NULL;
+    }
+    m->Fr[k] = (int)a2[k].size() / nt;
+    m->Fa[k] = (int)a3[k].size() / (3 * C);
+    if (k == 0) m->widths = widths;
+    if (widths != m->widths || n_af != m->Fr[k] + m->Fa[k] || (int)mu[k].size() != n_af ||
+        (int)e2[k].size() != nt * m->Fr[k] || (int)e3[k].size() != C * m->Fa[k] ||
+        (int)widths.size() > STAFB_MAX_DENSE || widths.back() != 1) {
+      fprintf(stderr, "libstaf: inconsistent model files for type %d in %s\n", k, model_dir);
+      delete m;
+      return NULL;
+    }
+  }
+  for (int k = 0; k < nt; k++) {
+    m->theta.insert(m->theta.end(), a2[k].begin(), a2[k].end());
+    m->theta.insert(m->theta.end(), a3[k].begin(), a3[k].end());
+    m->theta.insert(m->theta.end(), mu[k].begin(), mu[k].end());
+    m->theta.insert(m->theta.end(), w[k].begin(), w[k].end());
+    m->emb.insert(m->emb.end(), e2[k].begin(), e2[k].end());
+    m->emb.insert(m->emb.end(), e3[k].begin(), e3[k].end());
+  }
+  return m;
+}
+
+template <class T>
+static void upload(void* dst, const std::vector<double>& src) {
+  std::vector<T> t(src.begin(), src.end());
+  cudaMemcpy(dst, t.data(), sizeof(T) * t.size(), cudaMemcpyHostToDevice);
+}
+
+static int ensure_device(StafModel* m, int n, const std::vector<int>& tipos) {
+  if (m->ctx && n <= m->cap_n && tipos == m->tipos) return 0;
+  const size_t es = m->opt.precision == 1 ? 8 : 4;
+  if (!m->ctx || n > m->cap_n) {
+    release_device(m);
+    if (stafb_create(&m->ctx, m->opt.precision == 1 ? STAFB_F64 : STAFB_F32, m->Rc, m->Rs, m->Ra, m->nr, m->na, n,
+                     1) != STAFB_OK)
+      return -1;
+    m->cap_n = n;
+    if (cudaMalloc(&m->theta_d, es * m->theta.size()) != cudaSuccess ||
+        cudaMalloc(&m->emb_d, es * m->emb.size()) != cudaSuccess ||
+        cudaMalloc(&m->pos_d, es * 3 * (size_t)n) != cudaSuccess || cudaMalloc(&m->box_d, es * 6) != cudaSuccess ||
+        cudaMalloc(&m->e_d, es) != cudaSuccess || cudaMalloc(&m->f_d, es * 3 * (size_t)n) != cudaSuccess)
+      return -1;
+    if (es == 8) { upload<double>(m->theta_d, m->theta); upload<double>(m->emb_d, m->emb); }
+    else { upload<float>(m->theta_d, m->theta); upload<float>(m->emb_d, m->emb); }
+  }
+  if (m->model) { stafb_model_destroy(m->model); m->model = nullptr; }
+  int sd[20] = {0};
+  sd[0] = m->nt;
+  for (int t = 0; t < m->nt; t++) { sd[1 + t] = tipos[t]; sd[5 + t] = m->Fr[t]; sd[9 + t] = m->Fa[t]; }
+  sd[13] = (int)m->widths.size();
+  for (size_t l = 0; l < m->widths.size(); l++) sd[14 + l] = m->widths[l];
+  if (stafb_model_create(m->ctx, sd, &m->model) != STAFB_OK) return -1;
+  m->tipos = tipos;
+  return 0;
+}
+
+extern "C" int staf_compute(StafModel* m, int nlocal, int nghost, const double* x, const double* box,
+                            const int* type, const int* howmany, const int* with, int maxneigh, double* e_rank,
+                            double* f, double* virial) {
+  (void)nghost; (void)with; (void)maxneigh;
+  if (!m || !x || !box) return -1;
+  if (howmany != NULL) return -10;
+  if (nlocal <= 0) return -3;
+  if (box[0] == 0.0 || box[3] == 0.0 || box[5] == 0.0) return -7;
+  if (cudaSetDevice(m->opt.device_id) != cudaSuccess) return -14;
+  const int nt = m->nt;
+  // type-sorted slots (staf_api.cpp:249-294)
+  std::vector<int> tipos(nt, 0), cursor(nt, 0);
+  for (int i = 0; i < nlocal; i++) {
+    const int sp = type ? type[i] : 0;
+    if (sp < 0 || sp >= nt) { fprintf(stderr, "staf_compute: unsupported type %d at atom %d\n", sp, i); return -8; }
+    tipos[sp]++;
+  }
+  for (int t = 1; t < nt; t++) cursor[t] = cursor[t - 1] + tipos[t - 1];
+  m->to_slot.resize(nlocal);
+  m->from_slot.resize(nlocal);
+  for (int i = 0; i < nlocal; i++) {
+    const int slot = cursor[type ? type[i] : 0]++;
+    m->to_slot[i] = slot;
+    m->from_slot[slot] = i;
+  }
+  if (ensure_device(m, nlocal, tipos) != 0) return -1;
+  const bool dbl = m->opt.precision == 1;
+  const size_t es = dbl ? 8 : 4;
+  std::vector<double> pd(3 * (size_t)nlocal);
+  for (int i = 0; i < nlocal; i++)
+    for (int a = 0; a < 3; a++) pd[3 * (size_t)m->to_slot[i] + a] = x[3 * (size_t)i + a];
+  if (dbl) {
+    cudaMemcpy(m->pos_d, pd.data(), 8 * pd.size(), cudaMemcpyHostToDevice);
+    cudaMemcpy(m->box_d, box, 8 * 6, cudaMemcpyHostToDevice);
+  } else {
+    std::vector<float> pf(pd.begin(), pd.end());
+    float bf[6];
+    for (int a = 0; a < 6; a++) bf[a] = (float)box[a];
+    cudaMemcpy(m->pos_d, pf.data(), 4 * pf.size(), cudaMemcpyHostToDevice);
+    cudaMemcpy(m->box_d, bf, 4 * 6, cudaMemcpyHostToDevice);
+  }
+  int rc = stafb_energy_force(m->ctx, m->model, nullptr, m->pos_d, m->box_d, 1, m->theta_d, m->emb_d, 0, m->e_d,
+                              m->f_d);
+  if (rc != STAFB_OK) return rc == STAFB_ERR_CUDA ? -14 : -13;
+  const int st = stafb_status(m->ctx, nullptr);
+  if (st == STAFB_ERR_RADIAL_OVERFLOW) return -11;
+  if (st == STAFB_ERR_ANGULAR_OVERFLOW) return -12;
+  if (st == STAFB_ERR_BAD_BOX) return -7;
+  if (st == STAFB_ERR_CUDA) return -14;
+  if (st != STAFB_OK && st != STAFB_ERR_NONFINITE) return -13;
+  double energy = 0.0;
+  std::vector<double> fd(3 * (size_t)nlocal);
+  if (dbl) {
+    cudaMemcpy(&energy, m->e_d, 8, cudaMemcpyDeviceToHost);
+    cudaMemcpy(fd.data(), m->f_d, 8 * fd.size(), cudaMemcpyDeviceToHost);
+  } else {
+    float ef = 0.f;
+    std::vector<float> ff(fd.size());
+    cudaMemcpy(&ef, m->e_d, 4, cudaMemcpyDeviceToHost);
+    cudaMemcpy(ff.data(), m->f_d, 4 * ff.size(), cudaMemcpyDeviceToHost);
+    energy = ef;
+    for (size_t q = 0; q < fd.size(); q++) fd[q] = ff[q];
+  }
+  (void)es;
+  if (!isfinite(energy))
+    fprintf(stderr, "staf_compute: non-finite energy=%g nlocal=%d\n", energy, nlocal);  // as staf_api.cpp:378-381
+  if (e_rank) *e_rank = energy;
+  if (f)
+    for (int s = 0; s < nlocal; s++)
+      for (int a = 0; a < 3; a++) f[3 * (size_t)m->from_slot[s] + a] = fd[3 * (size_t)s + a];
+  if (virial)
+    for (int a = 0; a < 6; a++) virial[a] = 0.0;
+  return 0;
+}
+
+extern "C" void staf_free(StafModel* m) {
+  if (!m) return;
+  cudaSetDevice(m->opt.device_id);
+  release_device(m);
+  delete m;
+}
