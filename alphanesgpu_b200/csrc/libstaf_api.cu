@@ -158,9 +158,10 @@ extern "C" StafModel* staf_load(const char* model_dir, const StafOptions* opt) {
     int n_af = 0;
     std::vector<int> widths;
     snprintf(p, sizeof(p), "/mlp_type%d.bin", k);
+    const std::string bin_path = m->dir + p;
     if (!read_matrix(path("alpha_2body.dat"), a2[k]) || !read_matrix(path("alpha_3body.dat"), a3[k]) ||
         !read_matrix(path("type_emb_2b_sq.dat"), e2[k]) || !read_matrix(path("type_emb_3b_sq.dat"), e3[k]) ||
-        !read_matrix(path("alpha_mu.dat"), mu[k]) || !read_mlp_bin(m->dir + p, n_af, widths, w[k])) {
+        !read_matrix(path("alpha_mu.dat"), mu[k]) || !read_mlp_bin(bin_path, n_af, widths, w[k])) {
       delete m;
       return NULL;
     }
