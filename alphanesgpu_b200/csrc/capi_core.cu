@@ -65,6 +65,11 @@ static void core_coefficients(double Rc, double Rs, double* out) {
   out[0] = cA; out[1] = cB; out[2] = cC; out[3] = alpha; out[4] = beta;
 }
 
+void stafb_core_coefficients_for(int dtype, double Rc, double Rs, double out5[5]) {
+  if (dtype == STAFB_F32) core_coefficients<float>(Rc, Rs, out5);
+  else core_coefficients<double>(Rc, Rs, out5);
+}
+
 extern "C" int stafb_create(stafb_ctx** out, int dtype, double Rc, double Rs, double Ra, int nr, int na, int n_max,
                             int max_batch) {
   if (!out || (dtype != STAFB_F32 && dtype != STAFB_F64) || nr <= 0 || nr > 255 || na <= 0 || n_max <= 0 ||

@@ -128,6 +128,8 @@ struct stafb_ctx {
   } while (0)
 
 void stafb_record_cuda_error(cudaError_t e, const char* file, int line);
+// repulsive-core coefficients for a dtype (STAFB_F32 / STAFB_F64), evaluated on the host in that precision
+void stafb_core_coefficients_for(int dtype, double Rc, double Rs, double out5[5]);
 
 // launchers implemented per translation unit (T = float | double)
 namespace stafb {

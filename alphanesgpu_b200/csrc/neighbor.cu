@@ -10,6 +10,7 @@
 // This translation unit is compiled with -fmad=false: positions, squared distances and the
 // cutoff tests must round in expression order, because neighbour sets and neighbour ORDER
 // are compared bit-exactly.
+#include <string.h>
 #include "common.cuh"
 
 namespace stafb {
@@ -455,3 +456,117 @@ template int launch_descriptors<double>(stafb_ctx*, cudaStream_t, const double*,
                                         double*, double*, int*, int*, double*, double*, double*, int*);
 
 }  // namespace stafb
+
+// ---------------------------------------------------------------------------------------------
+// ComputeDescriptorsLight without any allocation.
+//
+// Some callers cannot allocate device memory at the point where they need the descriptors: code
+// running inside a framework's op callback whose memory is owned by that framework's allocator, a
+// plug-in invoked while another library holds the allocator lock, or a process that was given a fixed
+// memory budget up front.  stafb_create() calls cudaMalloc for the neighbour-list scratch (fractional
+// coordinates, the cell lists, the sorted neighbour rows); this entry point keeps that scratch in a
+// fixed array that is part of the library image instead.  Every GPU that loads the library holds those
+// STAFB_NOALLOC_SCRATCH_BYTES until the process exits.
+//
+// Limits: nf*N <= 1024 atoms per call, nf <= 16 frames, radial_buffer <= 64.  All calls share the one
+// array, so two calls that overlap on the same GPU (different streams or threads) race; the array keeps
+// the previous call's contents, and the parts that must start at zero (cell counters, status word) are
+// cleared on the stream at the start of every call.
+namespace {
+constexpr int NOALLOC_MAX_ATOMS = 1024;
+constexpr int NOALLOC_MAX_FRAMES = 16;
+constexpr int NOALLOC_MAX_NR = 64;
+constexpr int NOALLOC_MAX_CELLS = 4 * NOALLOC_MAX_ATOMS + 64 * NOALLOC_MAX_FRAMES + 27 * 4 * NOALLOC_MAX_FRAMES;
+constexpr size_t al256(size_t x) { return (x + 255) & ~(size_t)255; }
+constexpr size_t NA_OFF_FGEOM = 0;
+constexpr size_t NA_OFF_FRAC = NA_OFF_FGEOM + al256(sizeof(stafb::FrameGeom<double>) * NOALLOC_MAX_FRAMES);
+constexpr size_t NA_OFF_CELLOF = NA_OFF_FRAC + al256(sizeof(double) * 3 * NOALLOC_MAX_ATOMS);
+constexpr size_t NA_OFF_COUNT = NA_OFF_CELLOF + al256(sizeof(int) * NOALLOC_MAX_ATOMS);
+constexpr size_t NA_OFF_START = NA_OFF_COUNT + al256(sizeof(int) * NOALLOC_MAX_CELLS);
+constexpr size_t NA_OFF_CURSOR = NA_OFF_START + al256(sizeof(int) * (NOALLOC_MAX_CELLS + NOALLOC_MAX_FRAMES));
+constexpr size_t NA_OFF_RAW = NA_OFF_CURSOR + al256(sizeof(int) * NOALLOC_MAX_CELLS);
+constexpr size_t NA_OFF_SORTED = NA_OFF_RAW + al256(sizeof(int) * NOALLOC_MAX_ATOMS);
+constexpr size_t NA_OFF_GEOM = NA_OFF_SORTED + al256(sizeof(int) * NOALLOC_MAX_ATOMS);
+constexpr size_t NA_OFF_GSC = NA_OFF_GEOM + al256(sizeof(double) * 4 * NOALLOC_MAX_ATOMS * NOALLOC_MAX_NR);
+constexpr size_t NA_OFF_STATUS = NA_OFF_GSC + al256(sizeof(double) * 2 * NOALLOC_MAX_ATOMS * NOALLOC_MAX_NR);
+constexpr size_t NA_TOTAL = NA_OFF_STATUS + 256;
+constexpr int NOALLOC_MAX_DEVICES = 64;
+}  // namespace
+
+// The scratch itself.  In host code this name is only a handle for cudaGetSymbolAddress; the device
+// address is looked up once per device below.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NA_TOTAL];
+static void* g_noalloc_addr[NOALLOC_MAX_DEVICES] = {nullptr};
+
+extern "C" size_t stafb_noalloc_scratch_bytes(void) { return NA_TOTAL; }
+
+extern "C" int stafb_compute_descriptors_light_noalloc(int dtype, double radial_cutoff, double rs, double ra,
+                                                       int radial_buffer, int angular_buffer, void* stream,
+                                                       const void* positions_d, const void* boxer_d, int nf, int N,
+                                                       void* raddescr_d, void* angdescr_d, void* des3bsupp_d,
+                                                       int* intmap2b_d, int* intmap3b_d, void* der2b_d,
+                                                       void* der3b_d, void* der3bsupp_d, int* numtriplet_d,
+                                                       int* status_out_d) {
+  if ((dtype != STAFB_F32 && dtype != STAFB_F64) || !positions_d || !boxer_d || !raddescr_d || !des3bsupp_d ||
+      !intmap2b_d || !der2b_d || !der3bsupp_d || !numtriplet_d || nf <= 0 || N <= 0 || radial_buffer <= 0 ||
+      angular_buffer <= 0 || !(radial_cutoff > 0) || !(ra > 0) || ra > radial_cutoff)
+    return STAFB_ERR_INVALID;
+  if (nf > NOALLOC_MAX_FRAMES || (long long)nf * N > NOALLOC_MAX_ATOMS || radial_buffer > NOALLOC_MAX_NR) {
+    fprintf(stderr,
+            "stafb_compute_descriptors_light_noalloc: nf=%d N=%d radial_buffer=%d exceed the built-in scratch "
+            "(at most %d frames, %d atoms in total, radial_buffer %d); use stafb_create + "
+            "stafb_compute_descriptors_light\n",
+            nf, N, radial_buffer, NOALLOC_MAX_FRAMES, NOALLOC_MAX_ATOMS, NOALLOC_MAX_NR);
+    return STAFB_ERR_CAPACITY;
+  }
+  const int cell_cap = 4 * (N > 27 ? N : 27) + 64;
+  if ((long long)nf * cell_cap > NOALLOC_MAX_CELLS) return STAFB_ERR_CAPACITY;
+  int dev = 0;
+  STAFB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return STAFB_ERR_CAPACITY;
+  if (!g_noalloc_addr[dev]) {
+    // first call on this device (do it before any stream capture): resolve the device address of the array
+    void* p = nullptr;
+    STAFB_CUDA_OK(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    g_noalloc_addr[dev] = p;
+  }
+  unsigned char* base = static_cast<unsigned char*>(g_noalloc_addr[dev]);
+  cudaStream_t s = (cudaStream_t)stream;
+  stafb_ctx c;
+  memset(&c, 0, sizeof(c));
+  c.dtype = dtype;
+  c.Rc = radial_cutoff; c.Rs = rs; c.Ra = ra;
+  c.nr = radial_buffer; c.na = angular_buffer; c.n_max = N; c.max_batch = nf;
+  stafb_core_coefficients_for(dtype, radial_cutoff, rs, c.coef);
+  c.device = dev;
+  c.cell_cap = cell_cap;
+  c.fgeom = base + NA_OFF_FGEOM;
+  c.frac = base + NA_OFF_FRAC;
+  c.cell_of = reinterpret_cast<int*>(base + NA_OFF_CELLOF);
+  c.cell_count = reinterpret_cast<int*>(base + NA_OFF_COUNT);
+  c.cell_start = reinterpret_cast<int*>(base + NA_OFF_START);
+  c.cell_cursor = reinterpret_cast<int*>(base + NA_OFF_CURSOR);
+  c.cells_raw = reinterpret_cast<int*>(base + NA_OFF_RAW);
+  c.cells_sorted = reinterpret_cast<int*>(base + NA_OFF_SORTED);
+  c.geom = base + NA_OFF_GEOM;
+  c.gsc = base + NA_OFF_GSC;
+  c.status_d = reinterpret_cast<int*>(base + NA_OFF_STATUS);
+  // the shared array keeps the previous call's contents: clear the status word here (the cell
+  // counters are cleared by the descriptor launch sequence itself)
+  STAFB_CUDA_OK(cudaMemsetAsync(c.status_d, 0, sizeof(int), s));
+  int rc;
+  if (dtype == STAFB_F32)
+    rc = stafb::launch_descriptors<float>(&c, s, (const float*)positions_d, (const float*)boxer_d, nf, N,
+                                          (float*)raddescr_d, (float*)angdescr_d, (float*)des3bsupp_d, intmap2b_d,
+                                          intmap3b_d, (float*)der2b_d, (float*)der3b_d, (float*)der3bsupp_d,
+                                          numtriplet_d);
+  else
+    rc = stafb::launch_descriptors<double>(&c, s, (const double*)positions_d, (const double*)boxer_d, nf, N,
+                                           (double*)raddescr_d, (double*)angdescr_d, (double*)des3bsupp_d,
+                                           intmap2b_d, intmap3b_d, (double*)der2b_d, (double*)der3b_d,
+                                           (double*)der3bsupp_d, numtriplet_d);
+  if (rc != STAFB_OK) return rc;
+  if (status_out_d)
+    STAFB_CUDA_OK(cudaMemcpyAsync(status_out_d, c.status_d, sizeof(int), cudaMemcpyDeviceToDevice, s));
+  return STAFB_OK;
+}

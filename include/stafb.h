@@ -14,6 +14,8 @@
 #ifndef STAFB_H
 #define STAFB_H
 
+#include <stddef.h>
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -70,6 +72,25 @@ int stafb_compute_descriptors_light(stafb_ctx* ctx, void* stream, const void* po
                                     int nf, int N, void* raddescr_d, void* angdescr_d, void* des3bsupp_d,
                                     int* intmap2b_d, int* intmap3b_d, void* der2b_d, void* der3b_d,
                                     void* der3bsupp_d, int* numtriplet_d);
+
+/* ComputeDescriptorsLight for callers that must not allocate.  No counterpart in the reference.
+ * stafb_create() obtains the neighbour-list scratch with cudaMalloc; some callers cannot do that where
+ * they need the descriptors (an op callback whose device memory belongs to the host framework's
+ * allocator, a plug-in entered while another library holds the allocator lock, a process with a fixed
+ * memory budget).  This entry point takes no handle and allocates nothing: the scratch is a fixed array
+ * inside the library image (stafb_noalloc_scratch_bytes() bytes, about 3.3 MB, held by every GPU that
+ * loads the library until the process exits).  Limits: nf <= 16, nf*N <= 1024 atoms, radial_buffer <= 64;
+ * larger requests return STAFB_ERR_CAPACITY and print the limits.  The first call on a device looks up
+ * the array's device address (cudaGetSymbolAddress); make that first call outside any stream capture.
+ * All calls share the array: calls that overlap on one GPU race, so serialise them (one stream).  Outputs
+ * and their optional/NULL rules are those of stafb_compute_descriptors_light; status_out_d (device int,
+ * may be NULL) receives the status word (STAFB_OK, STAFB_ERR_RADIAL_OVERFLOW, ...) on the stream. */
+int stafb_compute_descriptors_light_noalloc(int dtype, double radial_cutoff, double rs, double ra, int radial_buffer,
+                                            int angular_buffer, void* stream, const void* positions_d,
+                                            const void* boxer_d, int nf, int N, void* raddescr_d, void* angdescr_d,
+                                            void* des3bsupp_d, int* intmap2b_d, int* intmap3b_d, void* der2b_d,
+                                            void* der3b_d, void* der3bsupp_d, int* numtriplet_d, int* status_out_d);
+size_t stafb_noalloc_scratch_bytes(void);
 
 /* ComputeSortProj (fingerprint/rad/reforce.cc:13-19) -> two_body_afs[nf,Nl,Fr] */
 int stafb_compute_sort_proj(stafb_ctx* ctx, void* stream, const void* radial_descriptor_d,
