@@ -78,7 +78,8 @@ struct SweepIn {
   int nf, nr;
 };
 
-enum { MODE_AF = 0, MODE_FORCE = 1, MODE_FGRAD = 2, MODE_AFGRAD = 3 };
+// AFV = AF forward that also leaves d(AF)/d(alpha) per atom (training); AFGRAD = stand-alone alpha gradient
+enum { MODE_AF = 0, MODE_FORCE = 1, MODE_FGRAD = 2, MODE_AFGRAD = 3, MODE_AFV = 4 };
 
 // species-major enumeration: block -> (species t, index q0 of its first atom among the nf*tipos[t]
 // atoms of that species); W atoms per block, blocks never mix species
@@ -169,11 +170,14 @@ __global__ void __launch_bounds__(WPA * 32)
             const T* __restrict__ chan_in,  // FORCE/FGRAD: netderiv[nf,N,Fmax]; AFGRAD: dL/dAF[nf,N,Fmax]
             const T* __restrict__ fbar,     // FGRAD: dL/dF[nf,3N]
             T* __restrict__ out,            // AF: af[nf,N,Fmax]; FORCE: force[nf,3N]; FGRAD: gradnet[nf,N,Fmax]
-            T* __restrict__ grad) {         // FGRAD/AFGRAD: flat parameter gradient (accumulated)
+            T* __restrict__ grad,           // FGRAD/AFGRAD: flat parameter gradient (accumulated)
+            T* __restrict__ vout, int nv) { // AFV: d(AF)/d(alpha2b|alpha3b) rows [nf,N,nv]
   extern __shared__ __align__(16) unsigned char smem_raw[];
   typedef typename Vec4<T>::type T4;
   typedef typename Vec2<T>::type T2;
   constexpr int NT = WPA * 32;
+  constexpr bool IS_AF = (MODE == MODE_AF || MODE == MODE_AFV);       // produces fingerprints
+  constexpr bool HAS_V = (MODE == MODE_AFGRAD || MODE == MODE_AFV);   // accumulates d(AF)/d(alpha) terms
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int t, b, i;
   if (!locate_atom(md, in.nf, 1, 0, t, b, i)) return;
@@ -295,9 +299,9 @@ __global__ void __launch_bounds__(WPA * 32)
       atomicAdd(&xtra[k * 3 + 2], gz);
       fix -= gx; fiy -= gy; fiz -= gz;
     }
-  } else {  // FGRAD / AFGRAD: gradients with respect to alpha2b (and gradnet for FGRAD)
+  } else {  // FGRAD / AFGRAD / AFV: alpha2b terms (plus gradnet for FGRAD, fingerprints for AFV)
     for (int c = warp; c < Fr; c += WPA) {
-      const T cin = chrow[c];  // FGRAD: netderiv ; AFGRAD: dL/dAF
+      const T cin = (MODE == MODE_AFV) ? T(1) : chrow[c];  // FGRAD: netderiv ; AFGRAD: dL/dAF
       T gn = T(0);
       T ga[STAFB_MAX_TYPES];
 #pragma unroll
@@ -315,12 +319,13 @@ __global__ void __launch_bounds__(WPA * 32)
           va = q * cin * ch * ex * dk * (T(2) + al * dk);
         } else {
           va = cin * ch * ex * dk * dk;
+          if (MODE == MODE_AFV) gn += dk * ex * ch;
         }
 #pragma unroll
         for (int q = 0; q < STAFB_MAX_TYPES; q++)
           if (q == tk) ga[q] += va;
       }
-      if (MODE == MODE_FGRAD) {
+      if (MODE == MODE_FGRAD || MODE == MODE_AFV) {
         gn = warp_sum(gn);
         if (lane == 0) out[gi * Fmax + c] = gn;
       }
@@ -370,7 +375,7 @@ __global__ void __launch_bounds__(WPA * 32)
           chpa[tid] = pa;
           T2 pb;
           pb.x = T(0); pb.y = T(0);
-          if (MODE == MODE_AF) pb.x = T(0.5) * ee;
+          if (IS_AF) pb.x = T(0.5) * ee;
           if (MODE == MODE_FORCE) pb.x = T(0.25) * chrow[Fr + c] * ee;
           if (MODE == MODE_FGRAD) { pb.x = T(0.5) * ee; pb.y = chrow[Fr + c]; }
           if (MODE == MODE_AFGRAD) pb.x = T(0.5) * chrow[Fr + c] * ee;
@@ -503,13 +508,14 @@ __global__ void __launch_bounds__(WPA * 32)
                 const T S1 = A.y * B.x;  // exp(a2*sj + a1*sk)
                 const T S2 = A.x * B.y;  // exp(a1*sj + a2*sk)
                 const T eb = Ex<T>::f(pa.w * tt);
-                if (MODE == MODE_AF) {
-                  r0[l] += tt * (S1 + S2) * eb;  // the channel coefficient is applied after the reduction
-                } else if (MODE == MODE_AFGRAD) {
+                if (IS_AF || MODE == MODE_AFGRAD) {
                   const T cm = eb * tt;
-                  r1[l] += cm * (S2 * fcj + S1 * fck);
-                  r2[l] += cm * (S2 * fck + S1 * fcj);
-                  r3[l] += cm * (S1 + S2) * tt;
+                  if (IS_AF) r0[l] += cm * (S1 + S2);  // the channel coefficient is applied after the reduction
+                  if (HAS_V) {
+                    r1[l] += cm * (S2 * fcj + S1 * fck);
+                    r2[l] += cm * (S2 * fck + S1 * fcj);
+                    r3[l] += cm * (S1 + S2) * tt;
+                  }
                 } else {  // FGRAD
                   const T al1 = pa.x, al2 = pa.y, be = pa.z;
                   const T ss = S1 + S2, opb = T(1) + be * tt;
@@ -532,11 +538,11 @@ __global__ void __launch_bounds__(WPA * 32)
 #pragma unroll
           for (int l = 0; l < MAXCH; l++) {
             if (l < nch) {
-              if (MODE == MODE_AF || MODE == MODE_FGRAD) {
+              if (IS_AF || MODE == MODE_FGRAD) {
                 const T v = warp_sum(r0[l]);
                 if (lane == 0) red[warp * 4 * MAXCH + 4 * l + 0] = v;
               }
-              if (MODE == MODE_AFGRAD || MODE == MODE_FGRAD) {
+              if (HAS_V || MODE == MODE_FGRAD) {
                 const T v1 = warp_sum(r1[l]), v2 = warp_sum(r2[l]), v3 = warp_sum(r3[l]);
                 if (lane == 0) {
                   red[warp * 4 * MAXCH + 4 * l + 1] = v1;
@@ -549,8 +555,7 @@ __global__ void __launch_bounds__(WPA * 32)
           gsync<WPA>();
           if (tid < 4 * nch) {
             const int l = tid >> 2, v = tid & 3;
-            const bool use = (v == 0) ? (MODE == MODE_AF || MODE == MODE_FGRAD)
-                                      : (MODE == MODE_AFGRAD || MODE == MODE_FGRAD);
+            const bool use = (v == 0) ? (IS_AF || MODE == MODE_FGRAD) : (HAS_V || MODE == MODE_FGRAD);
             if (use) {
               T sum = T(0);
 #pragma unroll
@@ -572,9 +577,23 @@ __global__ void __launch_bounds__(WPA * 32)
   gsync<WPA>();
 
   // ------------------------------------------------------------------ write-back
-  if (MODE == MODE_AF) {
+  if (IS_AF) {
     for (int c = tid; c < Fa; c += NT) out[gi * Fmax + Fr + c] = acc[ACC_GN + c];
     for (int c = Fr + Fa + tid; c < Fmax; c += NT) out[gi * Fmax + c] = T(0);
+    if (MODE == MODE_AFV) {
+      // d(AF)/d(alpha) of this atom, in the order alpha2b[nt,Fr] | alpha3b[C,3Fa] of the parameter block
+      T* vr = vout + gi * nv;
+      const int n2 = nt * Fr, nq = n2 + md.C * 3 * Fa;
+      for (int q = tid; q < nq; q += NT) {
+        T v;
+        if (q < n2) v = acc[ACC_A2 + (q / Fr) * md.Frmax + (q % Fr)];
+        else {
+          const int r = q - n2, sc = r / 3, comp = r - sc * 3, s = sc / Fa, c = sc - s * Fa;
+          v = acc[ACC_A3 + (s * md.Famax + c) * 3 + comp];
+        }
+        vr[q] = v;
+      }
+    }
   } else if (MODE == MODE_FORCE) {
     T* fb = out + (size_t)b * N * 3;
     for (int q = tid; q < 3 * n; q += NT) atomicAdd(fb + (size_t)ids[q / 3] * 3 + (q % 3), xtra[q]);
@@ -610,21 +629,52 @@ __global__ void __launch_bounds__(WPA * 32)
 // species; activations live in shared memory feature-major ([feature][atom]) so that a thread holds
 // APT atoms in registers while it streams one weight column, coalesced, from global memory.
 
+// Stages one Dense layer (weights [in][out] row-major + bias[out]) into shared memory with a padded
+// row stride of out+1 words, all threads loading at once: the dot-product loops then never wait on
+// global memory, and both access patterns (lanes over j, lanes over i) are bank-conflict free.
+template <class T>
+struct LayerView {
+  const T* W;  // element (i,j) at W[i*ld + j]
+  const T* B;  // bias
+  int ld;
+};
+
+// When the layer does not fit next to the activations (stage == false) the view points at global memory.
+template <class T>
+__device__ __forceinline__ LayerView<T> stage_layer(int in, int out, const T* __restrict__ Wl, T* wsm, bool stage) {
+  __syncthreads();  // previous users of wsm are done, inputs of the layer are complete
+  LayerView<T> v;
+  if (!stage) {
+    v.W = Wl; v.B = Wl + in * out; v.ld = out;
+    return v;
+  }
+  const int ld = out + 1;
+  v.W = wsm; v.B = wsm + in * ld; v.ld = ld;
+  for (int idx = threadIdx.x; idx < in * out; idx += ML_THREADS) {
+    const int i = idx / out, j = idx - i * out;
+    wsm[i * ld + j] = Wl[idx];
+  }
+  for (int j = threadIdx.x; j < out; j += ML_THREADS) wsm[in * ld + j] = Wl[in * out + j];
+  __syncthreads();
+  return v;
+}
+
 // Y[j][a] = act( b[j] + sum_i X[i][a] W[i,j] ), a in the thread's APT atoms, j over lanes
 template <class T, int APT, bool TANH, bool BIAS>
-__device__ __forceinline__ void dense_fwd(int in, int out, const T* __restrict__ Wl, const T* __restrict__ Bl,
-                                          const T* X, T* Y) {
+__device__ __forceinline__ void dense_fwd(int in, int out, const LayerView<T> lv, const T* X, T* Y) {
   constexpr int TA = 8 * APT;
-  const int jl = threadIdx.x & 31, ag = threadIdx.x >> 5;
+  const int jl = threadIdx.x & 31, ag = threadIdx.x >> 5, ld = lv.ld;
+  const T* wsm = lv.W;
   for (int j0 = 0; j0 < out; j0 += 32) {
     const int j = j0 + jl;
     if (j < out) {
       T a[APT];
-      const T bj = BIAS ? Bl[j] : T(0);
+      const T bj = BIAS ? lv.B[j] : T(0);
 #pragma unroll
       for (int q = 0; q < APT; q++) a[q] = bj;
+#pragma unroll 4
       for (int i = 0; i < in; i++) {
-        const T w = Wl[i * out + j];
+        const T w = wsm[i * ld + j];
         const T* xp = X + i * TA + ag * APT;
 #pragma unroll
         for (int q = 0; q < APT; q++) a[q] += xp[q] * w;
@@ -635,54 +685,36 @@ __device__ __forceinline__ void dense_fwd(int in, int out, const T* __restrict__
   }
 }
 
-// Xo[i][a] = sum_j D[j][a] W[i,j]  (and the same for a second cotangent D2 -> Xo2 when given).
-// W is staged through shared memory in column chunks; the transposed access is then conflict-free.
+// Xo[i][a] = sum_j D[j][a] W[i,j]  (and the same for a second cotangent D2 -> Xo2 when given)
 template <class T, int APT>
-__device__ __forceinline__ void dense_bwd(int in, int out, const T* __restrict__ Wl, const T* D, T* Xo, const T* D2,
-                                          T* Xo2, T* wt /*[in][33]*/) {
+__device__ __forceinline__ void dense_bwd(int in, int out, const LayerView<T> lv, const T* D, T* Xo, const T* D2,
+                                          T* Xo2) {
   constexpr int TA = 8 * APT;
-  const int il = threadIdx.x & 31, ag = threadIdx.x >> 5;
+  const int il = threadIdx.x & 31, ag = threadIdx.x >> 5, ld = lv.ld;
+  const T* wsm = lv.W;
   __syncthreads();
   for (int i0 = 0; i0 < in; i0 += 32) {
     const int i = i0 + il;
     if (i < in) {
+      T a[APT], a2[APT];
+#pragma unroll
+      for (int q = 0; q < APT; q++) a[q] = a2[q] = T(0);
+#pragma unroll 4
+      for (int j = 0; j < out; j++) {
+        const T w = wsm[i * ld + j];
+        const T* dp = D + j * TA + ag * APT;
+#pragma unroll
+        for (int q = 0; q < APT; q++) a[q] += dp[q] * w;
+        if (D2) {
+          const T* dp2 = D2 + j * TA + ag * APT;
+#pragma unroll
+          for (int q = 0; q < APT; q++) a2[q] += dp2[q] * w;
+        }
+      }
 #pragma unroll
       for (int q = 0; q < APT; q++) {
-        Xo[i * TA + ag * APT + q] = T(0);
-        if (D2) Xo2[i * TA + ag * APT + q] = T(0);
-      }
-    }
-  }
-  for (int j0 = 0; j0 < out; j0 += 32) {
-    const int jc = (out - j0) < 32 ? (out - j0) : 32;
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < in * jc; idx += ML_THREADS) {
-      const int i = idx / jc, jj = idx - i * jc;
-      wt[i * 33 + jj] = Wl[i * out + j0 + jj];
-    }
-    __syncthreads();
-    for (int i0 = 0; i0 < in; i0 += 32) {
-      const int i = i0 + il;
-      if (i < in) {
-        T a[APT], a2[APT];
-#pragma unroll
-        for (int q = 0; q < APT; q++) a[q] = a2[q] = T(0);
-        for (int jj = 0; jj < jc; jj++) {
-          const T w = wt[i * 33 + jj];
-          const T* dp = D + (j0 + jj) * TA + ag * APT;
-#pragma unroll
-          for (int q = 0; q < APT; q++) a[q] += dp[q] * w;
-          if (D2) {
-            const T* dp2 = D2 + (j0 + jj) * TA + ag * APT;
-#pragma unroll
-            for (int q = 0; q < APT; q++) a2[q] += dp2[q] * w;
-          }
-        }
-#pragma unroll
-        for (int q = 0; q < APT; q++) {
-          Xo[i * TA + ag * APT + q] += a[q];
-          if (D2) Xo2[i * TA + ag * APT + q] += a2[q];
-        }
+        Xo[i * TA + ag * APT + q] = a[q];
+        if (D2) Xo2[i * TA + ag * APT + q] = a2[q];
       }
     }
   }
@@ -692,7 +724,7 @@ __device__ __forceinline__ void dense_bwd(int in, int out, const T* __restrict__
 template <class T, int APT>
 __global__ void __launch_bounds__(ML_THREADS)
     k_mlp_fwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ af, T* __restrict__ acts,
-              T* __restrict__ e_atom, T* __restrict__ netderiv) {
+              T* __restrict__ e_atom, T* __restrict__ netderiv, int stage) {
   constexpr int TA = 8 * APT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int t, q0;
@@ -703,7 +735,7 @@ __global__ void __launch_bounds__(ML_THREADS)
   T* H = X + Fm * TA;                     // [Hs][TA]
   T* C0 = H + Hs * TA;                    // [mw][TA]
   T* C1 = C0 + mw * TA;                   // [mw][TA]
-  T* wt = C1 + mw * TA;                   // [mw][33]
+  T* wsm = C1 + mw * TA;                  // one staged layer: (in+1) x (out+1)
   const T* mu = theta + md.off_mu[t];
   const T* w = theta + md.off_w[t];
   auto gidx = [&](int a) -> long long {
@@ -717,17 +749,17 @@ __global__ void __launch_bounds__(ML_THREADS)
     const long long gi = gidx(a);
     X[i * TA + a] = gi >= 0 ? r_log(af[gi * Fm + i] + T(1e-3)) - mu[i] : T(0);
   }
-  __syncthreads();
   const T* hin = X;
+  LayerView<T> lv;
   for (int l = 0; l < Lq; l++) {
     const int in = md.in_of(t, l), out = md.width[l];
-    const T* Wl = w + md.w_off(t, l);
+    lv = stage_layer(in, out, w + md.w_off(t, l), wsm, stage != 0);
     T* hout = H + md.h_off(l) * TA;
-    if (l < Lq - 1) dense_fwd<T, APT, true, true>(in, out, Wl, Wl + in * out, hin, hout);
-    else dense_fwd<T, APT, false, true>(in, out, Wl, Wl + in * out, hin, hout);
-    __syncthreads();
+    if (l < Lq - 1) dense_fwd<T, APT, true, true>(in, out, lv, hin, hout);
+    else dense_fwd<T, APT, false, true>(in, out, lv, hin, hout);
     hin = hout;
   }
+  __syncthreads();
   // activations, block-local feature-major copy for the backward kernel
   T* ab = acts + (size_t)blockIdx.x * Hs * TA;
   for (int idx = threadIdx.x; idx < Hs * TA; idx += ML_THREADS) ab[idx] = H[idx];
@@ -739,14 +771,15 @@ __global__ void __launch_bounds__(ML_THREADS)
   T* cn = C0;
   T* cp = C1;
   if (threadIdx.x < TA) cn[threadIdx.x] = T(1);
-  __syncthreads();
   for (int l = Lq - 1; l >= 0; l--) {
     const int in = md.in_of(t, l), out = md.width[l];
+    if (l < Lq - 1) lv = stage_layer(in, out, w + md.w_off(t, l), wsm, stage != 0);  // the last layer is still staged
+    else __syncthreads();
     if (l < Lq - 1) {
       const T* hl = H + md.h_off(l) * TA;
       for (int idx = threadIdx.x; idx < out * TA; idx += ML_THREADS) cn[idx] *= (T(1) - hl[idx] * hl[idx]);
     }
-    dense_bwd<T, APT>(in, out, w + md.w_off(t, l), cn, cp, nullptr, nullptr, wt);
+    dense_bwd<T, APT>(in, out, lv, cn, cp, nullptr, nullptr);
     T* tmp = cn; cn = cp; cp = tmp;
   }
   for (int idx = threadIdx.x; idx < Fm * TA; idx += ML_THREADS) {
@@ -760,11 +793,14 @@ __global__ void __launch_bounds__(ML_THREADS)
 // weights, mu and AF: the first term is plain back-propagation, the second is the derivative
 // of a directional derivative (tangent v = u/(AF+eps) pushed forward, then reversed) - what
 // TensorFlow's autodiff does through grad_ene for the force loss (staf_model.py:191,225-228).
+// The kernel also contracts dL/dAF with the per-atom d(AF)/d(alpha) rows left by the AF sweep
+// (vrow), which yields the fingerprint part of dL/dalpha without another sweep over the triplets.
 template <class T, int APT>
 __global__ void __launch_bounds__(ML_THREADS)
     k_mlp_bwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ af,
               const T* __restrict__ acts, const T* __restrict__ ebar /*[nf]*/, const T* __restrict__ u /*[nf,N,Fmax]*/,
-              T* __restrict__ gaf, T* __restrict__ grad) {
+              const T* __restrict__ vrow /*[nf,N,nv] or null*/, int nv, T* __restrict__ gaf, T* __restrict__ grad,
+              int stage) {
   constexpr int TA = 8 * APT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int t, q0;
@@ -780,7 +816,7 @@ __global__ void __launch_bounds__(ML_THREADS)
   T* DP = DQ + Hs * TA;                   // cotangent on the pre-activation tangent
   T* CQ = DP + Hs * TA;                   // [mw][TA]
   T* CP = CQ + mw * TA;                   // [mw][TA]
-  T* wt = CP + mw * TA;                   // [mw][33]
+  T* wsm = CP + mw * TA;                  // one staged layer
   const T* mu = theta + md.off_mu[t];
   const T* w = theta + md.off_w[t];
   auto gidx = [&](int a) -> long long {
@@ -806,32 +842,33 @@ __global__ void __launch_bounds__(ML_THREADS)
     const int a = idx % TA;
     H[idx] = (q0 + a < nat) ? ab[idx] : T(0);
   }
-  __syncthreads();
   // forward tangent: AD = HDin W ; HD = AD * act'
   const T* hdin = V;
+  LayerView<T> lv;
   for (int l = 0; l < Lq; l++) {
     const int in = md.in_of(t, l), out = md.width[l];
+    lv = stage_layer(in, out, w + md.w_off(t, l), wsm, stage != 0);
     T* ado = AD + md.h_off(l) * TA;
     T* hdo = HD + md.h_off(l) * TA;
-    dense_fwd<T, APT, false, false>(in, out, w + md.w_off(t, l), nullptr, hdin, ado);
+    dense_fwd<T, APT, false, false>(in, out, lv, hdin, ado);
     __syncthreads();
     const T* ho = H + md.h_off(l) * TA;
     for (int idx = threadIdx.x; idx < out * TA; idx += ML_THREADS)
       hdo[idx] = (l < Lq - 1) ? ado[idx] * (T(1) - ho[idx] * ho[idx]) : ado[idx];
-    __syncthreads();
     hdin = hdo;
   }
+  __syncthreads();
   // reverse over (h, hd)
   if (threadIdx.x < TA) {
     const long long gi = gidx(threadIdx.x);
     CQ[threadIdx.x] = gi >= 0 ? ebar[gi / md.N] : T(0);
     CP[threadIdx.x] = gi >= 0 ? T(1) : T(0);
   }
-  __syncthreads();
   T* gw = grad + md.off_w[t];
   for (int l = Lq - 1; l >= 0; l--) {
     const int in = md.in_of(t, l), out = md.width[l];
-    const T* Wl = w + md.w_off(t, l);
+    if (l < Lq - 1) lv = stage_layer(in, out, w + md.w_off(t, l), wsm, stage != 0);  // the last layer is still staged
+    else __syncthreads();
     const T* ho = H + md.h_off(l) * TA;
     const T* ado = AD + md.h_off(l) * TA;
     T* dql = DQ + md.h_off(l) * TA;
@@ -856,14 +893,14 @@ __global__ void __launch_bounds__(ML_THREADS)
     const int woff = md.w_off(t, l);
     for (int idx = threadIdx.x; idx < in * out + out; idx += ML_THREADS) {
       T g = T(0);
+      // consecutive lanes hold consecutive j (stride TA words): start each lane at a different atom
+      const int rot = threadIdx.x & (TA - 1);
       if (idx < in * out) {
         const int q = idx / out, j = idx - q * out;
         const T* hp = hin + q * TA;
         const T* hdp = hdi + q * TA;
         const T* qp = dql + j * TA;
         const T* pp = dpl + j * TA;
-        // consecutive lanes hold consecutive j (stride TA words): start each lane at a different atom
-        const int rot = threadIdx.x & (TA - 1);
 #pragma unroll 8
         for (int a0 = 0; a0 < TA; a0++) {
           const int a = (a0 + rot) & (TA - 1);
@@ -871,31 +908,45 @@ __global__ void __launch_bounds__(ML_THREADS)
         }
       } else {
         const T* qp = dql + (idx - in * out) * TA;
-        const int rot = threadIdx.x & (TA - 1);
 #pragma unroll 8
         for (int a0 = 0; a0 < TA; a0++) g += qp[(a0 + rot) & (TA - 1)];
       }
       atomicAdd(gw + woff + idx, g);
     }
     // cotangents on the layer input
-    dense_bwd<T, APT>(in, out, Wl, dql, CQ, dpl, CP, wt);
+    dense_bwd<T, APT>(in, out, lv, dql, CQ, dpl, CP);
   }
-  // CQ = dS/dx, CP = dS/dv
+  // CQ = dS/dx, CP = dS/dv  ->  dL/dAF, kept in V for the contraction below
   for (int idx = threadIdx.x; idx < Fm * TA; idx += ML_THREADS) {
     const int a = idx % TA, i = idx / TA;
     const long long gi = gidx(a);
-    if (gi < 0) continue;
     T g = T(0);
-    if (i < F) {
+    if (gi >= 0 && i < F) {
       const T den = af[gi * Fm + i] + T(1e-3);
       g = CQ[idx] / den + CP[idx] * (-u[gi * Fm + i] / (den * den));
     }
-    gaf[gi * Fm + i] = g;
+    if (gi >= 0) gaf[gi * Fm + i] = g;
+    if (i < F) V[idx] = g;
   }
   for (int i = threadIdx.x; i < F; i += ML_THREADS) {
     T g = T(0);
     for (int a = 0; a < TA; a++) g -= CQ[i * TA + a];
     atomicAdd(grad + md.off_mu[t] + i, g);
+  }
+  if (vrow) {
+    __syncthreads();
+    // dL/dalpha (fingerprint part) = sum_atoms dL/dAF[c(q)] * dAF[c(q)]/dalpha[q]; alpha2b and alpha3b
+    // are contiguous in theta, q runs over both
+    const int Fr = md.Fr[t], Fa = md.Fa[t], n2 = md.nt * Fr, nq = n2 + md.C * 3 * Fa;
+    for (int q = threadIdx.x; q < nq; q += ML_THREADS) {
+      const int ch = q < n2 ? (q % Fr) : Fr + ((q - n2) / 3) % Fa;
+      T g = T(0);
+      for (int a = 0; a < TA; a++) {
+        const long long gi = gidx(a);
+        if (gi >= 0) g += V[ch * TA + a] * vrow[gi * nv + q];
+      }
+      if (g != T(0)) atomicAdd(grad + md.off_a2[t] + q, g);
+    }
   }
 }
 
@@ -1031,9 +1082,11 @@ struct stafb_model {
   int blk_size[STAFB_MAX_TYPES];
   size_t es;
   int apt;  // atoms per thread group of the MLP kernels (TA = 8*apt atoms per block)
+  int stage;  // 1: the MLP kernels stage each Dense layer in shared memory
   size_t mlp_fwd_smem, mlp_bwd_smem;
   // scratch for max_batch frames
-  void *rad, *d3s, *af, *nd, *acts, *e_atom, *force, *fbar, *ebar, *gradnet, *gaf, *energy;
+  void *rad, *d3s, *af, *nd, *acts, *e_atom, *force, *fbar, *ebar, *gradnet, *gaf, *energy, *vrow;
+  int nv;  // row length of vrow: nt*Frmax + C*3*Famax
   int *im2, *ntr;
   double* losses_d;  // 5 doubles: the four losses + the done-counter of k_loss
   // staging for the *_host entry points
@@ -1043,11 +1096,12 @@ struct stafb_model {
   size_t smem_limit;
 };
 
-static size_t mlp_smem_fwd(const ModelDev& d, size_t es, int apt) {
-  return es * ((size_t)(d.Fmax + d.Hsum + 2 * d.maxw) * 8 * apt + (size_t)d.maxw * 33);
+static size_t mlp_smem_fwd(const ModelDev& d, size_t es, int apt, bool stage) {
+  return es * ((size_t)(d.Fmax + d.Hsum + 2 * d.maxw) * 8 * apt + (stage ? (size_t)(d.maxw + 1) * (d.maxw + 1) : 0));
 }
-static size_t mlp_smem_bwd(const ModelDev& d, size_t es, int apt) {
-  return es * ((size_t)(2 * d.Fmax + 5 * d.Hsum + 2 * d.maxw) * 8 * apt + (size_t)d.maxw * 33);
+static size_t mlp_smem_bwd(const ModelDev& d, size_t es, int apt, bool stage) {
+  return es * ((size_t)(2 * d.Fmax + 5 * d.Hsum + 2 * d.maxw) * 8 * apt +
+               (stage ? (size_t)(d.maxw + 1) * (d.maxw + 1) : 0));
 }
 
 extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out) {
@@ -1103,16 +1157,17 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   m->apt = 0;
   int nsm = 148;
   cudaDeviceGetAttribute(&nsm, cudaDevAttrMultiProcessorCount, dev);
+  m->stage = 1;  // keep one Dense layer in shared memory if it fits next to the activations
+  if (mlp_smem_bwd(d, m->es, 1, true) > m->smem_limit) m->stage = 0;
   for (int apt = 4; apt >= 1; apt >>= 1) {
-    if (mlp_smem_bwd(d, m->es, apt) > m->smem_limit) continue;
-    if (!m->apt) m->apt = apt;  // largest tile that fits
-    m->apt = apt;               // keep shrinking until the grid gives every SM at least two blocks
+    if (mlp_smem_bwd(d, m->es, apt, m->stage != 0) > m->smem_limit) continue;
+    m->apt = apt;  // keep shrinking until the grid gives every SM at least two blocks
     if (species_blocks(d, c->max_batch, 8 * apt) >= 2 * nsm) break;
   }
   if (getenv("STAFB_MLP_APT")) m->apt = atoi(getenv("STAFB_MLP_APT"));
   if (!m->apt) { free(m); return STAFB_ERR_CAPACITY; }
-  m->mlp_fwd_smem = mlp_smem_fwd(d, m->es, m->apt);
-  m->mlp_bwd_smem = mlp_smem_bwd(d, m->es, m->apt);
+  m->mlp_fwd_smem = mlp_smem_fwd(d, m->es, m->apt, m->stage != 0);
+  m->mlp_bwd_smem = mlp_smem_bwd(d, m->es, m->apt, m->stage != 0);
   const size_t es = m->es, A = (size_t)c->max_batch * d.N, nr = c->nr;
   const size_t mlp_blocks = (size_t)species_blocks(d, c->max_batch, 8 * m->apt);
   STAFB_CUDA_OK(cudaMalloc(&m->rad, es * A * nr));
@@ -1123,6 +1178,8 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   STAFB_CUDA_OK(cudaMalloc(&m->nd, es * A * d.Fmax));
   STAFB_CUDA_OK(cudaMalloc(&m->gradnet, es * A * d.Fmax));
   STAFB_CUDA_OK(cudaMalloc(&m->gaf, es * A * d.Fmax));
+  m->nv = d.nt * d.Frmax + d.C * 3 * d.Famax;
+  STAFB_CUDA_OK(cudaMalloc(&m->vrow, es * A * (m->nv > 0 ? m->nv : 1)));
   STAFB_CUDA_OK(cudaMalloc(&m->acts, es * mlp_blocks * 8 * m->apt * d.Hsum));
   STAFB_CUDA_OK(cudaMalloc(&m->e_atom, es * A));
   STAFB_CUDA_OK(cudaMalloc(&m->force, es * A * 3));
@@ -1143,7 +1200,7 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
 extern "C" void stafb_model_destroy(stafb_model* m) {
   if (!m) return;
   void* ptrs[] = {m->rad, m->d3s, m->im2, m->ntr, m->af, m->nd, m->gradnet, m->gaf, m->acts, m->e_atom, m->force,
-                  m->fbar, m->ebar, m->energy, m->losses_d, m->pos_d, m->box_d, m->el_d, m->fl_d};
+                  m->fbar, m->ebar, m->energy, m->losses_d, m->pos_d, m->box_d, m->el_d, m->fl_d, m->vrow};
   for (void* p : ptrs) cudaFree(p);
   cudaFreeHost(m->pin);
   cudaFreeHost(m->losses_h);
@@ -1159,7 +1216,7 @@ extern "C" void stafb_model_offsets(const stafb_model* m, int t, int out6[6]) {
 
 template <class T, int MODE>
 static int launch_sweep(stafb_model* m, cudaStream_t s, int nf, const SweepIn<T>& in, const T* theta, const T* emb,
-                        const T* chan_in, const T* fbar, T* out, T* grad) {
+                        const T* chan_in, const T* fbar, T* out, T* grad, T* vout = nullptr, int nv = 0) {
   const ModelDev& d = m->md;
   const int xt = MODE == MODE_FORCE ? 3 : (MODE == MODE_FGRAD ? 4 : 0);
   const int nacc = d.Famax + d.nt * d.Frmax + d.C * 3 * d.Famax;
@@ -1167,7 +1224,7 @@ static int launch_sweep(stafb_model* m, cudaStream_t s, int nf, const SweepIn<T>
   SweepLayout L = sweep_layout<T>(in.nr, d.nt, xt, nacc, d.Famax > 0 ? d.Famax : 1, SW_WPA);
   const size_t sm = (size_t)L.total;
   if (sm > m->smem_limit) return STAFB_ERR_CAPACITY;
-  static bool attr[2][4] = {{false}};
+  static bool attr[2][5] = {{false}};
   if (sm > 48 * 1024 && !attr[sizeof(T) == 8][MODE]) {
     STAFB_CUDA_OK(cudaFuncSetAttribute(k_sweep<T, MODE, SW_WPA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)m->smem_limit));
@@ -1175,7 +1232,7 @@ static int launch_sweep(stafb_model* m, cudaStream_t s, int nf, const SweepIn<T>
   }
   const int blocks = nf * d.N;
   static const bool noatom = getenv("STAFB_EXP_NOATOM") != nullptr;
-  k_sweep<T, MODE, SW_WPA><<<blocks, SW_WPA * 32, sm, s>>>(d, in, L, theta, emb, chan_in, fbar, out, noatom ? nullptr : grad);
+  k_sweep<T, MODE, SW_WPA><<<blocks, SW_WPA * 32, sm, s>>>(d, in, L, theta, emb, chan_in, fbar, out, noatom ? nullptr : grad, vout, nv);
   m->ctx->launches++;
   return STAFB_OK;
 }
@@ -1190,7 +1247,7 @@ static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta
     attr = true;
   }
   k_mlp_fwd<T, APT><<<species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_fwd_smem, s>>>(m->md, nf, theta, af, acts,
-                                                                                           e_atom, nd);
+                                                                                           e_atom, nd, m->stage);
   m->ctx->launches++;
   return STAFB_OK;
 }
@@ -1199,13 +1256,14 @@ template <class T, int APT>
 static int launch_mlp_bwd(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, const T* acts,
                           const T* ebar, const T* u, T* gaf, T* grad) {
   static bool attr = false;
+  const T* vrow = (const T*)m->vrow;
   if (m->mlp_bwd_smem > 48 * 1024 && !attr) {
     STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_bwd<T, APT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)m->smem_limit));
     attr = true;
   }
   k_mlp_bwd<T, APT><<<species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_bwd_smem, s>>>(m->md, nf, theta, af, acts,
-                                                                                           ebar, u, gaf, grad);
+                                                                                           ebar, u, vrow, m->nv, gaf, grad, m->stage);
   m->ctx->launches++;
   return STAFB_OK;
 }
@@ -1240,7 +1298,8 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
   SweepIn<T> in;
   in.geom = (const T*)c->geom; in.gsc = (const T*)c->gsc; in.rad = rad; in.d3s = d3s; in.im2 = m->im2; in.ntr = m->ntr;
   in.nf = nf; in.nr = c->nr;
-  rc = launch_sweep<T, MODE_AF>(m, s, nf, in, theta, emb, nullptr, nullptr, af, nullptr);
+  rc = train ? launch_sweep<T, MODE_AFV>(m, s, nf, in, theta, emb, nullptr, nullptr, af, nullptr, (T*)m->vrow, m->nv)
+             : launch_sweep<T, MODE_AF>(m, s, nf, in, theta, emb, nullptr, nullptr, af, nullptr);
   if (rc != STAFB_OK) return rc;
   mark();  // af_fwd
   rc = m->apt == 4 ? launch_mlp_fwd<T, 4>(m, s, nf, theta, af, acts, e_atom, nd)
@@ -1275,11 +1334,8 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
                        : launch_mlp_bwd<T, 1>(m, s, nf, theta, af, acts, (const T*)m->ebar, gradnet, gaf, grad);
     if (rc != STAFB_OK) return rc;
     mark();  // mlp_bwd
-    rc = launch_sweep<T, MODE_AFGRAD>(m, s, nf, in, theta, emb, gaf, nullptr, nullptr, grad);
-    if (rc != STAFB_OK) return rc;
     if (losses_out != m->losses_d)
       STAFB_CUDA_OK(cudaMemcpyAsync(losses_out, m->losses_d, sizeof(double) * 4, cudaMemcpyDeviceToDevice, s));
-    mark();  // af_grad
   }
   STAFB_CUDA_OK(cudaGetLastError());
   return STAFB_OK;
