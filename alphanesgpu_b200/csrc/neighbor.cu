@@ -16,12 +16,7 @@
 namespace stafb {
 
 template <class T>
-__global__ void k_frame_setup(const T* __restrict__ box, int nf, int N, T cutoff, int cell_cap,
-                              FrameGeom<T>* __restrict__ fg, int* __restrict__ status) {
-  int b = blockIdx.x * blockDim.x + threadIdx.x;
-  if (b >= nf) return;
-  FrameGeom<T> g;
-  const T* B = box + 6 * b;
+__device__ void frame_geometry(const T* __restrict__ B, int N, T cutoff, int cell_cap, FrameGeom<T>& g, int* status) {
   for (int q = 0; q < 6; q++) g.box[q] = B[q];
   if (!(B[0] != T(0) && B[3] != T(0) && B[5] != T(0))) {
     set_status(status, STAFB_ERR_BAD_BOX);
@@ -29,7 +24,6 @@ __global__ void k_frame_setup(const T* __restrict__ box, int nf, int N, T cutoff
     g.nx = g.ny = g.nz = 3;
     g.ncell = 27;
     g.sx = g.sy = g.sz = T(1) / T(3);
-    fg[b] = g;
     return;
   }
   // inverse of the upper-triangular box: descriptor_builder/reforce.cc:283-299
@@ -65,24 +59,33 @@ __global__ void k_frame_setup(const T* __restrict__ box, int nf, int N, T cutoff
   g.sx = T(1.) / (T)cx;
   g.sy = T(1.) / (T)cy;
   g.sz = T(1.) / (T)cz;
-  fg[b] = g;
 }
 
-// Fractional coordinates (celle_gpu.cu.cc:11-28) and cell of every atom (celle_gpu.cu.cc:176-201).
+// Frame geometry, fractional coordinates (celle_gpu.cu.cc:11-28) and the cell of every atom
+// (celle_gpu.cu.cc:176-201) in one launch: grid (blocks over atoms, frames); every block derives its
+// frame's geometry again (a few dozen flops) instead of waiting for a separate set-up launch.
 template <class T>
-__global__ void k_bin(const T* __restrict__ pos, int nf, int N, const FrameGeom<T>* __restrict__ fg,
-                      T* __restrict__ frac, int* __restrict__ cell_of, int* __restrict__ cell_count, int cell_cap) {
-  int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= nf * N) return;
-  int b = t / N;
-  const FrameGeom<T>& g = fg[b];
-  T px = pos[(size_t)t * 3 + 0], py = pos[(size_t)t * 3 + 1], pz = pos[(size_t)t * 3 + 2];
+__global__ void k_cells(const T* __restrict__ pos, const T* __restrict__ box, int nf, int N, T cutoff, int cell_cap,
+                        FrameGeom<T>* __restrict__ fg, T* __restrict__ frac, int* __restrict__ cell_of,
+                        int* __restrict__ cell_count, int* __restrict__ status) {
+  __shared__ FrameGeom<T> gs;
+  const int b = blockIdx.y;
+  if (threadIdx.x == 0) {
+    frame_geometry<T>(box + 6 * b, N, cutoff, cell_cap, gs, status);
+    if (blockIdx.x == 0) fg[b] = gs;
+  }
+  __syncthreads();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= N) return;
+  const FrameGeom<T>& g = gs;
+  const size_t t = (size_t)b * N + i;
+  T px = pos[t * 3 + 0], py = pos[t * 3 + 1], pz = pos[t * 3 + 2];
   T fx = (g.inv[0] * px + g.inv[1] * py + g.inv[2] * pz);
   T fy = (g.inv[3] * py + g.inv[4] * pz);
   T fz = (g.inv[5] * pz);
-  frac[(size_t)t * 3 + 0] = fx;
-  frac[(size_t)t * 3 + 1] = fy;
-  frac[(size_t)t * 3 + 2] = fz;
+  frac[t * 3 + 0] = fx;
+  frac[t * 3 + 1] = fy;
+  frac[t * 3 + 2] = fz;
   int cx = (int)r_floor(fx / g.sx);
   cx = cx % g.nx;
   if (cx < 0) cx += g.nx;
@@ -95,6 +98,27 @@ __global__ void k_bin(const T* __restrict__ pos, int nf, int N, const FrameGeom<
   int c = cx + cy * g.nx + cz * (g.nx * g.ny);
   cell_of[t] = c;
   atomicAdd(cell_count + (size_t)b * cell_cap + c, 1);
+}
+
+// Members of every cell in ascending atom index, gathered directly by one warp per cell that walks
+// the frame's atoms 32 at a time (used for small systems; replaces the fill + sort pair).
+template <class T>
+__global__ void k_gather_cells(const FrameGeom<T>* __restrict__ fg, int nf, int N, const int* __restrict__ cell_of,
+                               const int* __restrict__ cell_start, int* __restrict__ cells_sorted, int cell_cap) {
+  int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  int b = gw / cell_cap, c = gw - b * cell_cap;
+  if (b >= nf || c >= fg[b].ncell) return;
+  const int* co = cell_of + (size_t)b * N;
+  int* dst = cells_sorted + (size_t)b * N + cell_start[(size_t)b * (cell_cap + 1) + c];
+  const unsigned lt = (1u << lane) - 1u;
+  int cnt = 0;
+  for (int j0 = 0; j0 < N; j0 += 32) {
+    const int j = j0 + lane;
+    const bool p = (j < N) && (co[j] == c);
+    const unsigned bal = __ballot_sync(0xffffffffu, p);
+    if (p) dst[cnt + __popc(bal & lt)] = j;
+    cnt += __popc(bal);
+  }
 }
 
 // Exclusive scan of the per-cell counts of one frame (one block per frame).
@@ -214,40 +238,59 @@ __global__ void __launch_bounds__(WARPS * 32)
   const int* cl = cells_sorted + (size_t)b * N;
   const T cut2 = cc.Rc * cc.Rc;
   const unsigned lt = (1u << lane) - 1u;
-  int count = 0;
-  for (int di = -1; di < 2; di++) {
-    int bi = cx + di;
-    if (bi < 0) bi = g.nx - 1; else if (bi == g.nx) bi = 0;
-    for (int dj = -1; dj < 2; dj++) {
-      int bj = cy + dj;
+  // The 27 neighbour cells in the reference's visiting order, flattened into one candidate list so
+  // that all 32 lanes work on every pass: lane q < 27 owns cell q, an inclusive scan gives each cell's
+  // offset in the list, and a candidate finds its cell by bisection.
+  int* cbeg = reinterpret_cast<int*>(reinterpret_cast<int*>(reinterpret_cast<T*>(smem_raw) + (size_t)WARPS * 2 * nr) +
+                                     (size_t)WARPS * 2 * nr) + warp * 64;  // [32] cell starts, [32] list offsets
+  int* coff = cbeg + 32;
+  {
+    int s0 = 0, cn = 0;
+    if (lane < 27) {
+      const int di = lane / 9 - 1, dj = (lane / 3) % 3 - 1, dk = lane % 3 - 1;
+      int bi = cx + di, bj = cy + dj, bk = cz + dk;
+      if (bi < 0) bi = g.nx - 1; else if (bi == g.nx) bi = 0;
       if (bj < 0) bj = g.ny - 1; else if (bj == g.ny) bj = 0;
-      for (int dk = -1; dk < 2; dk++) {
-        int bk = cz + dk;
-        if (bk < 0) bk = g.nz - 1; else if (bk == g.nz) bk = 0;
-        const int c = bi + bj * g.nx + bk * g.nx * g.ny;
-        const int s0 = cst[c], s1 = cst[c + 1];
-        for (int e0 = s0; e0 < s1; e0 += 32) {
-          const int e = e0 + lane;
-          bool pred = false;
-          int j = -1;
-          T dist2 = T(0);
-          if (e < s1) {
-            j = cl[e];
-            T dx, dy, dz;
-            mic_vec(g, fr[3 * j], fr[3 * j + 1], fr[3 * j + 2], pix, piy, piz, dx, dy, dz);
-            dist2 = dx * dx + dy * dy + dz * dz;
-            pred = (dist2 < cut2) && (j != i);
-          }
-          const unsigned bal = __ballot_sync(0xffffffffu, pred);
-          const int slot = count + __popc(bal & lt);
-          if (pred && slot < nr) {
-            d2a[slot] = dist2;
-            ja[slot] = j;
-          }
-          count += __popc(bal);
-        }
-      }
+      if (bk < 0) bk = g.nz - 1; else if (bk == g.nz) bk = 0;
+      const int c = bi + bj * g.nx + bk * g.nx * g.ny;
+      s0 = cst[c];
+      cn = cst[c + 1] - s0;
     }
+    int x = cn;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    cbeg[lane] = s0;
+    coff[lane] = x - cn;  // exclusive offset; lanes >= 27 hold the total
+  }
+  __syncwarp();
+  const int M = coff[27];
+  int count = 0;
+  for (int e0 = 0; e0 < M; e0 += 32) {
+    const int e = e0 + lane;
+    bool pred = false;
+    int j = -1;
+    T dist2 = T(0);
+    if (e < M) {
+      int q = 0;
+#pragma unroll
+      for (int st = 16; st > 0; st >>= 1)
+        if (q + st < 27 && coff[q + st] <= e) q += st;
+      j = cl[cbeg[q] + (e - coff[q])];
+      T dx, dy, dz;
+      mic_vec(g, fr[3 * j], fr[3 * j + 1], fr[3 * j + 2], pix, piy, piz, dx, dy, dz);
+      dist2 = dx * dx + dy * dy + dz * dz;
+      pred = (dist2 < cut2) && (j != i);
+    }
+    const unsigned bal = __ballot_sync(0xffffffffu, pred);
+    const int slot = count + __popc(bal & lt);
+    if (pred && slot < nr) {
+      d2a[slot] = dist2;
+      ja[slot] = j;
+    }
+    count += __popc(bal);
   }
   if (count > nr && lane == 0) set_status(status, STAFB_ERR_RADIAL_OVERFLOW);
   const int n = count < nr ? count : nr;
@@ -422,24 +465,29 @@ int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box,
   cc.Rc = (T)c->Rc; cc.Rs = (T)c->Rs; cc.Ra = (T)c->Ra;
   cc.A = (T)c->coef[0]; cc.B = (T)c->coef[1]; cc.C = (T)c->coef[2]; cc.pa = (T)c->coef[3]; cc.pb = (T)c->coef[4];
   STAFB_CUDA_OK(cudaMemsetAsync(c->cell_count, 0, sizeof(int) * (size_t)nf * cap, s));
-  k_frame_setup<T><<<(nf + 31) / 32, 32, 0, s>>>(box, nf, N, cc.Rc, cap, fg, c->status_d);
   const int tot = nf * N;
-  k_bin<T><<<(tot + 255) / 256, 256, 0, s>>>(pos, nf, N, fg, frac, c->cell_of, c->cell_count, cap);
+  k_cells<T><<<dim3((N + 255) / 256, nf), 256, 0, s>>>(pos, box, nf, N, cc.Rc, cap, fg, frac, c->cell_of, c->cell_count,
+                                                       c->status_d);
   k_scan<T><<<nf, 256, 0, s>>>(fg, c->cell_count, c->cell_start, c->cell_cursor, cap, mpc, c->status_d);
-  k_fill<<<(tot + 255) / 256, 256, 0, s>>>(nf, N, c->cell_of, c->cell_start, c->cell_cursor, c->cells_raw, cap);
-  {
-    long long warps = (long long)nf * cap;
+  const long long warps = (long long)nf * cap;
+  if (N <= 4096) {
+    k_gather_cells<T><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(fg, nf, N, c->cell_of, c->cell_start,
+                                                                         c->cells_sorted, cap);
+    c->launches += 4;
+  } else {
+    k_fill<<<(tot + 255) / 256, 256, 0, s>>>(nf, N, c->cell_of, c->cell_start, c->cell_cursor, c->cells_raw, cap);
     k_sort_cells<T><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(fg, nf, N, c->cell_start, c->cells_raw,
                                                                        c->cells_sorted, cap);
+    c->launches += 5;
   }
   {
     constexpr int W = 4;
-    size_t sm = (size_t)W * 2 * nr * (sizeof(T) + sizeof(int));
+    size_t sm = (size_t)W * 2 * nr * (sizeof(T) + sizeof(int)) + (size_t)W * 64 * sizeof(int);
     k_nl_radial<T, W><<<(tot + W - 1) / W, W * 32, sm, s>>>(nf, N, nr, cc, fg, frac, c->cell_of, c->cell_start,
                                                           c->cells_sorted, cap, raddescr, des3bsupp, intmap2b, der2b,
                                                           der3bsupp, numtriplet, geom, gsc, na, c->status_d);
   }
-  c->launches += 6;
+  c->launches += 1;
   if (angdescr && intmap3b && der3b) {
     constexpr int TH = 128;
     size_t sm = (size_t)nr * (sizeof(typename Vec4<T>::type) + 2 * sizeof(T) + sizeof(int));
