@@ -136,5 +136,9 @@ namespace stafb {
 template <class T>
 int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box, int nf, int N, T* raddescr,
                        T* angdescr, T* des3bsupp, int* intmap2b, int* intmap3b, T* der2b, T* der3b, T* der3bsupp,
-                       int* numtriplet);
+                       int* numtriplet, int ncen = -1);
+// rows of the first ncen atoms from a caller-supplied, distance-sorted neighbour list over nall atoms
+template <class T>
+int launch_rows_from_list(stafb_ctx* c, cudaStream_t s, const T* pos, int ncen, int nall, const int* howmany,
+                          const int* with, T* raddescr, T* des3bsupp, int* intmap2b, int* numtriplet);
 }

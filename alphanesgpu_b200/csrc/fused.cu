@@ -75,6 +75,11 @@ struct SweepIn {
   const T* d3s;    // [nf,N,nr]
   const int* im2;  // [nf,N,nr+1]
   const int* ntr;  // [nf,N]
+  // Domain mode (one frame): the centres are the first N atoms (species-sorted) of nall >= N atoms; the
+  // species of the others comes from tmap[nall] and forces are written for all nall atoms.  tmap == null:
+  // every atom is a centre (nall == N) and the species follows from the species-sorted order.
+  const int* tmap;
+  int nall;
   int nf, nr;
 };
 
@@ -171,7 +176,8 @@ __global__ void __launch_bounds__(WPA * 32)
             const T* __restrict__ fbar,     // FGRAD: dL/dF[nf,3N]
             T* __restrict__ out,            // AF: af[nf,N,Fmax]; FORCE: force[nf,3N]; FGRAD: gradnet[nf,N,Fmax]
             T* __restrict__ grad,           // FGRAD/AFGRAD: flat parameter gradient (accumulated)
-            T* __restrict__ vout, int nv) { // AFV: d(AF)/d(alpha2b|alpha3b) rows [nf,N,nv]
+            T* __restrict__ vout, int nv,   // AFV: d(AF)/d(alpha2b|alpha3b) rows [nf,N,nv]
+            double* __restrict__ vir) {     // FORCE: virial accumulators [nf,9] or null
   extern __shared__ __align__(16) unsigned char smem_raw[];
   typedef typename Vec4<T>::type T4;
   typedef typename Vec2<T>::type T2;
@@ -226,7 +232,7 @@ __global__ void __launch_bounds__(WPA * 32)
     P1[k] = q1;
     const int id = in.im2[gi * (nr + 1) + 1 + k];
     ids[k] = id;
-    tj[k] = (unsigned char)md.type_of(id);
+    tj[k] = (unsigned char)(in.tmap ? in.tmap[id] : md.type_of(id));
   }
   if (MODE != MODE_FORCE)
     for (int q = tid; q < NACC; q += NT) acc[q] = T(0);
@@ -254,7 +260,7 @@ __global__ void __launch_bounds__(WPA * 32)
   T fix = T(0), fiy = T(0), fiz = T(0);  // FORCE: force on the central atom
   if (MODE == MODE_FGRAD) {
     // dF_k = Fbar_k - Fbar_i and its projection on the unit vector
-    const T* fb = fbar + (size_t)b * N * 3;
+    const T* fb = fbar + (size_t)b * in.nall * 3;
     const T fx = fb[i * 3], fy = fb[i * 3 + 1], fz = fb[i * 3 + 2];
     for (int k = tid; k < n; k += NT) {
       const int id = ids[k];
@@ -595,13 +601,34 @@ __global__ void __launch_bounds__(WPA * 32)
       }
     }
   } else if (MODE == MODE_FORCE) {
-    T* fb = out + (size_t)b * N * 3;
+    T* fb = out + (size_t)b * in.nall * 3;
     for (int q = tid; q < 3 * n; q += NT) atomicAdd(fb + (size_t)ids[q / 3] * 3 + (q % 3), xtra[q]);
     fix = warp_sum(fix); fiy = warp_sum(fiy); fiz = warp_sum(fiz);
     if (lane == 0) {
       atomicAdd(fb + (size_t)i * 3 + 0, fix);
       atomicAdd(fb + (size_t)i * 3 + 1, fiy);
       atomicAdd(fb + (size_t)i * 3 + 2, fiz);
+    }
+    if (vir) {
+      // W_ab -= g_a * r_b with g the force this centre puts on neighbour k and r = r_i - r_k
+      // (force/rad/reforce.cu.cc:174-287, force/ang/reforce.cu.cc:269-457 of the reference)
+      T w[9];
+#pragma unroll
+      for (int c = 0; c < 9; c++) w[c] = T(0);
+      for (int k = tid; k < n; k += NT) {
+        const T4 u = P0[k];
+        const T r = T(1) / P1[k].x;
+        const T rv[3] = {u.x * r, u.y * r, u.z * r};
+#pragma unroll
+        for (int a = 0; a < 3; a++)
+#pragma unroll
+          for (int c = 0; c < 3; c++) w[a * 3 + c] -= xtra[k * 3 + a] * rv[c];
+      }
+#pragma unroll
+      for (int c = 0; c < 9; c++) {
+        const T v = warp_sum(w[c]);
+        if (lane == 0 && v != T(0)) atomicAdd(vir + (size_t)b * 9 + c, (double)v);
+      }
     }
   } else {
     if (MODE == MODE_FGRAD) {
@@ -975,11 +1002,13 @@ __global__ void __launch_bounds__(256)
     k_loss(ModelDev md, int nf, int fb, int per_atom, int train, const T* __restrict__ e_atom, T* __restrict__ energy,
            const T* __restrict__ e_label, const T* __restrict__ force, const T* __restrict__ f_label,
            const T* __restrict__ theta, T pe, T pf, T pb, T bound, int loss_kind, T* __restrict__ ebar,
-           T* __restrict__ fbar, T* __restrict__ grad, double* __restrict__ losses, int* __restrict__ status) {
+           T* __restrict__ fbar, T* __restrict__ grad, double* __restrict__ losses, int* __restrict__ status,
+           const double* __restrict__ vacc, T* __restrict__ virial_out) {
   __shared__ double red[9];
   const int N = md.N;
   const int blk = blockIdx.x;
   if (blk < nf) {
+    if (virial_out && threadIdx.x < 9) virial_out[blk * 9 + threadIdx.x] = (T)vacc[blk * 9 + threadIdx.x];
     double s = 0.0;
     for (int q = threadIdx.x; q < N; q += blockDim.x) s += (double)e_atom[(size_t)blk * N + q];
     s = block_sum<double, 8>(s, red);
@@ -1081,6 +1110,7 @@ struct stafb_model {
   int n_params, n_emb;
   int blk_size[STAFB_MAX_TYPES];
   size_t es;
+  int cap_atoms;  // atoms per frame the scratch was sized for
   int apt;  // atoms per thread group of the MLP kernels (TA = 8*apt atoms per block)
   int stage;  // 1: the MLP kernels stage each Dense layer in shared memory
   size_t mlp_fwd_smem, mlp_bwd_smem;
@@ -1088,7 +1118,7 @@ struct stafb_model {
   void *rad, *d3s, *af, *nd, *acts, *e_atom, *force, *fbar, *ebar, *gradnet, *gaf, *energy, *vrow;
   int nv;  // row length of vrow: nt*Frmax + C*3*Famax
   int *im2, *ntr;
-  double* losses_d;  // 5 doubles: the four losses + the done-counter of k_loss
+  double* losses_d;  // [0..4] the four losses + the done-counter of k_loss; [8 + 9*b + c] virial accumulators
   // staging for the *_host entry points
   void *pos_d, *box_d, *el_d, *fl_d;
   void* pin;  // pinned staging: pos | f_label | box | e_label
@@ -1168,8 +1198,11 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   if (!m->apt) { free(m); return STAFB_ERR_CAPACITY; }
   m->mlp_fwd_smem = mlp_smem_fwd(d, m->es, m->apt, m->stage != 0);
   m->mlp_bwd_smem = mlp_smem_bwd(d, m->es, m->apt, m->stage != 0);
-  const size_t es = m->es, A = (size_t)c->max_batch * d.N, nr = c->nr;
-  const size_t mlp_blocks = (size_t)species_blocks(d, c->max_batch, 8 * m->apt);
+  // scratch is sized for the context's atom capacity, so that stafb_model_set_counts can move atoms between
+  // species (or change their number) without reallocating
+  const size_t es = m->es, A = (size_t)c->max_batch * c->n_max, nr = c->nr;
+  m->cap_atoms = c->n_max;
+  const size_t mlp_blocks = A / (8 * m->apt) + d.nt + 1;
   STAFB_CUDA_OK(cudaMalloc(&m->rad, es * A * nr));
   STAFB_CUDA_OK(cudaMalloc(&m->d3s, es * A * nr));
   STAFB_CUDA_OK(cudaMalloc((void**)&m->im2, sizeof(int) * A * (nr + 1)));
@@ -1186,7 +1219,7 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   STAFB_CUDA_OK(cudaMalloc(&m->fbar, es * A * 3));
   STAFB_CUDA_OK(cudaMalloc(&m->ebar, es * c->max_batch));
   STAFB_CUDA_OK(cudaMalloc(&m->energy, es * c->max_batch));
-  STAFB_CUDA_OK(cudaMalloc((void**)&m->losses_d, sizeof(double) * 5));
+  STAFB_CUDA_OK(cudaMalloc((void**)&m->losses_d, sizeof(double) * (8 + 9 * (size_t)c->max_batch)));
   STAFB_CUDA_OK(cudaMalloc(&m->pos_d, es * A * 3));
   STAFB_CUDA_OK(cudaMalloc(&m->box_d, es * c->max_batch * 6));
   STAFB_CUDA_OK(cudaMalloc(&m->el_d, es * c->max_batch));
@@ -1207,6 +1240,25 @@ extern "C" void stafb_model_destroy(stafb_model* m) {
   free(m);
 }
 
+extern "C" int stafb_model_set_counts(stafb_model* m, const int* tipos) {
+  if (!m || !tipos) return STAFB_ERR_INVALID;
+  ModelDev& d = m->md;
+  int n = 0;
+  for (int t = 0; t < d.nt; t++) {
+    if (tipos[t] < 0) return STAFB_ERR_INVALID;
+    n += tipos[t];
+  }
+  if (n <= 0) return STAFB_ERR_INVALID;
+  if (n > m->cap_atoms) return STAFB_ERR_CAPACITY;
+  d.shift[0] = 0;
+  for (int t = 0; t < d.nt; t++) {
+    d.tipos[t] = tipos[t];
+    d.shift[t + 1] = d.shift[t] + tipos[t];
+  }
+  d.N = n;
+  return STAFB_OK;
+}
+
 extern "C" int stafb_model_n_params(const stafb_model* m) { return m ? m->n_params : -1; }
 extern "C" int stafb_model_n_emb(const stafb_model* m) { return m ? m->n_emb : -1; }
 extern "C" void stafb_model_offsets(const stafb_model* m, int t, int out6[6]) {
@@ -1216,7 +1268,8 @@ extern "C" void stafb_model_offsets(const stafb_model* m, int t, int out6[6]) {
 
 template <class T, int MODE>
 static int launch_sweep(stafb_model* m, cudaStream_t s, int nf, const SweepIn<T>& in, const T* theta, const T* emb,
-                        const T* chan_in, const T* fbar, T* out, T* grad, T* vout = nullptr, int nv = 0) {
+                        const T* chan_in, const T* fbar, T* out, T* grad, T* vout = nullptr, int nv = 0,
+                        double* vir = nullptr) {
   const ModelDev& d = m->md;
   const int xt = MODE == MODE_FORCE ? 3 : (MODE == MODE_FGRAD ? 4 : 0);
   const int nacc = d.Famax + d.nt * d.Frmax + d.C * 3 * d.Famax;
@@ -1232,7 +1285,7 @@ static int launch_sweep(stafb_model* m, cudaStream_t s, int nf, const SweepIn<T>
   }
   const int blocks = nf * d.N;
   static const bool noatom = getenv("STAFB_EXP_NOATOM") != nullptr;
-  k_sweep<T, MODE, SW_WPA><<<blocks, SW_WPA * 32, sm, s>>>(d, in, L, theta, emb, chan_in, fbar, out, noatom ? nullptr : grad, vout, nv);
+  k_sweep<T, MODE, SW_WPA><<<blocks, SW_WPA * 32, sm, s>>>(d, in, L, theta, emb, chan_in, fbar, out, noatom ? nullptr : grad, vout, nv, vir);
   m->ctx->launches++;
   return STAFB_OK;
 }
@@ -1268,16 +1321,28 @@ static int launch_mlp_bwd(stafb_model* m, cudaStream_t s, int nf, const T* theta
   return STAFB_OK;
 }
 
+// Domain mode of the fused path: one frame of nall atoms whose first N (the model's species-sorted
+// atoms) are the centres; the rest are ghosts that only act as neighbours and receive forces.
+struct DomainArgs {
+  int nall;
+  const int* tmap;     // device, [nall] species of every atom
+  const int* howmany;  // device, [N] or null: caller-supplied neighbour list (no search, no minimum image)
+  const int* with;     // device, [N, nr]
+};
+
 template <class T>
 static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos, const T* box, int nf,
                      const T* theta, const T* emb, int per_atom, bool train, const T* e_label, const T* f_label,
                      double pe, double pf, double pb, double bound, int loss_kind, double* losses_out, T* grad,
-                     T* energy_out, T* force_out) {
-  if (!c || !m || !pos || !box || !theta || !emb || nf <= 0) return STAFB_ERR_INVALID;
+                     T* energy_out, T* force_out, const DomainArgs* dom = nullptr, T* virial_out = nullptr) {
+  if (!c || !m || !pos || !theta || !emb || nf <= 0) return STAFB_ERR_INVALID;
+  if (!box && !(dom && dom->howmany)) return STAFB_ERR_INVALID;
   if (nf > c->max_batch) return STAFB_ERR_CAPACITY;
   if (train && (!e_label || !f_label || !grad || !losses_out)) return STAFB_ERR_INVALID;
   const ModelDev& d = m->md;
   const int N = d.N;
+  if (dom && (nf != 1 || train || !dom->tmap || dom->nall < N || !force_out)) return STAFB_ERR_INVALID;
+  const int nall = dom ? dom->nall : N;
   c->launches = 0;
   c->n_phase = 0;
   auto mark = [&]() {
@@ -1285,19 +1350,26 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
   };
   mark();
   T* rad = (T*)m->rad; T* d3s = (T*)m->d3s;
-  int rc = launch_descriptors<T>(c, s, pos, box, nf, N, rad, nullptr, d3s, m->im2, nullptr, nullptr, nullptr,
-                                 nullptr, m->ntr);
+  int rc;
+  if (dom && dom->howmany)
+    rc = launch_rows_from_list<T>(c, s, pos, N, nall, dom->howmany, dom->with, rad, d3s, m->im2, m->ntr);
+  else
+    rc = launch_descriptors<T>(c, s, pos, box, nf, nall, rad, nullptr, d3s, m->im2, nullptr, nullptr, nullptr,
+                               nullptr, m->ntr, N);
   if (rc != STAFB_OK) return rc;
   T* af = (T*)m->af; T* nd = (T*)m->nd; T* acts = (T*)m->acts; T* e_atom = (T*)m->e_atom;
   T* force = force_out ? force_out : (T*)m->force;
   T* energy = energy_out ? energy_out : (T*)m->energy;
-  k_zero3<<<64, 256, 0, s>>>(force, sizeof(T) * (size_t)nf * 3 * N, train ? (void*)grad : nullptr,
-                             train ? sizeof(T) * (size_t)m->n_params : 0, m->losses_d, sizeof(double) * 5);
+  k_zero3<<<64, 256, 0, s>>>(force, sizeof(T) * (size_t)nf * 3 * nall, train ? (void*)grad : nullptr,
+                             train ? sizeof(T) * (size_t)m->n_params : 0, m->losses_d,
+                             sizeof(double) * (virial_out ? 8 + 9 * (size_t)nf : 5));
   c->launches++;
   mark();  // descriptors
   SweepIn<T> in;
   in.geom = (const T*)c->geom; in.gsc = (const T*)c->gsc; in.rad = rad; in.d3s = d3s; in.im2 = m->im2; in.ntr = m->ntr;
   in.nf = nf; in.nr = c->nr;
+  in.tmap = dom ? dom->tmap : nullptr;
+  in.nall = nall;
   rc = train ? launch_sweep<T, MODE_AFV>(m, s, nf, in, theta, emb, nullptr, nullptr, af, nullptr, (T*)m->vrow, m->nv)
              : launch_sweep<T, MODE_AF>(m, s, nf, in, theta, emb, nullptr, nullptr, af, nullptr);
   if (rc != STAFB_OK) return rc;
@@ -1307,7 +1379,8 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
                      : launch_mlp_fwd<T, 1>(m, s, nf, theta, af, acts, e_atom, nd);
   if (rc != STAFB_OK) return rc;
   mark();  // mlp_fwd
-  rc = launch_sweep<T, MODE_FORCE>(m, s, nf, in, theta, emb, nd, nullptr, force, nullptr);
+  double* vacc = virial_out ? m->losses_d + 8 : nullptr;
+  rc = launch_sweep<T, MODE_FORCE>(m, s, nf, in, theta, emb, nd, nullptr, force, nullptr, nullptr, 0, vacc);
   if (rc != STAFB_OK) return rc;
   mark();  // force
   {
@@ -1319,7 +1392,7 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
     const int grid = nf + fb + (train ? 1 : 0);
     k_loss<T><<<grid, 256, 0, s>>>(d, nf, fb, per_atom, train ? 1 : 0, e_atom, energy, e_label, force, f_label, theta,
                                    (T)pe, (T)pf, (T)pb, (T)bound, loss_kind, (T*)m->ebar, (T*)m->fbar, grad,
-                                   m->losses_d, c->status_d);
+                                   m->losses_d, c->status_d, vacc, virial_out);
     c->launches++;
   }
   mark();  // loss
@@ -1353,6 +1426,38 @@ extern "C" int stafb_energy_force(stafb_ctx* c, stafb_model* m, void* stream, co
   return run_fused<double>(c, m, s, (const double*)pos, (const double*)box, nf, (const double*)theta,
                            (const double*)emb, per_atom, false, nullptr, nullptr, 0, 0, 0, 0, 0, nullptr, nullptr,
                            (double*)energy, (double*)force);
+}
+
+extern "C" int stafb_energy_force_domain(stafb_ctx* c, stafb_model* m, void* stream, const void* pos, const void* box,
+                                         int nall, const int* type_map, const int* howmany, const int* with,
+                                         const void* theta, const void* emb, void* energy, void* force,
+                                         void* virial) {
+  if (!c || !m || !type_map || (howmany && !with)) return STAFB_ERR_INVALID;
+  if (nall > c->n_max) return STAFB_ERR_CAPACITY;
+  cudaStream_t s = (cudaStream_t)stream;
+  DomainArgs dom;
+  dom.nall = nall; dom.tmap = type_map; dom.howmany = howmany; dom.with = with;
+  if (c->dtype == STAFB_F32)
+    return run_fused<float>(c, m, s, (const float*)pos, (const float*)box, 1, (const float*)theta, (const float*)emb,
+                            0, false, nullptr, nullptr, 0, 0, 0, 0, 0, nullptr, nullptr, (float*)energy,
+                            (float*)force, &dom, (float*)virial);
+  return run_fused<double>(c, m, s, (const double*)pos, (const double*)box, 1, (const double*)theta,
+                           (const double*)emb, 0, false, nullptr, nullptr, 0, 0, 0, 0, 0, nullptr, nullptr,
+                           (double*)energy, (double*)force, &dom, (double*)virial);
+}
+
+extern "C" int stafb_energy_force_virial(stafb_ctx* c, stafb_model* m, void* stream, const void* pos, const void* box,
+                                         int nf, const void* theta, const void* emb, int per_atom, void* energy,
+                                         void* force, void* virial) {
+  if (!c || !m) return STAFB_ERR_INVALID;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (c->dtype == STAFB_F32)
+    return run_fused<float>(c, m, s, (const float*)pos, (const float*)box, nf, (const float*)theta,
+                            (const float*)emb, per_atom, false, nullptr, nullptr, 0, 0, 0, 0, 0, nullptr, nullptr,
+                            (float*)energy, (float*)force, nullptr, (float*)virial);
+  return run_fused<double>(c, m, s, (const double*)pos, (const double*)box, nf, (const double*)theta,
+                           (const double*)emb, per_atom, false, nullptr, nullptr, 0, 0, 0, 0, 0, nullptr, nullptr,
+                           (double*)energy, (double*)force, nullptr, (double*)virial);
 }
 
 extern "C" int stafb_train_step(stafb_ctx* c, stafb_model* m, void* stream, const void* pos, const void* box, int nf,

@@ -14,9 +14,11 @@
 extern "C" {
 int stafb_model_create(stafb_ctx* ctx, const int* shape_desc, stafb_model** out);
 void stafb_model_destroy(stafb_model* m);
-int stafb_energy_force(stafb_ctx* ctx, stafb_model* m, void* stream, const void* positions_d, const void* boxer_d,
-                       int nf, const void* theta_d, const void* emb_d, int per_atom_energy, void* energy_d,
-                       void* force_d);
+int stafb_model_set_counts(stafb_model* m, const int* tipos);
+int stafb_energy_force_domain(stafb_ctx* ctx, stafb_model* m, void* stream, const void* positions_d,
+                              const void* boxer_d, int nall, const int* type_map_d, const int* howmany_d,
+                              const int* with_d, const void* theta_d, const void* emb_d, void* energy_d,
+                              void* force_d, void* virial_d);
 }
 
 struct StafModel {
@@ -29,10 +31,15 @@ struct StafModel {
   // device side, (re)built when the atom count or the species counts change
   stafb_ctx* ctx;
   stafb_model* model;
-  int cap_n;
-  std::vector<int> tipos;
-  void *theta_d, *emb_d, *pos_d, *box_d, *e_d, *f_d;
-  std::vector<int> to_slot, from_slot;
+  int cap_n;  // atoms (owned + ghost) the device buffers hold
+  void *theta_d, *emb_d;
+  // per-call staging: one pinned host block and one device block with the same layout
+  //   in : pos[3*cap] | box[6] | type_map[cap] | howmany[cap] | with[cap*nr]
+  //   out: force[3*cap] | energy[1] | virial[9]
+  char *in_h, *in_d, *out_h, *out_d;
+  size_t in_bytes, out_bytes;
+  cudaStream_t stream;
+  std::vector<int> to_slot;
 };
 
 static bool read_matrix(const std::string& path, std::vector<double>& out) {
@@ -110,8 +117,12 @@ static void release_device(StafModel* m) {
   if (m->ctx) stafb_destroy(m->ctx);
   m->model = nullptr;
   m->ctx = nullptr;
-  void** p[] = {&m->theta_d, &m->emb_d, &m->pos_d, &m->box_d, &m->e_d, &m->f_d};
-  for (void** q : p) { if (*q) cudaFree(*q); *q = nullptr; }
+  void* dv[] = {m->theta_d, m->emb_d, m->in_d, m->out_d};
+  for (void* q : dv) if (q) cudaFree(q);
+  if (m->in_h) cudaFreeHost(m->in_h);
+  if (m->out_h) cudaFreeHost(m->out_h);
+  m->theta_d = m->emb_d = nullptr;
+  m->in_d = m->out_d = m->in_h = m->out_h = nullptr;
   m->cap_n = 0;
 }
 
@@ -122,7 +133,9 @@ extern "C" StafModel* staf_load(const char* model_dir, const StafOptions* opt) {
   staf_options_default(&m->opt);
   if (opt) m->opt = *opt;
   m->ctx = nullptr; m->model = nullptr; m->cap_n = 0;
-  m->theta_d = m->emb_d = m->pos_d = m->box_d = m->e_d = m->f_d = nullptr;
+  m->theta_d = m->emb_d = nullptr;
+  m->in_d = m->out_d = m->in_h = m->out_h = nullptr;
+  m->stream = nullptr;
   const int dev = staf_cuda_set_device(m->opt.device_id);
   if (dev < 0) { delete m; return NULL; }
   m->opt.device_id = dev;
@@ -187,118 +200,196 @@ extern "C" StafModel* staf_load(const char* model_dir, const StafOptions* opt) {
   return m;
 }
 
+
 template <class T>
 static void upload(void* dst, const std::vector<double>& src) {
   std::vector<T> t(src.begin(), src.end());
   cudaMemcpy(dst, t.data(), sizeof(T) * t.size(), cudaMemcpyHostToDevice);
 }
 
-static int ensure_device(StafModel* m, int n, const std::vector<int>& tipos) {
-  if (m->ctx && n <= m->cap_n && tipos == m->tipos) return 0;
-  const size_t es = m->opt.precision == 1 ? 8 : 4;
-  if (!m->ctx || n > m->cap_n) {
-    release_device(m);
-    if (stafb_create(&m->ctx, m->opt.precision == 1 ? STAFB_F64 : STAFB_F32, m->Rc, m->Rs, m->Ra, m->nr, m->na, n,
-                     1) != STAFB_OK)
-      return -1;
-    m->cap_n = n;
-    if (cudaMalloc(&m->theta_d, es * m->theta.size()) != cudaSuccess ||
-        cudaMalloc(&m->emb_d, es * m->emb.size()) != cudaSuccess ||
-        cudaMalloc(&m->pos_d, es * 3 * (size_t)n) != cudaSuccess || cudaMalloc(&m->box_d, es * 6) != cudaSuccess ||
-        cudaMalloc(&m->e_d, es) != cudaSuccess || cudaMalloc(&m->f_d, es * 3 * (size_t)n) != cudaSuccess)
-      return -1;
-    if (es == 8) { upload<double>(m->theta_d, m->theta); upload<double>(m->emb_d, m->emb); }
-    else { upload<float>(m->theta_d, m->theta); upload<float>(m->emb_d, m->emb); }
-  }
-  if (m->model) { stafb_model_destroy(m->model); m->model = nullptr; }
-  int sd[20] = {0};
-  sd[0] = m->nt;
-  for (int t = 0; t < m->nt; t++) { sd[1 + t] = tipos[t]; sd[5 + t] = m->Fr[t]; sd[9 + t] = m->Fa[t]; }
-  sd[13] = (int)m->widths.size();
-  for (size_t l = 0; l < m->widths.size(); l++) sd[14 + l] = m->widths[l];
-  if (stafb_model_create(m->ctx, sd, &m->model) != STAFB_OK) return -1;
-  m->tipos = tipos;
-  return 0;
+static size_t al16(size_t x) { return (x + 15) & ~(size_t)15; }
+
+// Offsets inside the staging blocks for a capacity of `cap` atoms.
+struct StageLayout {
+  size_t pos, box, tmap, how, with, in_total, force, energy, virial, out_total;
+};
+static StageLayout stage_layout(size_t es, size_t cap, size_t nr) {
+  StageLayout L;
+  size_t o = 0;
+  L.pos = o; o = al16(o + es * 3 * cap);
+  L.box = o; o = al16(o + es * 6);
+  L.tmap = o; o = al16(o + 4 * cap);
+  L.how = o; o = al16(o + 4 * cap);
+  L.with = o; o = al16(o + 4 * cap * nr);
+  L.in_total = o;
+  o = 0;
+  L.force = o; o = al16(o + es * 3 * cap);
+  L.energy = o; o = al16(o + es);
+  L.virial = o; o = al16(o + es * 9);
+  L.out_total = o;
+  return L;
 }
 
-extern "C" int staf_compute(StafModel* m, int nlocal, int nghost, const double* x, const double* box,
-                            const int* type, const int* howmany, const int* with, int maxneigh, double* e_rank,
-                            double* f, double* virial) {
-  (void)nghost; (void)with; (void)maxneigh;
-  if (!m || !x || !box) return -1;
-  if (howmany != NULL) return -10;
-  if (nlocal <= 0) return -3;
-  if (box[0] == 0.0 || box[3] == 0.0 || box[5] == 0.0) return -7;
-  if (cudaSetDevice(m->opt.device_id) != cudaSuccess) return -14;
-  const int nt = m->nt;
-  // type-sorted slots (staf_api.cpp:249-294)
+// (Re)creates the device side when more atoms arrive than the buffers hold; the species counts of the
+// owned atoms are set per call with stafb_model_set_counts, which allocates nothing.
+static int ensure_device(StafModel* m, int nall, const std::vector<int>& tipos) {
+  const size_t es = m->opt.precision == 1 ? 8 : 4;
+  if (!m->ctx || nall > m->cap_n) {
+    release_device(m);
+    const int cap = nall + nall / 4 + 64;  // head-room: owned and ghost counts drift from step to step in MD
+    if (stafb_create(&m->ctx, m->opt.precision == 1 ? STAFB_F64 : STAFB_F32, m->Rc, m->Rs, m->Ra, m->nr, m->na, cap,
+                     1) != STAFB_OK)
+      return -1;
+    m->cap_n = cap;
+    const StageLayout L = stage_layout(es, (size_t)cap, (size_t)m->nr);
+    m->in_bytes = L.in_total;
+    m->out_bytes = L.out_total;
+    if (cudaMalloc(&m->theta_d, es * m->theta.size()) != cudaSuccess ||
+        cudaMalloc(&m->emb_d, es * m->emb.size()) != cudaSuccess ||
+        cudaMalloc((void**)&m->in_d, L.in_total) != cudaSuccess ||
+        cudaMalloc((void**)&m->out_d, L.out_total) != cudaSuccess ||
+        cudaMallocHost((void**)&m->in_h, L.in_total) != cudaSuccess ||
+        cudaMallocHost((void**)&m->out_h, L.out_total) != cudaSuccess)
+      return -1;
+    if (!m->stream && cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess) return -1;
+    if (es == 8) { upload<double>(m->theta_d, m->theta); upload<double>(m->emb_d, m->emb); }
+    else { upload<float>(m->theta_d, m->theta); upload<float>(m->emb_d, m->emb); }
+    int sd[20] = {0};
+    sd[0] = m->nt;
+    for (int t = 0; t < m->nt; t++) { sd[1 + t] = tipos[t]; sd[5 + t] = m->Fr[t]; sd[9 + t] = m->Fa[t]; }
+    sd[13] = (int)m->widths.size();
+    for (size_t l = 0; l < m->widths.size(); l++) sd[14 + l] = m->widths[l];
+    if (stafb_model_create(m->ctx, sd, &m->model) != STAFB_OK) return -1;
+  }
+  return stafb_model_set_counts(m->model, tipos.data()) == STAFB_OK ? 0 : -1;
+}
+
+// Shared body of staf_compute and staf_compute_domain.  Slots: owned atoms type-sorted in
+// [0, nlocal), ghosts appended in the caller's order (libstaf/src/staf_api.cpp:249-294).
+template <class T>
+static int compute_impl(StafModel* m, int nlocal, int nghost, const double* x, const double* box, const int* type,
+                        const int* howmany, const int* with, int maxneigh, bool use_ghosts, double* e_rank,
+                        double* f, double* virial) {
+  const int nt = m->nt, nr = m->nr;
+  const int nall = use_ghosts ? nlocal + (nghost > 0 ? nghost : 0) : nlocal;
   std::vector<int> tipos(nt, 0), cursor(nt, 0);
   for (int i = 0; i < nlocal; i++) {
     const int sp = type ? type[i] : 0;
     if (sp < 0 || sp >= nt) { fprintf(stderr, "staf_compute: unsupported type %d at atom %d\n", sp, i); return -8; }
     tipos[sp]++;
   }
+  for (int i = nlocal; i < nall; i++) {
+    const int sp = type ? type[i] : 0;
+    if (sp < 0 || sp >= nt) { fprintf(stderr, "staf_compute: unsupported type %d at atom %d\n", sp, i); return -8; }
+  }
   for (int t = 1; t < nt; t++) cursor[t] = cursor[t - 1] + tipos[t - 1];
-  m->to_slot.resize(nlocal);
-  m->from_slot.resize(nlocal);
-  for (int i = 0; i < nlocal; i++) {
-    const int slot = cursor[type ? type[i] : 0]++;
+  if (ensure_device(m, nall, tipos) != 0) return -1;
+  const StageLayout L = stage_layout(sizeof(T), (size_t)m->cap_n, (size_t)nr);
+  T* pos_h = reinterpret_cast<T*>(m->in_h + L.pos);
+  T* box_h = reinterpret_cast<T*>(m->in_h + L.box);
+  int* tmap_h = reinterpret_cast<int*>(m->in_h + L.tmap);
+  int* how_h = reinterpret_cast<int*>(m->in_h + L.how);
+  int* with_h = reinterpret_cast<int*>(m->in_h + L.with);
+  m->to_slot.resize(nall);
+  for (int i = 0; i < nall; i++) {
+    const int sp = type ? type[i] : 0;
+    const int slot = i < nlocal ? cursor[sp]++ : i;
     m->to_slot[i] = slot;
-    m->from_slot[slot] = i;
+    tmap_h[slot] = sp;
+    pos_h[3 * (size_t)slot + 0] = (T)x[3 * (size_t)i + 0];
+    pos_h[3 * (size_t)slot + 1] = (T)x[3 * (size_t)i + 1];
+    pos_h[3 * (size_t)slot + 2] = (T)x[3 * (size_t)i + 2];
   }
-  if (ensure_device(m, nlocal, tipos) != 0) return -1;
-  const bool dbl = m->opt.precision == 1;
-  const size_t es = dbl ? 8 : 4;
-  std::vector<double> pd(3 * (size_t)nlocal);
-  for (int i = 0; i < nlocal; i++)
-    for (int a = 0; a < 3; a++) pd[3 * (size_t)m->to_slot[i] + a] = x[3 * (size_t)i + a];
-  if (dbl) {
-    cudaMemcpy(m->pos_d, pd.data(), 8 * pd.size(), cudaMemcpyHostToDevice);
-    cudaMemcpy(m->box_d, box, 8 * 6, cudaMemcpyHostToDevice);
-  } else {
-    std::vector<float> pf(pd.begin(), pd.end());
-    float bf[6];
-    for (int a = 0; a < 6; a++) bf[a] = (float)box[a];
-    cudaMemcpy(m->pos_d, pf.data(), 4 * pf.size(), cudaMemcpyHostToDevice);
-    cudaMemcpy(m->box_d, bf, 4 * 6, cudaMemcpyHostToDevice);
+  for (int a = 0; a < 6; a++) box_h[a] = (T)box[a];
+  size_t in_used = L.how;  // pos | box | type_map are contiguous from 0
+  if (howmany) {
+    // caller's rows -> slot order and slot indices (staf_api.cpp:304-347)
+    for (int i = 0; i < nlocal; i++) {
+      const int slot = m->to_slot[i];
+      int nn = howmany[i];
+      if (nn < 0) nn = 0;
+      if (nn > nr) nn = nr;
+      if (nn > maxneigh) nn = maxneigh;
+      how_h[slot] = nn;
+      int* row = with_h + (size_t)slot * nr;
+      for (int k = 0; k < nn; k++) {
+        const int j = with[(size_t)i * maxneigh + k];
+        if (j < 0 || j >= nall) {
+          fprintf(stderr, "staf_compute: neighbor index %d out of range [0,%d)\n", j, nall);
+          return -9;
+        }
+        row[k] = m->to_slot[j];
+      }
+    }
+    in_used = L.with + 4 * (size_t)nlocal * nr;
   }
-  int rc = stafb_energy_force(m->ctx, m->model, nullptr, m->pos_d, m->box_d, 1, m->theta_d, m->emb_d, 0, m->e_d,
-                              m->f_d);
+  cudaStream_t s = m->stream;
+  if (cudaMemcpyAsync(m->in_d, m->in_h, in_used, cudaMemcpyHostToDevice, s) != cudaSuccess) return -14;
+  int rc = stafb_energy_force_domain(
+      m->ctx, m->model, s, m->in_d + L.pos, m->in_d + L.box, nall, reinterpret_cast<const int*>(m->in_d + L.tmap),
+      howmany ? reinterpret_cast<const int*>(m->in_d + L.how) : nullptr,
+      howmany ? reinterpret_cast<const int*>(m->in_d + L.with) : nullptr, m->theta_d, m->emb_d, m->out_d + L.energy,
+      m->out_d + L.force, m->out_d + L.virial);
   if (rc != STAFB_OK) return rc == STAFB_ERR_CUDA ? -14 : -13;
-  const int st = stafb_status(m->ctx, nullptr);
+  if (cudaMemcpyAsync(m->out_h, m->out_d, L.out_total, cudaMemcpyDeviceToHost, s) != cudaSuccess) return -14;
+  const int st = stafb_status(m->ctx, s);  // synchronises the stream
   if (st == STAFB_ERR_RADIAL_OVERFLOW) return -11;
   if (st == STAFB_ERR_ANGULAR_OVERFLOW) return -12;
   if (st == STAFB_ERR_BAD_BOX) return -7;
   if (st == STAFB_ERR_CUDA) return -14;
   if (st != STAFB_OK && st != STAFB_ERR_NONFINITE) return -13;
-  double energy = 0.0;
-  std::vector<double> fd(3 * (size_t)nlocal);
-  if (dbl) {
-    cudaMemcpy(&energy, m->e_d, 8, cudaMemcpyDeviceToHost);
-    cudaMemcpy(fd.data(), m->f_d, 8 * fd.size(), cudaMemcpyDeviceToHost);
-  } else {
-    float ef = 0.f;
-    std::vector<float> ff(fd.size());
-    cudaMemcpy(&ef, m->e_d, 4, cudaMemcpyDeviceToHost);
-    cudaMemcpy(ff.data(), m->f_d, 4 * ff.size(), cudaMemcpyDeviceToHost);
-    energy = ef;
-    for (size_t q = 0; q < fd.size(); q++) fd[q] = ff[q];
-  }
-  (void)es;
-  if (!isfinite(energy))
-    fprintf(stderr, "staf_compute: non-finite energy=%g nlocal=%d\n", energy, nlocal);  // as staf_api.cpp:378-381
+  const T* f_h = reinterpret_cast<const T*>(m->out_h + L.force);
+  const double energy = (double)*reinterpret_cast<const T*>(m->out_h + L.energy);
+  const T* v_h = reinterpret_cast<const T*>(m->out_h + L.virial);
+  if (!isfinite(energy))  // as staf_api.cpp:378-381
+    fprintf(stderr, "staf_compute: non-finite energy=%g nlocal=%d nghost=%d\n", energy, nlocal, nghost);
   if (e_rank) *e_rank = energy;
   if (f)
-    for (int s = 0; s < nlocal; s++)
-      for (int a = 0; a < 3; a++) f[3 * (size_t)m->from_slot[s] + a] = fd[3 * (size_t)s + a];
-  if (virial)
-    for (int a = 0; a < 6; a++) virial[a] = 0.0;
+    for (int i = 0; i < nall; i++) {
+      const size_t sl = (size_t)m->to_slot[i];
+      f[3 * (size_t)i + 0] = (double)f_h[3 * sl + 0];
+      f[3 * (size_t)i + 1] = (double)f_h[3 * sl + 1];
+      f[3 * (size_t)i + 2] = (double)f_h[3 * sl + 2];
+    }
+  if (virial) {
+    // diagonal only, like the reference (staf_api.cpp:398-403)
+    virial[0] = (double)v_h[0]; virial[1] = (double)v_h[4]; virial[2] = (double)v_h[8];
+    virial[3] = virial[4] = virial[5] = 0.0;
+  }
   return 0;
+}
+
+static int compute_checked(StafModel* m, int nlocal, int nghost, const double* x, const double* box, const int* type,
+                           const int* howmany, const int* with, int maxneigh, bool use_ghosts, double* e_rank,
+                           double* f, double* virial) {
+  if (!m || !x || !box) return -1;
+  if (nlocal <= 0) return -3;
+  if (howmany && (!with || maxneigh <= 0)) return -1;
+  if (box[0] == 0.0 || box[3] == 0.0 || box[5] == 0.0) return -7;
+  if (cudaSetDevice(m->opt.device_id) != cudaSuccess) return -14;
+  if (m->opt.precision == 1)
+    return compute_impl<double>(m, nlocal, nghost, x, box, type, howmany, with, maxneigh, use_ghosts, e_rank, f,
+                                virial);
+  return compute_impl<float>(m, nlocal, nghost, x, box, type, howmany, with, maxneigh, use_ghosts, e_rank, f, virial);
+}
+
+extern "C" int staf_compute(StafModel* m, int nlocal, int nghost, const double* x, const double* box,
+                            const int* type, const int* howmany, const int* with, int maxneigh, double* e_rank,
+                            double* f, double* virial) {
+  // howmany == NULL: own minimum-image list over the nlocal atoms, nghost ignored (staf_api.cpp:211-212)
+  return compute_checked(m, nlocal, nghost, x, box, type, howmany, with, maxneigh, howmany != NULL, e_rank, f,
+                         virial);
+}
+
+extern "C" int staf_compute_domain(StafModel* m, int nlocal, int nghost, const double* x, const double* box,
+                                   const int* type, double* e_rank, double* f, double* virial) {
+  return compute_checked(m, nlocal, nghost, x, box, type, NULL, NULL, 0, true, e_rank, f, virial);
 }
 
 extern "C" void staf_free(StafModel* m) {
   if (!m) return;
   cudaSetDevice(m->opt.device_id);
   release_device(m);
+  if (m->stream) cudaStreamDestroy(m->stream);
   delete m;
 }

@@ -206,13 +206,82 @@ __device__ __forceinline__ void mic_vec(const FrameGeom<T>& g, T ax, T ay, T az,
   dz = g.box[5] * oz;
 }
 
+// One slot of a central atom's radial row (reforce.cu.cc:17-110) from the vector v = r_i - r_j: radial
+// descriptor, angular-support cutoff, their gradients, the neighbour id and the compact geometry the
+// fused sweeps read.  Slots past the neighbour count (valid == false) are zero-filled.
+template <class T>
+__device__ __forceinline__ void radial_slot(const CoreCoef<T>& cc, bool valid, int j, T vx, T vy, T vz, size_t base,
+                                            int k, int nr, T* __restrict__ raddescr, T* __restrict__ des3bsupp,
+                                            int* __restrict__ intmap2b, T* __restrict__ der2b,
+                                            T* __restrict__ der3bsupp, T* __restrict__ geom, T* __restrict__ gsc,
+                                            int& nang) {
+  const T PI = PIc<T>();
+  T rd = T(0), d3 = T(0), g2x = T(0), g2y = T(0), g2z = T(0), g3x = T(0), g3y = T(0), g3z = T(0);
+  T dn = T(0), s2 = T(0), s3 = T(0);
+  if (valid) {
+    dn = r_sqrt(vx * vx + vy * vy + vz * vz);
+    if (dn < cc.Ra) {
+      nang++;
+      d3 = T(0.5) * (r_cos(PI * dn / cc.Ra) + T(1));
+      const T pre = T(-0.5) * r_sin(PI * dn / cc.Ra) * PI / cc.Ra;
+      s3 = pre;
+      g3x = pre * vx / dn;
+      g3y = pre * vy / dn;
+      g3z = pre * vz / dn;
+    }
+    if (dn < cc.Rs) {
+      // A/r^1 + B/r^-30 + C with the powers by repeated multiplication (the reference calls pow;
+      // the exponents are the constants 1 and -30 of descriptor_builder/reforce.cc:102-103)
+      const T r2 = dn * dn, r4 = r2 * r2, r8 = r4 * r4, r16 = r8 * r8;
+      const T r28 = r16 * r8 * r4, r29 = r28 * dn, r30 = r28 * r2;
+      rd = cc.A / dn + cc.B * r30 + cc.C;
+      const T pre = (-cc.pa * cc.A / r2 - cc.pb * cc.B * r29);
+      s2 = pre;
+      g2x = pre * vx / dn;
+      g2y = pre * vy / dn;
+      g2z = pre * vz / dn;
+    } else {
+      rd = T(0.5) * (r_cos(PI * dn / cc.Rc) + T(1));
+      const T pre = T(-0.5) * r_sin(PI * dn / cc.Rc) * PI / cc.Rc;
+      s2 = pre;
+      g2x = pre * vx / dn;
+      g2y = pre * vy / dn;
+      g2z = pre * vz / dn;
+    }
+  }
+  raddescr[base * nr + k] = rd;
+  des3bsupp[base * nr + k] = d3;
+  if (der2b) {
+    der2b[(base * 3 + 0) * nr + k] = g2x;
+    der2b[(base * 3 + 1) * nr + k] = g2y;
+    der2b[(base * 3 + 2) * nr + k] = g2z;
+  }
+  if (der3bsupp) {
+    der3bsupp[(base * 3 + 0) * nr + k] = g3x;
+    der3bsupp[(base * 3 + 1) * nr + k] = g3y;
+    der3bsupp[(base * 3 + 2) * nr + k] = g3z;
+  }
+  intmap2b[base * (nr + 1) + 1 + k] = valid ? j : 0;
+  if (geom) {
+    typename Vec4<T>::type q;
+    q.x = vx; q.y = vy; q.z = vz; q.w = dn;
+    reinterpret_cast<typename Vec4<T>::type*>(geom)[base * nr + k] = q;
+  }
+  if (gsc) {
+    // scalar radial derivatives: der2b = s2 * v/|v|, der3bsupp = s3 * v/|v|
+    typename Vec2<T>::type q;
+    q.x = s2; q.y = s3;
+    reinterpret_cast<typename Vec2<T>::type*>(gsc)[base * nr + k] = q;
+  }
+}
+
 // One warp per central atom: candidate discovery over the 27 neighbour cells in the
 // reference's visiting order (x outer, y, z inner, offsets -1,0,1: celle_gpu.cu.cc:61-82),
 // stable sort by dist2 (celle_gpu.cu.cc:128-152), then the radial descriptor row
 // (reforce.cu.cc:17-110).
 template <class T, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
-    k_nl_radial(int nf, int N, int nr, CoreCoef<T> cc, const FrameGeom<T>* __restrict__ fg,
+    k_nl_radial(int nf, int N, int ncen, int nr, CoreCoef<T> cc, const FrameGeom<T>* __restrict__ fg,
                 const T* __restrict__ frac, const int* __restrict__ cell_of, const int* __restrict__ cell_start,
                 const int* __restrict__ cells_sorted, int cell_cap, T* __restrict__ raddescr,
                 T* __restrict__ des3bsupp, int* __restrict__ intmap2b, T* __restrict__ der2b,
@@ -220,9 +289,9 @@ __global__ void __launch_bounds__(WARPS * 32)
                 int na, int* __restrict__ status) {
   extern __shared__ unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int gi = blockIdx.x * WARPS + warp;
-  if (gi >= nf * N) return;
-  const int b = gi / N, i = gi - b * N;
+  const int gi = blockIdx.x * WARPS + warp;  // row index: the centres are the first ncen atoms of each frame
+  if (gi >= nf * ncen) return;
+  const int b = gi / ncen, i = gi - b * ncen;
   // per-warp rows: d2a[nr] d2b[nr] (T) then ja[nr] jb[nr] (int)
   T* d2a = reinterpret_cast<T*>(smem_raw) + (size_t)warp * 2 * nr;
   T* d2b = d2a + nr;
@@ -232,7 +301,7 @@ __global__ void __launch_bounds__(WARPS * 32)
   const FrameGeom<T> g = fg[b];
   const T* fr = frac + (size_t)b * N * 3;
   const T pix = fr[3 * i], piy = fr[3 * i + 1], piz = fr[3 * i + 2];
-  const int ci = cell_of[gi];
+  const int ci = cell_of[(size_t)b * N + i];
   const int cz = ci / (g.nx * g.ny), rem = ci - cz * (g.nx * g.ny), cy = rem / g.nx, cx = rem - cy * g.nx;
   const int* cst = cell_start + (size_t)b * (cell_cap + 1);
   const int* cl = cells_sorted + (size_t)b * N;
@@ -307,70 +376,67 @@ __global__ void __launch_bounds__(WARPS * 32)
     jb[r] = ja[e];
   }
   __syncwarp();
-  const T PI = PIc<T>();
   const size_t base = (size_t)gi;
   int nang = 0;
   for (int k = lane; k < nr; k += 32) {
-    T rd = T(0), d3 = T(0), g2x = T(0), g2y = T(0), g2z = T(0), g3x = T(0), g3y = T(0), g3z = T(0);
-    T vx = T(0), vy = T(0), vz = T(0), dn = T(0), s2 = T(0), s3 = T(0);
+    T vx = T(0), vy = T(0), vz = T(0);
     int j = 0;
     if (k < n) {
       j = jb[k];
       mic_vec(g, pix, piy, piz, fr[3 * j], fr[3 * j + 1], fr[3 * j + 2], vx, vy, vz);
-      dn = r_sqrt(vx * vx + vy * vy + vz * vz);
-      if (dn < cc.Ra) {
-        nang++;
-        d3 = T(0.5) * (r_cos(PI * dn / cc.Ra) + T(1));
-        const T pre = T(-0.5) * r_sin(PI * dn / cc.Ra) * PI / cc.Ra;
-        s3 = pre;
-        g3x = pre * vx / dn;
-        g3y = pre * vy / dn;
-        g3z = pre * vz / dn;
-      }
-      if (dn < cc.Rs) {
-        // A/r^1 + B/r^-30 + C with the powers by repeated multiplication (the reference calls pow;
-        // the exponents are the constants 1 and -30 of descriptor_builder/reforce.cc:102-103)
-        const T r2 = dn * dn, r4 = r2 * r2, r8 = r4 * r4, r16 = r8 * r8;
-        const T r28 = r16 * r8 * r4, r29 = r28 * dn, r30 = r28 * r2;
-        rd = cc.A / dn + cc.B * r30 + cc.C;
-        const T pre = (-cc.pa * cc.A / r2 - cc.pb * cc.B * r29);
-        s2 = pre;
-        g2x = pre * vx / dn;
-        g2y = pre * vy / dn;
-        g2z = pre * vz / dn;
+    }
+    radial_slot<T>(cc, k < n, j, vx, vy, vz, base, k, nr, raddescr, des3bsupp, intmap2b, der2b, der3bsupp, geom, gsc,
+                   nang);
+  }
+  nang = warp_sum(nang);
+  if (lane == 0) {
+    intmap2b[base * (nr + 1)] = n;
+    numtriplet[base] = nang;
+    if ((long long)nang * (nang - 1) / 2 > na) set_status(status, STAFB_ERR_ANGULAR_OVERFLOW);
+  }
+}
+
+// Radial rows from a caller-supplied neighbour list: the contract LAMMPS drives libstaf with
+// (libstaf/src/staf_api.cpp:304-347, libstaf/vendor/jmd/nn_nn_mlp.cu:174-206,847-853).  The rows are
+// already cutoff-filtered and distance-sorted by the caller and ghost atoms carry their periodic image,
+// so there is no search, no sort and no minimum-image wrap: v = r_i - r_j in Cartesian space.
+// One warp per centre; the centres are the first ncen of the nall atoms.
+template <class T, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
+    k_rows_from_list(int ncen, int nall, int nr, CoreCoef<T> cc, const T* __restrict__ pos,
+                     const int* __restrict__ howmany, const int* __restrict__ with, T* __restrict__ raddescr,
+                     T* __restrict__ des3bsupp, int* __restrict__ intmap2b, int* __restrict__ numtriplet,
+                     T* __restrict__ geom, T* __restrict__ gsc, int na, int* __restrict__ status) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int i = blockIdx.x * WARPS + warp;
+  if (i >= ncen) return;
+  int n = howmany[i];
+  if (n < 0) n = 0;
+  if (n > nr) {
+    if (lane == 0) set_status(status, STAFB_ERR_RADIAL_OVERFLOW);
+    n = nr;
+  }
+  const T pix = pos[3 * i], piy = pos[3 * i + 1], piz = pos[3 * i + 2];
+  const size_t base = (size_t)i;
+  int nang = 0;
+  for (int k = lane; k < nr; k += 32) {
+    T vx = T(0), vy = T(0), vz = T(0);
+    int j = 0;
+    bool valid = k < n;
+    if (valid) {
+      j = with[(size_t)i * nr + k];
+      if (j < 0 || j >= nall || j == i) {
+        set_status(status, STAFB_ERR_INVALID);
+        valid = false;
+        j = 0;
       } else {
-        rd = T(0.5) * (r_cos(PI * dn / cc.Rc) + T(1));
-        const T pre = T(-0.5) * r_sin(PI * dn / cc.Rc) * PI / cc.Rc;
-        s2 = pre;
-        g2x = pre * vx / dn;
-        g2y = pre * vy / dn;
-        g2z = pre * vz / dn;
+        vx = pix - pos[3 * j];
+        vy = piy - pos[3 * j + 1];
+        vz = piz - pos[3 * j + 2];
       }
     }
-    raddescr[base * nr + k] = rd;
-    des3bsupp[base * nr + k] = d3;
-    if (der2b) {
-      der2b[(base * 3 + 0) * nr + k] = g2x;
-      der2b[(base * 3 + 1) * nr + k] = g2y;
-      der2b[(base * 3 + 2) * nr + k] = g2z;
-    }
-    if (der3bsupp) {
-      der3bsupp[(base * 3 + 0) * nr + k] = g3x;
-      der3bsupp[(base * 3 + 1) * nr + k] = g3y;
-      der3bsupp[(base * 3 + 2) * nr + k] = g3z;
-    }
-    intmap2b[base * (nr + 1) + 1 + k] = (k < n) ? j : 0;
-    if (geom) {
-      typename Vec4<T>::type q;
-      q.x = vx; q.y = vy; q.z = vz; q.w = dn;
-      reinterpret_cast<typename Vec4<T>::type*>(geom)[base * nr + k] = q;
-    }
-    if (gsc) {
-      // scalar radial derivatives: der2b = s2 * v/|v|, der3bsupp = s3 * v/|v|
-      typename Vec2<T>::type q;
-      q.x = s2; q.y = s3;
-      reinterpret_cast<typename Vec2<T>::type*>(gsc)[base * nr + k] = q;
-    }
+    radial_slot<T>(cc, valid, j, vx, vy, vz, base, k, nr, raddescr, des3bsupp, intmap2b, nullptr, nullptr, geom, gsc,
+                   nang);
   }
   nang = warp_sum(nang);
   if (lane == 0) {
@@ -450,9 +516,11 @@ __global__ void __launch_bounds__(THREADS)
 template <class T>
 int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box, int nf, int N, T* raddescr,
                        T* angdescr, T* des3bsupp, int* intmap2b, int* intmap3b, T* der2b, T* der3b, T* der3bsupp,
-                       int* numtriplet) {
+                       int* numtriplet, int ncen) {
   if (nf <= 0 || N <= 0) return STAFB_ERR_INVALID;
   if (nf > c->max_batch || N > c->n_max) return STAFB_ERR_CAPACITY;
+  if (ncen < 0) ncen = N;  // every atom is a centre unless the caller restricts the rows to the first ncen
+  if (ncen > N) return STAFB_ERR_INVALID;
   const int nr = c->nr, na = c->na, cap = c->cell_cap;
   FrameGeom<T>* fg = reinterpret_cast<FrameGeom<T>*>(c->fgeom);
   T* frac = reinterpret_cast<T*>(c->frac);
@@ -483,7 +551,8 @@ int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box,
   {
     constexpr int W = 4;
     size_t sm = (size_t)W * 2 * nr * (sizeof(T) + sizeof(int)) + (size_t)W * 64 * sizeof(int);
-    k_nl_radial<T, W><<<(tot + W - 1) / W, W * 32, sm, s>>>(nf, N, nr, cc, fg, frac, c->cell_of, c->cell_start,
+    const int rows = nf * ncen;
+    k_nl_radial<T, W><<<(rows + W - 1) / W, W * 32, sm, s>>>(nf, N, ncen, nr, cc, fg, frac, c->cell_of, c->cell_start,
                                                           c->cells_sorted, cap, raddescr, des3bsupp, intmap2b, der2b,
                                                           der3bsupp, numtriplet, geom, gsc, na, c->status_d);
   }
@@ -491,7 +560,7 @@ int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box,
   if (angdescr && intmap3b && der3b) {
     constexpr int TH = 128;
     size_t sm = (size_t)nr * (sizeof(typename Vec4<T>::type) + 2 * sizeof(T) + sizeof(int));
-    k_angular<T, TH><<<tot, TH, sm, s>>>(nf, N, nr, na, cc.Ra, geom, intmap2b, numtriplet, angdescr, intmap3b, der3b);
+    k_angular<T, TH><<<nf * ncen, TH, sm, s>>>(nf, N, nr, na, cc.Ra, geom, intmap2b, numtriplet, angdescr, intmap3b, der3b);
     c->launches += 1;
   }
   STAFB_CUDA_OK(cudaGetLastError());
@@ -499,9 +568,31 @@ int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box,
 }
 
 template int launch_descriptors<float>(stafb_ctx*, cudaStream_t, const float*, const float*, int, int, float*, float*,
-                                       float*, int*, int*, float*, float*, float*, int*);
+                                       float*, int*, int*, float*, float*, float*, int*, int);
 template int launch_descriptors<double>(stafb_ctx*, cudaStream_t, const double*, const double*, int, int, double*,
-                                        double*, double*, int*, int*, double*, double*, double*, int*);
+                                        double*, double*, int*, int*, double*, double*, double*, int*, int);
+
+template <class T>
+int launch_rows_from_list(stafb_ctx* c, cudaStream_t s, const T* pos, int ncen, int nall, const int* howmany,
+                          const int* with, T* raddescr, T* des3bsupp, int* intmap2b, int* numtriplet) {
+  if (ncen <= 0 || nall < ncen || !howmany || !with) return STAFB_ERR_INVALID;
+  if (nall > c->n_max) return STAFB_ERR_CAPACITY;
+  CoreCoef<T> cc;
+  cc.Rc = (T)c->Rc; cc.Rs = (T)c->Rs; cc.Ra = (T)c->Ra;
+  cc.A = (T)c->coef[0]; cc.B = (T)c->coef[1]; cc.C = (T)c->coef[2]; cc.pa = (T)c->coef[3]; cc.pb = (T)c->coef[4];
+  constexpr int W = 4;
+  k_rows_from_list<T, W><<<(ncen + W - 1) / W, W * 32, 0, s>>>(ncen, nall, c->nr, cc, pos, howmany, with, raddescr,
+                                                             des3bsupp, intmap2b, numtriplet,
+                                                             reinterpret_cast<T*>(c->geom),
+                                                             reinterpret_cast<T*>(c->gsc), c->na, c->status_d);
+  c->launches += 1;
+  STAFB_CUDA_OK(cudaGetLastError());
+  return STAFB_OK;
+}
+template int launch_rows_from_list<float>(stafb_ctx*, cudaStream_t, const float*, int, int, const int*, const int*,
+                                          float*, float*, int*, int*);
+template int launch_rows_from_list<double>(stafb_ctx*, cudaStream_t, const double*, int, int, const int*, const int*,
+                                           double*, double*, int*, int*);
 
 }  // namespace stafb
 

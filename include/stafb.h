@@ -182,6 +182,34 @@ int stafb_energy_force(stafb_ctx* ctx, stafb_model* m, void* stream, const void*
                        int nf, const void* theta_d, const void* emb_d, int per_atom_energy, void* energy_d,
                        void* force_d);
 
+/* New species counts for an existing model (same parameter layout): atoms per species may change from call
+ * to call as long as their sum stays within the n_max the context was created with.  An MD driver whose
+ * owned atoms migrate between domains (lammps/USER-STAF/pair_staf.cpp:180-256 rebuilds its arrays every step)
+ * calls this instead of recreating the model. */
+int stafb_model_set_counts(stafb_model* m, const int* tipos);
+
+/* Energy and forces of ONE frame in which only the first N atoms (the model's species-sorted atoms) are
+ * centres and the remaining nall-N atoms are ghosts: they act as neighbours and receive forces but
+ * contribute no atomic energy - the owned/ghost contract of libstaf's staf_compute
+ * (libstaf/include/staf.h:38-59, libstaf/src/staf_api.cpp:230-347).  type_map[nall] gives the species of
+ * every atom (the ghosts are not species-sorted).  energy[1] = 0.5*sum over the centres; force[nall,3].
+ *   howmany == NULL: the library builds the neighbour list over all nall atoms with the minimum-image
+ *     convention of boxer[6] (every physical atom must appear at most once among owned + ghosts);
+ *   howmany[N], with[N, radial_buffer] given: rows are taken as they are (cutoff-filtered and
+ *     distance-sorted by the caller, indices 0..nall-1), vectors are plain Cartesian differences because the
+ *     ghosts carry their periodic image (libstaf/vendor/jmd/nn_nn_mlp.cu:847-853); boxer may be NULL. */
+int stafb_energy_force_domain(stafb_ctx* ctx, stafb_model* m, void* stream, const void* positions_d,
+                              const void* boxer_d, int nall, const int* type_map_d, const int* howmany_d,
+                              const int* with_d, const void* theta_d, const void* emb_d, void* energy_d,
+                              void* force_d, void* virial_d /* [9] or NULL */);
+
+/* stafb_energy_force plus the 3x3 virial W_ab = -sum g_a r_b of every frame (virial[nf,9], row-major), the sum
+ * of what ComputeForceRadialVirial and ComputeForceTriplVirial return over all central species
+ * (force/rad/reforce.cc:133-146, force/ang/reforce.cc:159-176; staf_models/staf_model_inference_full.py:89-144). */
+int stafb_energy_force_virial(stafb_ctx* ctx, stafb_model* m, void* stream, const void* positions_d,
+                              const void* boxer_d, int nf, const void* theta_d, const void* emb_d,
+                              int per_atom_energy, void* energy_d, void* force_d, void* virial_d);
+
 /* One energy+force training evaluation (full_train_e_f, staf_models/staf_model.py:168-258, without
  * the optimizer update): loss = pe*L(E,e_label) + pb*sum(alpha*[alpha>alpha_bound]) + pf*L(F,f_label),
  * L = Keras Huber(delta=1, mean) if loss_kind == 0 else MSE.  Writes losses[4] (double: loss, loss_e,

@@ -83,12 +83,13 @@ def test_staf_compute_error_codes(lib, frame0):
     t2 = types.copy()
     t2[5] = 7
     assert _compute(lib, m, x, box, t2)[0] == -8
-    how = np.zeros(N, np.int32)
+    how = np.ones(N, np.int32)
+    bad_with = np.full(N, N + 5, np.int32)
     e = C.c_double()
     f = np.zeros(3 * N)
     xx = np.ascontiguousarray(x, np.float64)
     assert lib.staf_compute(m, N, 0, xx.ctypes.data, box.ctypes.data, types.ctypes.data, how.ctypes.data,
-                            how.ctypes.data, 1, C.byref(e), f.ctypes.data, None) == -10
+                            bad_with.ctypes.data, 1, C.byref(e), f.ctypes.data, None) == -9
     # a compressed box saturates the radial buffer: an error code, not an exit
     small = box * 0.6
     assert _compute(lib, m, x * 0.6, small, types)[0] == -11
@@ -96,3 +97,120 @@ def test_staf_compute_error_codes(lib, frame0):
     assert _compute(lib, m, x, box, types)[0] == 0
     lib.staf_free(m)
     assert lib.staf_load(b"/nonexistent/model/dir", None) is None
+
+
+def _wrapped(frame0):
+    """frame 0 wrapped into the (cubic) box: positions [N,3], L, species."""
+    N = frame0["shape"].N
+    L = float(frame0["box"][0][0])
+    x = frame0["pos"].reshape(N, 3)
+    return x - np.floor(x / L) * L, L, frame0["shape"].type_map.astype(np.int32)
+
+
+def _call(lib, m, fn, nlocal, nghost, x, box, types, how=None, wth=None, maxneigh=0):
+    nall = nlocal + nghost
+    e = C.c_double()
+    f = np.zeros(3 * nall)
+    vir = np.zeros(6)
+    x = np.ascontiguousarray(x, np.float64)
+    box = np.ascontiguousarray(box, np.float64)
+    types = np.ascontiguousarray(types, np.int32)
+    if fn == "list":
+        rc = lib.staf_compute(m, nlocal, nghost, x.ctypes.data, box.ctypes.data, types.ctypes.data, how.ctypes.data,
+                              wth.ctypes.data, maxneigh, C.byref(e), f.ctypes.data, vir.ctypes.data)
+    else:
+        rc = lib.staf_compute_domain(m, nlocal, nghost, x.ctypes.data, box.ctypes.data, types.ctypes.data,
+                                     C.byref(e), f.ctypes.data, vir.ctypes.data)
+    return rc, e.value, f.reshape(nall, 3), vir
+
+
+# fp32: the two paths round the pair vectors differently (Cartesian differences of coordinates up to L + Rc
+# against minimum-image differences of fractional coordinates), which moves forces by ~2e-5 relative; the bar
+# there is the reference's own domain-decomposition bar of 1e-4 (test/test-lammps-dd-parity/run_dd_parity.sh:14-15)
+@pytest.mark.parametrize("precision,tol", [(0, 1e-4), (1, 1e-10)])
+def test_staf_compute_caller_list_with_ghost_images(lib, frame0, precision, tol):
+    """The LAMMPS contract (lammps/USER-STAF/pair_staf.cpp:180-256 of the reference): owned atoms + ghost
+    images, rows cutoff-filtered and distance-sorted by the caller, no wrap inside the library, ghost forces
+    folded back by the caller.  Must reproduce the library's own minimum-image result."""
+    lib.staf_compute_domain.argtypes = [C.c_void_p, C.c_int, C.c_int] + [C.c_void_p] * 6
+    opt = StafOptions()
+    lib.staf_options_default(C.byref(opt))
+    opt.precision = precision
+    m = lib.staf_load(frame0["dir"].encode(), C.byref(opt))
+    xw, L, types = _wrapped(frame0)
+    N = len(types)
+    box = frame0["box"][0]
+    rc0, e0, f0, v0 = _compute(lib, m, xw.ravel(), box, types)
+    assert rc0 == 0
+    Rc = frame0["cfg"]["Rc"]
+    # ghost shell: every periodic image that lies within Rc of the box
+    gx, gowner = [], []
+    for sx in (-1, 0, 1):
+        for sy in (-1, 0, 1):
+            for sz in (-1, 0, 1):
+                if (sx, sy, sz) == (0, 0, 0):
+                    continue
+                img = xw + np.array([sx, sy, sz]) * L
+                keep = np.all((img > -Rc) & (img < L + Rc), axis=1)
+                gx.append(img[keep])
+                gowner.append(np.nonzero(keep)[0])
+    gx, gowner = np.concatenate(gx), np.concatenate(gowner)
+    xall = np.concatenate([xw, gx])
+    tall = np.concatenate([types, types[gowner]])
+    nghost = len(gowner)
+    maxneigh = 64
+    how = np.zeros(N, np.int32)
+    wth = np.zeros((N, maxneigh), np.int32)
+    for i in range(N):
+        d2 = ((xall - xw[i]) ** 2).sum(1)
+        d2[i] = np.inf
+        idx = np.nonzero(d2 < Rc * Rc)[0]
+        idx = idx[np.argsort(d2[idx], kind="stable")]
+        how[i] = len(idx)
+        wth[i, :len(idx)] = idx
+    assert how.max() <= 60
+    rc, e, f, v = _call(lib, m, "list", N, nghost, xall.ravel(), box, tall, how, wth, maxneigh)
+    assert rc == 0
+    folded = f[:N].copy()
+    np.add.at(folded, gowner, f[N:])
+    assert abs(e - e0) <= 10 * tol * abs(e0)
+    assert rel_err(folded, f0.reshape(N, 3)) <= tol
+    assert rel_err(v[:3], v0[:3]) <= 20 * tol and np.all(v[3:] == 0)
+    lib.staf_free(m)
+
+
+@pytest.mark.parametrize("nslab", [2, 4])
+@pytest.mark.parametrize("precision,tol", [(0, 1e-4), (1, 1e-10)])
+def test_staf_compute_domain_slab_parity(lib, frame0, nslab, precision, tol):
+    """Domain-decomposition parity, the reference's test/test-lammps-dd-parity (1 vs 2 vs 4 ranks: max|dE|,
+    max|dF| <= 1e-4) restated without LAMMPS: z-slabs with one-cutoff halos, ghost forces folded back."""
+    lib.staf_compute_domain.argtypes = [C.c_void_p, C.c_int, C.c_int] + [C.c_void_p] * 6
+    opt = StafOptions()
+    lib.staf_options_default(C.byref(opt))
+    opt.precision = precision
+    m = lib.staf_load(frame0["dir"].encode(), C.byref(opt))
+    xw, L, types = _wrapped(frame0)
+    N = len(types)
+    box = frame0["box"][0]
+    rc0, e0, f0, v0 = _compute(lib, m, xw.ravel(), box, types)
+    assert rc0 == 0
+    Rc = frame0["cfg"]["Rc"]
+    w = L / nslab
+    etot, ftot, vtot = 0.0, np.zeros((N, 3)), np.zeros(6)
+    for r in range(nslab):
+        z = xw[:, 2]
+        owned = np.nonzero((z >= r * w) & (z < (r + 1) * w))[0]
+        dz = (z - (r + 0.5) * w + 0.5 * L) % L - 0.5 * L  # periodic distance to the slab centre
+        ghost = np.nonzero((np.abs(dz) < 0.5 * w + Rc) & ~((z >= r * w) & (z < (r + 1) * w)))[0]
+        if nslab == 2:
+            ghost = np.unique(ghost)
+        ids = np.concatenate([owned, ghost])
+        rc, e, f, v = _call(lib, m, "domain", len(owned), len(ghost), xw[ids].ravel(), box, types[ids])
+        assert rc == 0
+        etot += e
+        np.add.at(ftot, ids, f)
+        vtot += v
+    assert abs(etot - e0) <= 10 * tol * abs(e0)
+    assert rel_err(ftot, f0.reshape(N, 3)) <= tol
+    assert rel_err(vtot[:3], v0[:3]) <= 20 * tol
+    lib.staf_free(m)
