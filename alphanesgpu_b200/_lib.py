@@ -48,6 +48,9 @@ _SIGS = {
     "stafb_model_n_emb": [_vp],
     "stafb_model_offsets": [_vp, _i, _vp],
     "stafb_energy_force": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp],
+    "stafb_energy_force_virial": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp],
+    "stafb_energy_force_domain": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "stafb_model_set_counts": [_vp, _vp],
     "stafb_train_step": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _i, _vp, _vp, _vp, _vp],
     "stafb_train_step_host": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _i, _vp, _vp],
     "stafb_adam_step_dev": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _d, _d, _d, _d, _vp, _d],

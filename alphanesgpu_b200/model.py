@@ -23,11 +23,15 @@ class StafModel:
     """One potential: geometry config + parameter layout + device buffers."""
 
     def __init__(self, shape: ModelShape, cfg, theta, emb, max_batch, dtype=torch.float32, device=None,
-                 pe=1.0, pf=1.0, pb=1.0, alpha_bound=5.0, loss="huber"):
+                 pe=1.0, pf=1.0, pb=1.0, alpha_bound=5.0, loss="huber", n_max=None):
+        """n_max: atoms per frame the scratch is sized for (default shape.N); larger values leave room for
+        ghost atoms (energy_force_domain) and for set_counts()."""
         self.shape = shape
         self.cfg = dict(cfg)
         self.dtype = dtype
-        self.ctx = Context(cfg["Rc"], cfg["nr"], cfg["na"], shape.N, cfg["Rs"], cfg["Ra"], max_batch, dtype, device)
+        self.n_max = int(n_max) if n_max else shape.N
+        self.n_centres = shape.N
+        self.ctx = Context(cfg["Rc"], cfg["nr"], cfg["na"], self.n_max, cfg["Rs"], cfg["Ra"], max_batch, dtype, device)
         self.device = self.ctx.device
         self.max_batch = int(max_batch)
         h = C.c_void_p()
@@ -78,6 +82,45 @@ class StafModel:
         if check_status:
             self.ctx.raise_on_status("stafb_energy_force")
         return energy, force
+
+    def energy_force_virial(self, pos, box, per_atom_energy=False):
+        """energy_force plus the 3x3 virial W_ab = -sum g_a r_b per frame ([nf,9], row-major)."""
+        pos, box = self._dev(pos), self._dev(box)
+        nf = box.shape[0]
+        energy = torch.empty(nf, dtype=self.dtype, device=self.device)
+        force = torch.empty(nf, 3 * self.n_centres, dtype=self.dtype, device=self.device)
+        virial = torch.empty(nf, 9, dtype=self.dtype, device=self.device)
+        check(_lib.lib().stafb_energy_force_virial(self.ctx.h, self.h, self.ctx.stream(), _p(pos), _p(box), nf,
+                                                   _p(self.theta), _p(self.emb), int(per_atom_energy), _p(energy),
+                                                   _p(force), _p(virial)), "stafb_energy_force_virial")
+        self.ctx.raise_on_status("stafb_energy_force_virial")
+        return energy, force, virial
+
+    def set_counts(self, tipos):
+        """New numbers of (owned) atoms per species; the sum must stay within n_max."""
+        t = np.ascontiguousarray(tipos, np.int32)
+        check(_lib.lib().stafb_model_set_counts(self.h, t.ctypes.data_as(C.c_void_p)), "stafb_model_set_counts")
+        self.n_centres = int(t.sum())
+
+    def energy_force_domain(self, pos_all, box, type_map, howmany=None, with_=None, virial=False,
+                            check_status=True):
+        """One frame of nall atoms whose first n_centres (species-sorted) are owned and the rest are ghosts:
+        energy 0.5*sum over the owned atoms, forces [nall,3] for all.  type_map: int32 [nall] on the device.
+        howmany/with_ (int32 device tensors [n_centres], [n_centres, nr]): caller-built, distance-sorted rows
+        taken without any periodic wrap; otherwise the list is built with the minimum image of box[6]."""
+        pos_all = self._dev(pos_all)
+        box = None if box is None else self._dev(box)
+        nall = pos_all.numel() // 3
+        energy = torch.empty(1, dtype=self.dtype, device=self.device)
+        force = torch.empty(nall, 3, dtype=self.dtype, device=self.device)
+        vir = torch.empty(9, dtype=self.dtype, device=self.device) if virial else None
+        check(_lib.lib().stafb_energy_force_domain(self.ctx.h, self.h, self.ctx.stream(), _p(pos_all), _p(box), nall,
+                                                   _p(type_map), _p(howmany), _p(with_), _p(self.theta),
+                                                   _p(self.emb), _p(energy), _p(force), _p(vir)),
+              "stafb_energy_force_domain")
+        if check_status:
+            self.ctx.raise_on_status("stafb_energy_force_domain")
+        return (energy, force, vir) if virial else (energy, force)
 
     def loss_and_grad(self, pos, box, e_label, f_label, want_outputs=False):
         """One training evaluation on device tensors: fills self.losses (loss, loss_e, loss_bound, loss_f)

@@ -159,3 +159,50 @@ def load_model_dir(model_dir, dtype=np.float64):
         emb[o["emb"]:o["emb"] + nt * Fr] = e2[k].ravel()
         emb[o["emb"] + nt * Fr:o["emb"] + nt * Fr + C * Fa] = e3[k].ravel()
     return cfg, shape, theta.astype(dtype), emb.astype(dtype)
+
+
+def write_mlp_bin(path, mu, layers, precision=1):
+    """Writes the STAFMLP1 container read_mlp_bin reads (format of STAF/save_models/export_mlp_onnx.py:106-126
+    of the reference): layers = [(act, W[in,out], b[out])], act 1 = tanh, 0 = linear."""
+    dt = np.float64 if precision == 1 else np.float32
+    with open(path, "wb") as f:
+        f.write(b"STAFMLP1")
+        f.write(struct.pack("<3i", int(precision), len(mu), len(layers)))
+        f.write(np.asarray(mu, dt).tobytes())
+        for act, W, b in layers:
+            f.write(struct.pack("<3i", int(act), W.shape[0], W.shape[1]))
+            f.write(np.ascontiguousarray(W, dt).tobytes())
+            f.write(np.asarray(b, dt).tobytes())
+
+
+def save_model_dir(model_dir, cfg, shape, theta, emb, precision=1):
+    """Writes a model directory in the layout staf_load / load_model_dir read: staf_jmd.cfg, type.dat,
+    type{k}_alpha_{2body,3body,mu}.dat, type{k}_type_emb_{2b,3b}_sq.dat and mlp_type{k}.bin."""
+    os.makedirs(model_dir, exist_ok=True)
+    nt, C = shape.nt, shape.C
+    theta = np.asarray(theta, np.float64)
+    emb = np.asarray(emb, np.float64)
+    with open(os.path.join(model_dir, "staf_jmd.cfg"), "w") as f:
+        f.write("Buffer_radial_descriptors = %d\nBuffer_angular_descriptors = %d\n" % (cfg["nr"], cfg["na"]))
+        f.write("Cutoff = %r\nCutoff_Angular = %r\nHardcore_Cutoff = %r\n" % (cfg["Rc"], cfg["Ra"], cfg["Rs"]))
+        f.write("number_of_types = %d\nfile_of_tipos = type.dat\nnn_export_dir = .\n" % nt)
+    np.savetxt(os.path.join(model_dir, "type.dat"), np.asarray(shape.tipos, int).reshape(1, -1), fmt="%d")
+    for k in range(nt):
+        o = shape.offsets(k)
+        Fr, Fa = shape.Fr[k], shape.Fa[k]
+        sv = lambda name, a: np.savetxt(os.path.join(model_dir, "type%d_%s.dat" % (k, name)), a, fmt="%.17g")
+        sv("alpha_2body", theta[o["a2"]:o["a2"] + nt * Fr].reshape(nt, Fr))
+        sv("alpha_3body", theta[o["a3"]:o["a3"] + C * 3 * Fa].reshape(C, 3 * Fa))
+        mu = theta[o["mu"]:o["mu"] + Fr + Fa]
+        sv("alpha_mu", mu)
+        sv("type_emb_2b_sq", emb[o["emb"]:o["emb"] + nt * Fr].reshape(nt, Fr))
+        sv("type_emb_3b_sq", emb[o["emb"] + nt * Fr:o["emb"] + nt * Fr + C * Fa].reshape(C, Fa))
+        w, n_in, layers = o["w"], Fr + Fa, []
+        for li, width in enumerate(shape.widths):
+            W = theta[w:w + n_in * width].reshape(n_in, width)
+            w += n_in * width
+            b = theta[w:w + width]
+            w += width
+            layers.append((1 if li < len(shape.widths) - 1 else 0, W, b))
+            n_in = width
+        write_mlp_bin(os.path.join(model_dir, "mlp_type%d.bin" % k), mu, layers, precision)

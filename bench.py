@@ -367,6 +367,175 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+MD_METRIC = "24576-atom water E+F atom-steps/s (slab-decomposed inference)"
+
+
+def run_md(args):
+    """BASELINE configs[4]: energy+forces of one 24,576-atom water box, neighbour list rebuilt every call,
+    atoms cut into `world` slabs along z with one-cutoff halos (alphanesgpu_b200/slab.py)."""
+    import tempfile
+    import ctypes as C
+    import torch
+    import torch.distributed as dist
+    from alphanesgpu_b200 import params, synth, _lib
+    from alphanesgpu_b200.model import StafModel
+    from alphanesgpu_b200.params import ModelShape
+    from alphanesgpu_b200.slab import SlabDomain, model_compute
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    K, W = args.steps, max(args.warmup, 3)
+    pos, box, tipos = synth.water_frames("water24576", [1400])
+    gshape = synth.baseline_shape(tipos)
+    theta, emb = synth.init_params(gshape, dtype=np.float32)
+    N = gshape.N
+    types = gshape.type_map.astype(np.int32)
+    gpos = torch.as_tensor(pos.reshape(N, 3).astype(np.float32)).to(dev)
+    gtypes = torch.as_tensor(types).to(dev)
+    SKIN, HALO_EVERY = 1.0, 10  # ghost sets are re-chosen every 10 evaluations with a 1 A skin, as an MD code does
+    dom = SlabDomain(None, box[0], CFG["Rc"], rank, world, nt=gshape.nt, skin=SKIN, halo_every=HALO_EVERY)
+    own_idx = dom.set_owned_from_global(gpos, gtypes)
+    n_own = dom.pos.shape[0]
+    halo = 0 if world == 1 else 2.0 * dom.reach / (dom.L / world)
+    cap = int(n_own * (1.0 + halo) * 1.25) + 1024
+    shape = ModelShape(nt=gshape.nt, tipos=list(dom.counts), Fr=gshape.Fr, Fa=gshape.Fa, widths=gshape.widths)
+    model = StafModel(shape, CFG, theta, emb, 1, dtype=torch.float32, device=dev, n_max=cap)
+    dom.compute = model_compute(model, box[0])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        e, f = dom.step()
+    dd_err = None
+    if world > 1:
+        # decomposition parity (the reference's test/test-lammps-dd-parity): every rank also evaluates the whole
+        # box on its own GPU once and compares its owned forces and the total energy
+        full = StafModel(gshape, CFG, theta, emb, 1, dtype=torch.float32, device=dev)
+        e_full, f_full = full.energy_force(gpos.reshape(1, -1), torch.as_tensor(box.astype(np.float32)).to(dev))
+        f_ref = f_full.reshape(N, 3)[own_idx]
+        err = torch.stack([(f - f_ref).abs().max() / f_full.abs().max(), ((e - e_full).abs() / e_full.abs()).max()])
+        dist.all_reduce(err, op=dist.ReduceOp.MAX)
+        dd_err = {"force_rel": float(err[0]), "energy_rel": float(err[1])}
+        full.close()
+        del full, e_full, f_full
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    sampler = ClockSampler(local)
+    ev0 = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+    ev1 = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+    barrier()
+    sampler.start()
+    for k in range(K):
+        flush.zero_()
+        ev0[k].record()
+        e, f = dom.step()
+        ev1[k].record()
+    barrier()
+    clocks = sampler.stop()
+    total_ms = float(sum(a.elapsed_time(b) for a, b in zip(ev0, ev1)))
+    launches = model.launches()
+    # end to end: owned positions start in (pinned) host memory and owned forces end there, every step
+    pin_x = dom.pos.cpu().pin_memory()
+    pin_f = torch.empty_like(pin_x)
+    lib = _lib.lib()
+    if world == 1:
+        # through the libstaf C API (host double arrays in and out), the call LAMMPS makes
+        class StafOptions(C.Structure):
+            _fields_ = [("mlp_backend", C.c_int), ("device_id", C.c_int), ("precision", C.c_int), ("reserved", C.c_int)]
+        tmp = tempfile.mkdtemp(prefix="stafb_md_")
+        params.save_model_dir(tmp, CFG, gshape, theta.astype(np.float64), emb.astype(np.float64))
+        lib.staf_load.restype = C.c_void_p
+        lib.staf_load.argtypes = [C.c_char_p, C.c_void_p]
+        lib.staf_compute.argtypes = [C.c_void_p, C.c_int, C.c_int] + [C.c_void_p] * 5 + [C.c_int] + [C.c_void_p] * 3
+        lib.staf_free.argtypes = [C.c_void_p]
+        opt = StafOptions(0, local, 0, 0)
+        h = lib.staf_load(tmp.encode(), C.byref(opt))
+        assert h
+        x64 = np.ascontiguousarray(pos[0], np.float64)
+        b64 = np.ascontiguousarray(box[0], np.float64)
+        f64 = np.zeros(3 * N)
+        e64 = C.c_double()
+        vir = np.zeros(6)
+
+        def e2e_step():
+            rc = lib.staf_compute(h, N, 0, x64.ctypes.data, b64.ctypes.data, types.ctypes.data, None, None, 0,
+                                  C.byref(e64), f64.ctypes.data, vir.ctypes.data)
+            assert rc == 0, rc
+        h2d, d2h = 4 * (3 * N + 6 + N), 4 * (3 * N + 1 + 9)
+    else:
+        def e2e_step():
+            dom.pos.copy_(pin_x, non_blocking=True)
+            e_, f_ = dom.step()
+            pin_f.copy_(f_, non_blocking=True)
+            torch.cuda.synchronize()
+        h2d, d2h = 4 * 3 * n_own, 4 * 3 * n_own
+    Ke = max(5, min(K, 100))
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(Ke):
+        e2e_step()
+    barrier()
+    t = torch.tensor([total_ms, (time.perf_counter() - t0) * 1e3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = float(t[0]), float(t[1])
+    if world == 1:
+        e_check = float(e64.value)
+        assert abs(e_check - float(e)) <= 1e-4 * abs(float(e)), (e_check, float(e))
+        lib.staf_free(h)
+    # phases of one evaluation on this rank
+    model.set_phase_timing(True)
+    acc = {}
+    for k in range(5):
+        flush.zero_()
+        dom.step()
+        for name, ms in model.phase_times_ms().items():
+            acc[name] = acc.get(name, 0.0) + ms / 5
+    model.set_phase_timing(False)
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import oracle
+            t0 = time.perf_counter()
+            r = oracle.energy_force_grad(CFG, gshape.desc(), pos, box, gshape.type_map, theta, emb, np.float32,
+                                         per_atom_energy=False)
+            dt = time.perf_counter() - t0
+            assert r["status"] == 0
+            assert abs(float(r["energy"][0]) - float(e)) <= 2e-5 * abs(float(e)), (r["energy"], float(e))
+            cpu = {"value": N / dt, "unit": "atom-steps/s", "cores": oracle.max_threads(), "kind": "port",
+                   "sample": "1 evaluation of the 24576-atom box (%.1f s); energy agrees with the GPU" % dt}
+        line = {
+            "metric": MD_METRIC, "value": N * K / (total_ms * 1e-3), "unit": "atom-steps/s", "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "water24576 energy+forces, list rebuilt every call, fp32 (BASELINE configs[4])",
+                       "decomposition": "%d z-slab(s), %.1f A halos (cutoff + %.1f A skin, ghost sets re-chosen every "
+                                        "%d evaluations), owned atoms on rank 0: %d" % (world, dom.reach, SKIN,
+                                                                                         HALO_EVERY, n_own),
+                       "l2": "flushed between steps (256 MiB write); per-step CUDA events summed",
+                       "model": "2 species, Fr=10, Fa=15, MLP 25-64-32-1 tanh"},
+            "e2e": {"value": N * Ke / (e2e_ms * 1e-3), "unit": "atom-steps/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "steps": Ke,
+                    "path": "staf_compute (libstaf C API, host double arrays)" if world == 1 else
+                            "slab driver: pinned host -> device, halo exchange, forces -> pinned host"},
+            "gpu_launches": launches * K, "launches_per_step": launches, "clocks": clocks, "phase_ms": acc,
+            "energy": float(e), "dd_parity": dd_err, "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    model.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -375,9 +544,15 @@ def main():
     ap.add_argument("--batch", type=int, default=4)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="train", choices=["train", "md"],
+                    help="train: BASELINE configs[1]/[3] (the headline metric); md: BASELINE configs[4]")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "md":
+        if args.steps == 2000:
+            args.steps = 50
+        run_md(args)
     else:
         run_ours(args)
 

@@ -193,3 +193,15 @@ def test_status_codes(oracle):
     bad = box[0].copy()
     bad[3] = 0.0
     assert oracle.neighbour_list(4.5, 60, pos[0], bad, np.float64)["status"] == 4
+
+
+def test_model_dir_writer_round_trips(tmp_path):
+    """save_model_dir writes what load_model_dir (and staf_load) read."""
+    from alphanesgpu_b200 import params, synth
+    shape = synth.baseline_shape([5, 10])
+    theta, emb = synth.init_params(shape)
+    params.save_model_dir(str(tmp_path), CFG, shape, theta, emb)
+    cfg2, shape2, theta2, emb2 = params.load_model_dir(str(tmp_path))
+    assert cfg2 == CFG and shape2.tipos == [5, 10] and shape2.widths == shape.widths
+    assert shape2.Fr == shape.Fr and shape2.Fa == shape.Fa
+    assert np.array_equal(theta2, theta) and np.array_equal(emb2, emb)
