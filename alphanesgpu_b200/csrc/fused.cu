@@ -29,6 +29,17 @@ constexpr int MAXCH = 8;     // channels processed per pair sweep
 // warps per central atom (= per block) in the sweep kernels: the ordered force loop is long enough to
 // profit from two warps; the unordered sweeps run fastest with one
 template <int MODE> struct SweepWpa { static constexpr int value = (MODE == 1) ? 2 : 1; };
+// Resident blocks per SM the sweep kernels are compiled for (caps the registers per thread: 65536 / (threads *
+// blocks)).  Without the cap the register allocation of one mode moves by +-30 % with unrelated edits, and the
+// sweeps are occupancy-sensitive: a step's 3072 one-warp blocks fit the 148 SMs in one wave at <= 96 registers.
+template <int MODE, size_t ES> struct SweepMinBlocks { static constexpr int value = 28; };  // <= 73 registers
+template <> struct SweepMinBlocks<1, 4> { static constexpr int value = 12; };  // force, 64 threads: <= 85
+template <> struct SweepMinBlocks<2, 4> { static constexpr int value = 21; };  // force backward: <= 97
+template <> struct SweepMinBlocks<0, 8> { static constexpr int value = 21; };  // fp64: <= 97
+template <> struct SweepMinBlocks<1, 8> { static constexpr int value = 6; };   // <= 170
+template <> struct SweepMinBlocks<2, 8> { static constexpr int value = 13; };  // <= 157
+template <> struct SweepMinBlocks<3, 8> { static constexpr int value = 17; };  // <= 120
+template <> struct SweepMinBlocks<4, 8> { static constexpr int value = 17; };
 constexpr int ML_THREADS = 256;
 
 // exponential with a pre-scaled argument: fp32 uses 2^x (MUFU.EX2), fp64 the full-precision exp
@@ -41,6 +52,24 @@ template <> struct Ex<double> {
   static __host__ __device__ __forceinline__ double scale() { return 1.0; }
   static __device__ __forceinline__ double f(double x) { return exp(x); }
 };
+
+// Optional in-kernel phase clocks of the sweep kernels (build with -DSTAFB_SWEEP_CLOCKS): lane 0 of every warp
+// adds the clock64() ticks it spent in each phase to g_sweep_clk[mode][phase]; stafb_sweep_clocks() reads and
+// clears the table.  Phases: 0 staging, 1 species lists + cotangent staging, 2 radial part, 3 channel
+// parameters + exponential tables, 4 pair loop, 5 reductions, 6 write-back.
+#ifdef STAFB_SWEEP_CLOCKS
+__device__ unsigned long long g_sweep_clk[5][8];
+#define SWEEP_CLK_INIT long long clk_t0__ = clock64();
+#define SWEEP_TICK(p)                                                                       \
+  {                                                                                         \
+    const long long now__ = clock64();                                                      \
+    if ((threadIdx.x & 31) == 0) atomicAdd(&g_sweep_clk[MODE][p], (unsigned long long)(now__ - clk_t0__)); \
+    clk_t0__ = now__;                                                                       \
+  }
+#else
+#define SWEEP_CLK_INIT
+#define SWEEP_TICK(p)
+#endif
 
 struct ModelDev {
   int nt, C, N, ncls;
@@ -118,11 +147,11 @@ static inline int species_blocks(const ModelDev& md, int nf, int W) {
 
 // per-warp shared memory layout of the sweep kernels (offsets in bytes)
 struct SweepLayout {
-  int p0, p1, tab, chpa, chpb, xtra, acc, red, ids, cnts, tj, lst, actl, total;
+  int p0, p1, tab, chpa, chpb, pall, pball, xtra, acc, red, rsum, ids, cnts, tj, lst, actl, eflag, total;
 };
 
 template <class T>
-static inline SweepLayout sweep_layout(int nr, int nt, int xt, int nacc, int famax, int wpa) {
+static inline SweepLayout sweep_layout(int nr, int nt, int xt, int nacc, int famax, int wpa, int nrs, int ncf) {
   SweepLayout L;
   int o = 0;
   auto take = [&](int bytes) { int r = o; o += (bytes + 15) & ~15; return r; };
@@ -131,14 +160,18 @@ static inline SweepLayout sweep_layout(int nr, int nt, int xt, int nacc, int fam
   L.tab = take(MAXCH * nr * 2 * sizeof(T));
   L.chpa = take(MAXCH * 4 * sizeof(T));
   L.chpb = take(MAXCH * 2 * sizeof(T));
+  L.pall = take(ncf * 4 * sizeof(T));
+  L.pball = take(ncf * 2 * sizeof(T));
   L.xtra = take(nr * xt * sizeof(T));
   L.acc = take(nacc * sizeof(T));
   L.red = take(wpa * 4 * MAXCH * sizeof(T));
+  L.rsum = take(nrs * sizeof(T));
   L.ids = take(nr * sizeof(int));
-  L.cnts = take(STAFB_MAX_TYPES * sizeof(int));
+  L.cnts = take(2 * STAFB_MAX_TYPES * sizeof(int));
   L.tj = take(nr);
   L.lst = take(nt * nr);
   L.actl = take(famax);
+  L.eflag = take(ncf);
   L.total = o;
   return L;
 }
@@ -163,14 +196,39 @@ struct PairStep {
   }
 };
 
+// Sums NV per-lane values over the 32 lanes of a warp.  Every step halves the number of values a lane
+// still carries (lanes with the step's bit set keep the upper half and hand over the lower one), so
+// NV-1 shuffles replace 5*NV; once one value is left the remaining steps are a plain butterfly.
+// On return lane L holds the total of value index L >> log2(32 / NV).  NV is a power of two <= 32.
+template <class T, int NV>
+__device__ __forceinline__ T multi_reduce(T (&v)[NV], int lane) {
+  static_assert(NV == 1 || NV == 2 || NV == 4 || NV == 8 || NV == 16 || NV == 32, "NV must be a power of two");
+  int off = 16;
+#pragma unroll
+  for (int half = NV / 2; half >= 1; half >>= 1) {
+    const bool up = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < half; i++) {
+      const T keep = up ? v[i + half] : v[i];
+      const T send = up ? v[i] : v[i + half];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+    }
+    off >>= 1;
+  }
+  T r = v[0];
+  for (; off >= 1; off >>= 1) r += __shfl_xor_sync(0xffffffffu, r, off);
+  return r;
+}
+
 template <int WPA>
 __device__ __forceinline__ void gsync() {
   if (WPA == 1) __syncwarp(); else __syncthreads();
 }
 
-// One block of WPA warps per central atom.
-template <class T, int MODE, int WPA>
-__global__ void __launch_bounds__(WPA * 32)
+// One block of WPA warps per central atom.  VIR (force mode only) adds the virial; it is a template
+// parameter so that the training step's force sweep does not carry its registers.
+template <class T, int MODE, int WPA, bool VIR>
+__global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::value)
     k_sweep(ModelDev md, SweepIn<T> in, SweepLayout L, const T* __restrict__ theta, const T* __restrict__ emb,
             const T* __restrict__ chan_in,  // FORCE/FGRAD: netderiv[nf,N,Fmax]; AFGRAD: dL/dAF[nf,N,Fmax]
             const T* __restrict__ fbar,     // FGRAD: dL/dF[nf,3N]
@@ -193,14 +251,18 @@ __global__ void __launch_bounds__(WPA * 32)
   T2* tab = reinterpret_cast<T2*>(base + L.tab);
   T4* chpa = reinterpret_cast<T4*>(base + L.chpa);  // alpha1, alpha2, beta, beta*scale
   T2* chpb = reinterpret_cast<T2*>(base + L.chpb);  // mode-dependent coefficient, netderiv
+  T4* pall = reinterpret_cast<T4*>(base + L.pall);  // the same two for every (class, channel), fetched once
+  T2* pball = reinterpret_cast<T2*>(base + L.pball);
   T* xtra = reinterpret_cast<T*>(base + L.xtra);
   T* acc = reinterpret_cast<T*>(base + L.acc);
   T* red = reinterpret_cast<T*>(base + L.red);      // [WPA][4*MAXCH] per-warp partial sums
+  T* rsum = reinterpret_cast<T*>(base + L.rsum);    // [nt][Frmax] radial partial sums per neighbour species
   int* ids = reinterpret_cast<int*>(base + L.ids);
   int* cnts = reinterpret_cast<int*>(base + L.cnts);
   unsigned char* tj = base + L.tj;
   unsigned char* lst = base + L.lst;
   unsigned char* actl = base + L.actl;
+  unsigned char* eflag = base + L.eflag;  // [ncls][Fa] squared embedding != 0
 
   const int N = md.N, nr = in.nr, nt = md.nt;
   const int Fr = md.Fr[t], Fa = md.Fa[t], Fmax = md.Fmax;
@@ -217,6 +279,7 @@ __global__ void __launch_bounds__(WPA * 32)
   const int ACC_A3 = ACC_A2 + nt * md.Frmax; // [C*3*Famax] dL/dalpha3b
   const int NACC = ACC_A3 + md.C * 3 * md.Famax;
 
+  SWEEP_CLK_INIT
   int n = in.im2[gi * (nr + 1)];
   if (n > nr) n = nr;
   int m = in.ntr[gi];
@@ -234,26 +297,46 @@ __global__ void __launch_bounds__(WPA * 32)
     ids[k] = id;
     tj[k] = (unsigned char)(in.tmap ? in.tmap[id] : md.type_of(id));
   }
+  // angular parameters of every (class, channel), fetched while the neighbour row is still in flight
+  for (int idx = tid; idx < md.ncls * Fa; idx += NT) {
+    const int c = idx % Fa;
+    const T ee = e3[idx];
+    const T* al = a3 + idx * 3;
+    T4 pa;
+    pa.x = al[0]; pa.y = al[1]; pa.z = al[2]; pa.w = al[2] * SC;
+    T2 pb;
+    pb.x = T(0); pb.y = T(0);
+    if (IS_AF) pb.x = T(0.5) * ee;
+    if (MODE == MODE_FORCE) pb.x = T(0.25) * chrow[Fr + c] * ee;
+    if (MODE == MODE_FGRAD) { pb.x = T(0.5) * ee; pb.y = chrow[Fr + c]; }
+    if (MODE == MODE_AFGRAD) pb.x = T(0.5) * chrow[Fr + c] * ee;
+    pall[idx] = pa;
+    pball[idx] = pb;
+    eflag[idx] = ee != T(0);
+  }
   if (MODE != MODE_FORCE)
     for (int q = tid; q < NACC; q += NT) acc[q] = T(0);
   if (MODE == MODE_FORCE)
     for (int q = tid; q < 3 * nr; q += NT) xtra[q] = T(0);
   gsync<WPA>();
-  // per-species lists of the angular neighbours (first m sorted entries), built by warp 0
+  SWEEP_TICK(0)
+  // per-species lists of the neighbours in sorted order, built by warp 0; the angular neighbours (the
+  // first m of the row) are a prefix of every list
   const unsigned lt = (1u << lane) - 1u;
   if (warp == 0) {
 #pragma unroll
     for (int t2 = 0; t2 < STAFB_MAX_TYPES; t2++) {
       if (t2 < nt) {
-        int c2 = 0;
-        for (int k0 = 0; k0 < m; k0 += 32) {
+        int c2 = 0, ca = 0;
+        for (int k0 = 0; k0 < n; k0 += 32) {
           const int k = k0 + lane;
-          const bool p = (k < m) && (tj[k] == t2);
+          const bool p = (k < n) && (tj[k] == t2);
           const unsigned bal = __ballot_sync(0xffffffffu, p);
           if (p) lst[t2 * nr + c2 + __popc(bal & lt)] = (unsigned char)k;
           c2 += __popc(bal);
+          ca += __popc(__ballot_sync(0xffffffffu, p && k < m));
         }
-        if (lane == 0) cnts[t2] = c2;
+        if (lane == 0) { cnts[t2] = ca; cnts[STAFB_MAX_TYPES + t2] = c2; }
       }
     }
   }
@@ -274,20 +357,9 @@ __global__ void __launch_bounds__(WPA * 32)
 #pragma unroll
   for (int t2 = 0; t2 < STAFB_MAX_TYPES; t2++) cnt[t2] = (t2 < nt) ? cnts[t2] : 0;
 
+  SWEEP_TICK(1)
   // ------------------------------------------------------------------ radial part
-  // channels are dealt round-robin to the warps, so no cross-warp reduction is needed
-  if (MODE == MODE_AF) {
-    for (int c = warp; c < Fr; c += WPA) {
-      T s = T(0);
-      for (int k = lane; k < n; k += 32) {
-        const T ch = e2[Fr * tj[k] + c];
-        const T dk = P1[k].z;
-        if (ch != T(0)) s += dk * (Ex<T>::f(a2[Fr * tj[k] + c] * SC * dk) * ch);
-      }
-      s = warp_sum(s);
-      if (lane == 0) out[gi * Fmax + c] = s;
-    }
-  } else if (MODE == MODE_FORCE) {
+  if (MODE == MODE_FORCE) {
     for (int k = tid; k < n; k += NT) {
       const int tk = tj[k];
       const T dk = P1[k].z;
@@ -305,46 +377,54 @@ __global__ void __launch_bounds__(WPA * 32)
       atomicAdd(&xtra[k * 3 + 2], gz);
       fix -= gx; fiy -= gy; fiz -= gz;
     }
-  } else {  // FGRAD / AFGRAD / AFV: alpha2b terms (plus gradnet for FGRAD, fingerprints for AFV)
-    for (int c = warp; c < Fr; c += WPA) {
-      const T cin = (MODE == MODE_AFV) ? T(1) : chrow[c];  // FGRAD: netderiv ; AFGRAD: dL/dAF
-      T gn = T(0);
-      T ga[STAFB_MAX_TYPES];
-#pragma unroll
-      for (int q = 0; q < STAFB_MAX_TYPES; q++) ga[q] = T(0);
-      for (int k = lane; k < n; k += 32) {
-        const int tk = tj[k];
-        const T ch = e2[Fr * tk + c];
-        if (ch == T(0)) continue;
-        const T al = a2[Fr * tk + c], dk = P1[k].z;
-        const T ex = Ex<T>::f(al * SC * dk);
-        T va;
-        if (MODE == MODE_FGRAD) {
-          const T q = T(0.5) * P1[k].w * xtra[k * 4 + 3];
-          gn += q * ch * ex * (T(1) + al * dk);
-          va = q * cin * ch * ex * dk * (T(2) + al * dk);
-        } else {
-          va = cin * ch * ex * dk * dk;
-          if (MODE == MODE_AFV) gn += dk * ex * ch;
+  } else {
+    // AF / AFV / FGRAD / AFGRAD: one thread per (neighbour species q, channel c) walks the neighbour row,
+    // so the sums over neighbours need no cross-lane reduction; the per-species partial sums of a channel
+    // are combined through rsum[].  AF, AFV: fingerprints; FGRAD: gradnet; all but AF: alpha2b terms.
+    const int nqc = nt * Fr;
+    for (int L0 = 0; L0 < nqc; L0 += NT) {
+      const int Lq = L0 + tid;
+      if (Lq < nqc) {
+        const int q = Lq / Fr, c = Lq - q * Fr;
+        const T ch = e2[Lq];
+        T gn = T(0), ga = T(0);
+        if (ch != T(0)) {
+          const T al = a2[Lq], als = al * SC;
+          const T cin = (IS_AF) ? T(1) : chrow[c];  // FGRAD: netderiv ; AFGRAD: dL/dAF
+          const unsigned char* lq = lst + q * nr;
+          const int nq = cnts[STAFB_MAX_TYPES + q];
+#pragma unroll 2
+          for (int r = 0; r < nq; r++) {
+            const int k = lq[r];
+            const T dk = P1[k].z;
+            const T ex = Ex<T>::f(als * dk);
+            if (MODE == MODE_FGRAD) {
+              const T qq = T(0.5) * P1[k].w * xtra[k * 4 + 3];
+              gn += qq * ex * (T(1) + al * dk);
+              ga += qq * ex * dk * (T(2) + al * dk);
+            } else {
+              gn += dk * ex;
+              ga += ex * dk * dk;
+            }
+          }
+          gn *= ch;
+          ga *= cin * ch;
         }
-#pragma unroll
-        for (int q = 0; q < STAFB_MAX_TYPES; q++)
-          if (q == tk) ga[q] += va;
+        rsum[q * md.Frmax + c] = gn;
+        if (MODE != MODE_AF) acc[ACC_A2 + q * md.Frmax + c] = ga;
       }
-      if (MODE == MODE_FGRAD || MODE == MODE_AFV) {
-        gn = warp_sum(gn);
-        if (lane == 0) out[gi * Fmax + c] = gn;
-      }
-#pragma unroll
-      for (int q = 0; q < STAFB_MAX_TYPES; q++) {
-        if (q < nt) {
-          const T s = warp_sum(ga[q]);
-          if (lane == 0) acc[ACC_A2 + q * md.Frmax + c] += s;
-        }
+    }
+    if (MODE != MODE_AFGRAD) {
+      gsync<WPA>();
+      for (int c = tid; c < Fr; c += NT) {
+        T v = T(0);
+        for (int q = 0; q < nt; q++) v += rsum[q * md.Frmax + c];
+        out[gi * Fmax + c] = v;
       }
     }
   }
 
+  SWEEP_TICK(2)
   // ------------------------------------------------------------------ angular part
   for (int ta = 0; ta < nt; ta++) {
     for (int tb = ta; tb < nt; tb++) {
@@ -364,7 +444,7 @@ __global__ void __launch_bounds__(WPA * 32)
       int nact = 0;
       for (int c0 = 0; c0 < Fa; c0 += 32) {
         const int c = c0 + lane;
-        const bool p = (c < Fa) && (e3[s * Fa + c] != T(0));
+        const bool p = (c < Fa) && eflag[s * Fa + c];
         const unsigned bal = __ballot_sync(0xffffffffu, p);
         if (p && warp == 0) actl[nact + __popc(bal & lt)] = (unsigned char)c;
         nact += __popc(bal);
@@ -374,34 +454,29 @@ __global__ void __launch_bounds__(WPA * 32)
         gsync<WPA>();  // actl visible; previous chunk's readers of chp/tab/red are done
         if (tid < nch) {
           const int c = actl[c0 + tid];
-          const T* al = a3 + (s * Fa + c) * 3;
-          const T ee = e3[s * Fa + c];
-          T4 pa;
-          pa.x = al[0]; pa.y = al[1]; pa.z = al[2]; pa.w = al[2] * SC;
-          chpa[tid] = pa;
-          T2 pb;
-          pb.x = T(0); pb.y = T(0);
-          if (IS_AF) pb.x = T(0.5) * ee;
-          if (MODE == MODE_FORCE) pb.x = T(0.25) * chrow[Fr + c] * ee;
-          if (MODE == MODE_FGRAD) { pb.x = T(0.5) * ee; pb.y = chrow[Fr + c]; }
-          if (MODE == MODE_AFGRAD) pb.x = T(0.5) * chrow[Fr + c] * ee;
-          chpb[tid] = pb;
+          chpa[tid] = pall[s * Fa + c];
+          chpb[tid] = pball[s * Fa + c];
         }
         gsync<WPA>();
         // tables exp(a1*fc_k), exp(a2*fc_k) for the neighbours of the two species
         const int nu = same ? na_ : na_ + nb_;
-        for (int l = 0; l < nch; l++) {
-          const T a1s = chpa[l].x * SC, a2s = chpa[l].y * SC;
-          for (int r = tid; r < nu; r += NT) {
-            const int k = (r < na_) ? la[r] : lb[r - na_];
-            const T fck = P0[k].w;
-            T2 v;
-            v.x = Ex<T>::f(a1s * fck);
-            v.y = Ex<T>::f(a2s * fck);
-            tab[l * nr + k] = v;
+        for (int r = tid; r < nu; r += NT) {
+          const int k = (r < na_) ? la[r] : lb[r - na_];
+          const T fck = P0[k].w * SC;
+          // all channels of one neighbour in flight together: independent multiply -> exp2 -> store chains
+#pragma unroll
+          for (int l = 0; l < MAXCH; l++) {
+            if (l < nch) {
+              const T4 pa = chpa[l];
+              T2 v;
+              v.x = Ex<T>::f(pa.x * fck);
+              v.y = Ex<T>::f(pa.y * fck);
+              tab[l * nr + k] = v;
+            }
           }
         }
         gsync<WPA>();
+        SWEEP_TICK(3)
 
         if (MODE == MODE_FORCE) {
           // ordered pairs (owner j, partner k): each thread takes a contiguous run of the row-major
@@ -540,23 +615,28 @@ __global__ void __launch_bounds__(WPA * 32)
               }
             }
           }
+          SWEEP_TICK(4)
           // per-warp sums -> red[warp][4*l + v]; then one thread per value combines the warps
+          // transposing butterfly: 4*MAXCH (or fewer) per-lane values are summed over the warp with one
+          // shuffle per surviving value and step instead of five per value
+          if (MODE == MODE_AF) {
+            T v[MAXCH];
 #pragma unroll
-          for (int l = 0; l < MAXCH; l++) {
-            if (l < nch) {
-              if (IS_AF || MODE == MODE_FGRAD) {
-                const T v = warp_sum(r0[l]);
-                if (lane == 0) red[warp * 4 * MAXCH + 4 * l + 0] = v;
-              }
-              if (HAS_V || MODE == MODE_FGRAD) {
-                const T v1 = warp_sum(r1[l]), v2 = warp_sum(r2[l]), v3 = warp_sum(r3[l]);
-                if (lane == 0) {
-                  red[warp * 4 * MAXCH + 4 * l + 1] = v1;
-                  red[warp * 4 * MAXCH + 4 * l + 2] = v2;
-                  red[warp * 4 * MAXCH + 4 * l + 3] = v3;
-                }
-              }
-            }
+            for (int l = 0; l < MAXCH; l++) v[l] = r0[l];
+            const T tot = multi_reduce<T, MAXCH>(v, lane);  // lane holds channel lane >> 2
+            if ((lane & 3) == 0) red[warp * 4 * MAXCH + 4 * (lane >> 2)] = tot;
+          } else if (nch <= MAXCH / 2) {
+            T v[2 * MAXCH];
+#pragma unroll
+            for (int l = 0; l < MAXCH / 2; l++) { v[4 * l] = r0[l]; v[4 * l + 1] = r1[l]; v[4 * l + 2] = r2[l]; v[4 * l + 3] = r3[l]; }
+            const T tot = multi_reduce<T, 2 * MAXCH>(v, lane);  // lane holds value lane >> 1
+            if ((lane & 1) == 0) red[warp * 4 * MAXCH + (lane >> 1)] = tot;
+          } else {
+            T v[4 * MAXCH];
+#pragma unroll
+            for (int l = 0; l < MAXCH; l++) { v[4 * l] = r0[l]; v[4 * l + 1] = r1[l]; v[4 * l + 2] = r2[l]; v[4 * l + 3] = r3[l]; }
+            const T tot = multi_reduce<T, 4 * MAXCH>(v, lane);  // lane holds value lane
+            red[warp * 4 * MAXCH + lane] = tot;
           }
           gsync<WPA>();
           if (tid < 4 * nch) {
@@ -576,11 +656,13 @@ __global__ void __launch_bounds__(WPA * 32)
             }
           }
         }
+        SWEEP_TICK(MODE == MODE_FORCE ? 4 : 5)
       }
       gsync<WPA>();  // before the next class rewrites actl
     }
   }
   gsync<WPA>();
+  SWEEP_TICK(5)
 
   // ------------------------------------------------------------------ write-back
   if (IS_AF) {
@@ -609,25 +691,24 @@ __global__ void __launch_bounds__(WPA * 32)
       atomicAdd(fb + (size_t)i * 3 + 1, fiy);
       atomicAdd(fb + (size_t)i * 3 + 2, fiz);
     }
-    if (vir) {
+    if (VIR) {
       // W_ab -= g_a * r_b with g the force this centre puts on neighbour k and r = r_i - r_k
       // (force/rad/reforce.cu.cc:174-287, force/ang/reforce.cu.cc:269-457 of the reference)
-      T w[9];
-#pragma unroll
-      for (int c = 0; c < 9; c++) w[c] = T(0);
-      for (int k = tid; k < n; k += NT) {
-        const T4 u = P0[k];
-        const T r = T(1) / P1[k].x;
-        const T rv[3] = {u.x * r, u.y * r, u.z * r};
-#pragma unroll
-        for (int a = 0; a < 3; a++)
-#pragma unroll
-          for (int c = 0; c < 3; c++) w[a * 3 + c] -= xtra[k * 3 + a] * rv[c];
-      }
-#pragma unroll
-      for (int c = 0; c < 9; c++) {
-        const T v = warp_sum(w[c]);
-        if (lane == 0 && v != T(0)) atomicAdd(vir + (size_t)b * 9 + c, (double)v);
+      // one row of W at a time keeps the epilogue's register footprint below the main loop's
+#pragma unroll 1
+      for (int a = 0; a < 3; a++) {
+        T w0 = T(0), w1 = T(0), w2 = T(0);
+        for (int k = tid; k < n; k += NT) {
+          const T4 u = P0[k];
+          const T g = xtra[k * 3 + a] / P1[k].x;  // g_a * |r|
+          w0 -= g * u.x; w1 -= g * u.y; w2 -= g * u.z;
+        }
+        w0 = warp_sum(w0); w1 = warp_sum(w1); w2 = warp_sum(w2);
+        if (lane == 0) {
+          atomicAdd(vir + (size_t)b * 9 + a * 3 + 0, (double)w0);
+          atomicAdd(vir + (size_t)b * 9 + a * 3 + 1, (double)w1);
+          atomicAdd(vir + (size_t)b * 9 + a * 3 + 2, (double)w2);
+        }
       }
     }
   } else {
@@ -635,7 +716,10 @@ __global__ void __launch_bounds__(WPA * 32)
       for (int c = tid; c < Fa; c += NT) out[gi * Fmax + Fr + c] = acc[ACC_GN + c];
       for (int c = Fr + Fa + tid; c < Fmax; c += NT) out[gi * Fmax + c] = T(0);
     }
-    if (grad == nullptr) return;
+    if (grad == nullptr) {
+      SWEEP_TICK(6)
+      return;
+    }
     T* g2 = grad + md.off_a2[t];
     for (int q = tid; q < nt * Fr; q += NT) {
       const T v = acc[ACC_A2 + (q / Fr) * md.Frmax + (q % Fr)];
@@ -648,7 +732,18 @@ __global__ void __launch_bounds__(WPA * 32)
       if (v != T(0)) atomicAdd(g3 + q, v);
     }
   }
+  SWEEP_TICK(6)
 }
+
+#ifdef STAFB_SWEEP_CLOCKS
+}  // namespace stafb
+extern "C" int stafb_sweep_clocks(unsigned long long* out40) {
+  if (cudaMemcpyFromSymbol(out40, stafb::g_sweep_clk, sizeof(unsigned long long) * 40) != cudaSuccess) return 1;
+  unsigned long long z[40] = {0};
+  return cudaMemcpyToSymbol(stafb::g_sweep_clk, z, sizeof(z)) == cudaSuccess ? 0 : 1;
+}
+namespace stafb {
+#endif
 
 // ---------------------------------------------------------------------------- MLP head
 // x = log(AF+1e-3) - mu ; Dense(tanh)... Dense(1)  (staf_models/staf_model.py:188-191,
@@ -1274,18 +1369,26 @@ static int launch_sweep(stafb_model* m, cudaStream_t s, int nf, const SweepIn<T>
   const int xt = MODE == MODE_FORCE ? 3 : (MODE == MODE_FGRAD ? 4 : 0);
   const int nacc = d.Famax + d.nt * d.Frmax + d.C * 3 * d.Famax;
   constexpr int SW_WPA = SweepWpa<MODE>::value;
-  SweepLayout L = sweep_layout<T>(in.nr, d.nt, xt, nacc, d.Famax > 0 ? d.Famax : 1, SW_WPA);
+  SweepLayout L = sweep_layout<T>(in.nr, d.nt, xt, nacc, d.Famax > 0 ? d.Famax : 1, SW_WPA,
+                                  d.nt * d.Frmax > 0 ? d.nt * d.Frmax : 1, d.ncls * d.Famax > 0 ? d.ncls * d.Famax : 1);
   const size_t sm = (size_t)L.total;
   if (sm > m->smem_limit) return STAFB_ERR_CAPACITY;
   static bool attr[2][5] = {{false}};
   if (sm > 48 * 1024 && !attr[sizeof(T) == 8][MODE]) {
-    STAFB_CUDA_OK(cudaFuncSetAttribute(k_sweep<T, MODE, SW_WPA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    STAFB_CUDA_OK(cudaFuncSetAttribute(k_sweep<T, MODE, SW_WPA, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)m->smem_limit));
+    if (MODE == MODE_FORCE)
+      STAFB_CUDA_OK(cudaFuncSetAttribute(k_sweep<T, MODE, SW_WPA, MODE == MODE_FORCE>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)m->smem_limit));
     attr[sizeof(T) == 8][MODE] = true;
   }
   const int blocks = nf * d.N;
-  static const bool noatom = getenv("STAFB_EXP_NOATOM") != nullptr;
-  k_sweep<T, MODE, SW_WPA><<<blocks, SW_WPA * 32, sm, s>>>(d, in, L, theta, emb, chan_in, fbar, out, noatom ? nullptr : grad, vout, nv, vir);
+  if (MODE == MODE_FORCE && vir)
+    k_sweep<T, MODE, SW_WPA, MODE == MODE_FORCE><<<blocks, SW_WPA * 32, sm, s>>>(d, in, L, theta, emb, chan_in, fbar,
+                                                                                out, grad, vout, nv, vir);
+  else
+    k_sweep<T, MODE, SW_WPA, false><<<blocks, SW_WPA * 32, sm, s>>>(d, in, L, theta, emb, chan_in, fbar, out, grad,
+                                                                   vout, nv, nullptr);
   m->ctx->launches++;
   return STAFB_OK;
 }

@@ -121,6 +121,99 @@ __global__ void k_gather_cells(const FrameGeom<T>* __restrict__ fg, int nf, int 
   }
 }
 
+// Small systems: frame geometry, fractional coordinates, cell of every atom, per-cell counts, their
+// exclusive scan and the members of every cell in ascending atom index - one block per frame, all
+// bookkeeping in shared memory (k_cells + k_scan + k_gather_cells in one launch, no counter memset).
+// Dynamic shared memory: (cell_cap + 1 + N) ints.
+template <class T>
+__global__ void __launch_bounds__(1024)
+    k_cell_lists_small(const T* __restrict__ pos, const T* __restrict__ box, int N, T cutoff, int cell_cap, int mpc,
+                       FrameGeom<T>* __restrict__ fg, T* __restrict__ frac, int* __restrict__ cell_of,
+                       int* __restrict__ cell_start, int* __restrict__ cells_sorted, int* __restrict__ status) {
+  extern __shared__ int sm_i[];
+  __shared__ FrameGeom<T> gs;
+  __shared__ int part[32];
+  __shared__ int carry;
+  int* cnt = sm_i;                  // [cell_cap + 1] counts, then exclusive starts
+  int* cof = sm_i + cell_cap + 1;   // [N] cell of every atom
+  const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5, nw = blockDim.x >> 5;
+  if (tid == 0) {
+    frame_geometry<T>(box + 6 * b, N, cutoff, cell_cap, gs, status);
+    fg[b] = gs;
+    carry = 0;
+  }
+  for (int c = tid; c <= cell_cap; c += blockDim.x) cnt[c] = 0;
+  __syncthreads();
+  const FrameGeom<T>& g = gs;
+  for (int i = tid; i < N; i += blockDim.x) {
+    const size_t t = (size_t)b * N + i;
+    T px = pos[t * 3 + 0], py = pos[t * 3 + 1], pz = pos[t * 3 + 2];
+    T fx = (g.inv[0] * px + g.inv[1] * py + g.inv[2] * pz);
+    T fy = (g.inv[3] * py + g.inv[4] * pz);
+    T fz = (g.inv[5] * pz);
+    frac[t * 3 + 0] = fx;
+    frac[t * 3 + 1] = fy;
+    frac[t * 3 + 2] = fz;
+    int cx = (int)r_floor(fx / g.sx);
+    cx = cx % g.nx;
+    if (cx < 0) cx += g.nx;
+    int cy = (int)r_floor(fy / g.sy);
+    cy = cy % g.ny;
+    if (cy < 0) cy += g.ny;
+    int cz = (int)r_floor(fz / g.sz);
+    cz = cz % g.nz;
+    if (cz < 0) cz += g.nz;
+    const int c = cx + cy * g.nx + cz * (g.nx * g.ny);
+    cell_of[t] = c;
+    cof[i] = c;
+    atomicAdd(&cnt[c], 1);
+  }
+  __syncthreads();
+  const int ncell = g.ncell;
+  int* st = cell_start + (size_t)b * (cell_cap + 1);
+  for (int base = 0; base < ncell; base += blockDim.x) {
+    const int c = base + tid;
+    const int v = (c < ncell) ? cnt[c] : 0;
+    if (v > mpc) set_status(status, STAFB_ERR_CELL_OVERFLOW);
+    int x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) part[w] = x;
+    __syncthreads();
+    int off = carry;
+    for (int q = 0; q < w; q++) off += part[q];
+    if (c < ncell) {
+      cnt[c] = off + x - v;
+      st[c] = off + x - v;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int tot = 0;
+      for (int q = 0; q < nw; q++) tot += part[q];
+      carry += tot;
+    }
+    __syncthreads();
+  }
+  if (tid == 0) st[ncell] = carry;
+  // members in ascending atom index: one warp per cell walks the frame's atoms 32 at a time
+  const unsigned lt = (1u << lane) - 1u;
+  int* dstb = cells_sorted + (size_t)b * N;
+  for (int c = w; c < ncell; c += nw) {
+    int* dst = dstb + cnt[c];
+    int k = 0;
+    for (int j0 = 0; j0 < N; j0 += 32) {
+      const int j = j0 + lane;
+      const bool p = (j < N) && (cof[j] == c);
+      const unsigned bal = __ballot_sync(0xffffffffu, p);
+      if (p) dst[k + __popc(bal & lt)] = j;
+      k += __popc(bal);
+    }
+  }
+}
+
 // Exclusive scan of the per-cell counts of one frame (one block per frame).
 template <class T>
 __global__ void k_scan(const FrameGeom<T>* __restrict__ fg, const int* __restrict__ cell_count,
@@ -532,21 +625,28 @@ int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box,
   CoreCoef<T> cc;
   cc.Rc = (T)c->Rc; cc.Rs = (T)c->Rs; cc.Ra = (T)c->Ra;
   cc.A = (T)c->coef[0]; cc.B = (T)c->coef[1]; cc.C = (T)c->coef[2]; cc.pa = (T)c->coef[3]; cc.pb = (T)c->coef[4];
-  STAFB_CUDA_OK(cudaMemsetAsync(c->cell_count, 0, sizeof(int) * (size_t)nf * cap, s));
   const int tot = nf * N;
-  k_cells<T><<<dim3((N + 255) / 256, nf), 256, 0, s>>>(pos, box, nf, N, cc.Rc, cap, fg, frac, c->cell_of, c->cell_count,
-                                                       c->status_d);
-  k_scan<T><<<nf, 256, 0, s>>>(fg, c->cell_count, c->cell_start, c->cell_cursor, cap, mpc, c->status_d);
-  const long long warps = (long long)nf * cap;
-  if (N <= 4096) {
-    k_gather_cells<T><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(fg, nf, N, c->cell_of, c->cell_start,
-                                                                         c->cells_sorted, cap);
-    c->launches += 4;
+  const size_t small_sm = sizeof(int) * ((size_t)cap + 1 + N);
+  if (small_sm <= 48 * 1024 && N <= 2048) {
+    k_cell_lists_small<T><<<nf, 1024, small_sm, s>>>(pos, box, N, cc.Rc, cap, mpc, fg, frac, c->cell_of, c->cell_start,
+                                                    c->cells_sorted, c->status_d);
+    c->launches += 1;
   } else {
-    k_fill<<<(tot + 255) / 256, 256, 0, s>>>(nf, N, c->cell_of, c->cell_start, c->cell_cursor, c->cells_raw, cap);
-    k_sort_cells<T><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(fg, nf, N, c->cell_start, c->cells_raw,
-                                                                       c->cells_sorted, cap);
-    c->launches += 5;
+    STAFB_CUDA_OK(cudaMemsetAsync(c->cell_count, 0, sizeof(int) * (size_t)nf * cap, s));
+    k_cells<T><<<dim3((N + 255) / 256, nf), 256, 0, s>>>(pos, box, nf, N, cc.Rc, cap, fg, frac, c->cell_of, c->cell_count,
+                                                         c->status_d);
+    k_scan<T><<<nf, 256, 0, s>>>(fg, c->cell_count, c->cell_start, c->cell_cursor, cap, mpc, c->status_d);
+    const long long warps = (long long)nf * cap;
+    if (N <= 4096) {
+      k_gather_cells<T><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(fg, nf, N, c->cell_of, c->cell_start,
+                                                                           c->cells_sorted, cap);
+      c->launches += 4;
+    } else {
+      k_fill<<<(tot + 255) / 256, 256, 0, s>>>(nf, N, c->cell_of, c->cell_start, c->cell_cursor, c->cells_raw, cap);
+      k_sort_cells<T><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(fg, nf, N, c->cell_start, c->cells_raw,
+                                                                         c->cells_sorted, cap);
+      c->launches += 5;
+    }
   }
   {
     constexpr int W = 4;
