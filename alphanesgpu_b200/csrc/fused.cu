@@ -746,331 +746,16 @@ namespace stafb {
 #endif
 
 // ---------------------------------------------------------------------------- MLP head
-// x = log(AF+1e-3) - mu ; Dense(tanh)... Dense(1)  (staf_models/staf_model.py:188-191,
-// libstaf/src/mlp/staf_mlp_ort.cc:196-242).  A block of 256 threads owns TA = 8*APT atoms of one
-// species; activations live in shared memory feature-major ([feature][atom]) so that a thread holds
-// APT atoms in registers while it streams one weight column, coalesced, from global memory.
-
-// Stages one Dense layer (weights [in][out] row-major + bias[out]) into shared memory with a padded
-// row stride of out+1 words, all threads loading at once: the dot-product loops then never wait on
-// global memory, and both access patterns (lanes over j, lanes over i) are bank-conflict free.
-template <class T>
-struct LayerView {
-  const T* W;  // element (i,j) at W[i*ld + j]
-  const T* B;  // bias
-  int ld;
-};
-
-// When the layer does not fit next to the activations (stage == false) the view points at global memory.
-template <class T>
-__device__ __forceinline__ LayerView<T> stage_layer(int in, int out, const T* __restrict__ Wl, T* wsm, bool stage) {
-  __syncthreads();  // previous users of wsm are done, inputs of the layer are complete
-  LayerView<T> v;
-  if (!stage) {
-    v.W = Wl; v.B = Wl + in * out; v.ld = out;
-    return v;
-  }
-  const int ld = out + 1;
-  v.W = wsm; v.B = wsm + in * ld; v.ld = ld;
-  for (int idx = threadIdx.x; idx < in * out; idx += ML_THREADS) {
-    const int i = idx / out, j = idx - i * out;
-    wsm[i * ld + j] = Wl[idx];
-  }
-  for (int j = threadIdx.x; j < out; j += ML_THREADS) wsm[in * ld + j] = Wl[in * out + j];
-  __syncthreads();
-  return v;
+#include "mlp.cuh"
+#ifdef STAFB_SWEEP_CLOCKS
+}  // namespace stafb
+extern "C" int stafb_mlp_clocks(unsigned long long* out32) {
+  if (cudaMemcpyFromSymbol(out32, stafb::g_mlp_clk, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
+  unsigned long long z[32] = {0};
+  return cudaMemcpyToSymbol(stafb::g_mlp_clk, z, sizeof(z)) == cudaSuccess ? 0 : 1;
 }
-
-// Y[j][a] = act( b[j] + sum_i X[i][a] W[i,j] ), a in the thread's APT atoms, j over lanes
-template <class T, int APT, bool TANH, bool BIAS>
-__device__ __forceinline__ void dense_fwd(int in, int out, const LayerView<T> lv, const T* X, T* Y) {
-  constexpr int TA = 8 * APT;
-  const int jl = threadIdx.x & 31, ag = threadIdx.x >> 5, ld = lv.ld;
-  const T* wsm = lv.W;
-  for (int j0 = 0; j0 < out; j0 += 32) {
-    const int j = j0 + jl;
-    if (j < out) {
-      T a[APT];
-      const T bj = BIAS ? lv.B[j] : T(0);
-#pragma unroll
-      for (int q = 0; q < APT; q++) a[q] = bj;
-#pragma unroll 4
-      for (int i = 0; i < in; i++) {
-        const T w = wsm[i * ld + j];
-        const T* xp = X + i * TA + ag * APT;
-#pragma unroll
-        for (int q = 0; q < APT; q++) a[q] += xp[q] * w;
-      }
-#pragma unroll
-      for (int q = 0; q < APT; q++) Y[j * TA + ag * APT + q] = TANH ? r_tanh(a[q]) : a[q];
-    }
-  }
-}
-
-// Xo[i][a] = sum_j D[j][a] W[i,j]  (and the same for a second cotangent D2 -> Xo2 when given)
-template <class T, int APT>
-__device__ __forceinline__ void dense_bwd(int in, int out, const LayerView<T> lv, const T* D, T* Xo, const T* D2,
-                                          T* Xo2) {
-  constexpr int TA = 8 * APT;
-  const int il = threadIdx.x & 31, ag = threadIdx.x >> 5, ld = lv.ld;
-  const T* wsm = lv.W;
-  __syncthreads();
-  for (int i0 = 0; i0 < in; i0 += 32) {
-    const int i = i0 + il;
-    if (i < in) {
-      T a[APT], a2[APT];
-#pragma unroll
-      for (int q = 0; q < APT; q++) a[q] = a2[q] = T(0);
-#pragma unroll 4
-      for (int j = 0; j < out; j++) {
-        const T w = wsm[i * ld + j];
-        const T* dp = D + j * TA + ag * APT;
-#pragma unroll
-        for (int q = 0; q < APT; q++) a[q] += dp[q] * w;
-        if (D2) {
-          const T* dp2 = D2 + j * TA + ag * APT;
-#pragma unroll
-          for (int q = 0; q < APT; q++) a2[q] += dp2[q] * w;
-        }
-      }
-#pragma unroll
-      for (int q = 0; q < APT; q++) {
-        Xo[i * TA + ag * APT + q] = a[q];
-        if (D2) Xo2[i * TA + ag * APT + q] = a2[q];
-      }
-    }
-  }
-  __syncthreads();
-}
-
-template <class T, int APT>
-__global__ void __launch_bounds__(ML_THREADS)
-    k_mlp_fwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ af, T* __restrict__ acts,
-              T* __restrict__ e_atom, T* __restrict__ netderiv, int stage) {
-  constexpr int TA = 8 * APT;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  int t, q0;
-  locate_block(md, nf, TA, t, q0);
-  const int nat = nf * md.tipos[t];
-  const int F = md.Fr[t] + md.Fa[t], Lq = md.n_dense, Fm = md.Fmax, Hs = md.Hsum, mw = md.maxw;
-  T* X = reinterpret_cast<T*>(smem_raw);  // [Fm][TA]
-  T* H = X + Fm * TA;                     // [Hs][TA]
-  T* C0 = H + Hs * TA;                    // [mw][TA]
-  T* C1 = C0 + mw * TA;                   // [mw][TA]
-  T* wsm = C1 + mw * TA;                  // one staged layer: (in+1) x (out+1)
-  const T* mu = theta + md.off_mu[t];
-  const T* w = theta + md.off_w[t];
-  auto gidx = [&](int a) -> long long {
-    const int q = q0 + a;
-    if (q >= nat) return -1;
-    const int b = q / md.tipos[t];
-    return (long long)b * md.N + md.shift[t] + (q - b * md.tipos[t]);
-  };
-  for (int idx = threadIdx.x; idx < F * TA; idx += ML_THREADS) {
-    const int a = idx % TA, i = idx / TA;
-    const long long gi = gidx(a);
-    X[i * TA + a] = gi >= 0 ? r_log(af[gi * Fm + i] + T(1e-3)) - mu[i] : T(0);
-  }
-  const T* hin = X;
-  LayerView<T> lv;
-  for (int l = 0; l < Lq; l++) {
-    const int in = md.in_of(t, l), out = md.width[l];
-    lv = stage_layer(in, out, w + md.w_off(t, l), wsm, stage != 0);
-    T* hout = H + md.h_off(l) * TA;
-    if (l < Lq - 1) dense_fwd<T, APT, true, true>(in, out, lv, hin, hout);
-    else dense_fwd<T, APT, false, true>(in, out, lv, hin, hout);
-    hin = hout;
-  }
-  __syncthreads();
-  // activations, block-local feature-major copy for the backward kernel
-  T* ab = acts + (size_t)blockIdx.x * Hs * TA;
-  for (int idx = threadIdx.x; idx < Hs * TA; idx += ML_THREADS) ab[idx] = H[idx];
-  if (threadIdx.x < TA) {
-    const long long gi = gidx(threadIdx.x);
-    if (gi >= 0) e_atom[gi] = H[md.h_off(Lq - 1) * TA + threadIdx.x];
-  }
-  // de/dx by the reverse sweep: cn = cotangent on the output of layer l
-  T* cn = C0;
-  T* cp = C1;
-  if (threadIdx.x < TA) cn[threadIdx.x] = T(1);
-  for (int l = Lq - 1; l >= 0; l--) {
-    const int in = md.in_of(t, l), out = md.width[l];
-    if (l < Lq - 1) lv = stage_layer(in, out, w + md.w_off(t, l), wsm, stage != 0);  // the last layer is still staged
-    else __syncthreads();
-    if (l < Lq - 1) {
-      const T* hl = H + md.h_off(l) * TA;
-      for (int idx = threadIdx.x; idx < out * TA; idx += ML_THREADS) cn[idx] *= (T(1) - hl[idx] * hl[idx]);
-    }
-    dense_bwd<T, APT>(in, out, lv, cn, cp, nullptr, nullptr);
-    T* tmp = cn; cn = cp; cp = tmp;
-  }
-  for (int idx = threadIdx.x; idx < Fm * TA; idx += ML_THREADS) {
-    const int a = idx % TA, i = idx / TA;
-    const long long gi = gidx(a);
-    if (gi >= 0) netderiv[gi * Fm + i] = (i < F) ? cn[i * TA + a] / (af[gi * Fm + i] + T(1e-3)) : T(0);
-  }
-}
-
-// Backward of  S = sum_a ebar[a]*e[a] + sum_{a,c} u[a,c]*netderiv[a,c]  with respect to the
-// weights, mu and AF: the first term is plain back-propagation, the second is the derivative
-// of a directional derivative (tangent v = u/(AF+eps) pushed forward, then reversed) - what
-// TensorFlow's autodiff does through grad_ene for the force loss (staf_model.py:191,225-228).
-// The kernel also contracts dL/dAF with the per-atom d(AF)/d(alpha) rows left by the AF sweep
-// (vrow), which yields the fingerprint part of dL/dalpha without another sweep over the triplets.
-template <class T, int APT>
-__global__ void __launch_bounds__(ML_THREADS)
-    k_mlp_bwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ af,
-              const T* __restrict__ acts, const T* __restrict__ ebar /*[nf]*/, const T* __restrict__ u /*[nf,N,Fmax]*/,
-              const T* __restrict__ vrow /*[nf,N,nv] or null*/, int nv, T* __restrict__ gaf, T* __restrict__ grad,
-              int stage) {
-  constexpr int TA = 8 * APT;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  int t, q0;
-  locate_block(md, nf, TA, t, q0);
-  const int nat = nf * md.tipos[t];
-  const int F = md.Fr[t] + md.Fa[t], Lq = md.n_dense, Fm = md.Fmax, Hs = md.Hsum, mw = md.maxw;
-  T* X = reinterpret_cast<T*>(smem_raw);  // [Fm][TA] x
-  T* V = X + Fm * TA;                     // [Fm][TA] tangent on x
-  T* H = V + Fm * TA;                     // [Hs][TA] activations
-  T* HD = H + Hs * TA;                    // tangents of the activations
-  T* AD = HD + Hs * TA;                   // tangents of the pre-activations
-  T* DQ = AD + Hs * TA;                   // cotangent on the pre-activation (first-order channel)
-  T* DP = DQ + Hs * TA;                   // cotangent on the pre-activation tangent
-  T* CQ = DP + Hs * TA;                   // [mw][TA]
-  T* CP = CQ + mw * TA;                   // [mw][TA]
-  T* wsm = CP + mw * TA;                  // one staged layer
-  const T* mu = theta + md.off_mu[t];
-  const T* w = theta + md.off_w[t];
-  auto gidx = [&](int a) -> long long {
-    const int q = q0 + a;
-    if (q >= nat) return -1;
-    const int b = q / md.tipos[t];
-    return (long long)b * md.N + md.shift[t] + (q - b * md.tipos[t]);
-  };
-  for (int idx = threadIdx.x; idx < F * TA; idx += ML_THREADS) {
-    const int a = idx % TA, i = idx / TA;
-    const long long gi = gidx(a);
-    T xv = T(0), vv = T(0);
-    if (gi >= 0) {
-      const T den = af[gi * Fm + i] + T(1e-3);
-      xv = r_log(den) - mu[i];
-      vv = u[gi * Fm + i] / den;
-    }
-    X[idx] = xv;
-    V[idx] = vv;
-  }
-  const T* ab = acts + (size_t)blockIdx.x * Hs * TA;
-  for (int idx = threadIdx.x; idx < Hs * TA; idx += ML_THREADS) {
-    const int a = idx % TA;
-    H[idx] = (q0 + a < nat) ? ab[idx] : T(0);
-  }
-  // forward tangent: AD = HDin W ; HD = AD * act'
-  const T* hdin = V;
-  LayerView<T> lv;
-  for (int l = 0; l < Lq; l++) {
-    const int in = md.in_of(t, l), out = md.width[l];
-    lv = stage_layer(in, out, w + md.w_off(t, l), wsm, stage != 0);
-    T* ado = AD + md.h_off(l) * TA;
-    T* hdo = HD + md.h_off(l) * TA;
-    dense_fwd<T, APT, false, false>(in, out, lv, hdin, ado);
-    __syncthreads();
-    const T* ho = H + md.h_off(l) * TA;
-    for (int idx = threadIdx.x; idx < out * TA; idx += ML_THREADS)
-      hdo[idx] = (l < Lq - 1) ? ado[idx] * (T(1) - ho[idx] * ho[idx]) : ado[idx];
-    hdin = hdo;
-  }
-  __syncthreads();
-  // reverse over (h, hd)
-  if (threadIdx.x < TA) {
-    const long long gi = gidx(threadIdx.x);
-    CQ[threadIdx.x] = gi >= 0 ? ebar[gi / md.N] : T(0);
-    CP[threadIdx.x] = gi >= 0 ? T(1) : T(0);
-  }
-  T* gw = grad + md.off_w[t];
-  for (int l = Lq - 1; l >= 0; l--) {
-    const int in = md.in_of(t, l), out = md.width[l];
-    if (l < Lq - 1) lv = stage_layer(in, out, w + md.w_off(t, l), wsm, stage != 0);  // the last layer is still staged
-    else __syncthreads();
-    const T* ho = H + md.h_off(l) * TA;
-    const T* ado = AD + md.h_off(l) * TA;
-    T* dql = DQ + md.h_off(l) * TA;
-    T* dpl = DP + md.h_off(l) * TA;
-    for (int idx = threadIdx.x; idx < out * TA; idx += ML_THREADS) {
-      T qa, pa;
-      if (l < Lq - 1) {
-        const T hh = ho[idx], d1 = T(1) - hh * hh;
-        pa = CP[idx] * d1;
-        qa = CQ[idx] * d1 + CP[idx] * (T(-2) * hh * d1 * ado[idx]);
-      } else {
-        pa = CP[idx];
-        qa = CQ[idx];
-      }
-      dql[idx] = qa;
-      dpl[idx] = pa;
-    }
-    __syncthreads();
-    // weight and bias gradients of this layer, summed over the block's atoms
-    const T* hin = (l == 0) ? X : H + md.h_off(l - 1) * TA;
-    const T* hdi = (l == 0) ? V : HD + md.h_off(l - 1) * TA;
-    const int woff = md.w_off(t, l);
-    for (int idx = threadIdx.x; idx < in * out + out; idx += ML_THREADS) {
-      T g = T(0);
-      // consecutive lanes hold consecutive j (stride TA words): start each lane at a different atom
-      const int rot = threadIdx.x & (TA - 1);
-      if (idx < in * out) {
-        const int q = idx / out, j = idx - q * out;
-        const T* hp = hin + q * TA;
-        const T* hdp = hdi + q * TA;
-        const T* qp = dql + j * TA;
-        const T* pp = dpl + j * TA;
-#pragma unroll 8
-        for (int a0 = 0; a0 < TA; a0++) {
-          const int a = (a0 + rot) & (TA - 1);
-          g += hp[a] * qp[a] + hdp[a] * pp[a];
-        }
-      } else {
-        const T* qp = dql + (idx - in * out) * TA;
-#pragma unroll 8
-        for (int a0 = 0; a0 < TA; a0++) g += qp[(a0 + rot) & (TA - 1)];
-      }
-      atomicAdd(gw + woff + idx, g);
-    }
-    // cotangents on the layer input
-    dense_bwd<T, APT>(in, out, lv, dql, CQ, dpl, CP);
-  }
-  // CQ = dS/dx, CP = dS/dv  ->  dL/dAF, kept in V for the contraction below
-  for (int idx = threadIdx.x; idx < Fm * TA; idx += ML_THREADS) {
-    const int a = idx % TA, i = idx / TA;
-    const long long gi = gidx(a);
-    T g = T(0);
-    if (gi >= 0 && i < F) {
-      const T den = af[gi * Fm + i] + T(1e-3);
-      g = CQ[idx] / den + CP[idx] * (-u[gi * Fm + i] / (den * den));
-    }
-    if (gi >= 0) gaf[gi * Fm + i] = g;
-    if (i < F) V[idx] = g;
-  }
-  for (int i = threadIdx.x; i < F; i += ML_THREADS) {
-    T g = T(0);
-    for (int a = 0; a < TA; a++) g -= CQ[i * TA + a];
-    atomicAdd(grad + md.off_mu[t] + i, g);
-  }
-  if (vrow) {
-    __syncthreads();
-    // dL/dalpha (fingerprint part) = sum_atoms dL/dAF[c(q)] * dAF[c(q)]/dalpha[q]; alpha2b and alpha3b
-    // are contiguous in theta, q runs over both
-    const int Fr = md.Fr[t], Fa = md.Fa[t], n2 = md.nt * Fr, nq = n2 + md.C * 3 * Fa;
-    for (int q = threadIdx.x; q < nq; q += ML_THREADS) {
-      const int ch = q < n2 ? (q % Fr) : Fr + ((q - n2) / 3) % Fa;
-      T g = T(0);
-      for (int a = 0; a < TA; a++) {
-        const long long gi = gidx(a);
-        if (gi >= 0) g += V[ch * TA + a] * vrow[gi * nv + q];
-      }
-      if (g != T(0)) atomicAdd(grad + md.off_a2[t] + q, g);
-    }
-  }
-}
+namespace stafb {
+#endif
 
 // ---------------------------------------------------------------------------- energy, loss
 template <class T>
@@ -1207,7 +892,7 @@ struct stafb_model {
   size_t es;
   int cap_atoms;  // atoms per frame the scratch was sized for
   int apt;  // atoms per thread group of the MLP kernels (TA = 8*apt atoms per block)
-  int stage;  // 1: the MLP kernels stage each Dense layer in shared memory
+  int stage;  // Dense layers in shared memory: 2 all at kernel start, 1 one at a time, 0 none
   size_t mlp_fwd_smem, mlp_bwd_smem;
   // scratch for max_batch frames
   void *rad, *d3s, *af, *nd, *acts, *e_atom, *force, *fbar, *ebar, *gradnet, *gaf, *energy, *vrow;
@@ -1221,12 +906,26 @@ struct stafb_model {
   size_t smem_limit;
 };
 
-static size_t mlp_smem_fwd(const ModelDev& d, size_t es, int apt, bool stage) {
-  return es * ((size_t)(d.Fmax + d.Hsum + 2 * d.maxw) * 8 * apt + (stage ? (size_t)(d.maxw + 1) * (d.maxw + 1) : 0));
+// words of shared memory the staged Dense layers need: stage 1 = the largest (in + 1) x row stride over the
+// layers, stage 2 = all layers of one species back to back
+static size_t mlp_stage_words(const ModelDev& d, int stage) {
+  size_t best = 0;
+  for (int t = 0; t < d.nt; t++) {
+    size_t sum = 0;
+    for (int l = 0; l < d.n_dense; l++) {
+      const size_t wds = (size_t)(d.in_of(t, l) + 1) * ml_ld(d.width[l]);
+      sum += wds;
+      if (stage == 1) best = wds > best ? wds : best;
+    }
+    if (stage == 2) best = sum > best ? sum : best;
+  }
+  return stage ? best : 0;
 }
-static size_t mlp_smem_bwd(const ModelDev& d, size_t es, int apt, bool stage) {
-  return es * ((size_t)(2 * d.Fmax + 5 * d.Hsum + 2 * d.maxw) * 8 * apt +
-               (stage ? (size_t)(d.maxw + 1) * (d.maxw + 1) : 0));
+static size_t mlp_smem_fwd(const ModelDev& d, size_t es, int apt, int stage) {
+  return es * ((size_t)(d.Fmax + d.Hsum + 2 * d.maxw) * (8 * apt + ML_PAD) + mlp_stage_words(d, stage));
+}
+static size_t mlp_smem_bwd(const ModelDev& d, size_t es, int apt, int stage) {
+  return es * ((size_t)(2 * d.Fmax + 5 * d.Hsum + 2 * d.maxw) * (8 * apt + ML_PAD) + mlp_stage_words(d, stage));
 }
 
 extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out) {
@@ -1282,17 +981,22 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   m->apt = 0;
   int nsm = 148;
   cudaDeviceGetAttribute(&nsm, cudaDevAttrMultiProcessorCount, dev);
-  m->stage = 1;  // keep one Dense layer in shared memory if it fits next to the activations
-  if (mlp_smem_bwd(d, m->es, 1, true) > m->smem_limit) m->stage = 0;
+  // Dense layers in shared memory: all of them (2) if they fit next to the activations of 8 atoms within half
+  // of the SM (two resident blocks), else one at a time (1), else none (0)
+  const size_t mlp_room = m->smem_limit - 1024;  // the MLP kernels also hold a little static shared memory
+  m->stage = 2;
+  if (mlp_smem_bwd(d, m->es, 1, 2) > mlp_room / 2) m->stage = 1;
+  if (mlp_smem_bwd(d, m->es, 1, m->stage) > mlp_room) m->stage = 0;
+  if (getenv("STAFB_MLP_STAGE")) m->stage = atoi(getenv("STAFB_MLP_STAGE"));
   for (int apt = 4; apt >= 1; apt >>= 1) {
-    if (mlp_smem_bwd(d, m->es, apt, m->stage != 0) > m->smem_limit) continue;
+    if (mlp_smem_bwd(d, m->es, apt, m->stage) > mlp_room) continue;
     m->apt = apt;  // keep shrinking until the grid gives every SM at least two blocks
     if (species_blocks(d, c->max_batch, 8 * apt) >= 2 * nsm) break;
   }
   if (getenv("STAFB_MLP_APT")) m->apt = atoi(getenv("STAFB_MLP_APT"));
   if (!m->apt) { free(m); return STAFB_ERR_CAPACITY; }
-  m->mlp_fwd_smem = mlp_smem_fwd(d, m->es, m->apt, m->stage != 0);
-  m->mlp_bwd_smem = mlp_smem_bwd(d, m->es, m->apt, m->stage != 0);
+  m->mlp_fwd_smem = mlp_smem_fwd(d, m->es, m->apt, m->stage);
+  m->mlp_bwd_smem = mlp_smem_bwd(d, m->es, m->apt, m->stage);
   // scratch is sized for the context's atom capacity, so that stafb_model_set_counts can move atoms between
   // species (or change their number) without reallocating
   const size_t es = m->es, A = (size_t)c->max_batch * c->n_max, nr = c->nr;
@@ -1396,11 +1100,11 @@ static int launch_sweep(stafb_model* m, cudaStream_t s, int nf, const SweepIn<T>
 template <class T, int APT>
 static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, T* acts, T* e_atom,
                           T* nd) {
-  static bool attr = false;
-  if (m->mlp_fwd_smem > 48 * 1024 && !attr) {
+  static size_t attr = 0;  // largest dynamic shared-memory size this instantiation was opted in for
+  if (m->mlp_fwd_smem > 48 * 1024 && m->mlp_fwd_smem > attr) {
     STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_fwd<T, APT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)m->smem_limit));
-    attr = true;
+                                       (int)m->mlp_fwd_smem));
+    attr = m->mlp_fwd_smem;
   }
   k_mlp_fwd<T, APT><<<species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_fwd_smem, s>>>(m->md, nf, theta, af, acts,
                                                                                            e_atom, nd, m->stage);
@@ -1411,12 +1115,12 @@ static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta
 template <class T, int APT>
 static int launch_mlp_bwd(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, const T* acts,
                           const T* ebar, const T* u, T* gaf, T* grad) {
-  static bool attr = false;
+  static size_t attr = 0;
   const T* vrow = (const T*)m->vrow;
-  if (m->mlp_bwd_smem > 48 * 1024 && !attr) {
+  if (m->mlp_bwd_smem > 48 * 1024 && m->mlp_bwd_smem > attr) {
     STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_bwd<T, APT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)m->smem_limit));
-    attr = true;
+                                       (int)m->mlp_bwd_smem));
+    attr = m->mlp_bwd_smem;
   }
   k_mlp_bwd<T, APT><<<species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_bwd_smem, s>>>(m->md, nf, theta, af, acts,
                                                                                            ebar, u, vrow, m->nv, gaf, grad, m->stage);
