@@ -179,3 +179,48 @@ extern "C" int stafb_init_force_radial(int) { return 0; }
 extern "C" int stafb_init_force_tripl(int) { return 0; }
 extern "C" int stafb_init_grad_force_radial(int) { return 0; }
 extern "C" int stafb_init_grad_force_tripl(int) { return 0; }
+
+// ---- measured FP32 / FP64 FMA throughput of the device (the denominator of pipe-utilisation figures) ----
+// Every thread runs `iters` rounds of eight independent fused multiply-adds; 2 flops each.
+template <class T>
+__global__ void __launch_bounds__(256) k_fma_peak(int iters, T seed, T* __restrict__ out) {
+  T a0 = seed + threadIdx.x, a1 = a0 + T(1), a2 = a0 + T(2), a3 = a0 + T(3), a4 = a0 + T(4), a5 = a0 + T(5),
+    a6 = a0 + T(6), a7 = a0 + T(7);
+  const T m = T(0.999), c = T(1e-3);
+  for (int i = 0; i < iters; i++) {
+    a0 = a0 * m + c; a1 = a1 * m + c; a2 = a2 * m + c; a3 = a3 * m + c;
+    a4 = a4 * m + c; a5 = a5 * m + c; a6 = a6 * m + c; a7 = a7 * m + c;
+  }
+  out[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = a0 + a1 + a2 + a3 + a4 + a5 + a6 + a7;
+}
+
+extern "C" int stafb_measure_fma_peak(int dtype, void* stream, double* tflops_out) {
+  if (!tflops_out || (dtype != STAFB_F32 && dtype != STAFB_F64)) return STAFB_ERR_INVALID;
+  cudaStream_t s = (cudaStream_t)stream;
+  int dev = 0, nsm = 0;
+  STAFB_CUDA_OK(cudaGetDevice(&dev));
+  STAFB_CUDA_OK(cudaDeviceGetAttribute(&nsm, cudaDevAttrMultiProcessorCount, dev));
+  const int blocks = nsm * 8, threads = 256, iters = dtype == STAFB_F32 ? 1 << 15 : 1 << 12;
+  void* buf = nullptr;
+  STAFB_CUDA_OK(cudaMalloc(&buf, (size_t)blocks * threads * 8));
+  cudaEvent_t e0, e1;
+  STAFB_CUDA_OK(cudaEventCreate(&e0));
+  STAFB_CUDA_OK(cudaEventCreate(&e1));
+  float best = 1e30f;
+  for (int rep = 0; rep < 4; rep++) {  // the first repetition warms up
+    cudaEventRecord(e0, s);
+    if (dtype == STAFB_F32) k_fma_peak<float><<<blocks, threads, 0, s>>>(iters, 1.0f, (float*)buf);
+    else k_fma_peak<double><<<blocks, threads, 0, s>>>(iters, 1.0, (double*)buf);
+    cudaEventRecord(e1, s);
+    cudaEventSynchronize(e1);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    if (rep > 0 && ms < best) best = ms;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(buf);
+  STAFB_CUDA_OK(cudaGetLastError());
+  *tflops_out = 2.0 * 8.0 * iters * (double)blocks * threads / (best * 1e-3) / 1e12;
+  return STAFB_OK;
+}

@@ -302,6 +302,12 @@ def run_ours(args):
     alg = {"af_fwd": row_bytes + chan, "force": row_bytes + chan + float(((n_i + 1) * 3 * isz).sum()),
            "force_grad": row_bytes + 2 * chan + float(((n_i + 1) * 3 * isz).sum()),
            "af_grad": row_bytes + chan, "mlp_fwd": 3 * chan, "mlp_bwd": 4 * chan}[dom]
+    # DRAM traffic per launch of each sweep (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of
+    # this workload at batch 4, profiles/k_sweep_water768_b4_fp32.md); it scales with the number of atoms
+    traffic_ncu_b4 = {"af_fwd": 5.23e6, "force": 5.58e6, "force_grad": 5.58e6, "mlp_fwd": 0.40e6, "mlp_bwd": 3.85e6}
+    traffic = traffic_ncu_b4.get(dom)
+    if traffic is not None:
+        traffic *= B / 4.0
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -310,31 +316,84 @@ def run_ours(args):
     peak = float(peaks.get("hbm_gbs", 6650.0))
     achieved = alg / (acc[dom] * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": "k_sweep<%s>" % dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
+                "frac": achieved / peak, "traffic": traffic, "peak_source": "measured" if peaks else "fallback",
                 "ms_per_launch": acc[dom], "algorithmic_bytes_per_launch": alg,
                 "note": "geometry is rebuilt on chip, so this kernel is bound by the FP32/SFU pipes, not by HBM; "
                         "triplet-channel evaluations per launch = %.3g" % (trip * shape.Fa[0] / shape.C)}
-    # the HBM-bound kernel of the operator boundary: the angular descriptor fill (write-once tensors)
+    # the HBM-bound kernel of the operator boundary: the angular descriptor fill (write-once tensors), timed as
+    # the difference between the operator with and without its three angular outputs (outputs preallocated,
+    # no host synchronisation inside the timed region)
+    import ctypes as C
+    from alphanesgpu_b200 import _lib
+    nr_, na_ = CFG["nr"], CFG["na"]
+    te = lambda *sh, d=torch.float32: torch.empty(*sh, dtype=d, device=dev)
+    o_rad, o_d3s, o_d2b, o_d3bs = te(B, N, nr_), te(B, N, nr_), te(B, N, 3, nr_), te(B, N, 3, nr_)
+    o_im2, o_ntr = te(B, N, nr_ + 1, d=torch.int32), te(B, N, d=torch.int32)
+    o_ang, o_im3, o_d3b = te(B, N, na_), te(B, N, 2 * na_, d=torch.int32), te(B, N, 3, 2 * na_)
+    vp = lambda t: None if t is None else C.c_void_p(t.data_ptr())
+
+    def desc_call(k, angular):
+        a = (o_ang, o_im3, o_d3b) if angular else (None, None, None)
+        rc = _lib.lib().stafb_compute_descriptors_light(ctx.h, ctx.stream(), vp(d_pos[k % NB]), vp(d_box[k % NB]), B, N,
+                                                        vp(o_rad), vp(a[0]), vp(o_d3s), vp(o_im2), vp(a[1]), vp(o_d2b),
+                                                        vp(a[2]), vp(o_d3bs), vp(o_ntr))
+        assert rc == 0, rc
     e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-    ops.compute_descriptors_light(d_pos[0], d_box[0], with_angular=True, ctx=ctx)
+    for k in range(3):
+        desc_call(k, True)
     t_no, t_with = 0.0, 0.0
     for k in range(10):
         flush.zero_()
         e0.record()
-        ops_out = ops.compute_descriptors_light(d_pos[k % NB], d_box[k % NB], with_angular=False, ctx=ctx)
+        desc_call(k, False)
         e1.record()
-        ops_out = ops.compute_descriptors_light(d_pos[k % NB], d_box[k % NB], with_angular=True, ctx=ctx)
+        desc_call(k, True)
         e2.record()
         torch.cuda.synchronize()
         t_no += e0.elapsed_time(e1) / 10
         t_with += e1.elapsed_time(e2) / 10
+    ctx.raise_on_status("operator-boundary descriptors")
     ang_bytes = B * N * CFG["na"] * (isz + 8 + 6 * isz)
     ang_ms = max(t_with - t_no, 1e-6)
     roofline_ops = {"bound": "hbm", "kernel": "k_angular (ComputeDescriptorsLight angular tensors)",
                     "achieved": ang_bytes / (ang_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                     "frac": ang_bytes / (ang_ms * 1e-3) / 1e9 / peak, "traffic": None, "ms_per_launch": ang_ms,
                     "algorithmic_bytes_per_launch": ang_bytes}
-    del ops_out
+    del o_ang, o_im3, o_d3b
+
+    # ---- FP32 pipe: measured FMA peak of this GPU against the algorithmic flops of the step
+    # (about 1.3 kFLOP per triplet for fingerprints + forces + both backward sweeps, 5 active channels per class)
+    pk32, pk64 = C.c_double(), C.c_double()
+    _lib.lib().stafb_measure_fma_peak(0, model.ctx.stream(), C.byref(pk32))
+    _lib.lib().stafb_measure_fma_peak(1, model.ctx.stream(), C.byref(pk64))
+    step_flops = trip * 1.3e3
+    fp32_pipe = {"fma_peak_tflops_measured": pk32.value, "fp64_fma_peak_tflops_measured": pk64.value,
+                 "algorithmic_flops_per_step": step_flops,
+                 "achieved_tflops": step_flops / (total_ms / K * 1e-3) / 1e12,
+                 "frac_of_fma_peak": step_flops / (total_ms / K * 1e-3) / 1e12 / pk32.value}
+
+    # ---- the same step in float64 (BASELINE configs[2]): time ratio against fp32
+    model64 = StafModel(shape, CFG, theta.astype(np.float64), emb.astype(np.float64), B, dtype=torch.float64, device=dev)
+    d64 = [torch.as_tensor(a.astype(np.float64)).to(dev) for a in (pos, box, el, fl)]
+    for k in range(3):
+        model64.loss_and_grad(d64[0][k % NB], d64[1][k % NB], d64[2][k % NB], d64[3][k % NB])
+        model64.adam_update_dev(lr)
+    K64 = 30
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t64 = 0.0
+    for k in range(K64):
+        flush.zero_()
+        e0.record()
+        model64.loss_and_grad(d64[0][k % NB], d64[1][k % NB], d64[2][k % NB], d64[3][k % NB])
+        model64.adam_update_dev(lr)
+        e1.record()
+        torch.cuda.synchronize()
+        t64 += e0.elapsed_time(e1)
+    model64.ctx.raise_on_status("fp64 leg")
+    fp64 = {"value": B * K64 / (t64 * 1e-3), "unit": "frames/s", "ms_per_step": t64 / K64, "steps": K64,
+            "time_ratio_fp64_over_fp32": (t64 / K64) / (total_ms / K),
+            "note": "eager launches (no graph); fp32 figure is the graph-replayed step"}
+    model64.close()
 
     line = None
     if rank == 0:
@@ -359,7 +418,7 @@ def run_ours(args):
                     "steps": Ke},
             "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step,
             "clocks": clocks, "roofline": roofline, "roofline_operator_boundary": roofline_ops,
-            "phase_ms": acc, "cpu_baseline": cpu,
+            "fp32_pipe": fp32_pipe, "fp64": fp64, "phase_ms": acc, "cpu_baseline": cpu,
         }
         print(json.dumps(line))
     model.close()

@@ -243,6 +243,11 @@ int stafb_train_step_host(stafb_ctx* ctx, stafb_model* m, void* stream, const vo
 int stafb_set_phase_timing(stafb_ctx* ctx, int on);
 int stafb_get_phase_times(stafb_ctx* ctx, float* ms, int cap);
 
+/* Measured FMA throughput of the current device in TFLOP/s (dtype STAFB_F32 or STAFB_F64): a register-resident
+ * loop of independent fused multiply-adds on every SM, best of three runs, timed with CUDA events on `stream`.
+ * The denominator for FP32 / FP64 pipe-utilisation figures (there is no reference counterpart). */
+int stafb_measure_fma_peak(int dtype, void* stream, double* tflops_out);
+
 /* number of kernels the last fused call launched (for accounting) */
 int stafb_last_launch_count(const stafb_ctx* ctx);
 
