@@ -40,6 +40,10 @@ _SIGS = {
     "stafb_compute_sort_proj3body_grad": [_vp, _vp] + [_vp] * 9 + [_i] * 4 + [_vp] * 2,
     "stafb_compute_force_radial_grad": [_vp, _vp] + [_vp] * 10 + [_i] * 5 + [_vp] * 3,
     "stafb_compute_force_tripl_grad": [_vp, _vp] + [_vp] * 14 + [_i] * 5 + [_vp] * 3,
+    "stafb_compute_force_radial_virial": [_vp, _vp] + [_vp] * 11 + [_i] * 5 + [_vp] * 2,
+    "stafb_compute_force_tripl_virial": [_vp, _vp] + [_vp] * 15 + [_i] * 5 + [_vp] * 2,
+    "stafb_compute_force_radial_virial_grad": [_vp, _vp] + [_vp] * 13 + [_i] * 5 + [_vp] * 3,
+    "stafb_compute_force_tripl_virial_grad": [_vp, _vp] + [_vp] * 17 + [_i] * 5 + [_vp] * 3,
     "stafb_init_force_radial": [_i], "stafb_init_force_tripl": [_i],
     "stafb_init_grad_force_radial": [_i], "stafb_init_grad_force_tripl": [_i],
     "stafb_model_create": [_vp, _vp, C.POINTER(_vp)],

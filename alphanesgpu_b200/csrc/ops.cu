@@ -14,6 +14,32 @@ namespace stafb {
 constexpr int OPS_THREADS = 128;
 constexpr int OPS_WARPS = OPS_THREADS / 32;
 
+// Extra inputs / outputs of the ...Virial and ...VirialGrad operators (null pointers: plain operator).
+template <class T>
+struct VirArgs {
+  const T* pos = nullptr;   // [nf,3N] Cartesian positions
+  const T* box = nullptr;   // [nf,6]
+  T* virial = nullptr;      // force ops: [nf,9] accumulated, W_ab -= g_a r_b
+  const T* wbar = nullptr;  // grad ops: [nf,9] cotangent on the virial
+};
+
+// r_i - r_j with the minimum image taken in fractional space, as the reference's virial kernels form it
+// (STAF/include/staf_force_pbc.cuh:15-49)
+template <class T>
+__device__ __forceinline__ void mic_cart(const T* __restrict__ pi, const T* __restrict__ pj, const T* __restrict__ B,
+                                         T* d) {
+  const T i0 = T(1.) / B[0], i1 = -B[1] / (B[0] * B[3]);
+  const T i2 = (B[1] * B[4]) / (B[0] * B[3] * B[5]) - B[2] / (B[0] * B[5]);
+  const T i3 = T(1.) / B[3], i4 = -B[4] / (B[3] * B[5]), i5 = T(1.) / B[5];
+  T rx = (i0 * pi[0] + i1 * pi[1] + i2 * pi[2]) - (i0 * pj[0] + i1 * pj[1] + i2 * pj[2]);
+  T ry = (i3 * pi[1] + i4 * pi[2]) - (i3 * pj[1] + i4 * pj[2]);
+  T rz = i5 * pi[2] - i5 * pj[2];
+  rx -= r_rint(rx); ry -= r_rint(ry); rz -= r_rint(rz);
+  d[0] = B[0] * rx + B[1] * ry + B[2] * rz;
+  d[1] = B[3] * ry + B[4] * rz;
+  d[2] = B[5] * rz;
+}
+
 __device__ __forceinline__ int species_shift(const int* tipos, const int* actual_type) {
   int at = actual_type[0], s = 0;
   for (int y = 0; y < at; y++) s += tipos[y];
@@ -116,7 +142,8 @@ __global__ void __launch_bounds__(OPS_THREADS)
     k_force_rad(int natoms, int Nl, int N, int nr, int Fr, const T* __restrict__ netderiv,
                 const T* __restrict__ der2b, const int* __restrict__ im2, const T* __restrict__ rad,
                 const T* __restrict__ alpha2b, const T* __restrict__ e2, const int* __restrict__ type_map,
-                const int* __restrict__ tipos, const int* __restrict__ actual_type, T* __restrict__ force) {
+                const int* __restrict__ tipos, const int* __restrict__ actual_type, T* __restrict__ force,
+                VirArgs<T> va) {
   const int gi = blockIdx.x * OPS_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (gi >= natoms) return;
   const int b = gi / Nl, par = gi - b * Nl;
@@ -125,6 +152,9 @@ __global__ void __launch_bounds__(OPS_THREADS)
   int n = im2[base * (nr + 1)];
   if (n > nr) n = nr;
   T fx = T(0), fy = T(0), fz = T(0);
+  T vw[9];
+#pragma unroll
+  for (int c = 0; c < 9; c++) vw[c] = T(0);
   for (int j = lane; j < n; j += 32) {
     const int nj = im2[base * (nr + 1) + 1 + j];
     const int tj = type_map[nj];
@@ -146,6 +176,15 @@ __global__ void __launch_bounds__(OPS_THREADS)
     atomicAdd(fj + 1, gy);
     atomicAdd(fj + 2, gz);
     fx -= gx; fy -= gy; fz -= gz;
+    if (va.virial) {  // W_ab -= g_a r_b (force/rad/reforce.cu.cc:174-287)
+      T r[3];
+      mic_cart(va.pos + ((size_t)b * N + ipar) * 3, va.pos + ((size_t)b * N + nj) * 3, va.box + (size_t)b * 6, r);
+      const T g[3] = {gx, gy, gz};
+#pragma unroll
+      for (int a = 0; a < 3; a++)
+#pragma unroll
+        for (int c = 0; c < 3; c++) vw[a * 3 + c] -= g[a] * r[c];
+    }
   }
   fx = warp_sum(fx); fy = warp_sum(fy); fz = warp_sum(fz);
   if (lane == 0) {
@@ -153,6 +192,13 @@ __global__ void __launch_bounds__(OPS_THREADS)
     atomicAdd(fi + 0, fx);
     atomicAdd(fi + 1, fy);
     atomicAdd(fi + 2, fz);
+  }
+  if (va.virial) {
+#pragma unroll
+    for (int c = 0; c < 9; c++) {
+      const T v = warp_sum(vw[c]);
+      if (lane == 0) atomicAdd(va.virial + (size_t)b * 9 + c, v);
+    }
   }
 }
 
@@ -163,7 +209,7 @@ __global__ void __launch_bounds__(OPS_THREADS)
                 const T* __restrict__ ang, const T* __restrict__ der3bsupp, const T* __restrict__ der3b,
                 const int* __restrict__ im2, const T* __restrict__ alpha3b, const T* __restrict__ e3,
                 const int* __restrict__ type_map, const int* __restrict__ tipos, const int* __restrict__ actual_type,
-                const int* __restrict__ numtriplet, T* __restrict__ force) {
+                const int* __restrict__ numtriplet, T* __restrict__ force, VirArgs<T> va) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ T red[OPS_WARPS + 1];
   typedef typename Vec2<T>::type T2;
@@ -228,6 +274,26 @@ __global__ void __launch_bounds__(OPS_THREADS)
     atomicAdd(fb + (size_t)ipar * 3 + 0, fx);
     atomicAdd(fb + (size_t)ipar * 3 + 1, fy);
     atomicAdd(fb + (size_t)ipar * 3 + 2, fz);
+  }
+  if (va.virial && threadIdx.x < 32) {
+    // W_ab -= f_ij,a r_ij,b + f_ik,a r_ik,b (force/ang/reforce.cu.cc:269-457): every force this centre puts on
+    // neighbour k multiplies the same r_ik, so the per-neighbour totals suffice
+    T w[9];
+#pragma unroll
+    for (int c = 0; c < 9; c++) w[c] = T(0);
+    for (int k = threadIdx.x; k < st.m; k += 32) {
+      T r[3];
+      mic_cart(va.pos + ((size_t)b * N + ipar) * 3, va.pos + ((size_t)b * N + ids[k]) * 3, va.box + (size_t)b * 6, r);
+#pragma unroll
+      for (int a = 0; a < 3; a++)
+#pragma unroll
+        for (int c = 0; c < 3; c++) w[a * 3 + c] -= fnb[k * 3 + a] * r[c];
+    }
+#pragma unroll
+    for (int c = 0; c < 9; c++) {
+      const T v = warp_sum(w[c]);
+      if (threadIdx.x == 0) atomicAdd(va.virial + (size_t)b * 9 + c, v);
+    }
   }
 }
 
@@ -322,7 +388,7 @@ __global__ void __launch_bounds__(OPS_THREADS)
                      const T* __restrict__ rad, const T* __restrict__ alpha2b, const T* __restrict__ e2,
                      const int* __restrict__ type_map, const int* __restrict__ tipos,
                      const int* __restrict__ actual_type, T* __restrict__ gradnet, T* __restrict__ g_alpha,
-                     T* __restrict__ g_emb) {
+                     T* __restrict__ g_emb, VirArgs<T> va) {
   const int gi = blockIdx.x * OPS_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (gi >= natoms) return;
   const int b = gi / Nl, par = gi - b * Nl;
@@ -344,9 +410,17 @@ __global__ void __launch_bounds__(OPS_THREADS)
       const int nj = im2[base * (nr + 1) + 1 + j];
       const int tj = type_map[nj];
       const T d = rad[base * nr + j];
-      const T q = T(0.5) * ((pgb[nj * 3] - pix) * der2b[(base * 3 + 0) * nr + j] +
-                            (pgb[nj * 3 + 1] - piy) * der2b[(base * 3 + 1) * nr + j] +
-                            (pgb[nj * 3 + 2] - piz) * der2b[(base * 3 + 2) * nr + j]);
+      T wd[3] = {T(0), T(0), T(0)};
+      if (va.wbar) {  // the virial cotangent shifts the neighbour's force cotangent by -(Wbar r) (grad_force/rad/reforce.cu.cc:165-234)
+        T r[3];
+        mic_cart(va.pos + ((size_t)b * N + ipar) * 3, va.pos + ((size_t)b * N + nj) * 3, va.box + (size_t)b * 6, r);
+        const T* Wg = va.wbar + (size_t)b * 9;
+#pragma unroll
+        for (int a = 0; a < 3; a++) wd[a] = Wg[a * 3] * r[0] + Wg[a * 3 + 1] * r[1] + Wg[a * 3 + 2] * r[2];
+      }
+      const T q = T(0.5) * ((pgb[nj * 3] - pix - wd[0]) * der2b[(base * 3 + 0) * nr + j] +
+                            (pgb[nj * 3 + 1] - piy - wd[1]) * der2b[(base * 3 + 1) * nr + j] +
+                            (pgb[nj * 3 + 2] - piz - wd[2]) * der2b[(base * 3 + 2) * nr + j]);
       const T al = alpha2b[Fr * tj + c], ch = e2[Fr * tj + c];
       const T s1 = r_exp(al * d);
       const T sds = s1 * (T(1.) + al * d);
@@ -383,7 +457,8 @@ __global__ void __launch_bounds__(OPS_THREADS)
                      const T* __restrict__ der3bsupp, const T* __restrict__ der3b, const int* __restrict__ im2,
                      const T* __restrict__ alpha3b, const T* __restrict__ e3, const int* __restrict__ type_map,
                      const int* __restrict__ tipos, const int* __restrict__ actual_type,
-                     const int* __restrict__ numtriplet, T* __restrict__ gradnet, T* __restrict__ g_alpha3) {
+                     const int* __restrict__ numtriplet, T* __restrict__ gradnet, T* __restrict__ g_alpha3,
+                     VirArgs<T> va) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ T red[OPS_WARPS + 1];
   typedef typename Vec2<T>::type T2;
@@ -401,8 +476,16 @@ __global__ void __launch_bounds__(OPS_THREADS)
   for (int k = threadIdx.x; k < nr; k += OPS_THREADS) {
     const int id = im2[base * (nr + 1) + 1 + k];
     T p = T(0);
+    T wd[3] = {T(0), T(0), T(0)};
+    if (va.wbar && k < numtriplet[base]) {  // grad_force/ang/reforce.cu.cc:274-446
+      T r[3];
+      mic_cart(va.pos + ((size_t)b * N + ipar) * 3, va.pos + ((size_t)b * N + id) * 3, va.box + (size_t)b * 6, r);
+      const T* Wg = va.wbar + (size_t)b * 9;
+#pragma unroll
+      for (int a = 0; a < 3; a++) wd[a] = Wg[a * 3] * r[0] + Wg[a * 3 + 1] * r[1] + Wg[a * 3 + 2] * r[2];
+    }
     for (int a = 0; a < 3; a++) {
-      const T d = pgb[id * 3 + a] - pgb[ipar * 3 + a];
+      const T d = pgb[id * 3 + a] - pgb[ipar * 3 + a] - wd[a];
       dF[k * 3 + a] = d;
       p += d * der3bsupp[(base * 3 + a) * nr + k];
     }
@@ -508,12 +591,13 @@ int op_sort_proj3(stafb_ctx* c, cudaStream_t s, const T* ang, const T* ds3, cons
 template <class T>
 int op_force_rad(stafb_ctx* c, cudaStream_t s, const T* nd, const T* der2b, const int* im2, const T* rad,
                  const T* a2, const T* e2, const int* tm, const int* tipos, const int* at, int nf, int Nl, int N,
-                 int nt, int Fr, T* force) {
+                 int nt, int Fr, T* force, VirArgs<T> va = VirArgs<T>()) {
   STAFB_CUDA_OK(cudaMemsetAsync(force, 0, sizeof(T) * (size_t)nf * 3 * N, s));
+  if (va.virial) STAFB_CUDA_OK(cudaMemsetAsync(va.virial, 0, sizeof(T) * (size_t)nf * 9, s));
   const int n = nf * Nl;
   if (n <= 0) return STAFB_OK;
   k_force_rad<T><<<(n + OPS_WARPS - 1) / OPS_WARPS, OPS_THREADS, 0, s>>>(n, Nl, N, c->nr, Fr, nd, der2b, im2, rad, a2,
-                                                                        e2, tm, tipos, at, force);
+                                                                        e2, tm, tipos, at, force, va);
   STAFB_CUDA_OK(cudaGetLastError());
   return STAFB_OK;
 }
@@ -521,13 +605,14 @@ int op_force_rad(stafb_ctx* c, cudaStream_t s, const T* nd, const T* der2b, cons
 template <class T>
 int op_force_ang(stafb_ctx* c, cudaStream_t s, const T* nd, const T* ds3, const T* ang, const T* d3s, const T* d3,
                  const int* im2, const T* a3, const T* e3, const int* tm, const int* tipos, const int* at,
-                 const int* ntr, int nf, int Nl, int N, int nt, int Fa, T* force) {
+                 const int* ntr, int nf, int Nl, int N, int nt, int Fa, T* force, VirArgs<T> va = VirArgs<T>()) {
   STAFB_CUDA_OK(cudaMemsetAsync(force, 0, sizeof(T) * (size_t)nf * 3 * N, s));
+  if (va.virial) STAFB_CUDA_OK(cudaMemsetAsync(va.virial, 0, sizeof(T) * (size_t)nf * 9, s));
   const int n = nf * Nl;
   if (n <= 0) return STAFB_OK;
   size_t sm = sizeof(T) * ((size_t)c->nr * 7 + Fa) + sizeof(int) * (size_t)c->nr * 2 + (size_t)c->na * 2;
   k_force_ang<T><<<n, OPS_THREADS, sm, s>>>(Nl, N, c->nr, c->na, Fa, nd, ds3, ang, d3s, d3, im2, a3, e3, tm, tipos, at,
-                                            ntr, force);
+                                            ntr, force, va);
   STAFB_CUDA_OK(cudaGetLastError());
   return STAFB_OK;
 }
@@ -564,7 +649,7 @@ int op_grad_af_ang(stafb_ctx* c, cudaStream_t s, const T* pg, const T* ang, cons
 template <class T>
 int op_grad_force_rad(stafb_ctx* c, cudaStream_t s, const T* pg, const T* nd, const T* der2b, const int* im2,
                       const T* rad, const T* a2, const T* e2, const int* tm, const int* tipos, const int* at, int nf,
-                      int Nl, int N, int nt, int Fr, T* gradnet, T* ga, T* ge) {
+                      int Nl, int N, int nt, int Fr, T* gradnet, T* ga, T* ge, VirArgs<T> va = VirArgs<T>()) {
   if (nt > STAFB_MAX_TYPES) return STAFB_ERR_INVALID;
   STAFB_CUDA_OK(cudaMemsetAsync(ga, 0, sizeof(T) * nt * Fr, s));
   STAFB_CUDA_OK(cudaMemsetAsync(ge, 0, sizeof(T) * nt * Fr, s));
@@ -572,7 +657,7 @@ int op_grad_force_rad(stafb_ctx* c, cudaStream_t s, const T* pg, const T* nd, co
   if (n <= 0) return STAFB_OK;
   k_grad_force_rad<T><<<(n + OPS_WARPS - 1) / OPS_WARPS, OPS_THREADS, 0, s>>>(n, Nl, N, c->nr, Fr, nt, pg, nd, der2b,
                                                                              im2, rad, a2, e2, tm, tipos, at, gradnet,
-                                                                             ga, ge);
+                                                                             ga, ge, va);
   STAFB_CUDA_OK(cudaGetLastError());
   return STAFB_OK;
 }
@@ -581,7 +666,7 @@ template <class T>
 int op_grad_force_ang(stafb_ctx* c, cudaStream_t s, const T* pg, const T* nd, const T* ds3, const T* ang,
                       const T* d3s, const T* d3, const int* im2, const T* a3, const T* e3, const int* tm,
                       const int* tipos, const int* at, const int* ntr, int nf, int Nl, int N, int nt, int Fa,
-                      T* gradnet, T* ga, T* gck) {
+                      T* gradnet, T* ga, T* gck, VirArgs<T> va = VirArgs<T>()) {
   const int C = nt * (nt + 1) / 2;
   STAFB_CUDA_OK(cudaMemsetAsync(ga, 0, sizeof(T) * C * 3 * Fa, s));
   STAFB_CUDA_OK(cudaMemsetAsync(gck, 0, sizeof(T) * C * Fa, s));
@@ -594,7 +679,7 @@ int op_grad_force_ang(stafb_ctx* c, cudaStream_t s, const T* pg, const T* nd, co
     attr_done[sizeof(T) == 8] = true;
   }
   k_grad_force_ang<T><<<n, OPS_THREADS, sm, s>>>(Nl, N, c->nr, c->na, Fa, ncls_of(nt), pg, nd, ds3, ang, d3s, d3, im2,
-                                                 a3, e3, tm, tipos, at, ntr, gradnet, ga);
+                                                 a3, e3, tm, tipos, at, ntr, gradnet, ga, va);
   STAFB_CUDA_OK(cudaGetLastError());
   return STAFB_OK;
 }
@@ -700,4 +785,78 @@ extern "C" int stafb_compute_force_tripl_grad(stafb_ctx* c, void* stream, const 
            op_grad_force_ang<R>(c, s, (const R*)pg, (const R*)nd, (const R*)ds3, (const R*)ang, (const R*)d3s,
                                 (const R*)d3, im2, (const R*)a3, (const R*)e3, tm, tipos, at, ntr, nf, Nl, N, nt, Fa,
                                 (R*)gradnet, (R*)ga, (R*)gck));
+}
+
+
+// ---- ...Virial / ...VirialGrad variants: the same kernels with the positions, the box and the virial (or its
+// cotangent) attached
+template <class R>
+static VirArgs<R> vir_args(const void* pos, const void* box, void* virial, const void* wbar) {
+  VirArgs<R> va;
+  va.pos = (const R*)pos; va.box = (const R*)box; va.virial = (R*)virial; va.wbar = (const R*)wbar;
+  return va;
+}
+
+extern "C" int stafb_compute_force_radial_virial(stafb_ctx* c, void* stream, const void* nd, const void* der2b,
+                                                 const int* im2, const void* rad, const void* a2, const void* e2,
+                                                 const int* tm, const int* tipos, const int* at, const void* pos,
+                                                 const void* box, int nf, int Nl, int N, int nt, int Fr, void* force,
+                                                 void* virial) {
+  if (!pos || !box || !virial) return STAFB_ERR_INVALID;
+  DISPATCH(c,
+           op_force_rad<R>(c, s, (const R*)nd, (const R*)der2b, im2, (const R*)rad, (const R*)a2, (const R*)e2, tm,
+                           tipos, at, nf, Nl, N, nt, Fr, (R*)force, vir_args<R>(pos, box, virial, nullptr)),
+           op_force_rad<R>(c, s, (const R*)nd, (const R*)der2b, im2, (const R*)rad, (const R*)a2, (const R*)e2, tm,
+                           tipos, at, nf, Nl, N, nt, Fr, (R*)force, vir_args<R>(pos, box, virial, nullptr)));
+}
+
+extern "C" int stafb_compute_force_tripl_virial(stafb_ctx* c, void* stream, const void* nd, const void* ds3,
+                                                const void* ang, const void* d3s, const void* d3, const int* im2,
+                                                const int* im3, const void* a3, const void* e3, const int* tm,
+                                                const int* tipos, const int* at, const int* ntr, const void* pos,
+                                                const void* box, int nf, int Nl, int N, int nt, int Fa, void* force,
+                                                void* virial) {
+  (void)im3;
+  if (!pos || !box || !virial) return STAFB_ERR_INVALID;
+  DISPATCH(c,
+           op_force_ang<R>(c, s, (const R*)nd, (const R*)ds3, (const R*)ang, (const R*)d3s, (const R*)d3, im2,
+                           (const R*)a3, (const R*)e3, tm, tipos, at, ntr, nf, Nl, N, nt, Fa, (R*)force,
+                           vir_args<R>(pos, box, virial, nullptr)),
+           op_force_ang<R>(c, s, (const R*)nd, (const R*)ds3, (const R*)ang, (const R*)d3s, (const R*)d3, im2,
+                           (const R*)a3, (const R*)e3, tm, tipos, at, ntr, nf, Nl, N, nt, Fa, (R*)force,
+                           vir_args<R>(pos, box, virial, nullptr)));
+}
+
+extern "C" int stafb_compute_force_radial_virial_grad(stafb_ctx* c, void* stream, const void* pg, const void* pgv,
+                                                      const void* nd, const void* der2b, const int* im2,
+                                                      const void* rad, const void* a2, const void* e2, const int* tm,
+                                                      const int* tipos, const int* at, const void* pos,
+                                                      const void* box, int nf, int Nl, int N, int nt, int Fr,
+                                                      void* gradnet, void* ga, void* ge) {
+  if (!pos || !box || !pgv) return STAFB_ERR_INVALID;
+  DISPATCH(c,
+           op_grad_force_rad<R>(c, s, (const R*)pg, (const R*)nd, (const R*)der2b, im2, (const R*)rad, (const R*)a2,
+                                (const R*)e2, tm, tipos, at, nf, Nl, N, nt, Fr, (R*)gradnet, (R*)ga, (R*)ge,
+                                vir_args<R>(pos, box, nullptr, pgv)),
+           op_grad_force_rad<R>(c, s, (const R*)pg, (const R*)nd, (const R*)der2b, im2, (const R*)rad, (const R*)a2,
+                                (const R*)e2, tm, tipos, at, nf, Nl, N, nt, Fr, (R*)gradnet, (R*)ga, (R*)ge,
+                                vir_args<R>(pos, box, nullptr, pgv)));
+}
+
+extern "C" int stafb_compute_force_tripl_virial_grad(stafb_ctx* c, void* stream, const void* pg, const void* pgv,
+                                                     const void* nd, const void* ds3, const void* ang,
+                                                     const void* d3s, const void* d3, const int* im2, const int* im3,
+                                                     const void* a3, const void* e3, const int* tm, const int* tipos,
+                                                     const int* at, const int* ntr, const void* pos, const void* box,
+                                                     int nf, int Nl, int N, int nt, int Fa, void* gradnet, void* ga,
+                                                     void* gck) {
+  (void)im3;
+  if (!pos || !box || !pgv) return STAFB_ERR_INVALID;
+  DISPATCH(c,
+           op_grad_force_ang<R>(c, s, (const R*)pg, (const R*)nd, (const R*)ds3, (const R*)ang, (const R*)d3s,
+                                (const R*)d3, im2, (const R*)a3, (const R*)e3, tm, tipos, at, ntr, nf, Nl, N, nt, Fa,
+                                (R*)gradnet, (R*)ga, (R*)gck, vir_args<R>(pos, box, nullptr, pgv)),
+           op_grad_force_ang<R>(c, s, (const R*)pg, (const R*)nd, (const R*)ds3, (const R*)ang, (const R*)d3s,
+                                (const R*)d3, im2, (const R*)a3, (const R*)e3, tm, tipos, at, ntr, nf, Nl, N, nt, Fa,
+                                (R*)gradnet, (R*)ga, (R*)gck, vir_args<R>(pos, box, nullptr, pgv)));
 }

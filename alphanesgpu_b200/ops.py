@@ -282,3 +282,86 @@ def compute_force_tripl_grad(prevgrad, netderiv, radial_descriptor, angular_desc
                                                     _p(ntr), nf, Nl, N, nt, Fa, _p(gn), _p(ga), _p(gck)),
           "ComputeForceTriplGrad")
     return gn, ga, gck
+
+
+def compute_force_radial_virial(netderiv, descriptor_derivative_rad, interaction_map_rad, radial_descriptor,
+                                alpha2b_parameters, type_emb2b_parameters, type_map, tipos, actual_type, pos, box):
+    """Op ComputeForceRadialVirial -> (force[nf,3N], virial[nf,9])."""
+    ctx = _ctx_for(netderiv)
+    nd, dd, rd, a2, e2, ps, bx = _real(ctx, netderiv, descriptor_derivative_rad, radial_descriptor,
+                                       alpha2b_parameters, type_emb2b_parameters, pos, box)
+    im2, tm = _int(interaction_map_rad, type_map)
+    tp, at = _dev_int(tipos, nd.device), _dev_int(actual_type, nd.device)
+    nf, Nl, Fr = nd.shape
+    N, nt = tm.shape[0], tp.shape[0]
+    out = torch.empty(nf, 3 * N, dtype=ctx.dtype, device=nd.device)
+    vir = torch.empty(nf, 9, dtype=ctx.dtype, device=nd.device)
+    check(_lib.lib().stafb_compute_force_radial_virial(ctx.h, ctx.stream(), _p(nd), _p(dd), _p(im2), _p(rd), _p(a2),
+                                                       _p(e2), _p(tm), _p(tp), _p(at), _p(ps), _p(bx), nf, Nl, N, nt,
+                                                       Fr, _p(out), _p(vir)), "ComputeForceRadialVirial")
+    return out, vir
+
+
+def compute_force_tripl_virial(netderiv, radial_descriptor, angular_descriptor, descriptor_derivative_rad,
+                               descriptor_derivative_ang, interaction_map_rad, interaction_map_ang,
+                               alpha3b_parameters, type_emb3b_parameters, type_map, tipos, actual_type, num_triplets,
+                               pos, box):
+    """Op ComputeForceTriplVirial -> (force[nf,3N], virial[nf,9])."""
+    ctx = _ctx_for(netderiv)
+    nd, rd, ad, ddr, dda, a3, e3, ps, bx = _real(ctx, netderiv, radial_descriptor, angular_descriptor,
+                                                 descriptor_derivative_rad, descriptor_derivative_ang,
+                                                 alpha3b_parameters, type_emb3b_parameters, pos, box)
+    im2, im3, tm, ntr = _int(interaction_map_rad, interaction_map_ang, type_map, num_triplets)
+    tp, at = _dev_int(tipos, nd.device), _dev_int(actual_type, nd.device)
+    nf, Nl, Fa = nd.shape
+    N, nt = tm.shape[0], tp.shape[0]
+    out = torch.empty(nf, 3 * N, dtype=ctx.dtype, device=nd.device)
+    vir = torch.empty(nf, 9, dtype=ctx.dtype, device=nd.device)
+    check(_lib.lib().stafb_compute_force_tripl_virial(ctx.h, ctx.stream(), _p(nd), _p(rd), _p(ad), _p(ddr), _p(dda),
+                                                      _p(im2), _p(im3), _p(a3), _p(e3), _p(tm), _p(tp), _p(at),
+                                                      _p(ntr), _p(ps), _p(bx), nf, Nl, N, nt, Fa, _p(out), _p(vir)),
+          "ComputeForceTriplVirial")
+    return out, vir
+
+
+def compute_force_radial_virial_grad(prevgrad, prevgrad_virial, netderiv, descriptor_derivative_rad,
+                                     interaction_map_rad, radial_descriptor, alpha2b_parameters,
+                                     type_emb2b_parameters, type_map, tipos, actual_type, pos, box):
+    """Op ComputeForceRadialVirialGrad -> (gradnet[nf,Nl,Fr], grad_alpha2b[nt,Fr], grad_emb2b[nt,Fr])."""
+    ctx = _ctx_for(prevgrad)
+    pg, pv, nd, dd, rd, a2, e2, ps, bx = _real(ctx, prevgrad, prevgrad_virial, netderiv, descriptor_derivative_rad,
+                                               radial_descriptor, alpha2b_parameters, type_emb2b_parameters, pos, box)
+    im2, tm = _int(interaction_map_rad, type_map)
+    tp, at = _dev_int(tipos, nd.device), _dev_int(actual_type, nd.device)
+    nf, Nl, Fr = nd.shape
+    N, nt = tm.shape[0], tp.shape[0]
+    gn, ga, ge = torch.empty_like(nd), torch.empty_like(a2), torch.empty_like(a2)
+    check(_lib.lib().stafb_compute_force_radial_virial_grad(ctx.h, ctx.stream(), _p(pg), _p(pv), _p(nd), _p(dd),
+                                                            _p(im2), _p(rd), _p(a2), _p(e2), _p(tm), _p(tp), _p(at),
+                                                            _p(ps), _p(bx), nf, Nl, N, nt, Fr, _p(gn), _p(ga),
+                                                            _p(ge)), "ComputeForceRadialVirialGrad")
+    return gn, ga, ge
+
+
+def compute_force_tripl_virial_grad(prevgrad, prevgrad_virial, netderiv, radial_descriptor, angular_descriptor,
+                                    descriptor_derivative_rad, descriptor_derivative_ang, interaction_map_rad,
+                                    interaction_map_ang, alpha3b_parameters, type_emb3b_parameters, type_map, tipos,
+                                    actual_type, num_triplets, pos, box):
+    """Op ComputeForceTriplVirialGrad -> (gradnet[nf,Nl,Fa], gradalpha[C,3Fa], gradck[C,Fa] == 0)."""
+    ctx = _ctx_for(prevgrad)
+    pg, pv, nd, rd, ad, ddr, dda, a3, e3, ps, bx = _real(ctx, prevgrad, prevgrad_virial, netderiv, radial_descriptor,
+                                                         angular_descriptor, descriptor_derivative_rad,
+                                                         descriptor_derivative_ang, alpha3b_parameters,
+                                                         type_emb3b_parameters, pos, box)
+    im2, im3, tm, ntr = _int(interaction_map_rad, interaction_map_ang, type_map, num_triplets)
+    tp, at = _dev_int(tipos, nd.device), _dev_int(actual_type, nd.device)
+    nf, Nl, Fa = nd.shape
+    N, nt = tm.shape[0], tp.shape[0]
+    gn, ga = torch.empty_like(nd), torch.empty_like(a3)
+    gck = torch.empty(a3.shape[0], Fa, dtype=ctx.dtype, device=nd.device)
+    check(_lib.lib().stafb_compute_force_tripl_virial_grad(ctx.h, ctx.stream(), _p(pg), _p(pv), _p(nd), _p(rd),
+                                                           _p(ad), _p(ddr), _p(dda), _p(im2), _p(im3), _p(a3),
+                                                           _p(e3), _p(tm), _p(tp), _p(at), _p(ntr), _p(ps), _p(bx),
+                                                           nf, Nl, N, nt, Fa, _p(gn), _p(ga), _p(gck)),
+          "ComputeForceTriplVirialGrad")
+    return gn, ga, gck

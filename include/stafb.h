@@ -161,6 +161,49 @@ int stafb_compute_force_tripl_grad(stafb_ctx* ctx, void* stream, const void* pre
                                    const int* tipos_d, const int* actual_type_d, const int* num_triplets_d, int nf,
                                    int Nl, int N, int nt, int Fa, void* gradnet_d, void* gradalpha_d, void* gradck_d);
 
+/* ComputeForceRadialVirial (force/rad/reforce.cc:133-146): ComputeForceRadial plus virial[nf,9] (row-major 3x3,
+ * W_ab = -sum g_a r_b with r = r_i - r_j under the minimum image of box; zero-filled, then this species'
+ * contribution).  pos[nf,3N] Cartesian, box[nf,6]. */
+int stafb_compute_force_radial_virial(stafb_ctx* ctx, void* stream, const void* netderiv_d,
+                                      const void* descriptor_derivative_rad_d, const int* interaction_map_rad_d,
+                                      const void* radial_descriptor_d, const void* alpha2b_d,
+                                      const void* type_emb2b_sq_d, const int* type_map_d, const int* tipos_d,
+                                      const int* actual_type_d, const void* pos_d, const void* box_d, int nf, int Nl,
+                                      int N, int nt, int Fr, void* force_d, void* virial_d);
+
+/* ComputeForceTriplVirial (force/ang/reforce.cc:159-176) */
+int stafb_compute_force_tripl_virial(stafb_ctx* ctx, void* stream, const void* netderiv_d,
+                                     const void* radial_descriptor_d, const void* angular_descriptor_d,
+                                     const void* descriptor_derivative_rad_d, const void* descriptor_derivative_ang_d,
+                                     const int* interaction_map_rad_d, const int* interaction_map_ang_d,
+                                     const void* alpha3b_d, const void* type_emb3b_sq_d, const int* type_map_d,
+                                     const int* tipos_d, const int* actual_type_d, const int* num_triplets_d,
+                                     const void* pos_d, const void* box_d, int nf, int Nl, int N, int nt, int Fa,
+                                     void* force_d, void* virial_d);
+
+/* ComputeForceRadialVirialGrad (grad_force/rad/reforce.cc:160-176): backward of ComputeForceRadialVirial for the
+ * cotangents prevgrad[nf,3N] on the force and prevgrad_virial[nf,9] on the virial. */
+int stafb_compute_force_radial_virial_grad(stafb_ctx* ctx, void* stream, const void* prevgrad_d,
+                                           const void* prevgrad_virial_d, const void* netderiv_d,
+                                           const void* descriptor_derivative_rad_d, const int* interaction_map_rad_d,
+                                           const void* radial_descriptor_d, const void* alpha2b_d,
+                                           const void* type_emb2b_sq_d, const int* type_map_d, const int* tipos_d,
+                                           const int* actual_type_d, const void* pos_d, const void* box_d, int nf,
+                                           int Nl, int N, int nt, int Fr, void* gradnet_d, void* grad_alpha2b_d,
+                                           void* grad_emb2b_d);
+
+/* ComputeForceTriplVirialGrad (grad_force/ang/reforce.cc:186-206); gradck is zeros like in ComputeForceTriplGrad */
+int stafb_compute_force_tripl_virial_grad(stafb_ctx* ctx, void* stream, const void* prevgrad_d,
+                                          const void* prevgrad_virial_d, const void* netderiv_d,
+                                          const void* radial_descriptor_d, const void* angular_descriptor_d,
+                                          const void* descriptor_derivative_rad_d,
+                                          const void* descriptor_derivative_ang_d, const int* interaction_map_rad_d,
+                                          const int* interaction_map_ang_d, const void* alpha3b_d,
+                                          const void* type_emb3b_sq_d, const int* type_map_d, const int* tipos_d,
+                                          const int* actual_type_d, const int* num_triplets_d, const void* pos_d,
+                                          const void* box_d, int nf, int Nl, int N, int nt, int Fa, void* gradnet_d,
+                                          void* gradalpha_d, void* gradck_d);
+
 /* ---- fused path ----------------------------------------------------------------------------
  * One model = nt per-species blocks of trained parameters in ONE flat buffer `theta`
  *     alpha2b[nt,Fr_t] | alpha3b[C,3Fa_t] | mu[Fr_t+Fa_t] | W0[in,out] b0 | W1 b1 | ...   (t = 0..nt-1)

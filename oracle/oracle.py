@@ -147,30 +147,44 @@ def af_angular(angdescr, des3bsupp, intmap3b, alpha3b, e3, type_map, numtriplet)
     return out
 
 
-def force_radial(netderiv, der2b, intmap2b, raddescr, alpha2b, e2, type_map, shift):
+def _vir_in(pos, box, dt):
+    if pos is None:
+        return None, None
+    return _c(pos, dt), _c(box, dt)
+
+
+def force_radial(netderiv, der2b, intmap2b, raddescr, alpha2b, e2, type_map, shift, pos=None, box=None):
+    """ComputeForceRadial; with pos[nf,3N] and box[nf,6] the ...Virial variant: returns (force, virial[nf,9])."""
     dt = raddescr.dtype
     nf, Nl, nr = raddescr.shape
     Fr = alpha2b.shape[1]
     N = len(type_map)
     out = np.zeros((nf, 3 * N), dt)
+    p_, b_ = _vir_in(pos, box, dt)
+    vir = None if pos is None else np.zeros((nf, 9), dt)
     getattr(lib(), "stafo_force_radial_" + _sfx(dt))(
         nf, Nl, N, nr, Fr, int(shift), _p(_c(netderiv, dt)), _p(_c(der2b, dt)), _p(_c(intmap2b, np.int32)),
-        _p(_c(raddescr, dt)), _p(_c(alpha2b, dt)), _p(_c(e2, dt)), _p(_c(type_map, np.int32)), _p(out))
-    return out
+        _p(_c(raddescr, dt)), _p(_c(alpha2b, dt)), _p(_c(e2, dt)), _p(_c(type_map, np.int32)), _p(out),
+        _p(p_), _p(b_), _p(vir))
+    return out if pos is None else (out, vir)
 
 
-def force_tripl(netderiv, des3bsupp, angdescr, der3bsupp, der3b, intmap3b, alpha3b, e3, type_map, numtriplet, shift):
+def force_tripl(netderiv, des3bsupp, angdescr, der3bsupp, der3b, intmap3b, alpha3b, e3, type_map, numtriplet, shift,
+                pos=None, box=None):
+    """ComputeForceTripl; with pos and box the ...Virial variant: returns (force, virial[nf,9])."""
     dt = angdescr.dtype
     nf, Nl, na = angdescr.shape
     nr = des3bsupp.shape[2]
     Fa = alpha3b.shape[1] // 3
     N = len(type_map)
     out = np.zeros((nf, 3 * N), dt)
+    p_, b_ = _vir_in(pos, box, dt)
+    vir = None if pos is None else np.zeros((nf, 9), dt)
     getattr(lib(), "stafo_force_tripl_" + _sfx(dt))(
         nf, Nl, N, nr, na, Fa, int(shift), _p(_c(netderiv, dt)), _p(_c(des3bsupp, dt)), _p(_c(angdescr, dt)),
         _p(_c(der3bsupp, dt)), _p(_c(der3b, dt)), _p(_c(intmap3b, np.int32)), _p(_c(alpha3b, dt)), _p(_c(e3, dt)),
-        _p(_c(type_map, np.int32)), _p(_c(numtriplet, np.int32)), _p(out))
-    return out
+        _p(_c(type_map, np.int32)), _p(_c(numtriplet, np.int32)), _p(out), _p(p_), _p(b_), _p(vir))
+    return out if pos is None else (out, vir)
 
 
 def grad_af_radial(prevgrad, raddescr, intmap2b, alpha2b, e2, type_map):
@@ -198,8 +212,12 @@ def grad_af_angular(prevgrad, angdescr, des3bsupp, intmap3b, alpha3b, e3, type_m
     return ga, ge
 
 
-def grad_force_radial(prevgrad, netderiv, der2b, intmap2b, raddescr, alpha2b, e2, type_map, shift):
+def grad_force_radial(prevgrad, netderiv, der2b, intmap2b, raddescr, alpha2b, e2, type_map, shift, pos=None,
+                      box=None, prevgrad_virial=None):
+    """ComputeForceRadialGrad; with pos, box and prevgrad_virial[nf,9] the ...VirialGrad variant."""
     dt = raddescr.dtype
+    p_, b_ = _vir_in(pos, box, dt)
+    w_ = None if prevgrad_virial is None else _c(prevgrad_virial, dt)
     nf, Nl, nr = raddescr.shape
     nt, Fr = alpha2b.shape
     N = len(type_map)
@@ -207,13 +225,16 @@ def grad_force_radial(prevgrad, netderiv, der2b, intmap2b, raddescr, alpha2b, e2
     getattr(lib(), "stafo_grad_force_radial_" + _sfx(dt))(
         nf, Nl, N, nr, Fr, nt, int(shift), _p(_c(prevgrad, dt)), _p(_c(netderiv, dt)), _p(_c(der2b, dt)),
         _p(_c(intmap2b, np.int32)), _p(_c(raddescr, dt)), _p(_c(alpha2b, dt)), _p(_c(e2, dt)),
-        _p(_c(type_map, np.int32)), _p(gn), _p(ga), _p(ge))
+        _p(_c(type_map, np.int32)), _p(gn), _p(ga), _p(ge), _p(p_), _p(b_), _p(w_))
     return gn, ga, ge
 
 
 def grad_force_tripl(prevgrad, netderiv, des3bsupp, angdescr, der3bsupp, der3b, intmap3b, alpha3b, e3, type_map,
-                     numtriplet, shift):
+                     numtriplet, shift, pos=None, box=None, prevgrad_virial=None):
+    """ComputeForceTriplGrad; with pos, box and prevgrad_virial[nf,9] the ...VirialGrad variant."""
     dt = angdescr.dtype
+    p_, b_ = _vir_in(pos, box, dt)
+    w_ = None if prevgrad_virial is None else _c(prevgrad_virial, dt)
     nf, Nl, na = angdescr.shape
     nr = des3bsupp.shape[2]
     Cc = alpha3b.shape[0]
@@ -224,7 +245,7 @@ def grad_force_tripl(prevgrad, netderiv, des3bsupp, angdescr, der3bsupp, der3b, 
         nf, Nl, N, nr, na, Fa, Cc, int(shift), _p(_c(prevgrad, dt)), _p(_c(netderiv, dt)), _p(_c(des3bsupp, dt)),
         _p(_c(angdescr, dt)), _p(_c(der3bsupp, dt)), _p(_c(der3b, dt)), _p(_c(intmap3b, np.int32)),
         _p(_c(alpha3b, dt)), _p(_c(e3, dt)), _p(_c(type_map, np.int32)), _p(_c(numtriplet, np.int32)), _p(gn), _p(ga),
-        _p(gc))
+        _p(gc), _p(p_), _p(b_), _p(w_))
     return gn, ga, gc
 
 

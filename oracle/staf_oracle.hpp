@@ -415,11 +415,32 @@ void af_angular(int nf, int Nl, int nr, int na, int Fa, const T* angdescr, const
   }
 }
 
+// Minimum-image separation r_i - r_j from Cartesian positions, as the virial kernels form it
+// (STAF/include/staf_force_pbc.cuh:15-49: Cartesian -> fractional with the inverse box, rint wrap, back).
+template <class T>
+inline void mic_cart(const T* pi, const T* pj, const T* B, T* d) {
+  T I[6];
+  I[0] = T(1.) / B[0];
+  I[1] = -B[1] / (B[0] * B[3]);
+  I[2] = (B[1] * B[4]) / (B[0] * B[3] * B[5]) - B[2] / (B[0] * B[5]);
+  I[3] = T(1.) / B[3];
+  I[4] = -B[4] / (B[3] * B[5]);
+  I[5] = T(1.) / B[5];
+  T fi[3] = {I[0] * pi[0] + I[1] * pi[1] + I[2] * pi[2], I[3] * pi[1] + I[4] * pi[2], I[5] * pi[2]};
+  T fj[3] = {I[0] * pj[0] + I[1] * pj[1] + I[2] * pj[2], I[3] * pj[1] + I[4] * pj[2], I[5] * pj[2]};
+  T r[3] = {fi[0] - fj[0], fi[1] - fj[1], fi[2] - fj[2]};
+  for (int a = 0; a < 3; a++) r[a] -= std::rint(r[a]);
+  d[0] = B[0] * r[0] + B[1] * r[1] + B[2] * r[2];
+  d[1] = B[3] * r[1] + B[4] * r[2];
+  d[2] = B[5] * r[2];
+}
+
 // ComputeForceRadial: force/rad/reforce.cu.cc:45-136.  force[nf,3N] is ADDED to.
 template <class T>
 void force_radial(int nf, int Nl, int N, int nr, int Fr, int shift, const T* netderiv, const T* der2b,
                   const int* intmap2b, const T* raddescr, const T* alpha2b, const T* e2, const int* type_map,
-                  double* force /*[nf,3N] double accumulators*/) {
+                  double* force /*[nf,3N] double accumulators*/, const T* pos = nullptr, const T* box = nullptr,
+                  double* virial = nullptr /*[nf,9]: ComputeForceRadialVirial, force/rad/reforce.cu.cc:174-287*/) {
 #pragma omp parallel for schedule(static)
   for (int bp = 0; bp < nf * Nl; bp++) {
     int b = bp / Nl, par = bp % Nl, ipar = par + shift;
@@ -442,16 +463,23 @@ void force_radial(int nf, int Nl, int N, int nr, int Fr, int shift, const T* net
         }
       }
       for (int a = 0; a < 3; a++) atomic_add(&force[((size_t)b * N + nj) * 3 + a], fj[a]);
+      if (virial) {  // W_ab -= g_a r_b
+        T r[3];
+        mic_cart(pos + ((size_t)b * N + ipar) * 3, pos + ((size_t)b * N + nj) * 3, box + (size_t)b * 6, r);
+        for (int a = 0; a < 3; a++)
+          for (int c = 0; c < 3; c++) atomic_add(&virial[(size_t)b * 9 + a * 3 + c], -fj[a] * (double)r[c]);
+      }
     }
     for (int a = 0; a < 3; a++) atomic_add(&force[((size_t)b * N + ipar) * 3 + a], fi[a]);
   }
 }
 
-// ComputeForceTripl: force/ang/reforce.cu.cc:48-232.
+// ComputeForceTripl: force/ang/reforce.cu.cc:48-232; with pos/box/virial the ...Virial variant (:269-457).
 template <class T>
 void force_tripl(int nf, int Nl, int N, int nr, int na, int Fa, int shift, const T* netderiv, const T* ds,
                  const T* angdescr, const T* der3bsupp, const T* der3b, const int* intmap3b, const T* alpha3b,
-                 const T* e3, const int* type_map, const int* numtriplet, double* force) {
+                 const T* e3, const int* type_map, const int* numtriplet, double* force, const T* pos = nullptr,
+                 const T* box = nullptr, double* virial = nullptr) {
 #pragma omp parallel for schedule(dynamic, 8)
   for (int bp = 0; bp < nf * Nl; bp++) {
     int b = bp / Nl, par = bp % Nl, ipar = par + shift;
@@ -490,6 +518,14 @@ void force_tripl(int nf, int Nl, int N, int nr, int na, int Fa, int shift, const
       for (int a = 0; a < 3; a++) {
         atomic_add(&force[((size_t)b * N + nj) * 3 + a], fj[a]);
         atomic_add(&force[((size_t)b * N + nk) * 3 + a], fk[a]);
+      }
+      if (virial) {  // W_ab -= f_ij,a r_ij,b + f_ik,a r_ik,b
+        T rij[3], rik[3];
+        mic_cart(pos + ((size_t)b * N + ipar) * 3, pos + ((size_t)b * N + nj) * 3, box + (size_t)b * 6, rij);
+        mic_cart(pos + ((size_t)b * N + ipar) * 3, pos + ((size_t)b * N + nk) * 3, box + (size_t)b * 6, rik);
+        for (int a = 0; a < 3; a++)
+          for (int c = 0; c < 3; c++)
+            atomic_add(&virial[(size_t)b * 9 + a * 3 + c], -(fj[a] * (double)rij[c] + fk[a] * (double)rik[c]));
       }
     }
     for (int a = 0; a < 3; a++) atomic_add(&force[((size_t)b * N + ipar) * 3 + a], fi[a]);
@@ -566,7 +602,8 @@ template <class T>
 void grad_force_radial(int nf, int Nl, int N, int nr, int Fr, int shift, const T* prevgrad /*[nf,3N]*/,
                        const T* netderiv, const T* der2b, const int* intmap2b, const T* raddescr, const T* alpha2b,
                        const T* e2, const int* type_map, int nt, double* gradnet /*[nf,Nl,Fr]*/,
-                       double* g_alpha_out, double* g_emb_out) {
+                       double* g_alpha_out, double* g_emb_out, const T* pos = nullptr, const T* box = nullptr,
+                       const T* wbar = nullptr /*[nf,9] dL/dvirial: ...VirialGrad, grad_force/rad/reforce.cu.cc:165-234*/) {
   ThreadAcc ta((size_t)2 * nt * Fr);
 #pragma omp parallel for schedule(static)
   for (int bp = 0; bp < nf * Nl; bp++) {
@@ -578,10 +615,17 @@ void grad_force_radial(int nf, int Nl, int N, int nr, int Fr, int shift, const T
       int nj = intmap2b[(size_t)bp * (nr + 1) + 1 + j];
       int cht = type_map[nj];
       T d = raddescr[(size_t)bp * nr + j];
+      T wdot[3] = {0, 0, 0};  // (dL/dW r)_a: the virial cotangent acts like a shift of the neighbour's force cotangent
+      if (wbar) {
+        T r[3];
+        mic_cart(pos + ((size_t)b * N + ipar) * 3, pos + ((size_t)b * N + nj) * 3, box + (size_t)b * 6, r);
+        const T* Wg = wbar + (size_t)b * 9;
+        for (int a = 0; a < 3; a++) wdot[a] = Wg[a * 3] * r[0] + Wg[a * 3 + 1] * r[1] + Wg[a * 3 + 2] * r[2];
+      }
       for (int i = 0; i < Fr; i++) {
         T a1 = 0, a2 = 0, a3 = 0;
         for (int a = 0; a < 3; a++) {
-          T pe = prevgrad[((size_t)b * N + ipar) * 3 + a], pn = prevgrad[((size_t)b * N + nj) * 3 + a];
+          T pe = prevgrad[((size_t)b * N + ipar) * 3 + a], pn = prevgrad[((size_t)b * N + nj) * 3 + a] - wdot[a];
           T common = T(0.5) * der2b[((size_t)bp * 3 + a) * nr + j];
           T al = alpha2b[Fr * cht + i], ch = e2[Fr * cht + i];
           T s1 = std::exp(al * d);
@@ -612,7 +656,8 @@ template <class T>
 void grad_force_tripl(int nf, int Nl, int N, int nr, int na, int Fa, int shift, const T* prevgrad, const T* netderiv,
                       const T* ds, const T* angdescr, const T* der3bsupp, const T* der3b, const int* intmap3b,
                       const T* alpha3b, const T* e3, const int* type_map, const int* numtriplet, int C,
-                      double* gradnet /*[nf,Nl,Fa]*/, double* g_alpha3_out /*[C,3Fa]*/) {
+                      double* gradnet /*[nf,Nl,Fa]*/, double* g_alpha3_out /*[C,3Fa]*/, const T* pos = nullptr,
+                      const T* box = nullptr, const T* wbar = nullptr /*grad_force/ang/reforce.cu.cc:274-446*/) {
   ThreadAcc ta((size_t)C * 3 * Fa);
 #pragma omp parallel for schedule(dynamic, 8)
   for (int bp = 0; bp < nf * Nl; bp++) {
@@ -627,6 +672,17 @@ void grad_force_tripl(int nf, int Nl, int N, int nr, int na, int Fa, int shift, 
       int sum = type_map[nj] + type_map[nk];
       T t = angdescr[(size_t)bp * na + nn];
       T rj = ds[(size_t)bp * nr + j], rk = ds[(size_t)bp * nr + k];
+      T wij[3] = {0, 0, 0}, wik[3] = {0, 0, 0};
+      if (wbar) {
+        T rij[3], rik[3];
+        mic_cart(pos + ((size_t)b * N + ipar) * 3, pos + ((size_t)b * N + nj) * 3, box + (size_t)b * 6, rij);
+        mic_cart(pos + ((size_t)b * N + ipar) * 3, pos + ((size_t)b * N + nk) * 3, box + (size_t)b * 6, rik);
+        const T* Wg = wbar + (size_t)b * 9;
+        for (int a = 0; a < 3; a++) {
+          wij[a] = Wg[a * 3] * rij[0] + Wg[a * 3 + 1] * rij[1] + Wg[a * 3 + 2] * rij[2];
+          wik[a] = Wg[a * 3] * rik[0] + Wg[a * 3 + 1] * rik[1] + Wg[a * 3 + 2] * rik[2];
+        }
+      }
       for (int c = 0; c < Fa; c++) {
         T NG = netderiv[(size_t)bp * Fa + c];
         T ax = alpha3b[(sum * Fa + c) * 3], ay = alpha3b[(sum * Fa + c) * 3 + 1], az = alpha3b[(sum * Fa + c) * 3 + 2];
@@ -644,7 +700,7 @@ void grad_force_tripl(int nf, int Nl, int N, int nr, int na, int Fa, int shift, 
           T ix = der3b[(((size_t)bp * 3 + cor) * na + nn) * 2], iy = der3b[(((size_t)bp * 3 + cor) * na + nn) * 2 + 1];
           T irj = der3bsupp[((size_t)bp * 3 + cor) * nr + j], irk = der3bsupp[((size_t)bp * 3 + cor) * nr + k];
           T pl = prevgrad[((size_t)b * N + ipar) * 3 + cor];
-          T pj = prevgrad[((size_t)b * N + nj) * 3 + cor], pk = prevgrad[((size_t)b * N + nk) * 3 + cor];
+          T pj = prevgrad[((size_t)b * N + nj) * 3 + cor] - wij[cor], pk = prevgrad[((size_t)b * N + nk) * 3 + cor] - wik[cor];
           T gij = ch * delta * ix + ch * Bj * irj;
           T gik = ch * delta * iy + ch * Bk * irk;
           acc1 += -pl * T(0.5) * (gij + gik);

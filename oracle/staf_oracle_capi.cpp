@@ -59,19 +59,24 @@ static ModelShape make_shape(const int* d) {
   }                                                                                                                    \
   extern "C" void stafo_force_radial_##SFX(int nf, int Nl, int N, int nr, int Fr, int shift, const T* netderiv,        \
                                            const T* der2b, const int* intmap2b, const T* raddescr, const T* alpha2b,   \
-                                           const T* e2, const int* type_map, T* force) {                               \
-    std::vector<double> F((size_t)nf * 3 * N, 0.0);                                                                    \
-    force_radial<T>(nf, Nl, N, nr, Fr, shift, netderiv, der2b, intmap2b, raddescr, alpha2b, e2, type_map, F.data());   \
+                                           const T* e2, const int* type_map, T* force, const T* pos,            \
+                                           const T* box, T* virial) {                                                   \
+    std::vector<double> F((size_t)nf * 3 * N, 0.0), W((size_t)nf * 9, 0.0);                                            \
+    force_radial<T>(nf, Nl, N, nr, Fr, shift, netderiv, der2b, intmap2b, raddescr, alpha2b, e2, type_map, F.data(),    \
+                    pos, box, virial ? W.data() : nullptr);                                                            \
     for (size_t i = 0; i < F.size(); i++) force[i] = (T)F[i];                                                          \
+    if (virial) for (size_t i = 0; i < W.size(); i++) virial[i] = (T)W[i];                                             \
   }                                                                                                                    \
   extern "C" void stafo_force_tripl_##SFX(int nf, int Nl, int N, int nr, int na, int Fa, int shift, const T* netderiv, \
                                           const T* ds, const T* angdescr, const T* der3bsupp, const T* der3b,          \
                                           const int* intmap3b, const T* alpha3b, const T* e3, const int* type_map,     \
-                                          const int* numtriplet, T* force) {                                           \
-    std::vector<double> F((size_t)nf * 3 * N, 0.0);                                                                    \
+                                          const int* numtriplet, T* force, const T* pos, const T* box,                 \
+                                          T* virial) {                                                                 \
+    std::vector<double> F((size_t)nf * 3 * N, 0.0), W((size_t)nf * 9, 0.0);                                            \
     force_tripl<T>(nf, Nl, N, nr, na, Fa, shift, netderiv, ds, angdescr, der3bsupp, der3b, intmap3b, alpha3b, e3,      \
-                   type_map, numtriplet, F.data());                                                                    \
+                   type_map, numtriplet, F.data(), pos, box, virial ? W.data() : nullptr);                             \
     for (size_t i = 0; i < F.size(); i++) force[i] = (T)F[i];                                                          \
+    if (virial) for (size_t i = 0; i < W.size(); i++) virial[i] = (T)W[i];                                             \
   }                                                                                                                    \
   extern "C" void stafo_grad_af_radial_##SFX(int nf, int Nl, int nr, int Fr, int nt, const T* prevgrad,                \
                                              const T* raddescr, const int* intmap2b, const T* alpha2b, const T* e2,    \
@@ -93,10 +98,11 @@ static ModelShape make_shape(const int* d) {
   extern "C" void stafo_grad_force_radial_##SFX(int nf, int Nl, int N, int nr, int Fr, int nt, int shift,              \
                                                 const T* prevgrad, const T* netderiv, const T* der2b,                  \
                                                 const int* intmap2b, const T* raddescr, const T* alpha2b,              \
-                                                const T* e2, const int* type_map, T* gradnet, T* g_alpha, T* g_emb) {  \
+                                                const T* e2, const int* type_map, T* gradnet, T* g_alpha, T* g_emb,    \
+                                                const T* pos, const T* box, const T* wbar) {                           \
     std::vector<double> gn((size_t)nf * Nl * Fr, 0.0), ga(nt * Fr, 0.0), ge(nt * Fr, 0.0);                             \
     grad_force_radial<T>(nf, Nl, N, nr, Fr, shift, prevgrad, netderiv, der2b, intmap2b, raddescr, alpha2b, e2,         \
-                         type_map, nt, gn.data(), ga.data(), ge.data());                                               \
+                         type_map, nt, gn.data(), ga.data(), ge.data(), pos, box, wbar);                               \
     for (size_t i = 0; i < gn.size(); i++) gradnet[i] = (T)gn[i];                                                      \
     for (int i = 0; i < nt * Fr; i++) { g_alpha[i] = (T)ga[i]; g_emb[i] = (T)ge[i]; }                                  \
   }                                                                                                                    \
@@ -104,10 +110,11 @@ static ModelShape make_shape(const int* d) {
                                                const T* prevgrad, const T* netderiv, const T* ds, const T* angdescr,   \
                                                const T* der3bsupp, const T* der3b, const int* intmap3b,                \
                                                const T* alpha3b, const T* e3, const int* type_map,                     \
-                                               const int* numtriplet, T* gradnet, T* g_alpha3, T* g_ck) {              \
+                                               const int* numtriplet, T* gradnet, T* g_alpha3, T* g_ck, const T* pos,  \
+                                               const T* box, const T* wbar) {                                          \
     std::vector<double> gn((size_t)nf * Nl * Fa, 0.0), ga((size_t)C * 3 * Fa, 0.0);                                    \
     grad_force_tripl<T>(nf, Nl, N, nr, na, Fa, shift, prevgrad, netderiv, ds, angdescr, der3bsupp, der3b, intmap3b,    \
-                        alpha3b, e3, type_map, numtriplet, C, gn.data(), ga.data());                                   \
+                        alpha3b, e3, type_map, numtriplet, C, gn.data(), ga.data(), pos, box, wbar);                   \
     for (size_t i = 0; i < gn.size(); i++) gradnet[i] = (T)gn[i];                                                      \
     for (int i = 0; i < C * 3 * Fa; i++) g_alpha3[i] = (T)ga[i];                                                       \
     for (int i = 0; i < C * Fa; i++) g_ck[i] = T(0);                                                                   \

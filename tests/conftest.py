@@ -64,3 +64,37 @@ def tie_groups_equal(with_a, with_b, d2, howmany):
                 assert with_a[i, k] == with_b[i, k], (i, k)
             k = e
     return groups
+
+
+def oracle_force_and_virial(oracle, shape, theta, emb, pos, box):
+    """Total force and virial of the op chain (descriptors -> AF -> MLP -> ...Virial force ops), double."""
+    import numpy as np
+    dt = np.float64
+    nf, N, nt, C = pos.shape[0], shape.N, shape.nt, shape.C
+    ref = oracle.descriptors(CFG["Rc"], CFG["Rs"], CFG["Ra"], CFG["nr"], CFG["na"], pos, box, dt)
+    tm = shape.type_map
+    F, W, E = np.zeros((nf, 3 * N)), np.zeros((nf, 9)), np.zeros(nf)
+    for t in range(nt):
+        s, Nl = shape.shift(t), shape.tipos[t]
+        d = {k: np.ascontiguousarray(v[:, s:s + Nl]) for k, v in ref.items() if isinstance(v, np.ndarray) and v.ndim >= 2}
+        o = shape.offsets(t)
+        Fr, Fa = shape.Fr[t], shape.Fa[t]
+        a2 = theta[o["a2"]:o["a2"] + nt * Fr].reshape(nt, Fr)
+        a3 = theta[o["a3"]:o["a3"] + C * 3 * Fa].reshape(C, 3 * Fa)
+        e2 = emb[o["emb"]:o["emb"] + nt * Fr].reshape(nt, Fr)
+        e3 = emb[o["emb"] + nt * Fr:o["emb"] + nt * Fr + C * Fa].reshape(C, Fa)
+        mu = theta[o["mu"]:o["mu"] + Fr + Fa]
+        w = theta[o["w"]:o["a2"] + o["size"]]
+        af2 = oracle.af_radial(d["raddescr"], d["intmap2b"], a2, e2, tm)
+        af3 = oracle.af_angular(d["angdescr"], d["des3bsupp"], d["intmap3b"], a3, e3, tm, d["numtriplet"])
+        af = np.concatenate([af2, af3], axis=2).reshape(nf * Nl, Fr + Fa)
+        e, nd = oracle.mlp_eval(shape.widths, af, mu, w)
+        nd = nd.reshape(nf, Nl, Fr + Fa)
+        E += 0.5 * e.reshape(nf, Nl).sum(1)
+        f2, w2 = oracle.force_radial(np.ascontiguousarray(nd[..., :Fr]), d["der2b"], d["intmap2b"], d["raddescr"], a2,
+                                     e2, tm, s, pos, box)
+        f3, w3 = oracle.force_tripl(np.ascontiguousarray(nd[..., Fr:]), d["des3bsupp"], d["angdescr"], d["der3bsupp"],
+                                    d["der3b"], d["intmap3b"], a3, e3, tm, d["numtriplet"], s, pos, box)
+        F += f2 + f3
+        W += w2 + w3
+    return E, F, W

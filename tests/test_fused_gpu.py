@@ -119,3 +119,22 @@ def test_training_reduces_the_loss():
         m.adam_update(2e-3)
     assert np.isfinite(last) and last < first
     m.close()
+
+
+@pytest.mark.parametrize("dtype,tol", [(np.float32, 2e-5), (np.float64, 1e-10)])
+def test_energy_force_virial_matches_the_virial_ops(oracle, dtype, tol):
+    """stafb_energy_force_virial = sum over central species of ComputeForceRadialVirial + ComputeForceTriplVirial
+    (oracle op chain in double, pinned by the strain finite-difference test in tests/test_oracle.py)."""
+    from alphanesgpu_b200.model import StafModel
+    from conftest import oracle_force_and_virial
+    pos, box, tipos = synth.water_frames("water96", [1000, 1001])
+    shape = synth.baseline_shape(tipos)
+    theta, emb = synth.init_params(shape)
+    E, F, W = oracle_force_and_virial(oracle, shape, theta, emb, pos, box)
+    tdt = torch.float32 if dtype == np.float32 else torch.float64
+    m = StafModel(shape, CFG, theta, emb, 2, dtype=tdt, device="cuda:0")
+    e, f, w = m.energy_force_virial(torch.as_tensor(pos.astype(dtype)).cuda(), torch.as_tensor(box.astype(dtype)).cuda())
+    assert rel_err(e.cpu().numpy(), E) <= tol
+    assert rel_err(f.cpu().numpy(), F) <= tol
+    assert rel_err(w.cpu().numpy(), W) <= tol
+    m.close()

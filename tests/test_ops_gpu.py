@@ -140,6 +140,34 @@ def test_all_operators(ops, oracle, frame0, case, dtype):
         assert rel_err(gn.cpu().numpy(), rn) <= tol
         assert rel_err(ga.cpu().numpy(), ra) <= tol
         assert np.all(gck.cpu().numpy() == 0)
+        # ...Virial and ...VirialGrad variants (STAF/src/force/*/reforce.cc:133-146 / 159-176,
+        # STAF/src/grad_force/*/reforce.cc:160-176 / 186-206)
+        tpos, tbox = _t(pos), _t(box)
+        pW = rng.normal(size=(nf, 9)).astype(dtype)
+        f2v, w2 = ops.compute_force_radial_virial(_t(nd2), g["der2b"], g["intmap2b"], g["raddescr"], ta2, te2, ttm,
+                                                  tipos, t, tpos, tbox)
+        rf, rw = oracle.force_radial(nd2, d["der2b"], d["intmap2b"], d["raddescr"], a2, e2, tm, sh, pos, box)
+        assert rel_err(f2v.cpu().numpy(), rf) <= tol and rel_err(w2.cpu().numpy(), rw) <= 10 * tol
+        f3v, w3 = ops.compute_force_tripl_virial(_t(nd3), g["des3bsupp"], g["angdescr"], g["der3bsupp"], g["der3b"],
+                                                 g["intmap2b"], g["intmap3b"], ta3, te3, ttm, tipos, t,
+                                                 g["numtriplet"], tpos, tbox)
+        rf, rw = oracle.force_tripl(nd3, d["des3bsupp"], d["angdescr"], d["der3bsupp"], d["der3b"], d["intmap3b"],
+                                    a3, e3, tm, d["numtriplet"], sh, pos, box)
+        assert rel_err(f3v.cpu().numpy(), rf) <= tol and rel_err(w3.cpu().numpy(), rw) <= 10 * tol
+        gn, ga, ge = ops.compute_force_radial_virial_grad(_t(pF), _t(pW), _t(nd2), g["der2b"], g["intmap2b"],
+                                                          g["raddescr"], ta2, te2, ttm, tipos, t, tpos, tbox)
+        rn, ra, re = oracle.grad_force_radial(pF, nd2, d["der2b"], d["intmap2b"], d["raddescr"], a2, e2, tm, sh,
+                                              pos, box, pW)
+        assert rel_err(gn.cpu().numpy(), rn) <= tol
+        assert rel_err(ga.cpu().numpy(), ra) <= tol and rel_err(ge.cpu().numpy(), re) <= tol
+        gn, ga, gck = ops.compute_force_tripl_virial_grad(_t(pF), _t(pW), _t(nd3), g["des3bsupp"], g["angdescr"],
+                                                          g["der3bsupp"], g["der3b"], g["intmap2b"], g["intmap3b"],
+                                                          ta3, te3, ttm, tipos, t, g["numtriplet"], tpos, tbox)
+        rn, ra, rck = oracle.grad_force_tripl(pF, nd3, d["des3bsupp"], d["angdescr"], d["der3bsupp"], d["der3b"],
+                                              d["intmap3b"], a3, e3, tm, d["numtriplet"], sh, pos, box, pW)
+        assert rel_err(gn.cpu().numpy(), rn) <= tol
+        assert rel_err(ga.cpu().numpy(), ra) <= tol
+        assert np.all(gck.cpu().numpy() == 0)
 
 
 def test_overflow_is_a_status_not_an_exit(ops):

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 from alphanesgpu_b200 import params, synth
-from conftest import CFG, GOLDEN, rel_err, tie_groups_equal
+from conftest import CFG, GOLDEN, oracle_force_and_virial, rel_err, tie_groups_equal
 
 
 @pytest.mark.parametrize("key,tag", [(k, t) for k in ("frame0", "water96_s1000", "water768_s1100")
@@ -205,3 +205,33 @@ def test_model_dir_writer_round_trips(tmp_path):
     assert cfg2 == CFG and shape2.tipos == [5, 10] and shape2.widths == shape.widths
     assert shape2.Fr == shape.Fr and shape2.Fa == shape.Fa
     assert np.array_equal(theta2, theta) and np.array_equal(emb2, emb)
+
+
+def test_virial_is_minus_strain_derivative_of_the_energy_fd(oracle):
+    """Pins the ...Virial force ops: W_ab = -dE/d(eps_ab) for a homogeneous strain r -> (1 + eps) r of positions
+    and box (upper-triangular eps keeps the box upper-triangular), and W is symmetric."""
+    pos, box, shape, theta, emb, el, fl = _small_case(np.float64, nf=1)
+    sd = shape.desc()
+    E0, F, W = oracle_force_and_virial(oracle, shape, theta, emb, pos, box)
+    full = oracle.energy_force_grad(CFG, sd, pos, box, shape.type_map, theta, emb, np.float64, per_atom_energy=False)
+    assert abs(E0[0] - full["energy"][0]) < 1e-12 * abs(E0[0])
+    assert rel_err(F, full["force"]) < 1e-12
+    W = W[0].reshape(3, 3)
+    assert np.abs(W - W.T).max() < 1e-9 * np.abs(W).max()
+
+    def E(eps):
+        M = np.eye(3) + eps
+        p = (pos.reshape(-1, 3) @ M.T).reshape(1, -1)
+        b = box[0]
+        H = np.array([[b[0], b[1], b[2]], [0, b[3], b[4]], [0, 0, b[5]]])
+        H2 = M @ H
+        b2 = np.array([[H2[0, 0], H2[0, 1], H2[0, 2], H2[1, 1], H2[1, 2], H2[2, 2]]])
+        return float(oracle.energy_force_grad(CFG, sd, p, b2, shape.type_map, theta, emb, np.float64,
+                                              per_atom_energy=False)["energy"][0])
+    h = 1e-6
+    for a in range(3):
+        for c in range(a, 3):
+            eps = np.zeros((3, 3))
+            eps[a, c] = h
+            fd = (E(eps) - E(-eps)) / (2 * h)
+            assert abs(-fd - W[a, c]) < 2e-6 * np.abs(W).max(), (a, c, fd, W[a, c])
