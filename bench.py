@@ -184,7 +184,8 @@ def run_ours(args):
     launches_per_step = model.launches() + 2  # + Adam and its step counter
     torch.cuda.synchronize()
 
-    # ---- CUDA graphs: one per distinct batch (pointers differ); NCCL stays outside the graphs
+    # ---- CUDA graphs: one per distinct batch (pointers differ); the NCCL all-reduce stays between two graphs
+    # (capturing it into the graph made a 2-rank run hang on this pool, so it is not attempted)
     graphs = []
     side = torch.cuda.Stream(device=dev)
     side.wait_stream(torch.cuda.current_stream())
@@ -411,7 +412,7 @@ def run_ours(args):
                        "frames": "seeded synthetic water, 256 O + 512 H, L=19.6 A, %d distinct batches" % NB,
                        "model": "2 species, Fr=10, Fa=15, MLP 25-64-32-1 tanh", "parallelism": "dp%d" % world,
                        "l2": "flushed between steps (256 MiB write); per-step CUDA events summed",
-                       "launch": "CUDA graph replay per step",
+                       "launch": "CUDA graph replay per step" + ("" if world == 1 else ", NCCL all-reduce between two graphs"),
                        "vs_baseline_note": "published number is the reference on a V100 (README.md:42-45)"},
             "value_l2_warm": value_warm, "ms_per_step_min": float(per_step.min()),
             "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
