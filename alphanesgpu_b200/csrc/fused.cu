@@ -783,7 +783,7 @@ __global__ void __launch_bounds__(256)
            const T* __restrict__ e_label, const T* __restrict__ force, const T* __restrict__ f_label,
            const T* __restrict__ theta, T pe, T pf, T pb, T bound, int loss_kind, T* __restrict__ ebar,
            T* __restrict__ fbar, T* __restrict__ grad, double* __restrict__ losses, int* __restrict__ status,
-           const double* __restrict__ vacc, T* __restrict__ virial_out) {
+           const double* __restrict__ vacc, T* __restrict__ virial_out, double* __restrict__ mirror) {
   __shared__ double red[9];
   const int N = md.N;
   const int blk = blockIdx.x;
@@ -834,7 +834,14 @@ __global__ void __launch_bounds__(256)
     if (done == gridDim.x - 1) {
       __threadfence();
       const double le = atomicAdd(losses + 1, 0.0), lb = atomicAdd(losses + 2, 0.0), lf = atomicAdd(losses + 3, 0.0);
-      losses[0] = (double)pe * le + (double)pb * lb + (double)pf * lf;
+      const double tot = (double)pe * le + (double)pb * lb + (double)pf * lf;
+      losses[0] = tot;
+      if (mirror) {
+        // results straight into the caller's mapped host memory: 4 losses, then the status word (read and cleared)
+        mirror[0] = tot; mirror[1] = le; mirror[2] = lb; mirror[3] = lf;
+        reinterpret_cast<int*>(mirror + 4)[0] = atomicExch(status, 0);
+        __threadfence_system();
+      }
     }
   }
 }
@@ -900,9 +907,21 @@ struct stafb_model {
   int *im2, *ntr;
   double* losses_d;  // [0..4] the four losses + the done-counter of k_loss; [8 + 9*b + c] virial accumulators
   // staging for the *_host entry points
-  void *pos_d, *box_d, *el_d, *fl_d;
-  void* pin;  // pinned staging: pos | f_label | box | e_label
-  double* losses_h;
+  // two pipelined slots for stafb_train_step_host_begin/_end: pinned input block (pos | f_label | box | e_label),
+  // pinned results (4 losses + status) and the event that marks the slot's step complete
+  char* slot_in_h[3];  // slots 0, 1: the pipelined calls; slot 2: the synchronous stafb_train_step_host
+  double* slot_out_h[3];
+  cudaEvent_t slot_done[3];
+  int slot_busy[3];
+  // per slot: the captured graph of (copy in, step, copy out) and the call signature it was captured for
+  struct SlotKey {
+    int nf, loss_kind;
+    const void *theta, *emb, *grad, *stream;
+    double pe, pf, pb, bound;
+  } slot_key[3];
+  double* mirror_next;  // mapped host memory the next training evaluation's k_loss writes its results to
+  int slot_state[3];  // 0: nothing yet, 1: signature seen once (ran eagerly), 2: graph instantiated, -1: capture failed
+  cudaGraphExec_t slot_exec[3];
   size_t smem_limit;
 };
 
@@ -1019,12 +1038,15 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   STAFB_CUDA_OK(cudaMalloc(&m->ebar, es * c->max_batch));
   STAFB_CUDA_OK(cudaMalloc(&m->energy, es * c->max_batch));
   STAFB_CUDA_OK(cudaMalloc((void**)&m->losses_d, sizeof(double) * (8 + 9 * (size_t)c->max_batch)));
-  STAFB_CUDA_OK(cudaMalloc(&m->pos_d, es * A * 3));
-  STAFB_CUDA_OK(cudaMalloc(&m->box_d, es * c->max_batch * 6));
-  STAFB_CUDA_OK(cudaMalloc(&m->el_d, es * c->max_batch));
-  STAFB_CUDA_OK(cudaMalloc(&m->fl_d, es * A * 3));
-  STAFB_CUDA_OK(cudaMallocHost(&m->pin, es * (A * 6 + (size_t)c->max_batch * 7)));
-  STAFB_CUDA_OK(cudaMallocHost((void**)&m->losses_h, sizeof(double) * 4));
+  {
+    const size_t blk = es * (A * 6 + (size_t)c->max_batch * 7 + 8);
+    for (int k = 0; k < 3; k++) {
+      STAFB_CUDA_OK(cudaMallocHost((void**)&m->slot_in_h[k], blk));
+      STAFB_CUDA_OK(cudaMallocHost((void**)&m->slot_out_h[k], sizeof(double) * 5));
+      STAFB_CUDA_OK(cudaEventCreateWithFlags(&m->slot_done[k], cudaEventDisableTiming));
+      m->slot_busy[k] = 0;
+    }
+  }
   *out = m;
   return STAFB_OK;
 }
@@ -1032,10 +1054,14 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
 extern "C" void stafb_model_destroy(stafb_model* m) {
   if (!m) return;
   void* ptrs[] = {m->rad, m->d3s, m->im2, m->ntr, m->af, m->nd, m->gradnet, m->gaf, m->acts, m->e_atom, m->force,
-                  m->fbar, m->ebar, m->energy, m->losses_d, m->pos_d, m->box_d, m->el_d, m->fl_d, m->vrow};
+                  m->fbar, m->ebar, m->energy, m->losses_d, m->vrow};
   for (void* p : ptrs) cudaFree(p);
-  cudaFreeHost(m->pin);
-  cudaFreeHost(m->losses_h);
+  for (int k = 0; k < 3; k++) {
+    cudaFreeHost(m->slot_in_h[k]);
+    cudaFreeHost(m->slot_out_h[k]);
+    if (m->slot_done[k]) cudaEventDestroy(m->slot_done[k]);
+    if (m->slot_exec[k]) cudaGraphExecDestroy(m->slot_exec[k]);
+  }
   free(m);
 }
 
@@ -1105,6 +1131,24 @@ static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta
     STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_fwd<T, APT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)m->mlp_fwd_smem));
     attr = m->mlp_fwd_smem;
+  }
+  static const bool no_warp_kernel = getenv("STAFB_MLP_BLOCK_FWD") != nullptr;
+  const ModelDev& d = m->md;
+  if (m->stage == 2 && d.maxw <= 32 * ML_MAXO && !no_warp_kernel) {
+    // one warp per atom: all layers staged once per block, no block-wide phases afterwards
+    const size_t r4 = (size_t)((d.Fmax + 3) & ~3) + ((d.Hsum + 3) & ~3) + 2 * ((d.maxw + 3) & ~3);
+    const size_t sm = sizeof(T) * (mlp_stage_words(d, 2) + (ML_THREADS / 32) * r4);
+    static size_t attr_w = 0;
+    if (sm <= m->smem_limit - 1024) {
+      if (sm > 48 * 1024 && sm > attr_w) {
+        STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_fwd_warp<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+        attr_w = sm;
+      }
+      k_mlp_fwd_warp<T><<<species_blocks(d, nf, ML_THREADS / 32), ML_THREADS, sm, s>>>(d, nf, 8 * APT, theta, af, acts,
+                                                                                      e_atom, nd);
+      m->ctx->launches++;
+      return STAFB_OK;
+    }
   }
   k_mlp_fwd<T, APT><<<species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_fwd_smem, s>>>(m->md, nf, theta, af, acts,
                                                                                            e_atom, nd, m->stage);
@@ -1199,7 +1243,8 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
     const int grid = nf + fb + (train ? 1 : 0);
     k_loss<T><<<grid, 256, 0, s>>>(d, nf, fb, per_atom, train ? 1 : 0, e_atom, energy, e_label, force, f_label, theta,
                                    (T)pe, (T)pf, (T)pb, (T)bound, loss_kind, (T*)m->ebar, (T*)m->fbar, grad,
-                                   m->losses_d, c->status_d, vacc, virial_out);
+                                   m->losses_d, c->status_d, vacc, virial_out, train ? m->mirror_next : nullptr);
+    m->mirror_next = nullptr;
     c->launches++;
   }
   mark();  // loss
@@ -1285,38 +1330,116 @@ extern "C" int stafb_train_step(stafb_ctx* c, stafb_model* m, void* stream, cons
 extern "C" int stafb_train_step_host(stafb_ctx* c, stafb_model* m, void* stream, const void* pos_h,
                                      const void* box_h, int nf, const void* theta, const void* emb,
                                      const void* el_h, const void* fl_h, double pe, double pf, double pb,
-                                     double bound, int loss_kind, double* losses_h, void* grad) {
-  if (!c || !m || !pos_h || !box_h || !el_h || !fl_h || !losses_h) return STAFB_ERR_INVALID;
-  if (nf > c->max_batch) return STAFB_ERR_CAPACITY;
+                                     double bound, int loss_kind, double* losses_h, void* grad);
+
+// Pipelined form of stafb_train_step_host: _begin copies the host inputs into the slot's pinned block,
+// enqueues ONE host->device copy, the step and the device->host copy of the losses and the status word, and
+// returns without waiting; _end waits for that slot and hands the results over.  With two slots the host
+// prepares step k+1 while the GPU runs step k.
+static int host_step_begin(stafb_ctx* c, stafb_model* m, void* stream, const void* pos_h, const void* box_h, int nf,
+                           const void* theta, const void* emb, const void* el_h, const void* fl_h, double pe,
+                           double pf, double pb, double bound, int loss_kind, void* grad, int slot) {
+  if (!c || !m || !pos_h || !box_h || !el_h || !fl_h || slot < 0 || slot > 2) return STAFB_ERR_INVALID;
+  if (nf <= 0 || nf > c->max_batch) return STAFB_ERR_CAPACITY;
+  if (m->slot_busy[slot]) return STAFB_ERR_INVALID;  // the previous step of this slot has not been collected
   cudaStream_t s = (cudaStream_t)stream;
   const size_t es = m->es, A = (size_t)nf * m->md.N;
-  // stage through pinned memory so that the copies are truly asynchronous
-  char* pin = (char*)m->pin;
-  char* p_pos = pin;
-  char* p_fl = p_pos + es * A * 3;
-  char* p_box = p_fl + es * A * 3;
-  char* p_el = p_box + es * (size_t)nf * 6;
-  memcpy(p_pos, pos_h, es * A * 3);
-  memcpy(p_fl, fl_h, es * A * 3);
-  memcpy(p_box, box_h, es * (size_t)nf * 6);
-  memcpy(p_el, el_h, es * (size_t)nf);
-  STAFB_CUDA_OK(cudaMemcpyAsync(m->pos_d, p_pos, es * A * 3, cudaMemcpyHostToDevice, s));
-  STAFB_CUDA_OK(cudaMemcpyAsync(m->fl_d, p_fl, es * A * 3, cudaMemcpyHostToDevice, s));
-  STAFB_CUDA_OK(cudaMemcpyAsync(m->box_d, p_box, es * (size_t)nf * 6, cudaMemcpyHostToDevice, s));
-  STAFB_CUDA_OK(cudaMemcpyAsync(m->el_d, p_el, es * (size_t)nf, cudaMemcpyHostToDevice, s));
-  int rc = stafb_train_step(c, m, stream, m->pos_d, m->box_d, nf, theta, emb, m->el_d, m->fl_d, pe, pf, pb, bound,
+  const size_t o_fl = es * A * 3, o_box = o_fl + es * A * 3, o_el = o_box + es * (size_t)nf * 6;
+  char* ph = m->slot_in_h[slot];
+  memcpy(ph, pos_h, es * A * 3);
+  memcpy(ph + o_fl, fl_h, es * A * 3);
+  memcpy(ph + o_box, box_h, es * (size_t)nf * 6);
+  memcpy(ph + o_el, el_h, es * (size_t)nf);
+  double* oh = m->slot_out_h[slot];
+  // No copy-engine transfers on the stream: the kernels read the step's inputs directly from the slot's pinned
+  // (device-mapped) block over PCIe - positions and box once in the cell-list kernel, the labels once in the
+  // loss kernel - and the loss kernel writes the four losses and the status word straight into the slot's
+  // pinned result block.  That takes one host->device and two device->host DMA latencies off every step.
+  auto enqueue = [&]() -> int {
+    m->mirror_next = oh;
+    return stafb_train_step(c, m, stream, ph, ph + o_box, nf, theta, emb, ph + o_el, ph + o_fl, pe, pf, pb, bound,
                             loss_kind, m->losses_d, grad, nullptr, nullptr);
-  if (rc != STAFB_OK) return rc;
-  STAFB_CUDA_OK(cudaMemcpyAsync(m->losses_h, m->losses_d, sizeof(double) * 4, cudaMemcpyDeviceToHost, s));
-  STAFB_CUDA_OK(cudaMemcpyAsync(c->status_h, c->status_d, sizeof(int), cudaMemcpyDeviceToHost, s));
-  STAFB_CUDA_OK(cudaStreamSynchronize(s));
-  for (int q = 0; q < 4; q++) losses_h[q] = m->losses_h[q];
-  if (*c->status_h != STAFB_OK) {
-    int st = *c->status_h;
-    cudaMemsetAsync(c->status_d, 0, sizeof(int), s);
-    return st;
+  };
+  // The same call signature on the same slot is first run as plain launches (which also performs the one-time
+  // kernel attribute set-up), then captured into a CUDA graph, then replayed: one launch per step instead of
+  // fourteen.  All addresses inside the graph are the slot's own buffers and the caller's theta/emb/grad.
+  stafb_model::SlotKey key;
+  memset(&key, 0, sizeof(key));
+  key.nf = nf; key.loss_kind = loss_kind; key.theta = theta; key.emb = emb; key.grad = grad; key.stream = stream;
+  key.pe = pe; key.pf = pf; key.pb = pb; key.bound = bound;
+  const bool same = m->slot_state[slot] != 0 && memcmp(&key, &m->slot_key[slot], sizeof(key)) == 0;
+  if (!same) {
+    if (m->slot_exec[slot]) { cudaGraphExecDestroy(m->slot_exec[slot]); m->slot_exec[slot] = nullptr; }
+    m->slot_key[slot] = key;
+    m->slot_state[slot] = 0;
   }
+  static const bool no_graph = getenv("STAFB_NO_STEP_GRAPH") != nullptr;
+  int rc = STAFB_OK;
+  if (m->slot_state[slot] == 2) {
+    STAFB_CUDA_OK(cudaGraphLaunch(m->slot_exec[slot], s));
+  } else if (m->slot_state[slot] == 1 && !c->timing && !no_graph) {
+    cudaGraph_t g = nullptr;
+    bool ok = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+    if (ok) {
+      rc = enqueue();
+      ok = cudaStreamEndCapture(s, &g) == cudaSuccess && rc == STAFB_OK && g != nullptr;
+    }
+    if (ok) ok = cudaGraphInstantiate(&m->slot_exec[slot], g, 0) == cudaSuccess;
+    if (g) cudaGraphDestroy(g);
+    if (ok) {
+      m->slot_state[slot] = 2;
+      STAFB_CUDA_OK(cudaGraphLaunch(m->slot_exec[slot], s));
+    } else {
+      cudaGetLastError();  // clear the capture error and fall back to plain launches for this signature
+      m->slot_exec[slot] = nullptr;
+      m->slot_state[slot] = -1;
+      rc = enqueue();
+      if (rc != STAFB_OK) return rc;
+    }
+  } else {
+    rc = enqueue();
+    if (rc != STAFB_OK) return rc;
+    if (m->slot_state[slot] == 0) m->slot_state[slot] = 1;
+  }
+  STAFB_CUDA_OK(cudaEventRecord(m->slot_done[slot], s));
+  m->slot_busy[slot] = 1;
   return STAFB_OK;
+}
+
+extern "C" int stafb_train_step_host_begin(stafb_ctx* c, stafb_model* m, void* stream, const void* pos_h,
+                                           const void* box_h, int nf, const void* theta, const void* emb,
+                                           const void* el_h, const void* fl_h, double pe, double pf, double pb,
+                                           double bound, int loss_kind, void* grad, int slot) {
+  if (slot < 0 || slot > 1) return STAFB_ERR_INVALID;
+  return host_step_begin(c, m, stream, pos_h, box_h, nf, theta, emb, el_h, fl_h, pe, pf, pb, bound, loss_kind, grad,
+                         slot);
+}
+
+static int host_step_end(stafb_ctx* c, stafb_model* m, int slot, double* losses_h) {
+  if (!c || !m || !losses_h || slot < 0 || slot > 2 || !m->slot_busy[slot]) return STAFB_ERR_INVALID;
+  STAFB_CUDA_OK(cudaEventSynchronize(m->slot_done[slot]));
+  m->slot_busy[slot] = 0;
+  const double* oh = m->slot_out_h[slot];
+  for (int q = 0; q < 4; q++) losses_h[q] = oh[q];
+  return *reinterpret_cast<const int*>(oh + 4);
+}
+
+extern "C" int stafb_train_step_host_end(stafb_ctx* c, stafb_model* m, int slot, double* losses_h) {
+  if (slot < 0 || slot > 1) return STAFB_ERR_INVALID;
+  return host_step_end(c, m, slot, losses_h);
+}
+
+
+// The one-call form: the same staging and result path on a slot of its own, then wait.
+extern "C" int stafb_train_step_host(stafb_ctx* c, stafb_model* m, void* stream, const void* pos_h,
+                                     const void* box_h, int nf, const void* theta, const void* emb,
+                                     const void* el_h, const void* fl_h, double pe, double pf, double pb,
+                                     double bound, int loss_kind, double* losses_h, void* grad) {
+  if (!losses_h) return STAFB_ERR_INVALID;
+  const int rc = host_step_begin(c, m, stream, pos_h, box_h, nf, theta, emb, el_h, fl_h, pe, pf, pb, bound, loss_kind,
+                                 grad, 2);
+  if (rc != STAFB_OK) return rc;
+  return host_step_end(c, m, 2, losses_h);
 }
 
 extern "C" int stafb_adam_step(stafb_ctx* c, void* stream, void* theta, const void* grad, void* mm, void* vv, int n,

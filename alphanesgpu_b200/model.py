@@ -150,6 +150,26 @@ class StafModel:
                                                vp(self.losses_h), _p(self.grad)), "stafb_train_step_host")
         return self.losses_h
 
+    def loss_and_grad_host_begin(self, pos, box, e_label, f_label, slot):
+        """Pipelined loss_and_grad_host: stages the HOST inputs, enqueues copies + step and returns at once.
+        Collect with loss_and_grad_host_end(slot); two slots (0, 1) let step k+1 be prepared while step k runs."""
+        dt = np.float32 if self.dtype == torch.float32 else np.float64
+        pos, box = np.ascontiguousarray(pos, dt), np.ascontiguousarray(box, dt)
+        e_label, f_label = np.ascontiguousarray(e_label, dt), np.ascontiguousarray(f_label, dt)
+        vp = lambda a: a.ctypes.data_as(C.c_void_p)
+        check(_lib.lib().stafb_train_step_host_begin(self.ctx.h, self.h, self.ctx.stream(), vp(pos), vp(box),
+                                                     box.shape[0], _p(self.theta), _p(self.emb), vp(e_label),
+                                                     vp(f_label), self.pe, self.pf, self.pb, self.alpha_bound,
+                                                     self.loss_kind, _p(self.grad), int(slot)),
+              "stafb_train_step_host_begin")
+
+    def loss_and_grad_host_end(self, slot):
+        """Waits for the step begun in `slot`; returns its losses (loss, loss_e, loss_bound, loss_f)."""
+        out = np.zeros(4, np.float64)
+        check(_lib.lib().stafb_train_step_host_end(self.ctx.h, self.h, int(slot), out.ctypes.data_as(C.c_void_p)),
+              "stafb_train_step_host_end")
+        return out
+
     def adam_update(self, lr, beta1=0.9, beta2=0.999, eps=1e-7, grad_scale=1.0):
         """Keras Adam (epsilon default 1e-7: STAF/optimizer_learning_rate_utility.py:64-68)."""
         self.step += 1

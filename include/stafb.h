@@ -279,6 +279,19 @@ int stafb_train_step_host(stafb_ctx* ctx, stafb_model* m, void* stream, const vo
                           const void* f_label_h, double pe, double pf, double pb, double alpha_bound, int loss_kind,
                           double* losses_h, void* grad_d);
 
+/* stafb_train_step_host split in two so that consecutive steps overlap: _begin stages the host inputs in the
+ * slot's pinned block and enqueues the step on `stream` (the kernels read that block directly over PCIe and
+ * write the losses and the status word straight into pinned memory; from the third call with the same
+ * arguments on, the step is one replayed CUDA graph) and returns at once; _end waits for that slot's step, writes losses_h[4] and returns the step's status
+ * (STAFB_OK, STAFB_ERR_RADIAL_OVERFLOW, ...).  slot is 0 or 1; a slot must be collected with _end before it is
+ * begun again.  Typical loop (what STAF/staf_train.py:678-755 does with a prefetch thread and TensorFlow's
+ * asynchronous executor): begin(k, slot k&1); adam(k); end(k-1, slot (k-1)&1). */
+int stafb_train_step_host_begin(stafb_ctx* ctx, stafb_model* m, void* stream, const void* positions_h,
+                                const void* boxer_h, int nf, const void* theta_d, const void* emb_d,
+                                const void* e_label_h, const void* f_label_h, double pe, double pf, double pb,
+                                double alpha_bound, int loss_kind, void* grad_d, int slot);
+int stafb_train_step_host_end(stafb_ctx* ctx, stafb_model* m, int slot, double* losses_h);
+
 /* Per-phase device timing of the fused calls, with CUDA events on the launching stream.  Phases, in
  * order: descriptors, af_fwd, mlp_fwd, force, loss, force_grad, mlp_bwd, af_grad (the last four only for
  * stafb_train_step).  stafb_get_phase_times waits for the last event, writes up to cap durations in

@@ -138,3 +138,31 @@ def test_energy_force_virial_matches_the_virial_ops(oracle, dtype, tol):
     assert rel_err(f.cpu().numpy(), F) <= tol
     assert rel_err(w.cpu().numpy(), W) <= tol
     m.close()
+
+
+def test_pipelined_host_steps_equal_the_synchronous_call():
+    """stafb_train_step_host_begin/_end: two steps in flight give the losses and the gradient of the one-call form."""
+    from alphanesgpu_b200.model import StafModel
+    pos, box, tipos = synth.water_frames("water96", [1000, 1001, 1002, 1003])
+    shape = synth.baseline_shape(tipos)
+    theta, emb = synth.init_params(shape, dtype=np.float32)
+    el, fl = synth.labels(4, shape.N)
+    m = StafModel(shape, CFG, theta, emb, 2, dtype=torch.float32, device="cuda:0")
+    f32 = lambda a: a.astype(np.float32)
+    ref, grads = [], []
+    for h in range(2):
+        sl = slice(2 * h, 2 * h + 2)
+        ref.append(m.loss_and_grad_host(f32(pos[sl]), f32(box[sl]), f32(el[sl]), f32(fl[sl])).copy())
+        grads.append(m.grad.clone())
+    for h in range(2):
+        sl = slice(2 * h, 2 * h + 2)
+        m.loss_and_grad_host_begin(f32(pos[sl]), f32(box[sl]), f32(el[sl]), f32(fl[sl]), h)
+    g_last = m.grad.clone()  # stream order: the second step's gradient
+    got = [m.loss_and_grad_host_end(0), m.loss_and_grad_host_end(1)]
+    torch.cuda.synchronize()
+    for h in range(2):
+        assert np.allclose(got[h], ref[h], rtol=1e-6, atol=0)
+    assert rel_err(g_last.cpu().numpy(), grads[1].cpu().numpy()) <= 1e-6
+    with pytest.raises(Exception):
+        m.loss_and_grad_host_end(0)  # nothing in flight in that slot
+    m.close()
