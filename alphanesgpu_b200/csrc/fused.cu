@@ -228,7 +228,7 @@ __device__ __forceinline__ void gsync() {
 // One block of WPA warps per central atom.  VIR (force mode only) adds the virial; it is a template
 // parameter so that the training step's force sweep does not carry its registers.
 template <class T, int MODE, int WPA, bool VIR>
-__global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::value)
+__global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::value * ((MODE == 1 && WPA == 1) ? 2 : 1))
     k_sweep(ModelDev md, SweepIn<T> in, SweepLayout L, const T* __restrict__ theta, const T* __restrict__ emb,
             const T* __restrict__ chan_in,  // FORCE/FGRAD: netderiv[nf,N,Fmax]; AFGRAD: dL/dAF[nf,N,Fmax]
             const T* __restrict__ fbar,     // FGRAD: dL/dF[nf,3N]
@@ -1091,19 +1091,18 @@ extern "C" void stafb_model_offsets(const stafb_model* m, int t, int out6[6]) {
   out6[4] = m->md.off_emb[t]; out6[5] = m->blk_size[t];
 }
 
-template <class T, int MODE>
+template <class T, int MODE, int SW_WPA = SweepWpa<MODE>::value>
 static int launch_sweep(stafb_model* m, cudaStream_t s, int nf, const SweepIn<T>& in, const T* theta, const T* emb,
                         const T* chan_in, const T* fbar, T* out, T* grad, T* vout = nullptr, int nv = 0,
                         double* vir = nullptr) {
   const ModelDev& d = m->md;
   const int xt = MODE == MODE_FORCE ? 3 : (MODE == MODE_FGRAD ? 4 : 0);
   const int nacc = d.Famax + d.nt * d.Frmax + d.C * 3 * d.Famax;
-  constexpr int SW_WPA = SweepWpa<MODE>::value;
   SweepLayout L = sweep_layout<T>(in.nr, d.nt, xt, nacc, d.Famax > 0 ? d.Famax : 1, SW_WPA,
                                   d.nt * d.Frmax > 0 ? d.nt * d.Frmax : 1, d.ncls * d.Famax > 0 ? d.ncls * d.Famax : 1);
   const size_t sm = (size_t)L.total;
   if (sm > m->smem_limit) return STAFB_ERR_CAPACITY;
-  static bool attr[2][5] = {{false}};
+  static bool attr[2][5] = {{false}};  // per instantiation (T, MODE, SW_WPA)
   if (sm > 48 * 1024 && !attr[sizeof(T) == 8][MODE]) {
     STAFB_CUDA_OK(cudaFuncSetAttribute(k_sweep<T, MODE, SW_WPA, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)m->smem_limit));
@@ -1131,24 +1130,6 @@ static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta
     STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_fwd<T, APT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)m->mlp_fwd_smem));
     attr = m->mlp_fwd_smem;
-  }
-  static const bool no_warp_kernel = getenv("STAFB_MLP_BLOCK_FWD") != nullptr;
-  const ModelDev& d = m->md;
-  if (m->stage == 2 && d.maxw <= 32 * ML_MAXO && !no_warp_kernel) {
-    // one warp per atom: all layers staged once per block, no block-wide phases afterwards
-    const size_t r4 = (size_t)((d.Fmax + 3) & ~3) + ((d.Hsum + 3) & ~3) + 2 * ((d.maxw + 3) & ~3);
-    const size_t sm = sizeof(T) * (mlp_stage_words(d, 2) + (ML_THREADS / 32) * r4);
-    static size_t attr_w = 0;
-    if (sm <= m->smem_limit - 1024) {
-      if (sm > 48 * 1024 && sm > attr_w) {
-        STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_fwd_warp<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        attr_w = sm;
-      }
-      k_mlp_fwd_warp<T><<<species_blocks(d, nf, ML_THREADS / 32), ML_THREADS, sm, s>>>(d, nf, 8 * APT, theta, af, acts,
-                                                                                      e_atom, nd);
-      m->ctx->launches++;
-      return STAFB_OK;
-    }
   }
   k_mlp_fwd<T, APT><<<species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_fwd_smem, s>>>(m->md, nf, theta, af, acts,
                                                                                            e_atom, nd, m->stage);
@@ -1231,7 +1212,14 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
   if (rc != STAFB_OK) return rc;
   mark();  // mlp_fwd
   double* vacc = virial_out ? m->losses_d + 8 : nullptr;
-  rc = launch_sweep<T, MODE_FORCE>(m, s, nf, in, theta, emb, nd, nullptr, force, nullptr, nullptr, 0, vacc);
+  // two warps per atom shorten the ordered-pair loop while the GPU is not full; once there are several blocks
+  // per warp slot, one warp per atom (no block barriers) has the higher throughput
+  static const long long one_warp_atoms =
+      getenv("STAFB_FORCE_WPA1_ATOMS") ? atoll(getenv("STAFB_FORCE_WPA1_ATOMS")) : 2048;
+  if ((long long)nf * N >= one_warp_atoms)
+    rc = launch_sweep<T, MODE_FORCE, 1>(m, s, nf, in, theta, emb, nd, nullptr, force, nullptr, nullptr, 0, vacc);
+  else
+    rc = launch_sweep<T, MODE_FORCE>(m, s, nf, in, theta, emb, nd, nullptr, force, nullptr, nullptr, 0, vacc);
   if (rc != STAFB_OK) return rc;
   mark();  // force
   {

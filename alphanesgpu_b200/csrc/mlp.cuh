@@ -485,153 +485,3 @@ __global__ void __launch_bounds__(ML_THREADS)
     }
   }
 }
-
-// hout[j] = act(b[j] + sum_i hin[i] W[i,j]) for one atom: lane owns outputs lane, lane+32, ... (NJ of them,
-// compile-time so that the inner loop carries no per-output tests); inputs are broadcast from shared memory.
-template <class T, int NJ>
-__device__ __forceinline__ void warp_dense_fwd(int in, int out, int ld, const T* __restrict__ W, const T* hin, T* hout,
-                                               int lane, bool tanh_act) {
-  T acc[NJ];
-  bool ok[NJ];
-#pragma unroll
-  for (int r = 0; r < NJ; r++) {
-    ok[r] = lane + 32 * r < out;
-    acc[r] = ok[r] ? W[in * ld + lane + 32 * r] : T(0);
-  }
-  // lanes past the last output read column `lane` again (any valid address) and discard the result
-  const T* wr = W + lane;
-  int offs[NJ];
-#pragma unroll
-  for (int r = 0; r < NJ; r++) offs[r] = ok[r] ? 32 * r : 0;
-#pragma unroll 4
-  for (int i = 0; i < in; i++) {
-    const T x = hin[i];
-#pragma unroll
-    for (int r = 0; r < NJ; r++) acc[r] += x * wr[i * ld + offs[r]];
-  }
-#pragma unroll
-  for (int r = 0; r < NJ; r++)
-    if (ok[r]) hout[lane + 32 * r] = tanh_act ? r_tanh(acc[r]) : acc[r];
-}
-
-// ---------------------------------------------------------------------------------------------------
-// Forward MLP, one warp per atom.  The block stages every Dense layer once (asynchronous copies); after
-// that single barrier each of its eight warps takes one atom through x = log(AF+1e-3)-mu, the layers and the
-// reverse sweep for d(sum e)/dAF on its own: no further block-wide phases, so the latency chain of an atom
-// is its own ~700 instructions instead of ~30 barrier-separated block phases.
-//   forward   lanes over the outputs j (j, j+32, ...), inputs broadcast from the warp's scratch
-//   reverse   lanes over the inputs i, outputs four at a time with 16-byte weight loads (conflict-free with
-//             the row stride of ml_ld())
-// Used when all layers fit in shared memory (stage mode 2); k_mlp_fwd is the fallback.
-constexpr int ML_MAXO = 8;  // outputs (or inputs) per lane: layer widths up to 256
-
-template <class T>
-__global__ void __launch_bounds__(ML_THREADS)
-    k_mlp_fwd_warp(ModelDev md, int nf, int ta_bwd, const T* __restrict__ theta, const T* __restrict__ af,
-                   T* __restrict__ acts, T* __restrict__ e_atom, T* __restrict__ netderiv) {
-  typedef typename Vec4<T>::type T4;
-  constexpr int WPB = ML_THREADS / 32;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  int t, q0;
-  locate_block(md, nf, WPB, t, q0);
-  const int nat = nf * md.tipos[t];
-  const int F = md.Fr[t] + md.Fa[t], Lq = md.n_dense, Fm = md.Fmax, Hs = md.Hsum, mw = md.maxw;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int Fm4 = (Fm + 3) & ~3, Hs4 = (Hs + 3) & ~3, mw4 = (mw + 3) & ~3;  // every array 16-byte aligned
-  const int per_warp = Fm4 + Hs4 + 2 * mw4;
-  T* wsm = reinterpret_cast<T*>(smem_raw);
-  int wtot = 0;
-  for (int l = 0; l < Lq; l++) wtot += (md.in_of(t, l) + 1) * ml_ld(md.width[l]);
-  T* X = wsm + wtot + warp * per_warp;  // [Fm4]
-  T* H = X + Fm4;                       // [Hs4]
-  T* C0 = H + Hs4;                      // [mw4]
-  T* C1 = C0 + mw4;                     // [mw4]
-  const T* mu = theta + md.off_mu[t];
-  stage_all_layers<T>(md, t, theta + md.off_w[t], wsm);
-  const long long gi = ml_atom_row(md, t, q0, nat, warp);
-  T afv[ML_MAXO];  // AF + 1e-3 of this lane's inputs (reused by the final division)
-#pragma unroll
-  for (int r = 0; r < ML_MAXO; r++) {
-    const int i = lane + 32 * r;
-    afv[r] = T(1);
-    if (i < F && gi >= 0) {
-      afv[r] = af[gi * Fm + i] + T(1e-3);
-      X[i] = r_log(afv[r]) - mu[i];
-    }
-  }
-  ml_stage_wait();  // the only block-wide barrier
-  if (gi < 0) return;
-  // ---- forward
-  const T* hin = X;
-  int woff = 0;
-  for (int l = 0; l < Lq; l++) {
-    const int in = md.in_of(t, l), out = md.width[l], ld = ml_ld(out);
-    const T* W = wsm + woff;
-    T* hout = H + md.h_off(l);
-    __syncwarp();
-    if (out == 1) {
-      // scalar output: lanes split the inputs, shuffle reduction
-      T s = T(0);
-      for (int i = lane; i < in; i += 32) s += hin[i] * W[i * ld];
-      s = warp_sum(s) + W[in * ld];
-      if (lane == 0) hout[0] = (l < Lq - 1) ? r_tanh(s) : s;
-    } else {
-      const bool th = l < Lq - 1;
-      const int nj = (out + 31) >> 5;
-      if (nj == 1) warp_dense_fwd<T, 1>(in, out, ld, W, hin, hout, lane, th);
-      else if (nj == 2) warp_dense_fwd<T, 2>(in, out, ld, W, hin, hout, lane, th);
-      else if (nj <= 4) warp_dense_fwd<T, 4>(in, out, ld, W, hin, hout, lane, th);
-      else warp_dense_fwd<T, ML_MAXO>(in, out, ld, W, hin, hout, lane, th);
-    }
-    hin = hout;
-    woff += (in + 1) * ld;
-  }
-  __syncwarp();
-  // ---- activations for the backward kernel (its block-local feature-major layout) and the atomic energy
-  {
-    const int q = q0 + warp;
-    int bb = 0;
-    for (int u = 0; u < t; u++) bb += (nf * md.tipos[u] + ta_bwd - 1) / ta_bwd;
-    T* ab = acts + ((size_t)(bb + q / ta_bwd) * Hs) * ta_bwd + (q % ta_bwd);
-    for (int f = lane; f < Hs; f += 32) ab[(size_t)f * ta_bwd] = H[f];
-    if (lane == 0) e_atom[gi] = H[md.h_off(Lq - 1)];
-  }
-  // ---- reverse sweep: cn = d e / d(output of layer l)
-  T* cn = C0;
-  T* cp = C1;
-  if (lane == 0) cn[0] = T(1);
-  for (int l = Lq - 1; l >= 0; l--) {
-    const int in = md.in_of(t, l), out = md.width[l], ld = ml_ld(out);
-    woff -= (in + 1) * ld;
-    const T* W = wsm + woff;
-    __syncwarp();
-    if (l < Lq - 1) {
-      const T* hl = H + md.h_off(l);
-      for (int j = lane; j < out; j += 32) cn[j] *= (T(1) - hl[j] * hl[j]);
-    }
-    // zero the padding up to a multiple of four outputs so that the 16-byte loads below read zeros
-    if (lane < 4 && (out & 3) && lane >= (out & 3)) cn[(out & ~3) + lane] = T(0);
-    __syncwarp();
-    const int nq = (out + 3) >> 2;
-#pragma unroll
-    for (int r = 0; r < ML_MAXO; r++) {
-      const int i = lane + 32 * r;
-      if (i < in) {
-        T s = T(0);
-        for (int q4 = 0; q4 < nq; q4++) {
-          const T4 w = *reinterpret_cast<const T4*>(W + i * ld + 4 * q4);  // padding columns are zero
-          const T4 d = *reinterpret_cast<const T4*>(cn + 4 * q4);
-          s += w.x * d.x + w.y * d.y + w.z * d.z + w.w * d.w;
-        }
-        cp[i] = s;
-      }
-    }
-    T* tmp = cn; cn = cp; cp = tmp;
-  }
-  __syncwarp();
-#pragma unroll
-  for (int r = 0; r < ML_MAXO; r++) {
-    const int i = lane + 32 * r;
-    if (i < Fm) netderiv[gi * Fm + i] = (i < F) ? cn[i] / afv[r] : T(0);
-  }
-}
