@@ -71,6 +71,22 @@ __device__ unsigned long long g_sweep_clk[5][8];
 #define SWEEP_TICK(p)
 #endif
 
+// Two-channel packed arithmetic.  On sm_100 a float2 multiply / add / fma is ONE instruction (__fmul2_rn,
+// __fadd2_rn, __ffma2_rn), so the channel loops of the sweeps carry two channels per instruction; double pairs
+// are two scalar operations.
+__device__ __forceinline__ float2 p_mul(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 p_add(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 p_fma(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ double2 p_mul(double2 a, double2 b) { return make_double2(a.x * b.x, a.y * b.y); }
+__device__ __forceinline__ double2 p_add(double2 a, double2 b) { return make_double2(a.x + b.x, a.y + b.y); }
+__device__ __forceinline__ double2 p_fma(double2 a, double2 b, double2 c) {
+  return make_double2(a.x * b.x + c.x, a.y * b.y + c.y);
+}
+__device__ __forceinline__ float2 mk2(float x, float y) { return make_float2(x, y); }
+__device__ __forceinline__ double2 mk2(double x, double y) { return make_double2(x, y); }
+__device__ __forceinline__ float2 p_ex(float2 a) { return make_float2(Ex<float>::f(a.x), Ex<float>::f(a.y)); }
+__device__ __forceinline__ double2 p_ex(double2 a) { return make_double2(Ex<double>::f(a.x), Ex<double>::f(a.y)); }
+
 struct ModelDev {
   int nt, C, N, ncls;
   int tipos[STAFB_MAX_TYPES], shift[STAFB_MAX_TYPES + 1], Fr[STAFB_MAX_TYPES], Fa[STAFB_MAX_TYPES];
@@ -253,6 +269,13 @@ __global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::val
   T2* chpb = reinterpret_cast<T2*>(base + L.chpb);  // mode-dependent coefficient, netderiv
   T4* pall = reinterpret_cast<T4*>(base + L.pall);  // the same two for every (class, channel), fetched once
   T2* pball = reinterpret_cast<T2*>(base + L.pball);
+  // channel PAIRS (2*lp, 2*lp+1) share one float4: tab4[lp][k] = exp(a1*fc_k) of both channels, exp(a2*fc_k) of both;
+  // chq[lp] = (alpha1 x2, alpha2 x2); chr[lp] = (beta x2, beta*scale x2); chs[lp] = (coefficient x2, netderiv x2)
+  constexpr int MAXP = MAXCH / 2;
+  T4* tab4 = reinterpret_cast<T4*>(tab);
+  T4* chq = chpa;
+  T4* chr = chpa + MAXP;
+  T4* chs = reinterpret_cast<T4*>(chpb);
   T* xtra = reinterpret_cast<T*>(base + L.xtra);
   T* acc = reinterpret_cast<T*>(base + L.acc);
   T* red = reinterpret_cast<T*>(base + L.red);      // [WPA][4*MAXCH] per-warp partial sums
@@ -452,10 +475,27 @@ __global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::val
       for (int c0 = 0; c0 < nact; c0 += MAXCH) {
         const int nch = (nact - c0) < MAXCH ? (nact - c0) : MAXCH;
         gsync<WPA>();  // actl visible; previous chunk's readers of chp/tab/red are done
-        if (tid < nch) {
-          const int c = actl[c0 + tid];
-          chpa[tid] = pall[s * Fa + c];
-          chpb[tid] = pball[s * Fa + c];
+        const int nchp = (nch + 1) >> 1;
+        if (tid < nchp) {
+          const int ca = actl[c0 + 2 * tid];
+          const T4 pa0 = pall[s * Fa + ca];
+          const T2 pb0 = pball[s * Fa + ca];
+          T4 pa1;
+          T2 pb1;
+          pa1.x = pa1.y = pa1.z = pa1.w = T(0);  // an odd channel count is padded with an all-zero channel
+          pb1.x = pb1.y = T(0);
+          if (2 * tid + 1 < nch) {
+            const int cb = actl[c0 + 2 * tid + 1];
+            pa1 = pall[s * Fa + cb];
+            pb1 = pball[s * Fa + cb];
+          }
+          T4 q;
+          q.x = pa0.x; q.y = pa1.x; q.z = pa0.y; q.w = pa1.y;
+          chq[tid] = q;
+          q.x = pa0.z; q.y = pa1.z; q.z = pa0.w; q.w = pa1.w;
+          chr[tid] = q;
+          q.x = pb0.x; q.y = pb1.x; q.z = pb0.y; q.w = pb1.y;
+          chs[tid] = q;
         }
         gsync<WPA>();
         // tables exp(a1*fc_k), exp(a2*fc_k) for the neighbours of the two species
@@ -463,15 +503,16 @@ __global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::val
         for (int r = tid; r < nu; r += NT) {
           const int k = (r < na_) ? la[r] : lb[r - na_];
           const T fck = P0[k].w * SC;
-          // all channels of one neighbour in flight together: independent multiply -> exp2 -> store chains
+          const T2 f2 = mk2(fck, fck);
+          // all channel pairs of one neighbour in flight together: independent multiply -> exp2 -> store chains
 #pragma unroll
-          for (int l = 0; l < MAXCH; l++) {
-            if (l < nch) {
-              const T4 pa = chpa[l];
-              T2 v;
-              v.x = Ex<T>::f(pa.x * fck);
-              v.y = Ex<T>::f(pa.y * fck);
-              tab[l * nr + k] = v;
+          for (int lp = 0; lp < MAXP; lp++) {
+            if (lp < nchp) {
+              const T4 q = chq[lp];
+              const T2 a = p_ex(p_mul(mk2(q.x, q.y), f2)), b = p_ex(p_mul(mk2(q.z, q.w), f2));
+              T4 v;
+              v.x = a.x; v.y = a.y; v.z = b.x; v.w = b.y;
+              tab4[lp * nr + k] = v;
             }
           }
         }
@@ -497,11 +538,12 @@ __global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::val
               int j = lo[ja];
               T4 uj = P0[j];
               T rinvj = P1[j].x, gfcj = P1[j].y;
-              T2 Aj[MAXCH];
+              T4 Aj[MAXP];
 #pragma unroll
-              for (int l = 0; l < MAXCH; l++)
-                if (l < nch) Aj[l] = tab[l * nr + j];
+              for (int lp = 0; lp < MAXP; lp++)
+                if (lp < nchp) Aj[lp] = tab4[lp * nr + j];
               T ax = T(0), ay = T(0), az = T(0), as = T(0);
+              const T2 one2 = mk2(T(1), T(1));
               for (int e = e0; e < e1; e++) {
                 const int kk = (same && kb >= ja) ? kb + 1 : kb;
                 const int k = lp[kk];
@@ -509,18 +551,20 @@ __global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::val
                 const T cs = uj.x * uk.x + uj.y * uk.y + uj.z * uk.z;
                 const T half = T(0.5) * (cs + T(1));
                 const T tt = half * uj.w * uk.w;
-                T D = T(0), BJ = T(0);
+                const T2 tt2 = mk2(tt, tt);
+                T2 D2 = mk2(T(0), T(0)), BJ2 = mk2(T(0), T(0));
 #pragma unroll
-                for (int l = 0; l < MAXCH; l++) {
-                  if (l < nch) {
-                    const T2 B = tab[l * nr + k];
-                    const T4 pa = chpa[l];
-                    const T S1 = Aj[l].y * B.x, S2 = Aj[l].x * B.y;
-                    const T ev = chpb[l].x * Ex<T>::f(pa.w * tt);
-                    D += ev * (T(1) + pa.z * tt) * (S1 + S2);
-                    BJ += ev * tt * (pa.x * S2 + pa.y * S1);
+                for (int lp = 0; lp < MAXP; lp++) {
+                  if (lp < nchp) {
+                    const T4 B = tab4[lp * nr + k], cq = chq[lp], cr = chr[lp], cs4 = chs[lp];
+                    const T2 S1 = p_mul(mk2(Aj[lp].z, Aj[lp].w), mk2(B.x, B.y));  // exp(a2*sj + a1*sk)
+                    const T2 S2 = p_mul(mk2(Aj[lp].x, Aj[lp].y), mk2(B.z, B.w));  // exp(a1*sj + a2*sk)
+                    const T2 ev = p_mul(mk2(cs4.x, cs4.y), p_ex(p_mul(mk2(cr.z, cr.w), tt2)));
+                    D2 = p_fma(p_mul(ev, p_fma(mk2(cr.x, cr.y), tt2, one2)), p_add(S1, S2), D2);
+                    BJ2 = p_fma(p_mul(ev, tt2), p_fma(mk2(cq.x, cq.y), S2, p_mul(mk2(cq.z, cq.w), S1)), BJ2);
                   }
                 }
+                const T D = D2.x + D2.y, BJ = BJ2.x + BJ2.y;
                 // f_ij = cjk*u_k + cjj*u_j
                 const T cjk = D * T(0.5) * uj.w * uk.w * rinvj;
                 ax += cjk * uk.x; ay += cjk * uk.y; az += cjk * uk.z;
@@ -541,17 +585,18 @@ __global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::val
                     rinvj = P1[j].x;
                     gfcj = P1[j].y;
 #pragma unroll
-                    for (int l = 0; l < MAXCH; l++)
-                      if (l < nch) Aj[l] = tab[l * nr + j];
+                    for (int lp = 0; lp < MAXP; lp++)
+                      if (lp < nchp) Aj[lp] = tab4[lp * nr + j];
                   }
                 }
               }
             }
           }
         } else {
-          T r0[MAXCH], r1[MAXCH], r2[MAXCH], r3[MAXCH];
+          T2 r0[MAXP], r1[MAXP], r2[MAXP], r3[MAXP];
 #pragma unroll
-          for (int l = 0; l < MAXCH; l++) r0[l] = r1[l] = r2[l] = r3[l] = T(0);
+          for (int lp = 0; lp < MAXP; lp++) r0[lp] = r1[lp] = r2[lp] = r3[lp] = mk2(T(0), T(0));
+          const T2 one2 = mk2(T(1), T(1)), half2 = mk2(T(0.5), T(0.5)), two2 = mk2(T(2), T(2));
           PairStep ps;
           ps.ja = ps.kb = 0;
           const int qst = same ? 0 : NT / nb_, rst = same ? 0 : NT - qst * nb_;
@@ -581,36 +626,43 @@ __global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::val
               Pj = pj.y * dFj.w;
               Pk = pk.y * dFk.w;
             }
+            const T2 tt2 = mk2(tt, tt), fcj2 = mk2(fcj, fcj), fck2 = mk2(fck, fck);
+            const T2 Q2 = mk2(Q, Q), Pj2 = mk2(Pj, Pj), Pk2 = mk2(Pk, Pk);
 #pragma unroll
-            for (int l = 0; l < MAXCH; l++) {
-              if (l < nch) {
-                const T2 A = tab[l * nr + j], B = tab[l * nr + k];
-                const T4 pa = chpa[l];
-                const T S1 = A.y * B.x;  // exp(a2*sj + a1*sk)
-                const T S2 = A.x * B.y;  // exp(a1*sj + a2*sk)
-                const T eb = Ex<T>::f(pa.w * tt);
+            for (int lp = 0; lp < MAXP; lp++) {
+              if (lp < nchp) {
+                const T4 A = tab4[lp * nr + j], B = tab4[lp * nr + k], cr = chr[lp];
+                const T2 S1 = p_mul(mk2(A.z, A.w), mk2(B.x, B.y));  // exp(a2*sj + a1*sk)
+                const T2 S2 = p_mul(mk2(A.x, A.y), mk2(B.z, B.w));  // exp(a1*sj + a2*sk)
+                const T2 eb = p_ex(p_mul(mk2(cr.z, cr.w), tt2));
+                const T2 ss = p_add(S1, S2);
                 if (IS_AF || MODE == MODE_AFGRAD) {
-                  const T cm = eb * tt;
-                  if (IS_AF) r0[l] += cm * (S1 + S2);  // the channel coefficient is applied after the reduction
+                  const T2 cm = p_mul(eb, tt2);
+                  if (IS_AF) r0[lp] = p_fma(cm, ss, r0[lp]);  // the channel coefficient is applied after the reduction
                   if (HAS_V) {
-                    r1[l] += cm * (S2 * fcj + S1 * fck);
-                    r2[l] += cm * (S2 * fck + S1 * fcj);
-                    r3[l] += cm * (S1 + S2) * tt;
+                    r1[lp] = p_fma(cm, p_fma(S2, fcj2, p_mul(S1, fck2)), r1[lp]);
+                    r2[lp] = p_fma(cm, p_fma(S2, fck2, p_mul(S1, fcj2)), r2[lp]);
+                    r3[lp] = p_fma(p_mul(cm, tt2), ss, r3[lp]);
                   }
                 } else {  // FGRAD
-                  const T al1 = pa.x, al2 = pa.y, be = pa.z;
-                  const T ss = S1 + S2, opb = T(1) + be * tt;
-                  const T et = eb * T(0.5) * tt;
-                  const T eo = eb * opb * T(0.5);
-                  const T Bj = (al1 * S2 + al2 * S1) * et, Bk = (al1 * S1 + al2 * S2) * et;
-                  r0[l] += eo * ss * Q + Bj * Pj + Bk * Pk;
-                  const T a1j = (S2 + al1 * S2 * fcj + al2 * S1 * fck) * et;
-                  const T a2j = (S1 + al2 * S1 * fcj + al1 * S2 * fck) * et;
-                  const T a1k = (S1 + al1 * S1 * fck + al2 * S2 * fcj) * et;
-                  const T a2k = (S2 + al2 * S2 * fck + al1 * S1 * fcj) * et;
-                  r1[l] += eo * (S1 * fck + S2 * fcj) * Q + a1j * Pj + a1k * Pk;
-                  r2[l] += eo * (S1 * fcj + S2 * fck) * Q + a2j * Pj + a2k * Pk;
-                  r3[l] += eb * tt * (T(2) + be * tt) * ss * T(0.5) * Q + tt * (Bj * Pj + Bk * Pk);
+                  const T4 cq = chq[lp];
+                  const T2 al1 = mk2(cq.x, cq.y), al2 = mk2(cq.z, cq.w), be = mk2(cr.x, cr.y);
+                  const T2 opb = p_fma(be, tt2, one2);
+                  const T2 et = p_mul(p_mul(eb, half2), tt2);   // eb * 0.5 * tt
+                  const T2 eo = p_mul(p_mul(eb, opb), half2);   // eb * (1 + be*tt) * 0.5
+                  const T2 a1S1 = p_mul(al1, S1), a1S2 = p_mul(al1, S2), a2S1 = p_mul(al2, S1), a2S2 = p_mul(al2, S2);
+                  const T2 Bj = p_mul(p_add(a1S2, a2S1), et), Bk = p_mul(p_add(a1S1, a2S2), et);
+                  const T2 eoQ = p_mul(eo, Q2);
+                  r0[lp] = p_fma(eoQ, ss, p_fma(Bj, Pj2, p_fma(Bk, Pk2, r0[lp])));
+                  const T2 a1j = p_mul(p_fma(a1S2, fcj2, p_fma(a2S1, fck2, S2)), et);
+                  const T2 a2j = p_mul(p_fma(a2S1, fcj2, p_fma(a1S2, fck2, S1)), et);
+                  const T2 a1k = p_mul(p_fma(a1S1, fck2, p_fma(a2S2, fcj2, S1)), et);
+                  const T2 a2k = p_mul(p_fma(a2S2, fck2, p_fma(a1S1, fcj2, S2)), et);
+                  r1[lp] = p_fma(eoQ, p_fma(S1, fck2, p_mul(S2, fcj2)), p_fma(a1j, Pj2, p_fma(a1k, Pk2, r1[lp])));
+                  r2[lp] = p_fma(eoQ, p_fma(S1, fcj2, p_mul(S2, fck2)), p_fma(a2j, Pj2, p_fma(a2k, Pk2, r2[lp])));
+                  // eb*tt*(2 + be*tt)*ss*0.5*Q + tt*(Bj*Pj + Bk*Pk)
+                  const T2 c3 = p_mul(p_mul(p_mul(eb, tt2), p_fma(be, tt2, two2)), p_mul(half2, Q2));
+                  r3[lp] = p_fma(c3, ss, p_fma(tt2, p_fma(Bj, Pj2, p_mul(Bk, Pk2)), r3[lp]));
                 }
               }
             }
@@ -622,19 +674,25 @@ __global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::val
           if (MODE == MODE_AF) {
             T v[MAXCH];
 #pragma unroll
-            for (int l = 0; l < MAXCH; l++) v[l] = r0[l];
+            for (int lp = 0; lp < MAXP; lp++) { v[2 * lp] = r0[lp].x; v[2 * lp + 1] = r0[lp].y; }
             const T tot = multi_reduce<T, MAXCH>(v, lane);  // lane holds channel lane >> 2
             if ((lane & 3) == 0) red[warp * 4 * MAXCH + 4 * (lane >> 2)] = tot;
           } else if (nch <= MAXCH / 2) {
             T v[2 * MAXCH];
 #pragma unroll
-            for (int l = 0; l < MAXCH / 2; l++) { v[4 * l] = r0[l]; v[4 * l + 1] = r1[l]; v[4 * l + 2] = r2[l]; v[4 * l + 3] = r3[l]; }
+            for (int lp = 0; lp < MAXP / 2; lp++) {
+              v[8 * lp] = r0[lp].x; v[8 * lp + 1] = r1[lp].x; v[8 * lp + 2] = r2[lp].x; v[8 * lp + 3] = r3[lp].x;
+              v[8 * lp + 4] = r0[lp].y; v[8 * lp + 5] = r1[lp].y; v[8 * lp + 6] = r2[lp].y; v[8 * lp + 7] = r3[lp].y;
+            }
             const T tot = multi_reduce<T, 2 * MAXCH>(v, lane);  // lane holds value lane >> 1
             if ((lane & 1) == 0) red[warp * 4 * MAXCH + (lane >> 1)] = tot;
           } else {
             T v[4 * MAXCH];
 #pragma unroll
-            for (int l = 0; l < MAXCH; l++) { v[4 * l] = r0[l]; v[4 * l + 1] = r1[l]; v[4 * l + 2] = r2[l]; v[4 * l + 3] = r3[l]; }
+            for (int lp = 0; lp < MAXP; lp++) {
+              v[8 * lp] = r0[lp].x; v[8 * lp + 1] = r1[lp].x; v[8 * lp + 2] = r2[lp].x; v[8 * lp + 3] = r3[lp].x;
+              v[8 * lp + 4] = r0[lp].y; v[8 * lp + 5] = r1[lp].y; v[8 * lp + 6] = r2[lp].y; v[8 * lp + 7] = r3[lp].y;
+            }
             const T tot = multi_reduce<T, 4 * MAXCH>(v, lane);  // lane holds value lane
             red[warp * 4 * MAXCH + lane] = tot;
           }
@@ -647,10 +705,11 @@ __global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::val
 #pragma unroll
               for (int w = 0; w < WPA; w++) sum += red[w * 4 * MAXCH + tid];
               const int c = actl[c0 + l];
-              const T cf = chpb[l].x;
+              const T4 cs4 = chs[l >> 1];
+              const T cf = (l & 1) ? cs4.y : cs4.x;
               if (v == 0) acc[ACC_GN + c] += cf * sum;
               else {
-                const T hn = MODE == MODE_FGRAD ? cf * chpb[l].y : cf;
+                const T hn = MODE == MODE_FGRAD ? cf * ((l & 1) ? cs4.w : cs4.z) : cf;
                 acc[ACC_A3 + (s * md.Famax + c) * 3 + (v - 1)] += hn * sum;
               }
             }
@@ -763,12 +822,32 @@ __device__ __forceinline__ T huber(T e) { T a = r_abs(e); return a <= T(1) ? T(0
 template <class T>
 __device__ __forceinline__ T huber_d(T e) { return e > T(1) ? T(1) : (e < T(-1) ? T(-1) : e); }
 
-// zero-fills up to three buffers (sizes in bytes, multiples of 4) in one launch
-__global__ void k_zero3(void* a, size_t na, void* b, size_t nb, void* c, size_t nc) {
+// Start-of-evaluation housekeeping in one launch: zero-fills up to three buffers (sizes in bytes, multiples of
+// 4) and writes the packed, padded copy of the Dense layers that the MLP kernels stage (layout: mlp.cuh).
+template <class T>
+__global__ void k_prep(ModelDev md, const T* __restrict__ theta, T* __restrict__ wpack, int wstride, void* a,
+                       size_t na, void* b, size_t nb, void* c, size_t nc) {
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
   for (size_t q = tid; q < na / 4; q += st) reinterpret_cast<int*>(a)[q] = 0;
   for (size_t q = tid; q < nb / 4; q += st) reinterpret_cast<int*>(b)[q] = 0;
   for (size_t q = tid; q < nc / 4; q += st) reinterpret_cast<int*>(c)[q] = 0;
+  // one pass over all packed words: every thread's loads are independent, so the kernel costs one memory round trip
+  for (size_t q = tid; q < (size_t)md.nt * wstride; q += st) {
+    const int t = (int)(q / wstride);
+    int r = (int)(q - (size_t)t * wstride), l = 0, woff = 0;
+    while (l < md.n_dense && r >= ml_layer_words(md.in_of(t, l), md.width[l])) {
+      r -= ml_layer_words(md.in_of(t, l), md.width[l]);
+      woff += md.in_of(t, l) * md.width[l] + md.width[l];
+      l++;
+    }
+    T v = T(0);
+    if (l < md.n_dense) {
+      const int out = md.width[l], ld = ml_ld(out);
+      const int i = r / ld, j = r - i * ld;
+      if (j < out) v = theta[md.off_w[t] + woff + i * out + j];  // row `in` is the bias
+    }
+    wpack[q] = v;
+  }
 }
 
 // One launch for everything between the force sweep and the backward sweeps.  Blocks [0,nf):
@@ -903,6 +982,8 @@ struct stafb_model {
   size_t mlp_fwd_smem, mlp_bwd_smem;
   // scratch for max_batch frames
   void *rad, *d3s, *af, *nd, *acts, *e_atom, *force, *fbar, *ebar, *gradnet, *gaf, *energy, *vrow;
+  void* wpack;  // packed, padded Dense layers of every species (k_prep), wstride elements per species
+  int wstride;
   int nv;  // row length of vrow: nt*Frmax + C*3*Famax
   int *im2, *ntr;
   double* losses_d;  // [0..4] the four losses + the done-counter of k_loss; [8 + 9*b + c] virial accumulators
@@ -1032,6 +1113,8 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   m->nv = d.nt * d.Frmax + d.C * 3 * d.Famax;
   STAFB_CUDA_OK(cudaMalloc(&m->vrow, es * A * (m->nv > 0 ? m->nv : 1)));
   STAFB_CUDA_OK(cudaMalloc(&m->acts, es * mlp_blocks * 8 * m->apt * d.Hsum));
+  m->wstride = (int)mlp_stage_words(d, 2);
+  STAFB_CUDA_OK(cudaMalloc(&m->wpack, es * (size_t)d.nt * m->wstride));
   STAFB_CUDA_OK(cudaMalloc(&m->e_atom, es * A));
   STAFB_CUDA_OK(cudaMalloc(&m->force, es * A * 3));
   STAFB_CUDA_OK(cudaMalloc(&m->fbar, es * A * 3));
@@ -1054,7 +1137,7 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
 extern "C" void stafb_model_destroy(stafb_model* m) {
   if (!m) return;
   void* ptrs[] = {m->rad, m->d3s, m->im2, m->ntr, m->af, m->nd, m->gradnet, m->gaf, m->acts, m->e_atom, m->force,
-                  m->fbar, m->ebar, m->energy, m->losses_d, m->vrow};
+                  m->fbar, m->ebar, m->energy, m->losses_d, m->vrow, m->wpack};
   for (void* p : ptrs) cudaFree(p);
   for (int k = 0; k < 3; k++) {
     cudaFreeHost(m->slot_in_h[k]);
@@ -1131,8 +1214,8 @@ static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta
                                        (int)m->mlp_fwd_smem));
     attr = m->mlp_fwd_smem;
   }
-  k_mlp_fwd<T, APT><<<species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_fwd_smem, s>>>(m->md, nf, theta, af, acts,
-                                                                                           e_atom, nd, m->stage);
+  k_mlp_fwd<T, APT><<<species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_fwd_smem, s>>>(
+      m->md, nf, theta, (const T*)m->wpack, m->wstride, af, acts, e_atom, nd, m->stage);
   m->ctx->launches++;
   return STAFB_OK;
 }
@@ -1147,8 +1230,8 @@ static int launch_mlp_bwd(stafb_model* m, cudaStream_t s, int nf, const T* theta
                                        (int)m->mlp_bwd_smem));
     attr = m->mlp_bwd_smem;
   }
-  k_mlp_bwd<T, APT><<<species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_bwd_smem, s>>>(m->md, nf, theta, af, acts,
-                                                                                           ebar, u, vrow, m->nv, gaf, grad, m->stage);
+  k_mlp_bwd<T, APT><<<species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_bwd_smem, s>>>(
+      m->md, nf, theta, (const T*)m->wpack, m->wstride, af, acts, ebar, u, vrow, m->nv, gaf, grad, m->stage);
   m->ctx->launches++;
   return STAFB_OK;
 }
@@ -1192,9 +1275,9 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
   T* af = (T*)m->af; T* nd = (T*)m->nd; T* acts = (T*)m->acts; T* e_atom = (T*)m->e_atom;
   T* force = force_out ? force_out : (T*)m->force;
   T* energy = energy_out ? energy_out : (T*)m->energy;
-  k_zero3<<<64, 256, 0, s>>>(force, sizeof(T) * (size_t)nf * 3 * nall, train ? (void*)grad : nullptr,
-                             train ? sizeof(T) * (size_t)m->n_params : 0, m->losses_d,
-                             sizeof(double) * (virial_out ? 8 + 9 * (size_t)nf : 5));
+  k_prep<T><<<64, 256, 0, s>>>(d, theta, (T*)m->wpack, m->wstride, force, sizeof(T) * (size_t)nf * 3 * nall,
+                               train ? (void*)grad : nullptr, train ? sizeof(T) * (size_t)m->n_params : 0,
+                               m->losses_d, sizeof(double) * (virial_out ? 8 + 9 * (size_t)nf : 5));
   c->launches++;
   mark();  // descriptors
   SweepIn<T> in;

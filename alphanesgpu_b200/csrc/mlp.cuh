@@ -42,19 +42,18 @@ struct LayerView {
   bool vec;    // rows are 16-byte aligned and padded with zeros up to a multiple of four columns
 };
 
-// Copies one Dense layer (weights [in][out] row-major + bias[out]) into shared memory with the padded row
-// stride, as asynchronous global->shared copies: all of them are in flight together and no thread waits
-// for a load before it issues the next (a register-staged copy loop serialises on every element).  The
-// caller waits with ml_stage_wait().  Padding columns are zero-filled with ordinary stores.
+// The Dense layers reach the MLP kernels through a packed copy of the weights (k_prep writes it at the start
+// of every evaluation, theta changes with every optimizer step): per species, the layers back to back, each
+// as (in + 1) rows of ml_ld(out) words - weights [in][out] zero-padded to the row stride, then the bias row.
+// That layout is exactly what the kernels want in shared memory, 16-byte aligned, so staging is a plain run
+// of 16-byte asynchronous global->shared copies (all in flight together, no per-element address arithmetic).
+__host__ __device__ inline int ml_layer_words(int in, int out) { return (in + 1) * ml_ld(out); }
+
 template <class T>
-__device__ __forceinline__ void stage_copy(int in, int out, const T* __restrict__ Wl, T* wsm) {
-  const int ld = ml_ld(out), lane = threadIdx.x & 31;
-  for (int i = threadIdx.x >> 5; i <= in; i += ML_THREADS / 32) {  // row `in` is the bias
-    for (int j = lane; j < ld; j += 32) {
-      if (j < out) __pipeline_memcpy_async(wsm + i * ld + j, Wl + i * out + j, sizeof(T));
-      else wsm[i * ld + j] = T(0);
-    }
-  }
+__device__ __forceinline__ void stage_words(const T* __restrict__ src, T* wsm, int words) {
+  constexpr int PER = 16 / (int)sizeof(T);  // elements per 16-byte copy; words is a multiple of 4
+  for (int idx = threadIdx.x * PER; idx < words; idx += ML_THREADS * PER)
+    __pipeline_memcpy_async(wsm + idx, src + idx, 16);
   __pipeline_commit();
 }
 
@@ -64,46 +63,36 @@ __device__ __forceinline__ void ml_stage_wait() {
 }
 
 template <class T>
-__device__ __forceinline__ LayerView<T> staged_view(int in, int out, const T* wsm) {
+__device__ __forceinline__ LayerView<T> layer_view(int in, int out, const T* base) {
   LayerView<T> v;
   v.ld = ml_ld(out);
-  v.W = wsm; v.B = wsm + in * v.ld; v.vec = true;
+  v.W = base; v.B = base + in * v.ld; v.vec = true;
   return v;
 }
 
-// Dense layer l of species t for the products below.  mode 2: every layer was staged when the kernel
-// started (wsm holds them back to back); mode 1: stage this layer now; mode 0: read global memory (the
-// layer does not fit next to the activations; scalar paths of the products).
+// Dense layer l of species t for the products below; wp = the species' packed weights in global memory.
+// mode 2: every layer was staged when the kernel started (wsm holds them back to back); mode 1: stage this
+// layer now; mode 0: read the packed copy in global memory (the layer does not fit next to the activations).
 template <class T>
-__device__ __forceinline__ LayerView<T> get_layer(const ModelDev& md, int t, int l, const T* __restrict__ w, T* wsm,
+__device__ __forceinline__ LayerView<T> get_layer(const ModelDev& md, int t, int l, const T* __restrict__ wp, T* wsm,
                                                  int mode) {
   const int in = md.in_of(t, l), out = md.width[l];
-  if (mode == 2) {
-    int off = 0;
-    for (int k = 0; k < l; k++) off += (md.in_of(t, k) + 1) * ml_ld(md.width[k]);
-    return staged_view<T>(in, out, wsm + off);
-  }
+  int off = 0;
+  for (int k = 0; k < l; k++) off += ml_layer_words(md.in_of(t, k), md.width[k]);
+  if (mode == 2) return layer_view<T>(in, out, wsm + off);
   __syncthreads();  // previous users of wsm are done, inputs of the layer are complete
-  const T* Wl = w + md.w_off(t, l);
-  if (mode == 0) {
-    LayerView<T> v;
-    v.W = Wl; v.B = Wl + in * out; v.ld = out; v.vec = false;
-    return v;
-  }
-  stage_copy<T>(in, out, Wl, wsm);
+  if (mode == 0) return layer_view<T>(in, out, wp + off);
+  stage_words<T>(wp + off, wsm, ml_layer_words(in, out));
   ml_stage_wait();
-  return staged_view<T>(in, out, wsm);
+  return layer_view<T>(in, out, wsm);
 }
 
 // mode 2: issue the copies of every layer (the caller overlaps them with its own global loads, then waits)
 template <class T>
-__device__ __forceinline__ void stage_all_layers(const ModelDev& md, int t, const T* __restrict__ w, T* wsm) {
-  int off = 0;
-  for (int l = 0; l < md.n_dense; l++) {
-    const int in = md.in_of(t, l), out = md.width[l];
-    stage_copy<T>(in, out, w + md.w_off(t, l), wsm + off);
-    off += (in + 1) * ml_ld(out);
-  }
+__device__ __forceinline__ void stage_all_layers(const ModelDev& md, int t, const T* __restrict__ wp, T* wsm) {
+  int words = 0;
+  for (int l = 0; l < md.n_dense; l++) words += ml_layer_words(md.in_of(t, l), md.width[l]);
+  stage_words<T>(wp, wsm, words);
 }
 
 // Y[j][a] = act( b[j] + sum_i X[i][a] W[i,j] ).  A thread owns one output j for a group of eight atoms and
@@ -235,8 +224,9 @@ __device__ __forceinline__ long long ml_atom_row(const ModelDev& md, int t, int 
 
 template <class T, int APT>
 __global__ void __launch_bounds__(ML_THREADS)
-    k_mlp_fwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ af, T* __restrict__ acts,
-              T* __restrict__ e_atom, T* __restrict__ netderiv, int stage) {
+    k_mlp_fwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ wpack, int wstride,
+              const T* __restrict__ af, T* __restrict__ acts, T* __restrict__ e_atom, T* __restrict__ netderiv,
+              int stage) {
   constexpr int TA = 8 * APT, TAP = TA + ML_PAD;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ long long rows[TA];
@@ -250,7 +240,7 @@ __global__ void __launch_bounds__(ML_THREADS)
   T* C1 = C0 + mw * TAP;                  // [mw][TAP]
   T* wsm = C1 + mw * TAP;                 // one staged layer
   const T* mu = theta + md.off_mu[t];
-  const T* w = theta + md.off_w[t];
+  const T* w = wpack + (size_t)t * wstride;  // this species' packed layers
   ML_CLK_INIT
   if (threadIdx.x < TA) rows[threadIdx.x] = ml_atom_row(md, t, q0, nat, threadIdx.x);
   if (stage == 2) stage_all_layers<T>(md, t, w, wsm);
@@ -320,8 +310,8 @@ __global__ void __launch_bounds__(ML_THREADS)
 // (vrow), which yields the fingerprint part of dL/dalpha without another sweep over the triplets.
 template <class T, int APT>
 __global__ void __launch_bounds__(ML_THREADS)
-    k_mlp_bwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ af,
-              const T* __restrict__ acts, const T* __restrict__ ebar /*[nf]*/, const T* __restrict__ u /*[nf,N,Fmax]*/,
+    k_mlp_bwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ wpack, int wstride,
+              const T* __restrict__ af, const T* __restrict__ acts, const T* __restrict__ ebar /*[nf]*/, const T* __restrict__ u /*[nf,N,Fmax]*/,
               const T* __restrict__ vrow /*[nf,N,nv] or null*/, int nv, T* __restrict__ gaf, T* __restrict__ grad,
               int stage) {
   typedef typename Vec4<T>::type T4;
@@ -343,7 +333,7 @@ __global__ void __launch_bounds__(ML_THREADS)
   T* CP = CQ + mw * TAP;                  // [mw][TAP]
   T* wsm = CP + mw * TAP;                 // one staged layer
   const T* mu = theta + md.off_mu[t];
-  const T* w = theta + md.off_w[t];
+  const T* w = wpack + (size_t)t * wstride;  // this species' packed layers
   if (threadIdx.x < TA) rows[threadIdx.x] = ml_atom_row(md, t, q0, nat, threadIdx.x);
   if (stage == 2) stage_all_layers<T>(md, t, w, wsm);
   __syncthreads();
