@@ -32,7 +32,7 @@ template <int MODE> struct SweepWpa { static constexpr int value = (MODE == 1) ?
 // Resident blocks per SM the sweep kernels are compiled for (caps the registers per thread: 65536 / (threads *
 // blocks)).  Without the cap the register allocation of one mode moves by +-30 % with unrelated edits, and the
 // sweeps are occupancy-sensitive: a step's 3072 one-warp blocks fit the 148 SMs in one wave at <= 96 registers.
-template <int MODE, size_t ES> struct SweepMinBlocks { static constexpr int value = 28; };  // <= 73 registers
+template <int MODE, size_t ES> struct SweepMinBlocks { static constexpr int value = 21; };  // <= 97 registers
 template <> struct SweepMinBlocks<1, 4> { static constexpr int value = 12; };  // force, 64 threads: <= 85
 template <> struct SweepMinBlocks<2, 4> { static constexpr int value = 21; };  // force backward: <= 97
 template <> struct SweepMinBlocks<0, 8> { static constexpr int value = 21; };  // fp64: <= 97
@@ -256,6 +256,9 @@ __global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::val
   typedef typename Vec4<T>::type T4;
   typedef typename Vec2<T>::type T2;
   constexpr int NT = WPA * 32;
+  // independent pairs in flight per lane: two hide the shared-memory and exp2 latencies of the fingerprint sweeps
+  // (41 -> 36 us); the force-backward sweep needs 108 registers for that and gets slower
+  constexpr int PAIR_UNROLL = (MODE == MODE_FGRAD) ? 1 : 2;
   constexpr bool IS_AF = (MODE == MODE_AF || MODE == MODE_AFV);       // produces fingerprints
   constexpr bool HAS_V = (MODE == MODE_AFGRAD || MODE == MODE_AFV);   // accumulates d(AF)/d(alpha) terms
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -603,6 +606,7 @@ __global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::val
           if (tid < np) {
             if (same) ps.init_tri(tid, na_); else ps.init_rect(tid, nb_);
           }
+#pragma unroll(PAIR_UNROLL)
           for (int p = tid; p < np; p += NT) {
             const int j = la[ps.ja], k = lb[ps.kb];
             if (same) ps.step_tri(na_, NT); else ps.step_rect(nb_, qst, rst);
