@@ -334,6 +334,7 @@ __global__ void __launch_bounds__(ML_THREADS)
   T* wsm = CP + mw * TAP;                 // one staged layer
   const T* mu = theta + md.off_mu[t];
   const T* w = wpack + (size_t)t * wstride;  // this species' packed layers
+  ML_CLK_INIT
   if (threadIdx.x < TA) rows[threadIdx.x] = ml_atom_row(md, t, q0, nat, threadIdx.x);
   if (stage == 2) stage_all_layers<T>(md, t, w, wsm);
   __syncthreads();
@@ -355,6 +356,7 @@ __global__ void __launch_bounds__(ML_THREADS)
     H[(idx / TA) * TAP + a] = (q0 + a < nat) ? ab[idx] : T(0);
   }
   if (stage == 2) ml_stage_wait();
+  ML_TICK(1, 0)
   // forward tangent: AD = HDin W ; HD = AD * act'
   const T* hdin = V;
   LayerView<T> lv;
@@ -374,6 +376,7 @@ __global__ void __launch_bounds__(ML_THREADS)
     hdin = hdo;
   }
   __syncthreads();
+  ML_TICK(1, 1)
   // reverse over (h, hd)
   if (threadIdx.x < TA) {
     const long long gi = rows[threadIdx.x];
@@ -404,6 +407,7 @@ __global__ void __launch_bounds__(ML_THREADS)
       dpl[o] = pa;
     }
     __syncthreads();
+    ML_TICK(1, 2)
     // weight gradient of this layer, summed over the block's atoms: 2 inputs x 2 outputs per thread,
     // atoms four at a time (the padded row stride keeps the 16-byte loads of consecutive rows conflict-free)
     const T* hin = (l == 0) ? X : H + md.h_off(l - 1) * TAP;
@@ -439,8 +443,10 @@ __global__ void __launch_bounds__(ML_THREADS)
       for (int a = 0; a < TA; a++) g += dql[j * TAP + a];
       atomicAdd(gw + woff + in * out + j, g);
     }
+    ML_TICK(1, 3)
     // cotangents on the layer input
     dense_bwd<T, TA>(in, out, lv, dql, CQ, dpl, CP);
+    ML_TICK(1, 4)
   }
   // CQ = dS/dx, CP = dS/dv  ->  dL/dAF, kept in V for the contraction below
   for (int idx = threadIdx.x; idx < Fm * TA; idx += ML_THREADS) {
@@ -459,6 +465,7 @@ __global__ void __launch_bounds__(ML_THREADS)
     for (int a = 0; a < TA; a++) g -= CQ[i * TAP + a];
     atomicAdd(grad + md.off_mu[t] + i, g);
   }
+  ML_TICK(1, 5)
   if (vrow) {
     __syncthreads();
     // dL/dalpha (fingerprint part) = sum_atoms dL/dAF[c(q)] * dAF[c(q)]/dalpha[q]; alpha2b and alpha3b
@@ -474,4 +481,5 @@ __global__ void __launch_bounds__(ML_THREADS)
       if (g != T(0)) atomicAdd(grad + md.off_a2[t] + q, g);
     }
   }
+  ML_TICK(1, 6)
 }

@@ -322,7 +322,7 @@ def run_ours(args):
            "af_grad": row_bytes + chan, "mlp_fwd": 3 * chan, "mlp_bwd": 4 * chan}[dom]
     # DRAM traffic per launch of each sweep (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of
     # this workload at batch 4, profiles/k_sweep_water768_b4_fp32.md); it scales with the number of atoms
-    traffic_ncu_b4 = {"af_fwd": 5.23e6, "force": 5.58e6, "force_grad": 5.58e6, "mlp_fwd": 0.40e6, "mlp_bwd": 3.85e6}
+    traffic_ncu_b4 = {"af_fwd": 5.23e6, "force": 5.56e6, "force_grad": 5.58e6, "mlp_fwd": 0.40e6, "mlp_bwd": 3.85e6}
     traffic = traffic_ncu_b4.get(dom)
     if traffic is not None:
         traffic *= B / 4.0
