@@ -872,10 +872,8 @@ __global__ void __launch_bounds__(256)
   const int blk = blockIdx.x;
   if (blk < nf) {
     if (virial_out && threadIdx.x < 9) virial_out[blk * 9 + threadIdx.x] = (T)vacc[blk * 9 + threadIdx.x];
-    double s = 0.0;
-    for (int q = threadIdx.x; q < N; q += blockDim.x) s += (double)e_atom[(size_t)blk * N + q];
-    s = block_sum<double, 8>(s, red);
     if (threadIdx.x == 0) {
+      const double s = losses[8 + blk];  // sum of the frame's atomic energies, accumulated by the MLP kernel
       const double Eb = per_atom ? 0.5 * s / N : 0.5 * s;
       if (!isfinite(Eb)) set_status(status, STAFB_ERR_NONFINITE);
       if (energy) energy[blk] = (T)Eb;
@@ -990,7 +988,8 @@ struct stafb_model {
   int wstride;
   int nv;  // row length of vrow: nt*Frmax + C*3*Famax
   int *im2, *ntr;
-  double* losses_d;  // [0..4] the four losses + the done-counter of k_loss; [8 + 9*b + c] virial accumulators
+  double* losses_d;  // [0..4] the four losses + the done-counter of k_loss; [8 + b] sum of the atomic energies of
+                     // frame b (accumulated by the MLP kernel); [8 + max_batch + 9*b + c] virial accumulators
   // staging for the *_host entry points
   // two pipelined slots for stafb_train_step_host_begin/_end: pinned input block (pos | f_label | box | e_label),
   // pinned results (4 losses + status) and the event that marks the slot's step complete
@@ -1124,7 +1123,7 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   STAFB_CUDA_OK(cudaMalloc(&m->fbar, es * A * 3));
   STAFB_CUDA_OK(cudaMalloc(&m->ebar, es * c->max_batch));
   STAFB_CUDA_OK(cudaMalloc(&m->energy, es * c->max_batch));
-  STAFB_CUDA_OK(cudaMalloc((void**)&m->losses_d, sizeof(double) * (8 + 9 * (size_t)c->max_batch)));
+  STAFB_CUDA_OK(cudaMalloc((void**)&m->losses_d, sizeof(double) * (8 + 10 * (size_t)c->max_batch)));
   {
     const size_t blk = es * (A * 6 + (size_t)c->max_batch * 7 + 8);
     for (int k = 0; k < 3; k++) {
@@ -1219,7 +1218,7 @@ static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta
     attr = m->mlp_fwd_smem;
   }
   k_mlp_fwd<T, APT><<<species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_fwd_smem, s>>>(
-      m->md, nf, theta, (const T*)m->wpack, m->wstride, af, acts, e_atom, nd, m->stage);
+      m->md, nf, theta, (const T*)m->wpack, m->wstride, af, acts, e_atom, nd, m->losses_d + 8, m->stage);
   m->ctx->launches++;
   return STAFB_OK;
 }
@@ -1281,7 +1280,7 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
   T* energy = energy_out ? energy_out : (T*)m->energy;
   k_prep<T><<<64, 256, 0, s>>>(d, theta, (T*)m->wpack, m->wstride, force, sizeof(T) * (size_t)nf * 3 * nall,
                                train ? (void*)grad : nullptr, train ? sizeof(T) * (size_t)m->n_params : 0,
-                               m->losses_d, sizeof(double) * (virial_out ? 8 + 9 * (size_t)nf : 5));
+                               m->losses_d, sizeof(double) * (virial_out ? 8 + 10 * (size_t)c->max_batch : 8 + (size_t)c->max_batch));
   c->launches++;
   mark();  // descriptors
   SweepIn<T> in;
@@ -1298,7 +1297,7 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
                      : launch_mlp_fwd<T, 1>(m, s, nf, theta, af, acts, e_atom, nd);
   if (rc != STAFB_OK) return rc;
   mark();  // mlp_fwd
-  double* vacc = virial_out ? m->losses_d + 8 : nullptr;
+  double* vacc = virial_out ? m->losses_d + 8 + c->max_batch : nullptr;
   // two warps per atom shorten the ordered-pair loop while the GPU is not full; once there are several blocks
   // per warp slot, one warp per atom (no block barriers) has the higher throughput
   static const long long one_warp_atoms =

@@ -40,6 +40,12 @@ struct StafModel {
   size_t in_bytes, out_bytes;
   cudaStream_t stream;
   std::vector<int> to_slot;
+  // the device work of one call (copy in, kernels, copy out) captured as a CUDA graph; replayed while the call's
+  // shape (atom counts per species, ghosts, list or no list) stays the same, as it does between the
+  // re-neighbouring steps of an MD run
+  struct GraphKey { int nall, nlocal, has_list; size_t in_used; int tipos[STAFB_MAX_TYPES]; } gkey;
+  int gstate;  // 0 nothing, 1 shape seen once (ran as plain launches), 2 graph ready, -1 capture failed for this shape
+  cudaGraphExec_t gexec;
 };
 
 static bool read_matrix(const std::string& path, std::vector<double>& out) {
@@ -124,6 +130,9 @@ static void release_device(StafModel* m) {
   m->theta_d = m->emb_d = nullptr;
   m->in_d = m->out_d = m->in_h = m->out_h = nullptr;
   m->cap_n = 0;
+  if (m->gexec) cudaGraphExecDestroy(m->gexec);
+  m->gexec = nullptr;
+  m->gstate = 0;
 }
 
 extern "C" StafModel* staf_load(const char* model_dir, const StafOptions* opt) {
@@ -136,6 +145,9 @@ extern "C" StafModel* staf_load(const char* model_dir, const StafOptions* opt) {
   m->theta_d = m->emb_d = nullptr;
   m->in_d = m->out_d = m->in_h = m->out_h = nullptr;
   m->stream = nullptr;
+  m->gexec = nullptr;
+  m->gstate = 0;
+  memset(&m->gkey, 0, sizeof(m->gkey));
   const int dev = staf_cuda_set_device(m->opt.device_id);
   if (dev < 0) { delete m; return NULL; }
   m->opt.device_id = dev;
@@ -324,14 +336,54 @@ static int compute_impl(StafModel* m, int nlocal, int nghost, const double* x, c
     in_used = L.with + 4 * (size_t)nlocal * nr;
   }
   cudaStream_t s = m->stream;
-  if (cudaMemcpyAsync(m->in_d, m->in_h, in_used, cudaMemcpyHostToDevice, s) != cudaSuccess) return -14;
-  int rc = stafb_energy_force_domain(
-      m->ctx, m->model, s, m->in_d + L.pos, m->in_d + L.box, nall, reinterpret_cast<const int*>(m->in_d + L.tmap),
-      howmany ? reinterpret_cast<const int*>(m->in_d + L.how) : nullptr,
-      howmany ? reinterpret_cast<const int*>(m->in_d + L.with) : nullptr, m->theta_d, m->emb_d, m->out_d + L.energy,
-      m->out_d + L.force, m->out_d + L.virial);
-  if (rc != STAFB_OK) return rc == STAFB_ERR_CUDA ? -14 : -13;
-  if (cudaMemcpyAsync(m->out_h, m->out_d, L.out_total, cudaMemcpyDeviceToHost, s) != cudaSuccess) return -14;
+  auto enqueue = [&]() -> int {
+    if (cudaMemcpyAsync(m->in_d, m->in_h, in_used, cudaMemcpyHostToDevice, s) != cudaSuccess) return -14;
+    const int rc = stafb_energy_force_domain(
+        m->ctx, m->model, s, m->in_d + L.pos, m->in_d + L.box, nall, reinterpret_cast<const int*>(m->in_d + L.tmap),
+        howmany ? reinterpret_cast<const int*>(m->in_d + L.how) : nullptr,
+        howmany ? reinterpret_cast<const int*>(m->in_d + L.with) : nullptr, m->theta_d, m->emb_d, m->out_d + L.energy,
+        m->out_d + L.force, m->out_d + L.virial);
+    if (rc != STAFB_OK) return rc == STAFB_ERR_CUDA ? -14 : -13;
+    if (cudaMemcpyAsync(m->out_h, m->out_d, L.out_total, cudaMemcpyDeviceToHost, s) != cudaSuccess) return -14;
+    return 0;
+  };
+  StafModel::GraphKey key;
+  memset(&key, 0, sizeof(key));
+  key.nall = nall; key.nlocal = nlocal; key.has_list = howmany != nullptr; key.in_used = in_used;
+  for (int t = 0; t < nt; t++) key.tipos[t] = tipos[t];
+  if (m->gstate == 0 || memcmp(&key, &m->gkey, sizeof(key)) != 0) {
+    if (m->gexec) { cudaGraphExecDestroy(m->gexec); m->gexec = nullptr; }
+    m->gkey = key;
+    m->gstate = 0;
+  }
+  static const bool no_graph = getenv("STAFB_NO_STEP_GRAPH") != nullptr;
+  if (m->gstate == 2) {
+    if (cudaGraphLaunch(m->gexec, s) != cudaSuccess) return -14;
+  } else if (m->gstate == 1 && !no_graph) {
+    cudaGraph_t g = nullptr;
+    int rc = 0;
+    bool ok = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+    if (ok) {
+      rc = enqueue();
+      ok = cudaStreamEndCapture(s, &g) == cudaSuccess && rc == 0 && g != nullptr;
+    }
+    if (ok) ok = cudaGraphInstantiate(&m->gexec, g, 0) == cudaSuccess;
+    if (g) cudaGraphDestroy(g);
+    if (ok) {
+      m->gstate = 2;
+      if (cudaGraphLaunch(m->gexec, s) != cudaSuccess) return -14;
+    } else {
+      cudaGetLastError();
+      m->gexec = nullptr;
+      m->gstate = -1;
+      rc = enqueue();
+      if (rc != 0) return rc;
+    }
+  } else {
+    const int rc = enqueue();
+    if (rc != 0) return rc;
+    if (m->gstate == 0) m->gstate = 1;
+  }
   const int st = stafb_status(m->ctx, s);  // synchronises the stream
   if (st == STAFB_ERR_RADIAL_OVERFLOW) return -11;
   if (st == STAFB_ERR_ANGULAR_OVERFLOW) return -12;

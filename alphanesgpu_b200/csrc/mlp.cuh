@@ -226,7 +226,7 @@ template <class T, int APT>
 __global__ void __launch_bounds__(ML_THREADS)
     k_mlp_fwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ wpack, int wstride,
               const T* __restrict__ af, T* __restrict__ acts, T* __restrict__ e_atom, T* __restrict__ netderiv,
-              int stage) {
+              double* __restrict__ e_sum /*[nf] accumulated*/, int stage) {
   constexpr int TA = 8 * APT, TAP = TA + ML_PAD;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ long long rows[TA];
@@ -273,6 +273,24 @@ __global__ void __launch_bounds__(ML_THREADS)
   if (threadIdx.x < TA) {
     const long long gi = rows[threadIdx.x];
     if (gi >= 0) e_atom[gi] = H[md.h_off(Lq - 1) * TAP + threadIdx.x];
+  }
+  if (threadIdx.x == 0) {
+    // per-frame sums of the block's atomic energies (a block's atoms are consecutive: one or two frames)
+    const T* eo = H + md.h_off(Lq - 1) * TAP;
+    double acc = 0.0;
+    long long bcur = -1;
+    for (int a = 0; a < TA; a++) {
+      const long long gi = rows[a];
+      if (gi < 0) break;
+      const long long b = gi / md.N;
+      if (b != bcur) {
+        if (bcur >= 0) atomicAdd(e_sum + bcur, acc);
+        acc = 0.0;
+        bcur = b;
+      }
+      acc += (double)eo[a];
+    }
+    if (bcur >= 0) atomicAdd(e_sum + bcur, acc);
   }
   ML_TICK(0, 7)
   // de/dx by the reverse sweep: cn = cotangent on the output of layer l
