@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include "../../include/stafb.h"
 
 namespace stafb {
@@ -40,6 +41,39 @@ __device__ __forceinline__ double r_abs(double x) { return fabs(x); }
 
 // Device code never traps: problems are recorded once in a status word the host reads.
 __device__ __forceinline__ void set_status(int* st, int code) { atomicCAS(st, 0, code); }
+
+// Programmatic dependent launch.  A kernel launched through launch_chained() may become resident while the
+// kernel before it on the stream is still running; it must call chain_wait() before it reads anything that
+// kernel wrote and before its first global write.  What it does ahead of that (staging of neighbour rows or
+// weights that are at least two kernels old, shared-memory set-up) overlaps the predecessor's tail.  chain_wait()
+// returns once the predecessor has completed and its writes are visible, and only then lets the NEXT kernel of
+// the chain start: so whenever a kernel runs its prologue, everything up to two kernels back has completed.
+// Both calls are no-ops for a kernel that was launched the ordinary way.
+__device__ __forceinline__ void chain_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+inline bool chained_launches_enabled() {
+  static const bool on = getenv("STAFB_NO_CHAINED_LAUNCH") == nullptr;
+  return on;
+}
+
+template <class... KArgs, class... Args>
+inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                  Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = chained_launches_enabled() ? 1 : 0;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 template <class T>
 __device__ __forceinline__ T warp_sum(T v) {

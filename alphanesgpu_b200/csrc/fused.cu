@@ -323,6 +323,8 @@ __global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::val
     ids[k] = id;
     tj[k] = (unsigned char)(in.tmap ? in.tmap[id] : md.type_of(id));
   }
+  // the neighbour rows above are at least two kernels old; netderiv / dL/dF / the zeroed outputs below are not
+  chain_wait();
   // angular parameters of every (class, channel), fetched while the neighbour row is still in flight
   for (int idx = tid; idx < md.ncls * Fa; idx += NT) {
     const int c = idx % Fa;
@@ -831,6 +833,7 @@ __device__ __forceinline__ T huber_d(T e) { return e > T(1) ? T(1) : (e < T(-1) 
 template <class T>
 __global__ void k_prep(ModelDev md, const T* __restrict__ theta, T* __restrict__ wpack, int wstride, void* a,
                        size_t na, void* b, size_t nb, void* c, size_t nc) {
+  chain_wait();
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
   for (size_t q = tid; q < na / 4; q += st) reinterpret_cast<int*>(a)[q] = 0;
   for (size_t q = tid; q < nb / 4; q += st) reinterpret_cast<int*>(b)[q] = 0;
@@ -865,9 +868,10 @@ __global__ void __launch_bounds__(256)
     k_loss(ModelDev md, int nf, int fb, int per_atom, int train, const T* __restrict__ e_atom, T* __restrict__ energy,
            const T* __restrict__ e_label, const T* __restrict__ force, const T* __restrict__ f_label,
            const T* __restrict__ theta, T pe, T pf, T pb, T bound, int loss_kind, T* __restrict__ ebar,
-           T* __restrict__ fbar, T* __restrict__ grad, double* __restrict__ losses, int* __restrict__ status,
-           const double* __restrict__ vacc, T* __restrict__ virial_out, double* __restrict__ mirror) {
+           T* __restrict__ fbar, T* __restrict__ grad, double* __restrict__ losses, int* status,
+           int* status_main, const double* __restrict__ vacc, T* __restrict__ virial_out, double* __restrict__ mirror) {
   __shared__ double red[9];
+  chain_wait();
   const int N = md.N;
   const int blk = blockIdx.x;
   if (blk < nf) {
@@ -922,6 +926,10 @@ __global__ void __launch_bounds__(256)
         mirror[0] = tot; mirror[1] = le; mirror[2] = lb; mirror[3] = lf;
         reinterpret_cast<int*>(mirror + 4)[0] = atomicExch(status, 0);
         __threadfence_system();
+      } else if (status_main != status) {
+        // prefetched neighbour rows report into their own word: hand it over to the context's
+        const int v = atomicExch(status, 0);
+        if (v) set_status(status_main, v);
       }
     }
   }
@@ -929,7 +937,8 @@ __global__ void __launch_bounds__(256)
 
 template <class T>
 __global__ void k_adam(int n, T* __restrict__ theta, const T* __restrict__ grad, T* __restrict__ m,
-                       T* __restrict__ v, T lr_t, T b1, T b2, T eps, T gscale) {
+                       T* __restrict__ v, T lr_t, T b1, T b2, T eps, T gscale) {  chain_wait();
+
   const int q = blockIdx.x * blockDim.x + threadIdx.x;
   if (q >= n) return;
   const T g = grad[q] * gscale;
@@ -945,7 +954,8 @@ __global__ void k_adam(int n, T* __restrict__ theta, const T* __restrict__ grad,
 template <class T>
 __global__ void k_adam_dev(int n, T* __restrict__ theta, const T* __restrict__ grad, T* __restrict__ m,
                            T* __restrict__ v, double lr, double b1, double b2, T eps, T gscale,
-                           int* __restrict__ step_d /*[2]: step, blocks done*/) {
+                           int* __restrict__ step_d /*[2]: step, blocks done*/) {  chain_wait();
+
   const int q = blockIdx.x * blockDim.x + threadIdx.x;
   const int step = *reinterpret_cast<volatile int*>(step_d) + 1;
   if (q < n) {
@@ -1006,6 +1016,18 @@ struct stafb_model {
   double* mirror_next;  // mapped host memory the next training evaluation's k_loss writes its results to
   int slot_state[3];  // 0: nothing yet, 1: signature seen once (ran eagerly), 2: graph instantiated, -1: capture failed
   cudaGraphExec_t slot_exec[3];
+  // Two more sets of neighbour rows (a context of their own for the search scratch + the compact rows), so that
+  // the geometry of the NEXT step, which depends on no trainable parameter, can be built on another stream while
+  // this step's sweeps still read theirs.  Allocated on first use.
+  struct NlSet {
+    stafb_ctx* ctx;
+    void *rad, *d3s;
+    int *im2, *ntr;
+    cudaEvent_t ready;
+    int nf;  // frames the set currently describes (0: nothing)
+  } nl[2];
+  cudaStream_t side;  // stream of the prefetches issued by stafb_train_step_host_begin
+  cudaGraphExec_t nl_exec[2];
   size_t smem_limit;
 };
 
@@ -1148,6 +1170,14 @@ extern "C" void stafb_model_destroy(stafb_model* m) {
     if (m->slot_done[k]) cudaEventDestroy(m->slot_done[k]);
     if (m->slot_exec[k]) cudaGraphExecDestroy(m->slot_exec[k]);
   }
+  for (int k = 0; k < 2; k++) {
+    if (m->nl_exec[k]) cudaGraphExecDestroy(m->nl_exec[k]);
+    if (!m->nl[k].ctx) continue;
+    cudaFree(m->nl[k].rad); cudaFree(m->nl[k].d3s); cudaFree(m->nl[k].im2); cudaFree(m->nl[k].ntr);
+    cudaEventDestroy(m->nl[k].ready);
+    stafb_destroy(m->nl[k].ctx);
+  }
+  if (m->side) cudaStreamDestroy(m->side);
   free(m);
 }
 
@@ -1199,11 +1229,11 @@ static int launch_sweep(stafb_model* m, cudaStream_t s, int nf, const SweepIn<T>
   }
   const int blocks = nf * d.N;
   if (MODE == MODE_FORCE && vir)
-    k_sweep<T, MODE, SW_WPA, MODE == MODE_FORCE><<<blocks, SW_WPA * 32, sm, s>>>(d, in, L, theta, emb, chan_in, fbar,
-                                                                                out, grad, vout, nv, vir);
+    STAFB_CUDA_OK(launch_chained(k_sweep<T, MODE, SW_WPA, MODE == MODE_FORCE>, blocks, SW_WPA * 32, sm, s, d, in, L,
+                                 theta, emb, chan_in, fbar, out, grad, vout, nv, vir));
   else
-    k_sweep<T, MODE, SW_WPA, false><<<blocks, SW_WPA * 32, sm, s>>>(d, in, L, theta, emb, chan_in, fbar, out, grad,
-                                                                   vout, nv, nullptr);
+    STAFB_CUDA_OK(launch_chained(k_sweep<T, MODE, SW_WPA, false>, blocks, SW_WPA * 32, sm, s, d, in, L, theta, emb,
+                                 chan_in, fbar, out, grad, vout, nv, (double*)nullptr));
   m->ctx->launches++;
   return STAFB_OK;
 }
@@ -1217,8 +1247,9 @@ static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta
                                        (int)m->mlp_fwd_smem));
     attr = m->mlp_fwd_smem;
   }
-  k_mlp_fwd<T, APT><<<species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_fwd_smem, s>>>(
-      m->md, nf, theta, (const T*)m->wpack, m->wstride, af, acts, e_atom, nd, m->losses_d + 8, m->stage);
+  STAFB_CUDA_OK(launch_chained(k_mlp_fwd<T, APT>, species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_fwd_smem, s,
+                               m->md, nf, theta, (const T*)m->wpack, m->wstride, af, acts, e_atom, nd,
+                               m->losses_d + 8, m->stage));
   m->ctx->launches++;
   return STAFB_OK;
 }
@@ -1233,8 +1264,9 @@ static int launch_mlp_bwd(stafb_model* m, cudaStream_t s, int nf, const T* theta
                                        (int)m->mlp_bwd_smem));
     attr = m->mlp_bwd_smem;
   }
-  k_mlp_bwd<T, APT><<<species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_bwd_smem, s>>>(
-      m->md, nf, theta, (const T*)m->wpack, m->wstride, af, acts, ebar, u, vrow, m->nv, gaf, grad, m->stage);
+  STAFB_CUDA_OK(launch_chained(k_mlp_bwd<T, APT>, species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_bwd_smem, s,
+                               m->md, nf, theta, (const T*)m->wpack, m->wstride, af, acts, ebar, u, vrow, m->nv, gaf,
+                               grad, m->stage));
   m->ctx->launches++;
   return STAFB_OK;
 }
@@ -1252,9 +1284,11 @@ template <class T>
 static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos, const T* box, int nf,
                      const T* theta, const T* emb, int per_atom, bool train, const T* e_label, const T* f_label,
                      double pe, double pf, double pb, double bound, int loss_kind, double* losses_out, T* grad,
-                     T* energy_out, T* force_out, const DomainArgs* dom = nullptr, T* virial_out = nullptr) {
-  if (!c || !m || !pos || !theta || !emb || nf <= 0) return STAFB_ERR_INVALID;
-  if (!box && !(dom && dom->howmany)) return STAFB_ERR_INVALID;
+                     T* energy_out, T* force_out, const DomainArgs* dom = nullptr, T* virial_out = nullptr,
+                     const stafb_model::NlSet* pre = nullptr) {
+  if (!c || !m || (!pos && !pre) || !theta || !emb || nf <= 0) return STAFB_ERR_INVALID;
+  if (!box && !pre && !(dom && dom->howmany)) return STAFB_ERR_INVALID;
+  if (pre && (dom || pre->nf != nf)) return STAFB_ERR_INVALID;
   if (nf > c->max_batch) return STAFB_ERR_CAPACITY;
   if (train && (!e_label || !f_label || !grad || !losses_out)) return STAFB_ERR_INVALID;
   const ModelDev& d = m->md;
@@ -1267,24 +1301,30 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
     if (c->timing && c->n_phase < 16) cudaEventRecord(c->ev[c->n_phase++], s);
   };
   mark();
-  T* rad = (T*)m->rad; T* d3s = (T*)m->d3s;
-  int rc;
-  if (dom && dom->howmany)
-    rc = launch_rows_from_list<T>(c, s, pos, N, nall, dom->howmany, dom->with, rad, d3s, m->im2, m->ntr);
+  T* rad = (T*)(pre ? pre->rad : m->rad); T* d3s = (T*)(pre ? pre->d3s : m->d3s);
+  int* im2 = pre ? pre->im2 : m->im2;
+  int* ntr = pre ? pre->ntr : m->ntr;
+  const stafb_ctx* cg = pre ? pre->ctx : c;  // owner of the vector rows and of the status word of this evaluation
+  int rc = STAFB_OK;
+  if (pre)
+    c->launches = pre->ctx->launches;
+  else if (dom && dom->howmany)
+    rc = launch_rows_from_list<T>(c, s, pos, N, nall, dom->howmany, dom->with, rad, d3s, im2, ntr);
   else
-    rc = launch_descriptors<T>(c, s, pos, box, nf, nall, rad, nullptr, d3s, m->im2, nullptr, nullptr, nullptr,
-                               nullptr, m->ntr, N);
+    rc = launch_descriptors<T>(c, s, pos, box, nf, nall, rad, nullptr, d3s, im2, nullptr, nullptr, nullptr,
+                               nullptr, ntr, N);
   if (rc != STAFB_OK) return rc;
   T* af = (T*)m->af; T* nd = (T*)m->nd; T* acts = (T*)m->acts; T* e_atom = (T*)m->e_atom;
   T* force = force_out ? force_out : (T*)m->force;
   T* energy = energy_out ? energy_out : (T*)m->energy;
-  k_prep<T><<<64, 256, 0, s>>>(d, theta, (T*)m->wpack, m->wstride, force, sizeof(T) * (size_t)nf * 3 * nall,
-                               train ? (void*)grad : nullptr, train ? sizeof(T) * (size_t)m->n_params : 0,
-                               m->losses_d, sizeof(double) * (virial_out ? 8 + 10 * (size_t)c->max_batch : 8 + (size_t)c->max_batch));
+  STAFB_CUDA_OK(launch_chained(
+      k_prep<T>, 64, 256, 0, s, d, theta, (T*)m->wpack, m->wstride, (void*)force, sizeof(T) * (size_t)nf * 3 * nall,
+      train ? (void*)grad : (void*)nullptr, train ? sizeof(T) * (size_t)m->n_params : (size_t)0, (void*)m->losses_d,
+      sizeof(double) * (virial_out ? 8 + 10 * (size_t)c->max_batch : 8 + (size_t)c->max_batch)));
   c->launches++;
   mark();  // descriptors
   SweepIn<T> in;
-  in.geom = (const T*)c->geom; in.gsc = (const T*)c->gsc; in.rad = rad; in.d3s = d3s; in.im2 = m->im2; in.ntr = m->ntr;
+  in.geom = (const T*)cg->geom; in.gsc = (const T*)cg->gsc; in.rad = rad; in.d3s = d3s; in.im2 = im2; in.ntr = ntr;
   in.nf = nf; in.nr = c->nr;
   in.tmap = dom ? dom->tmap : nullptr;
   in.nall = nall;
@@ -1315,9 +1355,10 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
       if (fb > 296) fb = 296;
     }
     const int grid = nf + fb + (train ? 1 : 0);
-    k_loss<T><<<grid, 256, 0, s>>>(d, nf, fb, per_atom, train ? 1 : 0, e_atom, energy, e_label, force, f_label, theta,
-                                   (T)pe, (T)pf, (T)pb, (T)bound, loss_kind, (T*)m->ebar, (T*)m->fbar, grad,
-                                   m->losses_d, c->status_d, vacc, virial_out, train ? m->mirror_next : nullptr);
+    STAFB_CUDA_OK(launch_chained(k_loss<T>, grid, 256, 0, s, d, nf, fb, per_atom, train ? 1 : 0, e_atom, energy,
+                                 e_label, force, f_label, theta, (T)pe, (T)pf, (T)pb, (T)bound, loss_kind,
+                                 (T*)m->ebar, (T*)m->fbar, grad, m->losses_d, cg->status_d, c->status_d, vacc,
+                                 virial_out, train ? m->mirror_next : (double*)nullptr));
     m->mirror_next = nullptr;
     c->launches++;
   }
@@ -1401,6 +1442,60 @@ extern "C" int stafb_train_step(stafb_ctx* c, stafb_model* m, void* stream, cons
                            loss_kind, losses_d, (double*)grad, (double*)energy, (double*)force);
 }
 
+// Allocates neighbour-row set `slot` (0 or 1) of the model on first use.
+static int ensure_nl(stafb_ctx* c, stafb_model* m, int slot) {
+  stafb_model::NlSet& q = m->nl[slot];
+  if (q.ctx) return STAFB_OK;
+  int rc = stafb_create(&q.ctx, c->dtype, c->Rc, c->Rs, c->Ra, c->nr, c->na, c->n_max, c->max_batch);
+  if (rc != STAFB_OK) { q.ctx = nullptr; return rc; }
+  const size_t es = m->es, A = (size_t)c->max_batch * c->n_max, nr = c->nr;
+  STAFB_CUDA_OK(cudaMalloc(&q.rad, es * A * nr));
+  STAFB_CUDA_OK(cudaMalloc(&q.d3s, es * A * nr));
+  STAFB_CUDA_OK(cudaMalloc((void**)&q.im2, sizeof(int) * A * (nr + 1)));
+  STAFB_CUDA_OK(cudaMalloc((void**)&q.ntr, sizeof(int) * A));
+  STAFB_CUDA_OK(cudaEventCreateWithFlags(&q.ready, cudaEventDisableTiming));
+  q.nf = 0;
+  return STAFB_OK;
+}
+
+extern "C" int stafb_descriptors_prefetch(stafb_ctx* c, stafb_model* m, void* stream, const void* pos,
+                                          const void* box, int nf, int slot) {
+  if (!c || !m || !pos || !box || slot < 0 || slot > 1) return STAFB_ERR_INVALID;
+  if (nf <= 0 || nf > c->max_batch) return STAFB_ERR_CAPACITY;
+  int rc = ensure_nl(c, m, slot);
+  if (rc != STAFB_OK) return rc;
+  stafb_model::NlSet& q = m->nl[slot];
+  cudaStream_t s = (cudaStream_t)stream;
+  const int N = m->md.N;
+  q.ctx->launches = 0;
+  if (c->dtype == STAFB_F32)
+    rc = launch_descriptors<float>(q.ctx, s, (const float*)pos, (const float*)box, nf, N, (float*)q.rad, nullptr,
+                                   (float*)q.d3s, q.im2, nullptr, nullptr, nullptr, nullptr, q.ntr, N);
+  else
+    rc = launch_descriptors<double>(q.ctx, s, (const double*)pos, (const double*)box, nf, N, (double*)q.rad, nullptr,
+                                    (double*)q.d3s, q.im2, nullptr, nullptr, nullptr, nullptr, q.ntr, N);
+  if (rc != STAFB_OK) return rc;
+  q.nf = nf;
+  STAFB_CUDA_OK(cudaGetLastError());
+  return STAFB_OK;
+}
+
+extern "C" int stafb_train_step_prefetched(stafb_ctx* c, stafb_model* m, void* stream, int slot, int nf,
+                                           const void* theta, const void* emb, const void* el, const void* fl,
+                                           double pe, double pf, double pb, double bound, int loss_kind,
+                                           double* losses_d, void* grad, void* energy, void* force) {
+  if (!c || !m || slot < 0 || slot > 1 || !m->nl[slot].ctx) return STAFB_ERR_INVALID;
+  cudaStream_t s = (cudaStream_t)stream;
+  const stafb_model::NlSet* q = &m->nl[slot];
+  if (c->dtype == STAFB_F32)
+    return run_fused<float>(c, m, s, nullptr, nullptr, nf, (const float*)theta, (const float*)emb, 1, true,
+                            (const float*)el, (const float*)fl, pe, pf, pb, bound, loss_kind, losses_d, (float*)grad,
+                            (float*)energy, (float*)force, nullptr, nullptr, q);
+  return run_fused<double>(c, m, s, nullptr, nullptr, nf, (const double*)theta, (const double*)emb, 1, true,
+                           (const double*)el, (const double*)fl, pe, pf, pb, bound, loss_kind, losses_d,
+                           (double*)grad, (double*)energy, (double*)force, nullptr, nullptr, q);
+}
+
 extern "C" int stafb_train_step_host(stafb_ctx* c, stafb_model* m, void* stream, const void* pos_h,
                                      const void* box_h, int nf, const void* theta, const void* emb,
                                      const void* el_h, const void* fl_h, double pe, double pf, double pb,
@@ -1429,14 +1524,31 @@ static int host_step_begin(stafb_ctx* c, stafb_model* m, void* stream, const voi
   // (device-mapped) block over PCIe - positions and box once in the cell-list kernel, the labels once in the
   // loss kernel - and the loss kernel writes the four losses and the status word straight into the slot's
   // pinned result block.  That takes one host->device and two device->host DMA latencies off every step.
+  // Slots 0 and 1 build their neighbour rows on the model's side stream: the rows depend only on the positions,
+  // so the GPU works on them while the main stream is still in the previous step (or in the caller's gradient
+  // all-reduce and optimiser update); the rest of the step waits for them through an event.  Slot 2 (the
+  // one-call form) runs everything on the caller's stream.
+  const bool split = slot < 2;
+  if (split) {
+    if (!m->side) STAFB_CUDA_OK(cudaStreamCreateWithFlags(&m->side, cudaStreamNonBlocking));
+    const int rc0 = ensure_nl(c, m, slot);
+    if (rc0 != STAFB_OK) return rc0;
+  }
+  auto enqueue_rows = [&]() -> int {
+    return stafb_descriptors_prefetch(c, m, m->side, ph, ph + o_box, nf, slot);
+  };
   auto enqueue = [&]() -> int {
     m->mirror_next = oh;
+    if (split)
+      return stafb_train_step_prefetched(c, m, stream, slot, nf, theta, emb, ph + o_el, ph + o_fl, pe, pf, pb, bound,
+                                         loss_kind, m->losses_d, grad, nullptr, nullptr);
     return stafb_train_step(c, m, stream, ph, ph + o_box, nf, theta, emb, ph + o_el, ph + o_fl, pe, pf, pb, bound,
                             loss_kind, m->losses_d, grad, nullptr, nullptr);
   };
   // The same call signature on the same slot is first run as plain launches (which also performs the one-time
-  // kernel attribute set-up), then captured into a CUDA graph, then replayed: one launch per step instead of
-  // fourteen.  All addresses inside the graph are the slot's own buffers and the caller's theta/emb/grad.
+  // kernel attribute set-up), then captured into CUDA graphs (one for the rows, one for the rest), then replayed:
+  // two launches per step instead of fourteen.  All addresses inside the graphs are the slot's own buffers and
+  // the caller's theta/emb/grad.
   stafb_model::SlotKey key;
   memset(&key, 0, sizeof(key));
   key.nf = nf; key.loss_kind = loss_kind; key.theta = theta; key.emb = emb; key.grad = grad; key.stream = stream;
@@ -1444,37 +1556,45 @@ static int host_step_begin(stafb_ctx* c, stafb_model* m, void* stream, const voi
   const bool same = m->slot_state[slot] != 0 && memcmp(&key, &m->slot_key[slot], sizeof(key)) == 0;
   if (!same) {
     if (m->slot_exec[slot]) { cudaGraphExecDestroy(m->slot_exec[slot]); m->slot_exec[slot] = nullptr; }
+    if (split && m->nl_exec[slot]) { cudaGraphExecDestroy(m->nl_exec[slot]); m->nl_exec[slot] = nullptr; }
     m->slot_key[slot] = key;
     m->slot_state[slot] = 0;
   }
   static const bool no_graph = getenv("STAFB_NO_STEP_GRAPH") != nullptr;
-  int rc = STAFB_OK;
-  if (m->slot_state[slot] == 2) {
-    STAFB_CUDA_OK(cudaGraphLaunch(m->slot_exec[slot], s));
-  } else if (m->slot_state[slot] == 1 && !c->timing && !no_graph) {
+  // captures what `fn` enqueues on `cs` into an executable graph; false (and a cleared error) if that fails
+  auto capture = [&](cudaStream_t cs, cudaGraphExec_t* exec, auto&& fn) -> bool {
     cudaGraph_t g = nullptr;
-    bool ok = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+    bool ok = cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
     if (ok) {
-      rc = enqueue();
-      ok = cudaStreamEndCapture(s, &g) == cudaSuccess && rc == STAFB_OK && g != nullptr;
+      const int rcc = fn();
+      ok = cudaStreamEndCapture(cs, &g) == cudaSuccess && rcc == STAFB_OK && g != nullptr;
     }
-    if (ok) ok = cudaGraphInstantiate(&m->slot_exec[slot], g, 0) == cudaSuccess;
+    if (ok) ok = cudaGraphInstantiate(exec, g, 0) == cudaSuccess;
     if (g) cudaGraphDestroy(g);
-    if (ok) {
-      m->slot_state[slot] = 2;
-      STAFB_CUDA_OK(cudaGraphLaunch(m->slot_exec[slot], s));
-    } else {
-      cudaGetLastError();  // clear the capture error and fall back to plain launches for this signature
-      m->slot_exec[slot] = nullptr;
-      m->slot_state[slot] = -1;
-      rc = enqueue();
-      if (rc != STAFB_OK) return rc;
+    if (!ok) { cudaGetLastError(); *exec = nullptr; }
+    return ok;
+  };
+  if (m->slot_state[slot] == 1 && !c->timing && !no_graph) {
+    bool ok = capture(s, &m->slot_exec[slot], enqueue);
+    if (ok && split) ok = capture(m->side, &m->nl_exec[slot], enqueue_rows);
+    if (!ok) {
+      if (m->slot_exec[slot]) { cudaGraphExecDestroy(m->slot_exec[slot]); m->slot_exec[slot] = nullptr; }
+      m->mirror_next = nullptr;
     }
-  } else {
-    rc = enqueue();
-    if (rc != STAFB_OK) return rc;
-    if (m->slot_state[slot] == 0) m->slot_state[slot] = 1;
+    m->slot_state[slot] = ok ? 2 : -1;  // -1: plain launches for this signature from now on
+  } else if (m->slot_state[slot] == 0) {
+    m->slot_state[slot] = 1;
   }
+  const bool replay = m->slot_state[slot] == 2;
+  int rc = STAFB_OK;
+  if (split) {
+    if (replay) STAFB_CUDA_OK(cudaGraphLaunch(m->nl_exec[slot], m->side));
+    else if ((rc = enqueue_rows()) != STAFB_OK) return rc;
+    STAFB_CUDA_OK(cudaEventRecord(m->nl[slot].ready, m->side));
+    STAFB_CUDA_OK(cudaStreamWaitEvent(s, m->nl[slot].ready, 0));
+  }
+  if (replay) STAFB_CUDA_OK(cudaGraphLaunch(m->slot_exec[slot], s));
+  else if ((rc = enqueue()) != STAFB_OK) return rc;
   STAFB_CUDA_OK(cudaEventRecord(m->slot_done[slot], s));
   m->slot_busy[slot] = 1;
   return STAFB_OK;
@@ -1537,11 +1657,11 @@ extern "C" int stafb_adam_step_dev(stafb_ctx* c, void* stream, void* theta, cons
   if (!c || !theta || !grad || !mm || !vv || n <= 0 || !step_d) return STAFB_ERR_INVALID;
   cudaStream_t s = (cudaStream_t)stream;
   if (c->dtype == STAFB_F32)
-    k_adam_dev<float><<<(n + 255) / 256, 256, 0, s>>>(n, (float*)theta, (const float*)grad, (float*)mm, (float*)vv, lr,
-                                                      b1, b2, (float)eps, (float)gscale, step_d);
+    STAFB_CUDA_OK(launch_chained(k_adam_dev<float>, (n + 255) / 256, 256, 0, s, n, (float*)theta, (const float*)grad,
+                                 (float*)mm, (float*)vv, lr, b1, b2, (float)eps, (float)gscale, step_d));
   else
-    k_adam_dev<double><<<(n + 255) / 256, 256, 0, s>>>(n, (double*)theta, (const double*)grad, (double*)mm,
-                                                       (double*)vv, lr, b1, b2, eps, gscale, step_d);
+    STAFB_CUDA_OK(launch_chained(k_adam_dev<double>, (n + 255) / 256, 256, 0, s, n, (double*)theta,
+                                 (const double*)grad, (double*)mm, (double*)vv, lr, b1, b2, eps, gscale, step_d));
   STAFB_CUDA_OK(cudaGetLastError());
   return STAFB_OK;
 }

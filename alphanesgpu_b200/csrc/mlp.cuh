@@ -244,6 +244,7 @@ __global__ void __launch_bounds__(ML_THREADS)
   ML_CLK_INIT
   if (threadIdx.x < TA) rows[threadIdx.x] = ml_atom_row(md, t, q0, nat, threadIdx.x);
   if (stage == 2) stage_all_layers<T>(md, t, w, wsm);
+  chain_wait();  // the packed weights are older than the preceding kernel; everything read below is its output
   __syncthreads();
   ML_TICK(0, 0)
   for (int idx = threadIdx.x; idx < F * TA; idx += ML_THREADS) {
@@ -355,6 +356,7 @@ __global__ void __launch_bounds__(ML_THREADS)
   ML_CLK_INIT
   if (threadIdx.x < TA) rows[threadIdx.x] = ml_atom_row(md, t, q0, nat, threadIdx.x);
   if (stage == 2) stage_all_layers<T>(md, t, w, wsm);
+  chain_wait();  // the packed weights are older than the preceding kernel; everything read below is its output
   __syncthreads();
   for (int idx = threadIdx.x; idx < F * TA; idx += ML_THREADS) {
     const int i = idx % F, a = idx / F;

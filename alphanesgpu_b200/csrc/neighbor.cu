@@ -384,6 +384,7 @@ __global__ void __launch_bounds__(WARPS * 32)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gi = blockIdx.x * WARPS + warp;  // row index: the centres are the first ncen atoms of each frame
   if (gi >= nf * ncen) return;
+  chain_wait();  // the cell lists come from the kernel just before this one
   const int b = gi / ncen, i = gi - b * ncen;
   // per-warp rows: d2a[nr] d2b[nr] (T) then ja[nr] jb[nr] (int)
   T* d2a = reinterpret_cast<T*>(smem_raw) + (size_t)warp * 2 * nr;
@@ -652,9 +653,9 @@ int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box,
     constexpr int W = 4;
     size_t sm = (size_t)W * 2 * nr * (sizeof(T) + sizeof(int)) + (size_t)W * 64 * sizeof(int);
     const int rows = nf * ncen;
-    k_nl_radial<T, W><<<(rows + W - 1) / W, W * 32, sm, s>>>(nf, N, ncen, nr, cc, fg, frac, c->cell_of, c->cell_start,
-                                                          c->cells_sorted, cap, raddescr, des3bsupp, intmap2b, der2b,
-                                                          der3bsupp, numtriplet, geom, gsc, na, c->status_d);
+    STAFB_CUDA_OK(launch_chained(k_nl_radial<T, W>, (rows + W - 1) / W, W * 32, sm, s, nf, N, ncen, nr, cc, fg, frac,
+                                 c->cell_of, c->cell_start, c->cells_sorted, cap, raddescr, des3bsupp, intmap2b, der2b,
+                                 der3bsupp, numtriplet, geom, gsc, na, c->status_d));
   }
   c->launches += 1;
   if (angdescr && intmap3b && der3b) {

@@ -136,6 +136,21 @@ class StafModel:
                                           _p(energy), _p(force)), "stafb_train_step")
         return energy, force
 
+    def prefetch_rows(self, pos, box, slot):
+        """Builds the neighbour rows of a batch (device tensors) into row set `slot` (0 or 1) on the current
+        stream.  They depend on no trainable parameter, so this may run on a side stream while the previous
+        step is still in flight; loss_and_grad_prefetched(slot, ...) must be ordered after it."""
+        check(_lib.lib().stafb_descriptors_prefetch(self.ctx.h, self.h, self.ctx.stream(), _p(pos), _p(box),
+                                                    box.shape[0], int(slot)), "stafb_descriptors_prefetch")
+
+    def loss_and_grad_prefetched(self, slot, nf, e_label, f_label):
+        """loss_and_grad on the rows that prefetch_rows left in `slot`."""
+        check(_lib.lib().stafb_train_step_prefetched(self.ctx.h, self.h, self.ctx.stream(), int(slot), int(nf),
+                                                     _p(self.theta), _p(self.emb), _p(e_label), _p(f_label), self.pe,
+                                                     self.pf, self.pb, self.alpha_bound, self.loss_kind,
+                                                     _p(self.losses), _p(self.grad), None, None),
+              "stafb_train_step_prefetched")
+
     def loss_and_grad_host(self, pos, box, e_label, f_label):
         """Same with HOST numpy inputs: host->device copies, the step and the device->host read of the
         losses all happen inside the call (it returns after the stream has drained)."""

@@ -184,16 +184,29 @@ def run_ours(args):
     launches_per_step = model.launches() + 2  # + Adam and its step counter
     torch.cuda.synchronize()
 
-    # ---- CUDA graphs: one per distinct batch (pointers differ); the NCCL all-reduce stays between two graphs
-    # (capturing it into the graph made a 2-rank run hang on this pool, so it is not attempted)
+    # ---- CUDA graphs, two per distinct batch (pointers differ): the neighbour rows of a batch depend on its
+    # positions only, so they are built on a second stream while the previous step is still running (and, on
+    # several GPUs, during the gradient all-reduce and the Adam update); the rest of the step follows on the main
+    # stream.  The NCCL all-reduce stays between two graphs (capturing it into the graph made a 2-rank run hang
+    # on this pool, so it is not attempted).
+    assert NB % 2 == 0  # batch i always uses row set i & 1
     graphs = []
+    main = torch.cuda.current_stream(dev)
     side = torch.cuda.Stream(device=dev)
-    side.wait_stream(torch.cuda.current_stream())
+    rows_stream = torch.cuda.Stream(device=dev)
+    for i in range(2):  # allocate both row sets and set the kernels' attributes outside any capture
+        model.prefetch_rows(d_pos[i], d_box[i], i)
+        model.loss_and_grad_prefetched(i, B, d_el[i], d_fl[i])
+    torch.cuda.synchronize()
+    side.wait_stream(main)
     with torch.cuda.stream(side):
         for i in range(NB):
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=side):
+                model.prefetch_rows(d_pos[i], d_box[i], i & 1)
             g1 = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g1, stream=side):
-                model.loss_and_grad(d_pos[i], d_box[i], d_el[i], d_fl[i])
+                model.loss_and_grad_prefetched(i & 1, B, d_el[i], d_fl[i])
                 if world == 1:
                     model.adam_update_dev(lr)
             g2 = None
@@ -201,16 +214,35 @@ def run_ours(args):
                 g2 = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g2, stream=side):
                     model.adam_update_dev(lr, grad_scale=1.0 / world)
-            graphs.append((g1, g2))
-    torch.cuda.current_stream().wait_stream(side)
+            graphs.append((gr, g1, g2))
+    main.wait_stream(side)
     torch.cuda.synchronize()
 
-    def step_graph(i):
-        g1, g2 = graphs[i % NB]
-        g1.replay()
+    ready = [torch.cuda.Event(), torch.cuda.Event()]
+    go = torch.cuda.Event()
+    with torch.cuda.stream(rows_stream):  # rows of the very first step
+        graphs[0][0].replay()
+        ready[0].record(rows_stream)
+    counter = [0]
+
+    def step_graph(_k=None):
+        """One training step.  Steps are numbered by an internal counter, because every step also builds the rows
+        of the NEXT one; it returns only after those rows are complete on the device timeline of the main stream,
+        so that a CUDA-event interval around the call contains all the work of exactly one step."""
+        k = counter[0]
+        counter[0] += 1
+        i, s = k % NB, k & 1
+        go.record(main)
+        rows_stream.wait_event(go)  # the next rows start inside this step, not during the cache flush before it
+        with torch.cuda.stream(rows_stream):
+            graphs[(k + 1) % NB][0].replay()
+            ready[s ^ 1].record(rows_stream)
+        main.wait_event(ready[s])
+        graphs[i][1].replay()
         if world > 1:
             dist.all_reduce(model.grad)
-            g2.replay()
+            graphs[i][2].replay()
+        main.wait_event(ready[s ^ 1])
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     for w in range(W):
@@ -262,16 +294,25 @@ def run_ours(args):
     for k in range(3):
         model.loss_and_grad_host(pos[k % NB], box[k % NB], el[k % NB], fl[k % NB])
     barrier()
+
+    def e2e_loop(n):
+        # on a stream of its own: the library replays the step as CUDA graphs, which the legacy default stream
+        # cannot capture
+        with torch.cuda.stream(side):
+            for k in range(n):
+                i = k % NB
+                model.loss_and_grad_host_begin(pos[i], box[i], el[i], fl[i], k & 1)
+                if world > 1:
+                    dist.all_reduce(model.grad)
+                model.adam_update_dev(lr, grad_scale=1.0 / world)
+                if k > 0:
+                    losses = model.loss_and_grad_host_end((k - 1) & 1)
+            return model.loss_and_grad_host_end((n - 1) & 1)
+
+    e2e_loop(6)  # plain launches, capture, first replays
+    barrier()
     t0 = time.perf_counter()
-    for k in range(Ke):
-        i = k % NB
-        model.loss_and_grad_host_begin(pos[i], box[i], el[i], fl[i], k & 1)
-        if world > 1:
-            dist.all_reduce(model.grad)
-        model.adam_update_dev(lr, grad_scale=1.0 / world)
-        if k > 0:
-            e2e_losses = model.loss_and_grad_host_end((k - 1) & 1)
-    e2e_losses = model.loss_and_grad_host_end((Ke - 1) & 1)
+    e2e_losses = e2e_loop(Ke)
     barrier()
     e2e_s = time.perf_counter() - t0
     assert np.all(np.isfinite(e2e_losses))
@@ -429,7 +470,9 @@ def run_ours(args):
                        "frames": "seeded synthetic water, 256 O + 512 H, L=19.6 A, %d distinct batches" % NB,
                        "model": "2 species, Fr=10, Fa=15, MLP 25-64-32-1 tanh", "parallelism": "dp%d" % world,
                        "l2": "flushed between steps (256 MiB write); per-step CUDA events summed",
-                       "launch": "CUDA graph replay per step" + ("" if world == 1 else ", NCCL all-reduce between two graphs"),
+                       "launch": "two CUDA graphs per step: neighbour rows of the NEXT batch on a second stream, "
+                                 "the rest of the step on the main stream; each timed interval contains both"
+                                 + ("" if world == 1 else "; NCCL all-reduce between the step graph and the Adam graph"),
                        "vs_baseline_note": "published number is the reference on a V100 (README.md:42-45)"},
             "value_l2_warm": value_warm, "ms_per_step_min": float(per_step.min()),
             "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -262,6 +262,21 @@ int stafb_train_step(stafb_ctx* ctx, stafb_model* m, void* stream, const void* p
                      double pe, double pf, double pb, double alpha_bound, int loss_kind, double* losses_d,
                      void* grad_d, void* energy_d, void* force_d);
 
+/* stafb_train_step in two parts, for callers that know the next batch early (the reference's training loop
+ * prefetches its batches in a thread, STAF/staf_train.py:678-755).  The neighbour rows of a batch depend on its
+ * positions and boxes only - not on theta - so _prefetch may run on ANOTHER stream while the previous step, the
+ * gradient all-reduce or the optimiser update still occupy `stream`; the model keeps two sets of rows (slot 0, 1,
+ * allocated on first use).  stafb_train_step_prefetched then runs the rest of the step (fingerprints, network,
+ * forces, loss, backward) on the rows of `slot`.  Ordering is the caller's: the rest of the step must wait for
+ * the prefetch of its slot (an event), and a slot must not be prefetched again before the step that reads it has
+ * finished.  Results are identical to stafb_train_step's. */
+int stafb_descriptors_prefetch(stafb_ctx* ctx, stafb_model* m, void* stream, const void* positions_d,
+                               const void* boxer_d, int nf, int slot);
+int stafb_train_step_prefetched(stafb_ctx* ctx, stafb_model* m, void* stream, int slot, int nf, const void* theta_d,
+                                const void* emb_d, const void* e_label_d, const void* f_label_d, double pe,
+                                double pf, double pb, double alpha_bound, int loss_kind, double* losses_d,
+                                void* grad_d, void* energy_d, void* force_d);
+
 /* Adam update of theta in place (Keras Adam, epsilon default 1e-7: optimizer_learning_rate_utility.py:64-68):
  * g = grad*grad_scale; m,v moments; step counts from 1. */
 int stafb_adam_step(stafb_ctx* ctx, void* stream, void* theta_d, const void* grad_d, void* m_d, void* v_d, int n,
@@ -282,7 +297,8 @@ int stafb_train_step_host(stafb_ctx* ctx, stafb_model* m, void* stream, const vo
 /* stafb_train_step_host split in two so that consecutive steps overlap: _begin stages the host inputs in the
  * slot's pinned block and enqueues the step on `stream` (the kernels read that block directly over PCIe and
  * write the losses and the status word straight into pinned memory; from the third call with the same
- * arguments on, the step is one replayed CUDA graph) and returns at once; _end waits for that slot's step, writes losses_h[4] and returns the step's status
+ * arguments on, the step is two replayed CUDA graphs: the neighbour rows on a stream of the model's own, where
+ * they overlap the previous step, and the rest on `stream`) and returns at once; _end waits for that slot's step, writes losses_h[4] and returns the step's status
  * (STAFB_OK, STAFB_ERR_RADIAL_OVERFLOW, ...).  slot is 0 or 1; a slot must be collected with _end before it is
  * begun again.  Typical loop (what STAF/staf_train.py:678-755 does with a prefetch thread and TensorFlow's
  * asynchronous executor): begin(k, slot k&1); adam(k); end(k-1, slot (k-1)&1). */

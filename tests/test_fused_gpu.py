@@ -166,3 +166,62 @@ def test_pipelined_host_steps_equal_the_synchronous_call():
     with pytest.raises(Exception):
         m.loss_and_grad_host_end(0)  # nothing in flight in that slot
     m.close()
+
+
+@pytest.mark.gpu
+def test_pipelined_host_steps_replayed_as_graphs():
+    """Many begin/end rounds on both slots: plain launches, then capture, then graph replay (neighbour rows on the
+    model's side stream) all give the losses and the gradient of the one-call form for the batch of that round."""
+    from alphanesgpu_b200.model import StafModel
+    pos, box, tipos = synth.water_frames("water96", list(range(1100, 1108)))
+    shape = synth.baseline_shape(tipos)
+    theta, emb = synth.init_params(shape, dtype=np.float32)
+    el, fl = synth.labels(8, shape.N)
+    m = StafModel(shape, CFG, theta, emb, 2, dtype=torch.float32, device="cuda:0")
+    f32 = lambda a: a.astype(np.float32)
+    batch = lambda h: tuple(f32(a[2 * h:2 * h + 2]) for a in (pos, box, el, fl))
+    ref, grads = [], []
+    for h in range(4):
+        ref.append(m.loss_and_grad_host(*batch(h)).copy())
+        grads.append(m.grad.clone())
+    for k in range(12):
+        h = (k * 3) % 4  # the batch changes on every use of a slot; the call signature does not
+        m.loss_and_grad_host_begin(*batch(h), k & 1)
+        g = m.grad.clone()
+        got = m.loss_and_grad_host_end(k & 1)
+        assert np.allclose(got, ref[h], rtol=1e-6, atol=0), k
+        assert rel_err(g.cpu().numpy(), grads[h].cpu().numpy()) <= 1e-6, k
+    m.close()
+
+
+@pytest.mark.gpu
+def test_prefetched_rows_on_a_side_stream():
+    """stafb_descriptors_prefetch on another stream + stafb_train_step_prefetched == stafb_train_step."""
+    from alphanesgpu_b200.model import StafModel
+    pos, box, tipos = synth.water_frames("water96", [1200, 1201, 1202, 1203])
+    shape = synth.baseline_shape(tipos)
+    theta, emb = synth.init_params(shape, dtype=np.float64)
+    el, fl = synth.labels(4, shape.N)
+    dev = torch.device("cuda:0")
+    m = StafModel(shape, CFG, theta, emb, 2, dtype=torch.float64, device=dev)
+    d = [torch.as_tensor(a).to(dev) for a in (pos, box, el, fl)]
+    ref = []
+    for h in range(2):
+        m.loss_and_grad(*(a[2 * h:2 * h + 2] for a in d))
+        ref.append((m.losses.clone(), m.grad.clone()))
+    side = torch.cuda.Stream(device=dev)
+    main = torch.cuda.current_stream(dev)
+    ready = [torch.cuda.Event(), torch.cuda.Event()]
+    side.wait_stream(main)
+    with torch.cuda.stream(side):  # both batches' rows before either step runs
+        for h in range(2):
+            m.prefetch_rows(d[0][2 * h:2 * h + 2], d[1][2 * h:2 * h + 2], h)
+            ready[h].record(side)
+    for h in (1, 0):
+        main.wait_event(ready[h])
+        m.loss_and_grad_prefetched(h, 2, d[2][2 * h:2 * h + 2], d[3][2 * h:2 * h + 2])
+        torch.cuda.synchronize()
+        assert torch.allclose(m.losses[:4], ref[h][0][:4], rtol=1e-12, atol=0)
+        assert rel_err(m.grad.cpu().numpy(), ref[h][1].cpu().numpy()) <= 1e-11
+    m.ctx.raise_on_status("prefetched step")
+    m.close()
