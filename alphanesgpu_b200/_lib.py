@@ -59,6 +59,13 @@ _SIGS = {
     "stafb_descriptors_prefetch": [_vp, _vp, _vp, _vp, _vp, _i, _i],
     "stafb_train_step_prefetched": [_vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _i, _vp, _vp, _vp,
                                     _vp],
+    "stafb_peer_create": [_vp, _i, _i, _i, _vp],
+    "stafb_peer_handle": [_vp, _vp],
+    "stafb_peer_connect": [_vp, _vp],
+    "stafb_peer_status": [_vp],
+    "stafb_peer_grad": [_vp, _i],
+    "stafb_peer_destroy": [_vp],
+    "stafb_allreduce_adam": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _d, _d, _d, _d, _vp],
     "stafb_train_step_host": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _i, _vp, _vp],
     "stafb_train_step_host_begin": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _i, _vp, _i],
     "stafb_train_step_host_end": [_vp, _vp, _i, _vp],
@@ -87,7 +94,9 @@ def lib():
                 continue
             fn.argtypes = sig
             fn.restype = None if name in ("stafb_destroy", "stafb_model_destroy", "stafb_core_coefficients",
-                                          "stafb_model_offsets") else _i
+                                          "stafb_model_offsets", "stafb_peer_destroy") else _i
+            if name == "stafb_peer_grad":
+                fn.restype = C.c_void_p
         _LIB = L
     return _LIB
 

@@ -23,6 +23,7 @@ SOURCES = {
     "neighbor.cu": ["-fmad=false"],
     "ops.cu": [],
     "fused.cu": [],
+    "peer.cu": [],
     "libstaf_api.cu": [],
 }
 

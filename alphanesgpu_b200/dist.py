@@ -72,3 +72,75 @@ class HostWatchdog:
             if time.time() - t0 > self.timeout_s:
                 raise RuntimeError("ranks %s did not reach step %d within %.1f s" % (behind, step, self.timeout_s))
             time.sleep(0.01)
+
+
+class _DevArray:
+    """Minimal __cuda_array_interface__ carrier, so that torch can wrap memory the library allocated."""
+
+    def __init__(self, ptr, n, dtype):
+        self.__cuda_array_interface__ = {"shape": (int(n),), "typestr": "<f4" if dtype == torch.float32 else "<f8",
+                                         "data": (int(ptr), False), "version": 2}
+
+
+class PeerExchange:
+    """Gradient averaging + Adam as one kernel per rank over NVLink peer memory (stafb_allreduce_adam) for the
+    ranks of one node: the replacement of all_reduce(grad) + Adam in the data-parallel step.
+
+    Every rank calls the constructor collectively (the CUDA IPC handles travel through
+    torch.distributed.all_gather_object), then alternates parity 0 / 1 from step to step:
+
+        model.use_grad(px.grad(k & 1)); model.loss_and_grad(...); px.allreduce_adam(model, k & 1, lr)
+
+    The kernel's wait for the peers is bounded; status() returns STAFB_ERR_PEER_TIMEOUT after a miss."""
+
+    def __init__(self, model, group=None):
+        import ctypes as C
+        from . import _lib
+        self.model, self.group = model, group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = world_size(group)
+        self.n = model.theta.numel()
+        h = C.c_void_p()
+        _lib.check(_lib.lib().stafb_peer_create(model.ctx.h, self.rank, self.world, self.n, C.byref(h)),
+                   "stafb_peer_create")
+        self.h = h
+        if self.world > 1:
+            mine = C.create_string_buffer(64)
+            _lib.check(_lib.lib().stafb_peer_handle(self.h, mine), "stafb_peer_handle")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(mine.raw), group=group)
+            _lib.check(_lib.lib().stafb_peer_connect(self.h, b"".join(handles)), "stafb_peer_connect")
+            dist.barrier(group=group)
+        self._grads = []
+        for par in (0, 1):
+            ptr = _lib.lib().stafb_peer_grad(self.h, par)
+            self._grads.append(torch.as_tensor(_DevArray(ptr, self.n, model.dtype), device=model.device))
+
+    def grad(self, parity):
+        """Gradient buffer of this rank for steps of the given parity (a torch view of library memory)."""
+        return self._grads[parity & 1]
+
+    def allreduce_adam(self, model, parity, lr, beta1=0.9, beta2=0.999, eps=1e-7):
+        from . import _lib
+        from .model import _p
+        if not hasattr(model, "step_d"):
+            model.step_d = torch.zeros(2, dtype=torch.int32, device=model.device)
+        _lib.check(_lib.lib().stafb_allreduce_adam(model.ctx.h, self.h, model.ctx.stream(), int(parity) & 1,
+                                                   _p(model.theta), _p(model.adam_m), _p(model.adam_v), float(lr),
+                                                   float(beta1), float(beta2), float(eps), _p(model.step_d)),
+                   "stafb_allreduce_adam")
+
+    def status(self):
+        from . import _lib
+        return _lib.lib().stafb_peer_status(self.h)
+
+    def close(self):
+        """Collective: every rank must have finished its last step before any rank unmaps the buffers."""
+        from . import _lib
+        if self.h is not None:
+            torch.cuda.synchronize()
+            if self.world > 1:
+                dist.barrier(group=self.group)
+            self._grads = []
+            _lib.lib().stafb_peer_destroy(self.h)
+            self.h = None

@@ -136,6 +136,13 @@ class StafModel:
                                           _p(energy), _p(force)), "stafb_train_step")
         return energy, force
 
+    def use_grad(self, tensor):
+        """Makes the following evaluations accumulate their gradient into `tensor` (n_params elements on this
+        device, e.g. a PeerExchange buffer) instead of the model's own; returns the previous buffer."""
+        assert tensor.numel() == self.theta.numel() and tensor.dtype == self.dtype and tensor.is_cuda
+        old, self.grad = self.grad, tensor
+        return old
+
     def prefetch_rows(self, pos, box, slot):
         """Builds the neighbour rows of a batch (device tensors) into row set `slot` (0 or 1) on the current
         stream.  They depend on no trainable parameter, so this may run on a side stream while the previous

@@ -184,6 +184,14 @@ def run_ours(args):
     launches_per_step = model.launches() + 2  # + Adam and its step counter
     torch.cuda.synchronize()
 
+    # ---- several GPUs: gradient averaging + Adam as ONE kernel per rank over NVLink peer memory
+    # (stafb_allreduce_adam) instead of an NCCL all-reduce between two graphs; --allreduce nccl keeps the latter
+    px = None
+    if world > 1 and args.allreduce == "peer":
+        from alphanesgpu_b200.dist import PeerExchange
+        px = PeerExchange(model)
+    own_grad = model.grad
+
     # ---- CUDA graphs, two per distinct batch (pointers differ): the neighbour rows of a batch depend on its
     # positions only, so they are built on a second stream while the previous step is still running (and, on
     # several GPUs, during the gradient all-reduce and the Adam update); the rest of the step follows on the main
@@ -205,12 +213,16 @@ def run_ours(args):
             with torch.cuda.graph(gr, stream=side):
                 model.prefetch_rows(d_pos[i], d_box[i], i & 1)
             g1 = torch.cuda.CUDAGraph()
+            if px is not None:
+                model.use_grad(px.grad(i & 1))
             with torch.cuda.graph(g1, stream=side):
                 model.loss_and_grad_prefetched(i & 1, B, d_el[i], d_fl[i])
                 if world == 1:
                     model.adam_update_dev(lr)
+                elif px is not None:
+                    px.allreduce_adam(model, i & 1, lr)
             g2 = None
-            if world > 1:
+            if world > 1 and px is None:
                 g2 = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g2, stream=side):
                     model.adam_update_dev(lr, grad_scale=1.0 / world)
@@ -239,7 +251,7 @@ def run_ours(args):
             ready[s ^ 1].record(rows_stream)
         main.wait_event(ready[s])
         graphs[i][1].replay()
-        if world > 1:
+        if world > 1 and px is None:
             dist.all_reduce(model.grad)
             graphs[i][2].replay()
         main.wait_event(ready[s ^ 1])
@@ -301,10 +313,15 @@ def run_ours(args):
         with torch.cuda.stream(side):
             for k in range(n):
                 i = k % NB
+                if px is not None:
+                    model.use_grad(px.grad(k & 1))
                 model.loss_and_grad_host_begin(pos[i], box[i], el[i], fl[i], k & 1)
-                if world > 1:
-                    dist.all_reduce(model.grad)
-                model.adam_update_dev(lr, grad_scale=1.0 / world)
+                if px is not None:
+                    px.allreduce_adam(model, k & 1, lr)
+                else:
+                    if world > 1:
+                        dist.all_reduce(model.grad)
+                    model.adam_update_dev(lr, grad_scale=1.0 / world)
                 if k > 0:
                     losses = model.loss_and_grad_host_end((k - 1) & 1)
             return model.loss_and_grad_host_end((n - 1) & 1)
@@ -318,6 +335,7 @@ def run_ours(args):
     assert np.all(np.isfinite(e2e_losses))
     # the synchronous call (stage, run, wait, read back in one call) for comparison
     barrier()
+    model.use_grad(own_grad)
     t1 = time.perf_counter()
     for k in range(min(Ke, 100)):
         i = k % NB
@@ -472,7 +490,9 @@ def run_ours(args):
                        "l2": "flushed between steps (256 MiB write); per-step CUDA events summed",
                        "launch": "two CUDA graphs per step: neighbour rows of the NEXT batch on a second stream, "
                                  "the rest of the step on the main stream; each timed interval contains both"
-                                 + ("" if world == 1 else "; NCCL all-reduce between the step graph and the Adam graph"),
+                                 + ("" if world == 1 else ("; gradient averaging + Adam as one peer-memory kernel in the step graph"
+                                                            if px is not None else
+                                                            "; NCCL all-reduce between the step graph and the Adam graph")),
                        "vs_baseline_note": "published number is the reference on a V100 (README.md:42-45)"},
             "value_l2_warm": value_warm, "ms_per_step_min": float(per_step.min()),
             "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -483,6 +503,10 @@ def run_ours(args):
             "fp32_pipe": fp32_pipe, "fp64": fp64, "phase_ms": acc, "cpu_baseline": cpu,
         }
         print(json.dumps(line))
+    if px is not None:
+        if px.status() != 0:
+            raise SystemExit("peer exchange reported status %d" % px.status())
+        px.close()
     model.close()
     if world > 1:
         dist.destroy_process_group()
@@ -665,6 +689,8 @@ def main():
     ap.add_argument("--batch", type=int, default=4)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: gradient exchange by the fused peer-memory kernel or by an NCCL all-reduce")
     ap.add_argument("--workload", default="train", choices=["train", "md"],
                     help="train: BASELINE configs[1]/[3] (the headline metric); md: BASELINE configs[4]")
     args = ap.parse_args()

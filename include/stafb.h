@@ -32,6 +32,7 @@ extern "C" {
 #define STAFB_ERR_CUDA 6             /* a CUDA runtime call failed; see stafb_last_cuda_error() */
 #define STAFB_ERR_CAPACITY 7         /* nf or N larger than what the context was created for */
 #define STAFB_ERR_NONFINITE 8        /* non-finite energy */
+#define STAFB_ERR_PEER_TIMEOUT 9     /* stafb_allreduce_adam: a peer rank did not publish its gradient in time */
 
 #define STAFB_F32 0
 #define STAFB_F64 1
@@ -286,6 +287,30 @@ int stafb_adam_step(stafb_ctx* ctx, void* stream, void* theta_d, const void* gra
  * the call): the same launch sequence can be captured in a CUDA graph and replayed. */
 int stafb_adam_step_dev(stafb_ctx* ctx, void* stream, void* theta_d, const void* grad_d, void* m_d, void* v_d, int n,
                         double lr, double beta1, double beta2, double eps, int* step_d, double grad_scale);
+
+/* Data-parallel training on the GPUs of one node without a collective library between the backward pass and the
+ * optimiser: what hvd.DistributedOptimizer + Adam do in the reference (STAF/staf_train.py:484-487: average the
+ * gradients over the ranks, then update) as ONE kernel per rank and step over NVLink peer memory.
+ *   stafb_peer_create   allocates this rank's block: two gradient buffers (parity 0 / 1) and flag words;
+ *   stafb_peer_handle   writes the 64-byte CUDA IPC handle of that block (exchange them between the ranks by any
+ *                       host-side means: torch.distributed.all_gather_object, MPI ...);
+ *   stafb_peer_connect  maps the other ranks' blocks (handles[world][64], own entry ignored);
+ *   stafb_peer_grad     device pointer of a gradient buffer: pass it as grad_d to stafb_train_step*;
+ *   stafb_allreduce_adam  publishes "gradient complete" on every peer, waits for the peers (bounded: about two
+ *                       seconds, then STAFB_ERR_PEER_TIMEOUT is recorded and theta is left untouched), sums the
+ *                       buffers of `parity` in rank order - bit-identical on every rank -, divides by the world
+ *                       size and applies Adam (same formula and device step counter as stafb_adam_step_dev).
+ * Consecutive steps must alternate the parity; every rank must make the same calls in the same order.  Before
+ * stafb_peer_destroy all ranks must have finished their last step (a host-side barrier). */
+typedef struct stafb_peer stafb_peer;
+int stafb_peer_create(stafb_ctx* ctx, int rank, int world, int n_params, stafb_peer** out);
+int stafb_peer_handle(stafb_peer* p, void* handle64_out);
+int stafb_peer_connect(stafb_peer* p, const void* handles);
+void* stafb_peer_grad(stafb_peer* p, int parity);
+int stafb_peer_status(stafb_peer* p);
+void stafb_peer_destroy(stafb_peer* p);
+int stafb_allreduce_adam(stafb_ctx* ctx, stafb_peer* p, void* stream, int parity, void* theta_d, void* m_d, void* v_d,
+                         double lr, double beta1, double beta2, double eps, int* step_d);
 
 /* Same as stafb_train_step but positions, boxer and labels are HOST buffers and losses is a
  * host double[4]: copies in, runs, copies the losses back and synchronises the stream. */

@@ -1,0 +1,113 @@
+"""stafb_allreduce_adam: gradient averaging + Adam as one kernel over NVLink peer memory.
+
+world 1 (any GPU box): the fused kernel equals stafb_adam_step_dev on the same gradient.
+world 2 (needs two GPUs, skipped otherwise): two processes, one GPU each; every step of the fused exchange is
+compared with all_reduce(grad) + Adam on a twin model, and the replicas of theta must stay bit-identical
+across the ranks.  NVLS is switched off for the NCCL twin, as on any test that could lose a rank.
+"""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+from alphanesgpu_b200 import synth
+from conftest import CFG
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _setup(dev, seeds):
+    from alphanesgpu_b200.model import StafModel
+    pos, box, tipos = synth.water_frames("water96", seeds)
+    shape = synth.baseline_shape(tipos)
+    theta, emb = synth.init_params(shape, dtype=np.float32)
+    el, fl = synth.labels(len(seeds), shape.N)
+    mk = lambda: StafModel(shape, CFG, theta, emb, 2, dtype=torch.float32, device=dev)
+    d = [torch.as_tensor(a.astype(np.float32)).to(dev) for a in (pos, box, el, fl)]
+    return mk, d
+
+
+def test_world_one_equals_adam_step():
+    from alphanesgpu_b200.dist import PeerExchange
+    dev = torch.device("cuda:0")
+    mk, d = _setup(dev, [2000, 2001, 2002, 2003])
+    a, b = mk(), mk()
+    px = PeerExchange(a)
+    for k in range(4):
+        sl = slice(2 * (k & 1), 2 * (k & 1) + 2)
+        a.use_grad(px.grad(k & 1))
+        a.loss_and_grad(*(t[sl] for t in d))
+        b.grad.copy_(px.grad(k & 1))  # the same gradient for both updates (float atomics are not reproducible)
+        px.allreduce_adam(a, k & 1, 1e-3)
+        b.adam_update_dev(1e-3)
+    torch.cuda.synchronize()
+    assert px.status() == 0
+    # same gradient, same formula, two kernels: equal up to the compiler's choice of fused multiply-adds
+    assert float((a.theta - b.theta).abs().max()) <= 1e-7
+    assert int(a.step_d[0]) == 4
+    px.close()
+    a.close()
+    b.close()
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    from alphanesgpu_b200.dist import PeerExchange
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    mk, d = _setup(dev, [2100 + 4 * rank + i for i in range(4)])  # every rank its own frames
+    a, b = mk(), mk()
+    px = PeerExchange(a)
+    worst = 0.0
+    for k in range(6):
+        sl = slice(2 * (k & 1), 2 * (k & 1) + 2)
+        a.use_grad(px.grad(k & 1))
+        a.loss_and_grad(*(t[sl] for t in d))
+        b.grad.copy_(px.grad(k & 1))  # twin: the same local gradient, summed by NCCL, then the plain Adam kernel
+        px.allreduce_adam(a, k & 1, 1e-3)
+        dist.all_reduce(b.grad)
+        b.adam_update_dev(1e-3, grad_scale=1.0 / world)
+        torch.cuda.synchronize()
+        worst = max(worst, float((a.theta - b.theta).abs().max()))
+        b.theta.copy_(a.theta)
+    status = px.status()
+    mine = a.theta.clone()
+    other = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(other, mine)
+    same = all(torch.equal(o, mine) for o in other)
+    q.put((rank, status, worst, same))
+    px.close()
+    a.close()
+    b.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_world_two_matches_allreduce_then_adam():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=240) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, status, worst, same in got:
+        assert status == 0, (rank, status)
+        assert worst <= 1e-7, (rank, worst)  # same sums (a + b in either order), two kernels
+        assert same, rank  # rank-ordered sums: the replicas do not drift
