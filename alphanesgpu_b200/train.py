@@ -190,6 +190,15 @@ def train(cfg, out_dir=".", data=None, max_steps=None, log=print):
     rows, step, pending = [], 0, None
     displ = int(cfg["displ_freq"])
     t0 = time.time()
+    # Several ranks on one node: gradient averaging + Adam as one peer-memory kernel (grad_exchange: peer, the
+    # default); grad_exchange: allreduce keeps the NCCL all-reduce followed by the Adam kernel (needed across nodes).
+    px = None
+    if world > 1 and str(cfg.get("grad_exchange", "peer")).lower() == "peer":
+        px = dp.PeerExchange(model)
+    # a stream of its own: the library replays each step as CUDA graphs, which the legacy default stream cannot capture
+    stream = torch.cuda.Stream(device=dev)
+    stream.wait_stream(torch.cuda.current_stream(dev))
+    torch.cuda.set_stream(stream)
 
     def collect(p):
         st, slot, lr = p
@@ -211,9 +220,14 @@ def train(cfg, out_dir=".", data=None, max_steps=None, log=print):
                 sl = slice(k * bs, (k + 1) * bs)
                 lr = lr_of(step)
                 step += 1
+                if px is not None:
+                    model.use_grad(px.grad(step & 1))
                 model.loss_and_grad_host_begin(pos[sl].reshape(bs, 3 * N), box[sl], en[sl], fo[sl], step & 1)
-                dp.allreduce_sum_(model.grad)
-                model.adam_update_dev(lr, eps=eps, grad_scale=1.0 / world)
+                if px is not None:
+                    px.allreduce_adam(model, step & 1, lr, eps=eps)
+                else:
+                    dp.allreduce_sum_(model.grad)
+                    model.adam_update_dev(lr, eps=eps, grad_scale=1.0 / world)
                 if pending is not None:
                     collect(pending)
                 pending = (step, step & 1, lr)
@@ -233,6 +247,13 @@ def train(cfg, out_dir=".", data=None, max_steps=None, log=print):
     if chief:
         lcurve.close()
         lrfile.close()
+    stream.synchronize()
+    torch.cuda.set_stream(torch.cuda.default_stream(dev))
+    if px is not None:
+        st = px.status()
+        px.close()
+        if st != 0:
+            raise RuntimeError("gradient exchange: status %d (a peer rank did not arrive in time)" % st)
     result = dict(rows=rows, theta=model.theta.detach().cpu().numpy().copy(), shape=shape, geo=geo)
     model.close()
     if own_pg:
