@@ -323,21 +323,16 @@ __global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::val
     ids[k] = id;
     tj[k] = (unsigned char)(in.tmap ? in.tmap[id] : md.type_of(id));
   }
-  // the neighbour rows above are at least two kernels old; netderiv / dL/dF / the zeroed outputs below are not
-  chain_wait();
   // angular parameters of every (class, channel), fetched while the neighbour row is still in flight
   for (int idx = tid; idx < md.ncls * Fa; idx += NT) {
-    const int c = idx % Fa;
     const T ee = e3[idx];
     const T* al = a3 + idx * 3;
     T4 pa;
     pa.x = al[0]; pa.y = al[1]; pa.z = al[2]; pa.w = al[2] * SC;
     T2 pb;
     pb.x = T(0); pb.y = T(0);
-    if (IS_AF) pb.x = T(0.5) * ee;
-    if (MODE == MODE_FORCE) pb.x = T(0.25) * chrow[Fr + c] * ee;
-    if (MODE == MODE_FGRAD) { pb.x = T(0.5) * ee; pb.y = chrow[Fr + c]; }
-    if (MODE == MODE_AFGRAD) pb.x = T(0.5) * chrow[Fr + c] * ee;
+    // the factor that comes from the preceding kernel (netderiv, dL/dAF) is applied after chain_wait() below
+    pb.x = (MODE == MODE_FORCE) ? T(0.25) * ee : T(0.5) * ee;
     pall[idx] = pa;
     pball[idx] = pb;
     eflag[idx] = ee != T(0);
@@ -366,6 +361,17 @@ __global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::val
         }
         if (lane == 0) { cnts[t2] = ca; cnts[STAFB_MAX_TYPES + t2] = c2; }
       }
+    }
+  }
+  // Everything above read only what is at least two kernels old (neighbour rows, theta, emb); netderiv, dL/dF
+  // and the zeroed outputs below belong to the preceding kernels.
+  chain_wait();
+  if (!IS_AF) {
+    for (int idx = tid; idx < md.ncls * Fa; idx += NT) {  // same thread as the fill above
+      const T cin = chrow[Fr + idx % Fa];
+      T2 pb = pball[idx];
+      if (MODE == MODE_FGRAD) pb.y = cin; else pb.x *= cin;
+      pball[idx] = pb;
     }
   }
   T fix = T(0), fiy = T(0), fiz = T(0);  // FORCE: force on the central atom
@@ -871,9 +877,13 @@ __global__ void __launch_bounds__(256)
            T* __restrict__ fbar, T* __restrict__ grad, double* __restrict__ losses, int* status,
            int* status_main, const double* __restrict__ vacc, T* __restrict__ virial_out, double* __restrict__ mirror) {
   __shared__ double red[9];
-  chain_wait();
   const int N = md.N;
   const int blk = blockIdx.x;
+  // Only the force blocks (and the virial) need the force sweep that precedes this kernel; the frame energies
+  // come from the MLP kernel two launches back and the bound term from theta, so those blocks run under the
+  // sweep's tail and meet the chain only at their end.
+  const bool needs_pred = (blk >= nf && blk < nf + fb) || (blk < nf && virial_out);
+  if (needs_pred) chain_wait();
   if (blk < nf) {
     if (virial_out && threadIdx.x < 9) virial_out[blk * 9 + threadIdx.x] = (T)vacc[blk * 9 + threadIdx.x];
     if (threadIdx.x == 0) {
@@ -913,6 +923,7 @@ __global__ void __launch_bounds__(256)
     s = block_sum<double, 8>(s, red);
     if (threadIdx.x == 0) atomicAdd(losses + 2, s);
   }
+  if (!needs_pred) chain_wait();
   if (train && threadIdx.x == 0) {
     __threadfence();
     const unsigned done = atomicAdd(reinterpret_cast<unsigned*>(losses + 4), 1u);
