@@ -189,7 +189,15 @@ def run_ours(args):
     px = None
     if world > 1 and args.allreduce == "peer":
         from alphanesgpu_b200.dist import PeerExchange
-        px = PeerExchange(model)
+        ok = torch.ones(1, device=dev)
+        try:
+            px = PeerExchange(model)
+        except Exception as exc:  # e.g. no peer access between these GPUs: every rank falls back to NCCL
+            sys.stderr.write("rank %d: peer exchange unavailable (%s)\n" % (rank, exc))
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok) == 0.0:
+            px = None
     own_grad = model.grad
 
     # ---- CUDA graphs, two per distinct batch (pointers differ): the neighbour rows of a batch depend on its
@@ -198,7 +206,6 @@ def run_ours(args):
     # stream.  The NCCL all-reduce stays between two graphs (capturing it into the graph made a 2-rank run hang
     # on this pool, so it is not attempted).
     assert NB % 2 == 0  # batch i always uses row set i & 1
-    graphs = []
     main = torch.cuda.current_stream(dev)
     side = torch.cuda.Stream(device=dev)
     rows_stream = torch.cuda.Stream(device=dev)
@@ -206,29 +213,34 @@ def run_ours(args):
         model.prefetch_rows(d_pos[i], d_box[i], i)
         model.loss_and_grad_prefetched(i, B, d_el[i], d_fl[i])
     torch.cuda.synchronize()
-    side.wait_stream(main)
-    with torch.cuda.stream(side):
-        for i in range(NB):
-            gr = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gr, stream=side):
-                model.prefetch_rows(d_pos[i], d_box[i], i & 1)
-            g1 = torch.cuda.CUDAGraph()
-            if px is not None:
-                model.use_grad(px.grad(i & 1))
-            with torch.cuda.graph(g1, stream=side):
-                model.loss_and_grad_prefetched(i & 1, B, d_el[i], d_fl[i])
-                if world == 1:
-                    model.adam_update_dev(lr)
-                elif px is not None:
-                    px.allreduce_adam(model, i & 1, lr)
-            g2 = None
-            if world > 1 and px is None:
-                g2 = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g2, stream=side):
-                    model.adam_update_dev(lr, grad_scale=1.0 / world)
-            graphs.append((gr, g1, g2))
-    main.wait_stream(side)
-    torch.cuda.synchronize()
+
+    def build_graphs(px):
+        graphs = []
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            for i in range(NB):
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr, stream=side):
+                    model.prefetch_rows(d_pos[i], d_box[i], i & 1)
+                g1 = torch.cuda.CUDAGraph()
+                model.use_grad(px.grad(i & 1) if px is not None else own_grad)
+                with torch.cuda.graph(g1, stream=side):
+                    model.loss_and_grad_prefetched(i & 1, B, d_el[i], d_fl[i])
+                    if world == 1:
+                        model.adam_update_dev(lr)
+                    elif px is not None:
+                        px.allreduce_adam(model, i & 1, lr)
+                g2 = None
+                if world > 1 and px is None:
+                    g2 = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g2, stream=side):
+                        model.adam_update_dev(lr, grad_scale=1.0 / world)
+                graphs.append((gr, g1, g2))
+        main.wait_stream(side)
+        torch.cuda.synchronize()
+        return graphs
+
+    graphs = build_graphs(px)
 
     ready = [torch.cuda.Event(), torch.cuda.Event()]
     go = torch.cuda.Event()
@@ -261,6 +273,21 @@ def run_ours(args):
         step_graph(w)
         flush.zero_()
     torch.cuda.synchronize()
+    if px is not None:
+        # a peer that did not arrive within the kernel's bound leaves a status; then every rank goes back to NCCL
+        bad = torch.tensor([float(px.status())], device=dev)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if float(bad) != 0.0:
+            sys.stderr.write("rank %d: peer exchange status %d, falling back to NCCL\n" % (rank, int(bad)))
+            px.close()
+            px = None
+            model.use_grad(own_grad)
+            dist.broadcast(model.theta, 0)
+            graphs = build_graphs(None)
+            for w in range(W):
+                step_graph(w)
+                flush.zero_()
+            torch.cuda.synchronize()
 
     def barrier():
         if world > 1:

@@ -111,3 +111,53 @@ def test_world_two_matches_allreduce_then_adam():
         assert status == 0, (rank, status)
         assert worst <= 1e-7, (rank, worst)  # same sums (a + b in either order), two kernels
         assert same, rank  # rank-ordered sums: the replicas do not drift
+
+
+def _late_peer_worker(rank, world, port, q):
+    """The wait bound is set to zero and rank 1 arrives late: rank 0's kernel must give up, record the status
+    and leave theta untouched, and the context must stay usable (no trap, no hang)."""
+    import time
+    import torch.distributed as dist
+    from alphanesgpu_b200.dist import PeerExchange
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", STAFB_PEER_WAIT_MS="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    mk, d = _setup(dev, [2200 + 4 * rank + i for i in range(4)])
+    a = mk()
+    px = PeerExchange(a)
+    before = a.theta.clone()
+    a.use_grad(px.grad(0))
+    a.loss_and_grad(*(t[0:2] for t in d))
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank == 1:
+        time.sleep(0.5)  # rank 0 launches first and finds no flag
+    px.allreduce_adam(a, 0, 1e-3)
+    torch.cuda.synchronize()
+    status = px.status()
+    untouched = bool(torch.equal(a.theta, before))
+    e, f = a.energy_force(d[0][0:2], d[1][0:2])  # the context still works
+    usable = bool(torch.isfinite(e).all())
+    q.put((rank, status, untouched, usable))
+    px.close()
+    a.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_late_peer_gives_a_status_not_a_hang():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_late_peer_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict((r[0], r[1:]) for r in (q.get(timeout=240) for _ in range(2)))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    status, untouched, usable = got[0]
+    assert status == 9 and untouched and usable  # STAFB_ERR_PEER_TIMEOUT on the rank that waited
+    assert got[1][2]
