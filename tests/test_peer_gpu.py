@@ -53,7 +53,8 @@ def test_world_one_equals_adam_step():
     torch.cuda.synchronize()
     assert px.status() == 0
     # same gradient, same formula, two kernels: equal up to the compiler's choice of fused multiply-adds
-    assert float((a.theta - b.theta).abs().max()) <= 1e-7
+    # (an ulp or two of parameters of magnitude ~1)
+    assert float((a.theta - b.theta).abs().max()) <= 5e-7
     assert int(a.step_d[0]) == 4
     px.close()
     a.close()
@@ -109,7 +110,7 @@ def test_world_two_matches_allreduce_then_adam():
         assert p.exitcode == 0
     for rank, status, worst, same in got:
         assert status == 0, (rank, status)
-        assert worst <= 1e-7, (rank, worst)  # same sums (a + b in either order), two kernels
+        assert worst <= 5e-7, (rank, worst)  # same sums (a + b in either order), two kernels
         assert same, rank  # rank-ordered sums: the replicas do not drift
 
 
