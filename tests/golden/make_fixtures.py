@@ -1,6 +1,6 @@
-"""Generates tests/golden/* from the reference tree (run once where /root/reference exists).
+"""Generates tests/golden/* from a checkout of the reference (run once, where that checkout exists).
 
-  python tests/golden/make_fixtures.py [/root/reference]
+  python tests/golden/make_fixtures.py <path of the reference tree>
 
 What it writes:
   ref_frame0/            the reference's real 768-atom water frame
@@ -44,7 +44,9 @@ def write_mlp_bin(path, mu, layers, dtype):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/make_fixtures.py <path of the reference tree>")
+    ref = sys.argv[1]
     oracle.build()
     assert oracle.ref_available(), "oracle/_ref not built"
     out = os.path.join(HERE, "ref_frame0")
