@@ -63,6 +63,8 @@ _SIGS = {
     "stafb_peer_handle": [_vp, _vp],
     "stafb_peer_connect": [_vp, _vp],
     "stafb_peer_status": [_vp],
+    "stafb_peer_connect_local": [_vp, _vp],
+    "stafb_peer_preset_flags": [_vp, _vp, _i, _i],
     "stafb_peer_grad": [_vp, _i],
     "stafb_peer_destroy": [_vp],
     "stafb_allreduce_adam": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _d, _d, _d, _d, _vp],

@@ -165,6 +165,32 @@ extern "C" int stafb_peer_connect(stafb_peer* p, const void* handles) {
   return STAFB_OK;
 }
 
+// Ranks that live in ONE process (one thread or stream per GPU, or several emulated ranks on one GPU in a test)
+// connect through their handles directly, without IPC.
+extern "C" int stafb_peer_connect_local(stafb_peer* p, stafb_peer* const* all) {
+  if (!p || !all) return STAFB_ERR_INVALID;
+  for (int r = 0; r < p->world; r++) {
+    if (r == p->rank) continue;
+    if (!all[r] || all[r]->world != p->world || all[r]->rank != r || all[r]->n != p->n) return STAFB_ERR_INVALID;
+    p->peer[r] = all[r]->block;
+  }
+  p->connected = 2;  // nothing to unmap on destroy
+  return STAFB_OK;
+}
+
+// Writes `value` into every flag word of this rank's block for `parity`, as if all peers had published step
+// `value` already.  For emulating several ranks on one GPU, where their kernels run one after the other and
+// must therefore never wait for each other.
+extern "C" int stafb_peer_preset_flags(stafb_peer* p, void* stream, int parity, int value) {
+  if (!p || parity < 0 || parity > 1) return STAFB_ERR_INVALID;
+  int host[PEER_MAX];
+  for (int r = 0; r < PEER_MAX; r++) host[r] = value;
+  int* flags = reinterpret_cast<int*>(p->block + 2 * p->grad_bytes) + parity * PEER_MAX;
+  STAFB_CUDA_OK(cudaMemcpyAsync(flags, host, sizeof(host), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  STAFB_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+  return STAFB_OK;
+}
+
 extern "C" void* stafb_peer_grad(stafb_peer* p, int parity) {
   if (!p || parity < 0 || parity > 1) return nullptr;
   return p->block + (size_t)parity * p->grad_bytes;
@@ -179,7 +205,7 @@ extern "C" int stafb_peer_status(stafb_peer* p) {
 
 extern "C" void stafb_peer_destroy(stafb_peer* p) {
   if (!p) return;
-  for (int r = 0; r < p->world; r++)
+  for (int r = 0; r < p->world && p->connected == 1; r++)
     if (r != p->rank && p->peer[r]) cudaIpcCloseMemHandle(p->peer[r]);
   cudaFree(p->block);
   cudaFree(p->status_d);

@@ -306,6 +306,11 @@ typedef struct stafb_peer stafb_peer;
 int stafb_peer_create(stafb_ctx* ctx, int rank, int world, int n_params, stafb_peer** out);
 int stafb_peer_handle(stafb_peer* p, void* handle64_out);
 int stafb_peer_connect(stafb_peer* p, const void* handles);
+/* ranks inside one process connect through their handles (all[world], own entry ignored), without IPC */
+int stafb_peer_connect_local(stafb_peer* p, stafb_peer* const* all);
+/* marks every peer as having published step `value` for `parity`: for emulating several ranks on ONE GPU, where
+ * the ranks' kernels run one after the other and must never wait for each other */
+int stafb_peer_preset_flags(stafb_peer* p, void* stream, int parity, int value);
 void* stafb_peer_grad(stafb_peer* p, int parity);
 int stafb_peer_status(stafb_peer* p);
 void stafb_peer_destroy(stafb_peer* p);

@@ -162,3 +162,57 @@ def test_late_peer_gives_a_status_not_a_hang():
     status, untouched, usable = got[0]
     assert status == 9 and untouched and usable  # STAFB_ERR_PEER_TIMEOUT on the rank that waited
     assert got[1][2]
+
+
+def test_eight_emulated_ranks_on_one_gpu():
+    """The kernel's indexing for a full node: eight ranks emulated on one GPU.  Their kernels run one after the
+    other, so every flag is preset (no kernel may wait for another on the same GPU); what is checked is that
+    each rank reads the right eight buffers, sums them in rank order and that all replicas end up bit-identical."""
+    import ctypes as C
+    from alphanesgpu_b200 import _lib
+    from alphanesgpu_b200.dist import _DevArray
+    from alphanesgpu_b200.ops import Context
+    L = _lib.lib()
+    dev = torch.device("cuda:0")
+    ctx = Context(CFG["Rc"], CFG["nr"], CFG["na"], 96, CFG["Rs"], CFG["Ra"], 1, torch.float32, dev)
+    W, n, lr = 8, 3001, 1e-3
+    hs = (C.c_void_p * W)()
+    for r in range(W):
+        h = C.c_void_p()
+        _lib.check(L.stafb_peer_create(ctx.h, r, W, n, C.byref(h)), "stafb_peer_create")
+        hs[r] = h
+    gen = torch.Generator(device="cpu").manual_seed(5)
+    grads = [torch.randn(n, generator=gen).to(dev) for _ in range(W)]
+    theta0 = torch.randn(n, generator=gen).to(dev)
+    state = []
+    stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    for r in range(W):
+        _lib.check(L.stafb_peer_connect_local(hs[r], hs), "stafb_peer_connect_local")
+        for par in (0, 1):
+            g = torch.as_tensor(_DevArray(L.stafb_peer_grad(hs[r], par), n, torch.float32), device=dev)
+            g.copy_(grads[r] if par == 0 else -grads[r])
+        _lib.check(L.stafb_peer_preset_flags(hs[r], stream, 0, 1), "stafb_peer_preset_flags")
+        state.append(dict(theta=theta0.clone(), m=torch.zeros(n, device=dev), v=torch.zeros(n, device=dev),
+                          step=torch.zeros(2, dtype=torch.int32, device=dev)))
+    torch.cuda.synchronize()
+    p = lambda t: C.c_void_p(t.data_ptr())
+    for r in range(W):
+        s = state[r]
+        _lib.check(L.stafb_allreduce_adam(ctx.h, hs[r], stream, 0, p(s["theta"]), p(s["m"]), p(s["v"]), lr, 0.9, 0.999,
+                                          1e-7, p(s["step"])), "stafb_allreduce_adam")
+    torch.cuda.synchronize()
+    g = torch.zeros(n, device=dev)
+    for r in range(W):
+        g = g + grads[r]  # rank order, float32
+    g = g / W
+    m, v = 0.1 * g, 0.001 * g * g
+    lr_t = lr * np.sqrt(1 - 0.999) / (1 - 0.9)
+    want = theta0 - lr_t * m / (torch.sqrt(v) + 1e-7)
+    for r in range(W):
+        assert L.stafb_peer_status(hs[r]) == 0
+        assert int(state[r]["step"][0]) == 1
+        assert torch.equal(state[r]["theta"], state[0]["theta"]), r
+    assert torch.allclose(state[0]["theta"], want, rtol=2e-6, atol=2e-7)
+    for r in range(W):
+        L.stafb_peer_destroy(hs[r])
+    ctx.close()
