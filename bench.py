@@ -523,7 +523,8 @@ def run_ours(args):
                        "vs_baseline_note": "published number is the reference on a V100 (README.md:42-45)"},
             "value_l2_warm": value_warm, "ms_per_step_min": float(per_step.min()),
             "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": Ke, "path": "stafb_train_step_host_begin/_end (two pinned slots) + stafb_adam_step_dev",
+                    "steps": Ke, "path": "stafb_train_step_host_begin/_end (two pinned slots) + "
+                            + ("stafb_allreduce_adam" if px is not None else "stafb_adam_step_dev"),
                     "synchronous_call_value": world * B / e2e_sync_s},
             "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step,
             "clocks": clocks, "roofline": roofline, "roofline_operator_boundary": roofline_ops,
