@@ -51,6 +51,7 @@ _SIGS = {
     "stafb_model_n_params": [_vp],
     "stafb_model_n_emb": [_vp],
     "stafb_model_offsets": [_vp, _i, _vp],
+    "stafb_model_mlp_config": [_vp, _vp],
     "stafb_energy_force": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp],
     "stafb_energy_force_virial": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp],
     "stafb_energy_force_domain": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -66,6 +67,7 @@ _SIGS = {
     "stafb_peer_connect_local": [_vp, _vp],
     "stafb_peer_preset_flags": [_vp, _vp, _i, _i],
     "stafb_peer_grad": [_vp, _i],
+    "stafb_peer_set_wait_ms": [_vp, C.c_longlong],
     "stafb_peer_destroy": [_vp],
     "stafb_allreduce_adam": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _d, _d, _d, _d, _vp],
     "stafb_train_step_host": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _i, _vp, _vp],
@@ -96,7 +98,7 @@ def lib():
                 continue
             fn.argtypes = sig
             fn.restype = None if name in ("stafb_destroy", "stafb_model_destroy", "stafb_core_coefficients",
-                                          "stafb_model_offsets", "stafb_peer_destroy") else _i
+                                          "stafb_model_offsets", "stafb_peer_destroy", "stafb_model_mlp_config") else _i
             if name == "stafb_peer_grad":
                 fn.restype = C.c_void_p
         _LIB = L

@@ -880,21 +880,29 @@ __global__ void __launch_bounds__(256)
   const int N = md.N;
   const int blk = blockIdx.x;
   // Only the force blocks (and the virial) need the force sweep that precedes this kernel; the frame energies
-  // come from the MLP kernel two launches back and the bound term from theta, so those blocks run under the
-  // sweep's tail and meet the chain only at their end.
+  // come from the MLP kernel two launches back and the bound term from theta, so those blocks do their loads and
+  // arithmetic under the sweep's tail and wait for it only before their first global write.
   const bool needs_pred = (blk >= nf && blk < nf + fb) || (blk < nf && virial_out);
   if (needs_pred) chain_wait();
   if (blk < nf) {
-    if (virial_out && threadIdx.x < 9) virial_out[blk * 9 + threadIdx.x] = (T)vacc[blk * 9 + threadIdx.x];
+    // loads and arithmetic first, every global write after the wait below
+    double Eb = 0.0;
+    T le = T(0), de = T(0);
     if (threadIdx.x == 0) {
       const double s = losses[8 + blk];  // sum of the frame's atomic energies, accumulated by the MLP kernel
-      const double Eb = per_atom ? 0.5 * s / N : 0.5 * s;
+      Eb = per_atom ? 0.5 * s / N : 0.5 * s;
+      if (train) {
+        const T e = (T)Eb - e_label[blk];
+        le = loss_kind == 0 ? huber(e) : e * e;
+        de = loss_kind == 0 ? huber_d(e) : T(2) * e;
+      }
+    }
+    if (!needs_pred) chain_wait();
+    if (virial_out && threadIdx.x < 9) virial_out[blk * 9 + threadIdx.x] = (T)vacc[blk * 9 + threadIdx.x];
+    if (threadIdx.x == 0) {
       if (!isfinite(Eb)) set_status(status, STAFB_ERR_NONFINITE);
       if (energy) energy[blk] = (T)Eb;
       if (train) {
-        const T e = (T)Eb - e_label[blk];
-        const T le = loss_kind == 0 ? huber(e) : e * e;
-        const T de = loss_kind == 0 ? huber_d(e) : T(2) * e;
         atomicAdd(losses + 1, (double)le / nf);
         ebar[blk] = pe * de / T(nf) * T(0.5) / (per_atom ? T(N) : T(1));
       }
@@ -911,19 +919,26 @@ __global__ void __launch_bounds__(256)
     s = block_sum<double, 8>(s, red);
     if (threadIdx.x == 0) atomicAdd(losses + 3, s / (double)n);
   } else {
+    // bound term: the sum under the predecessor's tail, the gradient contributions after the wait
     double s = 0.0;
     for (int t = 0; t < md.nt; t++) {
       const int n2 = md.nt * md.Fr[t], n3 = md.C * 3 * md.Fa[t];
       for (int q = threadIdx.x; q < n2 + n3; q += blockDim.x) {
-        const int idx = q < n2 ? md.off_a2[t] + q : md.off_a3[t] + (q - n2);
-        const T x = theta[idx];
-        if (x > bound) { s += (double)x; atomicAdd(grad + idx, pb); }
+        const T x = theta[q < n2 ? md.off_a2[t] + q : md.off_a3[t] + (q - n2)];
+        if (x > bound) s += (double)x;
       }
     }
     s = block_sum<double, 8>(s, red);
+    chain_wait();
+    for (int t = 0; t < md.nt; t++) {
+      const int n2 = md.nt * md.Fr[t], n3 = md.C * 3 * md.Fa[t];
+      for (int q = threadIdx.x; q < n2 + n3; q += blockDim.x) {
+        const int idx = q < n2 ? md.off_a2[t] + q : md.off_a3[t] + (q - n2);
+        if (theta[idx] > bound) atomicAdd(grad + idx, pb);
+      }
+    }
     if (threadIdx.x == 0) atomicAdd(losses + 2, s);
   }
-  if (!needs_pred) chain_wait();
   if (train && threadIdx.x == 0) {
     __threadfence();
     const unsigned done = atomicAdd(reinterpret_cast<unsigned*>(losses + 4), 1u);
@@ -1213,9 +1228,23 @@ extern "C" int stafb_model_set_counts(stafb_model* m, const int* tipos) {
 
 extern "C" int stafb_model_n_params(const stafb_model* m) { return m ? m->n_params : -1; }
 extern "C" int stafb_model_n_emb(const stafb_model* m) { return m ? m->n_emb : -1; }
+extern "C" void stafb_model_mlp_config(const stafb_model* m, int out4[4]) {
+  out4[0] = m->stage; out4[1] = m->apt; out4[2] = (int)m->mlp_fwd_smem; out4[3] = (int)m->mlp_bwd_smem;
+}
 extern "C" void stafb_model_offsets(const stafb_model* m, int t, int out6[6]) {
   out6[0] = m->md.off_a2[t]; out6[1] = m->md.off_a3[t]; out6[2] = m->md.off_mu[t]; out6[3] = m->md.off_w[t];
   out6[4] = m->md.off_emb[t]; out6[5] = m->blk_size[t];
+}
+
+// cudaFuncSetAttribute applies to the device that is current when it is called, and one process may drive
+// several GPUs (staf_load honours StafOptions.device_id; stafb_peer_connect_local exists for that use): the
+// "already opted in" notes of the launchers below are therefore kept per device, as the reference keeps its
+// per-device context map (STAF/src/descriptor_builder/reforce.cc:143-158).
+constexpr int MAX_DEVICES = 64;
+static inline int device_slot() {
+  int d = 0;
+  cudaGetDevice(&d);
+  return (d >= 0 && d < MAX_DEVICES) ? d : 0;
 }
 
 template <class T, int MODE, int SW_WPA = SweepWpa<MODE>::value>
@@ -1229,14 +1258,15 @@ static int launch_sweep(stafb_model* m, cudaStream_t s, int nf, const SweepIn<T>
                                   d.nt * d.Frmax > 0 ? d.nt * d.Frmax : 1, d.ncls * d.Famax > 0 ? d.ncls * d.Famax : 1);
   const size_t sm = (size_t)L.total;
   if (sm > m->smem_limit) return STAFB_ERR_CAPACITY;
-  static bool attr[2][5] = {{false}};  // per instantiation (T, MODE, SW_WPA)
-  if (sm > 48 * 1024 && !attr[sizeof(T) == 8][MODE]) {
+  static bool attr_dev[MAX_DEVICES] = {false};  // per instantiation (T, MODE, SW_WPA) and device
+  bool& attr_done = attr_dev[device_slot()];
+  if (sm > 48 * 1024 && !attr_done) {
     STAFB_CUDA_OK(cudaFuncSetAttribute(k_sweep<T, MODE, SW_WPA, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)m->smem_limit));
     if (MODE == MODE_FORCE)
       STAFB_CUDA_OK(cudaFuncSetAttribute(k_sweep<T, MODE, SW_WPA, MODE == MODE_FORCE>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)m->smem_limit));
-    attr[sizeof(T) == 8][MODE] = true;
+    attr_done = true;
   }
   const int blocks = nf * d.N;
   if (MODE == MODE_FORCE && vir)
@@ -1252,7 +1282,8 @@ static int launch_sweep(stafb_model* m, cudaStream_t s, int nf, const SweepIn<T>
 template <class T, int APT>
 static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, T* acts, T* e_atom,
                           T* nd) {
-  static size_t attr = 0;  // largest dynamic shared-memory size this instantiation was opted in for
+  static size_t attr_dev[MAX_DEVICES] = {0};  // largest dynamic shared-memory size opted in for, per device
+  size_t& attr = attr_dev[device_slot()];
   if (m->mlp_fwd_smem > 48 * 1024 && m->mlp_fwd_smem > attr) {
     STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_fwd<T, APT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)m->mlp_fwd_smem));
@@ -1268,7 +1299,8 @@ static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta
 template <class T, int APT>
 static int launch_mlp_bwd(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, const T* acts,
                           const T* ebar, const T* u, T* gaf, T* grad) {
-  static size_t attr = 0;
+  static size_t attr_dev[MAX_DEVICES] = {0};
+  size_t& attr = attr_dev[device_slot()];
   const T* vrow = (const T*)m->vrow;
   if (m->mlp_bwd_smem > 48 * 1024 && m->mlp_bwd_smem > attr) {
     STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_bwd<T, APT>, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -765,7 +765,8 @@ extern "C" int stafb_compute_descriptors_light_noalloc(int dtype, double radial_
   STAFB_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return STAFB_ERR_CAPACITY;
   if (!g_noalloc_addr[dev]) {
-    // first call on this device (do it before any stream capture): resolve the device address of the array
+    // first call on this device (do it before any stream capture): resolve the device address of the array.
+    // Two threads making their first call together both store the same value; no lock is needed for that.
     void* p = nullptr;
     STAFB_CUDA_OK(cudaGetSymbolAddress(&p, g_noalloc_scratch));
     g_noalloc_addr[dev] = p;

@@ -673,10 +673,13 @@ int op_grad_force_ang(stafb_ctx* c, cudaStream_t s, const T* pg, const T* nd, co
   const int n = nf * Nl;
   if (n <= 0) return STAFB_OK;
   size_t sm = sizeof(T) * ((size_t)c->nr * 5 + c->na) + sizeof(int) * (size_t)c->nr + (size_t)c->na * 2;
-  static bool attr_done[2] = {false, false};
-  if (sm > 48 * 1024 && !attr_done[sizeof(T) == 8]) {
+  static bool attr_done[64] = {false};  // per instantiation and device: the attribute belongs to the current device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  bool& done = attr_done[(dev >= 0 && dev < 64) ? dev : 0];
+  if (sm > 48 * 1024 && !done) {
     STAFB_CUDA_OK(cudaFuncSetAttribute(k_grad_force_ang<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr_done[sizeof(T) == 8] = true;
+    done = true;
   }
   k_grad_force_ang<T><<<n, OPS_THREADS, sm, s>>>(Nl, N, c->nr, c->na, Fa, ncls_of(nt), pg, nd, ds3, ang, d3s, d3, im2,
                                                  a3, e3, tm, tipos, at, ntr, gradnet, ga, va);

@@ -6,9 +6,13 @@
 //   1. publishes "my gradient of this step is complete" in a flag word on every peer (a system-scope store
 //      over NVLink after a system fence),
 //   2. waits until all peers have published theirs (polling flag words in its OWN memory; bounded in time -
-//      when the bound is hit it records STAFB_ERR_PEER_TIMEOUT, leaves theta untouched and returns),
-//   3. reads the peers' gradients with plain peer loads, sums them in rank order (so that every rank computes
-//      bit-identical sums and the replicas of theta never drift), divides by the world size and applies Adam.
+//      when the bound is hit the launch as a whole records STAFB_ERR_PEER_TIMEOUT, leaves theta, the moments and
+//      the step counter untouched and returns: the decision is taken once per launch, see the kernel),
+//   3. reads the peers' gradients with plain peer loads, all in flight together, sums them in rank order (so
+//      that every rank computes bit-identical sums and the replicas of theta never drift), divides by the world
+//      size and applies Adam.
+// A rank that gave up and a late rank that then went ahead hold different parameters from that step on: the
+// host has to notice the status and re-broadcast (alphanesgpu_b200/train.py does, at every collection point).
 // Two gradient buffers alternate from step to step: a rank that is already accumulating step k+1 does not
 // touch what a slower peer still reads for step k, and no rank can run two steps ahead of another because step
 // k+1 cannot complete without every peer's flag of step k+1.  There is no multicast object, no collective
@@ -48,11 +52,16 @@ __device__ __forceinline__ double ld_peer(const double* p) {
   return v;
 }
 
+// One decision per launch.  Every block's thread 0 polls the peers' flags (bounded), then proposes its finding
+// (all flags seen / gave up) for this step in a verdict word of this rank's own memory with a compare-and-swap;
+// the first proposal stands and every block - whenever it runs - adopts it.  So either all blocks apply the
+// update or none does, also when a peer's flag lands just as the bound runs out, and the step counter advances
+// only with an applied update.  verdict = 2*step + ok; steps only grow, so the word never needs clearing.
 template <class T>
 __global__ void __launch_bounds__(256)
     k_allreduce_adam(PeerView pv, int n, T* __restrict__ theta, T* __restrict__ m, T* __restrict__ v, double lr,
                      double b1, double b2, T eps, int* __restrict__ step_d /*[2]: step, blocks done*/,
-                     long long wait_cycles, int* __restrict__ status) {
+                     long long wait_cycles, int* __restrict__ status /*[2]: status, verdict*/) {
   __shared__ int ok_s;
   chain_wait();  // the gradient is the output of the kernel before this one
   const int step = *reinterpret_cast<volatile int*>(step_d) + 1;  // the update being applied; equal on all ranks
@@ -62,27 +71,48 @@ __global__ void __launch_bounds__(256)
       for (int r = 0; r < pv.world; r++)
         if (r != pv.rank) st_sys(pv.flag_out[r], step);
     }
-    int ok = 1;
+    int seen = 1;
     const long long t0 = clock64();
-    for (int r = 0; r < pv.world && ok; r++) {
+    for (int r = 0; r < pv.world && seen; r++) {
       if (r == pv.rank) continue;
       while (ld_sys(pv.flag_in + r) < step) {  // flags only grow: a peer is never more than one step ahead
-        if (clock64() - t0 > wait_cycles) { ok = 0; break; }
-        __nanosleep(200);
+        const long long waited = clock64() - t0;
+        if (waited > wait_cycles) { seen = 0; break; }
+        if (waited > 20000) __nanosleep(100);  // spin for the first ~10 us, then back off
       }
     }
+    int* verdict = status + 1;
+    const int want = 2 * step + seen;
+    int cur = *reinterpret_cast<volatile int*>(verdict);
+    while ((cur >> 1) < step) {
+      const int prev = atomicCAS(verdict, cur, want);
+      if (prev == cur) { cur = want; break; }
+      cur = prev;
+    }
+    const int ok = ((cur >> 1) == step) ? (cur & 1) : 0;
     if (!ok) atomicCAS(status, 0, STAFB_ERR_PEER_TIMEOUT);
     __threadfence_system();
     ok_s = ok;
   }
   __syncthreads();
+  const int ok = ok_s;
   const int q = blockIdx.x * blockDim.x + threadIdx.x;
-  if (ok_s && q < n) {
-    T g = T(0);
-    for (int r = 0; r < pv.world; r++) {  // rank order: the same sum on every rank
-      const T* gr = reinterpret_cast<const T*>(pv.grad[r]);
-      g += (r == pv.rank) ? gr[q] : ld_peer(gr + q);
+  if (ok && q < n) {
+    // all peers' loads are issued before the first add (one NVLink round trip, not one per rank); the sum is
+    // taken in rank order, so every rank computes the same bits
+    T gv[PEER_MAX];
+#pragma unroll
+    for (int r = 0; r < PEER_MAX; r++) {
+      gv[r] = T(0);
+      if (r < pv.world) {
+        const T* gr = reinterpret_cast<const T*>(pv.grad[r]);
+        gv[r] = (r == pv.rank) ? gr[q] : ld_peer(gr + q);
+      }
     }
+    T g = T(0);
+#pragma unroll
+    for (int r = 0; r < PEER_MAX; r++)
+      if (r < pv.world) g += gv[r];
     g *= T(1) / T(pv.world);
     const T lr_t = (T)(lr * sqrt(1.0 - pow(b2, (double)step)) / (1.0 - pow(b1, (double)step)));
     const T mm = (T)b1 * m[q] + (T(1) - (T)b1) * g;
@@ -97,7 +127,10 @@ __global__ void __launch_bounds__(256)
     if (atomicAdd(step_d + 1, 1) == (int)gridDim.x - 1) {
       step_d[1] = 0;
       __threadfence();
-      atomicAdd(step_d, 1);
+      // a launch that gave up leaves theta, m, v AND the step count as they were; every block has read the
+      // verdict by now, so it is rewound to "nothing decided for this step" and a repeated launch decides anew
+      if (ok) atomicAdd(step_d, 1);
+      else status[1] = 2 * step - 1;
     }
   }
 }
@@ -129,8 +162,8 @@ extern "C" int stafb_peer_create(stafb_ctx* c, int rank, int world, int n_params
   const size_t bytes = 2 * p->grad_bytes + sizeof(int) * 2 * PEER_MAX;
   STAFB_CUDA_OK(cudaMalloc((void**)&p->block, bytes));
   STAFB_CUDA_OK(cudaMemset(p->block, 0, bytes));
-  STAFB_CUDA_OK(cudaMalloc((void**)&p->status_d, sizeof(int)));
-  STAFB_CUDA_OK(cudaMemset(p->status_d, 0, sizeof(int)));
+  STAFB_CUDA_OK(cudaMalloc((void**)&p->status_d, 2 * sizeof(int)));  // status word, verdict word
+  STAFB_CUDA_OK(cudaMemset(p->status_d, 0, 2 * sizeof(int)));
   STAFB_CUDA_OK(cudaDeviceSynchronize());
   p->peer[rank] = p->block;
   int khz = 1500000;
@@ -188,6 +221,15 @@ extern "C" int stafb_peer_preset_flags(stafb_peer* p, void* stream, int parity, 
   int* flags = reinterpret_cast<int*>(p->block + 2 * p->grad_bytes) + parity * PEER_MAX;
   STAFB_CUDA_OK(cudaMemcpyAsync(flags, host, sizeof(host), cudaMemcpyHostToDevice, (cudaStream_t)stream));
   STAFB_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+  return STAFB_OK;
+}
+
+extern "C" int stafb_peer_set_wait_ms(stafb_peer* p, long long ms) {
+  if (!p || ms < 0) return STAFB_ERR_INVALID;
+  int dev = 0, khz = 1500000;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev);
+  p->wait_cycles = ms * (long long)khz;
   return STAFB_OK;
 }
 

@@ -131,8 +131,14 @@ class PeerExchange:
                    "stafb_allreduce_adam")
 
     def status(self):
+        """First status the exchange kernels recorded (0, or STAFB_ERR_PEER_TIMEOUT); waits for the device."""
         from . import _lib
         return _lib.lib().stafb_peer_status(self.h)
+
+    def set_wait_ms(self, ms):
+        """Bound of the kernel's wait for the peers' flags, in milliseconds of SM clock."""
+        from . import _lib
+        _lib.check(_lib.lib().stafb_peer_set_wait_ms(self.h, int(ms)), "stafb_peer_set_wait_ms")
 
     def close(self):
         """Collective: every rank must have finished its last step before any rank unmaps the buffers."""

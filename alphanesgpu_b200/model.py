@@ -219,5 +219,11 @@ class StafModel:
         n = _lib.lib().stafb_get_phase_times(self.ctx.h, buf.ctypes.data_as(C.c_void_p), 16)
         return dict(zip(self.PHASES[:n], buf[:n].tolist()))
 
+    def mlp_config(self):
+        """(staging mode, atoms per thread group, forward smem bytes, backward smem bytes) of the MLP kernels."""
+        out = np.zeros(4, np.int32)
+        _lib.lib().stafb_model_mlp_config(self.h, out.ctypes.data_as(C.c_void_p))
+        return dict(stage=int(out[0]), apt=int(out[1]), fwd_smem=int(out[2]), bwd_smem=int(out[3]))
+
     def launches(self):
         return _lib.lib().stafb_last_launch_count(self.ctx.h)

@@ -84,8 +84,10 @@ int stafb_compute_descriptors_light(stafb_ctx* ctx, void* stream, const void* po
  * larger requests return STAFB_ERR_CAPACITY and print the limits.  The first call on a device looks up
  * the array's device address (cudaGetSymbolAddress); make that first call outside any stream capture.
  * All calls share the array: calls that overlap on one GPU race, so serialise them (one stream).  Outputs
- * and their optional/NULL rules are those of stafb_compute_descriptors_light; status_out_d (device int,
- * may be NULL) receives the status word (STAFB_OK, STAFB_ERR_RADIAL_OVERFLOW, ...) on the stream. */
+ * and their optional/NULL rules are those of stafb_compute_descriptors_light; status_out_d (device int)
+ * receives the status word (STAFB_OK, STAFB_ERR_RADIAL_OVERFLOW, ...) on the stream.  There is no handle, so
+ * that word is the ONLY report of a saturated radial or angular buffer, a bad box or a cell overflow: with
+ * status_out_d == NULL such a call returns STAFB_OK and truncated rows, unnoticed - pass it. */
 int stafb_compute_descriptors_light_noalloc(int dtype, double radial_cutoff, double rs, double ra, int radial_buffer,
                                             int angular_buffer, void* stream, const void* positions_d,
                                             const void* boxer_d, int nf, int N, void* raddescr_d, void* angdescr_d,
@@ -219,6 +221,14 @@ int stafb_model_n_emb(const stafb_model* m);
 /* offsets of species t: a2, a3, mu, w (into theta), emb (into emb), block size */
 void stafb_model_offsets(const stafb_model* m, int t, int out6[6]);
 
+/* How the MLP kernels of this model were configured (no reference counterpart; for tests and diagnostics):
+ * out4 = { staging mode of the Dense layers in shared memory (2: all layers at kernel start, 1: one layer at a
+ * time, 0: none, weights read from global memory), atoms per thread group (a block owns 8x that many atoms),
+ * dynamic shared memory of the forward kernel, of the backward kernel (bytes) }.  The mode follows from the
+ * layer sizes; the environment variables STAFB_MLP_STAGE / STAFB_MLP_APT, read by stafb_model_create,
+ * override it. */
+void stafb_model_mlp_config(const stafb_model* m, int out4[4]);
+
 /* Energy and forces of nf frames (staf_models/staf_model.py:174-211; inference convention
  * staf_models/staf_model_inference_full.py:118-119 when per_atom_energy == 0):
  * energy[nf] = 0.5*mean_i e_i (per_atom_energy) or 0.5*sum_i e_i; force[nf,3N]. */
@@ -297,9 +307,13 @@ int stafb_adam_step_dev(stafb_ctx* ctx, void* stream, void* theta_d, const void*
  *   stafb_peer_connect  maps the other ranks' blocks (handles[world][64], own entry ignored);
  *   stafb_peer_grad     device pointer of a gradient buffer: pass it as grad_d to stafb_train_step*;
  *   stafb_allreduce_adam  publishes "gradient complete" on every peer, waits for the peers (bounded: about two
- *                       seconds, then STAFB_ERR_PEER_TIMEOUT is recorded and theta is left untouched), sums the
- *                       buffers of `parity` in rank order - bit-identical on every rank -, divides by the world
- *                       size and applies Adam (same formula and device step counter as stafb_adam_step_dev).
+ *                       seconds; then the launch as a whole records STAFB_ERR_PEER_TIMEOUT and leaves theta, the
+ *                       moments and the step counter untouched - one decision per launch, never a partial
+ *                       update), sums the buffers of `parity` in rank order - bit-identical on every rank -,
+ *                       divides by the world size and applies Adam (same formula and device step counter as
+ *                       stafb_adam_step_dev).  After a timeout the ranks may hold different parameters (a late
+ *                       rank still finds the flags of the ranks that gave up): read stafb_peer_status on the
+ *                       host at regular points and re-broadcast theta, the moments and the step count.
  * Consecutive steps must alternate the parity; every rank must make the same calls in the same order.  Before
  * stafb_peer_destroy all ranks must have finished their last step (a host-side barrier). */
 typedef struct stafb_peer stafb_peer;
@@ -311,6 +325,9 @@ int stafb_peer_connect_local(stafb_peer* p, stafb_peer* const* all);
 /* marks every peer as having published step `value` for `parity`: for emulating several ranks on ONE GPU, where
  * the ranks' kernels run one after the other and must never wait for each other */
 int stafb_peer_preset_flags(stafb_peer* p, void* stream, int parity, int value);
+/* bound of the wait for the peers' flags, in milliseconds of SM clock (default: about two seconds, or the
+ * environment variable STAFB_PEER_WAIT_MS read by stafb_peer_create; 0 = give up at the first look) */
+int stafb_peer_set_wait_ms(stafb_peer* p, long long ms);
 void* stafb_peer_grad(stafb_peer* p, int parity);
 int stafb_peer_status(stafb_peer* p);
 void stafb_peer_destroy(stafb_peer* p);
@@ -337,6 +354,12 @@ int stafb_train_step_host_begin(stafb_ctx* ctx, stafb_model* m, void* stream, co
                                 const void* e_label_h, const void* f_label_h, double pe, double pf, double pb,
                                 double alpha_bound, int loss_kind, void* grad_d, int slot);
 int stafb_train_step_host_end(stafb_ctx* ctx, stafb_model* m, int slot, double* losses_h);
+
+/* ---- diagnostics ----------------------------------------------------------------------------
+ * The entry points from here to the end of the header are measurement aids of this library (no reference
+ * counterpart, not part of the operator surface): phase timers, a measured FMA peak, a launch counter.  A
+ * build with -DSTAFB_SWEEP_CLOCKS additionally exports stafb_sweep_clocks / stafb_mlp_clocks (in-kernel cycle
+ * counters per phase of the sweep and MLP kernels); the default build does not contain them. */
 
 /* Per-phase device timing of the fused calls, with CUDA events on the launching stream.  Phases, in
  * order: descriptors, af_fwd, mlp_fwd, force, loss, force_grad, mlp_bwd, af_grad (the last four only for

@@ -16,9 +16,21 @@ _LIB = None
 MAX_TYPES, MAX_DENSE = 4, 6
 
 
+def reference_dir():
+    """Root of the reference tree if one can be found: $STAF_REFERENCE_DIR, else a folder named `reference`
+    beside the repository; None otherwise (the prebuilt oracle/_ref files are then used as they are)."""
+    cands = [os.environ.get("STAF_REFERENCE_DIR"),
+             os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in cands:
+        if c and os.path.isdir(os.path.join(c, "STAF", "src")):
+            return c
+    return None
+
+
 def build(quiet=True):
     """Compile the oracle (and oracle/_ref when the reference tree is present)."""
-    out = subprocess.run(["make", "-C", _HERE], capture_output=True, text=True)
+    ref = reference_dir()
+    out = subprocess.run(["make", "-C", _HERE] + (["REF=" + ref] if ref else []), capture_output=True, text=True)
     if out.returncode != 0:
         raise RuntimeError("oracle build failed:\n" + out.stdout + out.stderr)
     if not quiet:

@@ -48,14 +48,111 @@ def test_energy_force(oracle, frame0, name, seeds, dtype):
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def _push_over_bound(shape, theta):
+    """Two exponents beyond alpha_bound = 5 (on channels whose squared embedding is not zero), so that the bound
+    term and its gradient are exercised."""
+    theta = theta.copy()
+    theta[shape.offsets(0)["a2"] + 1] = 5.5
+    theta[shape.offsets(1)["a3"] + 4] = 6.0
+    return theta
+
+
+def _check_train_step(oracle, m, shape, pos, box, el, fl, theta, emb, dtype, loss, kw, host_path=True):
+    """Energy, forces, the four losses and the gradient per parameter family (alpha2b, alpha3b, mu, Dense
+    weights+biases of every species) against the oracle: the reference's own gradient regression, restated
+    (test/test-regression/regression-grad-param/run_grad_param_regression.py:80-253)."""
+    ref = oracle.energy_force_grad(CFG, shape.desc(), pos, box, shape.type_map, theta, emb, dtype, with_grad=True,
+                                   e_label=el, f_label=fl, loss_kind=0 if loss == "huber" else 1, **kw)
+    assert ref["status"] == 0
+    d = lambda a: torch.as_tensor(a.astype(dtype)).cuda()
+    e, f = m.loss_and_grad(d(pos), d(box), d(el), d(fl), want_outputs=True)
+    m.ctx.raise_on_status("train_step")
+    tol = TOL[dtype]
+    assert rel_err(e.cpu().numpy(), ref["energy"]) <= tol
+    assert rel_err(f.cpu().numpy(), ref["force"]) <= tol
+    losses = m.losses.cpu().numpy()
+    assert np.allclose(losses, ref["losses"], rtol=tol * 10, atol=0)
+    g, gr = m.grad.cpu().numpy().astype(np.float64), ref["grad"].astype(np.float64)
+    for t in range(shape.nt):
+        o = shape.offsets(t)
+        for lo, hi in ((o["a2"], o["a3"]), (o["a3"], o["mu"]), (o["mu"], o["w"]), (o["w"], o["a2"] + o["size"])):
+            assert rel_err(g[lo:hi], gr[lo:hi]) <= tol, (t, lo, hi)
+    if host_path:  # host-buffer entry point gives the same numbers
+        lh = m.loss_and_grad_host(pos, box, el, fl).copy()
+        assert np.allclose(lh, losses, rtol=1e-6 if dtype == np.float32 else 1e-12)
+        assert rel_err(m.grad.cpu().numpy(), g) <= (2e-6 if dtype == np.float32 else 1e-12)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_train_step_on_the_reference_model_shape(oracle, frame0, dtype):
+    """The reference's real frame with its exported model (Fr = 20, Fa = 40, MLP 60-140-140-1 per species): the
+    training gradient per parameter family.  At this size the Dense layers no longer fit in shared memory all at
+    once, so the MLP kernels run in their other staging modes, and every species-pair class has more active
+    channels than one pass of the sweeps takes."""
+    from alphanesgpu_b200.model import StafModel
+    pos, box, shape, theta, emb = _case("frame0", None, frame0)
+    theta = _push_over_bound(shape, theta)
+    el, fl = synth.labels(1, shape.N)
+    kw = dict(pe=0.7, pf=1.3, pb=0.9, alpha_bound=5.0)
+    m = StafModel(shape, CFG, theta, emb, 1, dtype=_tdt(dtype), loss="huber", **kw)
+    cfg = m.mlp_config()
+    assert cfg["stage"] == (1 if dtype == np.float32 else 0), cfg  # layer-at-a-time in fp32, global reads in fp64
+    assert max(shape.Fa) // shape.C > 8  # more active angular channels per class than one chunk of the sweeps
+    _check_train_step(oracle, m, shape, pos, box, el, fl, theta, emb, dtype, "huber", kw)
+    m.close()
+
+
+@pytest.mark.parametrize("stage", [0, 1, 2])
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_train_step_in_every_mlp_staging_mode(oracle, frame0, monkeypatch, dtype, stage):
+    """The three ways the MLP kernels hold their Dense layers (all in shared memory, one layer at a time, read
+    from global memory), each forced on the small model and checked against the oracle."""
+    from alphanesgpu_b200.model import StafModel
+    monkeypatch.setenv("STAFB_MLP_STAGE", str(stage))
+    pos, box, shape, theta, emb = _case("water96", [1000, 1001], frame0)
+    theta = _push_over_bound(shape, theta)
+    el, fl = synth.labels(2, shape.N)
+    kw = dict(pe=0.7, pf=1.3, pb=0.9, alpha_bound=5.0)
+    m = StafModel(shape, CFG, theta, emb, 2, dtype=_tdt(dtype), loss="huber", **kw)
+    assert m.mlp_config()["stage"] == stage
+    _check_train_step(oracle, m, shape, pos, box, el, fl, theta, emb, dtype, "huber", kw, host_path=False)
+    m.close()
+
+
+def test_train_step_batch_of_eight(oracle, frame0):
+    """Eight 768-atom frames per step, the per-GPU batch of the data-parallel configuration."""
+    from alphanesgpu_b200.model import StafModel
+    pos, box, shape, theta, emb = _case("water768", list(range(1200, 1208)), frame0)
+    theta = _push_over_bound(shape, theta)
+    el, fl = synth.labels(8, shape.N)
+    kw = dict(pe=1.0, pf=1.0, pb=1.0, alpha_bound=5.0)
+    m = StafModel(shape, CFG, theta, emb, 8, dtype=torch.float32, loss="huber", **kw)
+    _check_train_step(oracle, m, shape, pos, box, el, fl, theta, emb, np.float32, "huber", kw)
+    m.close()
+
+
+def test_energy_force_of_the_24576_atom_box(oracle, frame0):
+    """The large inference box (8192 O + 16384 H, L = 62.7 A; 13 x 13 x 13 cells, the multi-kernel cell-list
+    path): energy and every force component against the oracle."""
+    from alphanesgpu_b200.model import StafModel
+    pos, box, shape, theta, emb = _case("water24576", [1400], frame0)
+    ref = oracle.energy_force_grad(CFG, shape.desc(), pos, box, shape.type_map, theta, emb, np.float32,
+                                   per_atom_energy=False)
+    assert ref["status"] == 0
+    m = StafModel(shape, CFG, theta, emb, 1, dtype=torch.float32)
+    e, f = m.energy_force(pos.astype(np.float32), box.astype(np.float32))
+    assert rel_err(e.cpu().numpy(), ref["energy"]) <= 1e-5
+    assert rel_err(f.cpu().numpy(), ref["force"]) <= 1e-5
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
 @pytest.mark.parametrize("name,seeds,loss", [("water96", [1000, 1001], "huber"), ("water96", [1000, 1001], "mse"),
                                              ("water768", [1100, 1101, 1102, 1103], "huber")])
 def test_train_step_losses_and_gradient(oracle, frame0, name, seeds, loss, dtype):
     from alphanesgpu_b200.model import StafModel
     pos, box, shape, theta, emb = _case(name, seeds, frame0)
-    theta = theta.copy()
-    theta[shape.offsets(0)["a2"] + 1] = 5.5  # exercise the bound term
-    theta[shape.offsets(1)["a3"] + 4] = 6.0
+    theta = _push_over_bound(shape, theta)
     nf = pos.shape[0]
     el, fl = synth.labels(nf, shape.N)
     kw = dict(pe=0.7, pf=1.3, pb=0.9, alpha_bound=5.0)

@@ -138,6 +138,9 @@ def _late_peer_worker(rank, world, port, q):
     torch.cuda.synchronize()
     status = px.status()
     untouched = bool(torch.equal(a.theta, before))
+    if rank == 0:  # the launch that gave up changed nothing at all: moments and step count included
+        untouched = untouched and int(a.step_d[0]) == 0 and float(a.adam_m.abs().max()) == 0.0 \
+            and float(a.adam_v.abs().max()) == 0.0
     e, f = a.energy_force(d[0][0:2], d[1][0:2])  # the context still works
     usable = bool(torch.isfinite(e).all())
     q.put((rank, status, untouched, usable))
@@ -213,6 +216,59 @@ def test_eight_emulated_ranks_on_one_gpu():
         assert int(state[r]["step"][0]) == 1
         assert torch.equal(state[r]["theta"], state[0]["theta"]), r
     assert torch.allclose(state[0]["theta"], want, rtol=2e-6, atol=2e-7)
+    for r in range(W):
+        L.stafb_peer_destroy(hs[r])
+    ctx.close()
+
+
+def test_a_launch_that_gives_up_changes_nothing():
+    """Flags that nothing sets and a zero bound: every block of the launch gives up together (the decision is
+    taken once per launch), so theta, both moments and the step counter are bit-identical to before, the status
+    says STAFB_ERR_PEER_TIMEOUT and the next launch - with the flags in place - applies its update in full."""
+    import ctypes as C
+    from alphanesgpu_b200 import _lib
+    from alphanesgpu_b200.dist import _DevArray
+    from alphanesgpu_b200.ops import Context
+    L = _lib.lib()
+    dev = torch.device("cuda:0")
+    ctx = Context(CFG["Rc"], CFG["nr"], CFG["na"], 96, CFG["Rs"], CFG["Ra"], 1, torch.float32, dev)
+    W, n, lr = 4, 70001, 1e-3  # 274 blocks: more than one per SM
+    hs = (C.c_void_p * W)()
+    for r in range(W):
+        h = C.c_void_p()
+        _lib.check(L.stafb_peer_create(ctx.h, r, W, n, C.byref(h)), "stafb_peer_create")
+        hs[r] = h
+    gen = torch.Generator(device="cpu").manual_seed(11)
+    grads = [torch.randn(n, generator=gen).to(dev) for _ in range(W)]
+    for r in range(W):
+        _lib.check(L.stafb_peer_connect_local(hs[r], hs), "stafb_peer_connect_local")
+        _lib.check(L.stafb_peer_set_wait_ms(hs[r], 0), "stafb_peer_set_wait_ms")
+        g = torch.as_tensor(_DevArray(L.stafb_peer_grad(hs[r], 0), n, torch.float32), device=dev)
+        g.copy_(grads[r])
+    theta0 = torch.randn(n, generator=gen).to(dev)
+    m0, v0 = torch.rand(n, generator=gen).to(dev), torch.rand(n, generator=gen).to(dev)
+    theta, m, v = theta0.clone(), m0.clone(), v0.clone()
+    step = torch.zeros(2, dtype=torch.int32, device=dev)
+    stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    p = lambda t: C.c_void_p(t.data_ptr())
+    call = lambda: _lib.check(L.stafb_allreduce_adam(ctx.h, hs[0], stream, 0, p(theta), p(m), p(v), lr, 0.9, 0.999,
+                                                     1e-7, p(step)), "stafb_allreduce_adam")
+    call()  # no peer has published anything
+    torch.cuda.synchronize()
+    assert L.stafb_peer_status(hs[0]) == 9
+    assert torch.equal(theta, theta0) and torch.equal(m, m0) and torch.equal(v, v0)
+    assert step.tolist() == [0, 0]
+    _lib.check(L.stafb_peer_preset_flags(hs[0], stream, 0, 1), "stafb_peer_preset_flags")
+    call()  # the same step again, now with every flag in place
+    torch.cuda.synchronize()
+    assert step.tolist() == [1, 0]
+    g = torch.zeros(n, device=dev)
+    for r in range(W):
+        g = g + grads[r]
+    g = g / W
+    mm, vv = 0.9 * m0 + 0.1 * g, 0.999 * v0 + 0.001 * g * g
+    want = theta0 - (lr * np.sqrt(1 - 0.999) / (1 - 0.9)) * mm / (torch.sqrt(vv) + 1e-7)
+    assert torch.allclose(theta, want, rtol=2e-6, atol=2e-7)
     for r in range(W):
         L.stafb_peer_destroy(hs[r])
     ctx.close()

@@ -17,7 +17,7 @@ torch = pytest.importorskip("torch")
 RC, RS, RA, NR, NA = 4.5, 2.25, 4.5, 60, 1770
 
 
-def _noalloc(L, pos, box, tdt):
+def _noalloc(L, pos, box, tdt, NR=NR, NA=NA):
     nf, N = box.shape[0], pos.shape[1] // 3
     dev = pos.device
     e = lambda *s, d=tdt: torch.full(s, -7, dtype=d, device=dev)  # poison: every element must be written
@@ -69,3 +69,25 @@ def test_noalloc_rejects_sizes_beyond_the_builtin_scratch():
     dbox = torch.as_tensor((box * 0.6).astype(np.float32)).cuda()
     rc, _, status = _noalloc(L, dpos, dbox, torch.float32)
     assert rc == 0 and status == 1
+
+
+def test_noalloc_at_the_edge_of_the_builtin_scratch():
+    """The largest request the built-in scratch takes in every dimension at once: 16 frames x 64 atoms = 1024
+    atoms, radial_buffer 64, float64 (the widest rows)."""
+    from alphanesgpu_b200 import _lib, ops
+    L = _lib.lib()
+    nr, na = 64, 64 * 63 // 2
+    pos, box, _ = synth.water_frames("water96", list(range(1300, 1316)))
+    pos = np.ascontiguousarray(pos.reshape(16, 96, 3)[:, :64].reshape(16, -1))  # any 64 atoms of each frame
+    dpos, dbox = torch.as_tensor(pos).cuda(), torch.as_tensor(box).cuda()
+    rc, got, status = _noalloc(L, dpos, dbox, torch.float64, nr, na)
+    assert rc == 0 and status == 0
+    ops.construct_descriptors_light(RC, nr, na, 64, None, RS, RA, 16, dtype=torch.float64)
+    ref = ops.compute_descriptors_light(dpos, dbox)
+    for g, r in zip(got, ref):
+        assert torch.equal(g, r)
+    # one more frame, one more atom or a wider row is refused
+    rc, _, _ = _noalloc(L, torch.cat([dpos, dpos[:1]]), torch.cat([dbox, dbox[:1]]), torch.float64, nr, na)
+    assert rc == 7
+    rc, _, _ = _noalloc(L, dpos, dbox, torch.float64, 65, 65 * 64 // 2)
+    assert rc == 7
