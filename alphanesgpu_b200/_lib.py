@@ -10,7 +10,7 @@ LIB_PATH = os.path.join(HERE, "libstafb.so")
 
 OK = 0
 STATUS_NAMES = {1: "RADIAL_OVERFLOW", 2: "ANGULAR_OVERFLOW", 3: "CELL_OVERFLOW", 4: "BAD_BOX", 5: "INVALID",
-                6: "CUDA", 7: "CAPACITY", 8: "NONFINITE"}
+                6: "CUDA", 7: "CAPACITY", 8: "NONFINITE", 9: "PEER_TIMEOUT", 10: "STAGE_TIMEOUT"}
 
 
 class StafbError(RuntimeError):

@@ -35,6 +35,7 @@ extern "C" const char* stafb_strerror(int s) {
     case STAFB_ERR_CAPACITY: return "batch, atom count or cell grid exceeds the capacity the context was created with";
     case STAFB_ERR_NONFINITE: return "non-finite result";
     case STAFB_ERR_PEER_TIMEOUT: return "a peer rank did not publish its gradient in time";
+    case STAFB_ERR_STAGE_TIMEOUT: return "an asynchronous copy into shared memory did not complete in time";
     default: return "unknown status";
   }
 }

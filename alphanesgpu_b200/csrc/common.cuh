@@ -123,6 +123,32 @@ struct CoreCoef {
   T Rc, Rs, Ra, A, B, C, pa, pb;
 };
 
+// Neighbour record of one central atom, the only thing the fused sweeps read about the geometry.  One
+// contiguous block per atom (so that a sweep stages it with a single bulk copy), neighbours grouped by species
+// (species 0 first, ...) and distance-sorted inside a group, so that a sweep addresses "the k-th neighbour of
+// species q" directly and the angular neighbours (r < Ra) are a prefix of every group:
+//   U[nr]   (4 reals)  unit vector (r_i - r_k)/r and the angular cutoff fc(r)
+//   V[nr]   (4 reals)  1/r, dfc/dr, radial descriptor d(r), dd/dr
+//   id[nr]  (int32)    index of the neighbour in the frame (padded to a multiple of 4 entries)
+//   hdr[12] (int32)    n, m = number of angular neighbours, cntR[4] neighbours per species, cntA[4] angular
+//                      neighbours per species, 2 unused
+// Entries past n are never read.
+constexpr int ROW_HDR_INTS = 12;
+__host__ __device__ inline int row_off_v(int nr, int es) { return nr * 4 * es; }
+__host__ __device__ inline int row_off_id(int nr, int es) { return 2 * nr * 4 * es; }
+__host__ __device__ inline int row_off_hdr(int nr, int es) { return 2 * nr * 4 * es + 4 * ((nr + 3) & ~3); }
+__host__ __device__ inline int row_stride_bytes(int nr, int es) { return row_off_hdr(nr, es) + 4 * ROW_HDR_INTS; }
+
+// Where the neighbour kernels leave the records, and how they find the species of a neighbour: atoms are
+// species-sorted with boundaries shift[] unless a per-atom map is given (owned + ghost atoms of a domain).
+struct RowSink {
+  void* rows;  // [nf, ncen] records of `stride` bytes; null: no records are written
+  int stride;
+  int nt;
+  int shift[STAFB_MAX_TYPES + 1];
+  const int* tmap;
+};
+
 }  // namespace stafb
 
 struct stafb_ctx {
@@ -167,12 +193,13 @@ void stafb_core_coefficients_for(int dtype, double Rc, double Rs, double out5[5]
 
 // launchers implemented per translation unit (T = float | double)
 namespace stafb {
+// The operator outputs (raddescr ... numtriplet) may all be null when only the records of `sink` are wanted.
 template <class T>
 int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box, int nf, int N, T* raddescr,
                        T* angdescr, T* des3bsupp, int* intmap2b, int* intmap3b, T* der2b, T* der3b, T* der3bsupp,
-                       int* numtriplet, int ncen = -1);
-// rows of the first ncen atoms from a caller-supplied, distance-sorted neighbour list over nall atoms
+                       int* numtriplet, int ncen = -1, const RowSink* sink = nullptr);
+// records of the first ncen atoms from a caller-supplied, distance-sorted neighbour list over nall atoms
 template <class T>
 int launch_rows_from_list(stafb_ctx* c, cudaStream_t s, const T* pos, int ncen, int nall, const int* howmany,
-                          const int* with, T* raddescr, T* des3bsupp, int* intmap2b, int* numtriplet);
+                          const int* with, const RowSink* sink);
 }

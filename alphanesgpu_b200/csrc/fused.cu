@@ -2,90 +2,21 @@
 //
 // The operator path (ops.cu) has to honour the reference's tensor contract, which pushes
 // ~110 KB per atom of angular descriptors (angdescr, intmap3b, der3b) through HBM.  Here the
-// neighbour kernel leaves only a compact sorted neighbour row per atom (MIC vector, radial
-// descriptor, cutoff, their scalar derivatives: ~2 KB) and every sweep rebuilds the triplet
-// geometry in registers from rows staged in shared memory.  One warp owns one central atom.
+// neighbour kernel leaves one compact record per atom (unit vectors, cutoffs, radial descriptors and
+// their derivatives, neighbour ids, grouped by species: ~2 KB, common.cuh) and every sweep (sweep.cuh)
+// rebuilds the triplet geometry in registers from the record staged in shared memory.
 //
-// Triplets are enumerated per species-pair class (ta <= tb) rather than in the reference's
-// j<k slot order: inside a class every triplet uses the same parameter row
-// (row = type_j + type_k, STAF/src/fingerprint/ang/reforce.cu.cc:56), so the channel loop is
-// uniform across the warp and channels whose squared embedding is zero are skipped for the
-// whole class.  exp(a1*sj + a2*sk) is formed as a product of per-neighbour factors
-// exp(a1*sj), exp(a2*sk) tabulated once per (class, channel chunk); in fp32 all exponentials
-// are base-2 with parameters pre-scaled by log2(e) (one multiply + one MUFU per evaluation).
-// The force sweep walks ORDERED pairs so that every lane accumulates the force on "its"
-// neighbour in registers - no shared-memory atomics in the inner loop.
-//
-// Math: STAF/src/fingerprint, force, grad_finger, grad_force (rad and ang) reforce.cu.cc and
-// STAF/staf_models/staf_model.py:168-258 of the reference (see include/stafb.h).
+// This file: the evaluation's housekeeping kernel, the loss, Adam, the model handle and the launch
+// sequences behind the fused entry points of include/stafb.h.  Math: STAF/staf_models/staf_model.py:168-258.
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
+#include <type_traits>
 #include "common.cuh"
 
 namespace stafb {
 
-constexpr int MAXCH = 8;     // channels processed per pair sweep
-// warps per central atom (= per block) in the sweep kernels: the ordered force loop is long enough to
-// profit from two warps; the unordered sweeps run fastest with one
-template <int MODE> struct SweepWpa { static constexpr int value = (MODE == 1) ? 2 : 1; };
-// Resident blocks per SM the sweep kernels are compiled for (caps the registers per thread: 65536 / (threads *
-// blocks)).  Without the cap the register allocation of one mode moves by +-30 % with unrelated edits, and the
-// sweeps are occupancy-sensitive: a step's 3072 one-warp blocks fit the 148 SMs in one wave at <= 96 registers.
-template <int MODE, size_t ES> struct SweepMinBlocks { static constexpr int value = 21; };  // <= 97 registers
-template <> struct SweepMinBlocks<1, 4> { static constexpr int value = 12; };  // force, 64 threads: <= 85
-template <> struct SweepMinBlocks<2, 4> { static constexpr int value = 21; };  // force backward: <= 97
-template <> struct SweepMinBlocks<0, 8> { static constexpr int value = 21; };  // fp64: <= 97
-template <> struct SweepMinBlocks<1, 8> { static constexpr int value = 6; };   // <= 170
-template <> struct SweepMinBlocks<2, 8> { static constexpr int value = 13; };  // <= 157
-template <> struct SweepMinBlocks<3, 8> { static constexpr int value = 17; };  // <= 120
-template <> struct SweepMinBlocks<4, 8> { static constexpr int value = 17; };
 constexpr int ML_THREADS = 256;
-
-// exponential with a pre-scaled argument: fp32 uses 2^x (MUFU.EX2), fp64 the full-precision exp
-template <class T> struct Ex;
-template <> struct Ex<float> {
-  static __host__ __device__ __forceinline__ float scale() { return 1.4426950408889634f; }
-  static __device__ __forceinline__ float f(float x) { return exp2f(x); }
-};
-template <> struct Ex<double> {
-  static __host__ __device__ __forceinline__ double scale() { return 1.0; }
-  static __device__ __forceinline__ double f(double x) { return exp(x); }
-};
-
-// Optional in-kernel phase clocks of the sweep kernels (build with -DSTAFB_SWEEP_CLOCKS): lane 0 of every warp
-// adds the clock64() ticks it spent in each phase to g_sweep_clk[mode][phase]; stafb_sweep_clocks() reads and
-// clears the table.  Phases: 0 staging, 1 species lists + cotangent staging, 2 radial part, 3 channel
-// parameters + exponential tables, 4 pair loop, 5 reductions, 6 write-back.
-#ifdef STAFB_SWEEP_CLOCKS
-__device__ unsigned long long g_sweep_clk[5][8];
-#define SWEEP_CLK_INIT long long clk_t0__ = clock64();
-#define SWEEP_TICK(p)                                                                       \
-  {                                                                                         \
-    const long long now__ = clock64();                                                      \
-    if ((threadIdx.x & 31) == 0) atomicAdd(&g_sweep_clk[MODE][p], (unsigned long long)(now__ - clk_t0__)); \
-    clk_t0__ = now__;                                                                       \
-  }
-#else
-#define SWEEP_CLK_INIT
-#define SWEEP_TICK(p)
-#endif
-
-// Two-channel packed arithmetic.  On sm_100 a float2 multiply / add / fma is ONE instruction (__fmul2_rn,
-// __fadd2_rn, __ffma2_rn), so the channel loops of the sweeps carry two channels per instruction; double pairs
-// are two scalar operations.
-__device__ __forceinline__ float2 p_mul(float2 a, float2 b) { return __fmul2_rn(a, b); }
-__device__ __forceinline__ float2 p_add(float2 a, float2 b) { return __fadd2_rn(a, b); }
-__device__ __forceinline__ float2 p_fma(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
-__device__ __forceinline__ double2 p_mul(double2 a, double2 b) { return make_double2(a.x * b.x, a.y * b.y); }
-__device__ __forceinline__ double2 p_add(double2 a, double2 b) { return make_double2(a.x + b.x, a.y + b.y); }
-__device__ __forceinline__ double2 p_fma(double2 a, double2 b, double2 c) {
-  return make_double2(a.x * b.x + c.x, a.y * b.y + c.y);
-}
-__device__ __forceinline__ float2 mk2(float x, float y) { return make_float2(x, y); }
-__device__ __forceinline__ double2 mk2(double x, double y) { return make_double2(x, y); }
-__device__ __forceinline__ float2 p_ex(float2 a) { return make_float2(Ex<float>::f(a.x), Ex<float>::f(a.y)); }
-__device__ __forceinline__ double2 p_ex(double2 a) { return make_double2(Ex<double>::f(a.x), Ex<double>::f(a.y)); }
 
 struct ModelDev {
   int nt, C, N, ncls;
@@ -111,25 +42,6 @@ struct ModelDev {
     return t;
   }
 };
-
-template <class T>
-struct SweepIn {
-  const T* geom;   // [nf,N,nr,4]
-  const T* gsc;    // [nf,N,nr,2]
-  const T* rad;    // [nf,N,nr]
-  const T* d3s;    // [nf,N,nr]
-  const int* im2;  // [nf,N,nr+1]
-  const int* ntr;  // [nf,N]
-  // Domain mode (one frame): the centres are the first N atoms (species-sorted) of nall >= N atoms; the
-  // species of the others comes from tmap[nall] and forces are written for all nall atoms.  tmap == null:
-  // every atom is a centre (nall == N) and the species follows from the species-sorted order.
-  const int* tmap;
-  int nall;
-  int nf, nr;
-};
-
-// AFV = AF forward that also leaves d(AF)/d(alpha) per atom (training); AFGRAD = stand-alone alpha gradient
-enum { MODE_AF = 0, MODE_FORCE = 1, MODE_FGRAD = 2, MODE_AFGRAD = 3, MODE_AFV = 4 };
 
 // species-major enumeration: block -> (species t, index q0 of its first atom among the nf*tipos[t]
 // atoms of that species); W atoms per block, blocks never mix species
@@ -161,660 +73,7 @@ static inline int species_blocks(const ModelDev& md, int nf, int W) {
   return s;
 }
 
-// per-warp shared memory layout of the sweep kernels (offsets in bytes)
-struct SweepLayout {
-  int p0, p1, tab, chpa, chpb, pall, pball, xtra, acc, red, rsum, ids, cnts, tj, lst, actl, eflag, total;
-};
-
-template <class T>
-static inline SweepLayout sweep_layout(int nr, int nt, int xt, int nacc, int famax, int wpa, int nrs, int ncf) {
-  SweepLayout L;
-  int o = 0;
-  auto take = [&](int bytes) { int r = o; o += (bytes + 15) & ~15; return r; };
-  L.p0 = take(nr * 4 * sizeof(T));
-  L.p1 = take(nr * 4 * sizeof(T));
-  L.tab = take(MAXCH * nr * 2 * sizeof(T));
-  L.chpa = take(MAXCH * 4 * sizeof(T));
-  L.chpb = take(MAXCH * 2 * sizeof(T));
-  L.pall = take(ncf * 4 * sizeof(T));
-  L.pball = take(ncf * 2 * sizeof(T));
-  L.xtra = take(nr * xt * sizeof(T));
-  L.acc = take(nacc * sizeof(T));
-  L.red = take(wpa * 4 * MAXCH * sizeof(T));
-  L.rsum = take(nrs * sizeof(T));
-  L.ids = take(nr * sizeof(int));
-  L.cnts = take(2 * STAFB_MAX_TYPES * sizeof(int));
-  L.tj = take(nr);
-  L.lst = take(nt * nr);
-  L.actl = take(famax);
-  L.eflag = take(ncf);
-  L.total = o;
-  return L;
-}
-
-// steps through the pairs of a class, 32 at a time, without divisions
-struct PairStep {
-  int ja, kb;
-  __device__ __forceinline__ void init_rect(int p, int nb) { ja = p / nb; kb = p - ja * nb; }
-  __device__ __forceinline__ void step_rect(int nb, int q32, int r32) {
-    ja += q32;
-    kb += r32;
-    if (kb >= nb) { kb -= nb; ja++; }
-  }
-  __device__ __forceinline__ void init_tri(int p, int n) { unrank_pair(p, n, ja, kb); }
-  __device__ __forceinline__ void step_tri(int n, int st) {  // advance st positions in the row-major upper triangle
-    kb += st;
-    while (kb >= n && ja < n - 1) {
-      const int o = kb - n;
-      ja++;
-      kb = ja + 1 + o;
-    }
-  }
-};
-
-// Sums NV per-lane values over the 32 lanes of a warp.  Every step halves the number of values a lane
-// still carries (lanes with the step's bit set keep the upper half and hand over the lower one), so
-// NV-1 shuffles replace 5*NV; once one value is left the remaining steps are a plain butterfly.
-// On return lane L holds the total of value index L >> log2(32 / NV).  NV is a power of two <= 32.
-template <class T, int NV>
-__device__ __forceinline__ T multi_reduce(T (&v)[NV], int lane) {
-  static_assert(NV == 1 || NV == 2 || NV == 4 || NV == 8 || NV == 16 || NV == 32, "NV must be a power of two");
-  int off = 16;
-#pragma unroll
-  for (int half = NV / 2; half >= 1; half >>= 1) {
-    const bool up = (lane & off) != 0;
-#pragma unroll
-    for (int i = 0; i < half; i++) {
-      const T keep = up ? v[i + half] : v[i];
-      const T send = up ? v[i] : v[i + half];
-      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-    }
-    off >>= 1;
-  }
-  T r = v[0];
-  for (; off >= 1; off >>= 1) r += __shfl_xor_sync(0xffffffffu, r, off);
-  return r;
-}
-
-template <int WPA>
-__device__ __forceinline__ void gsync() {
-  if (WPA == 1) __syncwarp(); else __syncthreads();
-}
-
-// One block of WPA warps per central atom.  VIR (force mode only) adds the virial; it is a template
-// parameter so that the training step's force sweep does not carry its registers.
-template <class T, int MODE, int WPA, bool VIR>
-__global__ void __launch_bounds__(WPA * 32, SweepMinBlocks<MODE, sizeof(T)>::value * ((MODE == 1 && WPA == 1) ? 2 : 1))
-    k_sweep(ModelDev md, SweepIn<T> in, SweepLayout L, const T* __restrict__ theta, const T* __restrict__ emb,
-            const T* __restrict__ chan_in,  // FORCE/FGRAD: netderiv[nf,N,Fmax]; AFGRAD: dL/dAF[nf,N,Fmax]
-            const T* __restrict__ fbar,     // FGRAD: dL/dF[nf,3N]
-            T* __restrict__ out,            // AF: af[nf,N,Fmax]; FORCE: force[nf,3N]; FGRAD: gradnet[nf,N,Fmax]
-            T* __restrict__ grad,           // FGRAD/AFGRAD: flat parameter gradient (accumulated)
-            T* __restrict__ vout, int nv,   // AFV: d(AF)/d(alpha2b|alpha3b) rows [nf,N,nv]
-            double* __restrict__ vir) {     // FORCE: virial accumulators [nf,9] or null
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  typedef typename Vec4<T>::type T4;
-  typedef typename Vec2<T>::type T2;
-  constexpr int NT = WPA * 32;
-  // independent pairs in flight per lane: two hide the shared-memory and exp2 latencies of the fingerprint sweeps
-  // (41 -> 36 us); the force-backward sweep needs 108 registers for that and gets slower
-  constexpr int PAIR_UNROLL = (MODE == MODE_FGRAD) ? 1 : 2;
-  constexpr bool IS_AF = (MODE == MODE_AF || MODE == MODE_AFV);       // produces fingerprints
-  constexpr bool HAS_V = (MODE == MODE_AFGRAD || MODE == MODE_AFV);   // accumulates d(AF)/d(alpha) terms
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  int t, b, i;
-  if (!locate_atom(md, in.nf, 1, 0, t, b, i)) return;
-  unsigned char* base = smem_raw;
-  T4* P0 = reinterpret_cast<T4*>(base + L.p0);   // unit vector (i - k)/r and cutoff fc
-  T4* P1 = reinterpret_cast<T4*>(base + L.p1);   // 1/r, dfc/dr, radial descriptor d, dd/dr
-  T2* tab = reinterpret_cast<T2*>(base + L.tab);
-  T4* chpa = reinterpret_cast<T4*>(base + L.chpa);  // alpha1, alpha2, beta, beta*scale
-  T2* chpb = reinterpret_cast<T2*>(base + L.chpb);  // mode-dependent coefficient, netderiv
-  T4* pall = reinterpret_cast<T4*>(base + L.pall);  // the same two for every (class, channel), fetched once
-  T2* pball = reinterpret_cast<T2*>(base + L.pball);
-  // channel PAIRS (2*lp, 2*lp+1) share one float4: tab4[lp][k] = exp(a1*fc_k) of both channels, exp(a2*fc_k) of both;
-  // chq[lp] = (alpha1 x2, alpha2 x2); chr[lp] = (beta x2, beta*scale x2); chs[lp] = (coefficient x2, netderiv x2)
-  constexpr int MAXP = MAXCH / 2;
-  T4* tab4 = reinterpret_cast<T4*>(tab);
-  T4* chq = chpa;
-  T4* chr = chpa + MAXP;
-  T4* chs = reinterpret_cast<T4*>(chpb);
-  T* xtra = reinterpret_cast<T*>(base + L.xtra);
-  T* acc = reinterpret_cast<T*>(base + L.acc);
-  T* red = reinterpret_cast<T*>(base + L.red);      // [WPA][4*MAXCH] per-warp partial sums
-  T* rsum = reinterpret_cast<T*>(base + L.rsum);    // [nt][Frmax] radial partial sums per neighbour species
-  int* ids = reinterpret_cast<int*>(base + L.ids);
-  int* cnts = reinterpret_cast<int*>(base + L.cnts);
-  unsigned char* tj = base + L.tj;
-  unsigned char* lst = base + L.lst;
-  unsigned char* actl = base + L.actl;
-  unsigned char* eflag = base + L.eflag;  // [ncls][Fa] squared embedding != 0
-
-  const int N = md.N, nr = in.nr, nt = md.nt;
-  const int Fr = md.Fr[t], Fa = md.Fa[t], Fmax = md.Fmax;
-  const size_t gi = (size_t)b * N + i;
-  const T* a2 = theta + md.off_a2[t];
-  const T* a3 = theta + md.off_a3[t];
-  const T* e2 = emb + md.off_emb[t];
-  const T* e3 = e2 + nt * Fr;
-  const T* chrow = chan_in ? chan_in + gi * Fmax : nullptr;
-  const T SC = Ex<T>::scale();
-  // accumulator regions inside acc[]
-  const int ACC_GN = 0;                      // [Famax]     AF: fingerprints; FGRAD: gradnet (angular part)
-  const int ACC_A2 = md.Famax;               // [nt*Frmax]  dL/dalpha2b
-  const int ACC_A3 = ACC_A2 + nt * md.Frmax; // [C*3*Famax] dL/dalpha3b
-  const int NACC = ACC_A3 + md.C * 3 * md.Famax;
-
-  SWEEP_CLK_INIT
-  int n = in.im2[gi * (nr + 1)];
-  if (n > nr) n = nr;
-  int m = in.ntr[gi];
-  if (m > n) m = n;
-  for (int k = tid; k < n; k += NT) {
-    const T4 g = reinterpret_cast<const T4*>(in.geom)[gi * nr + k];
-    const T2 s = reinterpret_cast<const T2*>(in.gsc)[gi * nr + k];
-    const T inv = T(1) / g.w;
-    T4 q0, q1;
-    q0.x = g.x * inv; q0.y = g.y * inv; q0.z = g.z * inv; q0.w = in.d3s[gi * nr + k];
-    q1.x = inv; q1.y = s.y; q1.z = in.rad[gi * nr + k]; q1.w = s.x;
-    P0[k] = q0;
-    P1[k] = q1;
-    const int id = in.im2[gi * (nr + 1) + 1 + k];
-    ids[k] = id;
-    tj[k] = (unsigned char)(in.tmap ? in.tmap[id] : md.type_of(id));
-  }
-  // angular parameters of every (class, channel), fetched while the neighbour row is still in flight
-  for (int idx = tid; idx < md.ncls * Fa; idx += NT) {
-    const T ee = e3[idx];
-    const T* al = a3 + idx * 3;
-    T4 pa;
-    pa.x = al[0]; pa.y = al[1]; pa.z = al[2]; pa.w = al[2] * SC;
-    T2 pb;
-    pb.x = T(0); pb.y = T(0);
-    // the factor that comes from the preceding kernel (netderiv, dL/dAF) is applied after chain_wait() below
-    pb.x = (MODE == MODE_FORCE) ? T(0.25) * ee : T(0.5) * ee;
-    pall[idx] = pa;
-    pball[idx] = pb;
-    eflag[idx] = ee != T(0);
-  }
-  if (MODE != MODE_FORCE)
-    for (int q = tid; q < NACC; q += NT) acc[q] = T(0);
-  if (MODE == MODE_FORCE)
-    for (int q = tid; q < 3 * nr; q += NT) xtra[q] = T(0);
-  gsync<WPA>();
-  SWEEP_TICK(0)
-  // per-species lists of the neighbours in sorted order, built by warp 0; the angular neighbours (the
-  // first m of the row) are a prefix of every list
-  const unsigned lt = (1u << lane) - 1u;
-  if (warp == 0) {
-#pragma unroll
-    for (int t2 = 0; t2 < STAFB_MAX_TYPES; t2++) {
-      if (t2 < nt) {
-        int c2 = 0, ca = 0;
-        for (int k0 = 0; k0 < n; k0 += 32) {
-          const int k = k0 + lane;
-          const bool p = (k < n) && (tj[k] == t2);
-          const unsigned bal = __ballot_sync(0xffffffffu, p);
-          if (p) lst[t2 * nr + c2 + __popc(bal & lt)] = (unsigned char)k;
-          c2 += __popc(bal);
-          ca += __popc(__ballot_sync(0xffffffffu, p && k < m));
-        }
-        if (lane == 0) { cnts[t2] = ca; cnts[STAFB_MAX_TYPES + t2] = c2; }
-      }
-    }
-  }
-  // Everything above read only what is at least two kernels old (neighbour rows, theta, emb); netderiv, dL/dF
-  // and the zeroed outputs below belong to the preceding kernels.
-  chain_wait();
-  if (!IS_AF) {
-    for (int idx = tid; idx < md.ncls * Fa; idx += NT) {  // same thread as the fill above
-      const T cin = chrow[Fr + idx % Fa];
-      T2 pb = pball[idx];
-      if (MODE == MODE_FGRAD) pb.y = cin; else pb.x *= cin;
-      pball[idx] = pb;
-    }
-  }
-  T fix = T(0), fiy = T(0), fiz = T(0);  // FORCE: force on the central atom
-  if (MODE == MODE_FGRAD) {
-    // dF_k = Fbar_k - Fbar_i and its projection on the unit vector
-    const T* fb = fbar + (size_t)b * in.nall * 3;
-    const T fx = fb[i * 3], fy = fb[i * 3 + 1], fz = fb[i * 3 + 2];
-    for (int k = tid; k < n; k += NT) {
-      const int id = ids[k];
-      const T dx = fb[id * 3] - fx, dy = fb[id * 3 + 1] - fy, dz = fb[id * 3 + 2] - fz;
-      xtra[k * 4 + 0] = dx; xtra[k * 4 + 1] = dy; xtra[k * 4 + 2] = dz;
-      xtra[k * 4 + 3] = dx * P0[k].x + dy * P0[k].y + dz * P0[k].z;
-    }
-  }
-  gsync<WPA>();
-  int cnt[STAFB_MAX_TYPES];
-#pragma unroll
-  for (int t2 = 0; t2 < STAFB_MAX_TYPES; t2++) cnt[t2] = (t2 < nt) ? cnts[t2] : 0;
-
-  SWEEP_TICK(1)
-  // ------------------------------------------------------------------ radial part
-  if (MODE == MODE_FORCE) {
-    for (int k = tid; k < n; k += NT) {
-      const int tk = tj[k];
-      const T dk = P1[k].z;
-      T w = T(0);
-      for (int c = 0; c < Fr; c++) {
-        const T ch = e2[Fr * tk + c];
-        if (ch == T(0)) continue;
-        const T al = a2[Fr * tk + c];
-        w += chrow[c] * (T(0.5) * ch * Ex<T>::f(al * SC * dk) * (T(1) + al * dk));
-      }
-      const T g = w * P1[k].w;
-      const T gx = g * P0[k].x, gy = g * P0[k].y, gz = g * P0[k].z;
-      atomicAdd(&xtra[k * 3 + 0], gx);
-      atomicAdd(&xtra[k * 3 + 1], gy);
-      atomicAdd(&xtra[k * 3 + 2], gz);
-      fix -= gx; fiy -= gy; fiz -= gz;
-    }
-  } else {
-    // AF / AFV / FGRAD / AFGRAD: one thread per (neighbour species q, channel c) walks the neighbour row,
-    // so the sums over neighbours need no cross-lane reduction; the per-species partial sums of a channel
-    // are combined through rsum[].  AF, AFV: fingerprints; FGRAD: gradnet; all but AF: alpha2b terms.
-    const int nqc = nt * Fr;
-    for (int L0 = 0; L0 < nqc; L0 += NT) {
-      const int Lq = L0 + tid;
-      if (Lq < nqc) {
-        const int q = Lq / Fr, c = Lq - q * Fr;
-        const T ch = e2[Lq];
-        T gn = T(0), ga = T(0);
-        if (ch != T(0)) {
-          const T al = a2[Lq], als = al * SC;
-          const T cin = (IS_AF) ? T(1) : chrow[c];  // FGRAD: netderiv ; AFGRAD: dL/dAF
-          const unsigned char* lq = lst + q * nr;
-          const int nq = cnts[STAFB_MAX_TYPES + q];
-#pragma unroll 2
-          for (int r = 0; r < nq; r++) {
-            const int k = lq[r];
-            const T dk = P1[k].z;
-            const T ex = Ex<T>::f(als * dk);
-            if (MODE == MODE_FGRAD) {
-              const T qq = T(0.5) * P1[k].w * xtra[k * 4 + 3];
-              gn += qq * ex * (T(1) + al * dk);
-              ga += qq * ex * dk * (T(2) + al * dk);
-            } else {
-              gn += dk * ex;
-              ga += ex * dk * dk;
-            }
-          }
-          gn *= ch;
-          ga *= cin * ch;
-        }
-        rsum[q * md.Frmax + c] = gn;
-        if (MODE != MODE_AF) acc[ACC_A2 + q * md.Frmax + c] = ga;
-      }
-    }
-    if (MODE != MODE_AFGRAD) {
-      gsync<WPA>();
-      for (int c = tid; c < Fr; c += NT) {
-        T v = T(0);
-        for (int q = 0; q < nt; q++) v += rsum[q * md.Frmax + c];
-        out[gi * Fmax + c] = v;
-      }
-    }
-  }
-
-  SWEEP_TICK(2)
-  // ------------------------------------------------------------------ angular part
-  for (int ta = 0; ta < nt; ta++) {
-    for (int tb = ta; tb < nt; tb++) {
-      const int s = ta + tb;
-      int na_ = 0, nb_ = 0;
-#pragma unroll
-      for (int q = 0; q < STAFB_MAX_TYPES; q++) {
-        if (q == ta) na_ = cnt[q];
-        if (q == tb) nb_ = cnt[q];
-      }
-      const bool same = (ta == tb);
-      const int np = same ? na_ * (na_ - 1) / 2 : na_ * nb_;
-      if (np <= 0 || s >= md.ncls) continue;
-      const unsigned char* la = lst + ta * nr;
-      const unsigned char* lb = lst + tb * nr;
-      // active channels of this class (every warp counts, warp 0 writes the list)
-      int nact = 0;
-      for (int c0 = 0; c0 < Fa; c0 += 32) {
-        const int c = c0 + lane;
-        const bool p = (c < Fa) && eflag[s * Fa + c];
-        const unsigned bal = __ballot_sync(0xffffffffu, p);
-        if (p && warp == 0) actl[nact + __popc(bal & lt)] = (unsigned char)c;
-        nact += __popc(bal);
-      }
-      for (int c0 = 0; c0 < nact; c0 += MAXCH) {
-        const int nch = (nact - c0) < MAXCH ? (nact - c0) : MAXCH;
-        gsync<WPA>();  // actl visible; previous chunk's readers of chp/tab/red are done
-        const int nchp = (nch + 1) >> 1;
-        if (tid < nchp) {
-          const int ca = actl[c0 + 2 * tid];
-          const T4 pa0 = pall[s * Fa + ca];
-          const T2 pb0 = pball[s * Fa + ca];
-          T4 pa1;
-          T2 pb1;
-          pa1.x = pa1.y = pa1.z = pa1.w = T(0);  // an odd channel count is padded with an all-zero channel
-          pb1.x = pb1.y = T(0);
-          if (2 * tid + 1 < nch) {
-            const int cb = actl[c0 + 2 * tid + 1];
-            pa1 = pall[s * Fa + cb];
-            pb1 = pball[s * Fa + cb];
-          }
-          T4 q;
-          q.x = pa0.x; q.y = pa1.x; q.z = pa0.y; q.w = pa1.y;
-          chq[tid] = q;
-          q.x = pa0.z; q.y = pa1.z; q.z = pa0.w; q.w = pa1.w;
-          chr[tid] = q;
-          q.x = pb0.x; q.y = pb1.x; q.z = pb0.y; q.w = pb1.y;
-          chs[tid] = q;
-        }
-        gsync<WPA>();
-        // tables exp(a1*fc_k), exp(a2*fc_k) for the neighbours of the two species
-        const int nu = same ? na_ : na_ + nb_;
-        for (int r = tid; r < nu; r += NT) {
-          const int k = (r < na_) ? la[r] : lb[r - na_];
-          const T fck = P0[k].w * SC;
-          const T2 f2 = mk2(fck, fck);
-          // all channel pairs of one neighbour in flight together: independent multiply -> exp2 -> store chains
-#pragma unroll
-          for (int lp = 0; lp < MAXP; lp++) {
-            if (lp < nchp) {
-              const T4 q = chq[lp];
-              const T2 a = p_ex(p_mul(mk2(q.x, q.y), f2)), b = p_ex(p_mul(mk2(q.z, q.w), f2));
-              T4 v;
-              v.x = a.x; v.y = a.y; v.z = b.x; v.w = b.y;
-              tab4[lp * nr + k] = v;
-            }
-          }
-        }
-        gsync<WPA>();
-        SWEEP_TICK(3)
-
-        if (MODE == MODE_FORCE) {
-          // ordered pairs (owner j, partner k): each thread takes a contiguous run of the row-major
-          // list, keeps the owner's data and its force accumulator in registers and flushes when the
-          // row changes.  Two passes when the two species differ (owners of ta, then owners of tb).
-          const int npass = same ? 1 : 2;
-          for (int pass = 0; pass < npass; pass++) {
-            const unsigned char* lo = pass == 0 ? la : lb;
-            const unsigned char* lp = pass == 0 ? lb : la;
-            const int no = pass == 0 ? na_ : nb_;
-            const int npt = same ? na_ - 1 : (pass == 0 ? nb_ : na_);
-            const int E = no * npt;
-            const int cchunk = (E + NT - 1) / NT;
-            int e0 = tid * cchunk, e1 = e0 + cchunk;
-            if (e1 > E) e1 = E;
-            if (e0 < e1) {
-              int ja = e0 / npt, kb = e0 - ja * npt;
-              int j = lo[ja];
-              T4 uj = P0[j];
-              T rinvj = P1[j].x, gfcj = P1[j].y;
-              T4 Aj[MAXP];
-#pragma unroll
-              for (int lp = 0; lp < MAXP; lp++)
-                if (lp < nchp) Aj[lp] = tab4[lp * nr + j];
-              T ax = T(0), ay = T(0), az = T(0), as = T(0);
-              const T2 one2 = mk2(T(1), T(1));
-              for (int e = e0; e < e1; e++) {
-                const int kk = (same && kb >= ja) ? kb + 1 : kb;
-                const int k = lp[kk];
-                const T4 uk = P0[k];
-                const T cs = uj.x * uk.x + uj.y * uk.y + uj.z * uk.z;
-                const T half = T(0.5) * (cs + T(1));
-                const T tt = half * uj.w * uk.w;
-                const T2 tt2 = mk2(tt, tt);
-                T2 D2 = mk2(T(0), T(0)), BJ2 = mk2(T(0), T(0));
-#pragma unroll
-                for (int lp = 0; lp < MAXP; lp++) {
-                  if (lp < nchp) {
-                    const T4 B = tab4[lp * nr + k], cq = chq[lp], cr = chr[lp], cs4 = chs[lp];
-                    const T2 S1 = p_mul(mk2(Aj[lp].z, Aj[lp].w), mk2(B.x, B.y));  // exp(a2*sj + a1*sk)
-                    const T2 S2 = p_mul(mk2(Aj[lp].x, Aj[lp].y), mk2(B.z, B.w));  // exp(a1*sj + a2*sk)
-                    const T2 ev = p_mul(mk2(cs4.x, cs4.y), p_ex(p_mul(mk2(cr.z, cr.w), tt2)));
-                    D2 = p_fma(p_mul(ev, p_fma(mk2(cr.x, cr.y), tt2, one2)), p_add(S1, S2), D2);
-                    BJ2 = p_fma(p_mul(ev, tt2), p_fma(mk2(cq.x, cq.y), S2, p_mul(mk2(cq.z, cq.w), S1)), BJ2);
-                  }
-                }
-                const T D = D2.x + D2.y, BJ = BJ2.x + BJ2.y;
-                // f_ij = cjk*u_k + cjj*u_j
-                const T cjk = D * T(0.5) * uj.w * uk.w * rinvj;
-                ax += cjk * uk.x; ay += cjk * uk.y; az += cjk * uk.z;
-                as += -cs * cjk + gfcj * (D * half * uk.w + BJ);
-                kb++;
-                if (kb == npt || e + 1 == e1) {
-                  const T fx = ax + as * uj.x, fy = ay + as * uj.y, fz = az + as * uj.z;
-                  atomicAdd(&xtra[j * 3 + 0], fx);
-                  atomicAdd(&xtra[j * 3 + 1], fy);
-                  atomicAdd(&xtra[j * 3 + 2], fz);
-                  fix -= fx; fiy -= fy; fiz -= fz;
-                  ax = ay = az = as = T(0);
-                  if (kb == npt && e + 1 < e1) {
-                    kb = 0;
-                    ja++;
-                    j = lo[ja];
-                    uj = P0[j];
-                    rinvj = P1[j].x;
-                    gfcj = P1[j].y;
-#pragma unroll
-                    for (int lp = 0; lp < MAXP; lp++)
-                      if (lp < nchp) Aj[lp] = tab4[lp * nr + j];
-                  }
-                }
-              }
-            }
-          }
-        } else {
-          T2 r0[MAXP], r1[MAXP], r2[MAXP], r3[MAXP];
-#pragma unroll
-          for (int lp = 0; lp < MAXP; lp++) r0[lp] = r1[lp] = r2[lp] = r3[lp] = mk2(T(0), T(0));
-          const T2 one2 = mk2(T(1), T(1)), half2 = mk2(T(0.5), T(0.5)), two2 = mk2(T(2), T(2));
-          PairStep ps;
-          ps.ja = ps.kb = 0;
-          const int qst = same ? 0 : NT / nb_, rst = same ? 0 : NT - qst * nb_;
-          if (tid < np) {
-            if (same) ps.init_tri(tid, na_); else ps.init_rect(tid, nb_);
-          }
-#pragma unroll(PAIR_UNROLL)
-          for (int p = tid; p < np; p += NT) {
-            const int j = la[ps.ja], k = lb[ps.kb];
-            if (same) ps.step_tri(na_, NT); else ps.step_rect(nb_, qst, rst);
-            const T4 uj = P0[j], uk = P0[k];
-            const T fcj = uj.w, fck = uk.w;
-            const T cs = uj.x * uk.x + uj.y * uk.y + uj.z * uk.z;
-            const T half = T(0.5) * (cs + T(1));
-            const T tt = half * fcj * fck;
-            T Q = T(0), Pj = T(0), Pk = T(0);
-            if (MODE == MODE_FGRAD) {
-              const T4 pj = P1[j], pk = P1[k];
-              const T hf = T(0.5) * fcj * fck;
-              const T ajk = hf * pj.x, akj = hf * pk.x;
-              const T bjk = -cs * ajk + half * pj.y * fck;
-              const T bkj = -cs * akj + half * pk.y * fcj;
-              const T4 dFj = *reinterpret_cast<const T4*>(xtra + j * 4);
-              const T4 dFk = *reinterpret_cast<const T4*>(xtra + k * 4);
-              const T djuk = dFj.x * uk.x + dFj.y * uk.y + dFj.z * uk.z;
-              const T dkuj = dFk.x * uj.x + dFk.y * uj.y + dFk.z * uj.z;
-              Q = ajk * djuk + bjk * dFj.w + akj * dkuj + bkj * dFk.w;
-              Pj = pj.y * dFj.w;
-              Pk = pk.y * dFk.w;
-            }
-            const T2 tt2 = mk2(tt, tt), fcj2 = mk2(fcj, fcj), fck2 = mk2(fck, fck);
-            const T2 Q2 = mk2(Q, Q), Pj2 = mk2(Pj, Pj), Pk2 = mk2(Pk, Pk);
-#pragma unroll
-            for (int lp = 0; lp < MAXP; lp++) {
-              if (lp < nchp) {
-                const T4 A = tab4[lp * nr + j], B = tab4[lp * nr + k], cr = chr[lp];
-                const T2 S1 = p_mul(mk2(A.z, A.w), mk2(B.x, B.y));  // exp(a2*sj + a1*sk)
-                const T2 S2 = p_mul(mk2(A.x, A.y), mk2(B.z, B.w));  // exp(a1*sj + a2*sk)
-                const T2 eb = p_ex(p_mul(mk2(cr.z, cr.w), tt2));
-                const T2 ss = p_add(S1, S2);
-                if (IS_AF || MODE == MODE_AFGRAD) {
-                  const T2 cm = p_mul(eb, tt2);
-                  if (IS_AF) r0[lp] = p_fma(cm, ss, r0[lp]);  // the channel coefficient is applied after the reduction
-                  if (HAS_V) {
-                    r1[lp] = p_fma(cm, p_fma(S2, fcj2, p_mul(S1, fck2)), r1[lp]);
-                    r2[lp] = p_fma(cm, p_fma(S2, fck2, p_mul(S1, fcj2)), r2[lp]);
-                    r3[lp] = p_fma(p_mul(cm, tt2), ss, r3[lp]);
-                  }
-                } else {  // FGRAD
-                  const T4 cq = chq[lp];
-                  const T2 al1 = mk2(cq.x, cq.y), al2 = mk2(cq.z, cq.w), be = mk2(cr.x, cr.y);
-                  const T2 opb = p_fma(be, tt2, one2);
-                  const T2 et = p_mul(p_mul(eb, half2), tt2);   // eb * 0.5 * tt
-                  const T2 eo = p_mul(p_mul(eb, opb), half2);   // eb * (1 + be*tt) * 0.5
-                  const T2 a1S1 = p_mul(al1, S1), a1S2 = p_mul(al1, S2), a2S1 = p_mul(al2, S1), a2S2 = p_mul(al2, S2);
-                  const T2 Bj = p_mul(p_add(a1S2, a2S1), et), Bk = p_mul(p_add(a1S1, a2S2), et);
-                  const T2 eoQ = p_mul(eo, Q2);
-                  r0[lp] = p_fma(eoQ, ss, p_fma(Bj, Pj2, p_fma(Bk, Pk2, r0[lp])));
-                  const T2 a1j = p_mul(p_fma(a1S2, fcj2, p_fma(a2S1, fck2, S2)), et);
-                  const T2 a2j = p_mul(p_fma(a2S1, fcj2, p_fma(a1S2, fck2, S1)), et);
-                  const T2 a1k = p_mul(p_fma(a1S1, fck2, p_fma(a2S2, fcj2, S1)), et);
-                  const T2 a2k = p_mul(p_fma(a2S2, fck2, p_fma(a1S1, fcj2, S2)), et);
-                  r1[lp] = p_fma(eoQ, p_fma(S1, fck2, p_mul(S2, fcj2)), p_fma(a1j, Pj2, p_fma(a1k, Pk2, r1[lp])));
-                  r2[lp] = p_fma(eoQ, p_fma(S1, fcj2, p_mul(S2, fck2)), p_fma(a2j, Pj2, p_fma(a2k, Pk2, r2[lp])));
-                  // eb*tt*(2 + be*tt)*ss*0.5*Q + tt*(Bj*Pj + Bk*Pk)
-                  const T2 c3 = p_mul(p_mul(p_mul(eb, tt2), p_fma(be, tt2, two2)), p_mul(half2, Q2));
-                  r3[lp] = p_fma(c3, ss, p_fma(tt2, p_fma(Bj, Pj2, p_mul(Bk, Pk2)), r3[lp]));
-                }
-              }
-            }
-          }
-          SWEEP_TICK(4)
-          // per-warp sums -> red[warp][4*l + v]; then one thread per value combines the warps
-          // transposing butterfly: 4*MAXCH (or fewer) per-lane values are summed over the warp with one
-          // shuffle per surviving value and step instead of five per value
-          if (MODE == MODE_AF) {
-            T v[MAXCH];
-#pragma unroll
-            for (int lp = 0; lp < MAXP; lp++) { v[2 * lp] = r0[lp].x; v[2 * lp + 1] = r0[lp].y; }
-            const T tot = multi_reduce<T, MAXCH>(v, lane);  // lane holds channel lane >> 2
-            if ((lane & 3) == 0) red[warp * 4 * MAXCH + 4 * (lane >> 2)] = tot;
-          } else if (nch <= MAXCH / 2) {
-            T v[2 * MAXCH];
-#pragma unroll
-            for (int lp = 0; lp < MAXP / 2; lp++) {
-              v[8 * lp] = r0[lp].x; v[8 * lp + 1] = r1[lp].x; v[8 * lp + 2] = r2[lp].x; v[8 * lp + 3] = r3[lp].x;
-              v[8 * lp + 4] = r0[lp].y; v[8 * lp + 5] = r1[lp].y; v[8 * lp + 6] = r2[lp].y; v[8 * lp + 7] = r3[lp].y;
-            }
-            const T tot = multi_reduce<T, 2 * MAXCH>(v, lane);  // lane holds value lane >> 1
-            if ((lane & 1) == 0) red[warp * 4 * MAXCH + (lane >> 1)] = tot;
-          } else {
-            T v[4 * MAXCH];
-#pragma unroll
-            for (int lp = 0; lp < MAXP; lp++) {
-              v[8 * lp] = r0[lp].x; v[8 * lp + 1] = r1[lp].x; v[8 * lp + 2] = r2[lp].x; v[8 * lp + 3] = r3[lp].x;
-              v[8 * lp + 4] = r0[lp].y; v[8 * lp + 5] = r1[lp].y; v[8 * lp + 6] = r2[lp].y; v[8 * lp + 7] = r3[lp].y;
-            }
-            const T tot = multi_reduce<T, 4 * MAXCH>(v, lane);  // lane holds value lane
-            red[warp * 4 * MAXCH + lane] = tot;
-          }
-          gsync<WPA>();
-          if (tid < 4 * nch) {
-            const int l = tid >> 2, v = tid & 3;
-            const bool use = (v == 0) ? (IS_AF || MODE == MODE_FGRAD) : (HAS_V || MODE == MODE_FGRAD);
-            if (use) {
-              T sum = T(0);
-#pragma unroll
-              for (int w = 0; w < WPA; w++) sum += red[w * 4 * MAXCH + tid];
-              const int c = actl[c0 + l];
-              const T4 cs4 = chs[l >> 1];
-              const T cf = (l & 1) ? cs4.y : cs4.x;
-              if (v == 0) acc[ACC_GN + c] += cf * sum;
-              else {
-                const T hn = MODE == MODE_FGRAD ? cf * ((l & 1) ? cs4.w : cs4.z) : cf;
-                acc[ACC_A3 + (s * md.Famax + c) * 3 + (v - 1)] += hn * sum;
-              }
-            }
-          }
-        }
-        SWEEP_TICK(MODE == MODE_FORCE ? 4 : 5)
-      }
-      gsync<WPA>();  // before the next class rewrites actl
-    }
-  }
-  gsync<WPA>();
-  SWEEP_TICK(5)
-
-  // ------------------------------------------------------------------ write-back
-  if (IS_AF) {
-    for (int c = tid; c < Fa; c += NT) out[gi * Fmax + Fr + c] = acc[ACC_GN + c];
-    for (int c = Fr + Fa + tid; c < Fmax; c += NT) out[gi * Fmax + c] = T(0);
-    if (MODE == MODE_AFV) {
-      // d(AF)/d(alpha) of this atom, in the order alpha2b[nt,Fr] | alpha3b[C,3Fa] of the parameter block
-      T* vr = vout + gi * nv;
-      const int n2 = nt * Fr, nq = n2 + md.C * 3 * Fa;
-      for (int q = tid; q < nq; q += NT) {
-        T v;
-        if (q < n2) v = acc[ACC_A2 + (q / Fr) * md.Frmax + (q % Fr)];
-        else {
-          const int r = q - n2, sc = r / 3, comp = r - sc * 3, s = sc / Fa, c = sc - s * Fa;
-          v = acc[ACC_A3 + (s * md.Famax + c) * 3 + comp];
-        }
-        vr[q] = v;
-      }
-    }
-  } else if (MODE == MODE_FORCE) {
-    T* fb = out + (size_t)b * in.nall * 3;
-    for (int q = tid; q < 3 * n; q += NT) atomicAdd(fb + (size_t)ids[q / 3] * 3 + (q % 3), xtra[q]);
-    fix = warp_sum(fix); fiy = warp_sum(fiy); fiz = warp_sum(fiz);
-    if (lane == 0) {
-      atomicAdd(fb + (size_t)i * 3 + 0, fix);
-      atomicAdd(fb + (size_t)i * 3 + 1, fiy);
-      atomicAdd(fb + (size_t)i * 3 + 2, fiz);
-    }
-    if (VIR) {
-      // W_ab -= g_a * r_b with g the force this centre puts on neighbour k and r = r_i - r_k
-      // (force/rad/reforce.cu.cc:174-287, force/ang/reforce.cu.cc:269-457 of the reference)
-      // one row of W at a time keeps the epilogue's register footprint below the main loop's
-#pragma unroll 1
-      for (int a = 0; a < 3; a++) {
-        T w0 = T(0), w1 = T(0), w2 = T(0);
-        for (int k = tid; k < n; k += NT) {
-          const T4 u = P0[k];
-          const T g = xtra[k * 3 + a] / P1[k].x;  // g_a * |r|
-          w0 -= g * u.x; w1 -= g * u.y; w2 -= g * u.z;
-        }
-        w0 = warp_sum(w0); w1 = warp_sum(w1); w2 = warp_sum(w2);
-        if (lane == 0) {
-          atomicAdd(vir + (size_t)b * 9 + a * 3 + 0, (double)w0);
-          atomicAdd(vir + (size_t)b * 9 + a * 3 + 1, (double)w1);
-          atomicAdd(vir + (size_t)b * 9 + a * 3 + 2, (double)w2);
-        }
-      }
-    }
-  } else {
-    if (MODE == MODE_FGRAD) {
-      for (int c = tid; c < Fa; c += NT) out[gi * Fmax + Fr + c] = acc[ACC_GN + c];
-      for (int c = Fr + Fa + tid; c < Fmax; c += NT) out[gi * Fmax + c] = T(0);
-    }
-    if (grad == nullptr) {
-      SWEEP_TICK(6)
-      return;
-    }
-    T* g2 = grad + md.off_a2[t];
-    for (int q = tid; q < nt * Fr; q += NT) {
-      const T v = acc[ACC_A2 + (q / Fr) * md.Frmax + (q % Fr)];
-      if (v != T(0)) atomicAdd(g2 + q, v);
-    }
-    T* g3 = grad + md.off_a3[t];
-    for (int q = tid; q < md.C * 3 * Fa; q += NT) {
-      const int sc = q / 3, comp = q - sc * 3, s = sc / Fa, c = sc - s * Fa;
-      const T v = acc[ACC_A3 + (s * md.Famax + c) * 3 + comp];
-      if (v != T(0)) atomicAdd(g3 + q, v);
-    }
-  }
-  SWEEP_TICK(6)
-}
-
-#ifdef STAFB_SWEEP_CLOCKS
-}  // namespace stafb
-extern "C" int stafb_sweep_clocks(unsigned long long* out40) {
-  if (cudaMemcpyFromSymbol(out40, stafb::g_sweep_clk, sizeof(unsigned long long) * 40) != cudaSuccess) return 1;
-  unsigned long long z[40] = {0};
-  return cudaMemcpyToSymbol(stafb::g_sweep_clk, z, sizeof(z)) == cudaSuccess ? 0 : 1;
-}
-namespace stafb {
-#endif
+#include "sweep.cuh"
 
 // ---------------------------------------------------------------------------- MLP head
 #include "mlp.cuh"
@@ -836,11 +95,23 @@ __device__ __forceinline__ T huber_d(T e) { return e > T(1) ? T(1) : (e < T(-1) 
 
 // Start-of-evaluation housekeeping in one launch: zero-fills up to three buffers (sizes in bytes, multiples of
 // 4) and writes the packed, padded copy of the Dense layers that the MLP kernels stage (layout: mlp.cuh).
+// It also packs the per-species parameter blocks of the sweeps (sweep.cuh): one warp per (species, class).
 template <class T>
-__global__ void k_prep(ModelDev md, const T* __restrict__ theta, T* __restrict__ wpack, int wstride, void* a,
+__global__ void k_prep(ModelDev md, const T* __restrict__ theta, const T* __restrict__ emb, T* __restrict__ wpack,
+                       int wstride, unsigned char* __restrict__ spar, int spar_stride, SparLayout sl, void* a,
                        size_t na, void* b, size_t nb, void* c, size_t nc) {
   chain_wait();
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  {
+    const int gw = (int)(tid >> 5), lane = threadIdx.x & 31;
+    if (gw < md.nt * md.ncls) {
+      const int t = gw / md.ncls, s = gw - t * md.ncls;
+      spar_fill_class<T>(md, sl, spar + (size_t)t * spar_stride, t, s, theta, emb, lane);
+    }
+    for (int t = 0; t < md.nt; t++)
+      for (size_t idx = tid; idx < (size_t)md.nt * md.Fr[t]; idx += st)
+        spar_fill_radial<T>(md, sl, spar + (size_t)t * spar_stride, t, theta, emb, (int)idx);
+  }
   for (size_t q = tid; q < na / 4; q += st) reinterpret_cast<int*>(a)[q] = 0;
   for (size_t q = tid; q < nb / 4; q += st) reinterpret_cast<int*>(b)[q] = 0;
   for (size_t q = tid; q < nc / 4; q += st) reinterpret_cast<int*>(c)[q] = 0;
@@ -1019,11 +290,13 @@ struct stafb_model {
   int stage;  // Dense layers in shared memory: 2 all at kernel start, 1 one at a time, 0 none
   size_t mlp_fwd_smem, mlp_bwd_smem;
   // scratch for max_batch frames
-  void *rad, *d3s, *af, *nd, *acts, *e_atom, *force, *fbar, *ebar, *gradnet, *gaf, *energy, *vrow;
+  void *rows, *af, *nd, *acts, *e_atom, *force, *fbar, *ebar, *gradnet, *gaf, *energy, *vrow;
+  int row_stride;      // bytes per neighbour record (common.cuh)
+  unsigned char* spar;  // per-species parameter blocks of the sweeps, rewritten by k_prep at every evaluation
+  SparLayout sl;
   void* wpack;  // packed, padded Dense layers of every species (k_prep), wstride elements per species
   int wstride;
   int nv;  // row length of vrow: nt*Frmax + C*3*Famax
-  int *im2, *ntr;
   double* losses_d;  // [0..4] the four losses + the done-counter of k_loss; [8 + b] sum of the atomic energies of
                      // frame b (accumulated by the MLP kernel); [8 + max_batch + 9*b + c] virial accumulators
   // staging for the *_host entry points
@@ -1047,8 +320,7 @@ struct stafb_model {
   // this step's sweeps still read theirs.  Allocated on first use.
   struct NlSet {
     stafb_ctx* ctx;
-    void *rad, *d3s;
-    int *im2, *ntr;
+    void* rows;
     cudaEvent_t ready;
     int nf;  // frames the set currently describes (0: nothing)
   } nl[2];
@@ -1153,10 +425,12 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   const size_t es = m->es, A = (size_t)c->max_batch * c->n_max, nr = c->nr;
   m->cap_atoms = c->n_max;
   const size_t mlp_blocks = A / (8 * m->apt) + d.nt + 1;
-  STAFB_CUDA_OK(cudaMalloc(&m->rad, es * A * nr));
-  STAFB_CUDA_OK(cudaMalloc(&m->d3s, es * A * nr));
-  STAFB_CUDA_OK(cudaMalloc((void**)&m->im2, sizeof(int) * A * (nr + 1)));
-  STAFB_CUDA_OK(cudaMalloc((void**)&m->ntr, sizeof(int) * A));
+  m->row_stride = row_stride_bytes((int)nr, (int)es);
+  STAFB_CUDA_OK(cudaMalloc(&m->rows, A * (size_t)m->row_stride));
+  STAFB_CUDA_OK(cudaMemset(m->rows, 0, A * (size_t)m->row_stride));
+  m->sl = es == 4 ? spar_layout<float>(d) : spar_layout<double>(d);
+  STAFB_CUDA_OK(cudaMalloc((void**)&m->spar, (size_t)d.nt * m->sl.total));
+  STAFB_CUDA_OK(cudaMemset(m->spar, 0, (size_t)d.nt * m->sl.total));
   STAFB_CUDA_OK(cudaMalloc(&m->af, es * A * d.Fmax));
   STAFB_CUDA_OK(cudaMalloc(&m->nd, es * A * d.Fmax));
   STAFB_CUDA_OK(cudaMalloc(&m->gradnet, es * A * d.Fmax));
@@ -1187,7 +461,7 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
 
 extern "C" void stafb_model_destroy(stafb_model* m) {
   if (!m) return;
-  void* ptrs[] = {m->rad, m->d3s, m->im2, m->ntr, m->af, m->nd, m->gradnet, m->gaf, m->acts, m->e_atom, m->force,
+  void* ptrs[] = {m->rows, m->spar, m->af, m->nd, m->gradnet, m->gaf, m->acts, m->e_atom, m->force,
                   m->fbar, m->ebar, m->energy, m->losses_d, m->vrow, m->wpack};
   for (void* p : ptrs) cudaFree(p);
   for (int k = 0; k < 3; k++) {
@@ -1199,7 +473,7 @@ extern "C" void stafb_model_destroy(stafb_model* m) {
   for (int k = 0; k < 2; k++) {
     if (m->nl_exec[k]) cudaGraphExecDestroy(m->nl_exec[k]);
     if (!m->nl[k].ctx) continue;
-    cudaFree(m->nl[k].rad); cudaFree(m->nl[k].d3s); cudaFree(m->nl[k].im2); cudaFree(m->nl[k].ntr);
+    cudaFree(m->nl[k].rows);
     cudaEventDestroy(m->nl[k].ready);
     stafb_destroy(m->nl[k].ctx);
   }
@@ -1247,36 +521,65 @@ static inline int device_slot() {
   return (d >= 0 && d < MAX_DEVICES) ? d : 0;
 }
 
-template <class T, int MODE, int SW_WPA = SweepWpa<MODE>::value>
-static int launch_sweep(stafb_model* m, cudaStream_t s, int nf, const SweepIn<T>& in, const T* theta, const T* emb,
-                        const T* chan_in, const T* fbar, T* out, T* grad, T* vout = nullptr, int nv = 0,
-                        double* vir = nullptr) {
+// what a sweep launch needs besides the model: the records of this evaluation and the per-call buffers
+template <class T>
+struct SweepCall {
+  const void* rows;
+  int nf, nall;
+  const T* chan_in;
+  const T* fbar;
+  T* out;
+  T* grad;
+  T* vout;
+  double* vir;
+  int* status;
+};
+
+template <class T, int MODE>
+static int launch_sweep(stafb_model* m, cudaStream_t s, const SweepCall<T>& call) {
   const ModelDev& d = m->md;
-  const int xt = MODE == MODE_FORCE ? 3 : (MODE == MODE_FGRAD ? 4 : 0);
-  const int nacc = d.Famax + d.nt * d.Frmax + d.C * 3 * d.Famax;
-  SweepLayout L = sweep_layout<T>(in.nr, d.nt, xt, nacc, d.Famax > 0 ? d.Famax : 1, SW_WPA,
-                                  d.nt * d.Frmax > 0 ? d.nt * d.Frmax : 1, d.ncls * d.Famax > 0 ? d.ncls * d.Famax : 1);
+  const int nr = m->ctx->nr;
+  const SweepSmem L = sweep_smem<T>(d, m->sl, nr, MODE);
   const size_t sm = (size_t)L.total;
   if (sm > m->smem_limit) return STAFB_ERR_CAPACITY;
-  static bool attr_dev[MAX_DEVICES] = {false};  // per instantiation (T, MODE, SW_WPA) and device
+  static bool attr_dev[MAX_DEVICES] = {false};  // per instantiation (T, MODE) and device
   bool& attr_done = attr_dev[device_slot()];
   if (sm > 48 * 1024 && !attr_done) {
-    STAFB_CUDA_OK(cudaFuncSetAttribute(k_sweep<T, MODE, SW_WPA, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    STAFB_CUDA_OK(cudaFuncSetAttribute(k_sweep<T, MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)m->smem_limit));
     if (MODE == MODE_FORCE)
-      STAFB_CUDA_OK(cudaFuncSetAttribute(k_sweep<T, MODE, SW_WPA, MODE == MODE_FORCE>,
+      STAFB_CUDA_OK(cudaFuncSetAttribute(k_sweep<T, MODE, MODE == MODE_FORCE>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)m->smem_limit));
     attr_done = true;
   }
-  const int blocks = nf * d.N;
-  if (MODE == MODE_FORCE && vir)
-    STAFB_CUDA_OK(launch_chained(k_sweep<T, MODE, SW_WPA, MODE == MODE_FORCE>, blocks, SW_WPA * 32, sm, s, d, in, L,
-                                 theta, emb, chan_in, fbar, out, grad, vout, nv, vir));
+  SweepArgs<T> a;
+  a.rows = static_cast<const unsigned char*>(call.rows);
+  a.row_stride = m->row_stride;
+  a.nr = nr; a.nf = call.nf; a.nall = call.nall;
+  a.spar = m->spar;
+  a.spar_stride = m->sl.total;
+  a.sl = m->sl;
+  a.chan_in = call.chan_in; a.fbar = call.fbar; a.out = call.out; a.grad = call.grad;
+  a.vout = call.vout; a.nv = m->nv; a.vir = call.vir; a.status = call.status;
+  const int blocks = call.nf * d.N;
+  if (MODE == MODE_FORCE && call.vir)
+    STAFB_CUDA_OK(launch_chained(k_sweep<T, MODE, MODE == MODE_FORCE>, blocks, 32, sm, s, d, a, L));
   else
-    STAFB_CUDA_OK(launch_chained(k_sweep<T, MODE, SW_WPA, false>, blocks, SW_WPA * 32, sm, s, d, in, L, theta, emb,
-                                 chan_in, fbar, out, grad, vout, nv, (double*)nullptr));
+    STAFB_CUDA_OK(launch_chained(k_sweep<T, MODE, false>, blocks, 32, sm, s, d, a, L));
   m->ctx->launches++;
   return STAFB_OK;
+}
+
+// where the neighbour kernels leave the records of a model's atoms
+static RowSink row_sink(const stafb_model* m, void* rows, const int* tmap) {
+  RowSink sk;
+  memset(&sk, 0, sizeof(sk));
+  sk.rows = rows;
+  sk.stride = m->row_stride;
+  sk.nt = m->md.nt;
+  for (int t = 0; t <= m->md.nt; t++) sk.shift[t] = m->md.shift[t];
+  sk.tmap = tmap;
+  return sk;
 }
 
 template <class T, int APT>
@@ -1344,35 +647,36 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
     if (c->timing && c->n_phase < 16) cudaEventRecord(c->ev[c->n_phase++], s);
   };
   mark();
-  T* rad = (T*)(pre ? pre->rad : m->rad); T* d3s = (T*)(pre ? pre->d3s : m->d3s);
-  int* im2 = pre ? pre->im2 : m->im2;
-  int* ntr = pre ? pre->ntr : m->ntr;
-  const stafb_ctx* cg = pre ? pre->ctx : c;  // owner of the vector rows and of the status word of this evaluation
+  void* rows = pre ? pre->rows : m->rows;
+  const stafb_ctx* cg = pre ? pre->ctx : c;  // owner of the status word the neighbour kernels of this evaluation used
   int rc = STAFB_OK;
-  if (pre)
+  if (pre) {
     c->launches = pre->ctx->launches;
-  else if (dom && dom->howmany)
-    rc = launch_rows_from_list<T>(c, s, pos, N, nall, dom->howmany, dom->with, rad, d3s, im2, ntr);
-  else
-    rc = launch_descriptors<T>(c, s, pos, box, nf, nall, rad, nullptr, d3s, im2, nullptr, nullptr, nullptr,
-                               nullptr, ntr, N);
+  } else {
+    const RowSink sk = row_sink(m, rows, dom ? dom->tmap : nullptr);
+    if (dom && dom->howmany)
+      rc = launch_rows_from_list<T>(c, s, pos, N, nall, dom->howmany, dom->with, &sk);
+    else
+      rc = launch_descriptors<T>(c, s, pos, box, nf, nall, (T*)nullptr, (T*)nullptr, (T*)nullptr, (int*)nullptr,
+                                 (int*)nullptr, (T*)nullptr, (T*)nullptr, (T*)nullptr, (int*)nullptr, N, &sk);
+  }
   if (rc != STAFB_OK) return rc;
   T* af = (T*)m->af; T* nd = (T*)m->nd; T* acts = (T*)m->acts; T* e_atom = (T*)m->e_atom;
   T* force = force_out ? force_out : (T*)m->force;
   T* energy = energy_out ? energy_out : (T*)m->energy;
   STAFB_CUDA_OK(launch_chained(
-      k_prep<T>, 64, 256, 0, s, d, theta, (T*)m->wpack, m->wstride, (void*)force, sizeof(T) * (size_t)nf * 3 * nall,
+      k_prep<T>, 64, 256, 0, s, d, theta, emb, (T*)m->wpack, m->wstride, m->spar, m->sl.total, m->sl, (void*)force,
+      sizeof(T) * (size_t)nf * 3 * nall,
       train ? (void*)grad : (void*)nullptr, train ? sizeof(T) * (size_t)m->n_params : (size_t)0, (void*)m->losses_d,
       sizeof(double) * (virial_out ? 8 + 10 * (size_t)c->max_batch : 8 + (size_t)c->max_batch)));
   c->launches++;
   mark();  // descriptors
-  SweepIn<T> in;
-  in.geom = (const T*)cg->geom; in.gsc = (const T*)cg->gsc; in.rad = rad; in.d3s = d3s; in.im2 = im2; in.ntr = ntr;
-  in.nf = nf; in.nr = c->nr;
-  in.tmap = dom ? dom->tmap : nullptr;
-  in.nall = nall;
-  rc = train ? launch_sweep<T, MODE_AFV>(m, s, nf, in, theta, emb, nullptr, nullptr, af, nullptr, (T*)m->vrow, m->nv)
-             : launch_sweep<T, MODE_AF>(m, s, nf, in, theta, emb, nullptr, nullptr, af, nullptr);
+  SweepCall<T> sc;
+  memset(&sc, 0, sizeof(sc));
+  sc.rows = rows; sc.nf = nf; sc.nall = nall; sc.status = cg->status_d;
+  sc.out = af;
+  sc.vout = train ? (T*)m->vrow : nullptr;
+  rc = train ? launch_sweep<T, MODE_AFV>(m, s, sc) : launch_sweep<T, MODE_AF>(m, s, sc);
   if (rc != STAFB_OK) return rc;
   mark();  // af_fwd
   rc = m->apt == 4 ? launch_mlp_fwd<T, 4>(m, s, nf, theta, af, acts, e_atom, nd)
@@ -1381,14 +685,8 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
   if (rc != STAFB_OK) return rc;
   mark();  // mlp_fwd
   double* vacc = virial_out ? m->losses_d + 8 + c->max_batch : nullptr;
-  // two warps per atom shorten the ordered-pair loop while the GPU is not full; once there are several blocks
-  // per warp slot, one warp per atom (no block barriers) has the higher throughput
-  static const long long one_warp_atoms =
-      getenv("STAFB_FORCE_WPA1_ATOMS") ? atoll(getenv("STAFB_FORCE_WPA1_ATOMS")) : 2048;
-  if ((long long)nf * N >= one_warp_atoms)
-    rc = launch_sweep<T, MODE_FORCE, 1>(m, s, nf, in, theta, emb, nd, nullptr, force, nullptr, nullptr, 0, vacc);
-  else
-    rc = launch_sweep<T, MODE_FORCE>(m, s, nf, in, theta, emb, nd, nullptr, force, nullptr, nullptr, 0, vacc);
+  sc.chan_in = nd; sc.out = force; sc.vout = nullptr; sc.vir = vacc;
+  rc = launch_sweep<T, MODE_FORCE>(m, s, sc);
   if (rc != STAFB_OK) return rc;
   mark();  // force
   {
@@ -1409,7 +707,8 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
   if (train) {
     T* gradnet = (T*)m->gradnet;
     T* gaf = (T*)m->gaf;
-    rc = launch_sweep<T, MODE_FGRAD>(m, s, nf, in, theta, emb, nd, (const T*)m->fbar, gradnet, grad);
+    sc.chan_in = nd; sc.fbar = (const T*)m->fbar; sc.out = gradnet; sc.grad = grad; sc.vir = nullptr;
+    rc = launch_sweep<T, MODE_FGRAD>(m, s, sc);
     if (rc != STAFB_OK) return rc;
     mark();  // force_grad
     rc = m->apt == 4 ? launch_mlp_bwd<T, 4>(m, s, nf, theta, af, acts, (const T*)m->ebar, gradnet, gaf, grad)
@@ -1492,10 +791,8 @@ static int ensure_nl(stafb_ctx* c, stafb_model* m, int slot) {
   int rc = stafb_create(&q.ctx, c->dtype, c->Rc, c->Rs, c->Ra, c->nr, c->na, c->n_max, c->max_batch);
   if (rc != STAFB_OK) { q.ctx = nullptr; return rc; }
   const size_t es = m->es, A = (size_t)c->max_batch * c->n_max, nr = c->nr;
-  STAFB_CUDA_OK(cudaMalloc(&q.rad, es * A * nr));
-  STAFB_CUDA_OK(cudaMalloc(&q.d3s, es * A * nr));
-  STAFB_CUDA_OK(cudaMalloc((void**)&q.im2, sizeof(int) * A * (nr + 1)));
-  STAFB_CUDA_OK(cudaMalloc((void**)&q.ntr, sizeof(int) * A));
+  STAFB_CUDA_OK(cudaMalloc(&q.rows, A * (size_t)m->row_stride));
+  STAFB_CUDA_OK(cudaMemset(q.rows, 0, A * (size_t)m->row_stride));
   STAFB_CUDA_OK(cudaEventCreateWithFlags(&q.ready, cudaEventDisableTiming));
   q.nf = 0;
   return STAFB_OK;
@@ -1511,12 +808,15 @@ extern "C" int stafb_descriptors_prefetch(stafb_ctx* c, stafb_model* m, void* st
   cudaStream_t s = (cudaStream_t)stream;
   const int N = m->md.N;
   q.ctx->launches = 0;
+  const RowSink sk = row_sink(m, q.rows, nullptr);
   if (c->dtype == STAFB_F32)
-    rc = launch_descriptors<float>(q.ctx, s, (const float*)pos, (const float*)box, nf, N, (float*)q.rad, nullptr,
-                                   (float*)q.d3s, q.im2, nullptr, nullptr, nullptr, nullptr, q.ntr, N);
+    rc = launch_descriptors<float>(q.ctx, s, (const float*)pos, (const float*)box, nf, N, (float*)nullptr,
+                                   (float*)nullptr, (float*)nullptr, (int*)nullptr, (int*)nullptr, (float*)nullptr,
+                                   (float*)nullptr, (float*)nullptr, (int*)nullptr, N, &sk);
   else
-    rc = launch_descriptors<double>(q.ctx, s, (const double*)pos, (const double*)box, nf, N, (double*)q.rad, nullptr,
-                                    (double*)q.d3s, q.im2, nullptr, nullptr, nullptr, nullptr, q.ntr, N);
+    rc = launch_descriptors<double>(q.ctx, s, (const double*)pos, (const double*)box, nf, N, (double*)nullptr,
+                                    (double*)nullptr, (double*)nullptr, (int*)nullptr, (int*)nullptr,
+                                    (double*)nullptr, (double*)nullptr, (double*)nullptr, (int*)nullptr, N, &sk);
   if (rc != STAFB_OK) return rc;
   q.nf = nf;
   STAFB_CUDA_OK(cudaGetLastError());

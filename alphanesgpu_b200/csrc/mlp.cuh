@@ -493,10 +493,18 @@ __global__ void __launch_bounds__(ML_THREADS)
     const int Fr = md.Fr[t], Fa = md.Fa[t], n2 = md.nt * Fr, nq = n2 + md.C * 3 * Fa;
     for (int q = threadIdx.x; q < nq; q += ML_THREADS) {
       const int ch = q < n2 ? (q % Fr) : Fr + ((q - n2) / 3) % Fa;
+      // position of parameter q in the rows the fingerprint sweep wrote: its accumulator layout
+      // alpha2b[nt,Frmax] | alpha3b[C,3*Famax] (equal to q when every species has the same channel counts)
+      int qa;
+      if (q < n2) qa = (q / Fr) * md.Frmax + (q % Fr);
+      else {
+        const int r = q - n2, sc = r / 3, s = sc / Fa;
+        qa = md.nt * md.Frmax + (s * md.Famax + (sc - s * Fa)) * 3 + (r - sc * 3);
+      }
       T g = T(0);
       for (int a = 0; a < TA; a++) {
         const long long gi = rows[a];
-        if (gi >= 0) g += V[ch * TAP + a] * vrow[gi * nv + q];
+        if (gi >= 0) g += V[ch * TAP + a] * vrow[gi * nv + qa];
       }
       if (g != T(0)) atomicAdd(grad + md.off_a2[t] + q, g);
     }

@@ -299,15 +299,22 @@ __device__ __forceinline__ void mic_vec(const FrameGeom<T>& g, T ax, T ay, T az,
   dz = g.box[5] * oz;
 }
 
+// What a fused sweep needs of one neighbour slot (the U and V entries of the record, common.cuh).
+template <class T>
+struct SlotVals {
+  T ux, uy, uz, fc, rinv, dfc, d, dd;
+};
+
 // One slot of a central atom's radial row (reforce.cu.cc:17-110) from the vector v = r_i - r_j: radial
 // descriptor, angular-support cutoff, their gradients, the neighbour id and the compact geometry the
-// fused sweeps read.  Slots past the neighbour count (valid == false) are zero-filled.
+// angular-descriptor kernel reads.  Slots past the neighbour count (valid == false) are zero-filled.  Every
+// output pointer may be null; `sv` always receives the slot's values for the record of the fused sweeps.
 template <class T>
 __device__ __forceinline__ void radial_slot(const CoreCoef<T>& cc, bool valid, int j, T vx, T vy, T vz, size_t base,
                                             int k, int nr, T* __restrict__ raddescr, T* __restrict__ des3bsupp,
                                             int* __restrict__ intmap2b, T* __restrict__ der2b,
                                             T* __restrict__ der3bsupp, T* __restrict__ geom, T* __restrict__ gsc,
-                                            int& nang) {
+                                            int& nang, SlotVals<T>& sv) {
   const T PI = PIc<T>();
   T rd = T(0), d3 = T(0), g2x = T(0), g2y = T(0), g2z = T(0), g3x = T(0), g3y = T(0), g3z = T(0);
   T dn = T(0), s2 = T(0), s3 = T(0);
@@ -342,8 +349,8 @@ __device__ __forceinline__ void radial_slot(const CoreCoef<T>& cc, bool valid, i
       g2z = pre * vz / dn;
     }
   }
-  raddescr[base * nr + k] = rd;
-  des3bsupp[base * nr + k] = d3;
+  if (raddescr) raddescr[base * nr + k] = rd;
+  if (des3bsupp) des3bsupp[base * nr + k] = d3;
   if (der2b) {
     der2b[(base * 3 + 0) * nr + k] = g2x;
     der2b[(base * 3 + 1) * nr + k] = g2y;
@@ -354,7 +361,7 @@ __device__ __forceinline__ void radial_slot(const CoreCoef<T>& cc, bool valid, i
     der3bsupp[(base * 3 + 1) * nr + k] = g3y;
     der3bsupp[(base * 3 + 2) * nr + k] = g3z;
   }
-  intmap2b[base * (nr + 1) + 1 + k] = valid ? j : 0;
+  if (intmap2b) intmap2b[base * (nr + 1) + 1 + k] = valid ? j : 0;
   if (geom) {
     typename Vec4<T>::type q;
     q.x = vx; q.y = vy; q.z = vz; q.w = dn;
@@ -365,6 +372,89 @@ __device__ __forceinline__ void radial_slot(const CoreCoef<T>& cc, bool valid, i
     typename Vec2<T>::type q;
     q.x = s2; q.y = s3;
     reinterpret_cast<typename Vec2<T>::type*>(gsc)[base * nr + k] = q;
+  }
+  const T inv = valid ? T(1) / dn : T(0);
+  sv.ux = vx * inv; sv.uy = vy * inv; sv.uz = vz * inv; sv.fc = d3;
+  sv.rinv = inv; sv.dfc = s3; sv.d = rd; sv.dd = s2;
+}
+
+__device__ __forceinline__ int sink_species(const RowSink& sk, int j) {
+  if (sk.tmap) return sk.tmap[j];
+  int t = 0;
+  while (t < sk.nt - 1 && j >= sk.shift[t + 1]) t++;
+  return t;
+}
+
+// Positions of a distance-sorted row in the species-grouped order of the record: slot k of species q goes to
+// (number of neighbours of species < q) + (number of species-q slots before k).  One warp; spos[k] receives
+// position | species << 16 for k < n, cnt[q] the neighbours per species.  ids[k] = neighbour of sorted slot k.
+__device__ __forceinline__ void group_by_species(const RowSink& sk, const int* ids, int n, int lane, int* spos,
+                                                 int (&cnt)[STAFB_MAX_TYPES]) {
+  const unsigned lt = (1u << lane) - 1u;
+#pragma unroll
+  for (int q = 0; q < STAFB_MAX_TYPES; q++) cnt[q] = 0;
+  for (int k0 = 0; k0 < n; k0 += 32) {
+    const int k = k0 + lane;
+    const int sp = (k < n) ? sink_species(sk, ids[k]) : -1;
+    int mine = 0;
+#pragma unroll
+    for (int q = 0; q < STAFB_MAX_TYPES; q++) {
+      const unsigned bal = __ballot_sync(0xffffffffu, sp == q);
+      if (sp == q) mine = cnt[q] + __popc(bal & lt);
+      cnt[q] += __popc(bal);
+    }
+    if (k < n) spos[k] = mine | (sp << 16);  // rank inside the species for now
+  }
+  __syncwarp();
+  int off[STAFB_MAX_TYPES];
+  off[0] = 0;
+#pragma unroll
+  for (int q = 1; q < STAFB_MAX_TYPES; q++) off[q] = off[q - 1] + cnt[q - 1];
+  for (int k = lane; k < n; k += 32) {
+    const int v = spos[k], sp = v >> 16;
+    int o = 0;
+#pragma unroll
+    for (int q = 0; q < STAFB_MAX_TYPES; q++)
+      if (q == sp) o = off[q];
+    spos[k] = ((v & 0xffff) + o) | (sp << 16);
+  }
+  __syncwarp();
+}
+
+template <class T>
+__device__ __forceinline__ void record_slot(const RowSink& sk, size_t row, int nr, int pos, int j,
+                                            const SlotVals<T>& sv) {
+  typedef typename Vec4<T>::type T4;
+  unsigned char* rec = static_cast<unsigned char*>(sk.rows) + row * (size_t)sk.stride;
+  T4 u, v;
+  u.x = sv.ux; u.y = sv.uy; u.z = sv.uz; u.w = sv.fc;
+  v.x = sv.rinv; v.y = sv.dfc; v.z = sv.d; v.w = sv.dd;
+  reinterpret_cast<T4*>(rec)[pos] = u;
+  reinterpret_cast<T4*>(rec + row_off_v(nr, (int)sizeof(T)))[pos] = v;
+  reinterpret_cast<int*>(rec + row_off_id(nr, (int)sizeof(T)))[pos] = j;
+}
+
+// header of a record: n, m, neighbours per species, angular neighbours per species (the first nang slots of the
+// distance-sorted row are the angular ones); one warp, after every slot has been written
+__device__ __forceinline__ void record_header(const RowSink& sk, size_t row, int nr, int es, const int* spos, int n,
+                                              int nang, const int (&cnt)[STAFB_MAX_TYPES], int lane) {
+  int ca[STAFB_MAX_TYPES];
+#pragma unroll
+  for (int q = 0; q < STAFB_MAX_TYPES; q++) ca[q] = 0;
+  for (int k0 = 0; k0 < nang; k0 += 32) {
+    const int k = k0 + lane;
+    const int sp = (k < nang) ? (spos[k] >> 16) : -1;
+#pragma unroll
+    for (int q = 0; q < STAFB_MAX_TYPES; q++) ca[q] += __popc(__ballot_sync(0xffffffffu, sp == q));
+  }
+  if (lane == 0) {
+    int* h = reinterpret_cast<int*>(static_cast<unsigned char*>(sk.rows) + row * (size_t)sk.stride +
+                                    row_off_hdr(nr, es));
+    h[0] = n;
+    h[1] = nang;
+#pragma unroll
+    for (int q = 0; q < STAFB_MAX_TYPES; q++) { h[2 + q] = cnt[q]; h[6 + q] = ca[q]; }
+    h[10] = 0; h[11] = 0;
   }
 }
 
@@ -379,7 +469,7 @@ __global__ void __launch_bounds__(WARPS * 32)
                 const int* __restrict__ cells_sorted, int cell_cap, T* __restrict__ raddescr,
                 T* __restrict__ des3bsupp, int* __restrict__ intmap2b, T* __restrict__ der2b,
                 T* __restrict__ der3bsupp, int* __restrict__ numtriplet, T* __restrict__ geom, T* __restrict__ gsc,
-                int na, int* __restrict__ status) {
+                int na, int* __restrict__ status, RowSink sink) {
   extern __shared__ unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gi = blockIdx.x * WARPS + warp;  // row index: the centres are the first ncen atoms of each frame
@@ -471,6 +561,8 @@ __global__ void __launch_bounds__(WARPS * 32)
   }
   __syncwarp();
   const size_t base = (size_t)gi;
+  int cnt[STAFB_MAX_TYPES];
+  if (sink.rows) group_by_species(sink, jb, n, lane, ja, cnt);  // ja[] is free after the sort
   int nang = 0;
   for (int k = lane; k < nr; k += 32) {
     T vx = T(0), vy = T(0), vz = T(0);
@@ -479,13 +571,16 @@ __global__ void __launch_bounds__(WARPS * 32)
       j = jb[k];
       mic_vec(g, pix, piy, piz, fr[3 * j], fr[3 * j + 1], fr[3 * j + 2], vx, vy, vz);
     }
+    SlotVals<T> sv;
     radial_slot<T>(cc, k < n, j, vx, vy, vz, base, k, nr, raddescr, des3bsupp, intmap2b, der2b, der3bsupp, geom, gsc,
-                   nang);
+                   nang, sv);
+    if (sink.rows && k < n) record_slot<T>(sink, base, nr, ja[k] & 0xffff, j, sv);
   }
   nang = warp_sum(nang);
+  if (sink.rows) record_header(sink, base, nr, (int)sizeof(T), ja, n, nang, cnt, lane);
   if (lane == 0) {
-    intmap2b[base * (nr + 1)] = n;
-    numtriplet[base] = nang;
+    if (intmap2b) intmap2b[base * (nr + 1)] = n;
+    if (numtriplet) numtriplet[base] = nang;
     if ((long long)nang * (nang - 1) / 2 > na) set_status(status, STAFB_ERR_ANGULAR_OVERFLOW);
   }
 }
@@ -498,46 +593,55 @@ __global__ void __launch_bounds__(WARPS * 32)
 template <class T, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
     k_rows_from_list(int ncen, int nall, int nr, CoreCoef<T> cc, const T* __restrict__ pos,
-                     const int* __restrict__ howmany, const int* __restrict__ with, T* __restrict__ raddescr,
-                     T* __restrict__ des3bsupp, int* __restrict__ intmap2b, int* __restrict__ numtriplet,
-                     T* __restrict__ geom, T* __restrict__ gsc, int na, int* __restrict__ status) {
+                     const int* __restrict__ howmany, const int* __restrict__ with, int na, int* __restrict__ status,
+                     RowSink sink) {
+  extern __shared__ unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int i = blockIdx.x * WARPS + warp;
   if (i >= ncen) return;
+  int* ids = reinterpret_cast<int*>(smem_raw) + (size_t)warp * 2 * nr;  // [nr] neighbour of slot k (0 if invalid)
+  int* spos = ids + nr;                                                 // [nr] position in the record | species << 16
   int n = howmany[i];
   if (n < 0) n = 0;
   if (n > nr) {
     if (lane == 0) set_status(status, STAFB_ERR_RADIAL_OVERFLOW);
     n = nr;
   }
-  const T pix = pos[3 * i], piy = pos[3 * i + 1], piz = pos[3 * i + 2];
-  const size_t base = (size_t)i;
-  int nang = 0;
-  for (int k = lane; k < nr; k += 32) {
-    T vx = T(0), vy = T(0), vz = T(0);
-    int j = 0;
-    bool valid = k < n;
-    if (valid) {
+  // a bad entry (out of range or the centre itself) is reported and dropped: the row is compacted first
+  int nv = 0;
+  const unsigned lt = (1u << lane) - 1u;
+  for (int k0 = 0; k0 < n; k0 += 32) {
+    const int k = k0 + lane;
+    int j = -1;
+    if (k < n) {
       j = with[(size_t)i * nr + k];
       if (j < 0 || j >= nall || j == i) {
         set_status(status, STAFB_ERR_INVALID);
-        valid = false;
-        j = 0;
-      } else {
-        vx = pix - pos[3 * j];
-        vy = piy - pos[3 * j + 1];
-        vz = piz - pos[3 * j + 2];
+        j = -1;
       }
     }
-    radial_slot<T>(cc, valid, j, vx, vy, vz, base, k, nr, raddescr, des3bsupp, intmap2b, nullptr, nullptr, geom, gsc,
-                   nang);
+    const unsigned bal = __ballot_sync(0xffffffffu, j >= 0);
+    if (j >= 0) ids[nv + __popc(bal & lt)] = j;
+    nv += __popc(bal);
+  }
+  n = nv;
+  __syncwarp();
+  const T pix = pos[3 * i], piy = pos[3 * i + 1], piz = pos[3 * i + 2];
+  const size_t base = (size_t)i;
+  int cnt[STAFB_MAX_TYPES];
+  group_by_species(sink, ids, n, lane, spos, cnt);
+  int nang = 0;
+  for (int k = lane; k < n; k += 32) {
+    const int j = ids[k];
+    SlotVals<T> sv;
+    radial_slot<T>(cc, true, j, pix - pos[3 * j], piy - pos[3 * j + 1], piz - pos[3 * j + 2], base, k, nr,
+                   (T*)nullptr, (T*)nullptr, (int*)nullptr, (T*)nullptr, (T*)nullptr, (T*)nullptr, (T*)nullptr, nang,
+                   sv);
+    record_slot<T>(sink, base, nr, spos[k] & 0xffff, j, sv);
   }
   nang = warp_sum(nang);
-  if (lane == 0) {
-    intmap2b[base * (nr + 1)] = n;
-    numtriplet[base] = nang;
-    if ((long long)nang * (nang - 1) / 2 > na) set_status(status, STAFB_ERR_ANGULAR_OVERFLOW);
-  }
+  record_header(sink, base, nr, (int)sizeof(T), spos, n, nang, cnt, lane);
+  if (lane == 0 && (long long)nang * (nang - 1) / 2 > na) set_status(status, STAFB_ERR_ANGULAR_OVERFLOW);
 }
 
 // Angular descriptor rows (reforce.cu.cc:112-236): one block per central atom; the sorted
@@ -610,7 +714,7 @@ __global__ void __launch_bounds__(THREADS)
 template <class T>
 int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box, int nf, int N, T* raddescr,
                        T* angdescr, T* des3bsupp, int* intmap2b, int* intmap3b, T* der2b, T* der3b, T* der3bsupp,
-                       int* numtriplet, int ncen) {
+                       int* numtriplet, int ncen, const RowSink* sink) {
   if (nf <= 0 || N <= 0) return STAFB_ERR_INVALID;
   if (nf > c->max_batch || N > c->n_max) return STAFB_ERR_CAPACITY;
   if (ncen < 0) ncen = N;  // every atom is a centre unless the caller restricts the rows to the first ncen
@@ -618,8 +722,14 @@ int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box,
   const int nr = c->nr, na = c->na, cap = c->cell_cap;
   FrameGeom<T>* fg = reinterpret_cast<FrameGeom<T>*>(c->fgeom);
   T* frac = reinterpret_cast<T*>(c->frac);
-  T* geom = reinterpret_cast<T*>(c->geom);
-  T* gsc = reinterpret_cast<T*>(c->gsc);
+  // the compact geometry rows feed the angular-descriptor kernel only
+  const bool want_angular = angdescr && intmap3b && der3b;
+  T* geom = want_angular ? reinterpret_cast<T*>(c->geom) : nullptr;
+  T* gsc = want_angular ? reinterpret_cast<T*>(c->gsc) : nullptr;
+  RowSink sk;
+  memset(&sk, 0, sizeof(sk));
+  if (sink) sk = *sink;
+  if (want_angular && (!intmap2b || !numtriplet)) return STAFB_ERR_INVALID;
   int mpc = N / 3;  // descriptor_builder/reforce.cc:306-309
   if (mpc < 1) mpc = 1;
   if (mpc > 256) mpc = 256;
@@ -655,10 +765,10 @@ int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box,
     const int rows = nf * ncen;
     STAFB_CUDA_OK(launch_chained(k_nl_radial<T, W>, (rows + W - 1) / W, W * 32, sm, s, nf, N, ncen, nr, cc, fg, frac,
                                  c->cell_of, c->cell_start, c->cells_sorted, cap, raddescr, des3bsupp, intmap2b, der2b,
-                                 der3bsupp, numtriplet, geom, gsc, na, c->status_d));
+                                 der3bsupp, numtriplet, geom, gsc, na, c->status_d, sk));
   }
   c->launches += 1;
-  if (angdescr && intmap3b && der3b) {
+  if (want_angular) {
     constexpr int TH = 128;
     size_t sm = (size_t)nr * (sizeof(typename Vec4<T>::type) + 2 * sizeof(T) + sizeof(int));
     k_angular<T, TH><<<nf * ncen, TH, sm, s>>>(nf, N, nr, na, cc.Ra, geom, intmap2b, numtriplet, angdescr, intmap3b, der3b);
@@ -669,31 +779,31 @@ int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box,
 }
 
 template int launch_descriptors<float>(stafb_ctx*, cudaStream_t, const float*, const float*, int, int, float*, float*,
-                                       float*, int*, int*, float*, float*, float*, int*, int);
+                                       float*, int*, int*, float*, float*, float*, int*, int, const RowSink*);
 template int launch_descriptors<double>(stafb_ctx*, cudaStream_t, const double*, const double*, int, int, double*,
-                                        double*, double*, int*, int*, double*, double*, double*, int*, int);
+                                        double*, double*, int*, int*, double*, double*, double*, int*, int,
+                                        const RowSink*);
 
 template <class T>
 int launch_rows_from_list(stafb_ctx* c, cudaStream_t s, const T* pos, int ncen, int nall, const int* howmany,
-                          const int* with, T* raddescr, T* des3bsupp, int* intmap2b, int* numtriplet) {
-  if (ncen <= 0 || nall < ncen || !howmany || !with) return STAFB_ERR_INVALID;
+                          const int* with, const RowSink* sink) {
+  if (ncen <= 0 || nall < ncen || !howmany || !with || !sink || !sink->rows) return STAFB_ERR_INVALID;
   if (nall > c->n_max) return STAFB_ERR_CAPACITY;
   CoreCoef<T> cc;
   cc.Rc = (T)c->Rc; cc.Rs = (T)c->Rs; cc.Ra = (T)c->Ra;
   cc.A = (T)c->coef[0]; cc.B = (T)c->coef[1]; cc.C = (T)c->coef[2]; cc.pa = (T)c->coef[3]; cc.pb = (T)c->coef[4];
   constexpr int W = 4;
-  k_rows_from_list<T, W><<<(ncen + W - 1) / W, W * 32, 0, s>>>(ncen, nall, c->nr, cc, pos, howmany, with, raddescr,
-                                                             des3bsupp, intmap2b, numtriplet,
-                                                             reinterpret_cast<T*>(c->geom),
-                                                             reinterpret_cast<T*>(c->gsc), c->na, c->status_d);
+  const size_t sm = (size_t)W * 2 * c->nr * sizeof(int);
+  k_rows_from_list<T, W><<<(ncen + W - 1) / W, W * 32, sm, s>>>(ncen, nall, c->nr, cc, pos, howmany, with, c->na,
+                                                              c->status_d, *sink);
   c->launches += 1;
   STAFB_CUDA_OK(cudaGetLastError());
   return STAFB_OK;
 }
 template int launch_rows_from_list<float>(stafb_ctx*, cudaStream_t, const float*, int, int, const int*, const int*,
-                                          float*, float*, int*, int*);
+                                          const RowSink*);
 template int launch_rows_from_list<double>(stafb_ctx*, cudaStream_t, const double*, int, int, const int*, const int*,
-                                           double*, double*, int*, int*);
+                                           const RowSink*);
 
 }  // namespace stafb
 

@@ -33,6 +33,7 @@ extern "C" {
 #define STAFB_ERR_CAPACITY 7         /* nf or N larger than what the context was created for */
 #define STAFB_ERR_NONFINITE 8        /* non-finite energy */
 #define STAFB_ERR_PEER_TIMEOUT 9     /* stafb_allreduce_adam: a peer rank did not publish its gradient in time */
+#define STAFB_ERR_STAGE_TIMEOUT 10   /* a kernel gave up waiting for its own asynchronous copy into shared memory */
 
 #define STAFB_F32 0
 #define STAFB_F64 1
