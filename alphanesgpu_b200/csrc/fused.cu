@@ -77,15 +77,6 @@ static inline int species_blocks(const ModelDev& md, int nf, int W) {
 
 // ---------------------------------------------------------------------------- MLP head
 #include "mlp.cuh"
-#ifdef STAFB_SWEEP_CLOCKS
-}  // namespace stafb
-extern "C" int stafb_mlp_clocks(unsigned long long* out32) {
-  if (cudaMemcpyFromSymbol(out32, stafb::g_mlp_clk, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
-  unsigned long long z[32] = {0};
-  return cudaMemcpyToSymbol(stafb::g_mlp_clk, z, sizeof(z)) == cudaSuccess ? 0 : 1;
-}
-namespace stafb {
-#endif
 
 // ---------------------------------------------------------------------------- energy, loss
 template <class T>
@@ -286,7 +277,7 @@ struct stafb_model {
   int blk_size[STAFB_MAX_TYPES];
   size_t es;
   int cap_atoms;  // atoms per frame the scratch was sized for
-  int apt;  // atoms per thread group of the MLP kernels (TA = 8*apt atoms per block)
+  int aw;   // atoms per warp of the MLP kernels (4, 2 or 1; a block of eight warps owns 8*aw atoms)
   int stage;  // Dense layers in shared memory: 2 all at kernel start, 1 one at a time, 0 none
   size_t mlp_fwd_smem, mlp_bwd_smem;
   // scratch for max_batch frames
@@ -344,11 +335,11 @@ static size_t mlp_stage_words(const ModelDev& d, int stage) {
   }
   return stage ? best : 0;
 }
-static size_t mlp_smem_fwd(const ModelDev& d, size_t es, int apt, int stage) {
-  return es * ((size_t)(d.Fmax + d.Hsum + 2 * d.maxw) * (8 * apt + ML_PAD) + mlp_stage_words(d, stage));
+static size_t mlp_smem_fwd(const ModelDev& d, size_t es, int aw, int stage) {
+  return es * (ML_WARPS * ml_fwd_words(d.Fmax, d.Hsum, d.maxw, aw) + mlp_stage_words(d, stage));
 }
-static size_t mlp_smem_bwd(const ModelDev& d, size_t es, int apt, int stage) {
-  return es * ((size_t)(2 * d.Fmax + 5 * d.Hsum + 2 * d.maxw) * (8 * apt + ML_PAD) + mlp_stage_words(d, stage));
+static size_t mlp_smem_bwd(const ModelDev& d, size_t es, int aw, int stage) {
+  return es * (ML_WARPS * ml_bwd_words(d.Fmax, d.Hsum, d.maxw, aw) + mlp_stage_words(d, stage));
 }
 
 extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out) {
@@ -401,30 +392,30 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&lim, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   m->smem_limit = (size_t)lim;
-  m->apt = 0;
+  m->aw = 0;
   int nsm = 148;
   cudaDeviceGetAttribute(&nsm, cudaDevAttrMultiProcessorCount, dev);
-  // Dense layers in shared memory: all of them (2) if they fit next to the activations of 8 atoms within half
-  // of the SM (two resident blocks), else one at a time (1), else none (0)
-  const size_t mlp_room = m->smem_limit - 1024;  // the MLP kernels also hold a little static shared memory
-  m->stage = 2;
-  if (mlp_smem_bwd(d, m->es, 1, 2) > mlp_room / 2) m->stage = 1;
-  if (mlp_smem_bwd(d, m->es, 1, m->stage) > mlp_room) m->stage = 0;
+  // Atoms per warp of the MLP kernels and where the Dense layers live.  Wanted: every SM busy (4 atoms per warp
+  // only if that still gives one block per SM, else 2) and all layers staged in shared memory at kernel start
+  // (2); what does not fit falls back to one layer at a time (1), then to fewer atoms per warp, then to reading
+  // the weights from global memory (0).
+  const size_t mlp_room = m->smem_limit - 1024;  // the backward kernel also holds a little static shared memory
+  const int aw_pref = species_blocks(d, c->max_batch, ML_WARPS * 4) >= nsm ? 4 : 2;
+  const int cand[7][2] = {{aw_pref, 2}, {aw_pref, 1}, {2, 1}, {1, 1}, {aw_pref, 0}, {2, 0}, {1, 0}};
+  m->stage = 0;
+  for (int k = 0; k < 7 && !m->aw; k++)
+    if (mlp_smem_bwd(d, m->es, cand[k][0], cand[k][1]) <= mlp_room) { m->aw = cand[k][0]; m->stage = cand[k][1]; }
   if (getenv("STAFB_MLP_STAGE")) m->stage = atoi(getenv("STAFB_MLP_STAGE"));
-  for (int apt = 4; apt >= 1; apt >>= 1) {
-    if (mlp_smem_bwd(d, m->es, apt, m->stage) > mlp_room) continue;
-    m->apt = apt;  // keep shrinking until the grid gives every SM at least two blocks
-    if (species_blocks(d, c->max_batch, 8 * apt) >= 2 * nsm) break;
-  }
-  if (getenv("STAFB_MLP_APT")) m->apt = atoi(getenv("STAFB_MLP_APT"));
-  if (!m->apt) { free(m); return STAFB_ERR_CAPACITY; }
-  m->mlp_fwd_smem = mlp_smem_fwd(d, m->es, m->apt, m->stage);
-  m->mlp_bwd_smem = mlp_smem_bwd(d, m->es, m->apt, m->stage);
+  if (getenv("STAFB_MLP_AW")) m->aw = atoi(getenv("STAFB_MLP_AW"));
+  if (m->aw != 1 && m->aw != 2 && m->aw != 4) { free(m); return STAFB_ERR_CAPACITY; }
+  if (m->stage < 0 || m->stage > 2 || mlp_smem_bwd(d, m->es, m->aw, m->stage) > mlp_room) { free(m); return STAFB_ERR_CAPACITY; }
+  m->mlp_fwd_smem = mlp_smem_fwd(d, m->es, m->aw, m->stage);
+  m->mlp_bwd_smem = mlp_smem_bwd(d, m->es, m->aw, m->stage);
   // scratch is sized for the context's atom capacity, so that stafb_model_set_counts can move atoms between
   // species (or change their number) without reallocating
   const size_t es = m->es, A = (size_t)c->max_batch * c->n_max, nr = c->nr;
   m->cap_atoms = c->n_max;
-  const size_t mlp_blocks = A / (8 * m->apt) + d.nt + 1;
+  const size_t mlp_blocks = A / (ML_WARPS * m->aw) + d.nt + 1;
   m->row_stride = row_stride_bytes((int)nr, (int)es);
   STAFB_CUDA_OK(cudaMalloc(&m->rows, A * (size_t)m->row_stride));
   STAFB_CUDA_OK(cudaMemset(m->rows, 0, A * (size_t)m->row_stride));
@@ -437,7 +428,7 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   STAFB_CUDA_OK(cudaMalloc(&m->gaf, es * A * d.Fmax));
   m->nv = d.nt * d.Frmax + d.C * 3 * d.Famax;
   STAFB_CUDA_OK(cudaMalloc(&m->vrow, es * A * (m->nv > 0 ? m->nv : 1)));
-  STAFB_CUDA_OK(cudaMalloc(&m->acts, es * mlp_blocks * 8 * m->apt * d.Hsum));
+  STAFB_CUDA_OK(cudaMalloc(&m->acts, es * mlp_blocks * ML_WARPS * m->aw * d.Hsum));
   m->wstride = (int)mlp_stage_words(d, 2);
   STAFB_CUDA_OK(cudaMalloc(&m->wpack, es * (size_t)d.nt * m->wstride));
   STAFB_CUDA_OK(cudaMalloc(&m->e_atom, es * A));
@@ -503,7 +494,7 @@ extern "C" int stafb_model_set_counts(stafb_model* m, const int* tipos) {
 extern "C" int stafb_model_n_params(const stafb_model* m) { return m ? m->n_params : -1; }
 extern "C" int stafb_model_n_emb(const stafb_model* m) { return m ? m->n_emb : -1; }
 extern "C" void stafb_model_mlp_config(const stafb_model* m, int out4[4]) {
-  out4[0] = m->stage; out4[1] = m->apt; out4[2] = (int)m->mlp_fwd_smem; out4[3] = (int)m->mlp_bwd_smem;
+  out4[0] = m->stage; out4[1] = m->aw; out4[2] = (int)m->mlp_fwd_smem; out4[3] = (int)m->mlp_bwd_smem;
 }
 extern "C" void stafb_model_offsets(const stafb_model* m, int t, int out6[6]) {
   out6[0] = m->md.off_a2[t]; out6[1] = m->md.off_a3[t]; out6[2] = m->md.off_mu[t]; out6[3] = m->md.off_w[t];
@@ -582,39 +573,67 @@ static RowSink row_sink(const stafb_model* m, void* rows, const int* tmap) {
   return sk;
 }
 
-template <class T, int APT>
-static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, T* acts, T* e_atom,
-                          T* nd) {
+template <class T, int AW, bool WG>
+static int launch_mlp_fwd_t(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, T* acts, T* e_atom,
+                            T* nd) {
   static size_t attr_dev[MAX_DEVICES] = {0};  // largest dynamic shared-memory size opted in for, per device
   size_t& attr = attr_dev[device_slot()];
   if (m->mlp_fwd_smem > 48 * 1024 && m->mlp_fwd_smem > attr) {
-    STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_fwd<T, APT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_fwd<T, AW, WG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)m->mlp_fwd_smem));
     attr = m->mlp_fwd_smem;
   }
-  STAFB_CUDA_OK(launch_chained(k_mlp_fwd<T, APT>, species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_fwd_smem, s,
-                               m->md, nf, theta, (const T*)m->wpack, m->wstride, af, acts, e_atom, nd,
-                               m->losses_d + 8, m->stage));
+  STAFB_CUDA_OK(launch_chained(k_mlp_fwd<T, AW, WG>, species_blocks(m->md, nf, ML_WARPS * AW), ML_THREADS,
+                               m->mlp_fwd_smem, s, m->md, nf, theta, (const T*)m->wpack, m->wstride, af, acts, e_atom,
+                               nd, m->losses_d + 8, m->stage, (int)mlp_stage_words(m->md, m->stage)));
   m->ctx->launches++;
   return STAFB_OK;
 }
 
-template <class T, int APT>
-static int launch_mlp_bwd(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, const T* acts,
-                          const T* ebar, const T* u, T* gaf, T* grad) {
+template <class T, int AW, bool WG>
+static int launch_mlp_bwd_t(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, const T* acts,
+                            const T* ebar, const T* u, T* gaf, T* grad) {
   static size_t attr_dev[MAX_DEVICES] = {0};
   size_t& attr = attr_dev[device_slot()];
   const T* vrow = (const T*)m->vrow;
   if (m->mlp_bwd_smem > 48 * 1024 && m->mlp_bwd_smem > attr) {
-    STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_bwd<T, APT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_bwd<T, AW, WG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)m->mlp_bwd_smem));
     attr = m->mlp_bwd_smem;
   }
-  STAFB_CUDA_OK(launch_chained(k_mlp_bwd<T, APT>, species_blocks(m->md, nf, 8 * APT), ML_THREADS, m->mlp_bwd_smem, s,
-                               m->md, nf, theta, (const T*)m->wpack, m->wstride, af, acts, ebar, u, vrow, m->nv, gaf,
-                               grad, m->stage));
+  STAFB_CUDA_OK(launch_chained(k_mlp_bwd<T, AW, WG>, species_blocks(m->md, nf, ML_WARPS * AW), ML_THREADS,
+                               m->mlp_bwd_smem, s, m->md, nf, theta, (const T*)m->wpack, m->wstride, af, acts, ebar, u,
+                               vrow, m->nv, gaf, grad, m->stage, (int)mlp_stage_words(m->md, m->stage)));
   m->ctx->launches++;
   return STAFB_OK;
+}
+
+template <class T>
+static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, T* acts, T* e_atom,
+                          T* nd) {
+  const bool wg = m->stage == 0;
+  switch (m->aw) {
+    case 4: return wg ? launch_mlp_fwd_t<T, 4, true>(m, s, nf, theta, af, acts, e_atom, nd)
+                      : launch_mlp_fwd_t<T, 4, false>(m, s, nf, theta, af, acts, e_atom, nd);
+    case 2: return wg ? launch_mlp_fwd_t<T, 2, true>(m, s, nf, theta, af, acts, e_atom, nd)
+                      : launch_mlp_fwd_t<T, 2, false>(m, s, nf, theta, af, acts, e_atom, nd);
+    default: return wg ? launch_mlp_fwd_t<T, 1, true>(m, s, nf, theta, af, acts, e_atom, nd)
+                       : launch_mlp_fwd_t<T, 1, false>(m, s, nf, theta, af, acts, e_atom, nd);
+  }
+}
+
+template <class T>
+static int launch_mlp_bwd(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, const T* acts,
+                          const T* ebar, const T* u, T* gaf, T* grad) {
+  const bool wg = m->stage == 0;
+  switch (m->aw) {
+    case 4: return wg ? launch_mlp_bwd_t<T, 4, true>(m, s, nf, theta, af, acts, ebar, u, gaf, grad)
+                      : launch_mlp_bwd_t<T, 4, false>(m, s, nf, theta, af, acts, ebar, u, gaf, grad);
+    case 2: return wg ? launch_mlp_bwd_t<T, 2, true>(m, s, nf, theta, af, acts, ebar, u, gaf, grad)
+                      : launch_mlp_bwd_t<T, 2, false>(m, s, nf, theta, af, acts, ebar, u, gaf, grad);
+    default: return wg ? launch_mlp_bwd_t<T, 1, true>(m, s, nf, theta, af, acts, ebar, u, gaf, grad)
+                       : launch_mlp_bwd_t<T, 1, false>(m, s, nf, theta, af, acts, ebar, u, gaf, grad);
+  }
 }
 
 // Domain mode of the fused path: one frame of nall atoms whose first N (the model's species-sorted
@@ -679,9 +698,7 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
   rc = train ? launch_sweep<T, MODE_AFV>(m, s, sc) : launch_sweep<T, MODE_AF>(m, s, sc);
   if (rc != STAFB_OK) return rc;
   mark();  // af_fwd
-  rc = m->apt == 4 ? launch_mlp_fwd<T, 4>(m, s, nf, theta, af, acts, e_atom, nd)
-       : m->apt == 2 ? launch_mlp_fwd<T, 2>(m, s, nf, theta, af, acts, e_atom, nd)
-                     : launch_mlp_fwd<T, 1>(m, s, nf, theta, af, acts, e_atom, nd);
+  rc = launch_mlp_fwd<T>(m, s, nf, theta, af, acts, e_atom, nd);
   if (rc != STAFB_OK) return rc;
   mark();  // mlp_fwd
   double* vacc = virial_out ? m->losses_d + 8 + c->max_batch : nullptr;
@@ -711,9 +728,7 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
     rc = launch_sweep<T, MODE_FGRAD>(m, s, sc);
     if (rc != STAFB_OK) return rc;
     mark();  // force_grad
-    rc = m->apt == 4 ? launch_mlp_bwd<T, 4>(m, s, nf, theta, af, acts, (const T*)m->ebar, gradnet, gaf, grad)
-         : m->apt == 2 ? launch_mlp_bwd<T, 2>(m, s, nf, theta, af, acts, (const T*)m->ebar, gradnet, gaf, grad)
-                       : launch_mlp_bwd<T, 1>(m, s, nf, theta, af, acts, (const T*)m->ebar, gradnet, gaf, grad);
+    rc = launch_mlp_bwd<T>(m, s, nf, theta, af, acts, (const T*)m->ebar, gradnet, gaf, grad);
     if (rc != STAFB_OK) return rc;
     mark();  // mlp_bwd
     if (losses_out != m->losses_d)

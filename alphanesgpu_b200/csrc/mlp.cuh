@@ -1,45 +1,33 @@
 // Per-species MLP energy head of the fused path (included by fused.cu inside namespace stafb).
 //
 // x = log(AF+1e-3) - mu ; Dense(tanh)... Dense(1)  (staf_models/staf_model.py:188-191,
-// libstaf/src/mlp/staf_mlp_ort.cc:196-242 of the reference).  A block of 256 threads owns TA = 8*APT
-// atoms of one species.  Every per-atom vector lives in shared memory feature-major ([feature][atom],
-// row stride TA+4 words) and every Dense layer is staged in shared memory once per block; the
-// matrix products are register-tiled so that one shared-memory load feeds several FMAs:
-//   forward   thread = 4 outputs x 2 atoms : one 16-byte weight load + one atom-pair load -> 8 FMA
-//   backward  thread = 1 input x 4 atoms   : one 16-byte weight load + four atom-quad loads -> 16 FMA
-//   dL/dW     thread = 2 inputs x 2 outputs, atoms four at a time
-// The weight row stride is chosen = 4 (mod 32) words, which makes both the forward pattern (lanes on
-// consecutive output groups) and the backward pattern (lanes on consecutive inputs) conflict-free.
+// libstaf/src/mlp/staf_mlp_ort.cc:196-242 of the reference).
+//
+// The layers of this network are small (25-64-32-1 up to 60-140-140-1), so a block-wide product per layer spends
+// its time in barriers.  Here every WARP carries AW atoms (4, 2 or 1) of one species through all layers on its own:
+// its vectors live in a private slice of shared memory, feature-major ([feature][atom], one 16-byte row per
+// feature at AW = 4), and only __syncwarp() separates the layers.  The eight warps of a block share the staged
+// Dense layers (all layers at kernel start, one layer at a time - the only mode with block barriers between
+// layers - or none, read from global memory).
+//   forward   Y[j][a]  = sum_i W[i][j] X[i][a]   lane = output j (and j+32): one broadcast row load of X and two
+//                                                conflict-free weight loads per 2*AW FMAs
+//   backward  Xo[i][a] = sum_j W[i][j] D[j][a]   lane = input i: the lane's weight row 16 bytes at a time (row
+//                                                stride = 4 mod 32 words: conflict-free), D rows broadcast
+//   dL/dW     G[i][j]  = sum_a h[i][a] q[j][a]   needs every atom of the block: once all warps are through, the
+//                                                block forms it 4 x 4 per thread over the eight warps' slices
 #pragma once
 #include <cuda_pipeline.h>
 
-constexpr int ML_PAD = 4;  // padding of the [feature][atom] rows, in words
-
-// Optional phase clocks (build with -DSTAFB_SWEEP_CLOCKS): thread 0 of every block adds the clock64() ticks
-// between consecutive ML_TICK marks to g_mlp_clk[kernel][phase]; read with stafb_mlp_clocks().
-#ifdef STAFB_SWEEP_CLOCKS
-__device__ unsigned long long g_mlp_clk[2][16];
-#define ML_CLK_INIT long long mclk__ = clock64();
-#define ML_TICK(k, p)                                                                              \
-  {                                                                                                \
-    const long long now__ = clock64();                                                             \
-    if (threadIdx.x == 0) atomicAdd(&g_mlp_clk[k][p], (unsigned long long)(now__ - mclk__));       \
-    mclk__ = now__;                                                                                \
-  }
-#else
-#define ML_CLK_INIT
-#define ML_TICK(k, p)
-#endif
+constexpr int ML_WARPS = ML_THREADS / 32;
 
 // row stride of a staged layer with `out` columns: smallest value >= out that is 4 mod 32
 __host__ __device__ inline int ml_ld(int out) { return ((out + 27) / 32) * 32 + 4; }
 
 template <class T>
 struct LayerView {
-  const T* W;  // element (i,j) at W[i*ld + j]
+  const T* W;  // element (i,j) at W[i*ld + j]; columns out..ld-1 are zero
   const T* B;  // bias
   int ld;
-  bool vec;    // rows are 16-byte aligned and padded with zeros up to a multiple of four columns
 };
 
 // The Dense layers reach the MLP kernels through a packed copy of the weights (k_prep writes it at the start
@@ -57,161 +45,191 @@ __device__ __forceinline__ void stage_words(const T* __restrict__ src, T* wsm, i
   __pipeline_commit();
 }
 
-__device__ __forceinline__ void ml_stage_wait() {
-  __pipeline_wait_prior(0);
-  __syncthreads();
-}
-
 template <class T>
 __device__ __forceinline__ LayerView<T> layer_view(int in, int out, const T* base) {
   LayerView<T> v;
   v.ld = ml_ld(out);
-  v.W = base; v.B = base + in * v.ld; v.vec = true;
+  v.W = base; v.B = base + in * v.ld;
   return v;
 }
 
-// Dense layer l of species t for the products below; wp = the species' packed weights in global memory.
-// mode 2: every layer was staged when the kernel started (wsm holds them back to back); mode 1: stage this
-// layer now; mode 0: read the packed copy in global memory (the layer does not fit next to the activations).
-template <class T>
+// Dense layer l of species t; wp = the species' packed weights in global memory.  WG: the weights stay in global
+// memory (the layers do not fit next to the warps' slices).  Otherwise stage 2: every layer was staged when the
+// kernel started (wsm holds them back to back); stage 1: stage this layer now, between two block barriers - every
+// warp of the block calls this at the same point.
+template <class T, bool WG>
 __device__ __forceinline__ LayerView<T> get_layer(const ModelDev& md, int t, int l, const T* __restrict__ wp, T* wsm,
-                                                 int mode) {
+                                                 int stage) {
   const int in = md.in_of(t, l), out = md.width[l];
   int off = 0;
   for (int k = 0; k < l; k++) off += ml_layer_words(md.in_of(t, k), md.width[k]);
-  if (mode == 2) return layer_view<T>(in, out, wsm + off);
-  __syncthreads();  // previous users of wsm are done, inputs of the layer are complete
-  if (mode == 0) return layer_view<T>(in, out, wp + off);
+  if (WG) return layer_view<T>(in, out, wp + off);
+  if (stage == 2) return layer_view<T>(in, out, wsm + off);
+  __syncthreads();  // every warp is done with the layer staged before
   stage_words<T>(wp + off, wsm, ml_layer_words(in, out));
-  ml_stage_wait();
+  __pipeline_wait_prior(0);
+  __syncthreads();
   return layer_view<T>(in, out, wsm);
 }
 
-// mode 2: issue the copies of every layer (the caller overlaps them with its own global loads, then waits)
-template <class T>
-__device__ __forceinline__ void stage_all_layers(const ModelDev& md, int t, const T* __restrict__ wp, T* wsm) {
-  int words = 0;
-  for (int l = 0; l < md.n_dense; l++) words += ml_layer_words(md.in_of(t, l), md.width[l]);
-  stage_words<T>(wp, wsm, words);
+// tanh for the activations: fp32 as 1 - 2/(2^(2x log2 e) + 1) with the hardware exponential and reciprocal
+// (absolute error of a few 1e-7, saturates correctly at +-1), fp64 the library function
+__device__ __forceinline__ float ml_tanh(float x) {
+  const float e = ex2_fast(x * 2.885390081777927f);
+  return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
+__device__ __forceinline__ double ml_tanh(double x) { return tanh(x); }
+
+// one [feature] row of a warp's slice: AW consecutive reals
+template <class T, int AW> struct RowIO;
+template <> struct RowIO<float, 4> {
+  static __device__ __forceinline__ void ld(const float* p, float (&x)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+  }
+  static __device__ __forceinline__ void st(float* p, const float (&x)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+  }
+};
+template <> struct RowIO<float, 2> {
+  static __device__ __forceinline__ void ld(const float* p, float (&x)[2]) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    x[0] = v.x; x[1] = v.y;
+  }
+  static __device__ __forceinline__ void st(float* p, const float (&x)[2]) {
+    *reinterpret_cast<float2*>(p) = make_float2(x[0], x[1]);
+  }
+};
+template <> struct RowIO<double, 4> {
+  static __device__ __forceinline__ void ld(const double* p, double (&x)[4]) {
+    const double2 a = *reinterpret_cast<const double2*>(p), b = *reinterpret_cast<const double2*>(p + 2);
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+  }
+  static __device__ __forceinline__ void st(double* p, const double (&x)[4]) {
+    *reinterpret_cast<double2*>(p) = make_double2(x[0], x[1]);
+    *reinterpret_cast<double2*>(p + 2) = make_double2(x[2], x[3]);
+  }
+};
+template <> struct RowIO<double, 2> {
+  static __device__ __forceinline__ void ld(const double* p, double (&x)[2]) {
+    const double2 a = *reinterpret_cast<const double2*>(p);
+    x[0] = a.x; x[1] = a.y;
+  }
+  static __device__ __forceinline__ void st(double* p, const double (&x)[2]) {
+    *reinterpret_cast<double2*>(p) = make_double2(x[0], x[1]);
+  }
+};
+template <class T> struct RowIO<T, 1> {
+  static __device__ __forceinline__ void ld(const T* p, T (&x)[1]) { x[0] = p[0]; }
+  static __device__ __forceinline__ void st(T* p, const T (&x)[1]) { p[0] = x[0]; }
+};
+// four consecutive weights of a row (16-byte aligned)
+__device__ __forceinline__ void ml_ld4(const float* p, float (&w)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+}
+__device__ __forceinline__ void ml_ld4(const double* p, double (&w)[4]) {
+  const double2 a = *reinterpret_cast<const double2*>(p), b = *reinterpret_cast<const double2*>(p + 2);
+  w[0] = a.x; w[1] = a.y; w[2] = b.x; w[3] = b.y;
 }
 
-// Y[j][a] = act( b[j] + sum_i X[i][a] W[i,j] ).  A thread owns one output j for a group of eight atoms and
-// one slice of the input range: the sum over i is split KS ways across adjacent lanes (so that all 256
-// threads work even when the layer is narrow and the dependent FMA chains stay short) and the slices are
-// combined with shuffles.
-template <class T, int TA, bool TANH, bool BIAS>
-__device__ __forceinline__ void dense_fwd(int in, int out, const LayerView<T> lv, const T* X, T* Y) {
-  typedef typename Vec4<T>::type T4;
-  constexpr int TAP = TA + ML_PAD, NO = TA / 8;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, ld = lv.ld;
-  int KS = 1;
-  while (KS < 32 && out * NO * KS < ML_THREADS && KS * 2 <= in) KS <<= 1;
-  const int JL = 32 / KS, njg = (out + JL - 1) / JL;
-  const int ks = lane & (KS - 1), jl = lane / KS;
-  for (int item = warp; item < njg * NO; item += ML_THREADS / 32) {
-    const int jg = item % njg, a0 = (item / njg) * 8;
-    const int j = jg * JL + jl;
-    T acc[8];
+// Y[j][a] = act( b[j] + sum_i X[i][a] W[i,j] ), one warp, AW atoms; a lane owns outputs j0+lane and j0+32+lane
+// of every group of 64.  The caller separates this from the producer of X with __syncwarp().
+template <class T, int AW, bool TANH, bool BIAS>
+__device__ __forceinline__ void warp_dense_fwd(int in, int out, const LayerView<T> lv, const T* __restrict__ X,
+                                               T* __restrict__ Y, int lane) {
+  const int ld = lv.ld;
+  for (int j0 = 0; j0 < out; j0 += 64) {
+    const int ja = j0 + lane, jb = ja + 32;
+    const bool two = j0 + 32 < out;  // warp-uniform
+    // a lane past the last output reads the last column and drops the result
+    const T* wa = lv.W + (ja < out ? ja : out - 1);
+    const T* wb = lv.W + (jb < out ? jb : out - 1);
+    T acc0[AW], acc1[AW];
 #pragma unroll
-    for (int q = 0; q < 8; q++) acc[q] = T(0);
-    if (j < out) {
+    for (int a = 0; a < AW; a++) acc0[a] = acc1[a] = T(0);
+    if (two) {
 #pragma unroll 4
-      for (int i = ks; i < in; i += KS) {
-        const T w = lv.W[i * ld + j];
-        const T4 x0 = *reinterpret_cast<const T4*>(X + i * TAP + a0);
-        const T4 x1 = *reinterpret_cast<const T4*>(X + i * TAP + a0 + 4);
-        acc[0] += x0.x * w; acc[1] += x0.y * w; acc[2] += x0.z * w; acc[3] += x0.w * w;
-        acc[4] += x1.x * w; acc[5] += x1.y * w; acc[6] += x1.z * w; acc[7] += x1.w * w;
-      }
-    }
-    for (int off = 1; off < KS; off <<= 1) {
+      for (int i = 0; i < in; i++) {
+        T x[AW];
+        RowIO<T, AW>::ld(X + i * AW, x);
+        const T w0 = wa[i * ld], w1 = wb[i * ld];
 #pragma unroll
-      for (int q = 0; q < 8; q++) acc[q] += __shfl_xor_sync(0xffffffffu, acc[q], off);
-    }
-    if (j < out && ks == 0) {
-      const T bj = BIAS ? lv.B[j] : T(0);
-      T4 y0, y1;
-      y0.x = acc[0] + bj; y0.y = acc[1] + bj; y0.z = acc[2] + bj; y0.w = acc[3] + bj;
-      y1.x = acc[4] + bj; y1.y = acc[5] + bj; y1.z = acc[6] + bj; y1.w = acc[7] + bj;
-      if (TANH) {
-        y0.x = r_tanh(y0.x); y0.y = r_tanh(y0.y); y0.z = r_tanh(y0.z); y0.w = r_tanh(y0.w);
-        y1.x = r_tanh(y1.x); y1.y = r_tanh(y1.y); y1.z = r_tanh(y1.z); y1.w = r_tanh(y1.w);
+        for (int a = 0; a < AW; a++) { acc0[a] += w0 * x[a]; acc1[a] += w1 * x[a]; }
       }
-      *reinterpret_cast<T4*>(Y + j * TAP + a0) = y0;
-      *reinterpret_cast<T4*>(Y + j * TAP + a0 + 4) = y1;
+    } else {
+#pragma unroll 4
+      for (int i = 0; i < in; i++) {
+        T x[AW];
+        RowIO<T, AW>::ld(X + i * AW, x);
+        const T w0 = wa[i * ld];
+#pragma unroll
+        for (int a = 0; a < AW; a++) acc0[a] += w0 * x[a];
+      }
+    }
+    if (ja < out) {
+      const T b = BIAS ? lv.B[ja] : T(0);
+#pragma unroll
+      for (int a = 0; a < AW; a++) { acc0[a] += b; if (TANH) acc0[a] = ml_tanh(acc0[a]); }
+      RowIO<T, AW>::st(Y + ja * AW, acc0);
+    }
+    if (two && jb < out) {
+      const T b = BIAS ? lv.B[jb] : T(0);
+#pragma unroll
+      for (int a = 0; a < AW; a++) { acc1[a] += b; if (TANH) acc1[a] = ml_tanh(acc1[a]); }
+      RowIO<T, AW>::st(Y + jb * AW, acc1);
     }
   }
 }
 
-// Xo[i][a] = sum_j D[j][a] W[i,j]  (and the same for a second cotangent D2 -> Xo2 when given).  A thread
-// owns one input i for a group of eight atoms and one slice of the output range (quads of outputs dealt
-// KS <= 4 ways); lanes of a quarter-warp sit on consecutive inputs, which makes the 16-byte weight loads
-// conflict-free with the row stride of ml_ld().
-template <class T, int TA>
-__device__ __forceinline__ void dense_bwd(int in, int out, const LayerView<T> lv, const T* D, T* Xo, const T* D2,
-                                          T* Xo2) {
-  typedef typename Vec4<T>::type T4;
-  constexpr int TAP = TA + ML_PAD, NO = TA / 8;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, ld = lv.ld;
-  const int nq = (out + 3) >> 2;
-  int KS = 1;
-  while (KS < 4 && in * NO * KS < ML_THREADS && KS * 2 <= nq) KS <<= 1;
-  const int IL = 32 / KS, nig = (in + IL - 1) / IL;
-  const int il = lane & (IL - 1), ks = lane / IL;
-  __syncthreads();
-  for (int item = warp; item < nig * NO; item += ML_THREADS / 32) {
-    const int ig = item % nig, a0 = (item / nig) * 8;
-    const int i = ig * IL + il;
-    T a[8], b[8];
+// Xo[i][a] = sum_j D[j][a] W[i,j]  (and the same for a second cotangent D2 -> Xo2 when TWO), one warp, AW atoms;
+// a lane owns input i0+lane of every group of 32 and walks its weight row four columns at a time.
+template <class T, int AW, bool TWO>
+__device__ __forceinline__ void warp_dense_bwd(int in, int out, const LayerView<T> lv, const T* __restrict__ D,
+                                               T* __restrict__ Xo, const T* __restrict__ D2, T* __restrict__ Xo2,
+                                               int lane) {
+  const int ld = lv.ld;
+  for (int i0 = 0; i0 < in; i0 += 32) {
+    const int i = i0 + lane;
+    const T* wr = lv.W + (size_t)(i < in ? i : in - 1) * ld;  // a lane past the last input repeats the last row
+    T acc[AW], acc2[AW];
 #pragma unroll
-    for (int q = 0; q < 8; q++) a[q] = b[q] = T(0);
-    auto fma8 = [&](T* s, const T w, const T* src) {
-      const T4 d0 = *reinterpret_cast<const T4*>(src), d1 = *reinterpret_cast<const T4*>(src + 4);
-      s[0] += w * d0.x; s[1] += w * d0.y; s[2] += w * d0.z; s[3] += w * d0.w;
-      s[4] += w * d1.x; s[5] += w * d1.y; s[6] += w * d1.z; s[7] += w * d1.w;
-    };
+    for (int a = 0; a < AW; a++) acc[a] = acc2[a] = T(0);
+    int j = 0;
+#pragma unroll 2
+    for (; j + 4 <= out; j += 4) {
+      T w[4];
+      ml_ld4(wr + j, w);
+#pragma unroll
+      for (int r = 0; r < 4; r++) {
+        T d[AW];
+        RowIO<T, AW>::ld(D + (j + r) * AW, d);
+#pragma unroll
+        for (int a = 0; a < AW; a++) acc[a] += w[r] * d[a];
+        if (TWO) {
+          RowIO<T, AW>::ld(D2 + (j + r) * AW, d);
+#pragma unroll
+          for (int a = 0; a < AW; a++) acc2[a] += w[r] * d[a];
+        }
+      }
+    }
+    for (; j < out; j++) {
+      const T w = wr[j];
+      T d[AW];
+      RowIO<T, AW>::ld(D + j * AW, d);
+#pragma unroll
+      for (int a = 0; a < AW; a++) acc[a] += w * d[a];
+      if (TWO) {
+        RowIO<T, AW>::ld(D2 + j * AW, d);
+#pragma unroll
+        for (int a = 0; a < AW; a++) acc2[a] += w * d[a];
+      }
+    }
     if (i < in) {
-      for (int q4 = ks; q4 < nq; q4 += KS) {
-        const int j = q4 * 4;
-        T wv[4];
-        if (lv.vec) {
-          const T4 w = *reinterpret_cast<const T4*>(lv.W + i * ld + j);  // padding columns are zero
-          wv[0] = w.x; wv[1] = w.y; wv[2] = w.z; wv[3] = w.w;
-        } else {
-#pragma unroll
-          for (int r = 0; r < 4; r++) wv[r] = (j + r < out) ? lv.W[i * ld + j + r] : T(0);
-        }
-#pragma unroll
-        for (int r = 0; r < 4; r++) {
-          if (j + r < out) {
-            fma8(a, wv[r], D + (j + r) * TAP + a0);
-            if (D2) fma8(b, wv[r], D2 + (j + r) * TAP + a0);
-          }
-        }
-      }
-    }
-    for (int off = IL; off < 32; off <<= 1) {
-#pragma unroll
-      for (int q = 0; q < 8; q++) {
-        a[q] += __shfl_xor_sync(0xffffffffu, a[q], off);
-        if (D2) b[q] += __shfl_xor_sync(0xffffffffu, b[q], off);
-      }
-    }
-    if (i < in && ks == 0) {
-      T4 o;
-      o.x = a[0]; o.y = a[1]; o.z = a[2]; o.w = a[3];
-      *reinterpret_cast<T4*>(Xo + i * TAP + a0) = o;
-      o.x = a[4]; o.y = a[5]; o.z = a[6]; o.w = a[7];
-      *reinterpret_cast<T4*>(Xo + i * TAP + a0 + 4) = o;
-      if (D2) {
-        o.x = b[0]; o.y = b[1]; o.z = b[2]; o.w = b[3];
-        *reinterpret_cast<T4*>(Xo2 + i * TAP + a0) = o;
-        o.x = b[4]; o.y = b[5]; o.z = b[6]; o.w = b[7];
-        *reinterpret_cast<T4*>(Xo2 + i * TAP + a0 + 4) = o;
-      }
+      RowIO<T, AW>::st(Xo + i * AW, acc);
+      if (TWO) RowIO<T, AW>::st(Xo2 + i * AW, acc2);
     }
   }
-  __syncthreads();
 }
 
 // global row of atom slot a of this block (species t, first species-local index q0), or -1 past the end
@@ -222,103 +240,102 @@ __device__ __forceinline__ long long ml_atom_row(const ModelDev& md, int t, int 
   return (long long)b * md.N + md.shift[t] + (q - b * md.tipos[t]);
 }
 
-template <class T, int APT>
+// words of a warp's slice in the two kernels
+__host__ __device__ inline size_t ml_fwd_words(int Fm, int Hs, int mw, int AW) {
+  return (size_t)(Fm + Hs + 2 * mw) * AW;
+}
+__host__ __device__ inline size_t ml_bwd_words(int Fm, int Hs, int mw, int AW) {
+  return (size_t)(2 * Fm + 5 * Hs + 4 * mw) * AW;
+}
+
+// Forward: e_i, the activations for the backward kernel, the per-frame energy sums and netderiv = d(sum e)/dAF.
+// acts: [block][warp][Hs][AW], the warps' activation slices as they are.
+template <class T, int AW, bool WG>
 __global__ void __launch_bounds__(ML_THREADS)
     k_mlp_fwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ wpack, int wstride,
               const T* __restrict__ af, T* __restrict__ acts, T* __restrict__ e_atom, T* __restrict__ netderiv,
-              double* __restrict__ e_sum /*[nf] accumulated*/, int stage) {
-  constexpr int TA = 8 * APT, TAP = TA + ML_PAD;
+              double* __restrict__ e_sum /*[nf] accumulated*/, int stage, int wsm_words) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ long long rows[TA];
+  constexpr int TB = ML_WARPS * AW;
   int t, q0;
-  locate_block(md, nf, TA, t, q0);
+  locate_block(md, nf, TB, t, q0);
   const int nat = nf * md.tipos[t];
   const int F = md.Fr[t] + md.Fa[t], Lq = md.n_dense, Fm = md.Fmax, Hs = md.Hsum, mw = md.maxw;
-  T* X = reinterpret_cast<T*>(smem_raw);  // [Fm][TAP]
-  T* H = X + Fm * TAP;                    // [Hs][TAP]
-  T* C0 = H + Hs * TAP;                   // [mw][TAP]
-  T* C1 = C0 + mw * TAP;                  // [mw][TAP]
-  T* wsm = C1 + mw * TAP;                 // one staged layer
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  T* wsm = reinterpret_cast<T*>(smem_raw);  // staged layer(s)
+  T* X = wsm + wsm_words + (size_t)warp * ml_fwd_words(Fm, Hs, mw, AW);  // [Fm][AW]
+  T* H = X + Fm * AW;                                                    // [Hs][AW]
+  T* C0 = H + Hs * AW;                                                   // [mw][AW]
+  T* C1 = C0 + mw * AW;                                                  // [mw][AW]
   const T* mu = theta + md.off_mu[t];
   const T* w = wpack + (size_t)t * wstride;  // this species' packed layers
-  ML_CLK_INIT
-  if (threadIdx.x < TA) rows[threadIdx.x] = ml_atom_row(md, t, q0, nat, threadIdx.x);
-  if (stage == 2) stage_all_layers<T>(md, t, w, wsm);
-  chain_wait();  // the packed weights are older than the preceding kernel; everything read below is its output
-  __syncthreads();
-  ML_TICK(0, 0)
-  for (int idx = threadIdx.x; idx < F * TA; idx += ML_THREADS) {
-    const int i = idx % F, a = idx / F;  // consecutive threads read consecutive fingerprints of one atom
-    const long long gi = rows[a];
-    X[i * TAP + a] = gi >= 0 ? r_log(af[gi * Fm + i] + T(1e-3)) - mu[i] : T(0);
+  long long gi[AW];
+#pragma unroll
+  for (int a = 0; a < AW; a++) gi[a] = ml_atom_row(md, t, q0, nat, warp * AW + a);
+  if (!WG && stage == 2) {
+    int words = 0;
+    for (int l = 0; l < Lq; l++) words += ml_layer_words(md.in_of(t, l), md.width[l]);
+    stage_words<T>(w, wsm, words);
   }
-  ML_TICK(0, 1)
-  if (stage == 2) ml_stage_wait();
-  ML_TICK(0, 2)
+  chain_wait();  // the packed weights are older than the preceding kernel; everything read below is its output
+  // lanes on consecutive fingerprints of one atom
+#pragma unroll
+  for (int a = 0; a < AW; a++)
+    for (int i = lane; i < F; i += 32)
+      X[i * AW + a] = gi[a] >= 0 ? r_log(af[gi[a] * Fm + i] + T(1e-3)) - mu[i] : T(0);
+  if (!WG && stage == 2) {
+    __pipeline_wait_prior(0);
+    __syncthreads();
+  }
   const T* hin = X;
   LayerView<T> lv;
   for (int l = 0; l < Lq; l++) {
     const int in = md.in_of(t, l), out = md.width[l];
-    lv = get_layer<T>(md, t, l, w, wsm, stage);
-    if (stage == 2) __syncthreads();  // the layer's input is complete
-    T* hout = H + md.h_off(l) * TAP;
-    if (l < Lq - 1) dense_fwd<T, TA, true, true>(in, out, lv, hin, hout);
-    else dense_fwd<T, TA, false, true>(in, out, lv, hin, hout);
+    lv = get_layer<T, WG>(md, t, l, w, wsm, stage);
+    __syncwarp();
+    T* hout = H + md.h_off(l) * AW;
+    if (l < Lq - 1) warp_dense_fwd<T, AW, true, true>(in, out, lv, hin, hout, lane);
+    else warp_dense_fwd<T, AW, false, true>(in, out, lv, hin, hout, lane);
     hin = hout;
-    ML_TICK(0, 3 + (l < 3 ? l : 3))
   }
-  __syncthreads();
-  // activations, block-local feature-major copy for the backward kernel
-  T* ab = acts + (size_t)blockIdx.x * Hs * TA;
-  for (int idx = threadIdx.x; idx < Hs * TA; idx += ML_THREADS) ab[idx] = H[(idx / TA) * TAP + (idx % TA)];
-  if (threadIdx.x < TA) {
-    const long long gi = rows[threadIdx.x];
-    if (gi >= 0) e_atom[gi] = H[md.h_off(Lq - 1) * TAP + threadIdx.x];
-  }
-  if (threadIdx.x == 0) {
-    // per-frame sums of the block's atomic energies (a block's atoms are consecutive: one or two frames)
-    const T* eo = H + md.h_off(Lq - 1) * TAP;
-    double acc = 0.0;
-    long long bcur = -1;
-    for (int a = 0; a < TA; a++) {
-      const long long gi = rows[a];
-      if (gi < 0) break;
-      const long long b = gi / md.N;
-      if (b != bcur) {
-        if (bcur >= 0) atomicAdd(e_sum + bcur, acc);
-        acc = 0.0;
-        bcur = b;
-      }
-      acc += (double)eo[a];
+  __syncwarp();
+  // activations: the warp's slice as it is
+  T* ab = acts + ((size_t)blockIdx.x * ML_WARPS + warp) * Hs * AW;
+  for (int idx = lane; idx < Hs * AW; idx += 32) ab[idx] = H[idx];
+  if (lane < AW && gi[0] >= 0) {
+    long long g = gi[0];
+#pragma unroll
+    for (int a = 1; a < AW; a++)
+      if (lane == a) g = gi[a];
+    if (g >= 0) {
+      const T e = H[md.h_off(Lq - 1) * AW + lane];
+      e_atom[g] = e;
+      atomicAdd(e_sum + g / md.N, (double)e);  // per-frame sum of the atomic energies
     }
-    if (bcur >= 0) atomicAdd(e_sum + bcur, acc);
   }
-  ML_TICK(0, 7)
   // de/dx by the reverse sweep: cn = cotangent on the output of layer l
   T* cn = C0;
   T* cp = C1;
-  if (threadIdx.x < TA) cn[threadIdx.x] = T(1);
+  if (lane < AW) cn[lane] = T(1);
   for (int l = Lq - 1; l >= 0; l--) {
     const int in = md.in_of(t, l), out = md.width[l];
-    if (l < Lq - 1 || stage == 2) lv = get_layer<T>(md, t, l, w, wsm, stage);  // else: the last layer is still staged
-    __syncthreads();
+    if (l < Lq - 1 || WG || stage == 2) lv = get_layer<T, WG>(md, t, l, w, wsm, stage);  // else: still staged
+    __syncwarp();
     if (l < Lq - 1) {
-      const T* hl = H + md.h_off(l) * TAP;
-      for (int idx = threadIdx.x; idx < out * TA; idx += ML_THREADS) {
-        const int o = (idx / TA) * TAP + (idx % TA);
-        cn[o] *= (T(1) - hl[o] * hl[o]);
-      }
+      const T* hl = H + md.h_off(l) * AW;
+      for (int idx = lane; idx < out * AW; idx += 32) cn[idx] *= (T(1) - hl[idx] * hl[idx]);
+      __syncwarp();
     }
-    dense_bwd<T, TA>(in, out, lv, cn, cp, nullptr, nullptr);
+    warp_dense_bwd<T, AW, false>(in, out, lv, cn, cp, nullptr, nullptr, lane);
     T* tmp = cn; cn = cp; cp = tmp;
-    ML_TICK(0, 8 + (l < 3 ? l : 3))
   }
-  for (int idx = threadIdx.x; idx < Fm * TA; idx += ML_THREADS) {
-    const int i = idx % Fm, a = idx / Fm;
-    const long long gi = rows[a];
-    if (gi >= 0) netderiv[gi * Fm + i] = (i < F) ? cn[i * TAP + a] / (af[gi * Fm + i] + T(1e-3)) : T(0);
+  __syncwarp();
+#pragma unroll
+  for (int a = 0; a < AW; a++) {
+    if (gi[a] < 0) continue;
+    for (int i = lane; i < Fm; i += 32)
+      netderiv[gi[a] * Fm + i] = (i < F) ? cn[i * AW + a] / (af[gi[a] * Fm + i] + T(1e-3)) : T(0);
   }
-  ML_TICK(0, 12)
 }
 
 // Backward of  S = sum_a ebar[a]*e[a] + sum_{a,c} u[a,c]*netderiv[a,c]  with respect to the
@@ -327,167 +344,236 @@ __global__ void __launch_bounds__(ML_THREADS)
 // TensorFlow's autodiff does through grad_ene for the force loss (staf_model.py:191,225-228).
 // The kernel also contracts dL/dAF with the per-atom d(AF)/d(alpha) rows left by the AF sweep
 // (vrow), which yields the fingerprint part of dL/dalpha without another sweep over the triplets.
-template <class T, int APT>
+template <class T, int AW, bool WG>
 __global__ void __launch_bounds__(ML_THREADS)
     k_mlp_bwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ wpack, int wstride,
               const T* __restrict__ af, const T* __restrict__ acts, const T* __restrict__ ebar /*[nf]*/, const T* __restrict__ u /*[nf,N,Fmax]*/,
               const T* __restrict__ vrow /*[nf,N,nv] or null*/, int nv, T* __restrict__ gaf, T* __restrict__ grad,
-              int stage) {
-  typedef typename Vec4<T>::type T4;
-  constexpr int TA = 8 * APT, TAP = TA + ML_PAD;
+              int stage, int wsm_words) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ long long rows[TA];
+  constexpr int TB = ML_WARPS * AW;
+  __shared__ long long rows[TB];
   int t, q0;
-  locate_block(md, nf, TA, t, q0);
+  locate_block(md, nf, TB, t, q0);
   const int nat = nf * md.tipos[t];
   const int F = md.Fr[t] + md.Fa[t], Lq = md.n_dense, Fm = md.Fmax, Hs = md.Hsum, mw = md.maxw;
-  T* X = reinterpret_cast<T*>(smem_raw);  // [Fm][TAP] x
-  T* V = X + Fm * TAP;                    // [Fm][TAP] tangent on x
-  T* H = V + Fm * TAP;                    // [Hs][TAP] activations
-  T* HD = H + Hs * TAP;                   // tangents of the activations
-  T* AD = HD + Hs * TAP;                  // tangents of the pre-activations
-  T* DQ = AD + Hs * TAP;                  // cotangent on the pre-activation (first-order channel)
-  T* DP = DQ + Hs * TAP;                  // cotangent on the pre-activation tangent
-  T* CQ = DP + Hs * TAP;                  // [mw][TAP]
-  T* CP = CQ + mw * TAP;                  // [mw][TAP]
-  T* wsm = CP + mw * TAP;                 // one staged layer
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t slice = ml_bwd_words(Fm, Hs, mw, AW);
+  T* wsm = reinterpret_cast<T*>(smem_raw);  // staged layer(s)
+  T* base = wsm + wsm_words;
+  // offsets inside a warp's slice
+  const int oX = 0, oV = Fm * AW, oH = 2 * Fm * AW, oHD = oH + Hs * AW, oAD = oHD + Hs * AW, oDQ = oAD + Hs * AW,
+            oDP = oDQ + Hs * AW, oC = oDP + Hs * AW;  // then four [mw][AW] cotangent buffers
+  T* my = base + (size_t)warp * slice;
+  T* X = my + oX;    // x
+  T* V = my + oV;    // tangent on x
+  T* H = my + oH;    // activations
+  T* HD = my + oHD;  // tangents of the activations
+  T* AD = my + oAD;  // tangents of the pre-activations
+  T* DQ = my + oDQ;  // cotangents on the pre-activations, every layer (first-order channel)
+  T* DP = my + oDP;  // cotangents on the tangents of the pre-activations
   const T* mu = theta + md.off_mu[t];
   const T* w = wpack + (size_t)t * wstride;  // this species' packed layers
-  ML_CLK_INIT
-  if (threadIdx.x < TA) rows[threadIdx.x] = ml_atom_row(md, t, q0, nat, threadIdx.x);
-  if (stage == 2) stage_all_layers<T>(md, t, w, wsm);
+  long long gi[AW];
+#pragma unroll
+  for (int a = 0; a < AW; a++) gi[a] = ml_atom_row(md, t, q0, nat, warp * AW + a);
+  if (threadIdx.x < TB) rows[threadIdx.x] = ml_atom_row(md, t, q0, nat, threadIdx.x);
+  if (!WG && stage == 2) {
+    int words = 0;
+    for (int l = 0; l < Lq; l++) words += ml_layer_words(md.in_of(t, l), md.width[l]);
+    stage_words<T>(w, wsm, words);
+  }
   chain_wait();  // the packed weights are older than the preceding kernel; everything read below is its output
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < F * TA; idx += ML_THREADS) {
-    const int i = idx % F, a = idx / F;
-    const long long gi = rows[a];
-    T xv = T(0), vv = T(0);
-    if (gi >= 0) {
-      const T den = af[gi * Fm + i] + T(1e-3);
-      xv = r_log(den) - mu[i];
-      vv = u[gi * Fm + i] / den;
+#pragma unroll
+  for (int a = 0; a < AW; a++) {
+    for (int i = lane; i < F; i += 32) {
+      T xv = T(0), vv = T(0);
+      if (gi[a] >= 0) {
+        const T den = af[gi[a] * Fm + i] + T(1e-3);
+        xv = r_log(den) - mu[i];
+        vv = u[gi[a] * Fm + i] / den;
+      }
+      X[i * AW + a] = xv;
+      V[i * AW + a] = vv;
     }
-    X[i * TAP + a] = xv;
-    V[i * TAP + a] = vv;
   }
-  const T* ab = acts + (size_t)blockIdx.x * Hs * TA;
-  for (int idx = threadIdx.x; idx < Hs * TA; idx += ML_THREADS) {
-    const int a = idx % TA;
-    H[(idx / TA) * TAP + a] = (q0 + a < nat) ? ab[idx] : T(0);
+  {
+    const T* ab = acts + ((size_t)blockIdx.x * ML_WARPS + warp) * Hs * AW;
+    for (int idx = lane; idx < Hs * AW; idx += 32) {
+      long long g = gi[0];
+#pragma unroll
+      for (int a = 1; a < AW; a++)
+        if ((idx % AW) == a) g = gi[a];
+      H[idx] = g >= 0 ? ab[idx] : T(0);
+    }
   }
-  if (stage == 2) ml_stage_wait();
-  ML_TICK(1, 0)
+  if (!WG && stage == 2) {
+    __pipeline_wait_prior(0);
+    __syncthreads();
+  }
   // forward tangent: AD = HDin W ; HD = AD * act'
   const T* hdin = V;
   LayerView<T> lv;
   for (int l = 0; l < Lq; l++) {
     const int in = md.in_of(t, l), out = md.width[l];
-    lv = get_layer<T>(md, t, l, w, wsm, stage);
-    if (stage == 2) __syncthreads();  // the layer's input is complete
-    T* ado = AD + md.h_off(l) * TAP;
-    T* hdo = HD + md.h_off(l) * TAP;
-    dense_fwd<T, TA, false, false>(in, out, lv, hdin, ado);
-    __syncthreads();
-    const T* ho = H + md.h_off(l) * TAP;
-    for (int idx = threadIdx.x; idx < out * TA; idx += ML_THREADS) {
-      const int o = (idx / TA) * TAP + (idx % TA);
-      hdo[o] = (l < Lq - 1) ? ado[o] * (T(1) - ho[o] * ho[o]) : ado[o];
-    }
+    lv = get_layer<T, WG>(md, t, l, w, wsm, stage);
+    __syncwarp();
+    T* ado = AD + md.h_off(l) * AW;
+    T* hdo = HD + md.h_off(l) * AW;
+    warp_dense_fwd<T, AW, false, false>(in, out, lv, hdin, ado, lane);
+    __syncwarp();
+    const T* ho = H + md.h_off(l) * AW;
+    for (int idx = lane; idx < out * AW; idx += 32)
+      hdo[idx] = (l < Lq - 1) ? ado[idx] * (T(1) - ho[idx] * ho[idx]) : ado[idx];
     hdin = hdo;
   }
-  __syncthreads();
-  ML_TICK(1, 1)
-  // reverse over (h, hd)
-  if (threadIdx.x < TA) {
-    const long long gi = rows[threadIdx.x];
-    CQ[threadIdx.x] = gi >= 0 ? ebar[gi / md.N] : T(0);
-    CP[threadIdx.x] = gi >= 0 ? T(1) : T(0);
+  __syncwarp();
+  // reverse over (h, hd): (CQ, CP) = cotangents on (h, hd) of the current layer's output
+  T* CQ = my + oC;
+  T* CP = CQ + mw * AW;
+  T* CQn = CP + mw * AW;
+  T* CPn = CQn + mw * AW;
+  if (lane < AW) {
+    long long g = gi[0];
+#pragma unroll
+    for (int a = 1; a < AW; a++)
+      if (lane == a) g = gi[a];
+    CQ[lane] = g >= 0 ? ebar[g / md.N] : T(0);
+    CP[lane] = g >= 0 ? T(1) : T(0);
   }
-  T* gw = grad + md.off_w[t];
   for (int l = Lq - 1; l >= 0; l--) {
     const int in = md.in_of(t, l), out = md.width[l];
-    if (l < Lq - 1 || stage == 2) lv = get_layer<T>(md, t, l, w, wsm, stage);  // else: the last layer is still staged
-    __syncthreads();
-    const T* ho = H + md.h_off(l) * TAP;
-    const T* ado = AD + md.h_off(l) * TAP;
-    T* dql = DQ + md.h_off(l) * TAP;
-    T* dpl = DP + md.h_off(l) * TAP;
-    for (int idx = threadIdx.x; idx < out * TA; idx += ML_THREADS) {
-      const int o = (idx / TA) * TAP + (idx % TA);
+    if (l < Lq - 1 || WG || stage == 2) lv = get_layer<T, WG>(md, t, l, w, wsm, stage);  // else: still staged
+    __syncwarp();
+    const int ho_ = md.h_off(l) * AW;
+    const T* ho = H + ho_;
+    const T* ado = AD + ho_;
+    T* dql = DQ + ho_;
+    T* dpl = DP + ho_;
+    for (int idx = lane; idx < out * AW; idx += 32) {
       T qa, pa;
       if (l < Lq - 1) {
-        const T hh = ho[o], d1 = T(1) - hh * hh;
-        pa = CP[o] * d1;
-        qa = CQ[o] * d1 + CP[o] * (T(-2) * hh * d1 * ado[o]);
+        const T hh = ho[idx], d1 = T(1) - hh * hh;
+        pa = CP[idx] * d1;
+        qa = CQ[idx] * d1 + CP[idx] * (T(-2) * hh * d1 * ado[idx]);
       } else {
-        pa = CP[o];
-        qa = CQ[o];
+        pa = CP[idx];
+        qa = CQ[idx];
       }
-      dql[o] = qa;
-      dpl[o] = pa;
+      dql[idx] = qa;
+      dpl[idx] = pa;
     }
-    __syncthreads();
-    ML_TICK(1, 2)
-    // weight gradient of this layer, summed over the block's atoms: 2 inputs x 2 outputs per thread,
-    // atoms four at a time (the padded row stride keeps the 16-byte loads of consecutive rows conflict-free)
-    const T* hin = (l == 0) ? X : H + md.h_off(l - 1) * TAP;
-    const T* hdi = (l == 0) ? V : HD + md.h_off(l - 1) * TAP;
+    __syncwarp();
+    warp_dense_bwd<T, AW, true>(in, out, lv, dql, CQn, dpl, CPn, lane);
+    T* tq = CQ; CQ = CQn; CQn = tq;
+    T* tp = CP; CP = CPn; CPn = tp;
+  }
+  __syncwarp();
+  // CQ = dS/dx, CP = dS/dv  ->  dL/dAF, also kept in the free cotangent buffer G for the contraction below
+  T* G = CQn;
+#pragma unroll
+  for (int a = 0; a < AW; a++) {
+    for (int i = lane; i < Fm; i += 32) {
+      T g = T(0);
+      if (gi[a] >= 0 && i < F) {
+        const T den = af[gi[a] * Fm + i] + T(1e-3);
+        g = CQ[i * AW + a] / den + CP[i * AW + a] * (-u[gi[a] * Fm + i] / (den * den));
+      }
+      if (gi[a] >= 0) gaf[gi[a] * Fm + i] = g;
+      G[i * AW + a] = g;
+    }
+  }
+  const int oCQ = (int)(CQ - my), oG = (int)(G - my);  // the same in every warp (same number of swaps)
+  __syncthreads();
+  // ---- block-wide sums over the atoms of all warps
+  T* gw = grad + md.off_w[t];
+  // weight gradients of ALL layers in one pass: the 4 x 4 tiles (4 inputs x 4 outputs) of every layer are
+  // numbered consecutively and dealt to the threads, so that the small layers do not leave most of the block
+  // idle (rows past the end of a layer's last tile repeat its last row and are not written)
+  int tile_end[STAFB_MAX_DENSE];
+  {
+    int tot = 0;
+    for (int l = 0; l < STAFB_MAX_DENSE; l++) {
+      if (l < Lq) tot += ((md.in_of(t, l) + 3) >> 2) * ((md.width[l] + 3) >> 2);
+      tile_end[l] = tot;
+    }
+  }
+  for (int tile = threadIdx.x; tile < tile_end[STAFB_MAX_DENSE - 1]; tile += ML_THREADS) {
+    int l = 0;
+#pragma unroll
+    for (int q = 0; q < STAFB_MAX_DENSE - 1; q++) l += (tile >= tile_end[q]) ? 1 : 0;
+    int tbeg = 0;
+#pragma unroll
+    for (int q = 0; q < STAFB_MAX_DENSE - 1; q++)
+      if (q < l) tbeg = tile_end[q];
+    const int in = md.in_of(t, l), out = md.width[l];
+    const int oin = (l == 0) ? oX : oH + md.h_off(l - 1) * AW;
+    const int odi = (l == 0) ? oV : oHD + md.h_off(l - 1) * AW;
+    const int oq = oDQ + md.h_off(l) * AW, op = oDP + md.h_off(l) * AW;
     const int woff = md.w_off(t, l);
-    const int nj2 = (out + 1) >> 1, ni2 = (in + 1) >> 1;
-    for (int tile = threadIdx.x; tile < nj2 * ni2; tile += ML_THREADS) {
-      const int j0 = (tile % nj2) * 2, i0 = (tile / nj2) * 2;
-      const int j1 = j0 + 1 < out ? j0 + 1 : j0, i1 = i0 + 1 < in ? i0 + 1 : i0;
-      T g00 = T(0), g01 = T(0), g10 = T(0), g11 = T(0);
-      auto dot4 = [](const T4 x, const T4 y) { return x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w; };
+    const int nj4 = (out + 3) >> 2;
+    const int lt = tile - tbeg, itl = lt / nj4, jt = lt - itl * nj4;
+    const int j0 = jt << 2, i0 = itl << 2;
+    T g[16];
+#pragma unroll
+    for (int q = 0; q < 16; q++) g[q] = T(0);
+    int ir[4], jr[4];
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+      ir[r] = (i0 + r < in ? i0 + r : in - 1) * AW;
+      jr[r] = (j0 + r < out ? j0 + r : out - 1) * AW;
+    }
 #pragma unroll 2
-      for (int a = 0; a < TA; a += 4) {
-        const T4 h0 = *reinterpret_cast<const T4*>(hin + i0 * TAP + a), h1 = *reinterpret_cast<const T4*>(hin + i1 * TAP + a);
-        const T4 d0 = *reinterpret_cast<const T4*>(hdi + i0 * TAP + a), d1 = *reinterpret_cast<const T4*>(hdi + i1 * TAP + a);
-        const T4 qa0 = *reinterpret_cast<const T4*>(dql + j0 * TAP + a), qa1 = *reinterpret_cast<const T4*>(dql + j1 * TAP + a);
-        const T4 pa0 = *reinterpret_cast<const T4*>(dpl + j0 * TAP + a), pa1 = *reinterpret_cast<const T4*>(dpl + j1 * TAP + a);
-        g00 += dot4(h0, qa0) + dot4(d0, pa0);
-        g01 += dot4(h0, qa1) + dot4(d0, pa1);
-        g10 += dot4(h1, qa0) + dot4(d1, pa0);
-        g11 += dot4(h1, qa1) + dot4(d1, pa1);
+    for (int wv = 0; wv < ML_WARPS; wv++) {
+      const T* sb = base + (size_t)wv * slice;
+      T hv[4][AW], dv[4][AW];
+#pragma unroll
+      for (int r = 0; r < 4; r++) {
+        RowIO<T, AW>::ld(sb + oin + ir[r], hv[r]);
+        RowIO<T, AW>::ld(sb + odi + ir[r], dv[r]);
       }
-      atomicAdd(gw + woff + i0 * out + j0, g00);
-      if (j0 + 1 < out) atomicAdd(gw + woff + i0 * out + j0 + 1, g01);
-      if (i0 + 1 < in) {
-        atomicAdd(gw + woff + i1 * out + j0, g10);
-        if (j0 + 1 < out) atomicAdd(gw + woff + i1 * out + j0 + 1, g11);
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        T qv[AW], pv[AW];
+        RowIO<T, AW>::ld(sb + oq + jr[c], qv);
+        RowIO<T, AW>::ld(sb + op + jr[c], pv);
+#pragma unroll
+        for (int r = 0; r < 4; r++)
+#pragma unroll
+          for (int a = 0; a < AW; a++) g[4 * r + c] += hv[r][a] * qv[a] + dv[r][a] * pv[a];
       }
     }
-    // bias gradient
+#pragma unroll
+    for (int r = 0; r < 4; r++)
+#pragma unroll
+      for (int c = 0; c < 4; c++)
+        if (i0 + r < in && j0 + c < out) atomicAdd(gw + woff + (i0 + r) * out + j0 + c, g[4 * r + c]);
+  }
+  // bias gradients
+  for (int l = 0; l < Lq; l++) {
+    const int in = md.in_of(t, l), out = md.width[l];
+    const int oq = oDQ + md.h_off(l) * AW;
+    const int woff = md.w_off(t, l);
     for (int j = threadIdx.x; j < out; j += ML_THREADS) {
       T g = T(0);
-      for (int a = 0; a < TA; a++) g += dql[j * TAP + a];
+      for (int wv = 0; wv < ML_WARPS; wv++) {
+        const T* q = base + (size_t)wv * slice + oq + j * AW;
+#pragma unroll
+        for (int a = 0; a < AW; a++) g += q[a];
+      }
       atomicAdd(gw + woff + in * out + j, g);
     }
-    ML_TICK(1, 3)
-    // cotangents on the layer input
-    dense_bwd<T, TA>(in, out, lv, dql, CQ, dpl, CP);
-    ML_TICK(1, 4)
-  }
-  // CQ = dS/dx, CP = dS/dv  ->  dL/dAF, kept in V for the contraction below
-  for (int idx = threadIdx.x; idx < Fm * TA; idx += ML_THREADS) {
-    const int i = idx % Fm, a = idx / Fm;
-    const long long gi = rows[a];
-    T g = T(0);
-    if (gi >= 0 && i < F) {
-      const T den = af[gi * Fm + i] + T(1e-3);
-      g = CQ[i * TAP + a] / den + CP[i * TAP + a] * (-u[gi * Fm + i] / (den * den));
-    }
-    if (gi >= 0) gaf[gi * Fm + i] = g;
-    if (i < F) V[i * TAP + a] = g;
   }
   for (int i = threadIdx.x; i < F; i += ML_THREADS) {
     T g = T(0);
-    for (int a = 0; a < TA; a++) g -= CQ[i * TAP + a];
+    for (int wv = 0; wv < ML_WARPS; wv++) {
+      const T* q = base + (size_t)wv * slice + oCQ + i * AW;
+#pragma unroll
+      for (int a = 0; a < AW; a++) g -= q[a];
+    }
     atomicAdd(grad + md.off_mu[t] + i, g);
   }
-  ML_TICK(1, 5)
   if (vrow) {
-    __syncthreads();
     // dL/dalpha (fingerprint part) = sum_atoms dL/dAF[c(q)] * dAF[c(q)]/dalpha[q]; alpha2b and alpha3b
     // are contiguous in theta, q runs over both
     const int Fr = md.Fr[t], Fa = md.Fa[t], n2 = md.nt * Fr, nq = n2 + md.C * 3 * Fa;
@@ -502,12 +588,15 @@ __global__ void __launch_bounds__(ML_THREADS)
         qa = md.nt * md.Frmax + (s * md.Famax + (sc - s * Fa)) * 3 + (r - sc * 3);
       }
       T g = T(0);
-      for (int a = 0; a < TA; a++) {
-        const long long gi = rows[a];
-        if (gi >= 0) g += V[ch * TAP + a] * vrow[gi * nv + qa];
+      for (int wv = 0; wv < ML_WARPS; wv++) {
+        const T* gs = base + (size_t)wv * slice + oG + ch * AW;
+#pragma unroll
+        for (int a = 0; a < AW; a++) {
+          const long long r = rows[wv * AW + a];
+          if (r >= 0) g += gs[a] * vrow[r * nv + qa];
+        }
       }
       if (g != T(0)) atomicAdd(grad + md.off_a2[t] + q, g);
     }
   }
-  ML_TICK(1, 6)
 }

@@ -20,6 +20,10 @@
 #pragma once
 
 constexpr int MAXP = 4;  // channel PAIRS processed per pass over the pairs of a class
+// Exponential tables: entry (neighbour k, channel pair lp) at tab4[k * TSTR + lp].  Neighbour-major, so that the
+// entries of one neighbour are at constant offsets from one address; the odd stride (5 x 16 bytes) keeps the
+// 16-byte loads of lanes on consecutive neighbours free of bank conflicts.
+constexpr int TSTR = MAXP + 1;
 
 // ---- bulk asynchronous copy global -> shared, completion on an mbarrier (this GPU's own memory only)
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -204,7 +208,7 @@ static inline SweepSmem sweep_smem(const ModelDev& d, const SparLayout& sl, int 
   const int es = (int)sizeof(T);
   L.row = take(row_stride_bytes(nr, es));
   L.spar = take(sl.total);
-  L.tab = take(MAXP * nr * 4 * es);
+  L.tab = take(TSTR * nr * 4 * es);
   L.xtra = take(mode == MODE_FORCE ? 3 * nr * es : (mode == MODE_FGRAD ? 4 * nr * es : 0));
   L.acc = take((d.nt * d.Frmax + d.C * 3 * d.Famax + d.Famax) * es);
   L.rsum = take(d.nt * (d.Frmax > 0 ? d.Frmax : 1) * es);
@@ -240,26 +244,25 @@ __device__ __forceinline__ T multi_reduce(T (&v)[NV], int lane) {
 }
 
 // Pairs of a class as a rectangle of rows x cols walked 32 positions at a time without divisions.  Two different
-// species: rows = neighbours of ta, cols = neighbours of tb.  One species with n neighbours: the strict upper
-// triangle j < k folded into a rectangle - row r of the triangle (n-1-r entries) is followed by row n-1-r (n even)
-// or n-2-r (n odd), which together have n-1 (n) entries.
+// species (SAME == false): rows = neighbours of ta, cols = neighbours of tb.  One species with n neighbours: the
+// strict upper triangle j < k folded into a rectangle - row r of the triangle (n-1-r entries) is followed by row
+// n-1-r (n even) or n-2-r (n odd), which together have n-1 (n) entries.
+template <bool SAME>
 struct PairWalk {
   int r, c, cols, q32, r32, nm1, odd;
-  bool same;
-  __device__ __forceinline__ void init(bool same_, int na, int nb, int lane) {
-    same = same_;
+  __device__ __forceinline__ void init(int na, int nb, int lane) {
     odd = na & 1;
     nm1 = na - 1;
-    cols = same ? (odd ? na : na - 1) : nb;
+    cols = SAME ? (odd ? na : na - 1) : nb;
     if (cols < 1) cols = 1;
     r = lane / cols;
     c = lane - r * cols;
     q32 = 32 / cols;
     r32 = 32 - q32 * cols;
   }
-  __device__ __forceinline__ static int count(bool same_, int na, int nb) { return same_ ? na * (na - 1) / 2 : na * nb; }
+  __device__ __forceinline__ static int count(int na, int nb) { return SAME ? na * (na - 1) / 2 : na * nb; }
   __device__ __forceinline__ void get(int& j, int& k) const {
-    if (same) {
+    if (SAME) {
       const bool first = c < nm1 - r;
       j = first ? r : nm1 - odd - r;
       k = first ? r + 1 + c : c + 1 - odd;
@@ -277,14 +280,14 @@ struct PairWalk {
 
 // ---- unordered pairs: fingerprints (AF), fingerprints + d(AF)/d(alpha) (AFV), backward of the forces (FGRAD).
 // Per-lane sums r[v][lp] (v = 0: fingerprint / gradnet, 1..3: alpha1, alpha2, beta terms) for NCHP channel pairs.
-template <class T, int MODE, int NCHP>
+template <class T, int MODE, int NCHP, bool SAME>
 __device__ __forceinline__ void pairs_unordered(const typename Vec4<T>::type* __restrict__ U,
                                                 const typename Vec4<T>::type* __restrict__ V,
                                                 const typename Vec4<T>::type* __restrict__ dF,
                                                 const typename Vec4<T>::type* __restrict__ tab4, int nr,
                                                 const typename Vec4<T>::type* __restrict__ chq,
-                                                const typename Vec4<T>::type* __restrict__ chr, bool same, int oa,
-                                                int ob, int na_, int nb_, int lane,
+                                                const typename Vec4<T>::type* __restrict__ chr, int oa, int ob,
+                                                int na_, int nb_, int lane,
                                                 typename Vec2<T>::type (&r0)[NCHP], typename Vec2<T>::type (&r1)[NCHP],
                                                 typename Vec2<T>::type (&r2)[NCHP],
                                                 typename Vec2<T>::type (&r3)[NCHP]) {
@@ -293,9 +296,9 @@ __device__ __forceinline__ void pairs_unordered(const typename Vec4<T>::type* __
 #pragma unroll
   for (int lp = 0; lp < NCHP; lp++) r0[lp] = r1[lp] = r2[lp] = r3[lp] = mk2(T(0), T(0));
   const T2 one2 = mk2(T(1), T(1));
-  const int np = PairWalk::count(same, na_, nb_);
-  PairWalk pw;
-  pw.init(same, na_, nb_, lane);
+  const int np = PairWalk<SAME>::count(na_, nb_);
+  PairWalk<SAME> pw;
+  pw.init(na_, nb_, lane);
   // beta*log2(e) of every channel pair stays in registers in the fingerprint modes
   T2 bsc[NCHP];
   if (MODE != MODE_FGRAD) {
@@ -317,7 +320,7 @@ __device__ __forceinline__ void pairs_unordered(const typename Vec4<T>::type* __
     if (MODE != MODE_FGRAD) {
 #pragma unroll
       for (int lp = 0; lp < NCHP; lp++) {
-        const T4 A = tab4[lp * nr + j], B = tab4[lp * nr + k];
+        const T4 A = tab4[j * TSTR + lp], B = tab4[k * TSTR + lp];
         const T2 S1 = p_mul(mk2(A.z, A.w), mk2(B.x, B.y));  // exp(a2*sj + a1*sk)
         const T2 S2 = p_mul(mk2(A.x, A.y), mk2(B.z, B.w));  // exp(a1*sj + a2*sk)
         const T2 cm = p_mul(p_ex(p_mul(bsc[lp], tt2)), tt2);  // t*exp(beta*t)
@@ -332,9 +335,11 @@ __device__ __forceinline__ void pairs_unordered(const typename Vec4<T>::type* __
     } else {
       // Backward of the triplet force for the cotangent dF_k = Fbar_k - Fbar_i (dF.w = dF . u).  With
       //   Q  = d(t)/d(positions) . dF  (symmetric in j,k),  Pj = fc'_j (dF_j . u_j),  Pk likewise,
-      //   S1 = exp(a2 sj + a1 sk), S2 = exp(a1 sj + a2 sk), E = exp(beta t), X1 = a1 S2 + a2 S1, X2 = a1 S1 + a2 S2,
-      // the channel's gradnet term is  g0 = E [ (1 + beta t) (Q/2) (S1+S2) + (t/2)(X1 Pj + X2 Pk) ]  and the
-      // parameter terms are its derivatives with respect to alpha1, alpha2, beta
+      //   Z1 = E exp(a1 sj + a2 sk), Z2 = E exp(a2 sj + a1 sk), E = exp(beta t), g = 1 + beta t,
+      //   H1 = g Q/2 + (t/2)(a1 Pj + a2 Pk),  H2 = g Q/2 + (t/2)(a1 Pk + a2 Pj)
+      // the channel's gradnet term is  Z1 H1 + Z2 H2  (the two orderings of the pair) and the parameter terms are
+      // its derivatives:  d/da1 = Z1 (sj H1 + t Pj/2) + Z2 (sk H2 + t Pk/2),  d/da2 with sj, sk and Pj, Pk
+      // exchanged inside each bracket,  d/dbeta = t [Z1 (H1 + Q/2) + Z2 (H2 + Q/2)]
       // (STAF/src/grad_force/ang/reforce.cu.cc:47-231).
       const T4 pj = V[j], pk = V[k];
       const T hf = T(0.5) * fcj * fck;
@@ -350,107 +355,100 @@ __device__ __forceinline__ void pairs_unordered(const typename Vec4<T>::type* __
       const T2 Qh2 = mk2(Qh, Qh), Pj2 = mk2(Pjh, Pjh), Pk2 = mk2(Pkh, Pkh);
 #pragma unroll
       for (int lp = 0; lp < NCHP; lp++) {
-        const T4 A = tab4[lp * nr + j], B = tab4[lp * nr + k], cq = chq[lp], cr = chr[lp];
+        const T4 A = tab4[j * TSTR + lp], B = tab4[k * TSTR + lp], cq = chq[lp], cr = chr[lp];
         const T2 al1 = mk2(cq.x, cq.y), al2 = mk2(cq.z, cq.w);
-        const T2 S1 = p_mul(mk2(A.z, A.w), mk2(B.x, B.y));
-        const T2 S2 = p_mul(mk2(A.x, A.y), mk2(B.z, B.w));
         const T2 E = p_ex(p_mul(mk2(cr.z, cr.w), tt2));
-        const T2 gQ = p_mul(p_fma(mk2(cr.x, cr.y), tt2, one2), Qh2);  // (1 + beta t) Q/2
-        const T2 ss = p_add(S1, S2);
-        const T2 Y1 = p_mul(al1, S2), Y2 = p_mul(al2, S1), Z1 = p_mul(al1, S1), Z2 = p_mul(al2, S2);
-        const T2 t0 = p_fma(gQ, ss, p_fma(p_add(Y1, Y2), Pj2, p_mul(p_add(Z1, Z2), Pk2)));
-        r0[lp] = p_fma(E, t0, r0[lp]);
-        const T2 d1j = p_fma(fcj2, Y1, p_fma(fck2, Y2, S2)), d1k = p_fma(fck2, Z1, p_fma(fcj2, Z2, S1));
-        const T2 t1 = p_fma(gQ, p_fma(fcj2, S2, p_mul(fck2, S1)), p_fma(Pj2, d1j, p_mul(Pk2, d1k)));
-        r1[lp] = p_fma(E, t1, r1[lp]);
-        const T2 d2j = p_fma(fck2, Y1, p_fma(fcj2, Y2, S1)), d2k = p_fma(fcj2, Z1, p_fma(fck2, Z2, S2));
-        const T2 t2 = p_fma(gQ, p_fma(fck2, S2, p_mul(fcj2, S1)), p_fma(Pj2, d2j, p_mul(Pk2, d2k)));
-        r2[lp] = p_fma(E, t2, r2[lp]);
-        r3[lp] = p_fma(p_mul(E, tt2), p_fma(Qh2, ss, t0), r3[lp]);
+        const T2 Z1 = p_mul(E, p_mul(mk2(A.x, A.y), mk2(B.z, B.w)));
+        const T2 Z2 = p_mul(E, p_mul(mk2(A.z, A.w), mk2(B.x, B.y)));
+        const T2 gQ = p_mul(p_fma(mk2(cr.x, cr.y), tt2, one2), Qh2);
+        const T2 H1 = p_fma(al1, Pj2, p_fma(al2, Pk2, gQ)), H2 = p_fma(al1, Pk2, p_fma(al2, Pj2, gQ));
+        r0[lp] = p_fma(Z1, H1, p_fma(Z2, H2, r0[lp]));
+        r1[lp] = p_fma(Z1, p_fma(fcj2, H1, Pj2), p_fma(Z2, p_fma(fck2, H2, Pk2), r1[lp]));
+        r2[lp] = p_fma(Z1, p_fma(fck2, H1, Pk2), p_fma(Z2, p_fma(fcj2, H2, Pj2), r2[lp]));
+        r3[lp] = p_fma(tt2, p_fma(Z1, p_add(H1, Qh2), p_mul(Z2, p_add(H2, Qh2))), r3[lp]);
       }
     }
   }
 }
 
-// ---- ordered pairs (owner j, partner k): forces.  Each lane takes a contiguous run of the row-major list of
-// (owner, partner) pairs, keeps the owner's data - including its table entries already multiplied by the
-// channel weights - and its force accumulator in registers and flushes when the owner changes.
-// fo[k*3 + a]: force on neighbour k; (fix, fiy, fiz): force on the central atom.
-template <class T, int NCHP>
+// ---- ordered pairs (owner j, partner k): forces.  The list of an owner's partners is cut into S segments and
+// every lane takes one (owner, segment): the owner's data - including its table entries already multiplied by the
+// channel weights - and its force accumulator stay in registers for the whole segment, all lanes run the same
+// number of iterations, and the accumulators are flushed once per round (S lanes share an owner).  S in 1..4 is
+// chosen per class to fill the 32 lanes.  fo[k*3 + a]: force on neighbour k; (fix, fiy, fiz): on the centre.
+template <class T, int NCHP, bool SAME>
 __device__ __forceinline__ void pairs_force(const typename Vec4<T>::type* __restrict__ U,
                                             const typename Vec4<T>::type* __restrict__ V,
-                                            const typename Vec4<T>::type* __restrict__ tab4, int nr,
+                                            const typename Vec4<T>::type* __restrict__ tab4,
                                             const typename Vec4<T>::type* __restrict__ chq,
                                             const typename Vec4<T>::type* __restrict__ chr,
-                                            const typename Vec2<T>::type* __restrict__ wch, bool same, int oo, int op,
-                                            int no, int npt, int lane, T* __restrict__ fo, T& fix, T& fiy, T& fiz) {
+                                            const typename Vec2<T>::type* __restrict__ wch, int oo, int op, int no,
+                                            int npt, int lane, T* __restrict__ fo, T& fix, T& fiy, T& fiz) {
   typedef typename Vec4<T>::type T4;
   typedef typename Vec2<T>::type T2;
-  const int E = no * npt;
-  const int cchunk = (E + 31) >> 5;
-  int e0 = lane * cchunk, e1 = e0 + cchunk;
-  if (e1 > E) e1 = E;
-  if (e0 >= e1) return;
+  if (no <= 0 || npt <= 0) return;
+  // segments per owner: fewest (iterations + 2) * rounds; the 2 stands for loading the owner and flushing
+  int S = 1, seg = npt, best = 0x7fffffff;
+#pragma unroll
+  for (int s = 1; s <= 4; s++) {
+    const int sg = (npt + s - 1) / s, rounds = (no * s + 31) >> 5, cost = rounds * (sg + 2);
+    if (cost < best) { best = cost; S = s; seg = sg; }
+  }
+  const int nseg = no * S;
   const T2 one2 = mk2(T(1), T(1));
-  int ja = e0 / npt, kb = e0 - ja * npt;
-  int j = oo + ja;
-  T4 uj;
-  T rinvj, gfcj;
-  T2 a1w[NCHP], a2w[NCHP], b1w[NCHP], b2w[NCHP];  // w*A1_j, w*A2_j, alpha1*w*A1_j, alpha2*w*A2_j
-  auto load_owner = [&]() {
-    uj = U[j];
+  for (int base = 0; base < nseg; base += 32) {
+    const int sidx = base + lane;
+    const bool active = sidx < nseg;
+    const int ow = active ? ((S == 1) ? sidx : (S == 2) ? (sidx >> 1) : (S == 4) ? (sidx >> 2) : (sidx * 21846) >> 16) : 0;
+    const int k0 = (sidx - ow * S) * seg;
+    const int j = oo + ow;
+    const T4 uj = U[j];
     const T4 vj = V[j];
-    rinvj = vj.x;
-    gfcj = vj.y;
+    const T rinvj = vj.x, gfcj = vj.y;
+    T2 a1w[NCHP], a2w[NCHP], b1w[NCHP], b2w[NCHP];  // w*A1_j, w*A2_j, alpha1*w*A1_j, alpha2*w*A2_j
 #pragma unroll
     for (int lp = 0; lp < NCHP; lp++) {
-      const T4 A = tab4[lp * nr + j], cq = chq[lp];
+      const T4 A = tab4[j * TSTR + lp], cq = chq[lp];
       const T2 w = wch[lp];
       a1w[lp] = p_mul(mk2(A.x, A.y), w);
       a2w[lp] = p_mul(mk2(A.z, A.w), w);
       b1w[lp] = p_mul(mk2(cq.x, cq.y), a1w[lp]);
       b2w[lp] = p_mul(mk2(cq.z, cq.w), a2w[lp]);
     }
-  };
-  load_owner();
-  T ax = T(0), ay = T(0), az = T(0), as = T(0);
-  for (int e = e0; e < e1; e++) {
-    const int kk = (same && kb >= ja) ? kb + 1 : kb;
-    const int k = op + kk;
-    const T4 uk = U[k];
-    const T cs = uj.x * uk.x + uj.y * uk.y + uj.z * uk.z;
-    const T half = T(0.5) * cs + T(0.5);
-    const T tt = half * uj.w * uk.w;
-    const T2 tt2 = mk2(tt, tt);
-    T2 D2 = mk2(T(0), T(0)), BJ2 = mk2(T(0), T(0));
+    T ax = T(0), ay = T(0), az = T(0), as = T(0);
+    // this lane's partners [k0, k1); for one species the owner itself is skipped: partner kb >= ow is row kb + 1
+    const int k1 = active ? ((k0 + seg < npt) ? k0 + seg : npt) : k0;
+    for (int kb = k0; kb < k1; kb++) {
+      {
+        const int k = op + kb + ((SAME && kb >= ow) ? 1 : 0);
+        const T4 uk = U[k];
+        const T cs = uj.x * uk.x + uj.y * uk.y + uj.z * uk.z;
+        const T half = T(0.5) * cs + T(0.5);
+        const T tt = half * uj.w * uk.w;
+        const T2 tt2 = mk2(tt, tt);
+        T2 D2 = mk2(T(0), T(0)), BJ2 = mk2(T(0), T(0));
 #pragma unroll
-    for (int lp = 0; lp < NCHP; lp++) {
-      const T4 B = tab4[lp * nr + k], cr = chr[lp];
-      const T2 A1k = mk2(B.x, B.y), A2k = mk2(B.z, B.w);
-      const T2 Ex2 = p_ex(p_mul(mk2(cr.z, cr.w), tt2));
-      const T2 sum = p_fma(a1w[lp], A2k, p_mul(a2w[lp], A1k));            // w (S2 + S1)
-      D2 = p_fma(p_mul(p_fma(mk2(cr.x, cr.y), tt2, one2), Ex2), sum, D2);  // w e^{bt} (1 + bt) (S1 + S2)
-      BJ2 = p_fma(Ex2, p_fma(b1w[lp], A2k, p_mul(b2w[lp], A1k)), BJ2);     // w e^{bt} (a1 S2 + a2 S1)
+        for (int lp = 0; lp < NCHP; lp++) {
+          const T4 B = tab4[k * TSTR + lp], cr = chr[lp];
+          const T2 A1k = mk2(B.x, B.y), A2k = mk2(B.z, B.w);
+          const T2 Ex2 = p_ex(p_mul(mk2(cr.z, cr.w), tt2));
+          const T2 sum = p_fma(a1w[lp], A2k, p_mul(a2w[lp], A1k));            // w (S2 + S1)
+          D2 = p_fma(p_mul(p_fma(mk2(cr.x, cr.y), tt2, one2), Ex2), sum, D2);  // w e^{bt} (1 + bt) (S1 + S2)
+          BJ2 = p_fma(Ex2, p_fma(b1w[lp], A2k, p_mul(b2w[lp], A1k)), BJ2);     // w e^{bt} (a1 S2 + a2 S1)
+        }
+        const T D = D2.x + D2.y, BJ = (BJ2.x + BJ2.y) * tt;
+        // f_ij = cjk*u_k + (...)*u_j
+        const T cjk = D * T(0.5) * uj.w * uk.w * rinvj;
+        ax += cjk * uk.x; ay += cjk * uk.y; az += cjk * uk.z;
+        as += -cs * cjk + gfcj * (D * half * uk.w + BJ);
+      }
     }
-    const T D = D2.x + D2.y, BJ = (BJ2.x + BJ2.y) * tt;
-    // f_ij = cjk*u_k + (...)*u_j
-    const T cjk = D * T(0.5) * uj.w * uk.w * rinvj;
-    ax += cjk * uk.x; ay += cjk * uk.y; az += cjk * uk.z;
-    as += -cs * cjk + gfcj * (D * half * uk.w + BJ);
-    kb++;
-    if (kb == npt || e + 1 == e1) {
+    if (active) {
       const T fx = ax + as * uj.x, fy = ay + as * uj.y, fz = az + as * uj.z;
       atomicAdd(&fo[j * 3 + 0], fx);
       atomicAdd(&fo[j * 3 + 1], fy);
       atomicAdd(&fo[j * 3 + 2], fz);
       fix -= fx; fiy -= fy; fiz -= fz;
-      ax = ay = az = as = T(0);
-      if (kb == npt && e + 1 < e1) {
-        kb = 0;
-        ja++;
-        j = oo + ja;
-        load_owner();
-      }
     }
   }
 }
@@ -648,7 +646,7 @@ __global__ void __launch_bounds__(32, SweepMinBlocks<MODE, sizeof(T)>::value)
         if (q == tb) { nb_ = cntA[q]; ob = off[q]; }
       }
       const bool same = (ta == tb);
-      const int np = PairWalk::count(same, na_, nb_);
+      const int np = same ? na_ * (na_ - 1) / 2 : na_ * nb_;
       if (np <= 0 || s >= md.ncls) continue;
       const int nact = nact_s[s];
       const int npair = (nact + 1) >> 1;
@@ -670,7 +668,7 @@ __global__ void __launch_bounds__(32, SweepMinBlocks<MODE, sizeof(T)>::value)
               const T2 e1 = p_ex(p_mul(mk2(q.x, q.y), f2)), e2 = p_ex(p_mul(mk2(q.z, q.w), f2));
               T4 v;
               v.x = e1.x; v.y = e1.y; v.z = e2.x; v.w = e2.y;
-              tab4[lp * nr + k] = v;
+              tab4[k * TSTR + lp] = v;
             }
           }
         }
@@ -682,11 +680,16 @@ __global__ void __launch_bounds__(32, SweepMinBlocks<MODE, sizeof(T)>::value)
             const int oo = pass == 0 ? oa : ob, op = pass == 0 ? ob : oa;
             const int no = pass == 0 ? na_ : nb_;
             const int npt = same ? na_ - 1 : (pass == 0 ? nb_ : na_);
+            auto go = [&](auto tag) {
+              constexpr int NCHP = decltype(tag)::value;
+              if (same) pairs_force<T, NCHP, true>(U, V, tab4, chq, chr, wch, oo, op, no, npt, lane, xtra, fix, fiy, fiz);
+              else pairs_force<T, NCHP, false>(U, V, tab4, chq, chr, wch, oo, op, no, npt, lane, xtra, fix, fiy, fiz);
+            };
             switch (nchp) {
-              case 1: pairs_force<T, 1>(U, V, tab4, nr, chq, chr, wch, same, oo, op, no, npt, lane, xtra, fix, fiy, fiz); break;
-              case 2: pairs_force<T, 2>(U, V, tab4, nr, chq, chr, wch, same, oo, op, no, npt, lane, xtra, fix, fiy, fiz); break;
-              case 3: pairs_force<T, 3>(U, V, tab4, nr, chq, chr, wch, same, oo, op, no, npt, lane, xtra, fix, fiy, fiz); break;
-              default: pairs_force<T, 4>(U, V, tab4, nr, chq, chr, wch, same, oo, op, no, npt, lane, xtra, fix, fiy, fiz); break;
+              case 1: go(std::integral_constant<int, 1>()); break;
+              case 2: go(std::integral_constant<int, 2>()); break;
+              case 3: go(std::integral_constant<int, 3>()); break;
+              default: go(std::integral_constant<int, 4>()); break;
             }
           }
         } else {
@@ -700,7 +703,8 @@ __global__ void __launch_bounds__(32, SweepMinBlocks<MODE, sizeof(T)>::value)
           auto run = [&](auto nchp_tag) {
             constexpr int NCHP = decltype(nchp_tag)::value;
             T2 r0[NCHP], r1[NCHP], r2[NCHP], r3[NCHP];
-            pairs_unordered<T, MODE, NCHP>(U, V, dF, tab4, nr, chq, chr, same, oa, ob, na_, nb_, lane, r0, r1, r2, r3);
+            if (same) pairs_unordered<T, MODE, NCHP, true>(U, V, dF, tab4, nr, chq, chr, oa, ob, na_, nb_, lane, r0, r1, r2, r3);
+            else pairs_unordered<T, MODE, NCHP, false>(U, V, dF, tab4, nr, chq, chr, oa, ob, na_, nb_, lane, r0, r1, r2, r3);
             if (MODE == MODE_AF) {
               constexpr int NV = NCHP == 1 ? 2 : (NCHP == 2 ? 4 : 8);
               T v[NV];

