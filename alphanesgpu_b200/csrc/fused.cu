@@ -86,13 +86,18 @@ __device__ __forceinline__ T huber_d(T e) { return e > T(1) ? T(1) : (e < T(-1) 
 
 // Start-of-evaluation housekeeping in one launch: zero-fills up to three buffers (sizes in bytes, multiples of
 // 4) and writes the packed, padded copy of the Dense layers that the MLP kernels stage (layout: mlp.cuh).
-// It also packs the per-species parameter blocks of the sweeps (sweep.cuh): one warp per (species, class).
+// It also packs the per-species parameter blocks of the sweeps (sweep.cuh): one warp per (species, class), and
+// copies the force labels of a training evaluation into device scratch.
 template <class T>
 __global__ void k_prep(ModelDev md, const T* __restrict__ theta, const T* __restrict__ emb, T* __restrict__ wpack,
                        int wstride, unsigned char* __restrict__ spar, int spar_stride, SparLayout sl, void* a,
-                       size_t na, void* b, size_t nb, void* c, size_t nc) {
+                       size_t na, void* b, size_t nb, void* c, size_t nc, const T* __restrict__ flab_src,
+                       T* __restrict__ flab_dst, size_t nflab) {
   chain_wait();
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  // force labels into device scratch: the backward sweep gathers them per neighbour, and the caller's copy may
+  // be mapped host memory (the host-buffer entry points), which is to be read exactly once
+  for (size_t q = tid; q < nflab; q += st) flab_dst[q] = flab_src[q];
   {
     const int gw = (int)(tid >> 5), lane = threadIdx.x & 31;
     if (gw < md.nt * md.ncls) {
@@ -125,29 +130,28 @@ __global__ void k_prep(ModelDev md, const T* __restrict__ theta, const T* __rest
   }
 }
 
-// One launch for everything between the force sweep and the backward sweeps.  Blocks [0,nf):
-// frame energy E_b = 0.5*mean_i e_i (or 0.5*sum), energy loss and the cotangent on the atomic
-// energies.  Blocks [nf, nf+fb): force loss and dL/dF.  Last block: bound loss
-// sum(alpha*[alpha>bound]) over alpha2b and alpha3b (Keras ReLU(threshold):
-// staf_models/staf_model.py:60-62,215-219) and its gradient.  The block that finishes last adds up
-// the total.  losses = {loss, loss_e, loss_bound, loss_f, done-counter}.
+// Losses of an evaluation in one launch.  Blocks [0,nf): frame energy E_b = 0.5*mean_i e_i (or 0.5*sum), energy
+// loss and the cotangent on the atomic energies.  Blocks [nf, nf+fb): force loss (the backward sweep forms dL/dF
+// itself, huber_d below is shared with it).  Last block: bound loss sum(alpha*[alpha>bound]) over alpha2b and
+// alpha3b (Keras ReLU(threshold): staf_models/staf_model.py:60-62,215-219) and its gradient.  The block that
+// finishes last adds up the total.  losses = {loss, loss_e, loss_bound, loss_f, done-counter}.
+// In a training evaluation the kernel is launched AFTER the backward sweep of the forces, which does not need
+// it: everything it reads (forces, atomic energies, theta) is at least two kernels old, so every block does its
+// loads, arithmetic and reductions under the sweep's tail and waits for the chain only before its first global
+// write.  In an inference evaluation it directly follows the force sweep; only the virial needs that one.
 template <class T>
 __global__ void __launch_bounds__(256)
     k_loss(ModelDev md, int nf, int fb, int per_atom, int train, const T* __restrict__ e_atom, T* __restrict__ energy,
            const T* __restrict__ e_label, const T* __restrict__ force, const T* __restrict__ f_label,
            const T* __restrict__ theta, T pe, T pf, T pb, T bound, int loss_kind, T* __restrict__ ebar,
-           T* __restrict__ fbar, T* __restrict__ grad, double* __restrict__ losses, int* status,
-           int* status_main, const double* __restrict__ vacc, T* __restrict__ virial_out, double* __restrict__ mirror) {
+           T* __restrict__ grad, double* __restrict__ losses, int* status, int* status_main,
+           const double* __restrict__ vacc, T* __restrict__ virial_out, double* __restrict__ mirror) {
   __shared__ double red[9];
   const int N = md.N;
   const int blk = blockIdx.x;
-  // Only the force blocks (and the virial) need the force sweep that precedes this kernel; the frame energies
-  // come from the MLP kernel two launches back and the bound term from theta, so those blocks do their loads and
-  // arithmetic under the sweep's tail and wait for it only before their first global write.
-  const bool needs_pred = (blk >= nf && blk < nf + fb) || (blk < nf && virial_out);
+  const bool needs_pred = (blk < nf && virial_out);
   if (needs_pred) chain_wait();
   if (blk < nf) {
-    // loads and arithmetic first, every global write after the wait below
     double Eb = 0.0;
     T le = T(0), de = T(0);
     if (threadIdx.x == 0) {
@@ -172,13 +176,12 @@ __global__ void __launch_bounds__(256)
   } else if (blk < nf + fb) {
     const size_t n = (size_t)nf * 3 * N;
     double s = 0.0;
-    const T scale = pf / T((double)n);
     for (size_t q = (size_t)(blk - nf) * blockDim.x + threadIdx.x; q < n; q += (size_t)fb * blockDim.x) {
       const T e = force[q] - f_label[q];
       s += (double)(loss_kind == 0 ? huber(e) : e * e);
-      fbar[q] = scale * (loss_kind == 0 ? huber_d(e) : T(2) * e);
     }
     s = block_sum<double, 8>(s, red);
+    chain_wait();
     if (threadIdx.x == 0) atomicAdd(losses + 3, s / (double)n);
   } else {
     // bound term: the sum under the predecessor's tail, the gradient contributions after the wait
@@ -281,7 +284,7 @@ struct stafb_model {
   int stage;  // Dense layers in shared memory: 2 all at kernel start, 1 one at a time, 0 none
   size_t mlp_fwd_smem, mlp_bwd_smem;
   // scratch for max_batch frames
-  void *rows, *af, *nd, *acts, *e_atom, *force, *fbar, *ebar, *gradnet, *gaf, *energy, *vrow;
+  void *rows, *af, *nd, *acts, *e_atom, *force, *flab, *ebar, *gradnet, *gaf, *energy, *vrow;
   int row_stride;      // bytes per neighbour record (common.cuh)
   unsigned char* spar;  // per-species parameter blocks of the sweeps, rewritten by k_prep at every evaluation
   SparLayout sl;
@@ -433,7 +436,7 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   STAFB_CUDA_OK(cudaMalloc(&m->wpack, es * (size_t)d.nt * m->wstride));
   STAFB_CUDA_OK(cudaMalloc(&m->e_atom, es * A));
   STAFB_CUDA_OK(cudaMalloc(&m->force, es * A * 3));
-  STAFB_CUDA_OK(cudaMalloc(&m->fbar, es * A * 3));
+  STAFB_CUDA_OK(cudaMalloc(&m->flab, es * A * 3));  // device copy of the force labels (k_prep)
   STAFB_CUDA_OK(cudaMalloc(&m->ebar, es * c->max_batch));
   STAFB_CUDA_OK(cudaMalloc(&m->energy, es * c->max_batch));
   STAFB_CUDA_OK(cudaMalloc((void**)&m->losses_d, sizeof(double) * (8 + 10 * (size_t)c->max_batch)));
@@ -453,7 +456,7 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
 extern "C" void stafb_model_destroy(stafb_model* m) {
   if (!m) return;
   void* ptrs[] = {m->rows, m->spar, m->af, m->nd, m->gradnet, m->gaf, m->acts, m->e_atom, m->force,
-                  m->fbar, m->ebar, m->energy, m->losses_d, m->vrow, m->wpack};
+                  m->flab, m->ebar, m->energy, m->losses_d, m->vrow, m->wpack};
   for (void* p : ptrs) cudaFree(p);
   for (int k = 0; k < 3; k++) {
     cudaFreeHost(m->slot_in_h[k]);
@@ -518,7 +521,10 @@ struct SweepCall {
   const void* rows;
   int nf, nall;
   const T* chan_in;
-  const T* fbar;
+  const T* force;  // force-backward sweep: the forces, their labels and the loss's scale (dL/dF is formed on the fly)
+  const T* flab;
+  T fscale;
+  int loss_kind;
   T* out;
   T* grad;
   T* vout;
@@ -550,7 +556,8 @@ static int launch_sweep(stafb_model* m, cudaStream_t s, const SweepCall<T>& call
   a.spar = m->spar;
   a.spar_stride = m->sl.total;
   a.sl = m->sl;
-  a.chan_in = call.chan_in; a.fbar = call.fbar; a.out = call.out; a.grad = call.grad;
+  a.chan_in = call.chan_in; a.force = call.force; a.flab = call.flab; a.fscale = call.fscale;
+  a.loss_kind = call.loss_kind; a.out = call.out; a.grad = call.grad;
   a.vout = call.vout; a.nv = m->nv; a.vir = call.vir; a.status = call.status;
   const int blocks = call.nf * d.N;
   if (MODE == MODE_FORCE && call.vir)
@@ -687,7 +694,8 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
       k_prep<T>, 64, 256, 0, s, d, theta, emb, (T*)m->wpack, m->wstride, m->spar, m->sl.total, m->sl, (void*)force,
       sizeof(T) * (size_t)nf * 3 * nall,
       train ? (void*)grad : (void*)nullptr, train ? sizeof(T) * (size_t)m->n_params : (size_t)0, (void*)m->losses_d,
-      sizeof(double) * (virial_out ? 8 + 10 * (size_t)c->max_batch : 8 + (size_t)c->max_batch)));
+      sizeof(double) * (virial_out ? 8 + 10 * (size_t)c->max_batch : 8 + (size_t)c->max_batch),
+      train ? f_label : (const T*)nullptr, (T*)m->flab, train ? (size_t)nf * 3 * N : (size_t)0));
   c->launches++;
   mark();  // descriptors
   SweepCall<T> sc;
@@ -706,6 +714,17 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
   rc = launch_sweep<T, MODE_FORCE>(m, s, sc);
   if (rc != STAFB_OK) return rc;
   mark();  // force
+  if (train) {
+    // the backward sweep of the forces forms dL/dF = pf/(3 nf N) * L'(F - F_label) per component itself, so the loss
+    // kernel is off the path between the two sweeps and runs under this sweep's tail
+    T* gradnet = (T*)m->gradnet;
+    sc.chan_in = nd; sc.force = force; sc.flab = (const T*)m->flab; sc.loss_kind = loss_kind;
+    sc.fscale = (T)pf / T((double)((size_t)nf * 3 * N));
+    sc.out = gradnet; sc.grad = grad; sc.vir = nullptr;
+    rc = launch_sweep<T, MODE_FGRAD>(m, s, sc);
+    if (rc != STAFB_OK) return rc;
+    mark();  // force_grad
+  }
   {
     int fb = 0;
     if (train) {
@@ -714,21 +733,16 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
     }
     const int grid = nf + fb + (train ? 1 : 0);
     STAFB_CUDA_OK(launch_chained(k_loss<T>, grid, 256, 0, s, d, nf, fb, per_atom, train ? 1 : 0, e_atom, energy,
-                                 e_label, force, f_label, theta, (T)pe, (T)pf, (T)pb, (T)bound, loss_kind,
-                                 (T*)m->ebar, (T*)m->fbar, grad, m->losses_d, cg->status_d, c->status_d, vacc,
-                                 virial_out, train ? m->mirror_next : (double*)nullptr));
+                                 e_label, force, (const T*)m->flab, theta, (T)pe, (T)pf, (T)pb, (T)bound, loss_kind,
+                                 (T*)m->ebar, grad, m->losses_d, cg->status_d, c->status_d, vacc, virial_out,
+                                 train ? m->mirror_next : (double*)nullptr));
     m->mirror_next = nullptr;
     c->launches++;
   }
   mark();  // loss
   if (train) {
-    T* gradnet = (T*)m->gradnet;
     T* gaf = (T*)m->gaf;
-    sc.chan_in = nd; sc.fbar = (const T*)m->fbar; sc.out = gradnet; sc.grad = grad; sc.vir = nullptr;
-    rc = launch_sweep<T, MODE_FGRAD>(m, s, sc);
-    if (rc != STAFB_OK) return rc;
-    mark();  // force_grad
-    rc = launch_mlp_bwd<T>(m, s, nf, theta, af, acts, (const T*)m->ebar, gradnet, gaf, grad);
+    rc = launch_mlp_bwd<T>(m, s, nf, theta, af, acts, (const T*)m->ebar, (const T*)m->gradnet, gaf, grad);
     if (rc != STAFB_OK) return rc;
     mark();  // mlp_bwd
     if (losses_out != m->losses_d)
@@ -805,7 +819,7 @@ static int ensure_nl(stafb_ctx* c, stafb_model* m, int slot) {
   if (q.ctx) return STAFB_OK;
   int rc = stafb_create(&q.ctx, c->dtype, c->Rc, c->Rs, c->Ra, c->nr, c->na, c->n_max, c->max_batch);
   if (rc != STAFB_OK) { q.ctx = nullptr; return rc; }
-  const size_t es = m->es, A = (size_t)c->max_batch * c->n_max, nr = c->nr;
+  const size_t A = (size_t)c->max_batch * c->n_max;
   STAFB_CUDA_OK(cudaMalloc(&q.rows, A * (size_t)m->row_stride));
   STAFB_CUDA_OK(cudaMemset(q.rows, 0, A * (size_t)m->row_stride));
   STAFB_CUDA_OK(cudaEventCreateWithFlags(&q.ready, cudaEventDisableTiming));

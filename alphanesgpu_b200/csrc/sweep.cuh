@@ -187,7 +187,10 @@ struct SweepArgs {
   int spar_stride;
   SparLayout sl;
   const T* chan_in;  // FORCE/FGRAD: netderiv[nf,N,Fmax]
-  const T* fbar;     // FGRAD: dL/dF[nf,3*nall]
+  const T* force;    // FGRAD: forces [nf,3*nall] and their labels; dL/dF = fscale * L'(force - label) with L the
+  const T* flab;     //        Huber (loss_kind 0) or the squared error
+  T fscale;
+  int loss_kind;
   T* out;            // AF/AFV: af[nf,N,Fmax]; FORCE: force[nf,3*nall]; FGRAD: gradnet[nf,N,Fmax]
   T* grad;           // FGRAD: flat parameter gradient (accumulated)
   T* vout;           // AFV: d(AF)/d(alpha) rows [nf,N,nv] in the accumulator layout (alpha2b[nt,Frmax] | alpha3b[C,3*Famax])
@@ -517,10 +520,19 @@ __global__ void __launch_bounds__(32, SweepMinBlocks<MODE, sizeof(T)>::value)
   // what the preceding kernels produced for this atom, fetched while the copies are in flight
   const T* chrow = a.chan_in ? a.chan_in + gi * Fmax : nullptr;
   T fbx = T(0), fby = T(0), fbz = T(0);
-  const T* fb = nullptr;
+  // dL/dF of one force component (the loss kernel's formula: Keras Huber(delta = 1) or squared error, mean)
+  const T* fo_g = nullptr;
+  const T* fl_g = nullptr;
+  const T fscale = a.fscale;
+  const bool hub = a.loss_kind == 0;
+  auto fbar_of = [&](int q) -> T {
+    const T e = fo_g[q] - fl_g[q];
+    return fscale * (hub ? (e > T(1) ? T(1) : (e < T(-1) ? T(-1) : e)) : T(2) * e);
+  };
   if (MODE == MODE_FGRAD) {
-    fb = a.fbar + (size_t)b * a.nall * 3;
-    fbx = fb[i * 3]; fby = fb[i * 3 + 1]; fbz = fb[i * 3 + 2];
+    fo_g = a.force + (size_t)b * a.nall * 3;
+    fl_g = a.flab + (size_t)b * a.nall * 3;
+    fbx = fbar_of(i * 3); fby = fbar_of(i * 3 + 1); fbz = fbar_of(i * 3 + 2);
   }
   if (!mbar_wait(bar, 0)) {
     if (lane == 0) set_status(a.status, STAFB_ERR_STAGE_TIMEOUT);
@@ -542,7 +554,7 @@ __global__ void __launch_bounds__(32, SweepMinBlocks<MODE, sizeof(T)>::value)
       const int id = ids[k];
       const T4 u = U[k];
       T4 d;
-      d.x = fb[id * 3] - fbx; d.y = fb[id * 3 + 1] - fby; d.z = fb[id * 3 + 2] - fbz;
+      d.x = fbar_of(id * 3) - fbx; d.y = fbar_of(id * 3 + 1) - fby; d.z = fbar_of(id * 3 + 2) - fbz;
       d.w = d.x * u.x + d.y * u.y + d.z * u.z;
       dF[k] = d;
     }

@@ -200,7 +200,9 @@ class StafModel:
                                          float(beta1), float(beta2), float(eps), self.step, float(grad_scale)),
               "stafb_adam_step")
 
-    PHASES = ["descriptors", "af_fwd", "mlp_fwd", "force", "loss", "force_grad", "mlp_bwd", "af_grad"]
+    # order of the phase marks of a training evaluation / of an inference evaluation
+    PHASES = ["descriptors", "af_fwd", "mlp_fwd", "force", "force_grad", "loss", "mlp_bwd"]
+    PHASES_INFERENCE = ["descriptors", "af_fwd", "mlp_fwd", "force", "loss"]
 
     def adam_update_dev(self, lr, beta1=0.9, beta2=0.999, eps=1e-7, grad_scale=1.0):
         """Adam with the step counter on the device (safe to capture in a CUDA graph and replay)."""
@@ -217,7 +219,8 @@ class StafModel:
     def phase_times_ms(self):
         buf = np.zeros(16, np.float32)
         n = _lib.lib().stafb_get_phase_times(self.ctx.h, buf.ctypes.data_as(C.c_void_p), 16)
-        return dict(zip(self.PHASES[:n], buf[:n].tolist()))
+        names = self.PHASES if n > len(self.PHASES_INFERENCE) else self.PHASES_INFERENCE
+        return dict(zip(names[:n], buf[:n].tolist()))
 
     def mlp_config(self):
         """(staging mode, atoms per thread group, forward smem bytes, backward smem bytes) of the MLP kernels."""

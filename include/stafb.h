@@ -358,14 +358,13 @@ int stafb_train_step_host_end(stafb_ctx* ctx, stafb_model* m, int slot, double* 
 
 /* ---- diagnostics ----------------------------------------------------------------------------
  * The entry points from here to the end of the header are measurement aids of this library (no reference
- * counterpart, not part of the operator surface): phase timers, a measured FMA peak, a launch counter.  A
- * build with -DSTAFB_SWEEP_CLOCKS additionally exports stafb_sweep_clocks / stafb_mlp_clocks (in-kernel cycle
- * counters per phase of the sweep and MLP kernels); the default build does not contain them. */
+ * counterpart, not part of the operator surface): phase timers, a measured FMA peak, a launch counter. */
 
-/* Per-phase device timing of the fused calls, with CUDA events on the launching stream.  Phases, in
- * order: descriptors, af_fwd, mlp_fwd, force, loss, force_grad, mlp_bwd, af_grad (the last four only for
- * stafb_train_step).  stafb_get_phase_times waits for the last event, writes up to cap durations in
- * milliseconds and returns how many.  Not for use while the stream is being captured. */
+/* Per-phase device timing of the fused calls, with CUDA events on the launching stream.  Phases, in order, of a
+ * training evaluation: descriptors, af_fwd, mlp_fwd, force, force_grad, loss, mlp_bwd; of an inference
+ * evaluation: descriptors, af_fwd, mlp_fwd, force, loss.  stafb_get_phase_times waits for the last event,
+ * writes up to cap durations in milliseconds and returns how many.  Not for use while the stream is being
+ * captured. */
 int stafb_set_phase_timing(stafb_ctx* ctx, int on);
 int stafb_get_phase_times(stafb_ctx* ctx, float* ms, int cap);
 
