@@ -154,8 +154,11 @@ __global__ void __launch_bounds__(256)
   if (blk < nf) {
     double Eb = 0.0;
     T le = T(0), de = T(0);
+    // sum of the frame's atomic energies (the MLP kernel is at least two kernels back)
+    double s = 0.0;
+    for (int q = threadIdx.x; q < N; q += blockDim.x) s += (double)e_atom[(size_t)blk * N + q];
+    s = block_sum<double, 8>(s, red);
     if (threadIdx.x == 0) {
-      const double s = losses[8 + blk];  // sum of the frame's atomic energies, accumulated by the MLP kernel
       Eb = per_atom ? 0.5 * s / N : 0.5 * s;
       if (train) {
         const T e = (T)Eb - e_label[blk];
@@ -398,12 +401,14 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   m->aw = 0;
   int nsm = 148;
   cudaDeviceGetAttribute(&nsm, cudaDevAttrMultiProcessorCount, dev);
-  // Atoms per warp of the MLP kernels and where the Dense layers live.  Wanted: every SM busy (4 atoms per warp
-  // only if that still gives one block per SM, else 2) and all layers staged in shared memory at kernel start
+  // Atoms per warp of the MLP kernels and where the Dense layers live.  Wanted: many resident warps (4 atoms per
+  // warp only if that still gives four blocks per SM, else 2: the kernels are latency-bound until the GPU is full,
+  // and the backward kernel's slices at 4 atoms per warp leave room for one block per SM only) and all layers
+  // staged in shared memory at kernel start
   // (2); what does not fit falls back to one layer at a time (1), then to fewer atoms per warp, then to reading
   // the weights from global memory (0).
   const size_t mlp_room = m->smem_limit - 1024;  // the backward kernel also holds a little static shared memory
-  const int aw_pref = species_blocks(d, c->max_batch, ML_WARPS * 4) >= nsm ? 4 : 2;
+  const int aw_pref = species_blocks(d, c->max_batch, ML_WARPS * 4) >= 4 * nsm ? 4 : 2;
   const int cand[7][2] = {{aw_pref, 2}, {aw_pref, 1}, {2, 1}, {1, 1}, {aw_pref, 0}, {2, 0}, {1, 0}};
   m->stage = 0;
   for (int k = 0; k < 7 && !m->aw; k++)
@@ -592,7 +597,7 @@ static int launch_mlp_fwd_t(stafb_model* m, cudaStream_t s, int nf, const T* the
   }
   STAFB_CUDA_OK(launch_chained(k_mlp_fwd<T, AW, WG>, species_blocks(m->md, nf, ML_WARPS * AW), ML_THREADS,
                                m->mlp_fwd_smem, s, m->md, nf, theta, (const T*)m->wpack, m->wstride, af, acts, e_atom,
-                               nd, m->losses_d + 8, m->stage, (int)mlp_stage_words(m->md, m->stage)));
+                               nd, m->stage, (int)mlp_stage_words(m->md, m->stage)));
   m->ctx->launches++;
   return STAFB_OK;
 }

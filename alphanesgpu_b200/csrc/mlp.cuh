@@ -248,13 +248,13 @@ __host__ __device__ inline size_t ml_bwd_words(int Fm, int Hs, int mw, int AW) {
   return (size_t)(2 * Fm + 5 * Hs + 4 * mw) * AW;
 }
 
-// Forward: e_i, the activations for the backward kernel, the per-frame energy sums and netderiv = d(sum e)/dAF.
+// Forward: e_i, the activations for the backward kernel and netderiv = d(sum e)/dAF.
 // acts: [block][warp][Hs][AW], the warps' activation slices as they are.
 template <class T, int AW, bool WG>
 __global__ void __launch_bounds__(ML_THREADS)
     k_mlp_fwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ wpack, int wstride,
               const T* __restrict__ af, T* __restrict__ acts, T* __restrict__ e_atom, T* __restrict__ netderiv,
-              double* __restrict__ e_sum /*[nf] accumulated*/, int stage, int wsm_words) {
+              int stage, int wsm_words) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int TB = ML_WARPS * AW;
   int t, q0;
@@ -307,11 +307,7 @@ __global__ void __launch_bounds__(ML_THREADS)
 #pragma unroll
     for (int a = 1; a < AW; a++)
       if (lane == a) g = gi[a];
-    if (g >= 0) {
-      const T e = H[md.h_off(Lq - 1) * AW + lane];
-      e_atom[g] = e;
-      atomicAdd(e_sum + g / md.N, (double)e);  // per-frame sum of the atomic energies
-    }
+    if (g >= 0) e_atom[g] = H[md.h_off(Lq - 1) * AW + lane];  // the loss kernel sums them per frame
   }
   // de/dx by the reverse sweep: cn = cotangent on the output of layer l
   T* cn = C0;
@@ -540,7 +536,10 @@ __global__ void __launch_bounds__(ML_THREADS)
 #pragma unroll
         for (int r = 0; r < 4; r++)
 #pragma unroll
-          for (int a = 0; a < AW; a++) g[4 * r + c] += hv[r][a] * qv[a] + dv[r][a] * pv[a];
+          for (int a = 0; a < AW; a++) {
+            g[4 * r + c] += hv[r][a] * qv[a];
+            g[4 * r + c] += dv[r][a] * pv[a];
+          }
       }
     }
 #pragma unroll

@@ -216,7 +216,7 @@ static inline SweepSmem sweep_smem(const ModelDev& d, const SparLayout& sl, int 
   L.acc = take((d.nt * d.Frmax + d.C * 3 * d.Famax + d.Famax) * es);
   L.rsum = take(d.nt * (d.Frmax > 0 ? d.Frmax : 1) * es);
   L.wch = take(mode == MODE_FORCE ? d.ncls * sl.maxp * 2 * es : 0);
-  L.red = take(32 * es);
+  L.red = take(32 * es);  // group offsets
   L.mbar = take(16);
   L.total = o;
   return L;
@@ -308,7 +308,10 @@ __device__ __forceinline__ void pairs_unordered(const typename Vec4<T>::type* __
 #pragma unroll
     for (int lp = 0; lp < NCHP; lp++) { const T4 cr = chr[lp]; bsc[lp] = mk2(cr.z, cr.w); }
   }
-#pragma unroll 2
+  // pairs in flight per lane: two hide the shared-memory and exponential latencies of the fingerprint loops; the
+  // force-backward loop is too large for that (its unrolled body falls out of the instruction cache)
+  constexpr int PAIR_UNROLL = (MODE == MODE_FGRAD) ? 1 : 2;
+#pragma unroll PAIR_UNROLL
   for (int p = lane; p < np; p += 32) {
     int jj, kk;
     pw.get(jj, kk);
@@ -490,7 +493,7 @@ __global__ void __launch_bounds__(32, SweepMinBlocks<MODE, sizeof(T)>::value)
   T* acc = reinterpret_cast<T*>(smem_raw + L.acc);
   T* rsum = reinterpret_cast<T*>(smem_raw + L.rsum);
   T2* wch_all = reinterpret_cast<T2*>(smem_raw + L.wch);
-  T* red = reinterpret_cast<T*>(smem_raw + L.red);
+  int* off = reinterpret_cast<int*>(smem_raw + L.red);  // [STAFB_MAX_TYPES + 1]
   const unsigned bar = smem_addr(smem_raw + L.mbar);
   // accumulator regions: the first nv entries are the d(AF)/d(alpha) row of the AFV mode
   const int ACC_A2 = 0;                      // [nt*Frmax]  alpha2b terms
@@ -540,13 +543,16 @@ __global__ void __launch_bounds__(32, SweepMinBlocks<MODE, sizeof(T)>::value)
   }
   int n = hdr[0];
   if (n > nr) n = nr;
-  int cntA[STAFB_MAX_TYPES], off[STAFB_MAX_TYPES + 1];
-  off[0] = 0;
-#pragma unroll
-  for (int q = 0; q < STAFB_MAX_TYPES; q++) {
-    cntA[q] = (q < nt) ? hdr[6 + q] : 0;
-    off[q + 1] = off[q] + ((q < nt) ? hdr[2 + q] : 0);
+  // first entry of every species' group (kept in shared memory like the counts, not in registers)
+  if (lane == 0) {
+    int o = 0;
+    for (int q = 0; q < STAFB_MAX_TYPES; q++) {
+      off[q] = o;
+      o += (q < nt) ? hdr[2 + q] : 0;
+    }
+    off[STAFB_MAX_TYPES] = o;
   }
+  __syncwarp();
   if (MODE == MODE_FGRAD) {
     // dF_k = Fbar_k - Fbar_i and its projection on the unit vector
     T4* dF = reinterpret_cast<T4*>(xtra);
@@ -612,10 +618,7 @@ __global__ void __launch_bounds__(32, SweepMinBlocks<MODE, sizeof(T)>::value)
         T gn = T(0), ga = T(0);
         if (rp.z != T(0)) {
           const T als = rp.x, al = rp.y;
-          int r0_ = 0, r1_ = 0;
-#pragma unroll
-          for (int qq = 0; qq < STAFB_MAX_TYPES; qq++)
-            if (qq == q) { r0_ = off[qq]; r1_ = off[qq + 1]; }
+          const int r0_ = off[q], r1_ = off[q + 1];
           const T4* dF = reinterpret_cast<const T4*>(xtra);
 #pragma unroll 4
           for (int r = r0_; r < r1_; r++) {
@@ -651,12 +654,7 @@ __global__ void __launch_bounds__(32, SweepMinBlocks<MODE, sizeof(T)>::value)
   for (int ta = 0; ta < nt; ta++) {
     for (int tb = ta; tb < nt; tb++) {
       const int s = ta + tb;
-      int na_ = 0, nb_ = 0, oa = 0, ob = 0;
-#pragma unroll
-      for (int q = 0; q < STAFB_MAX_TYPES; q++) {
-        if (q == ta) { na_ = cntA[q]; oa = off[q]; }
-        if (q == tb) { nb_ = cntA[q]; ob = off[q]; }
-      }
+      const int na_ = hdr[6 + ta], nb_ = hdr[6 + tb], oa = off[ta], ob = off[tb];
       const bool same = (ta == tb);
       const int np = same ? na_ * (na_ - 1) / 2 : na_ * nb_;
       if (np <= 0 || s >= md.ncls) continue;
@@ -769,7 +767,6 @@ __global__ void __launch_bounds__(32, SweepMinBlocks<MODE, sizeof(T)>::value)
     }
   }
   __syncwarp();
-  (void)red;
 
   // ------------------------------------------------------------------ write-back
   if (IS_AF) {
