@@ -65,6 +65,15 @@ __global__ void __launch_bounds__(256)
   __shared__ int ok_s;
   chain_wait();  // the gradient is the output of the kernel before this one
   const int step = *reinterpret_cast<volatile int*>(step_d) + 1;  // the update being applied; equal on all ranks
+  // everything that does not need the peers is done while thread 0 waits for them: this rank's own values and
+  // the step's learning-rate factor (two double-precision powers)
+  const int q = blockIdx.x * blockDim.x + threadIdx.x;
+  T g_own = T(0), m_old = T(0), v_old = T(0), th_old = T(0);
+  if (q < n && threadIdx.x != 0) {
+    g_own = reinterpret_cast<const T*>(pv.grad[pv.rank])[q];
+    m_old = m[q]; v_old = v[q]; th_old = theta[q];
+  }
+  const T lr_t = (T)(lr * sqrt(1.0 - pow(b2, (double)step)) / (1.0 - pow(b1, (double)step)));
   if (threadIdx.x == 0) {
     if (blockIdx.x == 0) {
       __threadfence_system();  // this rank's gradient (complete at the kernel boundary) before the flags
@@ -96,7 +105,10 @@ __global__ void __launch_bounds__(256)
   }
   __syncthreads();
   const int ok = ok_s;
-  const int q = blockIdx.x * blockDim.x + threadIdx.x;
+  if (q < n && threadIdx.x == 0) {  // thread 0 was busy with the flags
+    g_own = reinterpret_cast<const T*>(pv.grad[pv.rank])[q];
+    m_old = m[q]; v_old = v[q]; th_old = theta[q];
+  }
   if (ok && q < n) {
     // all peers' loads are issued before the first add (one NVLink round trip, not one per rank); the sum is
     // taken in rank order, so every rank computes the same bits
@@ -106,7 +118,7 @@ __global__ void __launch_bounds__(256)
       gv[r] = T(0);
       if (r < pv.world) {
         const T* gr = reinterpret_cast<const T*>(pv.grad[r]);
-        gv[r] = (r == pv.rank) ? gr[q] : ld_peer(gr + q);
+        gv[r] = (r == pv.rank) ? g_own : ld_peer(gr + q);
       }
     }
     T g = T(0);
@@ -114,12 +126,11 @@ __global__ void __launch_bounds__(256)
     for (int r = 0; r < PEER_MAX; r++)
       if (r < pv.world) g += gv[r];
     g *= T(1) / T(pv.world);
-    const T lr_t = (T)(lr * sqrt(1.0 - pow(b2, (double)step)) / (1.0 - pow(b1, (double)step)));
-    const T mm = (T)b1 * m[q] + (T(1) - (T)b1) * g;
-    const T vv = (T)b2 * v[q] + (T(1) - (T)b2) * g * g;
+    const T mm = (T)b1 * m_old + (T(1) - (T)b1) * g;
+    const T vv = (T)b2 * v_old + (T(1) - (T)b2) * g * g;
     m[q] = mm;
     v[q] = vv;
-    theta[q] -= lr_t * mm / (r_sqrt(vv) + eps);
+    theta[q] = th_old - lr_t * mm / (r_sqrt(vv) + eps);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
