@@ -69,6 +69,24 @@ _SIGS = {
     "stafb_peer_grad": [_vp, _i],
     "stafb_peer_set_wait_ms": [_vp, C.c_longlong],
     "stafb_peer_destroy": [_vp],
+    "stafb_halo_create": [_vp, _i, _i, _i, _i, _vp],
+    "stafb_halo_handle": [_vp, _vp],
+    "stafb_halo_connect": [_vp, _vp],
+    "stafb_halo_connect_local": [_vp, _vp],
+    "stafb_halo_positions": [_vp],
+    "stafb_halo_forces": [_vp],
+    "stafb_halo_set_wait_ms": [_vp, C.c_longlong],
+    "stafb_halo_set_plan": [_vp, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _i],
+    "stafb_halo_plan_select": [_vp, _vp, _i, _vp, _i, _d, _d],
+    "stafb_halo_plan_layout": [_vp, _vp, _vp],
+    "stafb_halo_plan_done": [_vp, _vp],
+    "stafb_halo_plan_finish": [_vp, _vp, _vp],
+    "stafb_halo_push_positions": [_vp, _vp],
+    "stafb_halo_wait_positions": [_vp, _vp],
+    "stafb_halo_return_forces": [_vp, _vp, _vp, _vp],
+    "stafb_halo_collect": [_vp, _vp, _vp, _vp],
+    "stafb_halo_status": [_vp],
+    "stafb_halo_destroy": [_vp],
     "stafb_allreduce_adam": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _d, _d, _d, _d, _vp],
     "stafb_train_step_host": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _i, _vp, _vp],
     "stafb_train_step_host_begin": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _i, _vp, _i],
@@ -98,8 +116,9 @@ def lib():
                 continue
             fn.argtypes = sig
             fn.restype = None if name in ("stafb_destroy", "stafb_model_destroy", "stafb_core_coefficients",
-                                          "stafb_model_offsets", "stafb_peer_destroy", "stafb_model_mlp_config") else _i
-            if name == "stafb_peer_grad":
+                                          "stafb_model_offsets", "stafb_peer_destroy", "stafb_model_mlp_config",
+                                          "stafb_halo_destroy") else _i
+            if name in ("stafb_peer_grad", "stafb_halo_positions", "stafb_halo_forces"):
                 fn.restype = C.c_void_p
         _LIB = L
     return _LIB

@@ -24,6 +24,7 @@ SOURCES = {
     "ops.cu": [],
     "fused.cu": [],
     "peer.cu": [],
+    "halo.cu": [],
     "libstaf_api.cu": [],
 }
 

@@ -103,16 +103,22 @@ class StafModel:
         self.n_centres = int(t.sum())
 
     def energy_force_domain(self, pos_all, box, type_map, howmany=None, with_=None, virial=False,
-                            check_status=True):
+                            check_status=True, out=None):
         """One frame of nall atoms whose first n_centres (species-sorted) are owned and the rest are ghosts:
         energy 0.5*sum over the owned atoms, forces [nall,3] for all.  type_map: int32 [nall] on the device.
         howmany/with_ (int32 device tensors [n_centres], [n_centres, nr]): caller-built, distance-sorted rows
-        taken without any periodic wrap; otherwise the list is built with the minimum image of box[6]."""
+        taken without any periodic wrap; otherwise the list is built with the minimum image of box[6].
+        out=(energy[1], force[>=nall,3]): device tensors to fill instead of fresh ones (fixed addresses, for a
+        captured graph)."""
         pos_all = self._dev(pos_all)
         box = None if box is None else self._dev(box)
         nall = pos_all.numel() // 3
-        energy = torch.empty(1, dtype=self.dtype, device=self.device)
-        force = torch.empty(nall, 3, dtype=self.dtype, device=self.device)
+        if out is not None:
+            energy, force = out
+            assert energy.dtype == self.dtype and force.dtype == self.dtype and force.numel() >= 3 * nall
+        else:
+            energy = torch.empty(1, dtype=self.dtype, device=self.device)
+            force = torch.empty(nall, 3, dtype=self.dtype, device=self.device)
         vir = torch.empty(9, dtype=self.dtype, device=self.device) if virial else None
         check(_lib.lib().stafb_energy_force_domain(self.ctx.h, self.h, self.ctx.stream(), _p(pos_all), _p(box), nall,
                                                    _p(type_map), _p(howmany), _p(with_), _p(self.theta),

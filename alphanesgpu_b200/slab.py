@@ -144,3 +144,211 @@ def model_compute(model, box6):
             model.set_counts(torch.bincount(type_all[:n_owned].to(torch.int64), minlength=nt).tolist())
         return model.energy_force_domain(pos_all, box, type_all, check_status=plan_changed)
     return compute
+
+
+class PeerSlabDomain(SlabDomain):
+    """The same decomposition with all traffic carried by the ranks' own kernels over NVLink peer memory
+    (stafb_halo_*): positions stored straight into the neighbours' atom arrays, ghost forces stored back, energies
+    summed in rank order; the ghost sets, too, are chosen on the device and agreed through mailboxes in the peers'
+    memory, with one host synchronisation (six integers) per re-choice and no message library anywhere.  An
+    evaluation is push, bounded wait, the model's energy/force kernels, return, collect - issued eagerly, or
+    (use_graph) captured once per plan and replayed, which pays when plans live long.
+
+    self.pos is a view of the owned rows of the shared atom array: write new positions into it in place.
+    One node only (CUDA IPC); every rank constructs it collectively with the same capacities.  local=True: the
+    ranks are objects of ONE process (several ranks emulated on one GPU in the tests) - connect them with
+    connect_local() and drive them with plan_local() and the phase_*() calls, every phase for all ranks before the
+    next, because kernels on one GPU must never wait for one another."""
+
+    def __init__(self, model, box6, cutoff, rank, world, cap_atoms, cap_face, axis=2, group=None, skin=0.0,
+                 halo_every=1, local=False, use_graph=False):
+        import ctypes as C
+        from . import _lib
+        super().__init__(None, box6, cutoff, rank, world, axis=axis, group=group, nt=model.shape.nt, skin=skin,
+                         halo_every=halo_every)
+        if world < 2:
+            raise ValueError("PeerSlabDomain needs at least two ranks; use SlabDomain for one")
+        self.model, self.cap_atoms, self.cap_face = model, int(cap_atoms), int(cap_face)
+        self.box = torch.as_tensor(np.asarray(box6, np.float64)).to(device=model.device, dtype=model.dtype)
+        self._lib = _lib
+        h = C.c_void_p()
+        _lib.check(_lib.lib().stafb_halo_create(model.ctx.h, self.rank, self.world, self.cap_atoms, self.cap_face,
+                                                C.byref(h)), "stafb_halo_create")
+        self.h = h
+        self._local = bool(local)
+        if not local:
+            mine = C.create_string_buffer(64)
+            _lib.check(_lib.lib().stafb_halo_handle(self.h, mine), "stafb_halo_handle")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(mine.raw), group=group)
+            _lib.check(_lib.lib().stafb_halo_connect(self.h, b"".join(handles)), "stafb_halo_connect")
+            dist.barrier(group=group)
+        from .dist import _DevArray
+        ptr = _lib.lib().stafb_halo_positions(self.h)
+        self.pos_all = torch.as_tensor(_DevArray(ptr, 3 * self.cap_atoms, model.dtype),
+                                       device=model.device).view(self.cap_atoms, 3)
+        self.type_all = torch.zeros(self.cap_atoms, dtype=torch.int32, device=model.device)
+        self.force = torch.zeros(self.cap_atoms, 3, dtype=model.dtype, device=model.device)
+        self.e_own = torch.zeros(1, dtype=model.dtype, device=model.device)
+        self.e_total = torch.zeros(1, dtype=model.dtype, device=model.device)
+        self._graph = None
+        self.use_graph = bool(use_graph) and not local
+
+    @staticmethod
+    def connect_local(domains):
+        """Ranks of one process: maps every rank's block into the others without IPC."""
+        import ctypes as C
+        arr = (C.c_void_p * len(domains))(*[d.h for d in domains])
+        for d in domains:
+            d._lib.check(d._lib.lib().stafb_halo_connect_local(d.h, arr), "stafb_halo_connect_local")
+
+    def set_owned_from_global(self, pos_all, types_all):
+        idx = super().set_owned_from_global(pos_all, types_all)
+        n = self.pos.shape[0]
+        if n > self.cap_atoms:
+            raise ValueError("%d owned atoms exceed cap_atoms %d" % (n, self.cap_atoms))
+        self.pos_all[:n].copy_(self.pos)
+        self.pos = self.pos_all[:n]
+        self.model.set_counts(self.counts)
+        return idx
+
+    # -- plans ------------------------------------------------------------------------------------
+    def _plan_launch(self, which):
+        from .model import _p
+        L, st = self._lib.lib(), self.model.ctx.stream()
+        if which == 0:
+            self._lib.check(L.stafb_halo_plan_select(self.h, st, self.pos.shape[0], _p(self.types), self.axis, self.L,
+                                                     self.reach), "stafb_halo_plan_select")
+        elif which == 1:
+            self._lib.check(L.stafb_halo_plan_layout(self.h, st, _p(self.type_all)), "stafb_halo_plan_layout")
+        else:
+            self._lib.check(L.stafb_halo_plan_done(self.h, st), "stafb_halo_plan_done")
+
+    def _plan_finish(self):
+        import ctypes as C
+        out = (C.c_int * 4)()
+        self._lib.check(self._lib.lib().stafb_halo_plan_finish(self.h, self.model.ctx.stream(), out),
+                        "stafb_halo_plan_finish")
+        n_lo, n_hi = int(out[0]), int(out[1])
+        nall = self.pos.shape[0] + n_lo + n_hi
+        self._plan = dict(n_lo=n_lo, n_hi=n_hi, n_send_lo=int(out[2]), n_send_hi=int(out[3]), nall=nall,
+                          type_all=self.type_all[:nall])
+        self._graph = None
+        self._fresh = True
+        # the stream has just been waited for: the model's status word (a saturated neighbour buffer during the
+        # evaluations of the previous plan) costs nothing to read here
+        self.model.ctx.raise_on_status("stafb_energy_force_domain")
+
+    def _make_plan(self):
+        for which in range(3):
+            self._plan_launch(which)
+        self._plan_finish()
+
+    @staticmethod
+    def plan_local(domains):
+        """Ranks of one process: each plan launch for all ranks before the next."""
+        for which in range(3):
+            for d in domains:
+                d._plan_launch(which)
+        for d in domains:
+            d._plan_finish()
+
+    def _faces(self):
+        w = self.L / self.world
+        z = self.pos[:, self.axis]
+        zw = z - torch.floor(z / self.L) * self.L - self.rank * w
+        return torch.nonzero(zw < self.reach).squeeze(1), torch.nonzero(zw >= w - self.reach).squeeze(1)
+
+    @staticmethod
+    def plan_local_explicit(domains):
+        """The same plan made on the host and installed with stafb_halo_set_plan - the entry point for a caller
+        that has its own ghost lists (an MD code's communication lists)."""
+        from .model import _p
+        torch.cuda.synchronize()
+        faces = [d._faces() for d in domains]
+        n_lo = [faces[d.lo][1].shape[0] for d in domains]  # what arrives from lo left through lo's upper face
+        for d in domains:
+            lo, hi = domains[d.lo], domains[d.hi]
+            t_lo = lo.types[faces[d.lo][1]]
+            t_hi = hi.types[faces[d.hi][0]]
+            n_own = d.pos.shape[0]
+            nall = n_own + t_lo.shape[0] + t_hi.shape[0]
+            d.type_all[:nall] = torch.cat([d.types, t_lo, t_hi])
+            s_lo = faces[d.rank][0].to(torch.int32).contiguous()
+            s_hi = faces[d.rank][1].to(torch.int32).contiguous()
+            dst_lo = lo.pos.shape[0] + n_lo[d.lo]  # lo's "ghosts from hi" rows
+            dst_hi = hi.pos.shape[0]               # hi's "ghosts from lo" rows
+            d._lib.check(d._lib.lib().stafb_halo_set_plan(
+                d.h, d.model.ctx.stream(), n_own, t_lo.shape[0], t_hi.shape[0], _p(s_lo), s_lo.shape[0], int(dst_lo),
+                _p(s_hi), s_hi.shape[0], int(dst_hi)), "stafb_halo_set_plan")
+            d._plan = dict(n_lo=t_lo.shape[0], n_hi=t_hi.shape[0], n_send_lo=s_lo.shape[0], n_send_hi=s_hi.shape[0],
+                           nall=nall, type_all=d.type_all[:nall])
+            d._graph, d._fresh = None, True
+        torch.cuda.synchronize()
+
+    # -- one evaluation, in the four phases that may be issued rank by rank ---------------------------
+    def phase_push(self):
+        self._lib.check(self._lib.lib().stafb_halo_push_positions(self.h, self.model.ctx.stream()), "stafb_halo_push")
+
+    def phase_wait(self):
+        self._lib.check(self._lib.lib().stafb_halo_wait_positions(self.h, self.model.ctx.stream()), "stafb_halo_wait")
+
+    def phase_eval_return(self):
+        from .model import _p
+        P = self._plan
+        self.model.energy_force_domain(self.pos_all[:P["nall"]], self.box, P["type_all"], check_status=False,
+                                       out=(self.e_own, self.force))
+        self._lib.check(self._lib.lib().stafb_halo_return_forces(self.h, self.model.ctx.stream(), _p(self.force),
+                                                                 _p(self.e_own)), "stafb_halo_return_forces")
+
+    def phase_collect(self):
+        from .model import _p
+        self._lib.check(self._lib.lib().stafb_halo_collect(self.h, self.model.ctx.stream(), _p(self.force),
+                                                           _p(self.e_total)), "stafb_halo_collect")
+
+    def _sequence(self):
+        self.phase_push()
+        self.phase_wait()
+        self.phase_eval_return()
+        self.phase_collect()
+
+    def step(self, rebuild=None):
+        """Energy of the whole system (tensor [1], bit-identical on every rank) and forces on the owned atoms;
+        both are views of buffers the next step overwrites.  Asynchronous except when the ghost sets are re-chosen."""
+        if rebuild is None:
+            rebuild = self._plan is None or self._nstep % self.halo_every == 0
+        self._nstep += 1
+        if rebuild:
+            self._make_plan()
+        if not self.use_graph or self._fresh:
+            self._sequence()  # a plan's first evaluation always runs eagerly (allocations on first use)
+            self._fresh = False
+        else:
+            if self._graph is None:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                    self._sequence()
+                self._graph = g
+            self._graph.replay()
+        return self.e_total, self.force[:self.pos.shape[0]]
+
+    def check(self):
+        """Reads the device status words of the model and of the exchange (waits for the device)."""
+        self.model.ctx.raise_on_status("stafb_energy_force_domain")
+        st = self._lib.lib().stafb_halo_status(self.h)
+        if st:
+            raise self._lib.StafbError(st, "stafb_halo")
+
+    def set_wait_ms(self, ms):
+        self._lib.check(self._lib.lib().stafb_halo_set_wait_ms(self.h, int(ms)), "stafb_halo_set_wait_ms")
+
+    def close(self):
+        """Collective: no rank unmaps while another may still store into its block."""
+        if self.h is not None:
+            torch.cuda.synchronize()
+            if not self._local:
+                dist.barrier(group=self.group)
+            self._graph = None
+            self.pos = self.pos_all = None
+            self._lib.lib().stafb_halo_destroy(self.h)
+            self.h = None

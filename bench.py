@@ -435,7 +435,7 @@ def md_record(torch, dist, args, rank, world, local, dev, K):
     from alphanesgpu_b200 import params, synth, _lib
     from alphanesgpu_b200.model import StafModel
     from alphanesgpu_b200.params import ModelShape
-    from alphanesgpu_b200.slab import SlabDomain, model_compute
+    from alphanesgpu_b200.slab import PeerSlabDomain, SlabDomain, model_compute, slab_of
 
     W = 3
     pos, box, tipos = synth.water_frames("water24576", [1400])
@@ -446,14 +446,28 @@ def md_record(torch, dist, args, rank, world, local, dev, K):
     gpos = torch.as_tensor(pos.reshape(N, 3).astype(np.float32)).to(dev)
     gtypes = torch.as_tensor(types).to(dev)
     SKIN, HALO_EVERY = 1.0, 10  # ghost sets are re-chosen every 10 evaluations with a 1 A skin, as an MD code does
-    dom = SlabDomain(None, box[0], CFG["Rc"], rank, world, nt=gshape.nt, skin=SKIN, halo_every=HALO_EVERY)
-    own_idx = dom.set_owned_from_global(gpos, gtypes)
-    n_own = dom.pos.shape[0]
-    halo = 0 if world == 1 else 2.0 * dom.reach / (dom.L / world)
-    cap = int(n_own * (1.0 + halo) * 1.25) + 1024
-    shape = ModelShape(nt=gshape.nt, tipos=list(dom.counts), Fr=gshape.Fr, Fa=gshape.Fa, widths=gshape.widths)
-    model = StafModel(shape, CFG, theta, emb, 1, dtype=torch.float32, device=dev, n_max=cap)
-    dom.compute = model_compute(model, box[0])
+    if world == 1:
+        dom = SlabDomain(None, box[0], CFG["Rc"], rank, world, nt=gshape.nt, skin=SKIN, halo_every=HALO_EVERY)
+        own_idx = dom.set_owned_from_global(gpos, gtypes)
+        n_own = dom.pos.shape[0]
+        shape = ModelShape(nt=gshape.nt, tipos=list(dom.counts), Fr=gshape.Fr, Fa=gshape.Fa, widths=gshape.widths)
+        model = StafModel(shape, CFG, theta, emb, 1, dtype=torch.float32, device=dev, n_max=n_own + 1024)
+        dom.compute = model_compute(model, box[0])
+    else:
+        # positions, ghost forces and energies travel by the ranks' own stores over NVLink (stafb_halo_*); every
+        # rank sizes its block alike (the peers address it by the common layout)
+        L = float(box[0][5])
+        n_mine = int((slab_of(gpos[:, 2], L, world) == rank).sum())
+        halo = 2.0 * (CFG["Rc"] + SKIN) / (L / world)
+        caps = torch.tensor([int(n_mine * (1.0 + halo) * 1.25) + 1024, int(n_mine * halo * 0.75) + 1024], device=dev)
+        dist.all_reduce(caps, op=dist.ReduceOp.MAX)
+        cap, cap_face = (int(v) for v in caps.tolist())
+        shape = ModelShape(nt=gshape.nt, tipos=[1] * gshape.nt, Fr=gshape.Fr, Fa=gshape.Fa, widths=gshape.widths)
+        model = StafModel(shape, CFG, theta, emb, 1, dtype=torch.float32, device=dev, n_max=cap)
+        dom = PeerSlabDomain(model, box[0], CFG["Rc"], rank, world, cap_atoms=cap, cap_face=cap_face, skin=SKIN,
+                             halo_every=HALO_EVERY)
+        own_idx = dom.set_owned_from_global(gpos, gtypes)
+        n_own = dom.pos.shape[0]
 
     def barrier():
         if world > 1:
@@ -488,7 +502,9 @@ def md_record(torch, dist, args, rank, world, local, dev, K):
     barrier()
     clocks = sampler.stop()
     total_ms = float(sum(a.elapsed_time(b) for a, b in zip(ev0, ev1)))
-    launches = model.launches()
+    launches = model.launches() + (4 if world > 1 else 0)  # push, wait, return, collect of the halo exchange
+    if world > 1:
+        dom.check()
     # end to end: owned positions start in (pinned) host memory and owned forces end there, every step
     pin_x = dom.pos.cpu().pin_memory()
     pin_f = torch.empty_like(pin_x)
@@ -545,7 +561,7 @@ def md_record(torch, dist, args, rank, world, local, dev, K):
     acc = {}
     for k in range(5):
         flush.zero_()
-        dom.step()
+        dom.step(rebuild=False)
         for name, ms in model.phase_times_ms().items():
             acc[name] = acc.get(name, 0.0) + ms / 5
     model.set_phase_timing(False)
@@ -576,10 +592,37 @@ def md_record(torch, dist, args, rank, world, local, dev, K):
             "e2e": {"value": N * Ke / (e2e_ms * 1e-3), "unit": "atom-steps/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": Ke,
                     "path": "staf_compute (libstaf C API, host double arrays)" if world == 1 else
-                            "slab driver: pinned host -> device, halo exchange, forces -> pinned host"},
+                            "slab driver: pinned host -> device, halo exchange over peer memory, forces -> pinned host"},
             "gpu_launches": launches * K, "launches_per_step": launches, "clocks": clocks, "phase_ms": acc,
             "energy": float(e), "dd_parity": dd_err, "cpu_baseline": cpu,
         }
+    messages_ms = None
+    if world > 1:
+        # the same decomposition with torch.distributed messages (NCCL send/recv per face, all-reduce of the
+        # energy) instead of the peer stores, for comparison
+        dom.check()
+        msg = SlabDomain(model_compute(model, box[0]), box[0], CFG["Rc"], rank, world, nt=gshape.nt, skin=SKIN,
+                         halo_every=HALO_EVERY)
+        msg.set_owned_from_global(gpos, gtypes)
+        for _ in range(W):
+            msg.step()
+        Km = max(5, min(K, 50))
+        a = [torch.cuda.Event(enable_timing=True) for _ in range(Km)]
+        b = [torch.cuda.Event(enable_timing=True) for _ in range(Km)]
+        barrier()
+        for k in range(Km):
+            flush.zero_()
+            a[k].record()
+            msg.step()
+            b[k].record()
+        barrier()
+        t = torch.tensor([sum(x.elapsed_time(y) for x, y in zip(a, b)) / Km], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        messages_ms = float(t[0])
+        if rec is not None:
+            rec["transport"] = {"halo": "peer stores over NVLink; ghost sets chosen on the device, one host sync per re-choice",
+                                "ms_per_step_with_nccl_messages": messages_ms}
+        dom.close()
     model.close()
     del flush
     return rec
@@ -944,7 +987,7 @@ def run_ours(args):
     md = md_record(torch, dist, args, rank, world, local, dev, 20)
     if md is not None:
         md = {k: md[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "scaling", "config", "e2e",
-                                 "launches_per_step", "phase_ms", "dd_parity")}
+                                 "launches_per_step", "phase_ms", "dd_parity", "transport") if k in md}
 
     if rank == 0:
         cpu = None

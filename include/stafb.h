@@ -32,7 +32,7 @@ extern "C" {
 #define STAFB_ERR_CUDA 6             /* a CUDA runtime call failed; see stafb_last_cuda_error() */
 #define STAFB_ERR_CAPACITY 7         /* nf or N larger than what the context was created for */
 #define STAFB_ERR_NONFINITE 8        /* non-finite energy */
-#define STAFB_ERR_PEER_TIMEOUT 9     /* stafb_allreduce_adam: a peer rank did not publish its gradient in time */
+#define STAFB_ERR_PEER_TIMEOUT 9     /* stafb_allreduce_adam, stafb_halo_*: a peer rank did not publish in time */
 #define STAFB_ERR_STAGE_TIMEOUT 10   /* a kernel gave up waiting for its own asynchronous copy into shared memory */
 
 #define STAFB_F32 0
@@ -334,6 +334,73 @@ int stafb_peer_status(stafb_peer* p);
 void stafb_peer_destroy(stafb_peer* p);
 int stafb_allreduce_adam(stafb_ctx* ctx, stafb_peer* p, void* stream, int parity, void* theta_d, void* m_d, void* v_d,
                          double lr, double beta1, double beta2, double eps, int* step_d);
+
+/* Halo exchange of a slab decomposition over NVLink peer memory, for the ranks (one per GPU) of one node.  No
+ * reference counterpart as a function: it is what LAMMPS' forward and reverse communication do around
+ * PairSTAF::compute (lammps/USER-STAF/pair_staf.cpp:129-145 ghost atoms as neighbours, :250 forces on ghosts, summed
+ * onto their owners by reverse_comm) without a message library on the path of an evaluation.  The periodic box is
+ * cut into `world` slabs along one axis; rank r exchanges with lo = r-1 and hi = r+1 (mod world).  Each rank owns
+ * one block that its peers map: its atom array (owned atoms | ghosts from lo | ghosts from hi; the neighbours store
+ * their face atoms straight into the ghost regions), a receive area for the forces on the atoms it sent, per-rank
+ * energies and flag words that carry the number of the evaluation.
+ *   stafb_halo_create       allocates the block for at most cap_atoms atoms (owned + ghosts) and cap_face atoms per
+ *                           face; every rank must pass the same two numbers (the peers address the block by them);
+ *   stafb_halo_handle / _connect / _connect_local   as for stafb_peer_*;
+ *   stafb_halo_positions    device pointer of the atom array [cap_atoms][3]: the caller keeps the owned positions in
+ *                           its first n_own rows and passes it as positions_d to stafb_energy_force_domain;
+ *   stafb_halo_forces       a [cap_atoms][3] array of the same type for that call's forces (convenience);
+ *   stafb_halo_set_plan     which atoms leave through each face (indices among the owned atoms, device int32,
+ *                           copied), how many ghosts arrive from each side, and where this rank's face atoms start
+ *                           in the neighbour's array: dst_off_lo = first row of "ghosts from hi" in lo's array,
+ *                           dst_off_hi = first row of "ghosts from lo" in hi's.  The ranks agree on these numbers
+ *                           by any host-side means whenever the ghost sets are re-chosen.  All ranks must have
+ *                           finished their evaluations under the old plan (a host-side barrier) before any sets
+ *                           a new one;
+ *   stafb_halo_plan_select / _layout / _done / _finish   the same agreement made on the device, for ranks that
+ *                           cut the box into equal slabs along `axis` (0..2; box length L there): select picks the
+ *                           owned atoms within `reach` (cutoff + skin) of this slab's faces, in index order, and
+ *                           mails their number and species (types_d: int32 per owned atom) to the neighbours;
+ *                           layout fills type_all_d[cap_atoms] (owned | from lo | from hi) and tells the
+ *                           neighbours where their face atoms start; done waits for those answers; finish waits
+ *                           for the stream - the only host synchronisation - and returns n_from_lo, n_from_hi,
+ *                           n_send_lo, n_send_hi.  No barrier between the ranks is needed: a neighbour stores by
+ *                           the new offsets only after this rank's layout launch, which follows this rank's last
+ *                           evaluation under the old plan in stream order;
+ *   one evaluation =  stafb_halo_push_positions; stafb_halo_wait_positions; stafb_energy_force_domain (energy_d =
+ *                           the owned atoms' share, force_d for owned and ghost atoms); stafb_halo_return_forces
+ *                           (ghost forces to their owners' ranks, this rank's energy to every rank);
+ *                           stafb_halo_collect (adds the returned forces onto force_d's owned rows, writes the sum
+ *                           of the ranks' energies, taken in rank order and so identical on every rank, to
+ *                           energy_out_d, and advances the evaluation counter).  All five are asynchronous on
+ *                           `stream` and read the evaluation number on the device, so the sequence may be captured
+ *                           in a CUDA graph once per plan and replayed.
+ * Every wait is bounded (about two seconds, STAFB_PEER_WAIT_MS or stafb_halo_set_wait_ms); after a miss
+ * stafb_halo_status returns STAFB_ERR_PEER_TIMEOUT, the collect leaves the counter where it was and the results of
+ * that evaluation are not valid.  Kernels of different ranks wait for each other: ranks that share ONE GPU (tests)
+ * must issue all pushes before any wait, all returns before any collect, and each plan launch for all ranks
+ * before the next. */
+typedef struct stafb_halo stafb_halo;
+int stafb_halo_create(stafb_ctx* ctx, int rank, int world, int cap_atoms, int cap_face, stafb_halo** out);
+int stafb_halo_handle(stafb_halo* h, void* handle64_out);
+int stafb_halo_connect(stafb_halo* h, const void* handles);
+int stafb_halo_connect_local(stafb_halo* h, stafb_halo* const* all);
+void* stafb_halo_positions(stafb_halo* h);
+void* stafb_halo_forces(stafb_halo* h);
+int stafb_halo_set_wait_ms(stafb_halo* h, long long ms);
+int stafb_halo_set_plan(stafb_halo* h, void* stream, int n_own, int n_from_lo, int n_from_hi,
+                        const int* send_lo_idx_d, int n_send_lo, int dst_off_lo, const int* send_hi_idx_d,
+                        int n_send_hi, int dst_off_hi);
+int stafb_halo_plan_select(stafb_halo* h, void* stream, int n_own, const int* types_d, int axis, double L,
+                           double reach);
+int stafb_halo_plan_layout(stafb_halo* h, void* stream, int* type_all_d);
+int stafb_halo_plan_done(stafb_halo* h, void* stream);
+int stafb_halo_plan_finish(stafb_halo* h, void* stream, int* counts_out4);
+int stafb_halo_push_positions(stafb_halo* h, void* stream);
+int stafb_halo_wait_positions(stafb_halo* h, void* stream);
+int stafb_halo_return_forces(stafb_halo* h, void* stream, const void* force_d, const void* energy_d);
+int stafb_halo_collect(stafb_halo* h, void* stream, void* force_d, void* energy_out_d);
+int stafb_halo_status(stafb_halo* h);
+void stafb_halo_destroy(stafb_halo* h);
 
 /* Same as stafb_train_step but positions, boxer and labels are HOST buffers and losses is a
  * host double[4]: copies in, runs, copies the losses back and synchronises the stream. */
