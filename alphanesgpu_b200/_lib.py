@@ -52,6 +52,7 @@ _SIGS = {
     "stafb_model_n_emb": [_vp],
     "stafb_model_offsets": [_vp, _i, _vp],
     "stafb_model_mlp_config": [_vp, _vp],
+    "stafb_model_mlp_mma_config": [_vp, _vp],
     "stafb_energy_force": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp],
     "stafb_energy_force_virial": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp],
     "stafb_energy_force_domain": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -117,6 +118,7 @@ def lib():
             fn.argtypes = sig
             fn.restype = None if name in ("stafb_destroy", "stafb_model_destroy", "stafb_core_coefficients",
                                           "stafb_model_offsets", "stafb_peer_destroy", "stafb_model_mlp_config",
+                                          "stafb_model_mlp_mma_config",
                                           "stafb_halo_destroy") else _i
             if name in ("stafb_peer_grad", "stafb_halo_positions", "stafb_halo_forces"):
                 fn.restype = C.c_void_p

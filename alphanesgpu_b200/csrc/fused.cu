@@ -77,6 +77,7 @@ static inline int species_blocks(const ModelDev& md, int nf, int W) {
 
 // ---------------------------------------------------------------------------- MLP head
 #include "mlp.cuh"
+#include "mlp_mma.cuh"
 
 // ---------------------------------------------------------------------------- energy, loss
 template <class T>
@@ -92,7 +93,7 @@ template <class T>
 __global__ void k_prep(ModelDev md, const T* __restrict__ theta, const T* __restrict__ emb, T* __restrict__ wpack,
                        int wstride, unsigned char* __restrict__ spar, int spar_stride, SparLayout sl, void* a,
                        size_t na, void* b, size_t nb, void* c, size_t nc, const T* __restrict__ flab_src,
-                       T* __restrict__ flab_dst, size_t nflab) {
+                       T* __restrict__ flab_dst, size_t nflab, T* __restrict__ wm, int wm_stride) {
   chain_wait();
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
   // force labels into device scratch: the backward sweep gathers them per neighbour, and the caller's copy may
@@ -128,7 +129,24 @@ __global__ void k_prep(ModelDev md, const T* __restrict__ theta, const T* __rest
     }
     wpack[q] = v;
   }
+  // the same layers split and ordered by MMA fragment for the tensor-core MLP kernels (mlp_mma.cuh; fp32 only)
+  if constexpr (std::is_same<T, float>::value) {
+    if (wm) {
+      for (size_t q = tid; q < (size_t)md.nt * wm_stride; q += st) {
+        const int t = (int)(q / wm_stride);
+        int r = (int)(q - (size_t)t * wm_stride), l = 0;
+        while (l < md.n_dense && r >= mm_layer_words(md.in_of(t, l), md.width[l])) {
+          r -= mm_layer_words(md.in_of(t, l), md.width[l]);
+          l++;
+        }
+        wm[q] = l < md.n_dense ? mm_pack_value(theta + md.off_w[t] + md.w_off(t, l), md.in_of(t, l), md.width[l], r)
+                               : 0.0f;
+      }
+    }
+  }
 }
+
+constexpr int LOSS_EB_MAX = 32;  // blocks that share the energy sum of one frame
 
 // Losses of an evaluation in one launch.  Blocks [0,nf): frame energy E_b = 0.5*mean_i e_i (or 0.5*sum), energy
 // loss and the cotangent on the atomic energies.  Blocks [nf, nf+fb): force loss (the backward sweep forms dL/dF
@@ -141,23 +159,47 @@ __global__ void k_prep(ModelDev md, const T* __restrict__ theta, const T* __rest
 // write.  In an inference evaluation it directly follows the force sweep; only the virial needs that one.
 template <class T>
 __global__ void __launch_bounds__(256)
-    k_loss(ModelDev md, int nf, int fb, int per_atom, int train, const T* __restrict__ e_atom, T* __restrict__ energy,
+    k_loss(ModelDev md, int nf, int eb, int fb, int per_atom, int train, const T* __restrict__ e_atom, T* __restrict__ energy,
            const T* __restrict__ e_label, const T* __restrict__ force, const T* __restrict__ f_label,
            const T* __restrict__ theta, T pe, T pf, T pb, T bound, int loss_kind, T* __restrict__ ebar,
            T* __restrict__ grad, double* __restrict__ losses, int* status, int* status_main,
-           const double* __restrict__ vacc, T* __restrict__ virial_out, double* __restrict__ mirror) {
+           const double* __restrict__ vacc, T* __restrict__ virial_out, double* __restrict__ mirror,
+           double* __restrict__ epart, unsigned* __restrict__ ecount) {
   __shared__ double red[9];
+  __shared__ int last_s;
   const int N = md.N;
-  const int blk = blockIdx.x;
-  const bool needs_pred = (blk < nf && virial_out);
+  int blk = blockIdx.x;
+  const bool needs_pred = (blk < nf * eb && virial_out);
   if (needs_pred) chain_wait();
-  if (blk < nf) {
+  if (blk < nf * eb) {
     double Eb = 0.0;
     T le = T(0), de = T(0);
-    // sum of the frame's atomic energies (the MLP kernel is at least two kernels back)
+    // sum of the frame's atomic energies (the MLP kernel is at least two kernels back).  A large frame is summed
+    // by eb blocks: each leaves its part, the one that arrives last adds the parts in their fixed order (the
+    // result does not depend on which block that is) and finishes the frame.
+    const int part = blk % eb;
+    blk /= eb;
+    const int per = (N + eb - 1) / eb, q1 = min(N, (part + 1) * per);
     double s = 0.0;
-    for (int q = threadIdx.x; q < N; q += blockDim.x) s += (double)e_atom[(size_t)blk * N + q];
+    for (int q = part * per + threadIdx.x; q < q1; q += blockDim.x) s += (double)e_atom[(size_t)blk * N + q];
     s = block_sum<double, 8>(s, red);
+    if (eb > 1) {
+      if (!needs_pred) chain_wait();
+      unsigned* count = ecount + blk;
+      if (threadIdx.x == 0) {
+        epart[(size_t)blk * eb + part] = s;
+        __threadfence();
+        last_s = atomicAdd(count, 1u) == (unsigned)(eb - 1);
+      }
+      __syncthreads();
+      if (!last_s) return;  // only inference evaluations use more than one block per frame
+      if (threadIdx.x == 0) {
+        __threadfence();
+        s = 0.0;
+        for (int k = 0; k < eb; k++) s += __ldcg(epart + (size_t)blk * eb + k);
+        *count = 0u;
+      }
+    }
     if (threadIdx.x == 0) {
       Eb = per_atom ? 0.5 * s / N : 0.5 * s;
       if (train) {
@@ -166,7 +208,7 @@ __global__ void __launch_bounds__(256)
         de = loss_kind == 0 ? huber_d(e) : T(2) * e;
       }
     }
-    if (!needs_pred) chain_wait();
+    if (!needs_pred && eb == 1) chain_wait();
     if (virial_out && threadIdx.x < 9) virial_out[blk * 9 + threadIdx.x] = (T)vacc[blk * 9 + threadIdx.x];
     if (threadIdx.x == 0) {
       if (!isfinite(Eb)) set_status(status, STAFB_ERR_NONFINITE);
@@ -176,10 +218,10 @@ __global__ void __launch_bounds__(256)
         ebar[blk] = pe * de / T(nf) * T(0.5) / (per_atom ? T(N) : T(1));
       }
     }
-  } else if (blk < nf + fb) {
+  } else if (blk < nf * eb + fb) {
     const size_t n = (size_t)nf * 3 * N;
     double s = 0.0;
-    for (size_t q = (size_t)(blk - nf) * blockDim.x + threadIdx.x; q < n; q += (size_t)fb * blockDim.x) {
+    for (size_t q = (size_t)(blk - nf * eb) * blockDim.x + threadIdx.x; q < n; q += (size_t)fb * blockDim.x) {
       const T e = force[q] - f_label[q];
       s += (double)(loss_kind == 0 ? huber(e) : e * e);
     }
@@ -294,6 +336,12 @@ struct stafb_model {
   void* wpack;  // packed, padded Dense layers of every species (k_prep), wstride elements per species
   int wstride;
   int nv;  // row length of vrow: nt*Frmax + C*3*Famax
+  // tensor-core MLP kernels (fp32): on/off, warps per block (16 atoms), the fragment-ordered pack and its
+  // per-species stride, dynamic shared memory of the two kernels
+  int mma, mma_nw, mma_stage, wm_stride;
+  void* wm;
+  size_t mma_fwd_smem, mma_bwd_smem;
+  double* epart;     // partial energy sums of k_loss: [nf][eb]; from [max_batch][LOSS_EB_MAX] on: one arrival counter per frame
   double* losses_d;  // [0..4] the four losses + the done-counter of k_loss; [8 + b] sum of the atomic energies of
                      // frame b (accumulated by the MLP kernel); [8 + max_batch + 9*b + c] virial accumulators
   // staging for the *_host entry points
@@ -419,6 +467,21 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   if (m->stage < 0 || m->stage > 2 || mlp_smem_bwd(d, m->es, m->aw, m->stage) > mlp_room) { free(m); return STAFB_ERR_CAPACITY; }
   m->mlp_fwd_smem = mlp_smem_fwd(d, m->es, m->aw, m->stage);
   m->mlp_bwd_smem = mlp_smem_bwd(d, m->es, m->aw, m->stage);
+  // The tensor-core form of the MLP kernels (mlp_mma.cuh; fp32 only, one block per 16 atoms, its warps - 4;
+  // STAFB_MLP_MMA_NW: 1, 2, 4, 8 - sharing the tiles) is the other arm, selected with STAFB_MLP_MMA=1: on B200
+  // mma.sync.m16n8k8.tf32 issues at about one instruction per 30 cycles per SM, which leaves these kernels
+  // 1.4-2x behind the FMA kernels at every size measured (768-atom frames at batch 4, 8, 16; a 24,576-atom box).
+  m->mma = 0; m->wm = nullptr; m->wm_stride = 0;
+  if (c->dtype == STAFB_F32 && d.width[d.n_dense - 1] == 1 && !getenv("STAFB_MLP_STAGE") &&
+      getenv("STAFB_MLP_MMA") && atoi(getenv("STAFB_MLP_MMA")) == 1) {
+    const size_t fw = 4 * mm_fwd_words(d), bw = 4 * mm_bwd_words(d);
+    int nw = getenv("STAFB_MLP_MMA_NW") ? atoi(getenv("STAFB_MLP_MMA_NW")) : 4;
+    if ((nw == 1 || nw == 2 || nw == 4 || nw == 8) && bw <= mlp_room && fw <= mlp_room) {
+      m->mma = 1; m->mma_nw = nw; m->mma_stage = 0;
+      m->mma_fwd_smem = fw; m->mma_bwd_smem = bw;
+      m->wm_stride = (int)mm_pack_words(d);
+    }
+  }
   // scratch is sized for the context's atom capacity, so that stafb_model_set_counts can move atoms between
   // species (or change their number) without reallocating
   const size_t es = m->es, A = (size_t)c->max_batch * c->n_max, nr = c->nr;
@@ -436,7 +499,16 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   STAFB_CUDA_OK(cudaMalloc(&m->gaf, es * A * d.Fmax));
   m->nv = d.nt * d.Frmax + d.C * 3 * d.Famax;
   STAFB_CUDA_OK(cudaMalloc(&m->vrow, es * A * (m->nv > 0 ? m->nv : 1)));
-  STAFB_CUDA_OK(cudaMalloc(&m->acts, es * mlp_blocks * ML_WARPS * m->aw * d.Hsum));
+  {
+    size_t acts_words = mlp_blocks * ML_WARPS * m->aw * d.Hsum;
+    if (m->mma) {
+      const size_t tiles = A / MM_ATOMS + (size_t)d.nt * c->max_batch + 1;
+      const size_t w2 = tiles * MM_ATOMS * (size_t)mm_shape(d, 0).hoff[d.n_dense];
+      acts_words = w2 > acts_words ? w2 : acts_words;
+      STAFB_CUDA_OK(cudaMalloc(&m->wm, sizeof(float) * (size_t)d.nt * m->wm_stride));
+    }
+    STAFB_CUDA_OK(cudaMalloc(&m->acts, es * acts_words));
+  }
   m->wstride = (int)mlp_stage_words(d, 2);
   STAFB_CUDA_OK(cudaMalloc(&m->wpack, es * (size_t)d.nt * m->wstride));
   STAFB_CUDA_OK(cudaMalloc(&m->e_atom, es * A));
@@ -445,6 +517,8 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   STAFB_CUDA_OK(cudaMalloc(&m->ebar, es * c->max_batch));
   STAFB_CUDA_OK(cudaMalloc(&m->energy, es * c->max_batch));
   STAFB_CUDA_OK(cudaMalloc((void**)&m->losses_d, sizeof(double) * (8 + 10 * (size_t)c->max_batch)));
+  STAFB_CUDA_OK(cudaMalloc((void**)&m->epart, sizeof(double) * (size_t)c->max_batch * (LOSS_EB_MAX + 1)));
+  STAFB_CUDA_OK(cudaMemset(m->epart, 0, sizeof(double) * (size_t)c->max_batch * (LOSS_EB_MAX + 1)));
   {
     const size_t blk = es * (A * 6 + (size_t)c->max_batch * 7 + 8);
     for (int k = 0; k < 3; k++) {
@@ -461,7 +535,7 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
 extern "C" void stafb_model_destroy(stafb_model* m) {
   if (!m) return;
   void* ptrs[] = {m->rows, m->spar, m->af, m->nd, m->gradnet, m->gaf, m->acts, m->e_atom, m->force,
-                  m->flab, m->ebar, m->energy, m->losses_d, m->vrow, m->wpack};
+                  m->flab, m->ebar, m->energy, m->losses_d, m->epart, m->vrow, m->wpack, m->wm};
   for (void* p : ptrs) cudaFree(p);
   for (int k = 0; k < 3; k++) {
     cudaFreeHost(m->slot_in_h[k]);
@@ -503,6 +577,11 @@ extern "C" int stafb_model_n_params(const stafb_model* m) { return m ? m->n_para
 extern "C" int stafb_model_n_emb(const stafb_model* m) { return m ? m->n_emb : -1; }
 extern "C" void stafb_model_mlp_config(const stafb_model* m, int out4[4]) {
   out4[0] = m->stage; out4[1] = m->aw; out4[2] = (int)m->mlp_fwd_smem; out4[3] = (int)m->mlp_bwd_smem;
+}
+
+extern "C" void stafb_model_mlp_mma_config(const stafb_model* m, int out4[4]) {
+  out4[0] = m->mma; out4[1] = m->mma ? m->mma_nw : 0; out4[2] = m->mma ? m->mma_stage : 0;
+  out4[3] = m->mma ? (int)m->mma_bwd_smem : 0;
 }
 extern "C" void stafb_model_offsets(const stafb_model* m, int t, int out6[6]) {
   out6[0] = m->md.off_a2[t]; out6[1] = m->md.off_a3[t]; out6[2] = m->md.off_mu[t]; out6[3] = m->md.off_w[t];
@@ -620,9 +699,43 @@ static int launch_mlp_bwd_t(stafb_model* m, cudaStream_t s, int nf, const T* the
   return STAFB_OK;
 }
 
+static int launch_mlp_fwd_mma(stafb_model* m, cudaStream_t s, int nf, const float* theta, const float* af, float* acts,
+                              float* e_atom, float* nd) {
+  static size_t attr_dev[MAX_DEVICES] = {0};
+  size_t& attr = attr_dev[device_slot()];
+  if (m->mma_fwd_smem > 48 * 1024 && m->mma_fwd_smem > attr) {
+    STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_fwd_mma, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)m->mma_fwd_smem));
+    attr = m->mma_fwd_smem;
+  }
+  STAFB_CUDA_OK(launch_chained(k_mlp_fwd_mma, species_blocks(m->md, nf, MM_ATOMS), 32 * m->mma_nw, m->mma_fwd_smem, s,
+                               m->md, nf, theta, (const float*)m->wm, m->wm_stride, af, acts, e_atom, nd));
+  m->ctx->launches++;
+  return STAFB_OK;
+}
+
+static int launch_mlp_bwd_mma(stafb_model* m, cudaStream_t s, int nf, const float* theta, const float* af,
+                              const float* acts, const float* ebar, const float* u, float* gaf, float* grad) {
+  static size_t attr_dev[MAX_DEVICES] = {0};
+  size_t& attr = attr_dev[device_slot()];
+  if (m->mma_bwd_smem > 48 * 1024 && m->mma_bwd_smem > attr) {
+    STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_bwd_mma, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)m->mma_bwd_smem));
+    attr = m->mma_bwd_smem;
+  }
+  STAFB_CUDA_OK(launch_chained(k_mlp_bwd_mma, species_blocks(m->md, nf, MM_ATOMS), 32 * m->mma_nw, m->mma_bwd_smem, s,
+                               m->md, nf, theta, (const float*)m->wm, m->wm_stride, af, acts, ebar, u,
+                               (const float*)m->vrow, m->nv, gaf, grad));
+  m->ctx->launches++;
+  return STAFB_OK;
+}
+
 template <class T>
 static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, T* acts, T* e_atom,
                           T* nd) {
+  if constexpr (std::is_same<T, float>::value) {
+    if (m->mma) return launch_mlp_fwd_mma(m, s, nf, theta, af, acts, e_atom, nd);
+  }
   const bool wg = m->stage == 0;
   switch (m->aw) {
     case 4: return wg ? launch_mlp_fwd_t<T, 4, true>(m, s, nf, theta, af, acts, e_atom, nd)
@@ -637,6 +750,9 @@ static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta
 template <class T>
 static int launch_mlp_bwd(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, const T* acts,
                           const T* ebar, const T* u, T* gaf, T* grad) {
+  if constexpr (std::is_same<T, float>::value) {
+    if (m->mma) return launch_mlp_bwd_mma(m, s, nf, theta, af, acts, ebar, u, gaf, grad);
+  }
   const bool wg = m->stage == 0;
   switch (m->aw) {
     case 4: return wg ? launch_mlp_bwd_t<T, 4, true>(m, s, nf, theta, af, acts, ebar, u, gaf, grad)
@@ -700,7 +816,8 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
       sizeof(T) * (size_t)nf * 3 * nall,
       train ? (void*)grad : (void*)nullptr, train ? sizeof(T) * (size_t)m->n_params : (size_t)0, (void*)m->losses_d,
       sizeof(double) * (virial_out ? 8 + 10 * (size_t)c->max_batch : 8 + (size_t)c->max_batch),
-      train ? f_label : (const T*)nullptr, (T*)m->flab, train ? (size_t)nf * 3 * N : (size_t)0));
+      train ? f_label : (const T*)nullptr, (T*)m->flab, train ? (size_t)nf * 3 * N : (size_t)0,
+      m->mma ? (T*)m->wm : (T*)nullptr, m->wm_stride));
   c->launches++;
   mark();  // descriptors
   SweepCall<T> sc;
@@ -736,11 +853,14 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
       fb = (int)(((size_t)nf * 3 * N + 255) / 256);
       if (fb > 296) fb = 296;
     }
-    const int grid = nf + fb + (train ? 1 : 0);
-    STAFB_CUDA_OK(launch_chained(k_loss<T>, grid, 256, 0, s, d, nf, fb, per_atom, train ? 1 : 0, e_atom, energy,
+    // a large frame of an inference evaluation: its atomic energies summed by several blocks
+    const int eb = train ? 1 : std::min(LOSS_EB_MAX, std::max(1, N / 1024));
+    const int grid = nf * eb + fb + (train ? 1 : 0);
+    STAFB_CUDA_OK(launch_chained(k_loss<T>, grid, 256, 0, s, d, nf, eb, fb, per_atom, train ? 1 : 0, e_atom, energy,
                                  e_label, force, (const T*)m->flab, theta, (T)pe, (T)pf, (T)pb, (T)bound, loss_kind,
                                  (T*)m->ebar, grad, m->losses_d, cg->status_d, c->status_d, vacc, virial_out,
-                                 train ? m->mirror_next : (double*)nullptr));
+                                 train ? m->mirror_next : (double*)nullptr, m->epart,
+                                 reinterpret_cast<unsigned*>(m->epart + (size_t)c->max_batch * LOSS_EB_MAX)));
     m->mirror_next = nullptr;
     c->launches++;
   }

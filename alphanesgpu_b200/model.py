@@ -232,7 +232,10 @@ class StafModel:
         """(staging mode, atoms per thread group, forward smem bytes, backward smem bytes) of the MLP kernels."""
         out = np.zeros(4, np.int32)
         _lib.lib().stafb_model_mlp_config(self.h, out.ctypes.data_as(C.c_void_p))
-        return dict(stage=int(out[0]), apt=int(out[1]), fwd_smem=int(out[2]), bwd_smem=int(out[3]))
+        mma = np.zeros(4, np.int32)
+        _lib.lib().stafb_model_mlp_mma_config(self.h, mma.ctypes.data_as(C.c_void_p))
+        return dict(stage=int(out[0]), apt=int(out[1]), fwd_smem=int(out[2]), bwd_smem=int(out[3]),
+                    mma=int(mma[0]), mma_warps=int(mma[1]), mma_staged=int(mma[2]), mma_bwd_smem=int(mma[3]))
 
     def launches(self):
         return _lib.lib().stafb_last_launch_count(self.ctx.h)

@@ -115,7 +115,10 @@ class SlabDomain:
             rebuild = self._plan is None or self._nstep % self.halo_every == 0
         self._nstep += 1
         if self.world == 1:
-            e, f = self.compute(pos, types, n_own, rebuild)
+            # no ghosts to re-choose: the counts (and the device status word) are looked at on the first call only
+            first = self._plan is None
+            self._plan = self._plan or {}
+            e, f = self.compute(pos, types, n_own, first)
             return e, f[:n_own]
         if rebuild:
             self._make_plan()

@@ -505,6 +505,8 @@ def md_record(torch, dist, args, rank, world, local, dev, K):
     launches = model.launches() + (4 if world > 1 else 0)  # push, wait, return, collect of the halo exchange
     if world > 1:
         dom.check()
+    else:
+        model.ctx.raise_on_status("md timed region")
     # end to end: owned positions start in (pinned) host memory and owned forces end there, every step
     pin_x = dom.pos.cpu().pin_memory()
     pin_f = torch.empty_like(pin_x)

@@ -226,9 +226,16 @@ void stafb_model_offsets(const stafb_model* m, int t, int out6[6]);
  * out4 = { staging mode of the Dense layers in shared memory (2: all layers at kernel start, 1: one layer at a
  * time, 0: none, weights read from global memory), atoms per thread group (a block owns 8x that many atoms),
  * dynamic shared memory of the forward kernel, of the backward kernel (bytes) }.  The mode follows from the
- * layer sizes; the environment variables STAFB_MLP_STAGE / STAFB_MLP_APT, read by stafb_model_create,
+ * layer sizes; the environment variables STAFB_MLP_STAGE / STAFB_MLP_AW, read by stafb_model_create,
  * override it. */
 void stafb_model_mlp_config(const stafb_model* m, int out4[4]);
+/* The other arm of the MLP kernels (fp32 models only, selected with STAFB_MLP_MMA=1 in the environment of
+ * stafb_model_create): every dense product as mma.sync on the tensor cores - TF32 operands split in two, three
+ * products per tile, the main product accumulated outside the unit: fp32 accuracy.  On B200 it is slower than
+ * the FMA kernels (the legacy mma.sync path issues about one m16n8k8 per 30 cycles per SM), so it is off by
+ * default.  out4 = { 1 if in use, its warps per block (a block owns 16 atoms; STAFB_MLP_MMA_NW: 1, 2, 4, 8),
+ * 0, dynamic shared memory of the backward kernel }. */
+void stafb_model_mlp_mma_config(const stafb_model* m, int out4[4]);
 
 /* Energy and forces of nf frames (staf_models/staf_model.py:174-211; inference convention
  * staf_models/staf_model_inference_full.py:118-119 when per_atom_energy == 0):

@@ -97,6 +97,7 @@ def test_train_step_on_the_reference_model_shape(oracle, frame0, dtype):
     m = StafModel(shape, CFG, theta, emb, 1, dtype=_tdt(dtype), loss="huber", **kw)
     cfg = m.mlp_config()
     assert cfg["stage"] == (1 if dtype == np.float32 else 0), cfg  # layer-at-a-time in fp32, global reads in fp64
+    assert cfg["mma"] == 0, cfg  # the tensor-core arm is opt-in
     assert max(shape.Fa) // shape.C > 8  # more active angular channels per class than one chunk of the sweeps
     _check_train_step(oracle, m, shape, pos, box, el, fl, theta, emb, dtype, "huber", kw)
     m.close()
@@ -116,6 +117,37 @@ def test_train_step_in_every_mlp_staging_mode(oracle, frame0, monkeypatch, dtype
     m = StafModel(shape, CFG, theta, emb, 2, dtype=_tdt(dtype), loss="huber", **kw)
     assert m.mlp_config()["stage"] == stage
     _check_train_step(oracle, m, shape, pos, box, el, fl, theta, emb, dtype, "huber", kw, host_path=False)
+    m.close()
+
+
+@pytest.mark.parametrize("warps", [1, 2, 4, 8])
+def test_train_step_with_the_tensor_core_mlp(oracle, frame0, monkeypatch, warps):
+    """The tensor-core arm of the MLP kernels (fp32, STAFB_MLP_MMA=1) with 1, 2, 4 and 8 warps sharing a 16-atom
+    tile; two frames of 96 atoms leave partly filled tiles."""
+    from alphanesgpu_b200.model import StafModel
+    monkeypatch.setenv("STAFB_MLP_MMA", "1")
+    monkeypatch.setenv("STAFB_MLP_MMA_NW", str(warps))
+    pos, box, shape, theta, emb = _case("water96", [1000, 1001], frame0)
+    theta = _push_over_bound(shape, theta)
+    el, fl = synth.labels(2, shape.N)
+    kw = dict(pe=0.7, pf=1.3, pb=0.9, alpha_bound=5.0)
+    m = StafModel(shape, CFG, theta, emb, 2, dtype=torch.float32, loss="huber", **kw)
+    cfg = m.mlp_config()
+    assert (cfg["mma"], cfg["mma_warps"]) == (1, warps), cfg
+    _check_train_step(oracle, m, shape, pos, box, el, fl, theta, emb, np.float32, "huber", kw, host_path=False)
+    m.close()
+
+
+def test_the_tensor_core_mlp_on_the_reference_model_shape(oracle, frame0, monkeypatch):
+    """60-140-140-1: 18 output tiles per layer, so the wide form of the product (five tiles per warp) runs."""
+    from alphanesgpu_b200.model import StafModel
+    monkeypatch.setenv("STAFB_MLP_MMA", "1")
+    pos, box, shape, theta, emb = _case("frame0", None, frame0)
+    el, fl = synth.labels(1, shape.N)
+    kw = dict(pe=0.7, pf=1.3, pb=0.9, alpha_bound=5.0)
+    m = StafModel(shape, CFG, theta, emb, 1, dtype=torch.float32, loss="huber", **kw)
+    assert m.mlp_config()["mma"] == 1
+    _check_train_step(oracle, m, shape, pos, box, el, fl, theta, emb, np.float32, "huber", kw, host_path=False)
     m.close()
 
 
