@@ -877,6 +877,45 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
   return STAFB_OK;
 }
 
+// The MLP head alone on caller-supplied fingerprints: energy = 0.5 * sum of the atomic energies,
+// dE_daf = d(sum of the atomic energies)/dAF - the convention of the reference's pluggable MLP
+// (libstaf/include/staf_mlp.h:10-15).  af and dE_daf: [N][Fmax] rows in the model's atom order.
+template <class T>
+static int run_mlp_only(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* af, const T* theta, const T* emb,
+                        T* energy, T* dE_daf) {
+  const ModelDev& d = m->md;
+  c->launches = 0;
+  STAFB_CUDA_OK(launch_chained(k_prep<T>, 64, 256, 0, s, d, theta, emb, (T*)m->wpack, m->wstride, m->spar, m->sl.total,
+                               m->sl, (void*)nullptr, (size_t)0, (void*)nullptr, (size_t)0, (void*)m->losses_d,
+                               sizeof(double) * (8 + (size_t)c->max_batch), (const T*)nullptr, (T*)m->flab, (size_t)0,
+                               m->mma ? (T*)m->wm : (T*)nullptr, m->wm_stride));
+  c->launches++;
+  int rc = launch_mlp_fwd<T>(m, s, 1, theta, af, (T*)m->acts, (T*)m->e_atom, dE_daf);
+  if (rc != STAFB_OK) return rc;
+  const int eb = std::min(LOSS_EB_MAX, std::max(1, d.N / 1024));
+  // an ordinary launch: k_loss sums the atomic energies ahead of its chain wait, which is only right when the MLP
+  // kernel is two kernels back (as in the fused sequences); here it is the direct predecessor
+  k_loss<T><<<eb, 256, 0, s>>>(d, 1, eb, 0, 0, 0, (const T*)m->e_atom, energy, (const T*)nullptr, (const T*)nullptr,
+                               (const T*)nullptr, theta, T(0), T(0), T(0), T(0), 0, (T*)m->ebar, (T*)nullptr,
+                               m->losses_d, c->status_d, c->status_d, (const double*)nullptr, (T*)nullptr,
+                               (double*)nullptr, m->epart,
+                               reinterpret_cast<unsigned*>(m->epart + (size_t)c->max_batch * LOSS_EB_MAX));
+  c->launches++;
+  STAFB_CUDA_OK(cudaGetLastError());
+  return STAFB_OK;
+}
+
+extern "C" int stafb_mlp_eval(stafb_ctx* c, stafb_model* m, void* stream, const void* af_d, const void* theta,
+                              const void* emb, void* energy_d, void* dE_daf_d) {
+  if (!c || !m || !af_d || !theta || !emb || !energy_d || !dE_daf_d) return STAFB_ERR_INVALID;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (c->dtype == STAFB_F32)
+    return run_mlp_only<float>(c, m, s, (const float*)af_d, (const float*)theta, (const float*)emb, (float*)energy_d,
+                               (float*)dE_daf_d);
+  return run_mlp_only<double>(c, m, s, (const double*)af_d, (const double*)theta, (const double*)emb,
+                              (double*)energy_d, (double*)dE_daf_d);
+}
+
 extern "C" int stafb_energy_force(stafb_ctx* c, stafb_model* m, void* stream, const void* pos, const void* box,
                                   int nf, const void* theta, const void* emb, int per_atom, void* energy,
                                   void* force) {

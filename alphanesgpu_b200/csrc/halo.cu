@@ -13,7 +13,8 @@
 //   flags                   "positions from lo / hi", "forces from lo / hi", "energy of rank r": the number of the
 //                           evaluation they belong to (monotonic, so nothing is ever cleared).
 // An evaluation is four small launches around stafb_energy_force_domain:
-//   push_positions   gather the face atoms, store them into the neighbours' arrays, publish;
+//   push_positions   gather the face atoms, store them into the neighbours' arrays, publish (a few blocks; the
+//                    one that finishes last publishes);
 //   wait_positions   bounded wait for both neighbours (a status on a miss, never a hang);
 //   return_forces    store the ghost forces into the neighbours' frecv, the energy into everybody's esl, publish;
 //   collect          bounded wait, add the returned forces onto the owners, sum the energies in rank order.
@@ -49,9 +50,27 @@ struct HaloView {
   int* flags_of[HALO_MAX];          // every rank's flag words
   int* step_d;                      // [1] evaluations completed
   int* status;
+  int* ctr;                         // [4] arrival counters of push / return / collect, failure mark of collect
   long long wait_cycles;
   int cap_face;
 };
+
+constexpr int HALO_BLOCKS = 8;    // blocks of the kernels that move face atoms
+constexpr int HALO_THREADS = 512;
+
+// The block that arrives last at `ctr` (all others have fenced their stores before arriving) returns true and
+// leaves the counter at zero for the next launch.
+__device__ __forceinline__ bool h_last_block(int* ctr) {
+  __shared__ int last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    last = atomicAdd(ctr, 1) == (int)gridDim.x - 1;
+    if (last) { *ctr = 0; __threadfence_system(); }
+  }
+  __syncthreads();
+  return last != 0;
+}
 
 // What the device-side choice of the ghost sets needs on top of the peers' pointers.
 struct HaloPlanView {
@@ -94,25 +113,24 @@ __device__ __forceinline__ bool h_wait(const int* p, int tag, long long cycles) 
   return true;
 }
 
-// One block.  The face atoms go to the neighbours; then the flags.
+// The face atoms go to the neighbours; the block that finishes last publishes the flags.
 template <class T>
-__global__ void __launch_bounds__(1024) k_halo_push_pos(HaloView v) {
+__global__ void __launch_bounds__(HALO_THREADS) k_halo_push_pos(HaloView v) {
   chain_wait();
   const int tag = *reinterpret_cast<volatile int*>(v.step_d) + 1;
   const T* pos = reinterpret_cast<const T*>(v.pos);
   T* plo = reinterpret_cast<T*>(v.pos_lo);
   T* phi = reinterpret_cast<T*>(v.pos_hi);
-  for (int q = threadIdx.x; q < 3 * v.n_send_lo; q += blockDim.x) {
+  const int tid = blockIdx.x * blockDim.x + threadIdx.x, nth = gridDim.x * blockDim.x;
+  for (int q = tid; q < 3 * v.n_send_lo; q += nth) {
     const int a = q / 3, c = q - 3 * a;
     plo[(size_t)(v.dst_lo + a) * 3 + c] = pos[(size_t)v.send_lo[a] * 3 + c];
   }
-  for (int q = threadIdx.x; q < 3 * v.n_send_hi; q += blockDim.x) {
+  for (int q = tid; q < 3 * v.n_send_hi; q += nth) {
     const int a = q / 3, c = q - 3 * a;
     phi[(size_t)(v.dst_hi + a) * 3 + c] = pos[(size_t)v.send_hi[a] * 3 + c];
   }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
+  if (h_last_block(v.ctr + 0) && threadIdx.x == 0) {
     // what leaves through my lower face arrives through lo's UPPER face
     h_st_sys(v.flags_of[v.lo] + 1, tag);
     h_st_sys(v.flags_of[v.hi] + 0, tag);
@@ -129,9 +147,10 @@ __global__ void k_halo_wait(const int* fa, const int* fb, const int* step_d, lon
   }
 }
 
-// One block.  Ghost forces back to their owners' ranks, my energy to everybody; then the flags.
+// Ghost forces back to their owners' ranks, my energy to everybody; the block that finishes last publishes.
 template <class T>
-__global__ void __launch_bounds__(1024) k_halo_return(HaloView v, const T* __restrict__ force, const T* __restrict__ energy) {
+__global__ void __launch_bounds__(HALO_THREADS)
+    k_halo_return(HaloView v, const T* __restrict__ force, const T* __restrict__ energy) {
   chain_wait();
   const int tag = *reinterpret_cast<volatile int*>(v.step_d) + 1;
   // my ghosts from lo are the atoms lo sent through ITS upper face: they go to lo's frecv[1]
@@ -139,55 +158,63 @@ __global__ void __launch_bounds__(1024) k_halo_return(HaloView v, const T* __res
   T* to_hi = reinterpret_cast<T*>(v.frecv_of_hi);
   const T* g_lo = force + (size_t)v.n_own * 3;
   const T* g_hi = g_lo + (size_t)v.n_from_lo * 3;
-  for (int q = threadIdx.x; q < 3 * v.n_from_lo; q += blockDim.x) to_lo[q] = g_lo[q];
-  for (int q = threadIdx.x; q < 3 * v.n_from_hi; q += blockDim.x) to_hi[q] = g_hi[q];
-  if (threadIdx.x < v.world) v.esl_of[threadIdx.x][(tag & 1) * HALO_MAX + v.rank] = (double)energy[0];
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    h_st_sys(v.flags_of[v.lo] + 3, tag);  // lo sees "forces from hi"
-    h_st_sys(v.flags_of[v.hi] + 2, tag);
-  }
-  if (threadIdx.x < v.world) {
-    __threadfence_system();
-    h_st_sys(v.flags_of[threadIdx.x] + 8 + v.rank, tag);
+  const int tid = blockIdx.x * blockDim.x + threadIdx.x, nth = gridDim.x * blockDim.x;
+  for (int q = tid; q < 3 * v.n_from_lo; q += nth) to_lo[q] = g_lo[q];
+  for (int q = tid; q < 3 * v.n_from_hi; q += nth) to_hi[q] = g_hi[q];
+  if (blockIdx.x == 0 && threadIdx.x < v.world)
+    v.esl_of[threadIdx.x][(tag & 1) * HALO_MAX + v.rank] = (double)energy[0];
+  if (h_last_block(v.ctr + 1)) {
+    if (threadIdx.x == 0) {
+      h_st_sys(v.flags_of[v.lo] + 3, tag);  // lo sees "forces from hi"
+      h_st_sys(v.flags_of[v.hi] + 2, tag);
+    }
+    if (threadIdx.x < v.world) h_st_sys(v.flags_of[threadIdx.x] + 8 + v.rank, tag);
   }
 }
 
-// One block.  Waits for the forces of both neighbours and the energies of all ranks, adds the returned forces
-// onto the owners (an atom near both faces gets two contributions: atomics) and sums the energies in rank order.
+// Every block waits for the forces of both neighbours (block 0 also for the energies of all ranks), adds its
+// share of the returned forces onto the owners (an atom near both faces gets two contributions: atomics); block 0
+// sums the energies in rank order.  The block that finishes last advances the evaluation number - unless a wait
+// ran out somewhere, in which case the number stays as it was.
 template <class T>
-__global__ void __launch_bounds__(1024) k_halo_collect(HaloView v, T* __restrict__ force, T* __restrict__ energy_out) {
+__global__ void __launch_bounds__(HALO_THREADS) k_halo_collect(HaloView v, T* __restrict__ force, T* __restrict__ energy_out) {
   __shared__ int ok_s;
   chain_wait();
   const int tag = *reinterpret_cast<volatile int*>(v.step_d) + 1;
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();
-  if (threadIdx.x < v.world + 2) {
-    const int* f = threadIdx.x < v.world ? v.flags + 8 + threadIdx.x : v.flags + 2 + (threadIdx.x - v.world);
-    if (!h_wait(f, tag, v.wait_cycles)) { ok_s = 0; atomicCAS(v.status, 0, STAFB_ERR_PEER_TIMEOUT); }
+  const int nwait = blockIdx.x == 0 ? v.world + 2 : 2;
+  if (threadIdx.x < nwait) {
+    const int* f = threadIdx.x < 2 ? v.flags + 2 + threadIdx.x : v.flags + 8 + (threadIdx.x - 2);
+    if (!h_wait(f, tag, v.wait_cycles)) {
+      ok_s = 0;
+      atomicCAS(v.status, 0, STAFB_ERR_PEER_TIMEOUT);
+      atomicExch(v.ctr + 3, 1);
+    }
     __threadfence_system();
   }
   __syncthreads();
   if (ok_s) {
     const T* r_lo = reinterpret_cast<const T*>(v.frecv);
     const T* r_hi = r_lo + (size_t)v.cap_face * 3;
-    for (int q = threadIdx.x; q < 3 * v.n_send_lo; q += blockDim.x) {
+    const int tid = blockIdx.x * blockDim.x + threadIdx.x, nth = gridDim.x * blockDim.x;
+    for (int q = tid; q < 3 * v.n_send_lo; q += nth) {
       const int a = q / 3, c = q - 3 * a;
       atomicAdd(force + (size_t)v.send_lo[a] * 3 + c, r_lo[q]);
     }
-    for (int q = threadIdx.x; q < 3 * v.n_send_hi; q += blockDim.x) {
+    for (int q = tid; q < 3 * v.n_send_hi; q += nth) {
       const int a = q / 3, c = q - 3 * a;
       atomicAdd(force + (size_t)v.send_hi[a] * 3 + c, r_hi[q]);
     }
-    if (threadIdx.x == 0) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
       double e = 0.0;
       for (int r = 0; r < v.world; r++) e += v.esl[(tag & 1) * HALO_MAX + r];
       energy_out[0] = (T)e;
     }
   }
-  __syncthreads();
-  if (threadIdx.x == 0 && ok_s) *v.step_d = tag;  // a collect that gave up leaves the evaluation number as it was
+  if (h_last_block(v.ctr + 2) && threadIdx.x == 0) {
+    if (atomicExch(v.ctr + 3, 0) == 0) *v.step_d = tag;
+  }
 }
 
 // One block.  Chooses, in index order, the owned atoms within `reach` of the lower / upper face of this rank's
@@ -318,6 +345,7 @@ struct stafb_halo {
   int* send_idx;  // [2][cap_face] device
   int* step_d;    // [1]
   int* status_d;  // [1]
+  int* ctr_d;     // [4]
   void* force;    // [cap_atoms][3] local scratch for the evaluation's forces
   long long wait_cycles;
   HaloView view;
@@ -345,6 +373,8 @@ extern "C" int stafb_halo_create(stafb_ctx* c, int rank, int world, int cap_atom
   STAFB_CUDA_OK(cudaMemset(h->step_d, 0, sizeof(int)));
   STAFB_CUDA_OK(cudaMalloc((void**)&h->status_d, sizeof(int)));
   STAFB_CUDA_OK(cudaMemset(h->status_d, 0, sizeof(int)));
+  STAFB_CUDA_OK(cudaMalloc((void**)&h->ctr_d, sizeof(int) * 4));
+  STAFB_CUDA_OK(cudaMemset(h->ctr_d, 0, sizeof(int) * 4));
   STAFB_CUDA_OK(cudaMalloc(&h->force, h->es * 3 * (size_t)cap_atoms));
   STAFB_CUDA_OK(cudaMalloc((void**)&h->plan_d, sizeof(int) * 8));
   STAFB_CUDA_OK(cudaMemset(h->plan_d, 0, sizeof(int) * 8));
@@ -431,6 +461,7 @@ static void fill_view(stafb_halo* h, int n_own, int n_from_lo, int n_from_hi, in
   }
   v.step_d = h->step_d;
   v.status = h->status_d;
+  v.ctr = h->ctr_d;
   v.wait_cycles = h->wait_cycles;
   v.cap_face = h->cap_face;
   h->planned = 1;
@@ -528,8 +559,8 @@ extern "C" int stafb_halo_set_plan(stafb_halo* h, void* stream, int n_own, int n
 extern "C" int stafb_halo_push_positions(stafb_halo* h, void* stream) {
   if (!h || !h->planned) return STAFB_ERR_INVALID;
   cudaStream_t s = (cudaStream_t)stream;
-  if (h->dtype == STAFB_F32) STAFB_CUDA_OK(launch_chained(k_halo_push_pos<float>, 1, 1024, 0, s, h->view));
-  else STAFB_CUDA_OK(launch_chained(k_halo_push_pos<double>, 1, 1024, 0, s, h->view));
+  if (h->dtype == STAFB_F32) STAFB_CUDA_OK(launch_chained(k_halo_push_pos<float>, HALO_BLOCKS, HALO_THREADS, 0, s, h->view));
+  else STAFB_CUDA_OK(launch_chained(k_halo_push_pos<double>, HALO_BLOCKS, HALO_THREADS, 0, s, h->view));
   return STAFB_OK;
 }
 
@@ -545,10 +576,10 @@ extern "C" int stafb_halo_return_forces(stafb_halo* h, void* stream, const void*
   if (!h || !h->planned || !force_d || !energy_d) return STAFB_ERR_INVALID;
   cudaStream_t s = (cudaStream_t)stream;
   if (h->dtype == STAFB_F32)
-    STAFB_CUDA_OK(launch_chained(k_halo_return<float>, 1, 1024, 0, s, h->view, (const float*)force_d,
+    STAFB_CUDA_OK(launch_chained(k_halo_return<float>, HALO_BLOCKS, HALO_THREADS, 0, s, h->view, (const float*)force_d,
                                  (const float*)energy_d));
   else
-    STAFB_CUDA_OK(launch_chained(k_halo_return<double>, 1, 1024, 0, s, h->view, (const double*)force_d,
+    STAFB_CUDA_OK(launch_chained(k_halo_return<double>, HALO_BLOCKS, HALO_THREADS, 0, s, h->view, (const double*)force_d,
                                  (const double*)energy_d));
   return STAFB_OK;
 }
@@ -557,9 +588,9 @@ extern "C" int stafb_halo_collect(stafb_halo* h, void* stream, void* force_d, vo
   if (!h || !h->planned || !force_d || !energy_out_d) return STAFB_ERR_INVALID;
   cudaStream_t s = (cudaStream_t)stream;
   if (h->dtype == STAFB_F32)
-    STAFB_CUDA_OK(launch_chained(k_halo_collect<float>, 1, 1024, 0, s, h->view, (float*)force_d, (float*)energy_out_d));
+    STAFB_CUDA_OK(launch_chained(k_halo_collect<float>, HALO_BLOCKS, HALO_THREADS, 0, s, h->view, (float*)force_d, (float*)energy_out_d));
   else
-    STAFB_CUDA_OK(launch_chained(k_halo_collect<double>, 1, 1024, 0, s, h->view, (double*)force_d,
+    STAFB_CUDA_OK(launch_chained(k_halo_collect<double>, HALO_BLOCKS, HALO_THREADS, 0, s, h->view, (double*)force_d,
                                  (double*)energy_out_d));
   return STAFB_OK;
 }
@@ -575,6 +606,6 @@ extern "C" void stafb_halo_destroy(stafb_halo* h) {
   if (!h) return;
   for (int r = 0; r < h->world && h->connected == 1; r++)
     if (r != h->rank && h->peer[r]) cudaIpcCloseMemHandle(h->peer[r]);
-  cudaFree(h->block); cudaFree(h->send_idx); cudaFree(h->step_d); cudaFree(h->status_d); cudaFree(h->force); cudaFree(h->plan_d);
+  cudaFree(h->block); cudaFree(h->send_idx); cudaFree(h->step_d); cudaFree(h->status_d); cudaFree(h->force); cudaFree(h->plan_d); cudaFree(h->ctr_d);
   free(h);
 }

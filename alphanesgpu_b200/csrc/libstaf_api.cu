@@ -3,6 +3,7 @@
 // (staf_api.cpp:249-294), Cartesian in / Cartesian forces out in the caller's atom order, energy
 // 0.5*sum(e_i), negative integer error codes, never exit().
 #include <math.h>
+#include <algorithm>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -445,3 +446,117 @@ extern "C" void staf_free(StafModel* m) {
   if (m->stream) cudaStreamDestroy(m->stream);
   delete m;
 }
+
+// ---------------------------------------------------------------------------- pluggable-MLP API (staf_mlp.h)
+#include "../../include/staf_mlp.h"
+
+extern "C" int stafb_mlp_eval(stafb_ctx* ctx, stafb_model* m, void* stream, const void* af_d, const void* theta_d,
+                              const void* emb_d, void* energy_d, void* dE_daf_d);
+extern "C" int stafb_status(stafb_ctx* ctx, void* stream);
+
+// The reference's StafMlp (libstaf/src/mlp/staf_mlp_ort.cc:24-60) owns an ONNX session or the Dense weights of
+// every type; here it is the loaded model plus two device arrays [atoms][Fmax] for the fingerprints and dE/dAF.
+struct StafMlp {
+  StafModel* m;
+  void *af_d, *nd_d, *e_d;
+  size_t cap_rows;
+  std::vector<char> host;  // packing scratch, rows of Fmax
+};
+
+extern "C" StafMlp* staf_mlp_create(StafMlpBackend backend, const char* model_dir, int precision, int device_id) {
+  if (precision != 0 && precision != 1) return NULL;
+  StafOptions opt;
+  staf_options_default(&opt);
+  opt.mlp_backend = backend;
+  opt.precision = precision;
+  opt.device_id = device_id;
+  StafModel* m = staf_load(model_dir, &opt);
+  if (!m) return NULL;
+  StafMlp* p = new StafMlp();
+  p->m = m;
+  p->af_d = p->nd_d = p->e_d = nullptr;
+  p->cap_rows = 0;
+  return p;
+}
+
+template <class T>
+static int mlp_eval_impl(StafMlp* p, StafMlpEval* io, const T* af, T* energy, T* dE) {
+  StafModel* m = p->m;
+  if (!af || !energy || !dE || !io->n_atoms || !io->n_af || io->n_type != m->nt) return io->n_type != m->nt ? -2 : -1;
+  std::vector<int> tipos(m->nt);
+  int N = 0, Fmax = 0;
+  for (int t = 0; t < m->nt; t++) {
+    if (io->n_af[t] != m->Fr[t] + m->Fa[t] || io->n_atoms[t] < 0) return -2;
+    tipos[t] = io->n_atoms[t];
+    N += tipos[t];
+    Fmax = std::max(Fmax, m->Fr[t] + m->Fa[t]);
+  }
+  if (N <= 0) return -1;
+  if (cudaSetDevice(m->opt.device_id) != cudaSuccess) return -14;
+  if (ensure_device(m, N, tipos) != 0) return -1;
+  const size_t rows = (size_t)N;
+  if (rows > p->cap_rows) {
+    cudaFree(p->af_d); cudaFree(p->nd_d); cudaFree(p->e_d);
+    p->af_d = p->nd_d = p->e_d = nullptr;
+    p->cap_rows = 0;
+    const size_t cap = rows + rows / 4 + 64;
+    if (cudaMalloc(&p->af_d, sizeof(T) * cap * Fmax) != cudaSuccess ||
+        cudaMalloc(&p->nd_d, sizeof(T) * cap * Fmax) != cudaSuccess || cudaMalloc(&p->e_d, sizeof(T)) != cudaSuccess)
+      return -1;
+    p->cap_rows = cap;
+  }
+  // packed [n_atoms_k][n_af_k] per type -> rows of Fmax in type order (the model's atom order)
+  p->host.resize(sizeof(T) * rows * Fmax);
+  T* h = reinterpret_cast<T*>(p->host.data());
+  {
+    size_t src = 0, row = 0;
+    for (int t = 0; t < m->nt; t++)
+      for (int a = 0; a < tipos[t]; a++, row++) {
+        const int F = io->n_af[t];
+        for (int i = 0; i < Fmax; i++) h[row * Fmax + i] = i < F ? af[src + i] : T(1);
+        src += F;
+      }
+  }
+  if (cudaMemcpyAsync(p->af_d, h, sizeof(T) * rows * Fmax, cudaMemcpyHostToDevice, m->stream) != cudaSuccess) return -14;
+  const int rc = stafb_mlp_eval(m->ctx, m->model, m->stream, p->af_d, m->theta_d, m->emb_d, p->e_d, p->nd_d);
+  if (rc != STAFB_OK) return rc == STAFB_ERR_CUDA ? -14 : -1;
+  T e = T(0);
+  if (cudaMemcpyAsync(h, p->nd_d, sizeof(T) * rows * Fmax, cudaMemcpyDeviceToHost, m->stream) != cudaSuccess ||
+      cudaMemcpyAsync(&e, p->e_d, sizeof(T), cudaMemcpyDeviceToHost, m->stream) != cudaSuccess)
+    return -14;
+  const int st = stafb_status(m->ctx, m->stream);  // waits for the stream
+  if (st == STAFB_ERR_CUDA) return -14;
+  if (st != STAFB_OK) return -13;
+  {
+    size_t dst = 0, row = 0;
+    for (int t = 0; t < m->nt; t++)
+      for (int a = 0; a < tipos[t]; a++, row++) {
+        const int F = io->n_af[t];
+        for (int i = 0; i < F; i++) dE[dst + i] = h[row * Fmax + i];
+        dst += F;
+      }
+  }
+  energy[0] = e;
+  return 0;
+}
+
+extern "C" int staf_mlp_eval(StafMlp* mlp, StafMlpEval* io) {
+  if (!mlp || !mlp->m || !io) return -1;
+  if (mlp->m->opt.precision == 1) return mlp_eval_impl<double>(mlp, io, io->af_f64, io->energy_f64, io->dE_daf_f64);
+  return mlp_eval_impl<float>(mlp, io, io->af_f32, io->energy_f32, io->dE_daf_f32);
+}
+
+extern "C" void staf_mlp_destroy(StafMlp* mlp) {
+  if (!mlp) return;
+  if (mlp->m) cudaSetDevice(mlp->m->opt.device_id);
+  cudaFree(mlp->af_d); cudaFree(mlp->nd_d); cudaFree(mlp->e_d);
+  staf_free(mlp->m);
+  delete mlp;
+}
+
+extern "C" int staf_mlp_ntypes(const StafMlp* mlp) { return mlp && mlp->m ? mlp->m->nt : 0; }
+extern "C" int staf_mlp_n_af(const StafMlp* mlp, int type) {
+  if (!mlp || !mlp->m || type < 0 || type >= mlp->m->nt) return 0;
+  return mlp->m->Fr[type] + mlp->m->Fa[type];
+}
+extern "C" int staf_mlp_precision(const StafMlp* mlp) { return mlp && mlp->m ? mlp->m->opt.precision : 0; }

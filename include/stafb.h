@@ -342,6 +342,13 @@ void stafb_peer_destroy(stafb_peer* p);
 int stafb_allreduce_adam(stafb_ctx* ctx, stafb_peer* p, void* stream, int parity, void* theta_d, void* m_d, void* v_d,
                          double lr, double beta1, double beta2, double eps, int* step_d);
 
+/* The MLP head alone on caller-supplied fingerprints (what libstaf/include/staf_mlp.h:10-15 of the reference
+ * defines for its pluggable MLP): energy_d[1] = 0.5 * sum of the atomic energies, dE_daf_d = d(sum of the atomic
+ * energies)/dAF.  af_d and dE_daf_d: [N][Fmax] rows in the model's atom order (species-sorted; a species with fewer
+ * fingerprints than Fmax leaves the tail of its rows unused).  One frame of the model's current atom counts. */
+int stafb_mlp_eval(stafb_ctx* ctx, stafb_model* m, void* stream, const void* af_d, const void* theta_d,
+                   const void* emb_d, void* energy_d, void* dE_daf_d);
+
 /* Halo exchange of a slab decomposition over NVLink peer memory, for the ranks (one per GPU) of one node.  No
  * reference counterpart as a function: it is what LAMMPS' forward and reverse communication do around
  * PairSTAF::compute (lammps/USER-STAF/pair_staf.cpp:129-145 ghost atoms as neighbours, :250 forces on ghosts, summed

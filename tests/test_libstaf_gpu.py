@@ -214,3 +214,59 @@ def test_staf_compute_domain_slab_parity(lib, frame0, nslab, precision, tol):
     assert rel_err(ftot, f0.reshape(N, 3)) <= tol
     assert rel_err(vtot[:3], v0[:3]) <= 20 * tol
     lib.staf_free(m)
+
+
+class StafMlpEval(C.Structure):
+    _fields_ = [("n_type", C.c_int), ("n_atoms", C.c_void_p), ("n_af", C.c_void_p), ("af_f32", C.c_void_p),
+                ("af_f64", C.c_void_p), ("energy_f32", C.c_void_p), ("energy_f64", C.c_void_p),
+                ("dE_daf_f32", C.c_void_p), ("dE_daf_f64", C.c_void_p)]
+
+
+@pytest.mark.parametrize("precision,tag,tol", [(0, "f32", 5e-6), (1, "f64", 1e-12)])
+def test_staf_mlp_eval_matches_the_reference_native_evaluator(lib, frame0, precision, tag, tol):
+    """include/staf_mlp.h (the reference's libstaf/include/staf_mlp.h:17-42) on the fingerprints and outputs
+    recorded from the reference's own native Dense evaluator (tests/golden/ref_mlp.npz, made by
+    tests/golden/make_ref_fixtures.py from libstaf/src/mlp/staf_mlp_ort.cc)."""
+    import os
+    from conftest import GOLDEN
+    g = np.load(os.path.join(GOLDEN, "ref_mlp.npz"))
+    dt = np.float32 if precision == 0 else np.float64
+    lib.staf_mlp_create.restype = C.c_void_p
+    lib.staf_mlp_create.argtypes = [C.c_int, C.c_char_p, C.c_int, C.c_int]
+    lib.staf_mlp_eval.argtypes = [C.c_void_p, C.POINTER(StafMlpEval)]
+    lib.staf_mlp_destroy.argtypes = [C.c_void_p]
+    for fn in (lib.staf_mlp_ntypes, lib.staf_mlp_precision):
+        fn.argtypes = [C.c_void_p]
+    lib.staf_mlp_n_af.argtypes = [C.c_void_p, C.c_int]
+    h = lib.staf_mlp_create(2, frame0["dir"].encode(), precision, 0)
+    assert h
+    assert lib.staf_mlp_ntypes(h) == 2 and lib.staf_mlp_precision(h) == precision
+    afs = [np.ascontiguousarray(g["af%d" % k], dt) for k in (0, 1)]
+    assert [lib.staf_mlp_n_af(h, k) for k in (0, 1)] == [a.shape[1] for a in afs]
+    for rep in range(2):
+        n_atoms = np.array([a.shape[0] for a in afs], np.int32)
+        n_af = np.array([a.shape[1] for a in afs], np.int32)
+        packed = np.concatenate([a.ravel() for a in afs])
+        energy = np.zeros(1, dt)
+        dE = np.zeros_like(packed)
+        io = StafMlpEval(2, n_atoms.ctypes.data, n_af.ctypes.data, None, None, None, None, None, None)
+        if precision == 0:
+            io.af_f32, io.energy_f32, io.dE_daf_f32 = packed.ctypes.data, energy.ctypes.data, dE.ctypes.data
+        else:
+            io.af_f64, io.energy_f64, io.dE_daf_f64 = packed.ctypes.data, energy.ctypes.data, dE.ctypes.data
+        assert lib.staf_mlp_eval(h, C.byref(io)) == 0
+        ref_d = np.concatenate([g["%s_d%d" % (tag, k)].ravel()[:a.size] for k, a in enumerate(afs)])
+        ref_e = float(g["%s_energy" % tag])
+        if rep == 0:
+            assert rel_err(dE, ref_d) <= tol
+            assert abs(float(energy[0]) - ref_e) <= 50 * tol * abs(ref_e)
+            full = dE.copy()
+            afs = [a[:3] for a in afs]  # next: fewer atoms of each type (the model's counts change)
+        else:
+            # the first 3 atoms of each type: the same rows of the full result
+            n0 = g["af0"].shape[0] * g["af0"].shape[1]
+            want = np.concatenate([full[:3 * afs[0].shape[1]], full[n0:n0 + 3 * afs[1].shape[1]]])
+            assert rel_err(dE, want) <= tol
+    bad = StafMlpEval(3, None, None, None, None, None, None, None, None)
+    assert lib.staf_mlp_eval(h, C.byref(bad)) != 0
+    lib.staf_mlp_destroy(h)
