@@ -337,12 +337,15 @@ struct stafb_halo {
   int rank, world, dtype, cap_atoms, cap_face;
   size_t es, off_frecv, off_esl, off_flags, off_mail, off_reply, bytes;
   int* plan_d;    // [8]
+  int* plan_h;    // pinned: [0..7] the plan, [8] the status word, copied behind plan_done
+  cudaEvent_t plan_ev;
   int plan_no;
+  int lists;      // which half of send_idx the plan in force uses (a plan under way fills the other)
   HaloPlanView pv;
   char* block;
   char* peer[HALO_MAX];
   int connected;  // 1: IPC mappings to close, 2: pointers of handles in this process
-  int* send_idx;  // [2][cap_face] device
+  int* send_idx;  // [2 sets][2][cap_face] device
   int* step_d;    // [1]
   int* status_d;  // [1]
   int* ctr_d;     // [4]
@@ -368,7 +371,9 @@ extern "C" int stafb_halo_create(stafb_ctx* c, int rank, int world, int cap_atom
   h->bytes = h->off_reply + up(sizeof(int) * 2);
   STAFB_CUDA_OK(cudaMalloc((void**)&h->block, h->bytes));
   STAFB_CUDA_OK(cudaMemset(h->block, 0, h->bytes));
-  STAFB_CUDA_OK(cudaMalloc((void**)&h->send_idx, sizeof(int) * 2 * (size_t)cap_face));
+  STAFB_CUDA_OK(cudaMalloc((void**)&h->send_idx, sizeof(int) * 4 * (size_t)cap_face));
+  STAFB_CUDA_OK(cudaMallocHost((void**)&h->plan_h, sizeof(int) * 16));
+  STAFB_CUDA_OK(cudaEventCreateWithFlags(&h->plan_ev, cudaEventDisableTiming));
   STAFB_CUDA_OK(cudaMalloc((void**)&h->step_d, sizeof(int)));
   STAFB_CUDA_OK(cudaMemset(h->step_d, 0, sizeof(int)));
   STAFB_CUDA_OK(cudaMalloc((void**)&h->status_d, sizeof(int)));
@@ -446,7 +451,7 @@ static void fill_view(stafb_halo* h, int n_own, int n_from_lo, int n_from_hi, in
   v.hi = (h->rank + 1) % h->world;
   v.n_own = n_own; v.n_from_lo = n_from_lo; v.n_from_hi = n_from_hi;
   v.n_send_lo = n_send_lo; v.n_send_hi = n_send_hi;
-  v.send_lo = h->send_idx; v.send_hi = h->send_idx + h->cap_face;
+  v.send_lo = h->send_idx + (size_t)h->lists * 2 * h->cap_face; v.send_hi = v.send_lo + h->cap_face;
   v.dst_lo = dst_off_lo; v.dst_hi = dst_off_hi;
   v.pos = h->block;
   v.pos_lo = h->peer[v.lo]; v.pos_hi = h->peer[v.hi];
@@ -488,7 +493,7 @@ extern "C" int stafb_halo_plan_select(stafb_halo* h, void* stream, int n_own, co
   v.tag = ++h->plan_no;
   v.L = L; v.reach = reach;
   v.pos = h->block; v.types = types_d;
-  v.send_idx = h->send_idx; v.plan = h->plan_d;
+  v.send_idx = h->send_idx + (size_t)(h->lists ^ 1) * 2 * h->cap_face; v.plan = h->plan_d;
   auto mail = [&](int r, int slot) {
     return reinterpret_cast<int*>(h->peer[r] + h->off_mail) + (size_t)slot * (1 + h->cap_face);
   };
@@ -518,19 +523,25 @@ extern "C" int stafb_halo_plan_layout(stafb_halo* h, void* stream, int* type_all
 
 extern "C" int stafb_halo_plan_done(stafb_halo* h, void* stream) {
   if (!h || !h->pv.n_own) return STAFB_ERR_INVALID;
-  STAFB_CUDA_OK(launch_chained(k_halo_plan_done, 1, 32, 0, (cudaStream_t)stream, h->pv));
+  cudaStream_t s = (cudaStream_t)stream;
+  STAFB_CUDA_OK(launch_chained(k_halo_plan_done, 1, 32, 0, s, h->pv));
+  // the result goes to pinned memory behind an event, so that _finish need not wait for work enqueued after this
+  STAFB_CUDA_OK(cudaMemcpyAsync(h->plan_h, h->plan_d, sizeof(int) * 8, cudaMemcpyDeviceToHost, s));
+  STAFB_CUDA_OK(cudaMemcpyAsync(h->plan_h + 8, h->status_d, sizeof(int), cudaMemcpyDeviceToHost, s));
+  STAFB_CUDA_OK(cudaEventRecord(h->plan_ev, s));
   return STAFB_OK;
 }
 
-// Waits for the stream; counts_out[4] = n_from_lo, n_from_hi, n_send_lo, n_send_hi.  Returns the exchange's status.
+// Waits for the three plan launches (not for anything enqueued after them) and puts the new plan in force for the
+// launches that follow; counts_out[4] = n_from_lo, n_from_hi, n_send_lo, n_send_hi.  Returns the exchange's status.
+// Evaluations under the old plan may be enqueued between _done and _finish: they keep the old lists and offsets.
 extern "C" int stafb_halo_plan_finish(stafb_halo* h, void* stream, int* counts_out) {
+  (void)stream;
   if (!h || !h->pv.n_own || !counts_out) return STAFB_ERR_INVALID;
-  int p[8], st = 0;
-  cudaStream_t s = (cudaStream_t)stream;
-  STAFB_CUDA_OK(cudaMemcpyAsync(p, h->plan_d, sizeof(p), cudaMemcpyDeviceToHost, s));
-  STAFB_CUDA_OK(cudaMemcpyAsync(&st, h->status_d, sizeof(int), cudaMemcpyDeviceToHost, s));
-  STAFB_CUDA_OK(cudaStreamSynchronize(s));
-  if (st) return st;
+  STAFB_CUDA_OK(cudaEventSynchronize(h->plan_ev));
+  const int* p = h->plan_h;
+  if (p[8]) return p[8];
+  h->lists ^= 1;
   fill_view(h, h->pv.n_own, p[2], p[3], p[0], p[1], p[4], p[5]);
   counts_out[0] = p[2]; counts_out[1] = p[3]; counts_out[2] = p[0]; counts_out[3] = p[1];
   return STAFB_OK;
@@ -547,11 +558,13 @@ extern "C" int stafb_halo_set_plan(stafb_halo* h, void* stream, int n_own, int n
       (long long)dst_off_hi + n_send_hi > h->cap_atoms)
     return STAFB_ERR_CAPACITY;
   cudaStream_t s = (cudaStream_t)stream;
+  int* lists = h->send_idx + (size_t)(h->lists ^ 1) * 2 * h->cap_face;
   if (n_send_lo)
-    STAFB_CUDA_OK(cudaMemcpyAsync(h->send_idx, send_lo_idx_d, sizeof(int) * n_send_lo, cudaMemcpyDeviceToDevice, s));
+    STAFB_CUDA_OK(cudaMemcpyAsync(lists, send_lo_idx_d, sizeof(int) * n_send_lo, cudaMemcpyDeviceToDevice, s));
   if (n_send_hi)
-    STAFB_CUDA_OK(cudaMemcpyAsync(h->send_idx + h->cap_face, send_hi_idx_d, sizeof(int) * n_send_hi,
+    STAFB_CUDA_OK(cudaMemcpyAsync(lists + h->cap_face, send_hi_idx_d, sizeof(int) * n_send_hi,
                                   cudaMemcpyDeviceToDevice, s));
+  h->lists ^= 1;
   fill_view(h, n_own, n_from_lo, n_from_hi, n_send_lo, n_send_hi, dst_off_lo, dst_off_hi);
   return STAFB_OK;
 }
@@ -607,5 +620,7 @@ extern "C" void stafb_halo_destroy(stafb_halo* h) {
   for (int r = 0; r < h->world && h->connected == 1; r++)
     if (r != h->rank && h->peer[r]) cudaIpcCloseMemHandle(h->peer[r]);
   cudaFree(h->block); cudaFree(h->send_idx); cudaFree(h->step_d); cudaFree(h->status_d); cudaFree(h->force); cudaFree(h->plan_d); cudaFree(h->ctr_d);
+  cudaFreeHost(h->plan_h);
+  if (h->plan_ev) cudaEventDestroy(h->plan_ev);
   free(h);
 }

@@ -70,6 +70,7 @@ __global__ void k_cells(const T* __restrict__ pos, const T* __restrict__ box, in
                         int* __restrict__ cell_count, int* __restrict__ status) {
   __shared__ FrameGeom<T> gs;
   const int b = blockIdx.y;
+  chain_wait();
   if (threadIdx.x == 0) {
     frame_geometry<T>(box + 6 * b, N, cutoff, cell_cap, gs, status);
     if (blockIdx.x == 0) fg[b] = gs;
@@ -105,6 +106,7 @@ __global__ void k_cells(const T* __restrict__ pos, const T* __restrict__ box, in
 template <class T>
 __global__ void k_gather_cells(const FrameGeom<T>* __restrict__ fg, int nf, int N, const int* __restrict__ cell_of,
                                const int* __restrict__ cell_start, int* __restrict__ cells_sorted, int cell_cap) {
+  chain_wait();
   int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   int b = gw / cell_cap, c = gw - b * cell_cap;
   if (b >= nf || c >= fg[b].ncell) return;
@@ -221,6 +223,7 @@ __global__ void k_scan(const FrameGeom<T>* __restrict__ fg, const int* __restric
                        int* __restrict__ status) {
   __shared__ int part[32];
   __shared__ int carry;
+  chain_wait();
   const int b = blockIdx.x, ncell = fg[b].ncell;
   const int* cnt = cell_count + (size_t)b * cell_cap;
   int* st = cell_start + (size_t)b * (cell_cap + 1);
@@ -259,6 +262,7 @@ __global__ void k_scan(const FrameGeom<T>* __restrict__ fg, const int* __restric
 
 __global__ void k_fill(int nf, int N, const int* __restrict__ cell_of, const int* __restrict__ cell_start,
                        int* __restrict__ cell_cursor, int* __restrict__ cells_raw, int cell_cap) {
+  chain_wait();
   int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= nf * N) return;
   int b = t / N, i = t - b * N;
@@ -272,6 +276,7 @@ __global__ void k_fill(int nf, int N, const int* __restrict__ cell_of, const int
 template <class T>
 __global__ void k_sort_cells(const FrameGeom<T>* __restrict__ fg, int nf, int N, const int* __restrict__ cell_start,
                              const int* __restrict__ cells_raw, int* __restrict__ cells_sorted, int cell_cap) {
+  chain_wait();
   int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   int b = gw / cell_cap, c = gw - b * cell_cap;
   if (b >= nf || c >= fg[b].ncell) return;
@@ -744,18 +749,23 @@ int launch_descriptors(stafb_ctx* c, cudaStream_t s, const T* pos, const T* box,
     c->launches += 1;
   } else {
     STAFB_CUDA_OK(cudaMemsetAsync(c->cell_count, 0, sizeof(int) * (size_t)nf * cap, s));
-    k_cells<T><<<dim3((N + 255) / 256, nf), 256, 0, s>>>(pos, box, nf, N, cc.Rc, cap, fg, frac, c->cell_of, c->cell_count,
-                                                         c->status_d);
-    k_scan<T><<<nf, 256, 0, s>>>(fg, c->cell_count, c->cell_start, c->cell_cursor, cap, mpc, c->status_d);
+    // each of these needs all of its predecessor's output: chained launches only save the launch gaps
+    STAFB_CUDA_OK(launch_chained(k_cells<T>, dim3((N + 255) / 256, nf), 256, 0, s, pos, box, nf, N, cc.Rc, cap, fg,
+                                 frac, c->cell_of, c->cell_count, c->status_d));
+    STAFB_CUDA_OK(launch_chained(k_scan<T>, nf, 1024, 0, s, (const FrameGeom<T>*)fg, (const int*)c->cell_count,
+                                 c->cell_start, c->cell_cursor, cap, mpc, c->status_d));
     const long long warps = (long long)nf * cap;
     if (N <= 4096) {
-      k_gather_cells<T><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(fg, nf, N, c->cell_of, c->cell_start,
-                                                                           c->cells_sorted, cap);
+      STAFB_CUDA_OK(launch_chained(k_gather_cells<T>, (unsigned)((warps * 32 + 255) / 256), 256, 0, s,
+                                   (const FrameGeom<T>*)fg, nf, N, (const int*)c->cell_of, (const int*)c->cell_start,
+                                   c->cells_sorted, cap));
       c->launches += 4;
     } else {
-      k_fill<<<(tot + 255) / 256, 256, 0, s>>>(nf, N, c->cell_of, c->cell_start, c->cell_cursor, c->cells_raw, cap);
-      k_sort_cells<T><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(fg, nf, N, c->cell_start, c->cells_raw,
-                                                                         c->cells_sorted, cap);
+      STAFB_CUDA_OK(launch_chained(k_fill, (tot + 255) / 256, 256, 0, s, nf, N, (const int*)c->cell_of,
+                                   (const int*)c->cell_start, c->cell_cursor, c->cells_raw, cap));
+      STAFB_CUDA_OK(launch_chained(k_sort_cells<T>, (unsigned)((warps * 32 + 255) / 256), 256, 0, s,
+                                   (const FrameGeom<T>*)fg, nf, N, (const int*)c->cell_start, (const int*)c->cells_raw,
+                                   c->cells_sorted, cap));
       c->launches += 5;
     }
   }

@@ -190,7 +190,10 @@ class PeerSlabDomain(SlabDomain):
         ptr = _lib.lib().stafb_halo_positions(self.h)
         self.pos_all = torch.as_tensor(_DevArray(ptr, 3 * self.cap_atoms, model.dtype),
                                        device=model.device).view(self.cap_atoms, 3)
-        self.type_all = torch.zeros(self.cap_atoms, dtype=torch.int32, device=model.device)
+        # species of owned + ghost atoms: two arrays, because a plan may be prepared while the one before is in use
+        self._types_all = [torch.zeros(self.cap_atoms, dtype=torch.int32, device=model.device) for _ in range(2)]
+        self._types_sel = 0
+        self._pending = False
         self.force = torch.zeros(self.cap_atoms, 3, dtype=model.dtype, device=model.device)
         self.e_own = torch.zeros(1, dtype=model.dtype, device=model.device)
         self.e_total = torch.zeros(1, dtype=model.dtype, device=model.device)
@@ -223,7 +226,8 @@ class PeerSlabDomain(SlabDomain):
             self._lib.check(L.stafb_halo_plan_select(self.h, st, self.pos.shape[0], _p(self.types), self.axis, self.L,
                                                      self.reach), "stafb_halo_plan_select")
         elif which == 1:
-            self._lib.check(L.stafb_halo_plan_layout(self.h, st, _p(self.type_all)), "stafb_halo_plan_layout")
+            self._lib.check(L.stafb_halo_plan_layout(self.h, st, _p(self._types_all[self._types_sel ^ 1])),
+                            "stafb_halo_plan_layout")
         else:
             self._lib.check(L.stafb_halo_plan_done(self.h, st), "stafb_halo_plan_done")
 
@@ -234,13 +238,12 @@ class PeerSlabDomain(SlabDomain):
                         "stafb_halo_plan_finish")
         n_lo, n_hi = int(out[0]), int(out[1])
         nall = self.pos.shape[0] + n_lo + n_hi
+        self._types_sel ^= 1
+        self._pending = False
         self._plan = dict(n_lo=n_lo, n_hi=n_hi, n_send_lo=int(out[2]), n_send_hi=int(out[3]), nall=nall,
-                          type_all=self.type_all[:nall])
+                          type_all=self._types_all[self._types_sel][:nall])
         self._graph = None
         self._fresh = True
-        # the stream has just been waited for: the model's status word (a saturated neighbour buffer during the
-        # evaluations of the previous plan) costs nothing to read here
-        self.model.ctx.raise_on_status("stafb_energy_force_domain")
 
     def _make_plan(self):
         for which in range(3):
@@ -276,7 +279,8 @@ class PeerSlabDomain(SlabDomain):
             t_hi = hi.types[faces[d.hi][0]]
             n_own = d.pos.shape[0]
             nall = n_own + t_lo.shape[0] + t_hi.shape[0]
-            d.type_all[:nall] = torch.cat([d.types, t_lo, t_hi])
+            d._types_sel ^= 1
+            d._types_all[d._types_sel][:nall] = torch.cat([d.types, t_lo, t_hi])
             s_lo = faces[d.rank][0].to(torch.int32).contiguous()
             s_hi = faces[d.rank][1].to(torch.int32).contiguous()
             dst_lo = lo.pos.shape[0] + n_lo[d.lo]  # lo's "ghosts from hi" rows
@@ -285,7 +289,7 @@ class PeerSlabDomain(SlabDomain):
                 d.h, d.model.ctx.stream(), n_own, t_lo.shape[0], t_hi.shape[0], _p(s_lo), s_lo.shape[0], int(dst_lo),
                 _p(s_hi), s_hi.shape[0], int(dst_hi)), "stafb_halo_set_plan")
             d._plan = dict(n_lo=t_lo.shape[0], n_hi=t_hi.shape[0], n_send_lo=s_lo.shape[0], n_send_hi=s_hi.shape[0],
-                           nall=nall, type_all=d.type_all[:nall])
+                           nall=nall, type_all=d._types_all[d._types_sel][:nall])
             d._graph, d._fresh = None, True
         torch.cuda.synchronize()
 
@@ -318,12 +322,28 @@ class PeerSlabDomain(SlabDomain):
     def step(self, rebuild=None):
         """Energy of the whole system (tensor [1], bit-identical on every rank) and forces on the owned atoms;
         both are views of buffers the next step overwrites.  Asynchronous except when the ghost sets are re-chosen."""
+        # The ghost sets of evaluations r, r+1, ... (r a multiple of halo_every) are chosen from the positions of
+        # evaluation r-1: the three plan launches go ahead of that evaluation's own launches, and the host picks the
+        # result up while the GPU is busy with it - no idle GPU at a re-plan.  (The skin covers the one evaluation
+        # of extra drift.)  The very first plan, and one the caller asks for, is made on the spot.
         if rebuild is None:
-            rebuild = self._plan is None or self._nstep % self.halo_every == 0
+            rebuild = self._plan is None
+            early = not rebuild and (self._nstep + 1) % self.halo_every == 0
+        else:
+            early = False
         self._nstep += 1
         if rebuild:
+            if self._pending:
+                self._plan_finish()  # a prepared plan must be consumed before the next is started
             self._make_plan()
-        if not self.use_graph or self._fresh:
+        if early:
+            for which in range(3):
+                self._plan_launch(which)
+            self._pending = True
+        if early:
+            self._sequence()  # under the plan still in force
+            self._plan_finish()
+        elif not self.use_graph or self._fresh:
             self._sequence()  # a plan's first evaluation always runs eagerly (allocations on first use)
             self._fresh = False
         else:
@@ -336,7 +356,8 @@ class PeerSlabDomain(SlabDomain):
         return self.e_total, self.force[:self.pos.shape[0]]
 
     def check(self):
-        """Reads the device status words of the model and of the exchange (waits for the device)."""
+        """Reads the device status words of the model (a saturated neighbour buffer ...) and of the exchange; waits
+        for the device.  step() itself never looks at them: call this at the points where a wait does not hurt."""
         self.model.ctx.raise_on_status("stafb_energy_force_domain")
         st = self._lib.lib().stafb_halo_status(self.h)
         if st:

@@ -376,10 +376,13 @@ int stafb_mlp_eval(stafb_ctx* ctx, stafb_model* m, void* stream, const void* af_
  *                           mails their number and species (types_d: int32 per owned atom) to the neighbours;
  *                           layout fills type_all_d[cap_atoms] (owned | from lo | from hi) and tells the
  *                           neighbours where their face atoms start; done waits for those answers; finish waits
- *                           for the stream - the only host synchronisation - and returns n_from_lo, n_from_hi,
- *                           n_send_lo, n_send_hi.  No barrier between the ranks is needed: a neighbour stores by
- *                           the new offsets only after this rank's layout launch, which follows this rank's last
- *                           evaluation under the old plan in stream order;
+ *                           for these three launches - the only host synchronisation -, puts the plan in force
+ *                           and returns n_from_lo, n_from_hi, n_send_lo, n_send_hi.  No barrier between the ranks
+ *                           is needed (a neighbour stores by the new offsets only after its own collect of the
+ *                           evaluation before).  The new plan may be prepared one evaluation early: select, layout
+ *                           (into a type_all array other than the one in use), done, then the push ... collect of
+ *                           one more evaluation under the old plan, then finish - the host then never waits for
+ *                           an idle GPU;
  *   one evaluation =  stafb_halo_push_positions; stafb_halo_wait_positions; stafb_energy_force_domain (energy_d =
  *                           the owned atoms' share, force_d for owned and ghost atoms); stafb_halo_return_forces
  *                           (ghost forces to their owners' ranks, this rank's energy to every rank);

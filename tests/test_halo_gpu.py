@@ -5,8 +5,8 @@ One GPU: 2, 3 and 4 ranks emulated in one process - every rank its own model and
 directly; all ranks' pushes are issued before any wait and all returns before any collect, so that no kernel ever
 waits for a kernel behind it on the same GPU.  The result must equal the evaluation of the whole box (the
 reference's test/test-lammps-dd-parity: 1 vs 2 vs 4 ranks), over several evaluations with moving atoms and a ghost
-set that is re-chosen in between - by the device-side planner (mailboxes in the peers' memory) and by a plan made
-on the host.
+set that is re-chosen in between - by the device-side planner (mailboxes in the peers' memory), by the same planner
+run one evaluation ahead, and by a plan made on the host.
 Two GPUs (skipped otherwise): two processes, CUDA IPC, the evaluation replayed as a CUDA graph.
 A wait that runs out (a flag nobody sets) must leave a status and a usable context.
 """
@@ -61,9 +61,10 @@ def _evaluate_emulated(doms):
         d.phase_collect()
 
 
-@pytest.mark.parametrize("world,explicit", [(2, False), (3, False), (4, False), (3, True)])
+@pytest.mark.parametrize("world,mode", [(2, "device"), (3, "device"), (4, "device"), (3, "host"), (3, "early"),
+                                        (2, "early")])
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-6), (torch.float64, 1e-12)])
-def test_emulated_ranks_equal_the_whole_box(world, explicit, dtype, tol):
+def test_emulated_ranks_equal_the_whole_box(world, mode, dtype, tol):
     from alphanesgpu_b200.slab import PeerSlabDomain
     dev = torch.device("cuda:0")
     shape, theta, emb, box6, gpos, gtypes, full = _system(dtype, dev)
@@ -79,10 +80,19 @@ def test_emulated_ranks_equal_the_whole_box(world, explicit, dtype, tol):
     gen = torch.Generator(device="cpu").manual_seed(5)
     boxt = torch.as_tensor(np.asarray(box6)[None].astype(np.float64)).to(dev, dtype)
     for k in range(5):
-        if k in (0, 3):
+        if k == 0 or (k == 3 and mode != "early"):
             # ghost sets re-chosen: on the device, or on the host and installed with stafb_halo_set_plan
-            (PeerSlabDomain.plan_local_explicit if explicit else PeerSlabDomain.plan_local)(doms)
+            (PeerSlabDomain.plan_local_explicit if mode == "host" else PeerSlabDomain.plan_local)(doms)
+        early = mode == "early" and k == 2
+        if early:
+            # the plan of evaluation 3 onwards prepared ahead of evaluation 2, which still runs under the old one
+            for which in range(3):
+                for d in doms:
+                    d._plan_launch(which)
         _evaluate_emulated(doms)
+        if early:
+            for d in doms:
+                d._plan_finish()
         torch.cuda.synchronize()
         for d in doms:
             d.check()
