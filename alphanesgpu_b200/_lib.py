@@ -66,7 +66,6 @@ _SIGS = {
     "stafb_peer_connect": [_vp, _vp],
     "stafb_peer_status": [_vp],
     "stafb_peer_connect_local": [_vp, _vp],
-    "stafb_peer_preset_flags": [_vp, _vp, _i, _i],
     "stafb_peer_grad": [_vp, _i],
     "stafb_peer_set_wait_ms": [_vp, C.c_longlong],
     "stafb_peer_destroy": [_vp],
@@ -89,6 +88,7 @@ _SIGS = {
     "stafb_halo_status": [_vp],
     "stafb_halo_destroy": [_vp],
     "stafb_allreduce_adam": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _d, _d, _d, _d, _vp],
+    "stafb_allreduce_adam_phase": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _d, _d, _d, _d, _vp, _i],
     "stafb_train_step_host": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _i, _vp, _vp],
     "stafb_train_step_host_begin": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _i, _vp, _i],
     "stafb_train_step_host_end": [_vp, _vp, _i, _vp],

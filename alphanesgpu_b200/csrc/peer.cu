@@ -1,22 +1,23 @@
 // Gradient exchange of data-parallel training over NVLink peer memory, fused with the optimiser update.
 //
 // What hvd.DistributedOptimizer does variable by variable in the reference (STAF/staf_train.py:484-487: average
-// the gradients over the ranks, then Adam) as ONE kernel per rank and step.  Every rank accumulates its gradient
-// in a buffer of its own device memory that the other ranks of the node have mapped (CUDA IPC).  The kernel
-//   1. publishes "my gradient of this step is complete" in a flag word on every peer (a system-scope store
-//      over NVLink after a system fence),
-//   2. waits until all peers have published theirs (polling flag words in its OWN memory; bounded in time -
-//      when the bound is hit the launch as a whole records STAFB_ERR_PEER_TIMEOUT, leaves theta, the moments and
-//      the step counter untouched and returns: the decision is taken once per launch, see the kernel),
-//   3. reads the peers' gradients with plain peer loads, all in flight together, sums them in rank order (so
-//      that every rank computes bit-identical sums and the replicas of theta never drift), divides by the world
-//      size and applies Adam.
+// the gradients over the ranks, then Adam) as ONE kernel per rank and step, with one NVLink trip on its critical
+// path.  Every rank owns a receive area that the other ranks of the node have mapped (CUDA IPC): one 8-byte word
+// per (source rank, element) holding the element's bits and the number of the step it belongs to.  The kernel
+//   1. stores its own gradient, element by element, into its slot of every peer's receive area (8-byte
+//      system-scope stores: value and step tag arrive together, so no flag, no fence and no second trip is needed),
+//   2. polls its own receive area until every peer's element carries this step's tag (bounded in time),
+//   3. agrees over the whole grid whether everything arrived - one decision per launch: either every block
+//      applies the update or none does; a launch that gives up records STAFB_ERR_PEER_TIMEOUT and leaves theta,
+//      the moments and the step counter untouched -,
+//   4. sums the gradients in rank order (every rank computes bit-identical sums, the replicas of theta never
+//      drift), divides by the world size and applies Adam.
 // A rank that gave up and a late rank that then went ahead hold different parameters from that step on: the
 // host has to notice the status and re-broadcast (alphanesgpu_b200/train.py does, at every collection point).
-// Two gradient buffers alternate from step to step: a rank that is already accumulating step k+1 does not
-// touch what a slower peer still reads for step k, and no rank can run two steps ahead of another because step
-// k+1 cannot complete without every peer's flag of step k+1.  There is no multicast object, no collective
-// library and no second launch between the backward pass and the parameter update.
+// Two receive areas alternate from step to step: a fast peer that already stores step k+1 does not touch what
+// this rank still reads for step k, and no rank can run two steps ahead of another because step k+1 cannot
+// complete without every peer's elements of step k+1.  There is no multicast object, no collective library and
+// no second launch between the backward pass and the parameter update.
 #include <math.h>
 #include <string.h>
 
@@ -25,106 +26,121 @@
 namespace stafb {
 
 constexpr int PEER_MAX = 16;
+constexpr int PEER_PUSH = 1, PEER_CONSUME = 2;  // phases of the kernel (both in one launch unless ranks share a GPU)
 
 struct PeerView {
   int rank, world;
-  const void* grad[PEER_MAX];  // gradient buffer of every rank for the parity of this launch (own: local pointer)
-  int* flag_out[PEER_MAX];     // on rank r: the word this rank writes (flags[parity][my rank] in r's block)
-  const int* flag_in;          // own block: flags[parity][0..world)
+  const void* grad;                       // this rank's gradient of this launch's parity
+  const unsigned long long* recv;         // own receive area of that parity: [PEER_MAX][words per rank]
+  unsigned long long* recv_of[PEER_MAX];  // the peers' receive areas of that parity
 };
 
-__device__ __forceinline__ int ld_sys(const int* p) {
-  int v;
-  asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_sys64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_sys(int* p, int v) {
-  asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_sys64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-__device__ __forceinline__ float ld_peer(const float* p) {
-  float v;
-  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ double ld_peer(const double* p) {
-  double v;
-  asm volatile("ld.relaxed.sys.global.f64 %0, [%1];" : "=d"(v) : "l"(p) : "memory");
-  return v;
-}
+// an element as tagged 8-byte words: one for fp32 (bits | tag << 32), two for fp64 (low half, high half)
+template <class T> struct PeerWords;
+template <> struct PeerWords<float> {
+  static constexpr int W = 1;
+  static __device__ __forceinline__ void push(unsigned long long* dst, float x, unsigned tag) {
+    st_sys64(dst, ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(x));
+  }
+  static __device__ __forceinline__ bool poll(const unsigned long long* src, unsigned tag, float& x) {
+    const unsigned long long w = ld_sys64(src);
+    x = __uint_as_float((unsigned)w);
+    return (unsigned)(w >> 32) == tag;
+  }
+};
+template <> struct PeerWords<double> {
+  static constexpr int W = 2;
+  static __device__ __forceinline__ void push(unsigned long long* dst, double x, unsigned tag) {
+    const unsigned long long b = (unsigned long long)__double_as_longlong(x);
+    st_sys64(dst, ((unsigned long long)tag << 32) | (b & 0xFFFFFFFFull));
+    st_sys64(dst + 1, ((unsigned long long)tag << 32) | (b >> 32));
+  }
+  static __device__ __forceinline__ bool poll(const unsigned long long* src, unsigned tag, double& x) {
+    const unsigned long long lo = ld_sys64(src), hi = ld_sys64(src + 1);
+    x = __longlong_as_double((long long)((hi << 32) | (lo & 0xFFFFFFFFull)));
+    return (unsigned)(lo >> 32) == tag && (unsigned)(hi >> 32) == tag;
+  }
+};
 
-// One decision per launch.  Every block's thread 0 polls the peers' flags (bounded), then proposes its finding
-// (all flags seen / gave up) for this step in a verdict word of this rank's own memory with a compare-and-swap;
-// the first proposal stands and every block - whenever it runs - adopts it.  So either all blocks apply the
-// update or none does, also when a peer's flag lands just as the bound runs out, and the step counter advances
-// only with an applied update.  verdict = 2*step + ok; steps only grow, so the word never needs clearing.
+// status: [0] first error, [1] unused, [2] blocks that saw everything, [3] blocks that gave up (both cleared by the
+// block that finishes last).  step_d: [0] updates applied so far, [1] blocks done.  The grid must be resident as
+// a whole (256-thread blocks, at most eight per SM: up to ~300,000 parameters), because its blocks wait for each
+// other's finding.
 template <class T>
 __global__ void __launch_bounds__(256)
     k_allreduce_adam(PeerView pv, int n, T* __restrict__ theta, T* __restrict__ m, T* __restrict__ v, double lr,
-                     double b1, double b2, T eps, int* __restrict__ step_d /*[2]: step, blocks done*/,
-                     long long wait_cycles, int* __restrict__ status /*[2]: status, verdict*/) {
+                     double b1, double b2, T eps, int* __restrict__ step_d, long long wait_cycles,
+                     int* __restrict__ status, int phase) {
   __shared__ int ok_s;
+  typedef PeerWords<T> PW;
   chain_wait();  // the gradient is the output of the kernel before this one
   const int step = *reinterpret_cast<volatile int*>(step_d) + 1;  // the update being applied; equal on all ranks
-  // everything that does not need the peers is done while thread 0 waits for them: this rank's own values and
-  // the step's learning-rate factor (two double-precision powers)
+  const unsigned tag = (unsigned)step;
   const int q = blockIdx.x * blockDim.x + threadIdx.x;
-  T g_own = T(0), m_old = T(0), v_old = T(0), th_old = T(0);
-  if (q < n && threadIdx.x != 0) {
-    g_own = reinterpret_cast<const T*>(pv.grad[pv.rank])[q];
-    m_old = m[q]; v_old = v[q]; th_old = theta[q];
+  const size_t per_rank = (size_t)n * PW::W;
+  T g_own = T(0);
+  if (q < n) g_own = reinterpret_cast<const T*>(pv.grad)[q];
+  if ((phase & PEER_PUSH) && q < n) {
+    // first of all: the peers are waiting for it
+#pragma unroll
+    for (int r = 0; r < PEER_MAX; r++)
+      if (r < pv.world && r != pv.rank) PW::push(pv.recv_of[r] + (size_t)pv.rank * per_rank + (size_t)q * PW::W, g_own, tag);
   }
+  if (!(phase & PEER_CONSUME)) return;
+  // everything that does not need the peers while their stores are on the way
+  T m_old = T(0), v_old = T(0), th_old = T(0);
+  if (q < n) { m_old = m[q]; v_old = v[q]; th_old = theta[q]; }
   const T lr_t = (T)(lr * sqrt(1.0 - pow(b2, (double)step)) / (1.0 - pow(b1, (double)step)));
-  if (threadIdx.x == 0) {
-    if (blockIdx.x == 0) {
-      __threadfence_system();  // this rank's gradient (complete at the kernel boundary) before the flags
-      for (int r = 0; r < pv.world; r++)
-        if (r != pv.rank) st_sys(pv.flag_out[r], step);
-    }
-    int seen = 1;
-    const long long t0 = clock64();
-    for (int r = 0; r < pv.world && seen; r++) {
-      if (r == pv.rank) continue;
-      while (ld_sys(pv.flag_in + r) < step) {  // flags only grow: a peer is never more than one step ahead
-        const long long waited = clock64() - t0;
-        if (waited > wait_cycles) { seen = 0; break; }
-        if (waited > 20000) __nanosleep(100);  // spin for the first ~10 us, then back off
+  T gv[PEER_MAX];
+  unsigned pending = 0u;
+  if (q < n)
+    for (int r = 0; r < pv.world; r++)
+      if (r != pv.rank) pending |= 1u << r;
+  const long long t0 = clock64();
+  while (pending) {
+    // all outstanding peers in one round: their loads are in flight together
+#pragma unroll
+    for (int r = 0; r < PEER_MAX; r++)
+      if ((pending >> r) & 1u) {
+        T x;
+        if (PW::poll(pv.recv + (size_t)r * per_rank + (size_t)q * PW::W, tag, x)) { gv[r] = x; pending &= ~(1u << r); }
       }
+    if (pending) {
+      const long long waited = clock64() - t0;
+      if (waited > wait_cycles) break;
+      if (waited > 20000) __nanosleep(100);  // spin for the first ~10 us, then back off
     }
-    int* verdict = status + 1;
-    const int want = 2 * step + seen;
-    int cur = *reinterpret_cast<volatile int*>(verdict);
-    while ((cur >> 1) < step) {
-      const int prev = atomicCAS(verdict, cur, want);
-      if (prev == cur) { cur = want; break; }
-      cur = prev;
+  }
+  // one decision per launch: every block reports what it found, then reads the tally once it is complete
+  const int blk_ok = __syncthreads_and(pending == 0u);
+  if (threadIdx.x == 0) {
+    atomicAdd(status + (blk_ok ? 2 : 3), 1);
+    int ok = 0;
+    const long long t1 = clock64();
+    while (true) {
+      const int a = *reinterpret_cast<volatile int*>(status + 2), f = *reinterpret_cast<volatile int*>(status + 3);
+      if (a + f >= (int)gridDim.x) { ok = f == 0; break; }
+      if (clock64() - t1 > wait_cycles + 4000000000ll) break;  // a block that never ran: the grid was too large
     }
-    const int ok = ((cur >> 1) == step) ? (cur & 1) : 0;
     if (!ok) atomicCAS(status, 0, STAFB_ERR_PEER_TIMEOUT);
-    __threadfence_system();
     ok_s = ok;
   }
   __syncthreads();
   const int ok = ok_s;
-  if (q < n && threadIdx.x == 0) {  // thread 0 was busy with the flags
-    g_own = reinterpret_cast<const T*>(pv.grad[pv.rank])[q];
-    m_old = m[q]; v_old = v[q]; th_old = theta[q];
-  }
   if (ok && q < n) {
-    // all peers' loads are issued before the first add (one NVLink round trip, not one per rank); the sum is
-    // taken in rank order, so every rank computes the same bits
-    T gv[PEER_MAX];
-#pragma unroll
-    for (int r = 0; r < PEER_MAX; r++) {
-      gv[r] = T(0);
-      if (r < pv.world) {
-        const T* gr = reinterpret_cast<const T*>(pv.grad[r]);
-        gv[r] = (r == pv.rank) ? g_own : ld_peer(gr + q);
-      }
-    }
+    // the sum is taken in rank order, so every rank computes the same bits
     T g = T(0);
 #pragma unroll
     for (int r = 0; r < PEER_MAX; r++)
-      if (r < pv.world) g += gv[r];
+      if (r < pv.world) g += (r == pv.rank) ? g_own : gv[r];
     g *= T(1) / T(pv.world);
     const T mm = (T)b1 * m_old + (T(1) - (T)b1) * g;
     const T vv = (T)b2 * v_old + (T(1) - (T)b2) * g * g;
@@ -136,12 +152,13 @@ __global__ void __launch_bounds__(256)
   if (threadIdx.x == 0) {
     __threadfence();
     if (atomicAdd(step_d + 1, 1) == (int)gridDim.x - 1) {
+      // every block has read the tally by now: cleared for the next launch.  A launch that gave up leaves
+      // theta, m, v AND the step count as they were, so that a repeated launch decides anew.
       step_d[1] = 0;
+      status[2] = 0;
+      status[3] = 0;
       __threadfence();
-      // a launch that gave up leaves theta, m, v AND the step count as they were; every block has read the
-      // verdict by now, so it is rewound to "nothing decided for this step" and a repeated launch decides anew
       if (ok) atomicAdd(step_d, 1);
-      else status[1] = 2 * step - 1;
     }
   }
 }
@@ -151,10 +168,10 @@ __global__ void __launch_bounds__(256)
 using namespace stafb;
 
 // One rank's side of the exchange.  Block layout (device memory of this rank, mapped by the peers):
-//   [ grad parity 0 : n elements | grad parity 1 : n elements | flags[2][PEER_MAX] int ]
+//   [ grad parity 0 : n elements | grad parity 1 : n elements | recv[2][PEER_MAX][n elements as tagged words] ]
 struct stafb_peer {
   int rank, world, n, dtype;
-  size_t es, grad_bytes;
+  size_t es, grad_bytes, recv_words;  // recv_words: 8-byte words of one source rank's slot
   char* block;             // own allocation
   char* peer[PEER_MAX];    // mapped blocks (own rank: block)
   int connected;
@@ -170,11 +187,12 @@ extern "C" int stafb_peer_create(stafb_ctx* c, int rank, int world, int n_params
   p->rank = rank; p->world = world; p->n = n_params; p->dtype = c->dtype;
   p->es = c->dtype == STAFB_F32 ? 4 : 8;
   p->grad_bytes = ((p->es * (size_t)n_params + 255) / 256) * 256;
-  const size_t bytes = 2 * p->grad_bytes + sizeof(int) * 2 * PEER_MAX;
+  p->recv_words = (size_t)n_params * (p->es / 4);
+  const size_t bytes = 2 * p->grad_bytes + 2 * (size_t)PEER_MAX * p->recv_words * sizeof(unsigned long long);
   STAFB_CUDA_OK(cudaMalloc((void**)&p->block, bytes));
   STAFB_CUDA_OK(cudaMemset(p->block, 0, bytes));
-  STAFB_CUDA_OK(cudaMalloc((void**)&p->status_d, 2 * sizeof(int)));  // status word, verdict word
-  STAFB_CUDA_OK(cudaMemset(p->status_d, 0, 2 * sizeof(int)));
+  STAFB_CUDA_OK(cudaMalloc((void**)&p->status_d, 4 * sizeof(int)));  // status word, spare, the launch's tally
+  STAFB_CUDA_OK(cudaMemset(p->status_d, 0, 4 * sizeof(int)));
   STAFB_CUDA_OK(cudaDeviceSynchronize());
   p->peer[rank] = p->block;
   int khz = 1500000;
@@ -222,19 +240,6 @@ extern "C" int stafb_peer_connect_local(stafb_peer* p, stafb_peer* const* all) {
   return STAFB_OK;
 }
 
-// Writes `value` into every flag word of this rank's block for `parity`, as if all peers had published step
-// `value` already.  For emulating several ranks on one GPU, where their kernels run one after the other and
-// must therefore never wait for each other.
-extern "C" int stafb_peer_preset_flags(stafb_peer* p, void* stream, int parity, int value) {
-  if (!p || parity < 0 || parity > 1) return STAFB_ERR_INVALID;
-  int host[PEER_MAX];
-  for (int r = 0; r < PEER_MAX; r++) host[r] = value;
-  int* flags = reinterpret_cast<int*>(p->block + 2 * p->grad_bytes) + parity * PEER_MAX;
-  STAFB_CUDA_OK(cudaMemcpyAsync(flags, host, sizeof(host), cudaMemcpyHostToDevice, (cudaStream_t)stream));
-  STAFB_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
-  return STAFB_OK;
-}
-
 extern "C" int stafb_peer_set_wait_ms(stafb_peer* p, long long ms) {
   if (!p || ms < 0) return STAFB_ERR_INVALID;
   int dev = 0, khz = 1500000;
@@ -265,28 +270,41 @@ extern "C" void stafb_peer_destroy(stafb_peer* p) {
   free(p);
 }
 
-extern "C" int stafb_allreduce_adam(stafb_ctx* c, stafb_peer* p, void* stream, int parity, void* theta, void* mm,
-                                    void* vv, double lr, double b1, double b2, double eps, int* step_d) {
-  if (!c || !p || !theta || !mm || !vv || !step_d || parity < 0 || parity > 1 || !p->connected)
+// phase: PEER_PUSH | PEER_CONSUME in one launch (ranks on GPUs of their own), or the two as separate launches for
+// ranks that share ONE GPU (tests): all ranks' pushes first, then their consumes - kernels on one GPU must never
+// wait for one another.
+extern "C" int stafb_allreduce_adam_phase(stafb_ctx* c, stafb_peer* p, void* stream, int parity, void* theta, void* mm,
+                                          void* vv, double lr, double b1, double b2, double eps, int* step_d,
+                                          int phase) {
+  if (!c || !p || !theta || !mm || !vv || !step_d || parity < 0 || parity > 1 || !p->connected || phase < 1 ||
+      phase > 3)
     return STAFB_ERR_INVALID;
   if (c->dtype != p->dtype) return STAFB_ERR_INVALID;
+  const int n = p->n, grid = (n + 255) / 256;
+  int nsm = 148;
+  cudaDeviceGetAttribute(&nsm, cudaDevAttrMultiProcessorCount, c->device);
+  if (grid > 8 * nsm) return STAFB_ERR_CAPACITY;  // the blocks wait for each other: the grid must be resident
   PeerView pv;
   memset(&pv, 0, sizeof(pv));
   pv.rank = p->rank;
   pv.world = p->world;
-  for (int r = 0; r < p->world; r++) {
-    pv.grad[r] = p->peer[r] + (size_t)parity * p->grad_bytes;
-    int* flags_r = reinterpret_cast<int*>(p->peer[r] + 2 * p->grad_bytes);
-    pv.flag_out[r] = flags_r + parity * PEER_MAX + p->rank;
-  }
-  pv.flag_in = reinterpret_cast<const int*>(p->block + 2 * p->grad_bytes) + parity * PEER_MAX;
+  pv.grad = p->block + (size_t)parity * p->grad_bytes;
+  const size_t area = (size_t)PEER_MAX * p->recv_words;  // words of one parity's receive area
+  for (int r = 0; r < p->world; r++)
+    pv.recv_of[r] = reinterpret_cast<unsigned long long*>(p->peer[r] + 2 * p->grad_bytes) + (size_t)parity * area;
+  pv.recv = pv.recv_of[p->rank];
   cudaStream_t s = (cudaStream_t)stream;
-  const int n = p->n, grid = (n + 255) / 256;
   if (c->dtype == STAFB_F32)
     STAFB_CUDA_OK(launch_chained(k_allreduce_adam<float>, grid, 256, 0, s, pv, n, (float*)theta, (float*)mm,
-                                 (float*)vv, lr, b1, b2, (float)eps, step_d, p->wait_cycles, p->status_d));
+                                 (float*)vv, lr, b1, b2, (float)eps, step_d, p->wait_cycles, p->status_d, phase));
   else
     STAFB_CUDA_OK(launch_chained(k_allreduce_adam<double>, grid, 256, 0, s, pv, n, (double*)theta, (double*)mm,
-                                 (double*)vv, lr, b1, b2, eps, step_d, p->wait_cycles, p->status_d));
+                                 (double*)vv, lr, b1, b2, eps, step_d, p->wait_cycles, p->status_d, phase));
   return STAFB_OK;
+}
+
+extern "C" int stafb_allreduce_adam(stafb_ctx* c, stafb_peer* p, void* stream, int parity, void* theta, void* mm,
+                                    void* vv, double lr, double b1, double b2, double eps, int* step_d) {
+  return stafb_allreduce_adam_phase(c, p, stream, parity, theta, mm, vv, lr, b1, b2, eps, step_d,
+                                    PEER_PUSH | PEER_CONSUME);
 }

@@ -136,7 +136,7 @@ class PeerExchange:
         return _lib.lib().stafb_peer_status(self.h)
 
     def set_wait_ms(self, ms):
-        """Bound of the kernel's wait for the peers' flags, in milliseconds of SM clock."""
+        """Bound of the kernel's wait for the peers' gradients, in milliseconds of SM clock."""
         from . import _lib
         _lib.check(_lib.lib().stafb_peer_set_wait_ms(self.h, int(ms)), "stafb_peer_set_wait_ms")
 

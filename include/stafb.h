@@ -309,31 +309,40 @@ int stafb_adam_step_dev(stafb_ctx* ctx, void* stream, void* theta_d, const void*
 /* Data-parallel training on the GPUs of one node without a collective library between the backward pass and the
  * optimiser: what hvd.DistributedOptimizer + Adam do in the reference (STAF/staf_train.py:484-487: average the
  * gradients over the ranks, then update) as ONE kernel per rank and step over NVLink peer memory.
- *   stafb_peer_create   allocates this rank's block: two gradient buffers (parity 0 / 1) and flag words;
+ *   stafb_peer_create   allocates this rank's block: two gradient buffers (parity 0 / 1) and two receive areas
+ *                       (one 8-byte word per source rank and element: the element's bits and its step number);
  *   stafb_peer_handle   writes the 64-byte CUDA IPC handle of that block (exchange them between the ranks by any
  *                       host-side means: torch.distributed.all_gather_object, MPI ...);
  *   stafb_peer_connect  maps the other ranks' blocks (handles[world][64], own entry ignored);
  *   stafb_peer_grad     device pointer of a gradient buffer: pass it as grad_d to stafb_train_step*;
- *   stafb_allreduce_adam  publishes "gradient complete" on every peer, waits for the peers (bounded: about two
- *                       seconds; then the launch as a whole records STAFB_ERR_PEER_TIMEOUT and leaves theta, the
- *                       moments and the step counter untouched - one decision per launch, never a partial
- *                       update), sums the buffers of `parity` in rank order - bit-identical on every rank -,
- *                       divides by the world size and applies Adam (same formula and device step counter as
- *                       stafb_adam_step_dev).  After a timeout the ranks may hold different parameters (a late
- *                       rank still finds the flags of the ranks that gave up): read stafb_peer_status on the
- *                       host at regular points and re-broadcast theta, the moments and the step count.
- * Consecutive steps must alternate the parity; every rank must make the same calls in the same order.  Before
- * stafb_peer_destroy all ranks must have finished their last step (a host-side barrier). */
+ *   stafb_allreduce_adam  stores this rank's gradient, tagged with the step, into every peer's receive area (one
+ *                       NVLink trip: value and tag travel in one word, no flag and no fence), waits until all
+ *                       peers' elements of this step have arrived (bounded: about two seconds; then the launch as
+ *                       a whole records STAFB_ERR_PEER_TIMEOUT and leaves theta, the moments and the step counter
+ *                       untouched - one decision per launch, never a partial update), sums the gradients of
+ *                       `parity` in rank order - bit-identical on every rank -, divides by the world size and
+ *                       applies Adam (same formula and device step counter as stafb_adam_step_dev).  After a
+ *                       timeout the ranks may hold different parameters (a late rank still finds the data of the
+ *                       ranks that gave up): read stafb_peer_status on the host at regular points, re-broadcast
+ *                       theta, the moments and the step count, and do not use this exchange again before
+ *                       step numbers beyond those already published are reached (train.py continues with an
+ *                       all-reduce).
+ * Consecutive steps must alternate the parity; every rank must make the same calls in the same order.  The
+ * blocks of the kernel wait for each other, so its grid must be resident as a whole: at most 8 x 256 parameters
+ * per SM (STAFB_ERR_CAPACITY beyond).  Before stafb_peer_destroy all ranks must have finished their last step (a
+ * host-side barrier). */
 typedef struct stafb_peer stafb_peer;
 int stafb_peer_create(stafb_ctx* ctx, int rank, int world, int n_params, stafb_peer** out);
 int stafb_peer_handle(stafb_peer* p, void* handle64_out);
 int stafb_peer_connect(stafb_peer* p, const void* handles);
 /* ranks inside one process connect through their handles (all[world], own entry ignored), without IPC */
 int stafb_peer_connect_local(stafb_peer* p, stafb_peer* const* all);
-/* marks every peer as having published step `value` for `parity`: for emulating several ranks on ONE GPU, where
- * the ranks' kernels run one after the other and must never wait for each other */
-int stafb_peer_preset_flags(stafb_peer* p, void* stream, int parity, int value);
-/* bound of the wait for the peers' flags, in milliseconds of SM clock (default: about two seconds, or the
+/* the two halves of stafb_allreduce_adam as separate launches (phase 1: store to the peers, 2: wait and update,
+ * 3: both), for emulating several ranks on ONE GPU, where the ranks' kernels run one after the other and must
+ * never wait for each other: every rank's phase 1 first, then every rank's phase 2 */
+int stafb_allreduce_adam_phase(stafb_ctx* ctx, stafb_peer* p, void* stream, int parity, void* theta_d, void* m_d,
+                               void* v_d, double lr, double beta1, double beta2, double eps, int* step_d, int phase);
+/* bound of the wait for the peers' elements, in milliseconds of SM clock (default: about two seconds, or the
  * environment variable STAFB_PEER_WAIT_MS read by stafb_peer_create; 0 = give up at the first look) */
 int stafb_peer_set_wait_ms(stafb_peer* p, long long ms);
 void* stafb_peer_grad(stafb_peer* p, int parity);

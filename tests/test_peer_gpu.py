@@ -133,7 +133,7 @@ def _late_peer_worker(rank, world, port, q):
     torch.cuda.synchronize()
     dist.barrier()
     if rank == 1:
-        time.sleep(0.5)  # rank 0 launches first and finds no flag
+        time.sleep(0.5)  # rank 0 launches first and finds nothing from its peer
     px.allreduce_adam(a, 0, 1e-3)
     torch.cuda.synchronize()
     status = px.status()
@@ -169,8 +169,9 @@ def test_late_peer_gives_a_status_not_a_hang():
 
 def test_eight_emulated_ranks_on_one_gpu():
     """The kernel's indexing for a full node: eight ranks emulated on one GPU.  Their kernels run one after the
-    other, so every flag is preset (no kernel may wait for another on the same GPU); what is checked is that
-    each rank reads the right eight buffers, sums them in rank order and that all replicas end up bit-identical."""
+    other, so all of them store to their peers first and wait afterwards (no kernel may wait for another on the same
+    GPU); what is checked is that each rank finds the right eight gradients, sums them in rank order and that all
+    replicas end up bit-identical."""
     import ctypes as C
     from alphanesgpu_b200 import _lib
     from alphanesgpu_b200.dist import _DevArray
@@ -194,15 +195,15 @@ def test_eight_emulated_ranks_on_one_gpu():
         for par in (0, 1):
             g = torch.as_tensor(_DevArray(L.stafb_peer_grad(hs[r], par), n, torch.float32), device=dev)
             g.copy_(grads[r] if par == 0 else -grads[r])
-        _lib.check(L.stafb_peer_preset_flags(hs[r], stream, 0, 1), "stafb_peer_preset_flags")
         state.append(dict(theta=theta0.clone(), m=torch.zeros(n, device=dev), v=torch.zeros(n, device=dev),
                           step=torch.zeros(2, dtype=torch.int32, device=dev)))
     torch.cuda.synchronize()
     p = lambda t: C.c_void_p(t.data_ptr())
-    for r in range(W):
-        s = state[r]
-        _lib.check(L.stafb_allreduce_adam(ctx.h, hs[r], stream, 0, p(s["theta"]), p(s["m"]), p(s["v"]), lr, 0.9, 0.999,
-                                          1e-7, p(s["step"])), "stafb_allreduce_adam")
+    for phase in (1, 2):  # every rank stores to its peers, then every rank waits and updates
+        for r in range(W):
+            s = state[r]
+            _lib.check(L.stafb_allreduce_adam_phase(ctx.h, hs[r], stream, 0, p(s["theta"]), p(s["m"]), p(s["v"]), lr,
+                                                    0.9, 0.999, 1e-7, p(s["step"]), phase), "stafb_allreduce_adam_phase")
     torch.cuda.synchronize()
     g = torch.zeros(n, device=dev)
     for r in range(W):
@@ -222,9 +223,10 @@ def test_eight_emulated_ranks_on_one_gpu():
 
 
 def test_a_launch_that_gives_up_changes_nothing():
-    """Flags that nothing sets and a zero bound: every block of the launch gives up together (the decision is
+    """Peers that store nothing and a zero bound: every block of the launch gives up together (the decision is
     taken once per launch), so theta, both moments and the step counter are bit-identical to before, the status
-    says STAFB_ERR_PEER_TIMEOUT and the next launch - with the flags in place - applies its update in full."""
+    says STAFB_ERR_PEER_TIMEOUT and the next launch - with the peers' gradients in place - applies its update in
+    full."""
     import ctypes as C
     from alphanesgpu_b200 import _lib
     from alphanesgpu_b200.dist import _DevArray
@@ -258,8 +260,11 @@ def test_a_launch_that_gives_up_changes_nothing():
     assert L.stafb_peer_status(hs[0]) == 9
     assert torch.equal(theta, theta0) and torch.equal(m, m0) and torch.equal(v, v0)
     assert step.tolist() == [0, 0]
-    _lib.check(L.stafb_peer_preset_flags(hs[0], stream, 0, 1), "stafb_peer_preset_flags")
-    call()  # the same step again, now with every flag in place
+    zeros = [torch.zeros(2, dtype=torch.int32, device=dev) for _ in range(W)]
+    for r in range(1, W):  # now the peers store their gradients of step 1 (phase 1 touches nothing else)
+        _lib.check(L.stafb_allreduce_adam_phase(ctx.h, hs[r], stream, 0, p(theta0), p(m0), p(v0), lr, 0.9, 0.999, 1e-7,
+                                                p(zeros[r]), 1), "stafb_allreduce_adam_phase")
+    call()  # the same step again, now with every peer's gradient in place
     torch.cuda.synchronize()
     assert step.tolist() == [1, 0]
     g = torch.zeros(n, device=dev)

@@ -89,8 +89,8 @@ def test_loss_curve_one_rank_vs_two_emulated_ranks(tmp_path, precision):
     """One rank with batch 4 against two ranks with batch 2 each (the two halves of every global batch),
     gradients averaged by the exchange kernel, learning rate not scaled: the mean of the two ranks' losses
     follows the single-rank curve for 125 steps and the two replicas stay bit-identical.  The ranks are two
-    models on ONE GPU connected inside the process; their kernels run one after the other, so the flags are
-    preset before every exchange (kernels on one GPU must never wait for each other)."""
+    models on ONE GPU connected inside the process; their kernels run one after the other, so both ranks
+    store to each other before either waits (kernels on one GPU must never wait for each other)."""
     import ctypes as C
     from alphanesgpu_b200 import _lib, train as T
     from alphanesgpu_b200.dist import _DevArray
@@ -137,12 +137,12 @@ def test_loss_curve_one_rank_vs_two_emulated_ranks(tmp_path, precision):
                     ms[r].loss_and_grad(dv(data["pos"][sl]), dv(data["box"][sl]), dv(data["energy"][sl]),
                                         dv(data["force"][sl]))
                     losses.append(ms[r].losses.cpu().numpy().copy())
-                for r in range(W):
-                    _lib.check(L.stafb_peer_preset_flags(hs[r], stream, par, step + 1), "stafb_peer_preset_flags")
-                for r in range(W):
-                    _lib.check(L.stafb_allreduce_adam(ms[r].ctx.h, hs[r], stream, par, _p(ms[r].theta),
-                                                      _p(ms[r].adam_m), _p(ms[r].adam_v), lr_of(step), 0.9, 0.999,
-                                                      1e-7, _p(ms[r].step_d)), "stafb_allreduce_adam")
+                for phase in (1, 2):  # both ranks store to each other, then both wait and update
+                    for r in range(W):
+                        _lib.check(L.stafb_allreduce_adam_phase(ms[r].ctx.h, hs[r], stream, par, _p(ms[r].theta),
+                                                                _p(ms[r].adam_m), _p(ms[r].adam_v), lr_of(step), 0.9,
+                                                                0.999, 1e-7, _p(ms[r].step_d), phase),
+                                   "stafb_allreduce_adam_phase")
                 l = np.mean(losses, axis=0)  # (loss, loss_e, loss_bound, loss_f)
                 curve.append([l[1], l[3], l[2]])
                 step += 1
