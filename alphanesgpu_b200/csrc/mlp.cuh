@@ -548,20 +548,19 @@ __global__ void __launch_bounds__(ML_THREADS)
       for (int c = 0; c < 4; c++)
         if (i0 + r < in && j0 + c < out) atomicAdd(gw + woff + (i0 + r) * out + j0 + c, g[4 * r + c]);
   }
-  // bias gradients
-  for (int l = 0; l < Lq; l++) {
-    const int in = md.in_of(t, l), out = md.width[l];
-    const int oq = oDQ + md.h_off(l) * AW;
-    const int woff = md.w_off(t, l);
-    for (int j = threadIdx.x; j < out; j += ML_THREADS) {
-      T g = T(0);
-      for (int wv = 0; wv < ML_WARPS; wv++) {
-        const T* q = base + (size_t)wv * slice + oq + j * AW;
+  // bias gradients: the outputs of all layers in one pass (the DQ rows of the layers lie back to back)
+  for (int jj = threadIdx.x; jj < Hs; jj += ML_THREADS) {
+    int l = 0;
+    while (l < Lq - 1 && jj >= md.h_off(l + 1)) l++;
+    const int in = md.in_of(t, l), out = md.width[l], j = jj - md.h_off(l);
+    T g = T(0);
 #pragma unroll
-        for (int a = 0; a < AW; a++) g += q[a];
-      }
-      atomicAdd(gw + woff + in * out + j, g);
+    for (int wv = 0; wv < ML_WARPS; wv++) {
+      const T* q = base + (size_t)wv * slice + oDQ + jj * AW;
+#pragma unroll
+      for (int a = 0; a < AW; a++) g += q[a];
     }
+    atomicAdd(gw + md.w_off(t, l) + in * out + j, g);
   }
   for (int i = threadIdx.x; i < F; i += ML_THREADS) {
     T g = T(0);
