@@ -47,6 +47,7 @@ WATER_CONFIGS = {
     # name: (nx, ny, nz, L)
     "water96": (4, 4, 2, 9.86),
     "water768": (8, 8, 4, 19.6),
+    "water6144": (16, 16, 8, 39.2),
     "water24576": (16, 16, 32, 62.7),
 }
 

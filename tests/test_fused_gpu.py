@@ -163,11 +163,12 @@ def test_train_step_batch_of_eight(oracle, frame0):
     m.close()
 
 
-def test_energy_force_of_the_24576_atom_box(oracle, frame0):
+@pytest.mark.parametrize("name", ["water24576", "water6144"])
+def test_energy_force_of_the_large_boxes(oracle, frame0, name):
     """The large inference box (8192 O + 16384 H, L = 62.7 A; 13 x 13 x 13 cells, the multi-kernel cell-list
-    path): energy and every force component against the oracle."""
+    path) and a 6144-atom box (the size of a slab domain): energy and every force component against the oracle."""
     from alphanesgpu_b200.model import StafModel
-    pos, box, shape, theta, emb = _case("water24576", [1400], frame0)
+    pos, box, shape, theta, emb = _case(name, [1400], frame0)
     ref = oracle.energy_force_grad(CFG, shape.desc(), pos, box, shape.type_map, theta, emb, np.float32,
                                    per_atom_energy=False)
     assert ref["status"] == 0
