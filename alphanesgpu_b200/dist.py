@@ -74,6 +74,44 @@ class HostWatchdog:
             time.sleep(0.01)
 
 
+def connect_collectively(create, get_handle, connect, destroy, world, device, group, what):
+    """Creates this rank's peer-memory block (create() -> handle), exchanges the CUDA IPC handles and maps the
+    peers' blocks.  A failure on any rank (no peer access between two GPUs, out of memory) reaches every rank:
+    all of them go through the same collectives, release what they made and raise RuntimeError together, so the
+    caller can fall back to a message-based path on all ranks alike."""
+    import ctypes as C
+    from . import _lib
+    h, err, mine = None, None, b""
+    try:
+        h = create()
+        buf = C.create_string_buffer(64)
+        _lib.check(get_handle(h, buf), what + "_handle")
+        mine = bytes(buf.raw)
+    except Exception as exc:  # noqa: BLE001 - whatever it is, the other ranks must learn of it
+        err = exc
+    handles = [None] * world
+    dist.all_gather_object(handles, mine, group=group)
+    if err is None and all(len(x) == 64 for x in handles):
+        try:
+            _lib.check(connect(h, b"".join(handles)), what + "_connect")
+        except Exception as exc:  # noqa: BLE001
+            err = exc
+    elif err is None:
+        err = RuntimeError("a peer rank could not create its block")
+    ok = torch.tensor([0.0 if err is not None else 1.0], device=device)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+    if float(ok) == 0.0:
+        if h is not None:
+            torch.cuda.synchronize()
+            dist.barrier(group=group)  # nobody unmaps while another rank may still be mapping
+            destroy(h)
+        else:
+            dist.barrier(group=group)
+        raise RuntimeError("%s: peer memory is not available on every rank (%s)" % (what, err))
+    dist.barrier(group=group)
+    return h
+
+
 class _DevArray:
     """Minimal __cuda_array_interface__ carrier, so that torch can wrap memory the library allocated."""
 
@@ -101,16 +139,19 @@ class PeerExchange:
         self.world = world_size(group)
         self.n = model.theta.numel()
         h = C.c_void_p()
-        _lib.check(_lib.lib().stafb_peer_create(model.ctx.h, self.rank, self.world, self.n, C.byref(h)),
-                   "stafb_peer_create")
-        self.h = h
-        if self.world > 1:
-            mine = C.create_string_buffer(64)
-            _lib.check(_lib.lib().stafb_peer_handle(self.h, mine), "stafb_peer_handle")
-            handles = [None] * self.world
-            dist.all_gather_object(handles, bytes(mine.raw), group=group)
-            _lib.check(_lib.lib().stafb_peer_connect(self.h, b"".join(handles)), "stafb_peer_connect")
-            dist.barrier(group=group)
+        self.h = None
+        if self.world == 1:
+            _lib.check(_lib.lib().stafb_peer_create(model.ctx.h, self.rank, self.world, self.n, C.byref(h)),
+                       "stafb_peer_create")
+            self.h = h
+        else:
+            # every rank goes through the same collectives whatever fails locally (no peer access between two
+            # GPUs, no memory ...), and all ranks raise together
+            self.h = connect_collectively(
+                lambda: _lib.check(_lib.lib().stafb_peer_create(model.ctx.h, self.rank, self.world, self.n,
+                                                                C.byref(h)), "stafb_peer_create") or h,
+                _lib.lib().stafb_peer_handle, _lib.lib().stafb_peer_connect, _lib.lib().stafb_peer_destroy,
+                self.world, model.device, group, "stafb_peer")
         self._grads = []
         for par in (0, 1):
             ptr = _lib.lib().stafb_peer_grad(self.h, par)

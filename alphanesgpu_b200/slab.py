@@ -175,17 +175,17 @@ class PeerSlabDomain(SlabDomain):
         self.box = torch.as_tensor(np.asarray(box6, np.float64)).to(device=model.device, dtype=model.dtype)
         self._lib = _lib
         h = C.c_void_p()
-        _lib.check(_lib.lib().stafb_halo_create(model.ctx.h, self.rank, self.world, self.cap_atoms, self.cap_face,
-                                                C.byref(h)), "stafb_halo_create")
-        self.h = h
         self._local = bool(local)
-        if not local:
-            mine = C.create_string_buffer(64)
-            _lib.check(_lib.lib().stafb_halo_handle(self.h, mine), "stafb_halo_handle")
-            handles = [None] * self.world
-            dist.all_gather_object(handles, bytes(mine.raw), group=group)
-            _lib.check(_lib.lib().stafb_halo_connect(self.h, b"".join(handles)), "stafb_halo_connect")
-            dist.barrier(group=group)
+        L = _lib.lib()
+        make = lambda: _lib.check(L.stafb_halo_create(model.ctx.h, self.rank, self.world, self.cap_atoms,
+                                                      self.cap_face, C.byref(h)), "stafb_halo_create") or h
+        if local:
+            self.h = make()
+        else:
+            from .dist import connect_collectively
+            # raises RuntimeError on every rank alike when peer memory is not available somewhere
+            self.h = connect_collectively(make, L.stafb_halo_handle, L.stafb_halo_connect, L.stafb_halo_destroy,
+                                          self.world, model.device, group, "stafb_halo")
         from .dist import _DevArray
         ptr = _lib.lib().stafb_halo_positions(self.h)
         self.pos_all = torch.as_tensor(_DevArray(ptr, 3 * self.cap_atoms, model.dtype),

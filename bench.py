@@ -464,7 +464,14 @@ def md_record(torch, dist, args, rank, world, local, dev, K):
         cap, cap_face = (int(v) for v in caps.tolist())
         shape = ModelShape(nt=gshape.nt, tipos=[1] * gshape.nt, Fr=gshape.Fr, Fa=gshape.Fa, widths=gshape.widths)
         model = StafModel(shape, CFG, theta, emb, 1, dtype=torch.float32, device=dev, n_max=cap)
-        dom = PeerSlabDomain(model, box[0], CFG["Rc"], rank, world, cap_atoms=cap, cap_face=cap_face, skin=SKIN,
+        transport = "peer"
+        try:
+            dom = PeerSlabDomain(model, box[0], CFG["Rc"], rank, world, cap_atoms=cap, cap_face=cap_face, skin=SKIN,
+                                 halo_every=HALO_EVERY)
+        except RuntimeError as exc:  # raised on every rank alike (e.g. no peer access between these GPUs)
+            sys.stderr.write("rank %d: halo exchange over peer memory unavailable (%s); using messages\n" % (rank, exc))
+            transport = "messages"
+            dom = SlabDomain(model_compute(model, box[0]), box[0], CFG["Rc"], rank, world, nt=gshape.nt, skin=SKIN,
                              halo_every=HALO_EVERY)
         own_idx = dom.set_owned_from_global(gpos, gtypes)
         n_own = dom.pos.shape[0]
@@ -502,8 +509,9 @@ def md_record(torch, dist, args, rank, world, local, dev, K):
     barrier()
     clocks = sampler.stop()
     total_ms = float(sum(a.elapsed_time(b) for a, b in zip(ev0, ev1)))
-    launches = model.launches() + (4 if world > 1 else 0)  # push, wait, return, collect of the halo exchange
-    if world > 1:
+    peer = world > 1 and transport == "peer"
+    launches = model.launches() + (4 if peer else 0)  # push, wait, return, collect of the halo exchange
+    if peer:
         dom.check()
     else:
         model.ctx.raise_on_status("md timed region")
@@ -594,12 +602,14 @@ def md_record(torch, dist, args, rank, world, local, dev, K):
             "e2e": {"value": N * Ke / (e2e_ms * 1e-3), "unit": "atom-steps/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": Ke,
                     "path": "staf_compute (libstaf C API, host double arrays)" if world == 1 else
-                            "slab driver: pinned host -> device, halo exchange over peer memory, forces -> pinned host"},
+                            "slab driver: pinned host -> device, halo exchange (%s), forces -> pinned host" % transport},
             "gpu_launches": launches * K, "launches_per_step": launches, "clocks": clocks, "phase_ms": acc,
             "energy": float(e), "dd_parity": dd_err, "cpu_baseline": cpu,
         }
     messages_ms = None
-    if world > 1:
+    if world > 1 and not peer and rec is not None:
+        rec["transport"] = {"halo": "torch.distributed messages (peer memory was not available)"}
+    if peer:
         # the same decomposition with torch.distributed messages (NCCL send/recv per face, all-reduce of the
         # energy) instead of the peer stores, for comparison
         dom.check()
