@@ -58,6 +58,8 @@ _SIGS = {
     "stafb_energy_force_domain": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "stafb_model_set_counts": [_vp, _vp],
     "stafb_train_step": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _i, _vp, _vp, _vp, _vp],
+    "stafb_train_step_virial": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _d, _i, _vp, _vp,
+                                _vp, _vp, _vp],
     "stafb_descriptors_prefetch": [_vp, _vp, _vp, _vp, _vp, _i, _i],
     "stafb_train_step_prefetched": [_vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _i, _vp, _vp, _vp,
                                     _vp],

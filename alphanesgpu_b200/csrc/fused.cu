@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(256)
            const T* __restrict__ theta, T pe, T pf, T pb, T bound, int loss_kind, T* __restrict__ ebar,
            T* __restrict__ grad, double* __restrict__ losses, int* status, int* status_main,
            const double* __restrict__ vacc, T* __restrict__ virial_out, double* __restrict__ mirror,
-           double* __restrict__ epart, unsigned* __restrict__ ecount) {
+           double* __restrict__ epart, unsigned* __restrict__ ecount, const T* __restrict__ v_label, T pv) {
   __shared__ double red[9];
   __shared__ int last_s;
   const int N = md.N;
@@ -210,6 +210,12 @@ __global__ void __launch_bounds__(256)
     }
     if (!needs_pred && eb == 1) chain_wait();
     if (virial_out && threadIdx.x < 9) virial_out[blk * 9 + threadIdx.x] = (T)vacc[blk * 9 + threadIdx.x];
+    if (v_label && threadIdx.x < 9) {
+      // virial term of the loss (staf_model.py:358-365): mean over [nf, 9]; its cotangent is formed by the
+      // backward sweep of the forces itself.  losses[5] (losses[4] is the done-counter).
+      const T e = (T)vacc[blk * 9 + threadIdx.x] - v_label[blk * 9 + threadIdx.x];
+      atomicAdd(losses + 5, (double)(loss_kind == 0 ? huber(e) : e * e) / (9.0 * nf));
+    }
     if (threadIdx.x == 0) {
       if (!isfinite(Eb)) set_status(status, STAFB_ERR_NONFINITE);
       if (energy) energy[blk] = (T)Eb;
@@ -255,7 +261,8 @@ __global__ void __launch_bounds__(256)
     if (done == gridDim.x - 1) {
       __threadfence();
       const double le = atomicAdd(losses + 1, 0.0), lb = atomicAdd(losses + 2, 0.0), lf = atomicAdd(losses + 3, 0.0);
-      const double tot = (double)pe * le + (double)pb * lb + (double)pf * lf;
+      const double lv = v_label ? atomicAdd(losses + 5, 0.0) : 0.0;
+      const double tot = (double)pe * le + (double)pb * lb + (double)pf * lf + (double)pv * lv;
       losses[0] = tot;
       if (mirror) {
         // results straight into the caller's mapped host memory: 4 losses, then the status word (read and cleared)
@@ -613,6 +620,9 @@ struct SweepCall {
   T* grad;
   T* vout;
   double* vir;
+  const double* vacc;  // force backward with a virial loss: the virials, their labels, the loss's scale
+  const T* vlab;
+  T vscale;
   int* status;
 };
 
@@ -643,6 +653,7 @@ static int launch_sweep(stafb_model* m, cudaStream_t s, const SweepCall<T>& call
   a.chan_in = call.chan_in; a.force = call.force; a.flab = call.flab; a.fscale = call.fscale;
   a.loss_kind = call.loss_kind; a.out = call.out; a.grad = call.grad;
   a.vout = call.vout; a.nv = m->nv; a.vir = call.vir; a.status = call.status;
+  a.vacc = call.vacc; a.vlab = call.vlab; a.vscale = call.vscale;
   const int blocks = call.nf * d.N;
   if (MODE == MODE_FORCE && call.vir)
     STAFB_CUDA_OK(launch_chained(k_sweep<T, MODE, MODE == MODE_FORCE>, blocks, 32, sm, s, d, a, L));
@@ -778,7 +789,7 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
                      const T* theta, const T* emb, int per_atom, bool train, const T* e_label, const T* f_label,
                      double pe, double pf, double pb, double bound, int loss_kind, double* losses_out, T* grad,
                      T* energy_out, T* force_out, const DomainArgs* dom = nullptr, T* virial_out = nullptr,
-                     const stafb_model::NlSet* pre = nullptr) {
+                     const stafb_model::NlSet* pre = nullptr, const T* v_label = nullptr, double pv = 0.0) {
   if (!c || !m || (!pos && !pre) || !theta || !emb || nf <= 0) return STAFB_ERR_INVALID;
   if (!box && !pre && !(dom && dom->howmany)) return STAFB_ERR_INVALID;
   if (pre && (dom || pre->nf != nf)) return STAFB_ERR_INVALID;
@@ -815,7 +826,7 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
       k_prep<T>, 64, 256, 0, s, d, theta, emb, (T*)m->wpack, m->wstride, m->spar, m->sl.total, m->sl, (void*)force,
       sizeof(T) * (size_t)nf * 3 * nall,
       train ? (void*)grad : (void*)nullptr, train ? sizeof(T) * (size_t)m->n_params : (size_t)0, (void*)m->losses_d,
-      sizeof(double) * (virial_out ? 8 + 10 * (size_t)c->max_batch : 8 + (size_t)c->max_batch),
+      sizeof(double) * ((virial_out || v_label) ? 8 + 10 * (size_t)c->max_batch : 8 + (size_t)c->max_batch),
       train ? f_label : (const T*)nullptr, (T*)m->flab, train ? (size_t)nf * 3 * N : (size_t)0,
       m->mma ? (T*)m->wm : (T*)nullptr, m->wm_stride));
   c->launches++;
@@ -831,7 +842,8 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
   rc = launch_mlp_fwd<T>(m, s, nf, theta, af, acts, e_atom, nd);
   if (rc != STAFB_OK) return rc;
   mark();  // mlp_fwd
-  double* vacc = virial_out ? m->losses_d + 8 + c->max_batch : nullptr;
+  if (v_label && !train) return STAFB_ERR_INVALID;
+  double* vacc = (virial_out || v_label) ? m->losses_d + 8 + c->max_batch : nullptr;
   sc.chan_in = nd; sc.out = force; sc.vout = nullptr; sc.vir = vacc;
   rc = launch_sweep<T, MODE_FORCE>(m, s, sc);
   if (rc != STAFB_OK) return rc;
@@ -843,6 +855,8 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
     sc.chan_in = nd; sc.force = force; sc.flab = (const T*)m->flab; sc.loss_kind = loss_kind;
     sc.fscale = (T)pf / T((double)((size_t)nf * 3 * N));
     sc.out = gradnet; sc.grad = grad; sc.vir = nullptr;
+    // with a virial loss its cotangent, pv/(9 nf) * L'(W - W_label), is formed on the fly as well
+    sc.vacc = v_label ? vacc : nullptr; sc.vlab = v_label; sc.vscale = (T)(pv / (9.0 * nf));
     rc = launch_sweep<T, MODE_FGRAD>(m, s, sc);
     if (rc != STAFB_OK) return rc;
     mark();  // force_grad
@@ -860,7 +874,8 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
                                  e_label, force, (const T*)m->flab, theta, (T)pe, (T)pf, (T)pb, (T)bound, loss_kind,
                                  (T*)m->ebar, grad, m->losses_d, cg->status_d, c->status_d, vacc, virial_out,
                                  train ? m->mirror_next : (double*)nullptr, m->epart,
-                                 reinterpret_cast<unsigned*>(m->epart + (size_t)c->max_batch * LOSS_EB_MAX)));
+                                 reinterpret_cast<unsigned*>(m->epart + (size_t)c->max_batch * LOSS_EB_MAX), v_label,
+                                 (T)pv));
     m->mirror_next = nullptr;
     c->launches++;
   }
@@ -872,6 +887,8 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
     mark();  // mlp_bwd
     if (losses_out != m->losses_d)
       STAFB_CUDA_OK(cudaMemcpyAsync(losses_out, m->losses_d, sizeof(double) * 4, cudaMemcpyDeviceToDevice, s));
+    if (v_label)  // fifth loss of the energy + force + virial training
+      STAFB_CUDA_OK(cudaMemcpyAsync(losses_out + 4, m->losses_d + 5, sizeof(double), cudaMemcpyDeviceToDevice, s));
   }
   STAFB_CUDA_OK(cudaGetLastError());
   return STAFB_OK;
@@ -899,7 +916,8 @@ static int run_mlp_only(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* a
                                (const T*)nullptr, theta, T(0), T(0), T(0), T(0), 0, (T*)m->ebar, (T*)nullptr,
                                m->losses_d, c->status_d, c->status_d, (const double*)nullptr, (T*)nullptr,
                                (double*)nullptr, m->epart,
-                               reinterpret_cast<unsigned*>(m->epart + (size_t)c->max_batch * LOSS_EB_MAX));
+                               reinterpret_cast<unsigned*>(m->epart + (size_t)c->max_batch * LOSS_EB_MAX),
+                               (const T*)nullptr, T(0));
   c->launches++;
   STAFB_CUDA_OK(cudaGetLastError());
   return STAFB_OK;
@@ -975,6 +993,27 @@ extern "C" int stafb_train_step(stafb_ctx* c, stafb_model* m, void* stream, cons
   return run_fused<double>(c, m, s, (const double*)pos, (const double*)box, nf, (const double*)theta,
                            (const double*)emb, 1, true, (const double*)el, (const double*)fl, pe, pf, pb, bound,
                            loss_kind, losses_d, (double*)grad, (double*)energy, (double*)force);
+}
+
+// Energy + force + virial training evaluation (full_train_e_f_v, STAF/staf_models/staf_model.py:313-384): the
+// loss gains pv * L(W - W_label), mean over [nf, 9], with W the virial of the ...Virial force operators.
+// losses_d[5] = loss, loss_e, loss_bound, loss_f, loss_v.
+extern "C" int stafb_train_step_virial(stafb_ctx* c, stafb_model* m, void* stream, const void* pos, const void* box,
+                                       int nf, const void* theta, const void* emb, const void* el, const void* fl,
+                                       const void* vl, double pe, double pf, double pv, double pb, double bound,
+                                       int loss_kind, double* losses_d, void* grad, void* energy, void* force,
+                                       void* virial) {
+  if (!c || !m || !vl) return STAFB_ERR_INVALID;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (c->dtype == STAFB_F32)
+    return run_fused<float>(c, m, s, (const float*)pos, (const float*)box, nf, (const float*)theta,
+                            (const float*)emb, 1, true, (const float*)el, (const float*)fl, pe, pf, pb, bound,
+                            loss_kind, losses_d, (float*)grad, (float*)energy, (float*)force, nullptr, (float*)virial,
+                            nullptr, (const float*)vl, pv);
+  return run_fused<double>(c, m, s, (const double*)pos, (const double*)box, nf, (const double*)theta,
+                           (const double*)emb, 1, true, (const double*)el, (const double*)fl, pe, pf, pb, bound,
+                           loss_kind, losses_d, (double*)grad, (double*)energy, (double*)force, nullptr,
+                           (double*)virial, nullptr, (const double*)vl, pv);
 }
 
 // Allocates neighbour-row set `slot` (0 or 1) of the model on first use.

@@ -196,6 +196,9 @@ struct SweepArgs {
   T* vout;           // AFV: d(AF)/d(alpha) rows [nf,N,nv] in the accumulator layout (alpha2b[nt,Frmax] | alpha3b[C,3*Famax])
   int nv;
   double* vir;       // FORCE with VIR: virial accumulators [nf,9]
+  const double* vacc;  // FGRAD with a virial loss: the virials [nf,9] the force sweep accumulated, their labels and
+  const T* vlab;       //        the loss's scale: dL/dW = vscale * L'(W - label)
+  T vscale;
   int* status;
 };
 
@@ -532,10 +535,17 @@ __global__ void __launch_bounds__(32, SweepMinBlocks<MODE, sizeof(T)>::value)
     const T e = fo_g[q] - fl_g[q];
     return fscale * (hub ? (e > T(1) ? T(1) : (e < T(-1) ? T(-1) : e)) : T(2) * e);
   };
+  // dL/dW of this frame (virial loss of the energy + force + virial training, staf_model.py:313-384), kept behind
+  // the group offsets
+  T* wbs = reinterpret_cast<T*>(smem_raw + L.red) + 8;
   if (MODE == MODE_FGRAD) {
     fo_g = a.force + (size_t)b * a.nall * 3;
     fl_g = a.flab + (size_t)b * a.nall * 3;
     fbx = fbar_of(i * 3); fby = fbar_of(i * 3 + 1); fbz = fbar_of(i * 3 + 2);
+    if (a.vacc && lane < 9) {
+      const T e = (T)a.vacc[b * 9 + lane] - a.vlab[b * 9 + lane];
+      wbs[lane] = a.vscale * (hub ? (e > T(1) ? T(1) : (e < T(-1) ? T(-1) : e)) : T(2) * e);
+    }
   }
   if (!mbar_wait(bar, 0)) {
     if (lane == 0) set_status(a.status, STAFB_ERR_STAGE_TIMEOUT);
@@ -561,6 +571,15 @@ __global__ void __launch_bounds__(32, SweepMinBlocks<MODE, sizeof(T)>::value)
       const T4 u = U[k];
       T4 d;
       d.x = fbar_of(id * 3) - fbx; d.y = fbar_of(id * 3 + 1) - fby; d.z = fbar_of(id * 3 + 2) - fbz;
+      if (a.vacc) {
+        // W_ab = -sum f_a r_b over the pairs: the virial's cotangent shifts the neighbour's force cotangent by
+        // -(dL/dW) r with r = r_i - r_k (grad_force/rad/reforce.cu.cc:165-234, grad_force/ang/reforce.cu.cc:274-446)
+        const T r = T(1) / V[k].x;
+        const T rx = u.x * r, ry = u.y * r, rz = u.z * r;
+        d.x -= wbs[0] * rx + wbs[1] * ry + wbs[2] * rz;
+        d.y -= wbs[3] * rx + wbs[4] * ry + wbs[5] * rz;
+        d.z -= wbs[6] * rx + wbs[7] * ry + wbs[8] * rz;
+      }
       d.w = d.x * u.x + d.y * u.y + d.z * u.z;
       dF[k] = d;
     }

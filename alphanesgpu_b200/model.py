@@ -142,6 +142,25 @@ class StafModel:
                                           _p(energy), _p(force)), "stafb_train_step")
         return energy, force
 
+    def loss_and_grad_virial(self, pos, box, e_label, f_label, v_label, pv=1.0, want_outputs=False):
+        """Energy + force + virial training evaluation (full_train_e_f_v, STAF/staf_models/staf_model.py:313-384):
+        v_label [nf,9] total virials; fills self.losses5 (loss, loss_e, loss_bound, loss_f, loss_v) and self.grad.
+        Returns (energy, force, virial) when want_outputs."""
+        nf = box.shape[0]
+        if not hasattr(self, "losses5"):
+            self.losses5 = torch.zeros(5, dtype=torch.float64, device=self.device)
+        energy = force = virial = None
+        if want_outputs:
+            energy = torch.empty(nf, dtype=self.dtype, device=self.device)
+            force = torch.empty(nf, 3 * self.shape.N, dtype=self.dtype, device=self.device)
+            virial = torch.empty(nf, 9, dtype=self.dtype, device=self.device)
+        check(_lib.lib().stafb_train_step_virial(self.ctx.h, self.h, self.ctx.stream(), _p(pos), _p(box), nf,
+                                                 _p(self.theta), _p(self.emb), _p(e_label), _p(f_label), _p(v_label),
+                                                 self.pe, self.pf, float(pv), self.pb, self.alpha_bound,
+                                                 self.loss_kind, _p(self.losses5), _p(self.grad), _p(energy),
+                                                 _p(force), _p(virial)), "stafb_train_step_virial")
+        return energy, force, virial
+
     def use_grad(self, tensor):
         """Makes the following evaluations accumulate their gradient into `tensor` (n_params elements on this
         device, e.g. a PeerExchange buffer) instead of the model's own; returns the previous buffer."""

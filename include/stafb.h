@@ -281,6 +281,16 @@ int stafb_train_step(stafb_ctx* ctx, stafb_model* m, void* stream, const void* p
                      double pe, double pf, double pb, double alpha_bound, int loss_kind, double* losses_d,
                      void* grad_d, void* energy_d, void* force_d);
 
+/* The same with the virial term of full_train_e_f_v (STAF/staf_models/staf_model.py:313-384): v_label_d[nf,9]
+ * total virials, loss = pe*loss_e + pb*loss_bound + pf*loss_f + pv*loss_v with loss_v the mean of L(W - W_label)
+ * over [nf,9]; W = -sum f_a r_b over the pairs as the ...Virial force operators define it.
+ * losses_d[5] = loss, loss_e, loss_bound, loss_f, loss_v; virial_d[nf,9] (optional) receives W. */
+int stafb_train_step_virial(stafb_ctx* ctx, stafb_model* m, void* stream, const void* positions_d,
+                            const void* boxer_d, int nf, const void* theta_d, const void* emb_d,
+                            const void* e_label_d, const void* f_label_d, const void* v_label_d, double pe, double pf,
+                            double pv, double pb, double alpha_bound, int loss_kind, double* losses_d, void* grad_d,
+                            void* energy_d, void* force_d, void* virial_d);
+
 /* stafb_train_step in two parts, for callers that know the next batch early (the reference's training loop
  * prefetches its batches in a thread, STAF/staf_train.py:678-755).  The neighbour rows of a batch depend on its
  * positions and boxes only - not on theta - so _prefetch may run on ANOTHER stream while the previous step, the

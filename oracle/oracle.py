@@ -306,6 +306,36 @@ def energy_force_grad(cfg, sd, pos, box, type_map, theta, emb, dtype, per_atom_e
     return out
 
 
+def energy_force_virial_grad(cfg, sd, pos, box, type_map, theta, emb, dtype, per_atom_energy=True, with_grad=False,
+                             e_label=None, f_label=None, v_label=None, pe=1.0, pf=1.0, pv=1.0, pb=1.0,
+                             alpha_bound=5.0, loss_kind=0):
+    """energy_force_grad with the virial [nf,9] and, with_grad, the virial term of the loss
+    (STAF/staf_models/staf_model.py:313-384): losses = (loss, loss_e, loss_bound, loss_f, loss_v)."""
+    pos = _c(pos, dtype)
+    box = _c(box, dtype)
+    nf = box.shape[0]
+    N = pos.shape[1] // 3
+    theta, emb = _c(theta, dtype), _c(emb, dtype)
+    energy = np.zeros(nf, dtype)
+    force = np.zeros((nf, 3 * N), dtype)
+    virial = np.zeros((nf, 9), dtype)
+    losses = np.zeros(5, np.float64)
+    grad = np.zeros_like(theta) if with_grad else None
+    el = _c(e_label, dtype) if with_grad else None
+    fl = _c(f_label, dtype) if with_grad else None
+    vl = _c(v_label, dtype) if with_grad else None
+    st = getattr(lib(), "stafo_energy_force_virial_grad_" + _sfx(dtype))(
+        C.c_double(cfg["Rc"]), C.c_double(cfg["Rs"]), C.c_double(cfg["Ra"]), cfg["nr"], cfg["na"], _p(sd), nf,
+        _p(pos), _p(box), _p(_c(type_map, np.int32)), _p(theta), _p(emb), int(per_atom_energy), _p(energy), _p(force),
+        _p(virial), int(with_grad), _p(el), _p(fl), _p(vl), C.c_double(pe), C.c_double(pf), C.c_double(pv),
+        C.c_double(pb), C.c_double(alpha_bound), int(loss_kind), _p(losses), _p(grad))
+    out = dict(status=st, energy=energy, force=force, virial=virial)
+    if with_grad:
+        out["losses"] = losses
+        out["grad"] = grad
+    return out
+
+
 # --------------------------------------------------------------------------
 # The reference's own CPU code, compiled into oracle/_ref (may be absent).
 def ref_available():

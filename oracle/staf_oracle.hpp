@@ -949,18 +949,21 @@ void split_atoms(int nf, int N, int shift, int Nl, size_t row, const U* src, std
 }
 
 struct StepOut {
-  double loss, loss_e, loss_bound, loss_f;
+  double loss, loss_e, loss_bound, loss_f, loss_v;
 };
 
 // One energy+force evaluation, optionally with the loss and the gradient with
 // respect to every trained parameter (staf_model.py:168-258, without the Adam
 // update).  energy[b] = 0.5*mean_i e_i when per_atom_energy, else 0.5*sum_i e_i
-// (staf_model_inference_full.py:118-119).
+// (staf_model_inference_full.py:118-119).  With v_label the loss also has the virial term of
+// full_train_e_f_v (staf_model.py:313-384): pv * L(W - W_label), mean over [nf,9], W from the ...Virial force
+// operators; virial_out[nf,9] receives W.
 template <class T>
 int energy_force_grad(const DescCfg<T>& c, const ModelShape& ms, int nf, const T* pos, const T* box,
                       const int* type_map, const T* theta, const T* emb, bool per_atom_energy, T* energy /*[nf]*/,
                       T* force /*[nf,3N]*/, bool with_grad, const T* e_label, const T* f_label, T pe, T pf, T pb,
-                      T alpha_bound, int loss_kind /*0 huber, 1 mse*/, StepOut* so, T* grad /*[n_params]*/) {
+                      T alpha_bound, int loss_kind /*0 huber, 1 mse*/, StepOut* so, T* grad /*[n_params]*/,
+                      const T* v_label = nullptr /*[nf,9]*/, T pv = T(0), T* virial_out = nullptr) {
   const int N = ms.N(), nr = c.nr, na = c.na, nt = ms.nt, C = ms.C();
   size_t A = (size_t)nf * N;
   std::vector<T> rad(A * nr), ang(A * na), d3s(A * nr), der2b(A * 3 * nr), der3b(A * 3 * na * 2), der3bs(A * 3 * nr);
@@ -975,6 +978,11 @@ int energy_force_grad(const DescCfg<T>& c, const ModelShape& ms, int nf, const T
   std::vector<Sp> sp(nt);
   std::vector<double> F64((size_t)nf * 3 * N, 0.0);
   std::vector<double> esum(nf, 0.0);
+  const bool with_virial = v_label != nullptr || virial_out != nullptr;
+  std::vector<double> W64((size_t)nf * 9, 0.0);
+  const T* vpos = with_virial ? pos : nullptr;
+  const T* vbox = with_virial ? box : nullptr;
+  double* vW = with_virial ? W64.data() : nullptr;
   for (int t = 0; t < nt; t++) {
     Sp& s = sp[t];
     int Nl = ms.tipos[t], sh = ms.shift(t), Fr = ms.Fr[t], Fa = ms.Fa[t], F = Fr + Fa;
@@ -1013,10 +1021,13 @@ int energy_force_grad(const DescCfg<T>& c, const ModelShape& ms, int nf, const T
       for (int i = 0; i < Fa; i++) nda[a * Fa + i] = s.nd[a * F + Fr + i];
     }
     force_radial(nf, Nl, N, nr, Fr, sh, ndr.data(), s.der2b.data(), s.im2.data(), s.rad.data(), a2, e2, type_map,
-                 F64.data());
+                 F64.data(), vpos, vbox, vW);
     force_tripl(nf, Nl, N, nr, na, Fa, sh, nda.data(), s.d3s.data(), s.ang.data(), s.der3bs.data(), s.der3b.data(),
-                s.im3.data(), a3, e3, type_map, s.ntr.data(), F64.data());
+                s.im3.data(), a3, e3, type_map, s.ntr.data(), F64.data(), vpos, vbox, vW);
   }
+  std::vector<T> Wv((size_t)nf * 9);
+  for (size_t i = 0; i < Wv.size(); i++) Wv[i] = (T)W64[i];
+  if (virial_out) std::copy(Wv.begin(), Wv.end(), virial_out);
   std::vector<T> Fv((size_t)nf * 3 * N);
   for (size_t i = 0; i < Fv.size(); i++) Fv[i] = (T)F64[i];
   if (force) std::copy(Fv.begin(), Fv.end(), force);
@@ -1040,6 +1051,19 @@ int energy_force_grad(const DescCfg<T>& c, const ModelShape& ms, int nf, const T
     Fbar[i] = pf * (loss_kind == 0 ? huber_d(e) : T(2) * e) / T((double)Fv.size());
   }
   lf /= (double)Fv.size();
+  double lv = 0;
+  std::vector<T> Wbar((size_t)nf * 9, T(0));
+  if (v_label) {
+    for (size_t i = 0; i < Wv.size(); i++) {
+      T e = Wv[i] - v_label[i];
+      lv += (double)(loss_kind == 0 ? huber(e) : e * e);
+      Wbar[i] = pv * (loss_kind == 0 ? huber_d(e) : T(2) * e) / T((double)Wv.size());
+    }
+    lv /= (double)Wv.size();
+  }
+  const T* wb = v_label ? Wbar.data() : nullptr;
+  const T* wpos = v_label ? pos : nullptr;
+  const T* wbox = v_label ? box : nullptr;
   const int P = ms.n_params();
   std::vector<double> G(P, 0.0);
   for (int t = 0; t < nt; t++) {
@@ -1071,10 +1095,10 @@ int energy_force_grad(const DescCfg<T>& c, const ModelShape& ms, int nf, const T
     }
     std::vector<double> gn2(n * Fr, 0.0), gn3(n * Fa, 0.0), ge2(nt * Fr, 0.0);
     grad_force_radial(nf, Nl, N, nr, Fr, sh, Fbar.data(), ndr.data(), s.der2b.data(), s.im2.data(), s.rad.data(), a2,
-                      e2, type_map, nt, gn2.data(), G.data() + ms.off_a2(t), ge2.data());
+                      e2, type_map, nt, gn2.data(), G.data() + ms.off_a2(t), ge2.data(), wpos, wbox, wb);
     grad_force_tripl(nf, Nl, N, nr, na, Fa, sh, Fbar.data(), nda.data(), s.d3s.data(), s.ang.data(), s.der3bs.data(),
                      s.der3b.data(), s.im3.data(), a3, e3, type_map, s.ntr.data(), C, gn3.data(),
-                     G.data() + ms.off_a3(t));
+                     G.data() + ms.off_a3(t), wpos, wbox, wb);
     std::vector<T> u(n * F), ebar(n), gaf(n * F);
     for (size_t a = 0; a < n; a++) {
       for (int i = 0; i < Fr; i++) u[a * F + i] = (T)gn2[a * Fr + i];
@@ -1101,7 +1125,8 @@ int energy_force_grad(const DescCfg<T>& c, const ModelShape& ms, int nf, const T
     so->loss_e = le;
     so->loss_f = lf;
     so->loss_bound = lb;
-    so->loss = (double)pe * le + (double)pb * lb + (double)pf * lf;
+    so->loss_v = lv;
+    so->loss = (double)pe * le + (double)pb * lb + (double)pf * lf + (double)pv * lv;
   }
   return OK;
 }

@@ -143,11 +143,29 @@ static ModelShape make_shape(const int* d) {
                                                double* losses4, T* grad) {                                             \
     DescCfg<T> c = make_cfg<T>(Rc, Rs, Ra, nr, na);                                                                    \
     ModelShape ms = make_shape(shape_desc);                                                                            \
-    StepOut so = {0, 0, 0, 0};                                                                                         \
+    StepOut so = {0, 0, 0, 0, 0};                                                                                      \
     int st = energy_force_grad<T>(c, ms, nf, pos, box, type_map, theta, emb, per_atom_energy != 0, energy, force,      \
                                   with_grad != 0, e_label, f_label, (T)pe, (T)pf, (T)pb, (T)alpha_bound, loss_kind,    \
                                   &so, grad);                                                                          \
     if (losses4) { losses4[0] = so.loss; losses4[1] = so.loss_e; losses4[2] = so.loss_bound; losses4[3] = so.loss_f; } \
+    return st;                                                                                                         \
+  }                                                                                                                    \
+  /* the same with the virial term of full_train_e_f_v: losses5 = loss, loss_e, loss_bound, loss_f, loss_v */         \
+  extern "C" int stafo_energy_force_virial_grad_##SFX(                                                                 \
+      double Rc, double Rs, double Ra, int nr, int na, const int* shape_desc, int nf, const T* pos, const T* box,      \
+      const int* type_map, const T* theta, const T* emb, int per_atom_energy, T* energy, T* force, T* virial,          \
+      int with_grad, const T* e_label, const T* f_label, const T* v_label, double pe, double pf, double pv, double pb, \
+      double alpha_bound, int loss_kind, double* losses5, T* grad) {                                                   \
+    DescCfg<T> c = make_cfg<T>(Rc, Rs, Ra, nr, na);                                                                    \
+    ModelShape ms = make_shape(shape_desc);                                                                            \
+    StepOut so = {0, 0, 0, 0, 0};                                                                                      \
+    int st = energy_force_grad<T>(c, ms, nf, pos, box, type_map, theta, emb, per_atom_energy != 0, energy, force,      \
+                                  with_grad != 0, e_label, f_label, (T)pe, (T)pf, (T)pb, (T)alpha_bound, loss_kind,    \
+                                  &so, grad, with_grad ? v_label : (const T*)nullptr, (T)pv, virial);                  \
+    if (losses5) {                                                                                                     \
+      losses5[0] = so.loss; losses5[1] = so.loss_e; losses5[2] = so.loss_bound; losses5[3] = so.loss_f;                \
+      losses5[4] = so.loss_v;                                                                                          \
+    }                                                                                                                  \
     return st;                                                                                                         \
   }
 

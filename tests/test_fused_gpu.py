@@ -151,6 +151,47 @@ def test_the_tensor_core_mlp_on_the_reference_model_shape(oracle, frame0, monkey
     m.close()
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("name,seeds,loss", [("water96", [1000, 1001], "huber"), ("water96", [1000, 1001], "mse"),
+                                             ("water768", [1100, 1101], "huber"), ("frame0", None, "huber")])
+def test_train_step_with_the_virial_loss(oracle, frame0, name, seeds, loss, dtype):
+    """Energy + force + virial training evaluation (full_train_e_f_v, staf_model.py:313-384): energies, forces,
+    virials, the five losses and the gradient per parameter family against the oracle, whose virial-loss gradient
+    is pinned by finite differences in tests/test_oracle.py."""
+    from alphanesgpu_b200.model import StafModel
+    pos, box, shape, theta, emb = _case(name, seeds, frame0)
+    theta = _push_over_bound(shape, theta)
+    nf = pos.shape[0]
+    el, fl = synth.labels(nf, shape.N)
+    vl = np.random.default_rng(23).normal(0.0, 2.0, (nf, 9))  # both branches of the Huber loss
+    kw = dict(pe=0.7, pf=1.3, pb=0.9, alpha_bound=5.0)
+    ref = oracle.energy_force_virial_grad(CFG, shape.desc(), pos, box, shape.type_map, theta, emb, dtype,
+                                          with_grad=True, e_label=el, f_label=fl, v_label=vl, pv=0.6,
+                                          loss_kind=0 if loss == "huber" else 1, **kw)
+    assert ref["status"] == 0 and ref["losses"][4] > 0
+    m = StafModel(shape, CFG, theta, emb, nf, dtype=_tdt(dtype), loss=loss, **kw)
+    d = lambda a: torch.as_tensor(a.astype(dtype)).cuda()
+    e, f, w = m.loss_and_grad_virial(d(pos), d(box), d(el), d(fl), d(vl), pv=0.6, want_outputs=True)
+    m.ctx.raise_on_status("train_step_virial")
+    tol = TOL[dtype]
+    assert rel_err(e.cpu().numpy(), ref["energy"]) <= tol
+    assert rel_err(f.cpu().numpy(), ref["force"]) <= tol
+    assert rel_err(w.cpu().numpy(), ref["virial"]) <= 10 * tol
+    assert np.allclose(m.losses5.cpu().numpy(), ref["losses"], rtol=tol * 20, atol=0)
+    g, gr = m.grad.cpu().numpy().astype(np.float64), ref["grad"].astype(np.float64)
+    for t in range(shape.nt):
+        o = shape.offsets(t)
+        for lo, hi in ((o["a2"], o["a3"]), (o["a3"], o["mu"]), (o["mu"], o["w"]), (o["w"], o["a2"] + o["size"])):
+            assert rel_err(g[lo:hi], gr[lo:hi]) <= 2 * tol, (t, lo, hi)
+    # the plain evaluation afterwards is not affected by the virial state
+    m.loss_and_grad(d(pos), d(box), d(el), d(fl))
+    plain = oracle.energy_force_grad(CFG, shape.desc(), pos, box, shape.type_map, theta, emb, dtype, with_grad=True,
+                                     e_label=el, f_label=fl, loss_kind=0 if loss == "huber" else 1, **kw)
+    assert np.allclose(m.losses.cpu().numpy(), plain["losses"], rtol=tol * 10, atol=0)
+    assert rel_err(m.grad.cpu().numpy(), plain["grad"]) <= tol
+    m.close()
+
+
 def test_train_step_batch_of_eight(oracle, frame0):
     """Eight 768-atom frames per step, the per-GPU batch of the data-parallel configuration."""
     from alphanesgpu_b200.model import StafModel

@@ -141,6 +141,46 @@ def test_parameter_gradients_fd(oracle, loss_kind):
         assert abs(fd - g[i]) < 2e-6 * max(abs(g).max(), 1e-3), (i, fd, g[i])
 
 
+@pytest.mark.parametrize("loss_kind", [0, 1])
+def test_parameter_gradients_with_the_virial_loss_fd(oracle, loss_kind):
+    """The energy + force + virial loss of full_train_e_f_v (staf_model.py:313-384): its gradient against central
+    differences of the total loss in double precision, all parameter families; without virial labels the
+    evaluation equals the energy + force one."""
+    pos, box, shape, theta, emb, el, fl = _small_case(np.float64, nf=2)
+    sd = shape.desc()
+    theta = theta.copy()
+    theta[shape.offsets(0)["a2"] + 1] = 5.5
+    rng = np.random.default_rng(17)
+    vl = rng.normal(0.0, 2.0, (2, 9))  # spread over both Huber branches
+    kw = dict(with_grad=True, e_label=el, f_label=fl, v_label=vl, pe=0.7, pf=1.3, pv=0.6, pb=0.9, alpha_bound=5.0,
+              loss_kind=loss_kind)
+    r = oracle.energy_force_virial_grad(CFG, sd, pos, box, shape.type_map, theta, emb, np.float64, **kw)
+    assert r["status"] == 0
+    ls = r["losses"]
+    assert abs(ls[0] - (0.7 * ls[1] + 0.9 * ls[2] + 1.3 * ls[3] + 0.6 * ls[4])) <= 1e-12 * abs(ls[0])
+    assert ls[4] > 0
+    plain = oracle.energy_force_grad(CFG, sd, pos, box, shape.type_map, theta, emb, np.float64, with_grad=True,
+                                     e_label=el, f_label=fl, pe=0.7, pf=1.3, pb=0.9, alpha_bound=5.0,
+                                     loss_kind=loss_kind)
+    assert np.allclose(plain["losses"][1:4], ls[1:4], rtol=1e-13)
+    assert np.abs(r["grad"] - plain["grad"]).max() > 1e-6  # the virial term does contribute
+    g = r["grad"]
+    picks = []
+    for t in range(shape.nt):
+        o = shape.offsets(t)
+        for lo, hi in ((o["a2"], o["a3"]), (o["a3"], o["mu"]), (o["mu"], o["w"]), (o["w"], o["a2"] + o["size"])):
+            picks += list(rng.integers(lo, hi, 3))
+    h = 1e-6
+    for i in picks:
+        tp, tm = theta.copy(), theta.copy()
+        tp[i] += h
+        tm[i] -= h
+        lp = oracle.energy_force_virial_grad(CFG, sd, pos, box, shape.type_map, tp, emb, np.float64, **kw)["losses"][0]
+        lm = oracle.energy_force_virial_grad(CFG, sd, pos, box, shape.type_map, tm, emb, np.float64, **kw)["losses"][0]
+        fd = (lp - lm) / (2 * h)
+        assert abs(fd - g[i]) < 2e-6 * max(abs(g).max(), 1e-3), (i, fd, g[i])
+
+
 def test_mlp_backward_fd(oracle):
     rng = np.random.default_rng(11)
     widths, F, n = [9, 6, 1], 7, 5
