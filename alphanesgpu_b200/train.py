@@ -12,7 +12,8 @@ batch with a per-step learning rate from `expdec` or `cosann` (optimizer_learnin
 the reference only the net optimizer is applied and it updates every trained parameter, staf_model.py:253);
 frame buffers sharded idx[rank::world] and the learning rate NOT scaled by the world size
 (staf_train.py:131-146,458-463); `lcurve_notmean`-style rows "step loss_e loss_f loss_bound" and `lr_step.dat`.
-What is not: restart modes, validation passes, SavedModel export, virial training (use the operators).
+What is not: restart modes, validation passes, SavedModel export; the energy + force + virial step exists as
+StafModel.loss_and_grad_virial (stafb_train_step_virial), this driver trains on energies and forces.
 Every device step is the C ABI (pipelined stafb_train_step_host_begin/_end + stafb_adam_step_dev).
 """
 import math
