@@ -938,6 +938,30 @@ def run_ours(args):
                 "blocks": int(len(tot)), "phase_ms": ph}
 
     Ksub = max(10, min(K, 200))
+    # energy + force + virial training evaluation beside the energy + force one, both as plain launches with the
+    # L2 flushed (the extra work: the virial in the force sweep, nine more loss terms, three more FMAs per neighbour
+    # in the backward sweep's prologue)
+    def eager_ms(fn, Kp=30):
+        a_ = [torch.cuda.Event(enable_timing=True) for _ in range(Kp)]
+        b_ = [torch.cuda.Event(enable_timing=True) for _ in range(Kp)]
+        for k in range(3):
+            fn(k)
+        torch.cuda.synchronize()
+        for k in range(Kp):
+            flush.zero_()
+            a_[k].record()
+            fn(k)
+            b_[k].record()
+        torch.cuda.synchronize()
+        return float(np.median([x.elapsed_time(y) for x, y in zip(a_, b_)]))
+    vlab = torch.zeros(B, 9, dtype=torch.float32, device=dev)
+    ms_plain = eager_ms(lambda k: model.loss_and_grad(d_pos[k % NB], d_box[k % NB], d_el[k % NB], d_fl[k % NB]))
+    ms_vir = eager_ms(lambda k: model.loss_and_grad_virial(d_pos[k % NB], d_box[k % NB], d_el[k % NB], d_fl[k % NB],
+                                                           vlab, pv=1.0))
+    model.ctx.raise_on_status("virial training leg")
+    virial_rec = {"ms_per_evaluation": ms_vir, "ms_per_evaluation_energy_force_only": ms_plain,
+                  "ratio": ms_vir / ms_plain, "what": "stafb_train_step_virial vs stafb_train_step, plain launches "
+                  "(neighbour records in line, no optimiser), batch %d" % B}
     # the same step in float64: time ratio and FP64-pipe fraction of the sweeps
     model64 = StafModel(shape, CFG, theta.astype(np.float64), emb.astype(np.float64), B, dtype=torch.float64, device=dev)
     d64 = to_dev(tuple(a.astype(np.float64) for a in (pos, box, el, fl)))
@@ -1027,7 +1051,7 @@ def run_ours(args):
                     "synchronous_call_value": world * B / e2e_sync_s},
             "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step,
             "clocks": clocks, "roofline": roofline, "roofline_operator_boundary": roofline_ops,
-            "operator_chain": opchain, "fp32_pipe": fp32_pipe, "fp64": fp64, "batch8": batch8, "real_model": real,
+            "operator_chain": opchain, "fp32_pipe": fp32_pipe, "fp64": fp64, "batch8": batch8, "real_model": real, "virial_training": virial_rec,
             "md": md, "multi_gpu": multi, "phase_ms": acc, "cpu_baseline": cpu,
         }
         if exchange_status:
