@@ -102,7 +102,8 @@ def connect_collectively(create, get_handle, connect, destroy, world, device, gr
     dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
     if float(ok) == 0.0:
         if h is not None:
-            torch.cuda.synchronize()
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
             dist.barrier(group=group)  # nobody unmaps while another rank may still be mapping
             destroy(h)
         else:

@@ -98,3 +98,64 @@ def test_host_watchdog_detects_missing_rank_without_hanging():
     for p in procs:
         p.join(timeout=30)
     assert any(m.startswith("detected") and "[1]" in m for m in msgs), msgs
+
+
+def _connect_worker(rank, world, port, q, failing):
+    """connect_collectively with stand-ins for the library calls: rank `failing` cannot create its block
+    (or, failing = -2, rank 1 cannot map a peer's block); every rank must raise, and release what it made."""
+    import ctypes as C
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from alphanesgpu_b200.dist import connect_collectively
+    log = []
+
+    def create():
+        if rank == failing:
+            raise RuntimeError("no memory on rank %d" % rank)
+        log.append("create")
+        return 1000 + rank
+
+    def get_handle(h, buf):
+        C.memmove(buf, bytes([rank]) * 64, 64)
+        return 0
+
+    def connect(h, blob):
+        assert len(blob) == 64 * world and blob[64 * rank] == rank
+        log.append("connect")
+        return 5 if (failing == -2 and rank == 1) else 0  # a non-zero status of the library raises
+
+    def destroy(h):
+        log.append("destroy")
+
+    try:
+        h = connect_collectively(create, get_handle, connect, destroy, world, torch.device("cpu"), None, "fake")
+        q.put((rank, "ok", h, log))
+    except RuntimeError as exc:
+        q.put((rank, "raised", str(exc), log))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("failing", [-1, 1, -2])
+def test_peer_memory_set_up_fails_on_every_rank_alike(failing):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_connect_worker, args=(r, 2, port, q, failing)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict((r[0], r[1:]) for r in (q.get(timeout=120) for _ in range(2)))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    if failing == -1:
+        assert got[0][0] == "ok" and got[1][0] == "ok" and got[0][1] == 1000 and got[1][1] == 1001
+        assert got[0][2] == ["create", "connect"]
+    else:
+        assert got[0][0] == "raised" and got[1][0] == "raised"
+        for r in (0, 1):
+            made = "create" in got[r][2]
+            assert ("destroy" in got[r][2]) == made  # whatever was created is released
+        if failing == 1:
+            assert "connect" not in got[0][2]  # nobody maps anything when a block is missing
