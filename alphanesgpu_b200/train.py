@@ -1,4 +1,5 @@
-"""Minimal training driver with the reference's step semantics (STAF/staf_train.py, energy+force).
+"""Minimal training driver with the reference's step semantics (STAF/staf_train.py, energy+force and
+energy+force+virial).
 
     python -m alphanesgpu_b200.train input.yaml            # one GPU
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m alphanesgpu_b200.train input.yaml
@@ -12,9 +13,11 @@ batch with a per-step learning rate from `expdec` or `cosann` (optimizer_learnin
 the reference only the net optimizer is applied and it updates every trained parameter, staf_model.py:253);
 frame buffers sharded idx[rank::world] and the learning rate NOT scaled by the world size
 (staf_train.py:131-146,458-463); `lcurve_notmean`-style rows "step loss_e loss_f loss_bound" and `lr_step.dat`.
-What is not: restart modes, validation passes, SavedModel export; the energy + force + virial step exists as
-StafModel.loss_and_grad_virial (stafb_train_step_virial), this driver trains on energies and forces.
-Every device step is the C ABI (pipelined stafb_train_step_host_begin/_end + stafb_adam_step_dev).
+type_of_training: energy+force+virial (staf_train.py:291-294,372-382: train/virial.npy with 9 values per frame,
+loss_virial_prefactor, rows "step loss_e loss_f loss_v loss_bound") runs stafb_train_step_virial per batch.
+What is not: restart modes, validation passes, SavedModel export.
+Every device step is the C ABI (energy+force: pipelined stafb_train_step_host_begin/_end; with the virial: device
+copies + stafb_train_step_virial; then stafb_adam_step_dev or the peer exchange).
 """
 import math
 import os
@@ -62,7 +65,8 @@ def build_learning_rate(param, n_epochs, batches_per_buffer, buffer_dim):
 # ---------------------------------------------------------------- configuration
 DEFAULTS = dict(precision="float", distribute="none", buffer_stream_dim_tr=4, batch_size=4, number_of_epochs=1,
                 Rc=4.5, Rs=2.25, Rc_Angular=4.5, Radial_Buffer=60, Max_Angular_Neigh=60, alpha_bound=5.0,
-                loss_energy_prefactor=1.0, loss_force_prefactor=1.0, loss_bound_prefactor=1.0, loss_method="huber",
+                loss_energy_prefactor=1.0, loss_force_prefactor=1.0, loss_bound_prefactor=1.0,
+                loss_virial_prefactor=1.0, loss_method="huber",
                 lr_dense_net="expdec 0.001 0.0000001", optimizer_net="adam", displ_freq=10, Seed=0,
                 type_of_training="energy+force", model_name="model_log", number_of_decoding_nodes="64 32",
                 map_rad_afs={0: [5, 5], 1: [5, 5]}, map_ang_afs={0: [5, 5, 5], 1: [5, 5, 5]})
@@ -76,8 +80,8 @@ def load_config(path_or_dict):
     else:
         with open(path_or_dict) as f:
             cfg.update(yaml.safe_load(f) or {})
-    if cfg["type_of_training"] != "energy+force":
-        raise ValueError("this driver trains energy+force only")
+    if cfg["type_of_training"] not in ("energy+force", "energy+force+virial"):
+        raise ValueError("type_of_training can be energy+force or energy+force+virial in this driver")
     return cfg
 
 
@@ -163,6 +167,15 @@ def train(cfg, out_dir=".", data=None, max_steps=None, log=print):
         ld = lambda n: np.load(os.path.join(root, "train", n), mmap_mode="r")
         data = dict(pos=ld("pos.npy"), box=ld("box.npy"), energy=ld("energy.npy"), force=ld("force.npy"),
                     tipos=np.loadtxt(os.path.join(root, "type.dat"), dtype=int).reshape(-1))
+        if cfg["type_of_training"] == "energy+force+virial":
+            data["virial"] = ld("virial.npy")
+    with_virial = cfg["type_of_training"] == "energy+force+virial"
+    if with_virial:
+        if "virial" not in data:
+            raise ValueError("type_of_training=energy+force+virial requires virial labels (train/virial.npy)")
+        if int(np.prod(data["virial"].shape[1:])) != 9:
+            raise ValueError("virial labels must have 9 values per frame (full tensor, total eV)")
+    pv = float(cfg["loss_virial_prefactor"])
     double = str(cfg["precision"]).lower() in ("double", "float64", "fp64")
     np_dt, t_dt = (np.float64, torch.float64) if double else (np.float32, torch.float32)
     shape = model_shape_from_config(cfg, data["tipos"])
@@ -234,9 +247,18 @@ def train(cfg, out_dir=".", data=None, max_steps=None, log=print):
 
     def collect(p):
         st, slot, lr = p
-        l = model.loss_and_grad_host_end(slot)
+        if with_virial:
+            l = model.losses5.cpu().numpy()  # waits for the step
+        else:
+            l = model.loss_and_grad_host_end(slot)
         if st % displ == 0:
             check_exchange("step %d" % st)
+        if with_virial:  # columns of the reference: step Loss_E Loss_F Loss_V Loss_Bound (staf_train.py:625,742-745)
+            rows.append((st, l[0], l[1], l[3], l[2], lr, l[4]))
+            if chief:
+                lcurve.write("%d %.9g %.9g %.9g %.9g\n" % (st, l[1], l[3], l[4], l[2]))
+                lrfile.write("%.9g\n" % lr)
+            return
         rows.append((st, l[0], l[1], l[3], l[2], lr))
         if chief:
             lcurve.write("%d %.9g %.9g %.9g\n" % (st, l[1], l[3], l[2]))
@@ -250,6 +272,7 @@ def train(cfg, out_dir=".", data=None, max_steps=None, log=print):
             box = np.asarray(data["box"][el], np_dt)
             en = np.asarray(data["energy"][el], np_dt).reshape(-1)
             fo = np.asarray(data["force"][el], np_dt).reshape(len(el), -1)
+            vi = np.asarray(data["virial"][el], np_dt).reshape(len(el), 9) if with_virial else None
             if world > 1:
                 dist.barrier()  # the ranks read different buffers: start the buffer's steps together
             for k in range(nb):
@@ -258,7 +281,12 @@ def train(cfg, out_dir=".", data=None, max_steps=None, log=print):
                 step += 1
                 if px is not None:
                     model.use_grad(px.grad(step & 1))
-                model.loss_and_grad_host_begin(pos[sl].reshape(bs, 3 * N), box[sl], en[sl], fo[sl], step & 1)
+                if with_virial:
+                    dv = lambda a: torch.as_tensor(np.ascontiguousarray(a)).to(dev, non_blocking=True)
+                    model.loss_and_grad_virial(dv(pos[sl].reshape(bs, 3 * N)), dv(box[sl]), dv(en[sl]), dv(fo[sl]),
+                                               dv(vi[sl]), pv=pv)
+                else:
+                    model.loss_and_grad_host_begin(pos[sl].reshape(bs, 3 * N), box[sl], en[sl], fo[sl], step & 1)
                 if px is not None:
                     px.allreduce_adam(model, step & 1, lr, eps=eps)
                 else:
@@ -267,6 +295,9 @@ def train(cfg, out_dir=".", data=None, max_steps=None, log=print):
                 if pending is not None:
                     collect(pending)
                 pending = (step, step & 1, lr)
+                if with_virial:  # one set of loss words: read them before the next evaluation overwrites them
+                    collect(pending)
+                    pending = None
                 if chief and step % displ == 0:
                     log("Epoch %d step %d. Time to elaborate %d batch of %d frames is %.4f"
                         % (ep, step, displ, bs, time.time() - t0))

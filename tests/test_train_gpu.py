@@ -47,6 +47,45 @@ def test_driver_matches_a_hand_written_loop(tmp_path):
     m.close()
 
 
+def test_driver_trains_on_energy_force_and_virial(tmp_path):
+    """type_of_training: energy+force+virial (staf_train.py:291-294): the driver's rows against the same sequence
+    of stafb_train_step_virial + Adam by hand; log columns step Loss_E Loss_F Loss_V Loss_Bound."""
+    from alphanesgpu_b200 import train as T
+    from alphanesgpu_b200.model import StafModel
+    pos, box, tipos = synth.water_frames("water96", list(range(1000, 1008)))
+    el, fl = synth.labels(8, 96, seed=11)
+    vl = np.random.default_rng(3).normal(0.0, 1.5, (8, 9))
+    cfg = T.load_config(dict(buffer_stream_dim_tr=4, batch_size=2, number_of_epochs=2, displ_freq=3, Seed=5,
+                             type_of_training="energy+force+virial", loss_virial_prefactor=0.5,
+                             lr_dense_net="expdec 0.002 0.0000001"))
+    data = dict(pos=pos, box=box, energy=el, force=fl, virial=vl, tipos=np.array(tipos))
+    res = T.train(cfg, str(tmp_path), data=data, log=lambda *_: None)
+    rows = res["rows"]
+    assert [r[0] for r in rows] == list(range(1, 9))
+    lines = [l for l in open(tmp_path / "lcurve_notmean").read().split("\n") if l]
+    assert len(lines) == 8 and all(len(l.split()) == 5 for l in lines)
+    shape = res["shape"]
+    theta, emb = T.init_params(shape, cfg, 5)
+    m = StafModel(shape, res["geo"], theta, emb, 2, dtype=torch.float32, device="cuda:0")
+    lr_of = T.build_learning_rate(cfg["lr_dense_net"], 2, 2, 4)
+    dv = lambda a: torch.as_tensor(np.ascontiguousarray(a, np.float32)).cuda()
+    step = 0
+    for ep in range(2):
+        for b in range(2):
+            for k in range(2):
+                sl = slice(4 * b + 2 * k, 4 * b + 2 * k + 2)
+                m.loss_and_grad_virial(dv(pos[sl]), dv(box[sl]), dv(el[sl]), dv(fl[sl]), dv(vl[sl]), pv=0.5)
+                l = m.losses5.cpu().numpy().copy()
+                m.adam_update_dev(lr_of(step))
+                r = rows[step]
+                assert np.allclose([r[1], r[2], r[4], r[3], r[6]], l, rtol=2e-5), (step, r, l)
+                step += 1
+    m.close()
+    with pytest.raises(ValueError):
+        T.train(cfg, str(tmp_path), data=dict(pos=pos, box=box, energy=el, force=fl, tipos=np.array(tipos)),
+                log=lambda *_: None)
+
+
 # ---- loss-curve parity of the data-parallel arm, the reference's none-vs-horovod check
 # (test/test-training-pipeline/compare_distribute_lcurve.py; recorded bar
 # test/test-training-pipeline/parity_distribute/float/summary.txt:1-12: 125 steps, rtol 1e-4, atol 1e-5)
