@@ -20,30 +20,31 @@ extern "C" {
 typedef struct StafMlp StafMlp;
 
 typedef struct StafMlpEval {
-  int n_type;
-  const int* n_atoms; /* [n_type] */
-  const int* n_af;    /* [n_type] */
-  /* Packed AF per type: type0 atoms, then type1, ... row-major [n_atoms_k, n_af_k] */
+  int n_type;         /* number of species */
+  const int* n_atoms; /* atoms of every species, n_type entries */
+  const int* n_af;    /* fingerprints per atom of every species, n_type entries */
+  /* Fingerprints of all atoms in one array: the atoms of species 0 first, then species 1 ...; inside a species
+   * one row of n_af[k] values per atom.  Only the array of the handle's precision is read. */
   const float* af_f32;
   const double* af_f64;
-  float* energy_f32; /* [1] total for all types */
+  /* Out: one value, half the sum of the atomic energies over all species. */
+  float* energy_f32;
   double* energy_f64;
-  float* dE_daf_f32; /* packed like af */
+  /* Out: derivative of the sum of the atomic energies with respect to every fingerprint, laid out as af. */
+  float* dE_daf_f32;
   double* dE_daf_f64;
 } StafMlpEval;
 
-/* precision: 0 = float32, 1 = float64.  Returns NULL on failure. */
+/* precision: 0 for float32, 1 for float64.  NULL when the model cannot be loaded. */
 StafMlp* staf_mlp_create(StafMlpBackend backend, const char* model_dir, int precision, int device_id);
-/* The arrays of the created precision are used (af_f32/energy_f32/dE_daf_f32 or the _f64 ones).
- * Returns 0, or -1 bad handle/argument/allocation, -2 n_type or n_af do not match the model, -13 device-side
+/* Returns 0, or -1 bad handle/argument/allocation, -2 n_type or n_af do not match the model, -13 device-side
  * status, -14 CUDA error. */
 int staf_mlp_eval(StafMlp* mlp, StafMlpEval* io);
 void staf_mlp_destroy(StafMlp* mlp);
 
-/* Number of loaded type nets (after create). */
+/* what was loaded: species count, fingerprints per atom of a species, precision (0 / 1 as in create) */
 int staf_mlp_ntypes(const StafMlp* mlp);
 int staf_mlp_n_af(const StafMlp* mlp, int type);
-/* 0 = float32, 1 = float64 (matches create precision). */
 int staf_mlp_precision(const StafMlp* mlp);
 
 #ifdef __cplusplus
