@@ -168,7 +168,10 @@ __global__ void __launch_bounds__(HALO_THREADS)
       h_st_sys(v.flags_of[v.lo] + 3, tag);  // lo sees "forces from hi"
       h_st_sys(v.flags_of[v.hi] + 2, tag);
     }
-    if (threadIdx.x < v.world) h_st_sys(v.flags_of[threadIdx.x] + 8 + v.rank, tag);
+    if (threadIdx.x < v.world) {
+      __threadfence_system();  // every publishing thread orders the block's earlier stores before its own flag
+      h_st_sys(v.flags_of[threadIdx.x] + 8 + v.rank, tag);
+    }
   }
 }
 
