@@ -150,7 +150,7 @@ def test_a_wait_that_runs_out_leaves_a_status_and_a_usable_context():
     full.close()
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, halo_every=4, use_graph=True):
     import torch.distributed as dist
     from alphanesgpu_b200.slab import PeerSlabDomain
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -161,13 +161,13 @@ def _worker(rank, world, port, q):
     shape, theta, emb, box6, gpos, gtypes, full = _system(dtype, dev)
     N = shape.N
     model = _rank_model(shape, theta, emb, dtype, dev, N)
-    dom = PeerSlabDomain(model, box6, CFG["Rc"], rank, world, cap_atoms=N, cap_face=N, skin=0.2, halo_every=4,
-                         use_graph=True)
+    dom = PeerSlabDomain(model, box6, CFG["Rc"], rank, world, cap_atoms=N, cap_face=N, skin=0.2,
+                         halo_every=halo_every, use_graph=use_graph)
     own = dom.set_owned_from_global(gpos, gtypes)
     boxt = torch.as_tensor(np.asarray(box6)[None].astype(np.float32)).to(dev)
     worst = 0.0
     gen = torch.Generator(device="cpu").manual_seed(7)  # the same walk on both ranks
-    for k in range(9):  # plans at k = 0, 4, 8; eager, captured, replayed evaluations in between
+    for k in range(9):  # halo_every 4: plans for k = 0, 4, 8; eager, captured, replayed evaluations in between
         e, f = dom.step()
         torch.cuda.synchronize()
         e_full, f_full = full.energy_force(gpos.reshape(1, -1), boxt)
@@ -187,12 +187,16 @@ def _worker(rank, world, port, q):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_processes_with_graph_replay():
+@pytest.mark.parametrize("halo_every,use_graph", [(4, True), (1, False)])
+def test_two_processes(halo_every, use_graph):
+    """Two ranks on two GPUs over CUDA IPC: ghost sets re-chosen every fourth evaluation with the evaluations in
+    between replayed as a CUDA graph, and re-chosen before every evaluation (each plan prepared one evaluation
+    ahead) with plain launches."""
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, halo_every, use_graph)) for r in range(2)]
     for p in procs:
         p.start()
     out = [q.get(timeout=300) for _ in procs]
