@@ -94,6 +94,9 @@ _SIGS = {
     "stafb_train_step_host": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _i, _vp, _vp],
     "stafb_train_step_host_begin": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _i, _vp, _i],
     "stafb_train_step_host_end": [_vp, _vp, _i, _vp],
+    "stafb_train_step_virial_host_begin": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _d, _d, _d, _d, _d, _i,
+                                           _vp, _i],
+    "stafb_train_step_virial_host_end": [_vp, _vp, _i, _vp],
     "stafb_adam_step_dev": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _d, _d, _d, _d, _vp, _d],
     "stafb_measure_fma_peak": [_i, _vp, _vp],
     "stafb_set_phase_timing": [_vp, _i],

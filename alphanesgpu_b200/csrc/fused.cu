@@ -265,8 +265,9 @@ __global__ void __launch_bounds__(256)
       const double tot = (double)pe * le + (double)pb * lb + (double)pf * lf + (double)pv * lv;
       losses[0] = tot;
       if (mirror) {
-        // results straight into the caller's mapped host memory: 4 losses, then the status word (read and cleared)
-        mirror[0] = tot; mirror[1] = le; mirror[2] = lb; mirror[3] = lf;
+        // results straight into the caller's mapped host memory: 4 losses, the status word (read and cleared),
+        // the virial loss
+        mirror[0] = tot; mirror[1] = le; mirror[2] = lb; mirror[3] = lf; mirror[5] = lv;
         reinterpret_cast<int*>(mirror + 4)[0] = atomicExch(status, 0);
         __threadfence_system();
       } else if (status_main != status) {
@@ -362,9 +363,11 @@ struct stafb_model {
   struct SlotKey {
     int nf, loss_kind;
     const void *theta, *emb, *grad, *stream;
-    double pe, pf, pb, bound;
+    double pe, pf, pb, bound, pv;
+    int with_v;
   } slot_key[3];
   double* mirror_next;  // mapped host memory the next training evaluation's k_loss writes its results to
+  void* vlab_d;         // device copy of the virial labels of a host-buffer step [max_batch][9]
   int slot_state[3];  // 0: nothing yet, 1: signature seen once (ran eagerly), 2: graph instantiated, -1: capture failed
   cudaGraphExec_t slot_exec[3];
   // Two more sets of neighbour rows (a context of their own for the search scratch + the compact rows), so that
@@ -527,10 +530,11 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   STAFB_CUDA_OK(cudaMalloc((void**)&m->epart, sizeof(double) * (size_t)c->max_batch * (LOSS_EB_MAX + 1)));
   STAFB_CUDA_OK(cudaMemset(m->epart, 0, sizeof(double) * (size_t)c->max_batch * (LOSS_EB_MAX + 1)));
   {
-    const size_t blk = es * (A * 6 + (size_t)c->max_batch * 7 + 8);
+    const size_t blk = es * (A * 6 + (size_t)c->max_batch * 16 + 8);  // pos | f_label | box | e_label | v_label
+    STAFB_CUDA_OK(cudaMalloc(&m->vlab_d, es * (size_t)c->max_batch * 9));
     for (int k = 0; k < 3; k++) {
       STAFB_CUDA_OK(cudaMallocHost((void**)&m->slot_in_h[k], blk));
-      STAFB_CUDA_OK(cudaMallocHost((void**)&m->slot_out_h[k], sizeof(double) * 5));
+      STAFB_CUDA_OK(cudaMallocHost((void**)&m->slot_out_h[k], sizeof(double) * 6));
       STAFB_CUDA_OK(cudaEventCreateWithFlags(&m->slot_done[k], cudaEventDisableTiming));
       m->slot_busy[k] = 0;
     }
@@ -542,7 +546,7 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
 extern "C" void stafb_model_destroy(stafb_model* m) {
   if (!m) return;
   void* ptrs[] = {m->rows, m->spar, m->af, m->nd, m->gradnet, m->gaf, m->acts, m->e_atom, m->force,
-                  m->flab, m->ebar, m->energy, m->losses_d, m->epart, m->vrow, m->wpack, m->wm};
+                  m->flab, m->ebar, m->energy, m->losses_d, m->epart, m->vrow, m->wpack, m->wm, m->vlab_d};
   for (void* p : ptrs) cudaFree(p);
   for (int k = 0; k < 3; k++) {
     cudaFreeHost(m->slot_in_h[k]);
@@ -887,7 +891,7 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
     mark();  // mlp_bwd
     if (losses_out != m->losses_d)
       STAFB_CUDA_OK(cudaMemcpyAsync(losses_out, m->losses_d, sizeof(double) * 4, cudaMemcpyDeviceToDevice, s));
-    if (v_label)  // fifth loss of the energy + force + virial training
+    if (v_label && losses_out != m->losses_d)  // fifth loss of the energy + force + virial training
       STAFB_CUDA_OK(cudaMemcpyAsync(losses_out + 4, m->losses_d + 5, sizeof(double), cudaMemcpyDeviceToDevice, s));
   }
   STAFB_CUDA_OK(cudaGetLastError());
@@ -1055,20 +1059,30 @@ extern "C" int stafb_descriptors_prefetch(stafb_ctx* c, stafb_model* m, void* st
   return STAFB_OK;
 }
 
-extern "C" int stafb_train_step_prefetched(stafb_ctx* c, stafb_model* m, void* stream, int slot, int nf,
-                                           const void* theta, const void* emb, const void* el, const void* fl,
-                                           double pe, double pf, double pb, double bound, int loss_kind,
-                                           double* losses_d, void* grad, void* energy, void* force) {
+// The step on the neighbour rows of `slot`; vl (device, [nf,9]) non-null adds the virial loss.
+static int step_prefetched(stafb_ctx* c, stafb_model* m, void* stream, int slot, int nf, const void* theta,
+                           const void* emb, const void* el, const void* fl, const void* vl, double pe, double pf,
+                           double pv, double pb, double bound, int loss_kind, double* losses_d, void* grad,
+                           void* energy, void* force) {
   if (!c || !m || slot < 0 || slot > 1 || !m->nl[slot].ctx) return STAFB_ERR_INVALID;
   cudaStream_t s = (cudaStream_t)stream;
   const stafb_model::NlSet* q = &m->nl[slot];
   if (c->dtype == STAFB_F32)
     return run_fused<float>(c, m, s, nullptr, nullptr, nf, (const float*)theta, (const float*)emb, 1, true,
                             (const float*)el, (const float*)fl, pe, pf, pb, bound, loss_kind, losses_d, (float*)grad,
-                            (float*)energy, (float*)force, nullptr, nullptr, q);
+                            (float*)energy, (float*)force, nullptr, nullptr, q, (const float*)vl, pv);
   return run_fused<double>(c, m, s, nullptr, nullptr, nf, (const double*)theta, (const double*)emb, 1, true,
                            (const double*)el, (const double*)fl, pe, pf, pb, bound, loss_kind, losses_d,
-                           (double*)grad, (double*)energy, (double*)force, nullptr, nullptr, q);
+                           (double*)grad, (double*)energy, (double*)force, nullptr, nullptr, q, (const double*)vl,
+                           pv);
+}
+
+extern "C" int stafb_train_step_prefetched(stafb_ctx* c, stafb_model* m, void* stream, int slot, int nf,
+                                           const void* theta, const void* emb, const void* el, const void* fl,
+                                           double pe, double pf, double pb, double bound, int loss_kind,
+                                           double* losses_d, void* grad, void* energy, void* force) {
+  return step_prefetched(c, m, stream, slot, nf, theta, emb, el, fl, nullptr, pe, pf, 0.0, pb, bound, loss_kind,
+                         losses_d, grad, energy, force);
 }
 
 extern "C" int stafb_train_step_host(stafb_ctx* c, stafb_model* m, void* stream, const void* pos_h,
@@ -1082,14 +1096,17 @@ extern "C" int stafb_train_step_host(stafb_ctx* c, stafb_model* m, void* stream,
 // prepares step k+1 while the GPU runs step k.
 static int host_step_begin(stafb_ctx* c, stafb_model* m, void* stream, const void* pos_h, const void* box_h, int nf,
                            const void* theta, const void* emb, const void* el_h, const void* fl_h, double pe,
-                           double pf, double pb, double bound, int loss_kind, void* grad, int slot) {
+                           double pf, double pb, double bound, int loss_kind, void* grad, int slot,
+                           const void* vl_h = nullptr, double pv = 0.0) {
   if (!c || !m || !pos_h || !box_h || !el_h || !fl_h || slot < 0 || slot > 2) return STAFB_ERR_INVALID;
   if (nf <= 0 || nf > c->max_batch) return STAFB_ERR_CAPACITY;
   if (m->slot_busy[slot]) return STAFB_ERR_INVALID;  // the previous step of this slot has not been collected
   cudaStream_t s = (cudaStream_t)stream;
   const size_t es = m->es, A = (size_t)nf * m->md.N;
   const size_t o_fl = es * A * 3, o_box = o_fl + es * A * 3, o_el = o_box + es * (size_t)nf * 6;
+  const size_t o_vl = o_el + es * (size_t)nf;
   char* ph = m->slot_in_h[slot];
+  if (vl_h) memcpy(ph + o_vl, vl_h, es * (size_t)nf * 9);
   memcpy(ph, pos_h, es * A * 3);
   memcpy(ph + o_fl, fl_h, es * A * 3);
   memcpy(ph + o_box, box_h, es * (size_t)nf * 6);
@@ -1113,10 +1130,18 @@ static int host_step_begin(stafb_ctx* c, stafb_model* m, void* stream, const voi
     return stafb_descriptors_prefetch(c, m, m->side, ph, ph + o_box, nf, slot);
   };
   auto enqueue = [&]() -> int {
+    // the virial labels are read by every block of the force-backward sweep: one small copy to the device
+    // instead of reads over PCIe (the other labels are read once, by the loss kernel and the preparation kernel)
+    if (vl_h &&
+        cudaMemcpyAsync(m->vlab_d, ph + o_vl, es * (size_t)nf * 9, cudaMemcpyHostToDevice, s) != cudaSuccess)
+      return STAFB_ERR_CUDA;
     m->mirror_next = oh;
     if (split)
-      return stafb_train_step_prefetched(c, m, stream, slot, nf, theta, emb, ph + o_el, ph + o_fl, pe, pf, pb, bound,
-                                         loss_kind, m->losses_d, grad, nullptr, nullptr);
+      return step_prefetched(c, m, stream, slot, nf, theta, emb, ph + o_el, ph + o_fl, vl_h ? m->vlab_d : nullptr, pe,
+                             pf, pv, pb, bound, loss_kind, m->losses_d, grad, nullptr, nullptr);
+    if (vl_h)
+      return stafb_train_step_virial(c, m, stream, ph, ph + o_box, nf, theta, emb, ph + o_el, ph + o_fl, m->vlab_d, pe,
+                                     pf, pv, pb, bound, loss_kind, m->losses_d, grad, nullptr, nullptr, nullptr);
     return stafb_train_step(c, m, stream, ph, ph + o_box, nf, theta, emb, ph + o_el, ph + o_fl, pe, pf, pb, bound,
                             loss_kind, m->losses_d, grad, nullptr, nullptr);
   };
@@ -1127,7 +1152,7 @@ static int host_step_begin(stafb_ctx* c, stafb_model* m, void* stream, const voi
   stafb_model::SlotKey key;
   memset(&key, 0, sizeof(key));
   key.nf = nf; key.loss_kind = loss_kind; key.theta = theta; key.emb = emb; key.grad = grad; key.stream = stream;
-  key.pe = pe; key.pf = pf; key.pb = pb; key.bound = bound;
+  key.pe = pe; key.pf = pf; key.pb = pb; key.bound = bound; key.pv = pv; key.with_v = vl_h != nullptr;
   const bool same = m->slot_state[slot] != 0 && memcmp(&key, &m->slot_key[slot], sizeof(key)) == 0;
   if (!same) {
     if (m->slot_exec[slot]) { cudaGraphExecDestroy(m->slot_exec[slot]); m->slot_exec[slot] = nullptr; }
@@ -1184,18 +1209,36 @@ extern "C" int stafb_train_step_host_begin(stafb_ctx* c, stafb_model* m, void* s
                          slot);
 }
 
-static int host_step_end(stafb_ctx* c, stafb_model* m, int slot, double* losses_h) {
+static int host_step_end(stafb_ctx* c, stafb_model* m, int slot, double* losses_h, bool with_v = false) {
   if (!c || !m || !losses_h || slot < 0 || slot > 2 || !m->slot_busy[slot]) return STAFB_ERR_INVALID;
   STAFB_CUDA_OK(cudaEventSynchronize(m->slot_done[slot]));
   m->slot_busy[slot] = 0;
   const double* oh = m->slot_out_h[slot];
   for (int q = 0; q < 4; q++) losses_h[q] = oh[q];
+  if (with_v) losses_h[4] = oh[5];
   return *reinterpret_cast<const int*>(oh + 4);
 }
 
 extern "C" int stafb_train_step_host_end(stafb_ctx* c, stafb_model* m, int slot, double* losses_h) {
   if (slot < 0 || slot > 1) return STAFB_ERR_INVALID;
   return host_step_end(c, m, slot, losses_h);
+}
+
+// The same pair for the energy + force + virial step: vl_h [nf,9] host virial labels; losses_h[5] = loss, loss_e,
+// loss_bound, loss_f, loss_v.
+extern "C" int stafb_train_step_virial_host_begin(stafb_ctx* c, stafb_model* m, void* stream, const void* pos_h,
+                                                  const void* box_h, int nf, const void* theta, const void* emb,
+                                                  const void* el_h, const void* fl_h, const void* vl_h, double pe,
+                                                  double pf, double pv, double pb, double bound, int loss_kind,
+                                                  void* grad, int slot) {
+  if (slot < 0 || slot > 1 || !vl_h) return STAFB_ERR_INVALID;
+  return host_step_begin(c, m, stream, pos_h, box_h, nf, theta, emb, el_h, fl_h, pe, pf, pb, bound, loss_kind, grad,
+                         slot, vl_h, pv);
+}
+
+extern "C" int stafb_train_step_virial_host_end(stafb_ctx* c, stafb_model* m, int slot, double* losses_h) {
+  if (slot < 0 || slot > 1) return STAFB_ERR_INVALID;
+  return host_step_end(c, m, slot, losses_h, true);
 }
 
 

@@ -217,6 +217,29 @@ class StafModel:
               "stafb_train_step_host_end")
         return out
 
+    def loss_and_grad_virial_host_begin(self, pos, box, e_label, f_label, v_label, slot, pv=1.0):
+        """Pipelined energy + force + virial evaluation with HOST numpy inputs (v_label [nf,9]); collect with
+        loss_and_grad_virial_host_end(slot)."""
+        dt = np.float32 if self.dtype == torch.float32 else np.float64
+        pos, box = np.ascontiguousarray(pos, dt), np.ascontiguousarray(box, dt)
+        e_label, f_label = np.ascontiguousarray(e_label, dt), np.ascontiguousarray(f_label, dt)
+        v_label = np.ascontiguousarray(v_label, dt).reshape(box.shape[0], 9)
+        vp = lambda a: a.ctypes.data_as(C.c_void_p)
+        check(_lib.lib().stafb_train_step_virial_host_begin(self.ctx.h, self.h, self.ctx.stream(), vp(pos), vp(box),
+                                                            box.shape[0], _p(self.theta), _p(self.emb), vp(e_label),
+                                                            vp(f_label), vp(v_label), self.pe, self.pf, float(pv),
+                                                            self.pb, self.alpha_bound, self.loss_kind, _p(self.grad),
+                                                            int(slot)),
+              "stafb_train_step_virial_host_begin")
+
+    def loss_and_grad_virial_host_end(self, slot):
+        """Waits for the step begun in `slot`; returns (loss, loss_e, loss_bound, loss_f, loss_v)."""
+        out = np.zeros(5, np.float64)
+        check(_lib.lib().stafb_train_step_virial_host_end(self.ctx.h, self.h, int(slot),
+                                                          out.ctypes.data_as(C.c_void_p)),
+              "stafb_train_step_virial_host_end")
+        return out
+
     def adam_update(self, lr, beta1=0.9, beta2=0.999, eps=1e-7, grad_scale=1.0):
         """Keras Adam (epsilon default 1e-7: STAF/optimizer_learning_rate_utility.py:64-68)."""
         self.step += 1

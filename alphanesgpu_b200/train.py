@@ -14,10 +14,10 @@ the reference only the net optimizer is applied and it updates every trained par
 frame buffers sharded idx[rank::world] and the learning rate NOT scaled by the world size
 (staf_train.py:131-146,458-463); `lcurve_notmean`-style rows "step loss_e loss_f loss_bound" and `lr_step.dat`.
 type_of_training: energy+force+virial (staf_train.py:291-294,372-382: train/virial.npy with 9 values per frame,
-loss_virial_prefactor, rows "step loss_e loss_f loss_v loss_bound") runs stafb_train_step_virial per batch.
+loss_virial_prefactor, rows "step loss_e loss_f loss_v loss_bound") runs the virial form of the step per batch.
 What is not: restart modes, validation passes, SavedModel export.
-Every device step is the C ABI (energy+force: pipelined stafb_train_step_host_begin/_end; with the virial: device
-copies + stafb_train_step_virial; then stafb_adam_step_dev or the peer exchange).
+Every device step is the C ABI (pipelined stafb_train_step_host_begin/_end, with the virial
+stafb_train_step_virial_host_begin/_end; then stafb_adam_step_dev or the peer exchange).
 """
 import math
 import os
@@ -248,7 +248,7 @@ def train(cfg, out_dir=".", data=None, max_steps=None, log=print):
     def collect(p):
         st, slot, lr = p
         if with_virial:
-            l = model.losses5.cpu().numpy()  # waits for the step
+            l = model.loss_and_grad_virial_host_end(slot)
         else:
             l = model.loss_and_grad_host_end(slot)
         if st % displ == 0:
@@ -282,9 +282,8 @@ def train(cfg, out_dir=".", data=None, max_steps=None, log=print):
                 if px is not None:
                     model.use_grad(px.grad(step & 1))
                 if with_virial:
-                    dv = lambda a: torch.as_tensor(np.ascontiguousarray(a)).to(dev, non_blocking=True)
-                    model.loss_and_grad_virial(dv(pos[sl].reshape(bs, 3 * N)), dv(box[sl]), dv(en[sl]), dv(fo[sl]),
-                                               dv(vi[sl]), pv=pv)
+                    model.loss_and_grad_virial_host_begin(pos[sl].reshape(bs, 3 * N), box[sl], en[sl], fo[sl], vi[sl],
+                                                          step & 1, pv=pv)
                 else:
                     model.loss_and_grad_host_begin(pos[sl].reshape(bs, 3 * N), box[sl], en[sl], fo[sl], step & 1)
                 if px is not None:
@@ -295,9 +294,6 @@ def train(cfg, out_dir=".", data=None, max_steps=None, log=print):
                 if pending is not None:
                     collect(pending)
                 pending = (step, step & 1, lr)
-                if with_virial:  # one set of loss words: read them before the next evaluation overwrites them
-                    collect(pending)
-                    pending = None
                 if chief and step % displ == 0:
                     log("Epoch %d step %d. Time to elaborate %d batch of %d frames is %.4f"
                         % (ep, step, displ, bs, time.time() - t0))

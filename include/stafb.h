@@ -459,6 +459,17 @@ int stafb_train_step_host_begin(stafb_ctx* ctx, stafb_model* m, void* stream, co
                                 double alpha_bound, int loss_kind, void* grad_d, int slot);
 int stafb_train_step_host_end(stafb_ctx* ctx, stafb_model* m, int slot, double* losses_h);
 
+/* The same pair for the energy + force + virial step (stafb_train_step_virial; full_train_e_f_v,
+ * STAF/staf_models/staf_model.py:313-384): v_label_h [nf,9] host virial labels (copied to the device by one small
+ * transfer, all other inputs are read in place); _end writes losses_h[5] = loss, loss_e, loss_bound, loss_f,
+ * loss_v.  The two pairs share the slots: a slot begun with one pair is collected with the same pair. */
+int stafb_train_step_virial_host_begin(stafb_ctx* ctx, stafb_model* m, void* stream, const void* positions_h,
+                                       const void* boxer_h, int nf, const void* theta_d, const void* emb_d,
+                                       const void* e_label_h, const void* f_label_h, const void* v_label_h,
+                                       double pe, double pf, double pv, double pb, double alpha_bound,
+                                       int loss_kind, void* grad_d, int slot);
+int stafb_train_step_virial_host_end(stafb_ctx* ctx, stafb_model* m, int slot, double* losses_h);
+
 /* ---- diagnostics ----------------------------------------------------------------------------
  * The entry points from here to the end of the header are measurement aids of this library (no reference
  * counterpart, not part of the operator surface): phase timers, a measured FMA peak, a launch counter. */

@@ -183,6 +183,17 @@ def test_train_step_with_the_virial_loss(oracle, frame0, name, seeds, loss, dtyp
         o = shape.offsets(t)
         for lo, hi in ((o["a2"], o["a3"]), (o["a3"], o["mu"]), (o["mu"], o["w"]), (o["w"], o["a2"] + o["size"])):
             assert rel_err(g[lo:hi], gr[lo:hi]) <= 2 * tol, (t, lo, hi)
+    # the pipelined host-buffer form, on a stream that can be captured: plain launches, capture, graph replay on
+    # each of the two slots
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for k in range(7):
+            m.grad.zero_()
+            m.loss_and_grad_virial_host_begin(pos, box, el, fl, vl, k & 1, pv=0.6)
+            lh = m.loss_and_grad_virial_host_end(k & 1)
+            assert np.allclose(lh, ref["losses"], rtol=tol * 20, atol=0), (k, lh)
+            assert rel_err(m.grad.cpu().numpy(), ref["grad"]) <= 2 * tol, k
+    torch.cuda.synchronize()
     # the plain evaluation afterwards is not affected by the virial state
     m.loss_and_grad(d(pos), d(box), d(el), d(fl))
     plain = oracle.energy_force_grad(CFG, shape.desc(), pos, box, shape.type_map, theta, emb, dtype, with_grad=True,
