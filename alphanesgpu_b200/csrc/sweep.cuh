@@ -403,6 +403,7 @@ __device__ __forceinline__ void pairs_force(const typename Vec4<T>::type* __rest
     const int sg = (npt + s - 1) / s, rounds = (no * s + 31) >> 5, cost = rounds * (sg + 2);
     if (cost < best) { best = cost; S = s; seg = sg; }
   }
+  constexpr int FORCE_UNROLL = sizeof(T) == 4 ? 2 : 1;  // two partners in flight where the registers allow it
   const int nseg = no * S;
   const T2 one2 = mk2(T(1), T(1));
   for (int base = 0; base < nseg; base += 32) {
@@ -427,6 +428,7 @@ __device__ __forceinline__ void pairs_force(const typename Vec4<T>::type* __rest
     T ax = T(0), ay = T(0), az = T(0), as = T(0);
     // this lane's partners [k0, k1); for one species the owner itself is skipped: partner kb >= ow is row kb + 1
     const int k1 = active ? ((k0 + seg < npt) ? k0 + seg : npt) : k0;
+#pragma unroll FORCE_UNROLL
     for (int kb = k0; kb < k1; kb++) {
       {
         const int k = op + kb + ((SAME && kb >= ow) ? 1 : 0);
