@@ -183,7 +183,8 @@ __device__ __forceinline__ void warp_dense_fwd(int in, int out, const LayerView<
 }
 
 // Xo[i][a] = sum_j D[j][a] W[i,j]  (and the same for a second cotangent D2 -> Xo2 when TWO), one warp, AW atoms;
-// a lane owns input i0+lane of every group of 32 and walks its weight row four columns at a time.
+// a lane owns input i0+lane of every group of 32 and walks its weight row four columns at a time (pointers that
+// advance by constants; summation order j = 0, 1, 2, ...).
 template <class T, int AW, bool TWO>
 __device__ __forceinline__ void warp_dense_bwd(int in, int out, const LayerView<T> lv, const T* __restrict__ D,
                                                T* __restrict__ Xo, const T* __restrict__ D2, T* __restrict__ Xo2,
@@ -192,38 +193,41 @@ __device__ __forceinline__ void warp_dense_bwd(int in, int out, const LayerView<
   for (int i0 = 0; i0 < in; i0 += 32) {
     const int i = i0 + lane;
     const T* wr = lv.W + (size_t)(i < in ? i : in - 1) * ld;  // a lane past the last input repeats the last row
+    const T* pd = D;
+    const T* pd2 = TWO ? D2 : D;
     T acc[AW], acc2[AW];
 #pragma unroll
     for (int a = 0; a < AW; a++) acc[a] = acc2[a] = T(0);
-    int j = 0;
 #pragma unroll 2
-    for (; j + 4 <= out; j += 4) {
+    for (int n = out >> 2; n > 0; n--) {
       T w[4];
-      ml_ld4(wr + j, w);
+      ml_ld4(wr, w);
 #pragma unroll
       for (int r = 0; r < 4; r++) {
         T d[AW];
-        RowIO<T, AW>::ld(D + (j + r) * AW, d);
+        RowIO<T, AW>::ld(pd + r * AW, d);
 #pragma unroll
         for (int a = 0; a < AW; a++) acc[a] += w[r] * d[a];
         if (TWO) {
-          RowIO<T, AW>::ld(D2 + (j + r) * AW, d);
+          RowIO<T, AW>::ld(pd2 + r * AW, d);
 #pragma unroll
           for (int a = 0; a < AW; a++) acc2[a] += w[r] * d[a];
         }
       }
+      wr += 4; pd += 4 * AW; pd2 += 4 * AW;
     }
-    for (; j < out; j++) {
-      const T w = wr[j];
+    for (int n = out & 3; n > 0; n--) {
+      const T w = wr[0];
       T d[AW];
-      RowIO<T, AW>::ld(D + j * AW, d);
+      RowIO<T, AW>::ld(pd, d);
 #pragma unroll
       for (int a = 0; a < AW; a++) acc[a] += w * d[a];
       if (TWO) {
-        RowIO<T, AW>::ld(D2 + j * AW, d);
+        RowIO<T, AW>::ld(pd2, d);
 #pragma unroll
         for (int a = 0; a < AW; a++) acc2[a] += w * d[a];
       }
+      wr++; pd += AW; pd2 += AW;
     }
     if (i < in) {
       RowIO<T, AW>::st(Xo + i * AW, acc);
