@@ -48,7 +48,7 @@ PUBLISHED_V100_FRAMES_PER_S = 10.9  # reference README.md:42-45 (V100, fp32, bat
 FLOPS_PER_TRIPLET_CHANNEL = 21 + 30 + 44
 FLOPS_PER_TRIPLET = 9 + 42 + 44
 # dram__bytes_read.sum + dram__bytes_write.sum per launch at batch 4 (one ncu capture; None: not captured)
-TRAFFIC_NCU_B4 = {"af_fwd": 6.852e6, "force": 7.182e6, "force_grad": 7.231e6, "mlp_fwd": 0.399e6, "mlp_bwd": 3.867e6}
+TRAFFIC_NCU_B4 = {"af_fwd": 6.852e6, "force": 7.196e6, "force_grad": 7.232e6, "mlp_fwd": 0.397e6, "mlp_bwd": 3.863e6}
 
 
 def make_batches(rank, n_batches, B, dtype, seed0=1100):
