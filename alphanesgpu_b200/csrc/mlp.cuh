@@ -133,6 +133,14 @@ __device__ __forceinline__ void ml_ld4(const double* p, double (&w)[4]) {
   w[0] = a.x; w[1] = a.y; w[2] = b.x; w[3] = b.y;
 }
 
+// four consecutive words of a gradient row in one atomic (fp32, 16-byte aligned address); fp64 has no such form
+__device__ __forceinline__ void ml_add4(float* p, float a, float b, float c, float d) {
+  atomicAdd(reinterpret_cast<float4*>(p), make_float4(a, b, c, d));
+}
+__device__ __forceinline__ void ml_add4(double* p, double a, double b, double c, double d) {
+  atomicAdd(p, a); atomicAdd(p + 1, b); atomicAdd(p + 2, c); atomicAdd(p + 3, d);
+}
+
 // Y[j][a] = act( b[j] + sum_i X[i][a] W[i,j] ), one warp, AW atoms; a lane owns outputs j0+lane and j0+32+lane
 // of every group of 64.  The caller separates this from the producer of X with __syncwarp().
 template <class T, int AW, bool TANH, bool BIAS>
@@ -344,8 +352,9 @@ __global__ void __launch_bounds__(ML_THREADS)
 // TensorFlow's autodiff does through grad_ene for the force loss (staf_model.py:191,225-228).
 // The kernel also contracts dL/dAF with the per-atom d(AF)/d(alpha) rows left by the AF sweep
 // (vrow), which yields the fingerprint part of dL/dalpha without another sweep over the triplets.
+// fp32 with up to 2 atoms per warp: three blocks per SM fit by shared memory, so the registers are capped for three
 template <class T, int AW, bool WG>
-__global__ void __launch_bounds__(ML_THREADS)
+__global__ void __launch_bounds__(ML_THREADS, (sizeof(T) == 4 && AW <= 2) ? 3 : 1)
     k_mlp_bwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ wpack, int wstride,
               const T* __restrict__ af, const T* __restrict__ acts, const T* __restrict__ ebar /*[nf]*/, const T* __restrict__ u /*[nf,N,Fmax]*/,
               const T* __restrict__ vrow /*[nf,N,nv] or null*/, int nv, T* __restrict__ gaf, T* __restrict__ grad,
@@ -490,11 +499,19 @@ __global__ void __launch_bounds__(ML_THREADS)
   // weight gradients of ALL layers in one pass: the 4 x 4 tiles (4 inputs x 4 outputs) of every layer are
   // numbered consecutively and dealt to the threads, so that the small layers do not leave most of the block
   // idle (rows past the end of a layer's last tile repeat its last row and are not written)
-  int tile_end[STAFB_MAX_DENSE];
+  // fp32, layer width a multiple of 4: the column tiles of a layer are shifted left by csh columns so that every
+  // tile row starts on a 16-byte boundary of the gradient array and goes out as ONE 4-wide atomic add (the first
+  // and the last tile of a row then hang over the edge and use scalar adds for the columns they have)
+  int tile_end[STAFB_MAX_DENSE], csh[STAFB_MAX_DENSE];
   {
     int tot = 0;
     for (int l = 0; l < STAFB_MAX_DENSE; l++) {
-      if (l < Lq) tot += ((md.in_of(t, l) + 3) >> 2) * ((md.width[l] + 3) >> 2);
+      csh[l] = 0;
+      if (l < Lq) {
+        if (sizeof(T) == 4 && (md.width[l] & 3) == 0)
+          csh[l] = (int)((reinterpret_cast<size_t>(gw + md.w_off(t, l)) >> 2) & 3);
+        tot += ((md.in_of(t, l) + 3) >> 2) * ((md.width[l] + csh[l] + 3) >> 2);
+      }
       tile_end[l] = tot;
     }
   }
@@ -502,18 +519,18 @@ __global__ void __launch_bounds__(ML_THREADS)
     int l = 0;
 #pragma unroll
     for (int q = 0; q < STAFB_MAX_DENSE - 1; q++) l += (tile >= tile_end[q]) ? 1 : 0;
-    int tbeg = 0;
+    int tbeg = 0, sh = csh[0];
 #pragma unroll
     for (int q = 0; q < STAFB_MAX_DENSE - 1; q++)
-      if (q < l) tbeg = tile_end[q];
+      if (q < l) { tbeg = tile_end[q]; sh = csh[q + 1]; }
     const int in = md.in_of(t, l), out = md.width[l];
     const int oin = (l == 0) ? oX : oH + md.h_off(l - 1) * AW;
     const int odi = (l == 0) ? oV : oHD + md.h_off(l - 1) * AW;
     const int oq = oDQ + md.h_off(l) * AW, op = oDP + md.h_off(l) * AW;
     const int woff = md.w_off(t, l);
-    const int nj4 = (out + 3) >> 2;
+    const int nj4 = (out + sh + 3) >> 2;
     const int lt = tile - tbeg, itl = lt / nj4, jt = lt - itl * nj4;
-    const int j0 = jt << 2, i0 = itl << 2;
+    const int j0 = (jt << 2) - sh, i0 = itl << 2;
     T g[16];
 #pragma unroll
     for (int q = 0; q < 16; q++) g[q] = T(0);
@@ -521,7 +538,7 @@ __global__ void __launch_bounds__(ML_THREADS)
 #pragma unroll
     for (int r = 0; r < 4; r++) {
       ir[r] = (i0 + r < in ? i0 + r : in - 1) * AW;
-      jr[r] = (j0 + r < out ? j0 + r : out - 1) * AW;
+      jr[r] = (j0 + r < 0 ? 0 : (j0 + r < out ? j0 + r : out - 1)) * AW;
     }
 #pragma unroll 2
     for (int wv = 0; wv < ML_WARPS; wv++) {
@@ -546,11 +563,19 @@ __global__ void __launch_bounds__(ML_THREADS)
           }
       }
     }
+    const bool whole = sizeof(T) == 4 && (out & 3) == 0 && j0 >= 0 && j0 + 4 <= out;  // aligned by construction
 #pragma unroll
-    for (int r = 0; r < 4; r++)
+    for (int r = 0; r < 4; r++) {
+      if (i0 + r >= in) continue;
+      T* dst = gw + woff + (i0 + r) * out + j0;
+      if (whole) {
+        ml_add4(dst, g[4 * r], g[4 * r + 1], g[4 * r + 2], g[4 * r + 3]);
+      } else {
 #pragma unroll
-      for (int c = 0; c < 4; c++)
-        if (i0 + r < in && j0 + c < out) atomicAdd(gw + woff + (i0 + r) * out + j0 + c, g[4 * r + c]);
+        for (int c = 0; c < 4; c++)
+          if (j0 + c >= 0 && j0 + c < out) atomicAdd(dst + c, g[4 * r + c]);
+      }
+    }
   }
   // bias gradients: the outputs of all layers in one pass (the DQ rows of the layers lie back to back)
   for (int jj = threadIdx.x; jj < Hs; jj += ML_THREADS) {
