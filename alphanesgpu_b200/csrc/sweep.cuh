@@ -97,7 +97,7 @@ enum { MODE_AF = 0, MODE_FORCE = 1, MODE_FGRAD = 2, MODE_AFV = 4 };
 template <int MODE, size_t ES> struct SweepMinBlocks { static constexpr int value = 20; };  // ptxas: 96 registers -> 21 resident
 template <> struct SweepMinBlocks<MODE_AF, 8> { static constexpr int value = 16; };          // <= 128
 template <> struct SweepMinBlocks<MODE_AFV, 8> { static constexpr int value = 12; };         // <= 168
-template <> struct SweepMinBlocks<MODE_FORCE, 8> { static constexpr int value = 12; };
+template <> struct SweepMinBlocks<MODE_FORCE, 8> { static constexpr int value = 8; };        // no spills at <= 255
 template <> struct SweepMinBlocks<MODE_FGRAD, 8> { static constexpr int value = 8; };        // <= 255
 
 // ---- per-species parameter block (global memory, written by k_prep at the start of every evaluation; a sweep
