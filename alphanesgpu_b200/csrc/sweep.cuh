@@ -93,8 +93,10 @@ enum { MODE_AF = 0, MODE_FORCE = 1, MODE_FGRAD = 2, MODE_AFV = 4 };
 
 // Resident one-warp blocks per SM the kernels are compiled for (caps the registers per thread at
 // 65536 / (32 * blocks)); the hardware holds at most 32 blocks per SM.
-// A batch of 4 x 768 atoms is 20.8 blocks per SM: 21 resident blocks (<= 96 registers) keep it in one wave.
-template <int MODE, size_t ES> struct SweepMinBlocks { static constexpr int value = 20; };  // ptxas: 96 registers -> 21 resident
+// fp32: 96 registers, five warps per scheduler = 20 blocks per SM (the shared memory of a block allows the same).  A
+// batch of 4 x 768 atoms is 20.8 blocks per SM; the few that do not fit start as the first ones retire.  Capping at
+// 80 registers for 24 blocks was measured: spills, and no gain in the chained step.
+template <int MODE, size_t ES> struct SweepMinBlocks { static constexpr int value = 20; };
 template <> struct SweepMinBlocks<MODE_AF, 8> { static constexpr int value = 16; };          // <= 128
 template <> struct SweepMinBlocks<MODE_AFV, 8> { static constexpr int value = 12; };         // <= 168
 template <> struct SweepMinBlocks<MODE_FORCE, 8> { static constexpr int value = 8; };        // no spills at <= 255
