@@ -209,11 +209,12 @@ __global__ void __launch_bounds__(256)
       }
     }
     if (!needs_pred && eb == 1) chain_wait();
-    if (virial_out && threadIdx.x < 9) virial_out[blk * 9 + threadIdx.x] = (T)vacc[blk * 9 + threadIdx.x];
+    const double wv = ((virial_out || v_label) && threadIdx.x < 9) ? vir_total(vacc, blk, threadIdx.x) : 0.0;
+    if (virial_out && threadIdx.x < 9) virial_out[blk * 9 + threadIdx.x] = (T)wv;
     if (v_label && threadIdx.x < 9) {
       // virial term of the loss (staf_model.py:358-365): mean over [nf, 9]; its cotangent is formed by the
       // backward sweep of the forces itself.  losses[5] (losses[4] is the done-counter).
-      const T e = (T)vacc[blk * 9 + threadIdx.x] - v_label[blk * 9 + threadIdx.x];
+      const T e = (T)wv - v_label[blk * 9 + threadIdx.x];
       atomicAdd(losses + 5, (double)(loss_kind == 0 ? huber(e) : e * e) / (9.0 * nf));
     }
     if (threadIdx.x == 0) {
@@ -351,7 +352,7 @@ struct stafb_model {
   size_t mma_fwd_smem, mma_bwd_smem;
   double* epart;     // partial energy sums of k_loss: [nf][eb]; from [max_batch][LOSS_EB_MAX] on: one arrival counter per frame
   double* losses_d;  // [0..4] the four losses + the done-counter of k_loss; [8 + b] sum of the atomic energies of
-                     // frame b (accumulated by the MLP kernel); [8 + max_batch + 9*b + c] virial accumulators
+                     // frame b (accumulated by the MLP kernel); from [8 + max_batch] on the virial accumulators [b][9][VIR_SLOTS]
   // staging for the *_host entry points
   // two pipelined slots for stafb_train_step_host_begin/_end: pinned input block (pos | f_label | box | e_label),
   // pinned results (4 losses + status) and the event that marks the slot's step complete
@@ -526,7 +527,8 @@ extern "C" int stafb_model_create(stafb_ctx* c, const int* sd, stafb_model** out
   STAFB_CUDA_OK(cudaMalloc(&m->flab, es * A * 3));  // device copy of the force labels (k_prep)
   STAFB_CUDA_OK(cudaMalloc(&m->ebar, es * c->max_batch));
   STAFB_CUDA_OK(cudaMalloc(&m->energy, es * c->max_batch));
-  STAFB_CUDA_OK(cudaMalloc((void**)&m->losses_d, sizeof(double) * (8 + 10 * (size_t)c->max_batch)));
+  // 8 loss words, a counter per frame, the virial accumulators
+  STAFB_CUDA_OK(cudaMalloc((void**)&m->losses_d, sizeof(double) * (8 + (1 + 9 * VIR_SLOTS) * (size_t)c->max_batch)));
   STAFB_CUDA_OK(cudaMalloc((void**)&m->epart, sizeof(double) * (size_t)c->max_batch * (LOSS_EB_MAX + 1)));
   STAFB_CUDA_OK(cudaMemset(m->epart, 0, sizeof(double) * (size_t)c->max_batch * (LOSS_EB_MAX + 1)));
   {
@@ -830,7 +832,8 @@ static int run_fused(stafb_ctx* c, stafb_model* m, cudaStream_t s, const T* pos,
       k_prep<T>, 64, 256, 0, s, d, theta, emb, (T*)m->wpack, m->wstride, m->spar, m->sl.total, m->sl, (void*)force,
       sizeof(T) * (size_t)nf * 3 * nall,
       train ? (void*)grad : (void*)nullptr, train ? sizeof(T) * (size_t)m->n_params : (size_t)0, (void*)m->losses_d,
-      sizeof(double) * ((virial_out || v_label) ? 8 + 10 * (size_t)c->max_batch : 8 + (size_t)c->max_batch),
+      sizeof(double) * ((virial_out || v_label) ? 8 + (1 + 9 * VIR_SLOTS) * (size_t)c->max_batch
+                                                : 8 + (size_t)c->max_batch),
       train ? f_label : (const T*)nullptr, (T*)m->flab, train ? (size_t)nf * 3 * N : (size_t)0,
       m->mma ? (T*)m->wm : (T*)nullptr, m->wm_stride));
   c->launches++;

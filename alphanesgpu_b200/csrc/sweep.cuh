@@ -180,6 +180,18 @@ __device__ __forceinline__ void spar_fill_radial(const ModelDev& md, const SparL
   rp[0] = al * Ex<T>::scale(); rp[1] = al; rp[2] = emb[md.off_emb[t] + idx]; rp[3] = T(0);
 }
 
+// The virial of a frame is accumulated by every centre of the frame: 9 words would take one atomic add per atom
+// each (24,576 on one address for a large box), so every component has VIR_SLOTS words, a centre adds to slot
+// (its index mod VIR_SLOTS) and the readers sum the slots.  Layout [frame][9][VIR_SLOTS] doubles.
+constexpr int VIR_SLOTS = 32;
+__device__ __forceinline__ double vir_total(const double* __restrict__ vacc, int frame, int q) {
+  const double* p = vacc + ((size_t)frame * 9 + q) * VIR_SLOTS;
+  double w = 0.0;
+#pragma unroll 8
+  for (int s = 0; s < VIR_SLOTS; s++) w += p[s];
+  return w;
+}
+
 template <class T>
 struct SweepArgs {
   const unsigned char* rows;  // [nf, N] neighbour records
@@ -197,8 +209,8 @@ struct SweepArgs {
   T* grad;           // FGRAD: flat parameter gradient (accumulated)
   T* vout;           // AFV: d(AF)/d(alpha) rows [nf,N,nv] in the accumulator layout (alpha2b[nt,Frmax] | alpha3b[C,3*Famax])
   int nv;
-  double* vir;       // FORCE with VIR: virial accumulators [nf,9]
-  const double* vacc;  // FGRAD with a virial loss: the virials [nf,9] the force sweep accumulated, their labels and
+  double* vir;       // FORCE with VIR: virial accumulators [nf,9,VIR_SLOTS]
+  const double* vacc;  // FGRAD with a virial loss: the accumulators the force sweep filled, the labels [nf,9] and
   const T* vlab;       //        the loss's scale: dL/dW = vscale * L'(W - label)
   T vscale;
   int* status;
@@ -546,9 +558,18 @@ __global__ void __launch_bounds__(32, SweepMinBlocks<MODE, sizeof(T)>::value)
     fo_g = a.force + (size_t)b * a.nall * 3;
     fl_g = a.flab + (size_t)b * a.nall * 3;
     fbx = fbar_of(i * 3); fby = fbar_of(i * 3 + 1); fbz = fbar_of(i * 3 + 2);
-    if (a.vacc && lane < 9) {
-      const T e = (T)a.vacc[b * 9 + lane] - a.vlab[b * 9 + lane];
-      wbs[lane] = a.vscale * (hub ? (e > T(1) ? T(1) : (e < T(-1) ? T(-1) : e)) : T(2) * e);
+    if (a.vacc) {
+      // lane = slot: nine coalesced loads, nine warp sums
+      double w = 0.0;
+#pragma unroll
+      for (int q = 0; q < 9; q++) {
+        const double v = warp_sum(a.vacc[((size_t)b * 9 + q) * VIR_SLOTS + lane]);
+        if (lane == q) w = v;
+      }
+      if (lane < 9) {
+        const T e = (T)w - a.vlab[b * 9 + lane];
+        wbs[lane] = a.vscale * (hub ? (e > T(1) ? T(1) : (e < T(-1) ? T(-1) : e)) : T(2) * e);
+      }
     }
   }
   if (!mbar_wait(bar, 0)) {
@@ -822,9 +843,10 @@ __global__ void __launch_bounds__(32, SweepMinBlocks<MODE, sizeof(T)>::value)
         }
         w0 = warp_sum(w0); w1 = warp_sum(w1); w2 = warp_sum(w2);
         if (lane == 0) {
-          atomicAdd(a.vir + (size_t)b * 9 + c * 3 + 0, (double)w0);
-          atomicAdd(a.vir + (size_t)b * 9 + c * 3 + 1, (double)w1);
-          atomicAdd(a.vir + (size_t)b * 9 + c * 3 + 2, (double)w2);
+          double* vs = a.vir + ((size_t)b * 9 + c * 3) * VIR_SLOTS + (i & (VIR_SLOTS - 1));
+          atomicAdd(vs, (double)w0);
+          atomicAdd(vs + VIR_SLOTS, (double)w1);
+          atomicAdd(vs + 2 * VIR_SLOTS, (double)w2);
         }
       }
     }
