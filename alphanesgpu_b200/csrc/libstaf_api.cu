@@ -37,10 +37,19 @@ struct StafModel {
   // per-call staging: one pinned host block and one device block with the same layout
   //   in : pos[3*cap] | box[6] | type_map[cap] | howmany[cap] | with[cap*nr]
   //   out: force[3*cap] | energy[1] | virial[9]
+  // in the computing precision and in slot order.  The caller's double arrays travel as they are (xin: x[3*nall] |
+  // box[6]; fout: f[3*nall] | energy | virial[9], caller order) and two small kernels convert and permute on the
+  // device, so the host only copies into and out of pinned memory.
   char *in_h, *in_d, *out_h, *out_d;
+  double *xin_h, *xin_d, *fout_h, *fout_d;
+  int* slot_d;  // to_slot on the device
   size_t in_bytes, out_bytes;
   cudaStream_t stream;
   std::vector<int> to_slot;
+  // the species array of the previous call: while it repeats (every step of an MD run between re-neighbourings),
+  // counting, validation, the slot map and its upload are skipped
+  std::vector<int> type_prev, tipos_prev;
+  int type_prev_null, nlocal_prev;
   // the device work of one call (copy in, kernels, copy out) captured as a CUDA graph; replayed while the call's
   // shape (atom counts per species, ghosts, list or no list) stays the same, as it does between the
   // re-neighbouring steps of an MD run
@@ -124,12 +133,18 @@ static void release_device(StafModel* m) {
   if (m->ctx) stafb_destroy(m->ctx);
   m->model = nullptr;
   m->ctx = nullptr;
-  void* dv[] = {m->theta_d, m->emb_d, m->in_d, m->out_d};
+  void* dv[] = {m->theta_d, m->emb_d, m->in_d, m->out_d, m->xin_d, m->fout_d, m->slot_d};
   for (void* q : dv) if (q) cudaFree(q);
   if (m->in_h) cudaFreeHost(m->in_h);
   if (m->out_h) cudaFreeHost(m->out_h);
+  if (m->xin_h) cudaFreeHost(m->xin_h);
+  if (m->fout_h) cudaFreeHost(m->fout_h);
   m->theta_d = m->emb_d = nullptr;
   m->in_d = m->out_d = m->in_h = m->out_h = nullptr;
+  m->xin_h = m->xin_d = m->fout_h = m->fout_d = nullptr;
+  m->slot_d = nullptr;
+  m->type_prev.clear();
+  m->nlocal_prev = -1;
   m->cap_n = 0;
   if (m->gexec) cudaGraphExecDestroy(m->gexec);
   m->gexec = nullptr;
@@ -145,6 +160,10 @@ extern "C" StafModel* staf_load(const char* model_dir, const StafOptions* opt) {
   m->ctx = nullptr; m->model = nullptr; m->cap_n = 0;
   m->theta_d = m->emb_d = nullptr;
   m->in_d = m->out_d = m->in_h = m->out_h = nullptr;
+  m->xin_h = m->xin_d = m->fout_h = m->fout_d = nullptr;
+  m->slot_d = nullptr;
+  m->nlocal_prev = -1;
+  m->type_prev_null = 0;
   m->stream = nullptr;
   m->gexec = nullptr;
   m->gstate = 0;
@@ -262,7 +281,12 @@ static int ensure_device(StafModel* m, int nall, const std::vector<int>& tipos) 
         cudaMalloc((void**)&m->in_d, L.in_total) != cudaSuccess ||
         cudaMalloc((void**)&m->out_d, L.out_total) != cudaSuccess ||
         cudaMallocHost((void**)&m->in_h, L.in_total) != cudaSuccess ||
-        cudaMallocHost((void**)&m->out_h, L.out_total) != cudaSuccess)
+        cudaMallocHost((void**)&m->out_h, L.out_total) != cudaSuccess ||
+        cudaMalloc((void**)&m->xin_d, sizeof(double) * (3 * (size_t)cap + 8)) != cudaSuccess ||
+        cudaMalloc((void**)&m->fout_d, sizeof(double) * (3 * (size_t)cap + 16)) != cudaSuccess ||
+        cudaMalloc((void**)&m->slot_d, sizeof(int) * (size_t)cap) != cudaSuccess ||
+        cudaMallocHost((void**)&m->xin_h, sizeof(double) * (3 * (size_t)cap + 8)) != cudaSuccess ||
+        cudaMallocHost((void**)&m->fout_h, sizeof(double) * (3 * (size_t)cap + 16)) != cudaSuccess)
       return -1;
     if (!m->stream && cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess) return -1;
     if (es == 8) { upload<double>(m->theta_d, m->theta); upload<double>(m->emb_d, m->emb); }
@@ -277,6 +301,29 @@ static int ensure_device(StafModel* m, int nall, const std::vector<int>& tipos) 
   return stafb_model_set_counts(m->model, tipos.data()) == STAFB_OK ? 0 : -1;
 }
 
+// Caller order, double -> slot order, computing precision (positions and box), and back (forces, energy, virial).
+template <class T>
+__global__ void k_stage_in(int nall, const double* __restrict__ xin, const int* __restrict__ slot, T* __restrict__ pos,
+                           T* __restrict__ box) {
+  const int q = blockIdx.x * blockDim.x + threadIdx.x;
+  if (q < 3 * nall) {
+    const int i = q / 3, c = q - 3 * i;
+    pos[3 * (size_t)slot[i] + c] = (T)xin[q];
+  }
+  if (q < 6) box[q] = (T)xin[3 * (size_t)nall + q];
+}
+template <class T>
+__global__ void k_stage_out(int nall, const T* __restrict__ force, const T* __restrict__ energy,
+                            const T* __restrict__ virial, const int* __restrict__ slot, double* __restrict__ fout) {
+  const int q = blockIdx.x * blockDim.x + threadIdx.x;
+  if (q < 3 * nall) {
+    const int i = q / 3, c = q - 3 * i;
+    fout[q] = (double)force[3 * (size_t)slot[i] + c];
+  }
+  if (q == 0) fout[3 * (size_t)nall] = (double)energy[0];
+  if (q < 9) fout[3 * (size_t)nall + 1 + q] = (double)virial[q];
+}
+
 // Shared body of staf_compute and staf_compute_domain.  Slots: owned atoms type-sorted in
 // [0, nlocal), ghosts appended in the caller's order (libstaf/src/staf_api.cpp:249-294).
 template <class T>
@@ -285,36 +332,54 @@ static int compute_impl(StafModel* m, int nlocal, int nghost, const double* x, c
                         double* f, double* virial) {
   const int nt = m->nt, nr = m->nr;
   const int nall = use_ghosts ? nlocal + (nghost > 0 ? nghost : 0) : nlocal;
-  std::vector<int> tipos(nt, 0), cursor(nt, 0);
-  for (int i = 0; i < nlocal; i++) {
-    const int sp = type ? type[i] : 0;
-    if (sp < 0 || sp >= nt) { fprintf(stderr, "staf_compute: unsupported type %d at atom %d\n", sp, i); return -8; }
-    tipos[sp]++;
+  const bool same_types = m->ctx && m->nlocal_prev == nlocal && (int)m->to_slot.size() == nall &&
+                          m->type_prev_null == (type == nullptr) &&
+                          (!type || memcmp(type, m->type_prev.data(), sizeof(int) * (size_t)nall) == 0);
+  std::vector<int> tipos(nt, 0);
+  if (same_types) {
+    tipos = m->tipos_prev;
+  } else {
+    for (int i = 0; i < nall; i++) {
+      const int sp = type ? type[i] : 0;
+      if (sp < 0 || sp >= nt) { fprintf(stderr, "staf_compute: unsupported type %d at atom %d\n", sp, i); return -8; }
+      if (i < nlocal) tipos[sp]++;
+    }
   }
-  for (int i = nlocal; i < nall; i++) {
-    const int sp = type ? type[i] : 0;
-    if (sp < 0 || sp >= nt) { fprintf(stderr, "staf_compute: unsupported type %d at atom %d\n", sp, i); return -8; }
-  }
-  for (int t = 1; t < nt; t++) cursor[t] = cursor[t - 1] + tipos[t - 1];
+  const int cap_before = m->cap_n;
   if (ensure_device(m, nall, tipos) != 0) return -1;
+  const bool remap = !same_types || m->cap_n != cap_before;  // new buffers are empty
   const StageLayout L = stage_layout(sizeof(T), (size_t)m->cap_n, (size_t)nr);
-  T* pos_h = reinterpret_cast<T*>(m->in_h + L.pos);
-  T* box_h = reinterpret_cast<T*>(m->in_h + L.box);
   int* tmap_h = reinterpret_cast<int*>(m->in_h + L.tmap);
   int* how_h = reinterpret_cast<int*>(m->in_h + L.how);
   int* with_h = reinterpret_cast<int*>(m->in_h + L.with);
-  m->to_slot.resize(nall);
-  for (int i = 0; i < nall; i++) {
-    const int sp = type ? type[i] : 0;
-    const int slot = i < nlocal ? cursor[sp]++ : i;
-    m->to_slot[i] = slot;
-    tmap_h[slot] = sp;
-    pos_h[3 * (size_t)slot + 0] = (T)x[3 * (size_t)i + 0];
-    pos_h[3 * (size_t)slot + 1] = (T)x[3 * (size_t)i + 1];
-    pos_h[3 * (size_t)slot + 2] = (T)x[3 * (size_t)i + 2];
+  cudaStream_t s = m->stream;
+  if (remap) {
+    std::vector<int> cursor(nt, 0);
+    for (int t = 1; t < nt; t++) cursor[t] = cursor[t - 1] + tipos[t - 1];
+    m->to_slot.resize(nall);
+    for (int i = 0; i < nall; i++) {
+      const int sp = type ? type[i] : 0;
+      const int slot = i < nlocal ? cursor[sp]++ : i;
+      m->to_slot[i] = slot;
+      tmap_h[slot] = sp;
+    }
+    // to_slot itself is pageable: stage it behind the type map in the pinned block (the list area is rewritten
+    // after this copy has been enqueued only when a list is given, and then it is ordered behind it on the stream)
+    if (cudaMemcpyAsync(m->in_d + L.tmap, tmap_h, sizeof(int) * (size_t)nall, cudaMemcpyHostToDevice, s) !=
+            cudaSuccess ||
+        cudaMemcpyAsync(m->slot_d, m->to_slot.data(), sizeof(int) * (size_t)nall, cudaMemcpyHostToDevice, s) !=
+            cudaSuccess ||
+        cudaStreamSynchronize(s) != cudaSuccess)
+      return -14;
+    m->type_prev_null = type == nullptr;
+    if (type) m->type_prev.assign(type, type + nall);
+    else m->type_prev.clear();
+    m->tipos_prev = tipos;
+    m->nlocal_prev = nlocal;
   }
-  for (int a = 0; a < 6; a++) box_h[a] = (T)box[a];
-  size_t in_used = L.how;  // pos | box | type_map are contiguous from 0
+  memcpy(m->xin_h, x, sizeof(double) * 3 * (size_t)nall);
+  for (int a = 0; a < 6; a++) m->xin_h[3 * (size_t)nall + a] = box[a];
+  size_t list_bytes = 0;
   if (howmany) {
     // caller's rows -> slot order and slot indices (staf_api.cpp:304-347)
     for (int i = 0; i < nlocal; i++) {
@@ -334,23 +399,35 @@ static int compute_impl(StafModel* m, int nlocal, int nghost, const double* x, c
         row[k] = m->to_slot[j];
       }
     }
-    in_used = L.with + 4 * (size_t)nlocal * nr;
+    list_bytes = L.with + 4 * (size_t)nlocal * nr - L.how;
   }
-  cudaStream_t s = m->stream;
+  const int nb = (3 * nall + 255) / 256;
   auto enqueue = [&]() -> int {
-    if (cudaMemcpyAsync(m->in_d, m->in_h, in_used, cudaMemcpyHostToDevice, s) != cudaSuccess) return -14;
+    if (cudaMemcpyAsync(m->xin_d, m->xin_h, sizeof(double) * (3 * (size_t)nall + 6), cudaMemcpyHostToDevice, s) !=
+        cudaSuccess)
+      return -14;
+    if (list_bytes &&
+        cudaMemcpyAsync(m->in_d + L.how, m->in_h + L.how, list_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
+      return -14;
+    k_stage_in<T><<<nb, 256, 0, s>>>(nall, m->xin_d, m->slot_d, reinterpret_cast<T*>(m->in_d + L.pos),
+                                     reinterpret_cast<T*>(m->in_d + L.box));
     const int rc = stafb_energy_force_domain(
         m->ctx, m->model, s, m->in_d + L.pos, m->in_d + L.box, nall, reinterpret_cast<const int*>(m->in_d + L.tmap),
         howmany ? reinterpret_cast<const int*>(m->in_d + L.how) : nullptr,
         howmany ? reinterpret_cast<const int*>(m->in_d + L.with) : nullptr, m->theta_d, m->emb_d, m->out_d + L.energy,
         m->out_d + L.force, m->out_d + L.virial);
     if (rc != STAFB_OK) return rc == STAFB_ERR_CUDA ? -14 : -13;
-    if (cudaMemcpyAsync(m->out_h, m->out_d, L.out_total, cudaMemcpyDeviceToHost, s) != cudaSuccess) return -14;
+    k_stage_out<T><<<nb, 256, 0, s>>>(nall, reinterpret_cast<const T*>(m->out_d + L.force),
+                                      reinterpret_cast<const T*>(m->out_d + L.energy),
+                                      reinterpret_cast<const T*>(m->out_d + L.virial), m->slot_d, m->fout_d);
+    if (cudaMemcpyAsync(m->fout_h, m->fout_d, sizeof(double) * (3 * (size_t)nall + 10), cudaMemcpyDeviceToHost, s) !=
+        cudaSuccess)
+      return -14;
     return 0;
   };
   StafModel::GraphKey key;
   memset(&key, 0, sizeof(key));
-  key.nall = nall; key.nlocal = nlocal; key.has_list = howmany != nullptr; key.in_used = in_used;
+  key.nall = nall; key.nlocal = nlocal; key.has_list = howmany != nullptr; key.in_used = list_bytes;
   for (int t = 0; t < nt; t++) key.tipos[t] = tipos[t];
   if (m->gstate == 0 || memcmp(&key, &m->gkey, sizeof(key)) != 0) {
     if (m->gexec) { cudaGraphExecDestroy(m->gexec); m->gexec = nullptr; }
@@ -391,22 +468,15 @@ static int compute_impl(StafModel* m, int nlocal, int nghost, const double* x, c
   if (st == STAFB_ERR_BAD_BOX) return -7;
   if (st == STAFB_ERR_CUDA) return -14;
   if (st != STAFB_OK && st != STAFB_ERR_NONFINITE) return -13;
-  const T* f_h = reinterpret_cast<const T*>(m->out_h + L.force);
-  const double energy = (double)*reinterpret_cast<const T*>(m->out_h + L.energy);
-  const T* v_h = reinterpret_cast<const T*>(m->out_h + L.virial);
+  const double* o = m->fout_h + 3 * (size_t)nall;
+  const double energy = o[0];
   if (!isfinite(energy))  // as staf_api.cpp:378-381
     fprintf(stderr, "staf_compute: non-finite energy=%g nlocal=%d nghost=%d\n", energy, nlocal, nghost);
   if (e_rank) *e_rank = energy;
-  if (f)
-    for (int i = 0; i < nall; i++) {
-      const size_t sl = (size_t)m->to_slot[i];
-      f[3 * (size_t)i + 0] = (double)f_h[3 * sl + 0];
-      f[3 * (size_t)i + 1] = (double)f_h[3 * sl + 1];
-      f[3 * (size_t)i + 2] = (double)f_h[3 * sl + 2];
-    }
+  if (f) memcpy(f, m->fout_h, sizeof(double) * 3 * (size_t)nall);
   if (virial) {
     // diagonal only, like the reference (staf_api.cpp:398-403)
-    virial[0] = (double)v_h[0]; virial[1] = (double)v_h[4]; virial[2] = (double)v_h[8];
+    virial[0] = o[1]; virial[1] = o[5]; virial[2] = o[9];
     virial[3] = virial[4] = virial[5] = 0.0;
   }
   return 0;

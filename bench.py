@@ -542,7 +542,9 @@ def md_record(torch, dist, args, rank, world, local, dev, K):
             rc = lib.staf_compute(h, N, 0, x64.ctypes.data, b64.ctypes.data, types.ctypes.data, None, None, 0,
                                   C.byref(e64), f64.ctypes.data, vir.ctypes.data)
             assert rc == 0, rc
-        h2d, d2h = 4 * (3 * N + 6 + N), 4 * (3 * N + 1 + 9)
+        # the caller's double arrays travel as they are (the library converts and permutes on the device); the
+        # species array is uploaded only when it changes
+        h2d, d2h = 8 * (3 * N + 6), 8 * (3 * N + 1 + 9)
     else:
         def e2e_step():
             dom.pos.copy_(pin_x, non_blocking=True)
