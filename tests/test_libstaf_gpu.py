@@ -63,6 +63,16 @@ def test_staf_compute_frame0(lib, oracle, frame0, precision, tol):
         # recorded by the reference for this frame: E = -102.25880432 (TF) / -102.25872 (libstaf)
         # (test/test-lammps-STAF-inference-STAF-comp/results/frames.csv:2)
         assert abs(e - (-102.25880432)) < 1.2e-4
+    # the same species array again (the cached slot map and, from the third call on, the replayed graph), moved
+    # atoms; then the same atoms in another caller order with the same species counts (the map is re-made)
+    for k in range(3):
+        rc, e_k, f_k, _ = _compute(lib, m, x, frame0["box"][0], types)
+        assert rc == 0 and abs(e_k - e) <= tol * abs(e) and rel_err(f_k, fref) <= tol, k  # forces: atomic sums
+    perm2 = np.random.default_rng(2).permutation(N)
+    rc, e_p, f_p, _ = _compute(lib, m, frame0["pos"].reshape(N, 3)[perm2].ravel(), frame0["box"][0],
+                               shape.type_map[perm2])
+    assert rc == 0 and abs(e_p - e) <= tol * abs(e) * 10
+    assert rel_err(f_p, ref["force"].reshape(N, 3)[perm2].ravel()) <= tol
     # a second call with fewer atoms of another composition reuses the handle
     sub = np.concatenate([np.arange(0, 200), np.arange(256, 256 + 400)])
     rc2, e2, f2, _ = _compute(lib, m, frame0["pos"].reshape(N, 3)[sub].ravel(), frame0["box"][0],
