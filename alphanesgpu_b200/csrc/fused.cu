@@ -681,35 +681,35 @@ static RowSink row_sink(const stafb_model* m, void* rows, const int* tmap) {
   return sk;
 }
 
-template <class T, int AW, bool WG>
+template <class T, int AW, bool WG, bool WIDE>
 static int launch_mlp_fwd_t(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, T* acts, T* e_atom,
                             T* nd) {
   static size_t attr_dev[MAX_DEVICES] = {0};  // largest dynamic shared-memory size opted in for, per device
   size_t& attr = attr_dev[device_slot()];
   if (m->mlp_fwd_smem > 48 * 1024 && m->mlp_fwd_smem > attr) {
-    STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_fwd<T, AW, WG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_fwd<T, AW, WG, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)m->mlp_fwd_smem));
     attr = m->mlp_fwd_smem;
   }
-  STAFB_CUDA_OK(launch_chained(k_mlp_fwd<T, AW, WG>, species_blocks(m->md, nf, ML_WARPS * AW), ML_THREADS,
+  STAFB_CUDA_OK(launch_chained(k_mlp_fwd<T, AW, WG, WIDE>, species_blocks(m->md, nf, ML_WARPS * AW), ML_THREADS,
                                m->mlp_fwd_smem, s, m->md, nf, theta, (const T*)m->wpack, m->wstride, af, acts, e_atom,
                                nd, m->stage, (int)mlp_stage_words(m->md, m->stage)));
   m->ctx->launches++;
   return STAFB_OK;
 }
 
-template <class T, int AW, bool WG>
+template <class T, int AW, bool WG, bool WIDE>
 static int launch_mlp_bwd_t(stafb_model* m, cudaStream_t s, int nf, const T* theta, const T* af, const T* acts,
                             const T* ebar, const T* u, T* gaf, T* grad) {
   static size_t attr_dev[MAX_DEVICES] = {0};
   size_t& attr = attr_dev[device_slot()];
   const T* vrow = (const T*)m->vrow;
   if (m->mlp_bwd_smem > 48 * 1024 && m->mlp_bwd_smem > attr) {
-    STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_bwd<T, AW, WG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    STAFB_CUDA_OK(cudaFuncSetAttribute(k_mlp_bwd<T, AW, WG, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)m->mlp_bwd_smem));
     attr = m->mlp_bwd_smem;
   }
-  STAFB_CUDA_OK(launch_chained(k_mlp_bwd<T, AW, WG>, species_blocks(m->md, nf, ML_WARPS * AW), ML_THREADS,
+  STAFB_CUDA_OK(launch_chained(k_mlp_bwd<T, AW, WG, WIDE>, species_blocks(m->md, nf, ML_WARPS * AW), ML_THREADS,
                                m->mlp_bwd_smem, s, m->md, nf, theta, (const T*)m->wpack, m->wstride, af, acts, ebar, u,
                                vrow, m->nv, gaf, grad, m->stage, (int)mlp_stage_words(m->md, m->stage)));
   m->ctx->launches++;
@@ -753,14 +753,14 @@ static int launch_mlp_fwd(stafb_model* m, cudaStream_t s, int nf, const T* theta
   if constexpr (std::is_same<T, float>::value) {
     if (m->mma) return launch_mlp_fwd_mma(m, s, nf, theta, af, acts, e_atom, nd);
   }
-  const bool wg = m->stage == 0;
+  const bool wg = m->stage == 0, wide = m->md.maxw > 64;  // the dense products' form: see mlp.cuh
   switch (m->aw) {
-    case 4: return wg ? launch_mlp_fwd_t<T, 4, true>(m, s, nf, theta, af, acts, e_atom, nd)
-                      : launch_mlp_fwd_t<T, 4, false>(m, s, nf, theta, af, acts, e_atom, nd);
-    case 2: return wg ? launch_mlp_fwd_t<T, 2, true>(m, s, nf, theta, af, acts, e_atom, nd)
-                      : launch_mlp_fwd_t<T, 2, false>(m, s, nf, theta, af, acts, e_atom, nd);
-    default: return wg ? launch_mlp_fwd_t<T, 1, true>(m, s, nf, theta, af, acts, e_atom, nd)
-                       : launch_mlp_fwd_t<T, 1, false>(m, s, nf, theta, af, acts, e_atom, nd);
+    case 4: return wg ? (wide ? launch_mlp_fwd_t<T, 4, true, true>(m, s, nf, theta, af, acts, e_atom, nd) : launch_mlp_fwd_t<T, 4, true, false>(m, s, nf, theta, af, acts, e_atom, nd))
+                      : (wide ? launch_mlp_fwd_t<T, 4, false, true>(m, s, nf, theta, af, acts, e_atom, nd) : launch_mlp_fwd_t<T, 4, false, false>(m, s, nf, theta, af, acts, e_atom, nd));
+    case 2: return wg ? (wide ? launch_mlp_fwd_t<T, 2, true, true>(m, s, nf, theta, af, acts, e_atom, nd) : launch_mlp_fwd_t<T, 2, true, false>(m, s, nf, theta, af, acts, e_atom, nd))
+                      : (wide ? launch_mlp_fwd_t<T, 2, false, true>(m, s, nf, theta, af, acts, e_atom, nd) : launch_mlp_fwd_t<T, 2, false, false>(m, s, nf, theta, af, acts, e_atom, nd));
+    default: return wg ? (wide ? launch_mlp_fwd_t<T, 1, true, true>(m, s, nf, theta, af, acts, e_atom, nd) : launch_mlp_fwd_t<T, 1, true, false>(m, s, nf, theta, af, acts, e_atom, nd))
+                       : (wide ? launch_mlp_fwd_t<T, 1, false, true>(m, s, nf, theta, af, acts, e_atom, nd) : launch_mlp_fwd_t<T, 1, false, false>(m, s, nf, theta, af, acts, e_atom, nd));
   }
 }
 
@@ -770,14 +770,14 @@ static int launch_mlp_bwd(stafb_model* m, cudaStream_t s, int nf, const T* theta
   if constexpr (std::is_same<T, float>::value) {
     if (m->mma) return launch_mlp_bwd_mma(m, s, nf, theta, af, acts, ebar, u, gaf, grad);
   }
-  const bool wg = m->stage == 0;
+  const bool wg = m->stage == 0, wide = m->md.maxw > 64;  // the dense products' form: see mlp.cuh
   switch (m->aw) {
-    case 4: return wg ? launch_mlp_bwd_t<T, 4, true>(m, s, nf, theta, af, acts, ebar, u, gaf, grad)
-                      : launch_mlp_bwd_t<T, 4, false>(m, s, nf, theta, af, acts, ebar, u, gaf, grad);
-    case 2: return wg ? launch_mlp_bwd_t<T, 2, true>(m, s, nf, theta, af, acts, ebar, u, gaf, grad)
-                      : launch_mlp_bwd_t<T, 2, false>(m, s, nf, theta, af, acts, ebar, u, gaf, grad);
-    default: return wg ? launch_mlp_bwd_t<T, 1, true>(m, s, nf, theta, af, acts, ebar, u, gaf, grad)
-                       : launch_mlp_bwd_t<T, 1, false>(m, s, nf, theta, af, acts, ebar, u, gaf, grad);
+    case 4: return wg ? (wide ? launch_mlp_bwd_t<T, 4, true, true>(m, s, nf, theta, af, acts, ebar, u, gaf, grad) : launch_mlp_bwd_t<T, 4, true, false>(m, s, nf, theta, af, acts, ebar, u, gaf, grad))
+                      : (wide ? launch_mlp_bwd_t<T, 4, false, true>(m, s, nf, theta, af, acts, ebar, u, gaf, grad) : launch_mlp_bwd_t<T, 4, false, false>(m, s, nf, theta, af, acts, ebar, u, gaf, grad));
+    case 2: return wg ? (wide ? launch_mlp_bwd_t<T, 2, true, true>(m, s, nf, theta, af, acts, ebar, u, gaf, grad) : launch_mlp_bwd_t<T, 2, true, false>(m, s, nf, theta, af, acts, ebar, u, gaf, grad))
+                      : (wide ? launch_mlp_bwd_t<T, 2, false, true>(m, s, nf, theta, af, acts, ebar, u, gaf, grad) : launch_mlp_bwd_t<T, 2, false, false>(m, s, nf, theta, af, acts, ebar, u, gaf, grad));
+    default: return wg ? (wide ? launch_mlp_bwd_t<T, 1, true, true>(m, s, nf, theta, af, acts, ebar, u, gaf, grad) : launch_mlp_bwd_t<T, 1, true, false>(m, s, nf, theta, af, acts, ebar, u, gaf, grad))
+                       : (wide ? launch_mlp_bwd_t<T, 1, false, true>(m, s, nf, theta, af, acts, ebar, u, gaf, grad) : launch_mlp_bwd_t<T, 1, false, false>(m, s, nf, theta, af, acts, ebar, u, gaf, grad));
   }
 }
 

@@ -141,10 +141,11 @@ __device__ __forceinline__ void ml_add4(double* p, double a, double b, double c,
   atomicAdd(p, a); atomicAdd(p + 1, b); atomicAdd(p + 2, c); atomicAdd(p + 3, d);
 }
 
+// ---- dense products, two forms.  Narrow layers (at most 64 wide): two output columns or one weight row per lane.
 // Y[j][a] = act( b[j] + sum_i X[i][a] W[i,j] ), one warp, AW atoms; a lane owns outputs j0+lane and j0+32+lane
 // of every group of 64.  The caller separates this from the producer of X with __syncwarp().
 template <class T, int AW, bool TANH, bool BIAS>
-__device__ __forceinline__ void warp_dense_fwd(int in, int out, const LayerView<T> lv, const T* __restrict__ X,
+__device__ __forceinline__ void warp_dense_fwd_narrow(int in, int out, const LayerView<T> lv, const T* __restrict__ X,
                                                T* __restrict__ Y, int lane) {
   const int ld = lv.ld;
   for (int j0 = 0; j0 < out; j0 += 64) {
@@ -194,7 +195,7 @@ __device__ __forceinline__ void warp_dense_fwd(int in, int out, const LayerView<
 // a lane owns input i0+lane of every group of 32 and walks its weight row four columns at a time (pointers that
 // advance by constants; summation order j = 0, 1, 2, ...).
 template <class T, int AW, bool TWO>
-__device__ __forceinline__ void warp_dense_bwd(int in, int out, const LayerView<T> lv, const T* __restrict__ D,
+__device__ __forceinline__ void warp_dense_bwd_narrow(int in, int out, const LayerView<T> lv, const T* __restrict__ D,
                                                T* __restrict__ Xo, const T* __restrict__ D2, T* __restrict__ Xo2,
                                                int lane) {
   const int ld = lv.ld;
@@ -244,6 +245,165 @@ __device__ __forceinline__ void warp_dense_bwd(int in, int out, const LayerView<
   }
 }
 
+// ---- wide layers: up to four output columns or two weight rows per lane
+// NG output columns per lane (j, j+32, ...): acc[g][a] += sum_i X[i][a] W[i, j + 32 g].  One broadcast row load of X
+// serves NG * AW multiply-adds and the NG sums are independent chains.
+template <class T, int AW, int NG>
+__device__ __forceinline__ void ml_fwd_cols(int in, int ld, const T* __restrict__ w0, const T* __restrict__ w1,
+                                            const T* __restrict__ w2, const T* __restrict__ w3,
+                                            const T* __restrict__ X, T (&acc)[4][AW]) {
+#pragma unroll 4
+  for (int i = 0; i < in; i++) {
+    T x[AW];
+    RowIO<T, AW>::ld(X + i * AW, x);
+    const T v0 = w0[i * ld], v1 = NG > 1 ? w1[i * ld] : T(0), v2 = NG > 2 ? w2[i * ld] : T(0),
+            v3 = NG > 3 ? w3[i * ld] : T(0);
+#pragma unroll
+    for (int a = 0; a < AW; a++) {
+      acc[0][a] += v0 * x[a];
+      if (NG > 1) acc[1][a] += v1 * x[a];
+      if (NG > 2) acc[2][a] += v2 * x[a];
+      if (NG > 3) acc[3][a] += v3 * x[a];
+    }
+  }
+}
+
+// Y[j][a] = act( b[j] + sum_i X[i][a] W[i,j] ), one warp, AW atoms; a lane owns outputs j0+lane, j0+32+lane, ... of
+// every group of 128 (as many of the four as the layer has).  The caller separates this from the producer of X
+// with __syncwarp().
+template <class T, int AW, bool TANH, bool BIAS>
+__device__ __forceinline__ void warp_dense_fwd_wide(int in, int out, const LayerView<T> lv, const T* __restrict__ X,
+                                               T* __restrict__ Y, int lane) {
+  const int ld = lv.ld;
+  for (int j0 = 0; j0 < out; j0 += 128) {
+    const int ng = (out - j0 + 31) >> 5;  // 32-column groups left; warp-uniform
+    // a lane past the last output reads the last column and drops the result
+    T acc[4][AW];
+#pragma unroll
+    for (int g = 0; g < 4; g++)
+#pragma unroll
+      for (int a = 0; a < AW; a++) acc[g][a] = T(0);
+    const int last = out - 1, jl = j0 + lane;
+    const T* w0 = lv.W + (jl < out ? jl : last);
+    const T* w1 = lv.W + (jl + 32 < out ? jl + 32 : last);
+    const T* w2 = lv.W + (jl + 64 < out ? jl + 64 : last);
+    const T* w3 = lv.W + (jl + 96 < out ? jl + 96 : last);
+    if (ng >= 4) ml_fwd_cols<T, AW, 4>(in, ld, w0, w1, w2, w3, X, acc);
+    else if (ng == 3) ml_fwd_cols<T, AW, 3>(in, ld, w0, w1, w2, w3, X, acc);
+    else if (ng == 2) ml_fwd_cols<T, AW, 2>(in, ld, w0, w1, w2, w3, X, acc);
+    else ml_fwd_cols<T, AW, 1>(in, ld, w0, w1, w2, w3, X, acc);
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+      const int j = j0 + 32 * g + lane;
+      if (g < ng && j < out) {
+        const T b = BIAS ? lv.B[j] : T(0);
+#pragma unroll
+        for (int a = 0; a < AW; a++) { acc[g][a] += b; if (TANH) acc[g][a] = ml_tanh(acc[g][a]); }
+        RowIO<T, AW>::st(Y + j * AW, acc[g]);
+      }
+    }
+  }
+}
+
+// NR weight rows per lane (i, i+32): acc[r][a] += sum_j D[j][a] W[i + 32 r, j] (and acc2 with D2 when TWO), four
+// columns per trip, pointers that advance by constants; summation order j = 0, 1, 2, ...  The D rows are loaded
+// once for both weight rows.
+template <class T, int AW, bool TWO, int NR>
+__device__ __forceinline__ void ml_bwd_rows(int out, const T* __restrict__ wr0, const T* __restrict__ wr1,
+                                            const T* __restrict__ D, const T* __restrict__ D2, T (&acc)[2][AW],
+                                            T (&acc2)[2][AW]) {
+  const T* pd = D;
+  const T* pd2 = TWO ? D2 : D;
+#pragma unroll 2
+  for (int n = out >> 2; n > 0; n--) {
+    T w[2][4];
+    ml_ld4(wr0, w[0]);
+    if (NR == 2) ml_ld4(wr1, w[1]);
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+      T d[AW];
+      RowIO<T, AW>::ld(pd + r * AW, d);
+#pragma unroll
+      for (int q = 0; q < NR; q++)
+#pragma unroll
+        for (int a = 0; a < AW; a++) acc[q][a] += w[q][r] * d[a];
+      if (TWO) {
+        RowIO<T, AW>::ld(pd2 + r * AW, d);
+#pragma unroll
+        for (int q = 0; q < NR; q++)
+#pragma unroll
+          for (int a = 0; a < AW; a++) acc2[q][a] += w[q][r] * d[a];
+      }
+    }
+    wr0 += 4; wr1 += 4; pd += 4 * AW; pd2 += 4 * AW;
+  }
+  for (int n = out & 3; n > 0; n--) {
+    T w[2];
+    w[0] = wr0[0];
+    w[1] = NR == 2 ? wr1[0] : T(0);
+    T d[AW];
+    RowIO<T, AW>::ld(pd, d);
+#pragma unroll
+    for (int q = 0; q < NR; q++)
+#pragma unroll
+      for (int a = 0; a < AW; a++) acc[q][a] += w[q] * d[a];
+    if (TWO) {
+      RowIO<T, AW>::ld(pd2, d);
+#pragma unroll
+      for (int q = 0; q < NR; q++)
+#pragma unroll
+        for (int a = 0; a < AW; a++) acc2[q][a] += w[q] * d[a];
+    }
+    wr0++; wr1++; pd += AW; pd2 += AW;
+  }
+}
+
+// Xo[i][a] = sum_j D[j][a] W[i,j]  (and the same for a second cotangent D2 -> Xo2 when TWO), one warp, AW atoms;
+// a lane owns inputs i0+lane and i0+32+lane of every group of 64 and walks their weight rows four columns at a time.
+template <class T, int AW, bool TWO>
+__device__ __forceinline__ void warp_dense_bwd_wide(int in, int out, const LayerView<T> lv, const T* __restrict__ D,
+                                               T* __restrict__ Xo, const T* __restrict__ D2, T* __restrict__ Xo2,
+                                               int lane) {
+  const int ld = lv.ld;
+  for (int i0 = 0; i0 < in; i0 += 64) {
+    const int ia = i0 + lane, ib = ia + 32;
+    const bool two = i0 + 32 < in;  // warp-uniform
+    // a lane past the last input repeats the last row and drops the result
+    const T* wra = lv.W + (size_t)(ia < in ? ia : in - 1) * ld;
+    const T* wrb = lv.W + (size_t)(ib < in ? ib : in - 1) * ld;
+    T acc[2][AW], acc2[2][AW];
+#pragma unroll
+    for (int a = 0; a < AW; a++) acc[0][a] = acc[1][a] = acc2[0][a] = acc2[1][a] = T(0);
+    if (two) ml_bwd_rows<T, AW, TWO, 2>(out, wra, wrb, D, D2, acc, acc2);
+    else ml_bwd_rows<T, AW, TWO, 1>(out, wra, wrb, D, D2, acc, acc2);
+    if (ia < in) {
+      RowIO<T, AW>::st(Xo + ia * AW, acc[0]);
+      if (TWO) RowIO<T, AW>::st(Xo2 + ia * AW, acc2[0]);
+    }
+    if (two && ib < in) {
+      RowIO<T, AW>::st(Xo + ib * AW, acc[1]);
+      if (TWO) RowIO<T, AW>::st(Xo2 + ib * AW, acc2[1]);
+    }
+  }
+}
+
+// The form is a template parameter of the kernels, chosen per model by the widest layer: the wide form shares every
+// operand load between more multiply-adds and keeps more independent sums in flight, which pays for 140-wide layers
+// (-9 % / -5 % on the 60-140-140-1 kernels) and costs about a microsecond on 64-wide ones.
+template <class T, int AW, bool TANH, bool BIAS, bool WIDE>
+__device__ __forceinline__ void warp_dense_fwd(int in, int out, const LayerView<T> lv, const T* __restrict__ X,
+                                               T* __restrict__ Y, int lane) {
+  if (WIDE) warp_dense_fwd_wide<T, AW, TANH, BIAS>(in, out, lv, X, Y, lane);
+  else warp_dense_fwd_narrow<T, AW, TANH, BIAS>(in, out, lv, X, Y, lane);
+}
+template <class T, int AW, bool TWO, bool WIDE>
+__device__ __forceinline__ void warp_dense_bwd(int in, int out, const LayerView<T> lv, const T* __restrict__ D,
+                                               T* __restrict__ Xo, const T* __restrict__ D2, T* __restrict__ Xo2,
+                                               int lane) {
+  if (WIDE) warp_dense_bwd_wide<T, AW, TWO>(in, out, lv, D, Xo, D2, Xo2, lane);
+  else warp_dense_bwd_narrow<T, AW, TWO>(in, out, lv, D, Xo, D2, Xo2, lane);
+}
+
 // global row of atom slot a of this block (species t, first species-local index q0), or -1 past the end
 __device__ __forceinline__ long long ml_atom_row(const ModelDev& md, int t, int q0, int nat, int a) {
   const int q = q0 + a;
@@ -262,7 +422,7 @@ __host__ __device__ inline size_t ml_bwd_words(int Fm, int Hs, int mw, int AW) {
 
 // Forward: e_i, the activations for the backward kernel and netderiv = d(sum e)/dAF.
 // acts: [block][warp][Hs][AW], the warps' activation slices as they are.
-template <class T, int AW, bool WG>
+template <class T, int AW, bool WG, bool WIDE>
 __global__ void __launch_bounds__(ML_THREADS)
     k_mlp_fwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ wpack, int wstride,
               const T* __restrict__ af, T* __restrict__ acts, T* __restrict__ e_atom, T* __restrict__ netderiv,
@@ -306,8 +466,8 @@ __global__ void __launch_bounds__(ML_THREADS)
     lv = get_layer<T, WG>(md, t, l, w, wsm, stage);
     __syncwarp();
     T* hout = H + md.h_off(l) * AW;
-    if (l < Lq - 1) warp_dense_fwd<T, AW, true, true>(in, out, lv, hin, hout, lane);
-    else warp_dense_fwd<T, AW, false, true>(in, out, lv, hin, hout, lane);
+    if (l < Lq - 1) warp_dense_fwd<T, AW, true, true, WIDE>(in, out, lv, hin, hout, lane);
+    else warp_dense_fwd<T, AW, false, true, WIDE>(in, out, lv, hin, hout, lane);
     hin = hout;
   }
   __syncwarp();
@@ -334,7 +494,7 @@ __global__ void __launch_bounds__(ML_THREADS)
       for (int idx = lane; idx < out * AW; idx += 32) cn[idx] *= (T(1) - hl[idx] * hl[idx]);
       __syncwarp();
     }
-    warp_dense_bwd<T, AW, false>(in, out, lv, cn, cp, nullptr, nullptr, lane);
+    warp_dense_bwd<T, AW, false, WIDE>(in, out, lv, cn, cp, nullptr, nullptr, lane);
     T* tmp = cn; cn = cp; cp = tmp;
   }
   __syncwarp();
@@ -353,7 +513,7 @@ __global__ void __launch_bounds__(ML_THREADS)
 // The kernel also contracts dL/dAF with the per-atom d(AF)/d(alpha) rows left by the AF sweep
 // (vrow), which yields the fingerprint part of dL/dalpha without another sweep over the triplets.
 // fp32 with up to 2 atoms per warp: three blocks per SM fit by shared memory, so the registers are capped for three
-template <class T, int AW, bool WG>
+template <class T, int AW, bool WG, bool WIDE>
 __global__ void __launch_bounds__(ML_THREADS, (sizeof(T) == 4 && AW <= 2) ? 3 : 1)
     k_mlp_bwd(ModelDev md, int nf, const T* __restrict__ theta, const T* __restrict__ wpack, int wstride,
               const T* __restrict__ af, const T* __restrict__ acts, const T* __restrict__ ebar /*[nf]*/, const T* __restrict__ u /*[nf,N,Fmax]*/,
@@ -429,7 +589,7 @@ __global__ void __launch_bounds__(ML_THREADS, (sizeof(T) == 4 && AW <= 2) ? 3 : 
     __syncwarp();
     T* ado = AD + md.h_off(l) * AW;
     T* hdo = HD + md.h_off(l) * AW;
-    warp_dense_fwd<T, AW, false, false>(in, out, lv, hdin, ado, lane);
+    warp_dense_fwd<T, AW, false, false, WIDE>(in, out, lv, hdin, ado, lane);
     __syncwarp();
     const T* ho = H + md.h_off(l) * AW;
     for (int idx = lane; idx < out * AW; idx += 32)
@@ -473,7 +633,7 @@ __global__ void __launch_bounds__(ML_THREADS, (sizeof(T) == 4 && AW <= 2) ? 3 : 
       dpl[idx] = pa;
     }
     __syncwarp();
-    warp_dense_bwd<T, AW, true>(in, out, lv, dql, CQn, dpl, CPn, lane);
+    warp_dense_bwd<T, AW, true, WIDE>(in, out, lv, dql, CQn, dpl, CPn, lane);
     T* tq = CQ; CQ = CQn; CQn = tq;
     T* tp = CP; CP = CPn; CPn = tp;
   }
